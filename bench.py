@@ -1,0 +1,538 @@
+#!/usr/bin/env python
+"""Benchmark of the TurboQuant hot path on B200 ("Measurement").
+
+Headline workload (BASELINE config 0): TQ8 fused dequant-GEMV, weight 4096x4096 drawn
+N(0, 0.02^2) in fp16, row-normalised, blocked WHT (block 128) after a seeded sign
+diagonal, 4-bit Lloyd-Max primary + 4-bit Lloyd-Max residual codebooks fitted to the
+data, batch-1 fp16 activation ~ N(0,1).  A step is one pass over NBUF distinct weight
+matrices (NBUF * 16.8 MB >> L2), one GEMV each, so every launch streams its codes from
+HBM.  metric = layer-forwards ("tokens" through this layer) per second.
+
+  python bench.py [--gpus N] [--steps K] [--warmup W]          the CUDA library
+  python bench.py --impl reference [...]                       the reference's CPU path
+
+Prints ONE JSON line (rank 0).  With N > 1 (torchrun, one rank per GPU) every rank runs
+its own NBUF matrices (independent layers, no collective on this path: weak scaling);
+the row-sharded LM head with its NCCL all-gather is reported under "lm_head".
+"""
+from __future__ import annotations
+
+import argparse
+import ctypes as C
+import json
+import os
+import statistics
+import subprocess
+import sys
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+OUT_F, IN_F, BLOCK = 4096, 4096, 128
+ALGO_BYTES = OUT_F * IN_F + 4 * OUT_F + 2 * IN_F + 2 * OUT_F   # codes + norms + x + y = 16 809 984
+PUBLISHED_TOK_S = 671.0   # reference README: 1.49 ms/token, Apple GPU, same shape, block 512
+# dram__bytes_read.sum + dram__bytes_write.sum of one tq8_gemv_kernel launch at this shape
+# (ncu capture summarised in profiles/); None until a capture exists.
+GEMV_DRAM_TRAFFIC = None
+
+
+def measured_peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return float(d["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+# ---- clocks --------------------------------------------------------------------------------
+
+class ClockSampler:
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.proc = None
+        self.gpu = gpu_index
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.gpu), "--query-gpu=" + self.Q,
+                                          "--format=csv,noheader,nounits", "-lms", "50"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+
+    def stop(self):
+        if not self.proc:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            out, _ = self.proc.communicate(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+            out, _ = self.proc.communicate()
+        sm, mx, reasons = [], [], set()
+        for line in out.strip().splitlines():
+            f = [x.strip() for x in line.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1]))
+                mx.append(float(f[2]))
+            except ValueError:
+                continue
+            for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+# ---- synthetic inputs ------------------------------------------------------------------------
+
+def fit_codebook_torch(data, init, iterations=100):
+    """Lloyd-Max on the device (input preparation only): bin by midpoints, ties to the lower
+    bin, float64 bin means, stop when no centroid moves by 1e-6 — the reference's rule
+    (src/codebook.cpp:99-143)."""
+    import torch
+    c = torch.tensor(init, dtype=torch.float32, device=data.device)
+    flat = data.reshape(-1)
+    flat64 = flat.double()
+    for _ in range(iterations):
+        b = (c[:-1] + c[1:]) * 0.5
+        idx = torch.bucketize(flat, b, right=False)
+        sums = torch.zeros(c.numel(), dtype=torch.float64, device=data.device).index_add_(0, idx, flat64)
+        cnt = torch.bincount(idx, minlength=c.numel()).double()
+        new = torch.where(cnt > 0, (sums / cnt.clamp(min=1)).float(), c)
+        shift = (new - c).abs().max().item()
+        c = new
+        if shift < 1e-6:
+            break
+    return c.cpu().numpy().astype(np.float32)
+
+
+def build_codebooks(tq, w0):
+    """Per-layer codebooks as the reference's converter fits them (src/converter.cpp:291-372):
+    primary on the rotated, scaled weights; residual on what the primary leaves."""
+    import torch
+    out_f, in_f = w0.shape
+    analytic = tq.generate_codebook(4)
+    qw = tq.quantize_weight(w0, analytic, analytic, tq.QuantizerConfig(4, 4, BLOCK, True))
+    seed = int(qw.seeds[0])
+    nrm = torch.linalg.vector_norm(w0, dim=1, keepdim=True).clamp(min=1e-10)
+    rot = tq.apply_wht_rotation((w0 / nrm).contiguous(), seed, BLOCK)
+    torch.cuda.synchronize()
+    rot = rot * float(np.sqrt(np.float32(in_f)))
+    cp = fit_codebook_torch(rot, analytic.centroids)
+    cpt = torch.tensor(cp, device=rot.device)
+    idx = torch.bucketize(rot.reshape(-1), (cpt[:-1] + cpt[1:]) * 0.5, right=False)
+    res = rot.reshape(-1) - cpt[idx]
+    cr = fit_codebook_torch(res, analytic.centroids)
+    return tq.codebook_from_centroids(cp), tq.codebook_from_centroids(cr)
+
+
+def make_layer(tq, seed, device, cbs=None, out_f=OUT_F, in_f=IN_F):
+    import torch
+    g = torch.Generator(device=device).manual_seed(seed)
+    w = (torch.randn((out_f, in_f), generator=g, device=device, dtype=torch.float32) * 0.02).half().float()
+    if cbs is None:
+        cbs = build_codebooks(tq, w)
+    qw = tq.quantize_weight(w, cbs[0], cbs[1], tq.QuantizerConfig(4, 4, BLOCK, True))
+    lin = tq.TurboQuantLinear(in_f, out_f, qw, cbs[0], cbs[1], BLOCK)
+    return lin, qw, cbs
+
+
+# ---- the CUDA arm ------------------------------------------------------------------------------
+
+def run_cuda(args):
+    import torch
+    import torch.distributed as dist
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if world != args.gpus:
+        if world == 1 and args.gpus > 1:
+            raise SystemExit("--gpus N > 1 must be launched with torch.distributed.run (one rank per GPU)")
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=device)
+
+    import turboquant_mlx_core_b200 as tq
+    L = tq.load()
+    if L.tq_set_device(local_rank) != 0:
+        raise SystemExit("tq_set_device failed: " + L.tq_last_error().decode())
+
+    nbuf = args.nbuf
+    layers = []
+    lin0, qw0, cbs = make_layer(tq, 1000 * rank, device)
+    layers.append(lin0)
+    for i in range(1, nbuf):
+        layers.append(make_layer(tq, 1000 * rank + i, device, cbs)[0])
+    g = torch.Generator(device=device).manual_seed(7 + rank)
+    x_dev = torch.randn((nbuf, IN_F), generator=g, device=device, dtype=torch.float32).half()
+    y_dev = torch.empty((nbuf, OUT_F), device=device, dtype=torch.float16)
+    x_host = x_dev.cpu().pin_memory()
+    y_host = torch.empty((nbuf, OUT_F), dtype=torch.float16).pin_memory()
+
+    stream = torch.cuda.Stream(device=device)
+    sp = C.c_void_p(stream.cuda_stream)
+
+    def one_pass():
+        for i, lin in enumerate(layers):
+            rc = L.tq_linear_forward(lin.handle, C.c_void_p(x_dev[i].data_ptr()), tq.TQ_F16, 1,
+                                     C.c_void_p(y_dev[i].data_ptr()), sp)
+            if rc:
+                raise RuntimeError(L.tq_last_error().decode())
+
+    # the launch-bound inner loop is captured once and replayed
+    with torch.cuda.stream(stream):
+        one_pass()
+    stream.synchronize()
+    launch_mode = "CUDA graph of one GEMV per layer"
+    try:
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=stream):
+            one_pass()
+    except Exception as exc:  # capture refused: time plain launches and say so
+        launch_mode = f"plain launches (graph capture failed: {type(exc).__name__})"
+        torch.cuda.synchronize()
+
+        class _Plain:
+            @staticmethod
+            def replay():
+                one_pass()
+        graph = _Plain()
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    sampler = ClockSampler(local_rank)
+    with torch.cuda.stream(stream):
+        for _ in range(args.warmup):
+            graph.replay()
+    barrier()
+    if rank == 0:
+        sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    with torch.cuda.stream(stream):
+        e0.record(stream)
+        for _ in range(args.steps):
+            graph.replay()
+        e1.record(stream)
+    barrier()
+    ms = e0.elapsed_time(e1)
+    clocks = sampler.stop() if rank == 0 else None
+    t = torch.tensor([ms], device=device, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms_max = float(t.item())
+    launches = args.steps * nbuf
+    value = world * launches / (ms_max * 1e-3)
+
+    # ---- end to end through the C-ABI with host buffers ----
+    e2e_steps = max(3, args.steps // 20)
+
+    def e2e_pass():
+        for i, lin in enumerate(layers):
+            rc = L.tq_linear_forward(lin.handle, C.c_void_p(x_host[i].data_ptr()), tq.TQ_F16, 1,
+                                     C.c_void_p(y_host[i].data_ptr()), sp)
+            if rc:
+                raise RuntimeError(L.tq_last_error().decode())
+
+    for _ in range(3):
+        e2e_pass()
+    barrier()
+    f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    f0.record(stream)
+    for _ in range(e2e_steps):
+        e2e_pass()
+    f1.record(stream)
+    barrier()
+    e2e_ms = torch.tensor([f0.elapsed_time(f1)], device=device, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(e2e_ms, op=dist.ReduceOp.MAX)
+    e2e_value = world * e2e_steps * nbuf / (float(e2e_ms.item()) * 1e-3)
+
+    # parity guard on what was timed: the device and host paths must agree bit for bit
+    torch.cuda.synchronize()
+    same = bool(torch.equal(y_dev.cpu(), y_host))
+
+    peak, peak_kind = measured_peaks()
+    per_launch_s = ms_max * 1e-3 / launches
+    achieved = ALGO_BYTES / per_launch_s / 1e9
+    line = {
+        "metric": "tq8_dequant_gemv_4096x4096_b1_tok_per_s", "value": value, "unit": "tok/s",
+        "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_max / args.steps,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": value / world / PUBLISHED_TOK_S if world == 1 else None,
+        "dtype": "tf32 multiply, fp32 accumulate (fp16 activations in, fp16 out)", "data": "synthetic",
+        "config": {"workload": "BASELINE config 0: TQ8 4+4-bit fused dequant-GEMV, 4096x4096, block 128, shared rotation, "
+                               "fitted Lloyd-Max codebooks, batch 1",
+                   "layers_per_step": nbuf, "l2_policy": f"{nbuf} distinct weight matrices per step "
+                                                         f"({nbuf * OUT_F * IN_F / 1e6:.0f} MB) > L2",
+                   "launch": launch_mode, "per_gpu": "independent layers, no collective",
+                   "vs_baseline_note": "published 671 tok/s is the reference on an Apple GPU at block 512"},
+        "gb_per_s": achieved * world,
+        "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                     "frac_of_nominal_8tbs": achieved / 8000.0, "peak_kind": peak_kind + " (burst copy)",
+                     "algorithmic_bytes_per_launch": ALGO_BYTES, "us_per_launch": per_launch_s * 1e6,
+                     "traffic": GEMV_DRAM_TRAFFIC},
+        "e2e": {"value": e2e_value, "unit": "tok/s", "h2d_bytes_per_step": nbuf * IN_F * 2,
+                "d2h_bytes_per_step": nbuf * OUT_F * 2, "steps": e2e_steps,
+                "path": "tq_linear_forward with pinned host x and y, one call per layer"},
+        "gpu_launches": launches,
+        "clocks": clocks,
+        "device_host_paths_bit_identical": same,
+    }
+
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        line["cpu_baseline"] = cpu_baseline(qw0, cbs, x_host[0].numpy(), y_dev[0].cpu().numpy(), budget_s=12.0)
+    if not args.no_extras:
+        try:
+            line["attention"] = bench_attention(tq, L, device, stream, rank, world, args)
+        except Exception as e:  # secondary measurement: report, do not hide the headline
+            line["attention"] = {"error": str(e)}
+        try:
+            line["lm_head"] = bench_lm_head(tq, L, device, stream, rank, world, cbs, args)
+        except Exception as e:
+            line["lm_head"] = {"error": str(e)}
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+    if rank == 0:
+        print(json.dumps(line))
+
+
+# ---- secondary: compressed-cache decode attention (BASELINE config 3) ---------------------------
+
+def bench_attention(tq, L, device, stream, rank, world, args):
+    """16 sequences, 4 KV / 28 query heads, d 128, ctx 32768, QJL on.  KV heads are split across
+    ranks when world <= 4 (heads are independent; outputs all-gathered by the caller)."""
+    import torch
+    n_seqs, kv_heads, q_heads, dim, ctx = 16, 4, 28, 128, args.attn_ctx
+    if world > kv_heads or kv_heads % world:
+        return {"skipped": f"{world} ranks over {kv_heads} KV heads needs a context split"}
+    heads_local = kv_heads // world
+    qh_local = q_heads // world
+    g = torch.Generator(device=device).manual_seed(100 + rank)
+    caches = []
+    for s in range(n_seqs):
+        c = tq.TQKVCache(1, heads_local, dim)
+        for t0 in range(0, ctx, 8192):
+            n = min(8192, ctx - t0)
+            k = torch.randn((n, heads_local, dim), generator=g, device=device)
+            v = torch.randn((n, heads_local, dim), generator=g, device=device)
+            k[:, :, ::20] *= 8.0          # ~5 % outlier channels
+            v[:, :, ::20] *= 8.0
+            c.append(0, k.half(), v.half())
+        caches.append(c)
+    q = torch.randn((n_seqs, qh_local, dim), generator=g, device=device).half()
+    out = torch.empty_like(q)
+    arr = (C.c_void_p * n_seqs)(*[c.handle for c in caches])
+    sp = C.c_void_p(stream.cuda_stream)
+
+    def call():
+        rc = L.tq_kv_attention(arr, n_seqs, 0, C.c_void_p(q.data_ptr()), tq.TQ_F16, qh_local,
+                               C.c_void_p(out.data_ptr()), 0, -1, 1, sp)
+        if rc:
+            raise RuntimeError(L.tq_last_error().decode())
+
+    with torch.cuda.stream(stream):
+        for _ in range(3):
+            call()
+    torch.cuda.synchronize()
+    reps = 10
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with torch.cuda.stream(stream):
+        e0.record(stream)
+        for _ in range(reps):
+            call()
+        e1.record(stream)
+    torch.cuda.synchronize()
+    us = e0.elapsed_time(e1) * 1e3 / reps
+    algo = n_seqs * heads_local * ctx * 118          # compact bytes per (token, KV head) with QJL
+    peak, kind = measured_peaks()
+    for c in caches:
+        c.close()
+    return {"workload": f"config 3: {n_seqs} seqs x ctx {ctx}, {kv_heads} KV / {q_heads} query heads, d {dim}, QJL on",
+            "us_per_layer_step": us, "tok_per_s": n_seqs / (us * 1e-6), "gb_per_s_per_gpu": algo / (us * 1e-6) / 1e9,
+            "frac_of_peak": algo / (us * 1e-6) / 1e9 / peak, "peak_kind": kind, "kv_heads_per_gpu": heads_local,
+            "l2_policy": f"cache {n_seqs * heads_local * ctx * 132 / 1e6:.0f} MB > L2"}
+
+
+# ---- secondary: row-sharded LM head (BASELINE config 2) -------------------------------------------
+
+def bench_lm_head(tq, L, device, stream, rank, world, cbs, args):
+    import torch
+    import torch.distributed as dist
+    from turboquant_mlx_core_b200.sharding import all_gather_rows, row_range
+    vocab, hidden = 151936, 2048
+    s, e = row_range(vocab, rank, world)
+    rows = e - s
+    g = torch.Generator(device=device).manual_seed(500 + rank)
+    w = (torch.randn((rows, hidden), generator=g, device=device) * 0.02).half().float()
+    qw = tq.quantize_weight(w, cbs[0], cbs[1], tq.QuantizerConfig(4, 4, BLOCK, True))
+    del w
+    lin = tq.TurboQuantLinear(hidden, rows, qw, cbs[0], cbs[1], BLOCK)
+    res = {}
+    sp = C.c_void_p(stream.cuda_stream)
+    for batch in (1, 32):
+        x = torch.randn((batch, hidden), generator=g, device=device).half()
+        y = torch.empty((batch, rows), device=device, dtype=torch.float16)
+
+        def call():
+            rc = L.tq_linear_forward(lin.handle, C.c_void_p(x.data_ptr()), tq.TQ_F16, batch, C.c_void_p(y.data_ptr()), sp)
+            if rc:
+                raise RuntimeError(L.tq_last_error().decode())
+            if world > 1:
+                return all_gather_rows(y, vocab, world)
+            return y
+
+        with torch.cuda.stream(stream):
+            for _ in range(3):
+                call()
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        reps = 20
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        with torch.cuda.stream(stream):
+            e0.record(stream)
+            for _ in range(reps):
+                call()
+            e1.record(stream)
+        torch.cuda.synchronize()
+        t = torch.tensor([e0.elapsed_time(e1) * 1e3 / reps], device=device, dtype=torch.float64)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        us = float(t.item())
+        algo = vocab * hidden + 4 * vocab + 2 * batch * hidden + 2 * batch * vocab
+        res[f"b{batch}"] = {"us": us, "tok_per_s": batch / (us * 1e-6), "gb_per_s_aggregate": algo / (us * 1e-6) / 1e9}
+    lin.close()
+    res["workload"] = f"config 2: LM head {vocab}x{hidden}, rows sharded over {world} GPU(s), fp16 logits all-gather"
+    return res
+
+
+# ---- CPU legs ---------------------------------------------------------------------------------------
+
+def cpu_threads():
+    try:
+        return len(os.sched_getaffinity(0))
+    except AttributeError:
+        return os.cpu_count() or 1
+
+
+def cpu_linear_once(ref, ora, qw, cbs, x, threads):
+    """The reference's CPU linear: dequantize_weight_cpu, then an fp32 matmul over the
+    fp16-rounded activation (src/dequantizer.cpp:52-256, tests/integration/test_linear.cpp:98-107)."""
+    cp, cr = cbs[0].centroids, cbs[1].centroids
+    if ref is not None:
+        w = ref.dequantize_weight_mt(qw.packed_primary, qw.packed_residual, qw.norms, qw.seeds, cp, cr, BLOCK, threads)
+    else:
+        w = ora.dequantize_weight(qw.packed_primary, qw.packed_residual, qw.norms, qw.seeds, cp, cr, BLOCK)
+    xh = x.astype(np.float16).astype(np.float32)
+    return xh @ w.T
+
+
+def load_cpu_libs():
+    from oracle import build as obuild
+    from oracle.pyoracle import Oracle, Ref, have_ref
+    obuild.build_oracle()
+    ora = Oracle()
+    ref = Ref() if have_ref() else None
+    return ref, ora
+
+
+def cpu_baseline(qw, cbs, x, y_gpu, budget_s):
+    ref, ora = load_cpu_libs()
+    threads = cpu_threads() if ref is not None else 1
+    t0 = time.perf_counter()
+    y = cpu_linear_once(ref, ora, qw, cbs, x[None], threads)
+    first = time.perf_counter() - t0
+    n = max(1, min(20, int(budget_s / max(first, 1e-3)) - 1))
+    times = [first]
+    for _ in range(n):
+        t0 = time.perf_counter()
+        cpu_linear_once(ref, ora, qw, cbs, x[None], threads)
+        times.append(time.perf_counter() - t0)
+    med = statistics.median(times)
+    rel = float(np.linalg.norm(y_gpu.astype(np.float64) - y[0]) / np.linalg.norm(y[0]))
+    return {"value": 1.0 / med, "unit": "tok/s", "cores": threads, "kind": "reference" if ref is not None else "port",
+            "sample": f"{len(times)} forwards of one 4096x4096 layer (dequantize_weight_cpu + fp32 GEMV), median",
+            "gpu_vs_cpu_rel_l2": rel}
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    ref, ora = load_cpu_libs()
+    threads = cpu_threads() if ref is not None else 1
+    rng = np.random.default_rng(0)
+    w = (rng.standard_normal((OUT_F, IN_F)) * 0.02).astype(np.float16).astype(np.float32)
+    cb4 = ora.codebook(4)[0]
+    src = ref if ref is not None else ora
+    pp, pr, norms, seeds = src.quantize_weight(w, cb4, cb4, 4, 4, BLOCK, True)
+
+    class QW:
+        pass
+    qw = QW()
+    qw.packed_primary, qw.packed_residual, qw.norms, qw.seeds = pp, pr, norms, seeds
+
+    class CB:
+        def __init__(self, c):
+            self.centroids = c
+    cbs = (CB(cb4), CB(cb4))
+    x = rng.standard_normal((1, IN_F)).astype(np.float16).astype(np.float32)
+    for _ in range(args.warmup):
+        cpu_linear_once(ref, ora, qw, cbs, x, threads)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        cpu_linear_once(ref, ora, qw, cbs, x, threads)
+    dt = time.perf_counter() - t0
+    value = args.steps / dt
+    kind = "reference" if ref is not None else "port"
+    print(json.dumps({
+        "impl": "reference", "metric": "tq8_dequant_gemv_4096x4096_b1_tok_per_s", "value": value, "unit": "tok/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "fp32", "data": "synthetic",
+        "config": {"workload": "BASELINE config 0: TQ8 4+4-bit linear, 4096x4096, block 128, shared rotation, batch 1; "
+                               "each step = one layer forward on the host cores"},
+        "cpu_baseline": {"value": value, "unit": "tok/s", "cores": threads, "kind": kind,
+                         "sample": "one 4096x4096 layer forward per step: the reference's dequantize_weight_cpu "
+                                   "(row-sliced over all host threads) + fp32 GEMV"},
+        "e2e": {"value": value, "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=None)
+    ap.add_argument("--warmup", type=int, default=None)
+    ap.add_argument("--impl", default="cuda", choices=["cuda", "reference"])
+    ap.add_argument("--nbuf", type=int, default=64, help="distinct 4096x4096 layers per step")
+    ap.add_argument("--attn-ctx", type=int, default=32768)
+    ap.add_argument("--no-extras", action="store_true", help="skip the attention and LM-head measurements")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    a = ap.parse_args()
+    if a.impl == "reference":
+        a.steps = a.steps if a.steps is not None else 5
+        a.warmup = a.warmup if a.warmup is not None else 1
+        run_reference(a)
+    else:
+        a.steps = a.steps if a.steps is not None else 2000
+        a.warmup = max(3, a.warmup if a.warmup is not None else 50)
+        run_cuda(a)
+
+
+if __name__ == "__main__":
+    main()

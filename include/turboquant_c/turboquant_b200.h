@@ -1,0 +1,160 @@
+/*
+ * turboquant_b200.h — tensor-level C entry points of the B200 TurboQuant core.
+ *
+ * turboquant_c.h (next to this file) carries the reference project's C symbols
+ * unchanged in meaning.  That API passes tensors as opaque `void*` and has no
+ * tensor-level "linear forward / quantise / dequantise / rotate" calls: those live in
+ * the reference's C++ layer.  This header exposes exactly that layer over a plain C
+ * ABI — pointers and sizes only — so that a cgo / JNI / N-API / ctypes / Swift binding
+ * can reach the CUDA kernels.  Each declaration names the reference interface it stands
+ * in for (paths relative to the reference project root).
+ *
+ * Conventions
+ *   - Every data pointer may be a HOST pointer or a CUDA DEVICE pointer; the library
+ *     looks the pointer up and copies when needed.  Device pointers are used in place.
+ *   - `stream` is a cudaStream_t passed as void* (NULL = the default stream).  Work is
+ *     enqueued asynchronously; when an OUTPUT pointer is host memory the call waits
+ *     for the stream before returning so the bytes are valid.
+ *   - Functions returning int return 0 on success, non-zero on error; functions
+ *     returning a handle return NULL on error.  tq_last_error() then gives the reason
+ *     (thread-local string).  No C++ exception crosses this boundary.
+ *   - There is no CPU fallback: without a usable CUDA device every call fails.
+ */
+#ifndef TURBOQUANT_B200_H
+#define TURBOQUANT_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* dtype tags for activation / result buffers */
+enum { TQ_F32 = 0, TQ_F16 = 1, TQ_U8 = 2, TQ_U32 = 3 };
+
+/* ---- library / device -------------------------------------------------------- */
+
+/** Message of the last failed call on this thread ("" if none). */
+const char* tq_last_error(void);
+/** Number of CUDA devices visible; <= 0 means the library cannot run. */
+int tq_device_count(void);
+/** Select the device used by this thread for subsequent calls and new handles. */
+int tq_set_device(int device);
+
+/* ---- opaque tensor handle for the void* slots of turboquant_c.h ------------------
+ * The reference passes `mlx::core::array*` through those slots
+ * (src/turboquant_c.cpp:115-116, 127, 149).  Here the slot carries a tq_array: a
+ * device buffer with dtype and shape. */
+typedef struct tq_array_s* tq_array_t;
+
+/** Copy `data` (host or device) into a new device-resident array. */
+tq_array_t tq_array_create(const void* data, int dtype, int ndim, const int* shape);
+/** Wrap an existing device buffer without copying or taking ownership. */
+tq_array_t tq_array_wrap_device(void* device_ptr, int dtype, int ndim, const int* shape);
+int tq_array_ndim(tq_array_t a);
+int tq_array_dim(tq_array_t a, int axis);
+int tq_array_dtype(tq_array_t a);
+size_t tq_array_nbytes(tq_array_t a);
+/** Device pointer of the payload. */
+void* tq_array_data(tq_array_t a);
+/** Copy the payload to host memory (waits for pending work on the array). */
+int tq_array_to_host(tq_array_t a, void* dst, size_t dst_bytes);
+/* tq_array_free(void*) is declared in turboquant_c.h. */
+
+/* ---- codebooks: include/turboquant/codebook.h:25-46 ------------------------------ */
+
+/** generate_codebook (src/codebook.cpp:71-85): 2^bits centroids, 2^bits-1 boundaries. */
+int tq_codebook_generate(int bits, float* centroids, float* boundaries);
+
+/* ---- rotation: apply_wht_rotation / apply_inverse_wht_rotation
+ *      (include/turboquant/quantizer.h:29-39, src/rotation.cpp:364-403) --------------- */
+
+/** fp32 [rows, cols] -> fp32 [rows, cols]; cols % block == 0, block a power of two in
+ *  [32, 1024].  Bit-identical to the reference's CPU route. */
+int tq_wht_rotate(const float* in, float* out, int rows, int cols, uint32_t seed, uint32_t block, int inverse,
+                  void* stream);
+
+/* ---- weight quantiser: quantize_weight
+ *      (include/turboquant/quantizer.h:54-60, src/quantizer.cpp:41-261) -------------- */
+
+/** weight fp32 [out, in].  packed_primary u8 [out, in/2] (primary_bits <= 4) or
+ *  [out, in] (5); packed_residual u8 [out, in/2]; norms fp32 [out]; seeds u32[3] =
+ *  {seed_primary, seed_residual or 0, block}.  Codes, norms and seeds are bit-identical
+ *  to the reference's CPU path. */
+int tq_quantize_weight(const float* weight, int out_features, int in_features, const float* primary_centroids,
+                       int n_primary, const float* residual_centroids, int n_residual, int primary_bits,
+                       int residual_bits, uint32_t block, int shared_rotation, uint8_t* packed_primary,
+                       uint8_t* packed_residual, float* norms, uint32_t* seeds, void* stream);
+
+/* ---- TurboQuantLinear (include/turboquant/linear.h:11-35) and the dequantiser
+ *      (include/turboquant/dequantizer.h:11-39) ------------------------------------- */
+
+typedef struct tq_linear_s* tq_linear_t;
+
+/** Build a device-resident linear layer from a QuantizedWeight
+ *  (include/turboquant/quantizer.h:22-27) plus its two codebooks.
+ *  primary_cols is in/2 (4-bit primary) or in (5-bit primary); the residual plane is
+ *  always [out, in/2].  The packing mode, "residual present" and shared-vs-dual
+ *  rotation are detected exactly as src/dequantizer.cpp:72-74, 118-133 do — once, here,
+ *  not on every forward. */
+tq_linear_t tq_linear_create(int in_features, int out_features, const uint8_t* packed_primary, int primary_cols,
+                             const uint8_t* packed_residual, const float* norms, const uint32_t* seeds,
+                             const float* primary_centroids, int n_primary, const float* residual_centroids,
+                             int n_residual, uint32_t block);
+
+/** TurboQuantLinear::forward / fused_dequant_matmul (src/linear.cpp:20-26,
+ *  src/dequantizer.cpp:606-721): x [batch, in] of x_dtype (TQ_F32 or TQ_F16; cast to
+ *  fp16 first) -> y fp16 [batch, out], fp32 accumulation. */
+int tq_linear_forward(tq_linear_t lin, const void* x, int x_dtype, int batch, void* y_fp16, void* stream);
+
+/** dequantize_weight_cpu / dequantize_weight_gpu (src/dequantizer.cpp:52-256, 347-451):
+ *  result [out, in] as TQ_F32 (bit-identical to the reference's CPU result) or TQ_F16
+ *  (the same values rounded to nearest even, src/turboquant_c_dequant.cpp:156-167). */
+int tq_linear_dequantize(tq_linear_t lin, void* result, int result_dtype, void* stream);
+
+int tq_linear_in_features(tq_linear_t lin);
+int tq_linear_out_features(tq_linear_t lin);
+/** Safe to call with NULL. */
+void tq_linear_free(tq_linear_t lin);
+
+/* ---- compressed KV cache, pointer-level (handle type from turboquant_c.h) ------------
+ * The reference's tq_kv_cache_* calls take opaque arrays; these take plain pointers
+ * (host or device) and a stream, and add what a decode loop needs: a batched attention
+ * over several caches (one cache = one sequence, as in the reference) and an export of
+ * the raw compressed storage in the reference's layout. */
+#ifndef TURBOQUANT_C_H
+typedef struct tq_kv_cache_s* tq_kv_cache_t;
+#endif
+
+/** TQKVCache::append (src/kv_cache.cpp:16-61): keys/values [tokens, heads, head_dim] of
+ *  dtype TQ_F32 or TQ_F16.  3-bit codes, norms, QJL sign words and QJL norms are
+ *  bit-identical to the reference's encoder. */
+int tq_kv_append(tq_kv_cache_t cache, int layer, const void* keys, const void* values, int dtype, int tokens,
+                 void* stream);
+
+/** TQKVCache::get_keys_fp16 / get_values_fp16 (src/kv_cache.cpp:260-365): tokens
+ *  [start, end) as fp16 [end-start, heads, head_dim]; values != 0 selects V. */
+int tq_kv_get_fp16(tq_kv_cache_t cache, int layer, int values, int start, int end, void* out_fp16, void* stream);
+
+/** Raw storage of one layer, token-major as in include/turboquant/kv_cache.h:25-36:
+ *  code words [tokens*heads, ceil(d/10)], norms [tokens*heads], QJL words
+ *  [tokens*heads, ceil(d/32)], QJL norms [tokens*heads].  Any pointer may be NULL.
+ *  Returns the layer's token count, or -1. */
+int tq_kv_export(tq_kv_cache_t cache, int layer, uint32_t* k_words, uint32_t* v_words, float* k_norms,
+                 float* v_norms, uint32_t* qjl_words, float* qjl_norms);
+
+/** Decode attention for a batch of sequences: hybrid_attention's long-context branch
+ *  (src/attention_dispatch.cpp:58-73) computed directly on the compressed cache.
+ *  queries [n_seqs, q_heads, head_dim] (TQ_F32 / TQ_F16, rounded to fp16 first) ->
+ *  out fp16 [n_seqs, q_heads, head_dim]; tokens [start, end) of every cache, end < 0
+ *  meaning "all tokens of that cache"; q_heads a multiple of the cache's heads
+ *  (grouped-query attention).  use_qjl != 0 adds the 1-bit residual correction to the
+ *  key scores (an extension: the reference stores those bits but never reads them). */
+int tq_kv_attention(const tq_kv_cache_t* caches, int n_seqs, int layer, const void* queries, int q_dtype,
+                    int q_heads, void* out_fp16, int start, int end, int use_qjl, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* TURBOQUANT_B200_H */

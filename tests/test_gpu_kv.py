@@ -1,0 +1,129 @@
+"""GPU parity tests for the compressed KV cache: encoder bits, range decode, attention."""
+import ctypes as C
+
+import numpy as np
+import pytest
+
+from tests.conftest import rel_l2
+from tests.golden.make_golden import kv_inputs
+
+pytestmark = pytest.mark.gpu
+
+ATTN_TOL = 1e-3   # relative L2 against the oracle, as the task states
+
+KV_CASES = [("kv4x128", 2, 4, 128, 24, 5), ("kv2x32", 1, 2, 32, 40, 6), ("kv1x64", 1, 1, 64, 9, 8)]
+
+
+def bits_equal(a, b):
+    a, b = np.ascontiguousarray(a), np.ascontiguousarray(b)
+    return a.shape == b.shape and np.array_equal(a.view(np.uint8), b.view(np.uint8))
+
+
+@pytest.mark.parametrize("case", KV_CASES, ids=[c[0] for c in KV_CASES])
+@pytest.mark.parametrize("dtype", [np.float16, np.float32])
+def test_append_bits_and_decode(tq, golden, case, dtype):
+    name, layers, heads, dim, tokens, seed = case
+    lay = layers - 1
+    k, v = kv_inputs(seed, tokens, heads, dim)
+    cache = tq.TQKVCache(layers, heads, dim)
+    assert cache.seq_length() == 0
+    cache.append(lay, k[: tokens // 2].astype(dtype), v[: tokens // 2].astype(dtype))
+    for t in range(tokens // 2, tokens):                      # then one token per step, as in decode
+        cache.append(lay, k[t:t + 1].astype(dtype), v[t:t + 1].astype(dtype))
+    assert cache.seq_length() == tokens
+    ex = cache.export(lay)
+    assert ex["tokens"] == tokens
+    for key in ("k_words", "v_words", "k_norms", "v_norms", "qjl_words", "qjl_norms"):
+        assert bits_equal(ex[key], golden[f"{name}_{key}"]), key
+    assert bits_equal(cache.get_keys_fp16(lay, 0, tokens).view(np.uint16), golden[f"{name}_keys_fp16"])
+    assert bits_equal(cache.get_values_fp16(lay, 0, tokens).view(np.uint16), golden[f"{name}_values_fp16"])
+    part = cache.get_keys_fp16(lay, 3, 7)
+    assert bits_equal(part.view(np.uint16), golden[f"{name}_keys_fp16"][3:7])
+    with pytest.raises(IndexError):
+        cache.get_keys_fp16(lay, 0, tokens + 1)               # tests/unit/test_kv_cache.cpp:203-211
+    with pytest.raises(IndexError):
+        cache.get_keys_fp16(lay, 5, 5)
+    with pytest.raises(IndexError):
+        cache.append(layers, k, v)
+    cache.close()
+
+
+@pytest.mark.parametrize("case", KV_CASES, ids=[c[0] for c in KV_CASES])
+@pytest.mark.parametrize("use_qjl", [False, True])
+def test_attention_matches_oracle(tq, golden, case, use_qjl):
+    name, layers, heads, dim, tokens, seed = case
+    lay = layers - 1
+    k, v = kv_inputs(seed, tokens, heads, dim)
+    cache = tq.TQKVCache(layers, heads, dim)
+    cache.append(lay, k, v)
+    q_heads = heads * (7 if heads == 4 else 1)
+    q = np.random.default_rng(seed + 100).standard_normal((q_heads, dim)).astype(np.float16).astype(np.float32)
+    out = tq.compressed_attention([cache], lay, q[None], use_qjl=use_qjl)
+    want = golden[f"{name}_attn_qjl{int(use_qjl)}"]
+    assert out.shape == (1, q_heads, dim) and out.dtype == np.float16
+    assert rel_l2(out[0], want) < ATTN_TOL, rel_l2(out[0], want)
+    cache.close()
+
+
+def test_attention_long_context_batch_and_ranges(tq, oracle):
+    """Several sequences of different lengths, many context splits, sub-ranges, GQA 7."""
+    rng = np.random.default_rng(9)
+    heads, dim, q_heads = 4, 128, 28
+    lens = [700, 1301]
+    caches, stores = [], []
+    for n in lens:
+        k, v = kv_inputs(int(rng.integers(1 << 30)), n, heads, dim)
+        c = tq.TQKVCache(1, heads, dim)
+        c.append(0, k, v)
+        caches.append(c)
+        stores.append(c.export(0))
+    q = rng.standard_normal((len(lens), q_heads, dim)).astype(np.float16)
+    for use_qjl in (False, True):
+        out = tq.compressed_attention(caches, 0, q, use_qjl=use_qjl)
+        for i, ex in enumerate(stores):
+            want = oracle.attention(q[i].astype(np.float32), heads, ex["k_words"], ex["k_norms"], ex["v_words"],
+                                    ex["v_norms"], ex["qjl_words"], ex["qjl_norms"], layer=0, use_qjl=use_qjl)
+            assert rel_l2(out[i], want) < ATTN_TOL, (i, use_qjl, rel_l2(out[i], want))
+    out = tq.compressed_attention(caches[:1], 0, q[:1], start=100, end=333)
+    ex = stores[0]
+    want = oracle.attention(q[0].astype(np.float32), heads, ex["k_words"], ex["k_norms"], ex["v_words"], ex["v_norms"],
+                            ex["qjl_words"], ex["qjl_norms"], layer=0, start=100, end=333)
+    assert rel_l2(out[0], want) < ATTN_TOL
+    with pytest.raises(tq.TQError):
+        tq.compressed_attention(caches[:1], 0, q[:1], start=0, end=10_000)
+    for c in caches:
+        c.close()
+
+
+def test_reference_c_api_with_arrays(tq, golden):
+    """The reference's own entry points (tq_kv_cache_append / get_keys_fp16 / attention) driven
+    through tq_array handles, plus multi-layer independence (tests/unit/test_kv_cache.cpp)."""
+    L = tq.load()
+    name, layers, heads, dim, tokens, seed = KV_CASES[0]
+    k, v = kv_inputs(seed, tokens, heads, dim)
+    shape = (C.c_int * 3)(tokens, heads, dim)
+    ka = L.tq_array_create(k.ctypes.data, 1, 3, shape)
+    va = L.tq_array_create(v.ctypes.data, 1, 3, shape)
+    assert ka and va
+    cache = L.tq_kv_cache_create(layers, heads, dim, 3, 4096, 128)
+    L.tq_kv_cache_append(cache, layers - 1, ka, va)
+    L.tq_kv_cache_append(cache, layers + 5, ka, va)           # silently ignored, as in the reference
+    assert L.tq_kv_cache_seq_length(cache) == tokens
+    arr = L.tq_kv_cache_get_keys_fp16(cache, layers - 1, 0, tokens)
+    assert arr and L.tq_array_ndim(arr) == 3 and L.tq_array_dim(arr, 2) == dim
+    host = np.zeros((tokens, heads, dim), np.uint16)
+    assert L.tq_array_to_host(arr, host.ctypes.data, host.nbytes) == 0
+    assert np.array_equal(host, golden[f"{name}_keys_fp16"])
+    L.tq_array_free(arr)
+    assert L.tq_kv_cache_get_keys_fp16(cache, 0, 0, 1) is None  # layer 0 is empty
+    assert L.tq_kv_cache_get_values_fp16(cache, layers - 1, 4, 2) is None
+    q = np.random.default_rng(seed + 100).standard_normal((heads * 7, dim)).astype(np.float16)
+    qa = L.tq_array_create(q.ctypes.data, 1, 2, (C.c_int * 2)(heads * 7, dim))
+    oa = L.tq_kv_cache_attention(cache, layers - 1, qa, 0, tokens)
+    assert oa
+    out = np.zeros((heads * 7, dim), np.float16)
+    assert L.tq_array_to_host(oa, out.ctypes.data, out.nbytes) == 0
+    assert rel_l2(out, golden[f"{name}_attn_qjl0"]) < ATTN_TOL
+    for a in (oa, qa, ka, va):
+        L.tq_array_free(a)
+    L.tq_kv_cache_free(cache)

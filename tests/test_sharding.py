@@ -1,0 +1,73 @@
+"""CPU tests of the multi-GPU host logic: the row partition of column-parallel linears and
+the KV-head partition, plus a world_size-2 gloo run of the all-gather that follows them."""
+import os
+import socket
+
+import numpy as np
+import pytest
+
+from turboquant_mlx_core_b200.sharding import head_range, row_range, shard_quantized_rows
+
+
+def test_row_range_covers_everything_once():
+    for out in (151936, 4096, 18944, 512, 7, 1):
+        for world in (1, 2, 4, 8):
+            spans = [row_range(out, r, world) for r in range(world)]
+            assert spans[0][0] == 0 and spans[-1][1] == out
+            for a, b in zip(spans, spans[1:]):
+                assert a[1] == b[0]
+            sizes = [e - s for s, e in spans]
+            assert max(sizes) - min(sizes) <= 16      # whole 16-row tiles except the tail
+    assert row_range(151936, 3, 8) == (3 * 18992, 4 * 18992)
+
+
+def test_head_range():
+    assert [head_range(4, r, 2) for r in range(2)] == [(0, 2), (2, 4)]
+    assert [head_range(8, r, 8) for r in range(8)] == [(r, r + 1) for r in range(8)]
+    with pytest.raises(ValueError):
+        head_range(4, 0, 8)          # more ranks than KV heads: callers split context instead
+
+
+def test_shard_quantized_rows_slices_planes():
+    pp = np.arange(64 * 8, dtype=np.uint8).reshape(64, 8)
+    pr = pp[::-1].copy()
+    norms = np.arange(64, dtype=np.float32)
+    a, b, c = shard_quantized_rows(pp, pr, norms, 1, 2)
+    s, e = row_range(64, 1, 2)
+    assert np.array_equal(a, pp[s:e]) and np.array_equal(b, pr[s:e]) and np.array_equal(c, norms[s:e])
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    p = s.getsockname()[1]
+    s.close()
+    return p
+
+
+def _worker(rank, world, port, out_features, q):
+    import torch
+    import torch.distributed as dist
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    from turboquant_mlx_core_b200.sharding import all_gather_rows, row_range
+    s, e = row_range(out_features, rank, world)
+    full = torch.arange(3 * out_features, dtype=torch.float32).reshape(3, out_features).to(torch.float16)
+    local = full[:, s:e].contiguous()
+    got = all_gather_rows(local, out_features, world)
+    q.put((rank, bool(torch.equal(got, full))))
+    dist.destroy_process_group()
+
+
+def test_all_gather_of_row_shards_gloo():
+    import torch.multiprocessing as mp
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_worker, args=(r, 2, port, 1000, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    res = sorted(q.get(timeout=120) for _ in procs)
+    for p in procs:
+        p.join(60)
+    assert res == [(0, True), (1, True)]

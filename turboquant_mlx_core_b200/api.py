@@ -1,0 +1,333 @@
+"""Host-side mirror of the reference's C++ interface for the hot path, over the C-ABI.
+
+Names follow the reference (include/turboquant/*.h): Codebook / generate_codebook,
+apply_wht_rotation / apply_inverse_wht_rotation, quantize_weight -> QuantizedWeight,
+dequantize_weight, TurboQuantLinear.forward, TQKVCache.append / get_keys_fp16 /
+get_values_fp16 / seq_length, hybrid_attention (compressed branch).
+
+Arguments may be numpy arrays (host memory) or torch CUDA tensors (used in place through
+their device pointer).  Everything runs in the CUDA library; nothing here computes.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from dataclasses import dataclass
+
+import numpy as np
+
+from . import _lib
+from ._lib import TQ_F16, TQ_F32, TQError, check
+
+
+def _is_torch(x) -> bool:
+    return type(x).__module__.startswith("torch")
+
+
+def _ptr(x):
+    """Raw address of a numpy array or torch tensor (must be contiguous)."""
+    if x is None:
+        return None
+    if _is_torch(x):
+        if not x.is_contiguous():
+            raise ValueError("tensor must be contiguous")
+        return C.c_void_p(x.data_ptr())
+    if not x.flags["C_CONTIGUOUS"]:
+        raise ValueError("array must be C-contiguous")
+    return C.c_void_p(x.ctypes.data)
+
+
+def _dtype_tag(x) -> int:
+    name = str(x.dtype)
+    if name.endswith("float32"):
+        return TQ_F32
+    if name.endswith("float16"):
+        return TQ_F16
+    raise TypeError(f"expected float32 or float16, got {x.dtype}")
+
+
+def _stream_ptr(stream):
+    if stream is None:
+        return None
+    if hasattr(stream, "cuda_stream"):
+        return C.c_void_p(stream.cuda_stream)
+    return C.c_void_p(int(stream))
+
+
+def _np(a, dt):
+    return np.ascontiguousarray(a, dtype=dt)
+
+
+# ---- codebooks -------------------------------------------------------------------------
+
+@dataclass
+class Codebook:
+    """include/turboquant/codebook.h:25-30."""
+    centroids: np.ndarray
+    boundaries: np.ndarray
+    bits: int
+
+
+def generate_codebook(bits: int) -> Codebook:
+    """generate_codebook (src/codebook.cpp:71-85); raises ValueError for bits outside 1..5."""
+    L = _lib.load()
+    if not 1 <= bits <= 5:
+        raise ValueError("Unsupported bit width; must be 1-5")
+    c = np.zeros(1 << bits, np.float32)
+    b = np.zeros(max((1 << bits) - 1, 1), np.float32)
+    check(L.tq_codebook_generate(bits, c.ctypes.data, b.ctypes.data), "generate_codebook")
+    return Codebook(c, b[: (1 << bits) - 1], bits)
+
+
+def codebook_from_centroids(centroids) -> Codebook:
+    c = _np(centroids, np.float32)
+    b = ((c[:-1] + c[1:]) * np.float32(0.5)).astype(np.float32)
+    bits = int(np.ceil(np.log2(max(c.size, 2))))
+    return Codebook(c, b, bits)
+
+
+# ---- rotation ----------------------------------------------------------------------------
+
+def _wht(matrix, seed, block_size, inverse, out, stream):
+    L = _lib.load()
+    if tuple(matrix.shape)[-1] % block_size:
+        raise ValueError("in_features must be divisible by block_size")
+    rows = int(np.prod(matrix.shape[:-1])) if len(matrix.shape) > 1 else 1
+    cols = matrix.shape[-1]
+    if out is None:
+        if _is_torch(matrix):
+            import torch
+            out = torch.empty_like(matrix)
+        else:
+            matrix = _np(matrix, np.float32)
+            out = np.empty_like(matrix)
+    check(L.tq_wht_rotate(_ptr(matrix), _ptr(out), rows, cols, seed, block_size, int(inverse), _stream_ptr(stream)),
+          "wht_rotate")
+    return out
+
+
+def apply_wht_rotation(matrix, seed: int, block_size: int, out=None, stream=None):
+    """apply_wht_rotation (src/rotation.cpp:364-383): fp32 [rows, cols] -> same."""
+    return _wht(matrix, seed, block_size, False, out, stream)
+
+
+def apply_inverse_wht_rotation(matrix, seed: int, block_size: int, out=None, stream=None):
+    """apply_inverse_wht_rotation (src/rotation.cpp:385-403)."""
+    return _wht(matrix, seed, block_size, True, out, stream)
+
+
+# ---- weights -------------------------------------------------------------------------------
+
+@dataclass
+class QuantizerConfig:
+    """include/turboquant/quantizer.h:11-19 (the fields the quantiser reads)."""
+    primary_bits: int = 4
+    residual_bits: int = 4
+    block_size: int = 512
+    shared_rotation: bool = False
+
+
+@dataclass
+class QuantizedWeight:
+    """include/turboquant/quantizer.h:22-27; norms are fp32 as the reference stores them."""
+    packed_primary: np.ndarray
+    packed_residual: np.ndarray
+    norms: np.ndarray
+    seeds: np.ndarray
+
+
+def quantize_weight(weight, primary_codebook: Codebook, residual_codebook: Codebook,
+                    config: QuantizerConfig) -> QuantizedWeight:
+    """quantize_weight (src/quantizer.cpp:41-261) on the device; host arrays in and out."""
+    L = _lib.load()
+    w = weight if _is_torch(weight) else _np(weight, np.float32)
+    out_f, in_f = int(w.shape[0]), int(w.shape[1])
+    if in_f % config.block_size:
+        raise ValueError("in_features must be divisible by block_size")
+    pp = np.zeros((out_f, in_f // 2 if config.primary_bits <= 4 else in_f), np.uint8)
+    pr = np.zeros((out_f, in_f // 2), np.uint8)
+    norms = np.zeros(out_f, np.float32)
+    seeds = np.zeros(3, np.uint32)
+    cp, cr = _np(primary_codebook.centroids, np.float32), _np(residual_codebook.centroids, np.float32)
+    check(L.tq_quantize_weight(_ptr(w), out_f, in_f, _ptr(cp), cp.size, _ptr(cr), cr.size, config.primary_bits,
+                               config.residual_bits, config.block_size, int(config.shared_rotation), _ptr(pp),
+                               _ptr(pr), _ptr(norms), _ptr(seeds), None), "quantize_weight")
+    return QuantizedWeight(pp, pr, norms, seeds)
+
+
+class TurboQuantLinear:
+    """turboquant::TurboQuantLinear (include/turboquant/linear.h:11-35)."""
+
+    def __init__(self, in_features: int, out_features: int, weights: QuantizedWeight, primary_codebook: Codebook,
+                 residual_codebook: Codebook, block_size: int):
+        L = _lib.load()
+        self._L = L
+        pp, pr = _np(weights.packed_primary, np.uint8), _np(weights.packed_residual, np.uint8)
+        norms, seeds = _np(weights.norms, np.float32), _np(weights.seeds, np.uint32)
+        cp, cr = _np(primary_codebook.centroids, np.float32), _np(residual_codebook.centroids, np.float32)
+        if pp.shape[0] != out_features or pr.shape != (out_features, in_features // 2):
+            raise ValueError("packed planes do not match in/out features")
+        self._h = L.tq_linear_create(in_features, out_features, _ptr(pp), pp.shape[1], _ptr(pr), _ptr(norms),
+                                     _ptr(seeds), _ptr(cp), cp.size, _ptr(cr), cr.size, block_size)
+        if not self._h:
+            raise TQError("TurboQuantLinear: " + _lib.last_error())
+        self.in_features_, self.out_features_ = in_features, out_features
+
+    def in_features(self) -> int:
+        return self.in_features_
+
+    def out_features(self) -> int:
+        return self.out_features_
+
+    @property
+    def handle(self):
+        return self._h
+
+    def forward(self, x, out=None, stream=None):
+        """[batch, in] fp32/fp16 -> fp16 [batch, out] (src/linear.cpp:20-26)."""
+        if not _is_torch(x):
+            x = np.ascontiguousarray(x)
+            if x.dtype not in (np.float32, np.float16):
+                x = x.astype(np.float32)
+        if x.shape[-1] != self.in_features_:
+            raise ValueError("input feature size mismatch")
+        batch = int(np.prod(x.shape[:-1])) if len(x.shape) > 1 else 1
+        if out is None:
+            if _is_torch(x):
+                import torch
+                out = torch.empty((batch, self.out_features_), dtype=torch.float16, device=x.device)
+            else:
+                out = np.empty((batch, self.out_features_), np.float16)
+        check(self._L.tq_linear_forward(self._h, _ptr(x), _dtype_tag(x), batch, _ptr(out), _stream_ptr(stream)),
+              "TurboQuantLinear.forward")
+        return out
+
+    def dequantize(self, dtype=np.float32, out=None, stream=None):
+        """dequantize_weight_cpu's result (src/dequantizer.cpp:52-256) as fp32, or fp16 (RN cast)."""
+        if out is None:
+            out = np.empty((self.out_features_, self.in_features_), dtype)
+        check(self._L.tq_linear_dequantize(self._h, _ptr(out), _dtype_tag(out), _stream_ptr(stream)), "dequantize")
+        return out
+
+    def close(self):
+        if getattr(self, "_h", None):
+            self._L.tq_linear_free(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+def dequantize_weight(qw: QuantizedWeight, primary_codebook: Codebook, residual_codebook: Codebook, block_size: int,
+                      dtype=np.float32):
+    """dequantize_weight_cpu / _gpu (include/turboquant/dequantizer.h:11-22) -> [out, in]."""
+    out_f = qw.packed_primary.shape[0]
+    in_f = qw.packed_residual.shape[1] * 2
+    lin = TurboQuantLinear(in_f, out_f, qw, primary_codebook, residual_codebook, block_size)
+    try:
+        return lin.dequantize(dtype)
+    finally:
+        lin.close()
+
+
+# ---- KV cache --------------------------------------------------------------------------------
+
+class TQKVCache:
+    """turboquant::TQKVCache (include/turboquant/kv_cache.h:42-133): one sequence."""
+
+    def __init__(self, num_layers: int, num_heads: int, head_dim: int, kv_bits: int = 3,
+                 max_context: int = 1048576, decode_window: int = 131072):
+        L = _lib.load()
+        self._L = L
+        self.num_layers, self.num_heads, self.head_dim = num_layers, num_heads, head_dim
+        self._h = L.tq_kv_cache_create(num_layers, num_heads, head_dim, kv_bits, max_context, decode_window)
+        if not self._h:
+            raise TQError("TQKVCache: " + _lib.last_error())
+
+    @property
+    def handle(self):
+        return self._h
+
+    def append(self, layer: int, keys, values, stream=None):
+        """[tokens, heads, head_dim] fp32/fp16 (src/kv_cache.cpp:16-61)."""
+        if not _is_torch(keys):
+            keys, values = np.ascontiguousarray(keys), np.ascontiguousarray(values)
+        if tuple(keys.shape) != tuple(values.shape) or tuple(keys.shape[1:]) != (self.num_heads, self.head_dim):
+            raise ValueError("keys/values must be [tokens, heads, head_dim]")
+        if not 0 <= layer < self.num_layers:
+            raise IndexError("Layer index out of range")
+        check(self._L.tq_kv_append(self._h, layer, _ptr(keys), _ptr(values), _dtype_tag(keys), int(keys.shape[0]),
+                                   _stream_ptr(stream)), "TQKVCache.append")
+
+    def seq_length(self) -> int:
+        return self._L.tq_kv_cache_seq_length(self._h)
+
+    def _get(self, layer, values, start, end, out, stream):
+        if not 0 <= layer < self.num_layers:
+            raise IndexError("Layer index out of range")
+        if out is None:
+            out = np.empty((max(end - start, 0), self.num_heads, self.head_dim), np.float16)
+        rc = self._L.tq_kv_get_fp16(self._h, layer, int(values), start, end, _ptr(out), _stream_ptr(stream))
+        if rc:
+            raise IndexError(_lib.last_error())
+        return out
+
+    def get_keys_fp16(self, layer, start, end, out=None, stream=None):
+        return self._get(layer, False, start, end, out, stream)
+
+    def get_values_fp16(self, layer, start, end, out=None, stream=None):
+        return self._get(layer, True, start, end, out, stream)
+
+    def export(self, layer: int) -> dict:
+        """Raw storage in the reference's layout (include/turboquant/kv_cache.h:25-36)."""
+        n = self._L.tq_kv_export(self._h, layer, None, None, None, None, None, None)
+        if n < 0:
+            raise TQError(_lib.last_error())
+        nv = n * self.num_heads
+        wph, qph = (self.head_dim + 9) // 10, (self.head_dim + 31) // 32
+        d = dict(k_words=np.zeros((nv, wph), np.uint32), v_words=np.zeros((nv, wph), np.uint32),
+                 k_norms=np.zeros(nv, np.float32), v_norms=np.zeros(nv, np.float32),
+                 qjl_words=np.zeros((nv, qph), np.uint32), qjl_norms=np.zeros(nv, np.float32))
+        self._L.tq_kv_export(self._h, layer, _ptr(d["k_words"]), _ptr(d["v_words"]), _ptr(d["k_norms"]),
+                             _ptr(d["v_norms"]), _ptr(d["qjl_words"]), _ptr(d["qjl_norms"]))
+        d["tokens"] = n
+        return d
+
+    def close(self):
+        if getattr(self, "_h", None):
+            self._L.tq_kv_cache_free(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+def compressed_attention(caches, layer: int, queries, start: int = 0, end: int = -1, use_qjl: bool = False,
+                         out=None, stream=None):
+    """Decode attention over the compressed caches of a batch of sequences: the long-context
+    branch of hybrid_attention (src/attention_dispatch.cpp:58-73) without materialising K/V.
+    queries: [n_seqs, q_heads, head_dim] -> fp16 of the same shape."""
+    L = _lib.load()
+    if isinstance(caches, TQKVCache):
+        caches = [caches]
+    n = len(caches)
+    if not _is_torch(queries):
+        queries = np.ascontiguousarray(queries)
+    if queries.shape[0] != n or queries.shape[-1] != caches[0].head_dim:
+        raise ValueError("queries must be [n_seqs, q_heads, head_dim]")
+    q_heads = int(queries.shape[1])
+    if out is None:
+        if _is_torch(queries):
+            import torch
+            out = torch.empty(tuple(queries.shape), dtype=torch.float16, device=queries.device)
+        else:
+            out = np.empty(queries.shape, np.float16)
+    arr = (C.c_void_p * n)(*[c.handle for c in caches])
+    check(L.tq_kv_attention(arr, n, layer, _ptr(queries), _dtype_tag(queries), q_heads, _ptr(out), start, end,
+                            int(use_qjl), _stream_ptr(stream)), "compressed_attention")
+    return out

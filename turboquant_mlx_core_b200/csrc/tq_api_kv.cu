@@ -1,0 +1,421 @@
+// TQKVCache on the device, and its C entry points (the reference's tq_kv_cache_* calls
+// plus pointer-level variants and a batched attention over several caches).
+//
+// Mirrors turboquant::TQKVCache (include/turboquant/kv_cache.h:42-133,
+// src/kv_cache.cpp) and hybrid_attention's long-context branch
+// (src/attention_dispatch.cpp:58-73).  One cache = one sequence, as in the reference;
+// a decode batch is a set of caches attended in one launch.
+#include <algorithm>
+#include <cmath>
+
+#include "tq_host.hpp"
+#include "tq_kernels.cuh"
+#include "turboquant_c/turboquant_b200.h"
+#include "turboquant_c/turboquant_c.h"
+
+namespace tq {
+// tq_kv_kernels.cu
+void launch_kv_encode(const void* x, bool x_is_f16, long n_vec, int head_dim, uint32_t wht_seed, uint32_t qjl_seed,
+                      bool with_qjl, uint32_t* words, float* norms, uint32_t* qjl_words, float* qjl_norms,
+                      cudaStream_t stream);
+void launch_kv_decode_f16(const uint32_t* words, const float* norms, long n_vec, int head_dim, uint32_t wht_seed,
+                          __half* out, cudaStream_t stream);
+size_t attn_scratch_bytes(int n_seqs, int q_heads, int head_dim, int n_splits);
+void launch_kv_attention(const void* d_seqs, int n_seqs, const void* q, bool q_is_f16, int q_heads, int kv_heads,
+                         int head_dim, int n_splits, uint32_t k_seed, uint32_t v_seed, uint32_t qjl_seed, bool use_qjl,
+                         void* scratch, __half* out, cudaStream_t stream);
+}  // namespace tq
+
+namespace turboquant {
+
+using tq::DeviceBuffer;
+using tq::Error;
+
+// Device image of the kernel-side per-sequence descriptor (tq_kv_kernels.cu: AttnSeq).
+struct SeqDesc {
+    const uint32_t* k_words;
+    const uint32_t* v_words;
+    const float* k_norms;
+    const float* v_norms;
+    const uint32_t* qjl_words;
+    const float* qjl_norms;
+    int start, end;
+};
+
+struct LayerKVStorage {
+    DeviceBuffer k_words, v_words, k_norms, v_norms, qjl_words, qjl_norms;
+    int num_tokens = 0;
+    int capacity = 0;
+};
+
+class TQKVCache {
+public:
+    TQKVCache(int num_layers, int num_heads, int head_dim, int kv_bits, int max_context, int decode_window)
+        : layers_n_(num_layers), heads_(num_heads), dim_(head_dim), kv_bits_(kv_bits), max_context_(max_context),
+          decode_window_(decode_window) {
+        TQ_REQUIRE(num_layers > 0 && num_heads > 0, "TQKVCache: layers and heads must be positive");
+        TQ_REQUIRE(tq::is_pow2(static_cast<uint32_t>(head_dim)) && head_dim >= 32 && head_dim <= 512,
+                   "TQKVCache: head_dim must be a power of two in [32, 512]");
+        device_ = tq::current_device();
+        layers_.resize(static_cast<size_t>(num_layers));
+    }
+
+    int num_layers() const { return layers_n_; }
+    int num_heads() const { return heads_; }
+    int head_dim() const { return dim_; }
+    int words_per_head() const { return (dim_ + 9) / 10; }
+    int qjl_words_per_head() const { return (dim_ + 31) / 32; }
+    int seq_length() const { return seq_length_; }  // max over layers, src/kv_cache.cpp:54-60
+    int layer_tokens(int layer) const { return layers_.at(static_cast<size_t>(layer)).num_tokens; }
+
+    // keys / values: [tokens, heads, dim], fp32 or fp16, host or device.
+    void append(int layer, const void* keys, const void* values, int dtype, int tokens, cudaStream_t st) {
+        TQ_REQUIRE(layer >= 0 && layer < layers_n_, "Layer index out of range");
+        TQ_REQUIRE(keys && values, "append: NULL argument");
+        TQ_REQUIRE(dtype == TQ_F32 || dtype == TQ_F16, "append: keys/values must be fp32 or fp16");
+        TQ_REQUIRE(tokens >= 0, "append: negative token count");
+        if (tokens == 0) return;
+        TQ_CUDA(cudaSetDevice(device_));
+        LayerKVStorage& L = layers_[static_cast<size_t>(layer)];
+        reserve(L, L.num_tokens + tokens, st);
+        const size_t es = dtype == TQ_F32 ? 4 : 2;
+        const size_t n_vec = static_cast<size_t>(tokens) * heads_;
+        const size_t bytes = n_vec * dim_ * es;
+        const void* d_k = keys;
+        const void* d_v = values;
+        if (!tq::is_device_pointer(keys)) {
+            stage_k_.reserve(bytes);
+            TQ_CUDA(cudaMemcpyAsync(stage_k_.as<void>(), keys, bytes, cudaMemcpyHostToDevice, st));
+            d_k = stage_k_.as<void>();
+        }
+        if (!tq::is_device_pointer(values)) {
+            stage_v_.reserve(bytes);
+            TQ_CUDA(cudaMemcpyAsync(stage_v_.as<void>(), values, bytes, cudaMemcpyHostToDevice, st));
+            d_v = stage_v_.as<void>();
+        }
+        const size_t off = static_cast<size_t>(L.num_tokens) * heads_;
+        const int wph = words_per_head(), qph = qjl_words_per_head();
+        const uint32_t ks = tq::kv_layer_seed(static_cast<uint32_t>(layer), 1);  // src/kv_cache.cpp:40-42
+        const uint32_t vs = tq::kv_layer_seed(static_cast<uint32_t>(layer), 2);
+        const uint32_t qs = tq::kv_layer_seed(static_cast<uint32_t>(layer), 3);
+        tq::launch_kv_encode(d_k, dtype == TQ_F16, static_cast<long>(n_vec), dim_, ks, qs, true,
+                             L.k_words.as<uint32_t>() + off * wph, L.k_norms.as<float>() + off,
+                             L.qjl_words.as<uint32_t>() + off * qph, L.qjl_norms.as<float>() + off, st);
+        tq::launch_kv_encode(d_v, dtype == TQ_F16, static_cast<long>(n_vec), dim_, vs, 0u, false,
+                             L.v_words.as<uint32_t>() + off * wph, L.v_norms.as<float>() + off, nullptr, nullptr, st);
+        L.num_tokens += tokens;
+        seq_length_ = std::max(seq_length_, L.num_tokens);
+    }
+
+    // fp16 [end-start, heads, dim] into `out` (host or device).
+    void get_fp16(int layer, bool values, int start, int end, void* out, cudaStream_t st) {
+        TQ_REQUIRE(layer >= 0 && layer < layers_n_, "Layer index out of range");
+        LayerKVStorage& L = layers_[static_cast<size_t>(layer)];
+        TQ_REQUIRE(start >= 0 && end <= L.num_tokens && start < end, "Invalid token range for dequantization");
+        TQ_REQUIRE(out, "get_fp16: NULL output");
+        TQ_CUDA(cudaSetDevice(device_));
+        const size_t n_vec = static_cast<size_t>(end - start) * heads_;
+        const size_t off = static_cast<size_t>(start) * heads_;
+        const bool dev = tq::is_device_pointer(out);
+        DeviceBuffer stage;
+        __half* d_out = static_cast<__half*>(out);
+        if (!dev) {
+            stage.reserve(n_vec * dim_ * sizeof(__half));
+            d_out = stage.as<__half>();
+        }
+        const uint32_t seed = tq::kv_layer_seed(static_cast<uint32_t>(layer), values ? 2 : 1);
+        const DeviceBuffer& W = values ? L.v_words : L.k_words;
+        const DeviceBuffer& N = values ? L.v_norms : L.k_norms;
+        tq::launch_kv_decode_f16(W.as<uint32_t>() + off * words_per_head(), N.as<float>() + off,
+                                 static_cast<long>(n_vec), dim_, seed, d_out, st);
+        if (!dev) {
+            TQ_CUDA(cudaMemcpyAsync(out, d_out, n_vec * dim_ * sizeof(__half), cudaMemcpyDeviceToHost, st));
+            TQ_CUDA(cudaStreamSynchronize(st));
+        }
+    }
+
+    // Raw storage of a layer in the reference's layout (any pointer may be NULL);
+    // destinations are host or device.  Returns the token count.
+    int export_layer(int layer, uint32_t* k_words, uint32_t* v_words, float* k_norms, float* v_norms,
+                     uint32_t* qjl_words, float* qjl_norms) {
+        TQ_REQUIRE(layer >= 0 && layer < layers_n_, "Layer index out of range");
+        LayerKVStorage& L = layers_[static_cast<size_t>(layer)];
+        TQ_CUDA(cudaSetDevice(device_));
+        TQ_CUDA(cudaDeviceSynchronize());
+        const size_t n = static_cast<size_t>(L.num_tokens) * heads_;
+        auto copy = [&](void* dst, const DeviceBuffer& src, size_t bytes) {
+            if (dst && bytes) TQ_CUDA(cudaMemcpy(dst, src.as<void>(), bytes, cudaMemcpyDefault));
+        };
+        copy(k_words, L.k_words, n * words_per_head() * 4);
+        copy(v_words, L.v_words, n * words_per_head() * 4);
+        copy(k_norms, L.k_norms, n * 4);
+        copy(v_norms, L.v_norms, n * 4);
+        copy(qjl_words, L.qjl_words, n * qjl_words_per_head() * 4);
+        copy(qjl_norms, L.qjl_norms, n * 4);
+        return L.num_tokens;
+    }
+
+    SeqDesc describe(int layer, int start, int end) const {
+        TQ_REQUIRE(layer >= 0 && layer < layers_n_, "Layer index out of range");
+        const LayerKVStorage& L = layers_[static_cast<size_t>(layer)];
+        TQ_REQUIRE(start >= 0 && end <= L.num_tokens && start < end, "Invalid token range for attention");
+        return SeqDesc{L.k_words.as<uint32_t>(), L.v_words.as<uint32_t>(), L.k_norms.as<float>(), L.v_norms.as<float>(),
+                       L.qjl_words.as<uint32_t>(), L.qjl_norms.as<float>(), start, end};
+    }
+
+    int device() const { return device_; }
+    DeviceBuffer& attn_scratch() { return attn_scratch_; }
+    DeviceBuffer& attn_desc() { return attn_desc_; }
+    DeviceBuffer& attn_q() { return attn_q_; }
+    DeviceBuffer& attn_out() { return attn_out_; }
+
+private:
+    // Grow a layer's buffers to hold `tokens` tokens (capacity doubles; old contents kept).
+    void reserve(LayerKVStorage& L, int tokens, cudaStream_t st) {
+        if (tokens <= L.capacity) return;
+        int cap = std::max(L.capacity * 2, std::max(tokens, 256));
+        const size_t per = static_cast<size_t>(heads_);
+        const size_t old_n = static_cast<size_t>(L.num_tokens) * per;
+        auto grow = [&](DeviceBuffer& b, size_t elem_bytes_per_vec) {
+            DeviceBuffer nb(static_cast<size_t>(cap) * per * elem_bytes_per_vec);
+            if (old_n) TQ_CUDA(cudaMemcpyAsync(nb.as<void>(), b.as<void>(), old_n * elem_bytes_per_vec, cudaMemcpyDeviceToDevice, st));
+            TQ_CUDA(cudaStreamSynchronize(st));  // the old buffer is freed on return
+            b = std::move(nb);
+        };
+        grow(L.k_words, static_cast<size_t>(words_per_head()) * 4);
+        grow(L.v_words, static_cast<size_t>(words_per_head()) * 4);
+        grow(L.k_norms, 4);
+        grow(L.v_norms, 4);
+        grow(L.qjl_words, static_cast<size_t>(qjl_words_per_head()) * 4);
+        grow(L.qjl_norms, 4);
+        L.capacity = cap;
+    }
+
+    int layers_n_, heads_, dim_, kv_bits_, max_context_, decode_window_;
+    int device_ = 0;
+    int seq_length_ = 0;
+    std::vector<LayerKVStorage> layers_;
+    DeviceBuffer stage_k_, stage_v_;
+    DeviceBuffer attn_scratch_, attn_desc_, attn_q_, attn_out_;
+};
+
+// Attention of one query position per sequence over [start, end) of each cache.
+// q: [n_seqs, q_heads, dim] fp32/fp16, out: fp16 same shape; host or device.
+void attention_batched(TQKVCache* const* caches, int n_seqs, int layer, const void* q, int q_dtype, int q_heads,
+                       const int* starts, const int* ends, bool use_qjl, void* out, cudaStream_t st) {
+    TQ_REQUIRE(caches && n_seqs > 0 && q && out, "attention: bad argument");
+    TQ_REQUIRE(q_dtype == TQ_F32 || q_dtype == TQ_F16, "attention: queries must be fp32 or fp16");
+    TQKVCache* c0 = caches[0];
+    TQ_REQUIRE(c0, "attention: NULL cache");
+    const int heads = c0->num_heads(), dim = c0->head_dim();
+    TQ_REQUIRE(q_heads > 0 && q_heads % heads == 0, "attention: query heads must be a multiple of KV heads");
+    TQ_REQUIRE(dim <= 256, "attention: head_dim above 256 is not supported");
+    TQ_CUDA(cudaSetDevice(c0->device()));
+    std::vector<SeqDesc> desc(static_cast<size_t>(n_seqs));
+    int max_tok = 0;
+    for (int i = 0; i < n_seqs; ++i) {
+        TQ_REQUIRE(caches[i] && caches[i]->num_heads() == heads && caches[i]->head_dim() == dim &&
+                       caches[i]->device() == c0->device(),
+                   "attention: caches of one call must share shape and device");
+        desc[i] = caches[i]->describe(layer, starts[i], ends[i]);
+        max_tok = std::max(max_tok, ends[i] - starts[i]);
+    }
+    // enough context splits to fill the machine, at least ~256 tokens each
+    const int G = q_heads / heads;
+    const int ctas_per_split = n_seqs * heads * ((G + 7) / 8);
+    int n_splits = std::max(1, std::min((148 * 4 + ctas_per_split - 1) / ctas_per_split, (max_tok + 255) / 256));
+    n_splits = std::min(n_splits, 64);
+
+    c0->attn_desc().reserve(desc.size() * sizeof(SeqDesc));
+    TQ_CUDA(cudaMemcpyAsync(c0->attn_desc().as<void>(), desc.data(), desc.size() * sizeof(SeqDesc), cudaMemcpyHostToDevice, st));
+    const size_t n_q = static_cast<size_t>(n_seqs) * q_heads * dim;
+    const size_t q_es = q_dtype == TQ_F32 ? 4 : 2;
+    const void* d_q = q;
+    if (!tq::is_device_pointer(q)) {
+        c0->attn_q().reserve(n_q * q_es);
+        TQ_CUDA(cudaMemcpyAsync(c0->attn_q().as<void>(), q, n_q * q_es, cudaMemcpyHostToDevice, st));
+        d_q = c0->attn_q().as<void>();
+    }
+    const bool out_dev = tq::is_device_pointer(out);
+    __half* d_out = static_cast<__half*>(out);
+    if (!out_dev) {
+        c0->attn_out().reserve(n_q * sizeof(__half));
+        d_out = c0->attn_out().as<__half>();
+    }
+    c0->attn_scratch().reserve(tq::attn_scratch_bytes(n_seqs, q_heads, dim, n_splits));
+    tq::launch_kv_attention(c0->attn_desc().as<void>(), n_seqs, d_q, q_dtype == TQ_F16, q_heads, heads, dim, n_splits,
+                            tq::kv_layer_seed(static_cast<uint32_t>(layer), 1), tq::kv_layer_seed(static_cast<uint32_t>(layer), 2),
+                            tq::kv_layer_seed(static_cast<uint32_t>(layer), 3), use_qjl, c0->attn_scratch().as<void>(), d_out, st);
+    // desc was copied from pageable host memory: the copy has been staged by the time
+    // cudaMemcpyAsync returned, so `desc` may die here.
+    if (!out_dev) {
+        TQ_CUDA(cudaMemcpyAsync(out, d_out, n_q * sizeof(__half), cudaMemcpyDeviceToHost, st));
+        TQ_CUDA(cudaStreamSynchronize(st));
+    }
+}
+
+}  // namespace turboquant
+
+struct tq_kv_cache_s {
+    turboquant::TQKVCache* cache;
+};
+
+using namespace tq;
+
+namespace {
+
+// [tokens, heads, dim] view of a tq_array for append; returns tokens or -1.
+int kv_tokens_of(const tq_array_s* a, int heads, int dim) {
+    if (!a || a->ndim != 3 || a->shape[1] != heads || a->shape[2] != dim) return -1;
+    if (a->dtype != TQ_F32 && a->dtype != TQ_F16) return -1;
+    return a->shape[0];
+}
+
+tq_array_s* new_f16_array(int ndim, const int* shape) {
+    auto* a = new tq_array_s();
+    a->dtype = TQ_F16;
+    a->ndim = ndim;
+    for (int i = 0; i < ndim; ++i) a->shape[i] = shape[i];
+    a->device = current_device();
+    a->owns = true;
+    if (a->nbytes()) {
+        cudaError_t e = cudaMalloc(&a->data, a->nbytes());
+        if (e != cudaSuccess) {
+            delete a;
+            throw Error(std::string("cudaMalloc: ") + cudaGetErrorString(e));
+        }
+    }
+    return a;
+}
+
+}  // namespace
+
+extern "C" {
+
+tq_kv_cache_t tq_kv_cache_create(int num_layers, int num_heads, int head_dim, int kv_bits, int max_context,
+                                 int decode_window) {
+    return guarded<tq_kv_cache_t>(nullptr, nullptr, [&]() -> tq_kv_cache_t {
+        auto* c = new turboquant::TQKVCache(num_layers, num_heads, head_dim, kv_bits, max_context, decode_window);
+        return new tq_kv_cache_s{c};
+    });
+}
+
+void tq_kv_cache_append(tq_kv_cache_t cache, int layer, const void* keys_array, const void* values_array) {
+    if (!cache || !cache->cache || !keys_array || !values_array) return;
+    guarded<int>(0, -1, [&]() {
+        const auto* k = static_cast<const tq_array_s*>(keys_array);
+        const auto* v = static_cast<const tq_array_s*>(values_array);
+        const int tokens = kv_tokens_of(k, cache->cache->num_heads(), cache->cache->head_dim());
+        TQ_REQUIRE(tokens >= 0 && tokens == kv_tokens_of(v, cache->cache->num_heads(), cache->cache->head_dim()) &&
+                       k->dtype == v->dtype,
+                   "tq_kv_cache_append: keys/values must be [tokens, heads, head_dim] of one float type");
+        cache->cache->append(layer, k->data, v->data, k->dtype, tokens, nullptr);
+        return 0;
+    });
+}
+
+static void* kv_get(tq_kv_cache_t cache, int layer, int start, int end, bool values) {
+    if (!cache || !cache->cache) return nullptr;
+    return guarded<void*>(nullptr, nullptr, [&]() -> void* {
+        TQ_REQUIRE(start < end, "Invalid token range for dequantization");
+        const int shape[3] = {end - start, cache->cache->num_heads(), cache->cache->head_dim()};
+        // validate before allocating
+        TQ_REQUIRE(layer >= 0 && layer < cache->cache->num_layers(), "Layer index out of range");
+        TQ_REQUIRE(start >= 0 && end <= cache->cache->layer_tokens(layer), "Invalid token range for dequantization");
+        tq_array_s* a = new_f16_array(3, shape);
+        try {
+            cache->cache->get_fp16(layer, values, start, end, a->data, nullptr);
+        } catch (...) {
+            tq_array_free(a);
+            throw;
+        }
+        return a;
+    });
+}
+
+void* tq_kv_cache_get_keys_fp16(tq_kv_cache_t cache, int layer, int start, int end) {
+    return kv_get(cache, layer, start, end, false);
+}
+void* tq_kv_cache_get_values_fp16(tq_kv_cache_t cache, int layer, int start, int end) {
+    return kv_get(cache, layer, start, end, true);
+}
+
+void* tq_kv_cache_attention(tq_kv_cache_t cache, int layer, const void* queries_array, int compressed_start,
+                            int compressed_end) {
+    if (!cache || !cache->cache || !queries_array) return nullptr;
+    return guarded<void*>(nullptr, nullptr, [&]() -> void* {
+        const auto* q = static_cast<const tq_array_s*>(queries_array);
+        const int dim = cache->cache->head_dim();
+        TQ_REQUIRE(q->dtype == TQ_F32 || q->dtype == TQ_F16, "tq_kv_cache_attention: queries must be fp32 or fp16");
+        int q_heads = 0;
+        if (q->ndim == 2 && q->shape[1] == dim) q_heads = q->shape[0];
+        else if (q->ndim == 4 && q->shape[0] == 1 && q->shape[2] == 1 && q->shape[3] == dim) q_heads = q->shape[1];
+        else if (q->ndim == 3 && q->shape[0] == 1 && q->shape[2] == dim) q_heads = q->shape[1];
+        TQ_REQUIRE(q_heads > 0, "tq_kv_cache_attention: queries must be [q_heads, d], [1, q_heads, d] or [1, q_heads, 1, d]");
+        tq_array_s* out = new_f16_array(q->ndim, q->shape);
+        try {
+            turboquant::TQKVCache* one[1] = {cache->cache};
+            turboquant::attention_batched(one, 1, layer, q->data, q->dtype, q_heads, &compressed_start, &compressed_end,
+                                          false, out->data, nullptr);
+        } catch (...) {
+            tq_array_free(out);
+            throw;
+        }
+        return out;
+    });
+}
+
+int tq_kv_cache_seq_length(tq_kv_cache_t cache) { return (cache && cache->cache) ? cache->cache->seq_length() : 0; }
+
+void tq_kv_cache_free(tq_kv_cache_t cache) {
+    if (!cache) return;
+    delete cache->cache;
+    delete cache;
+}
+
+// ---- pointer-level variants (declared in turboquant_b200.h) --------------------------------------
+
+int tq_kv_append(tq_kv_cache_t cache, int layer, const void* keys, const void* values, int dtype, int tokens,
+                 void* stream) {
+    return guarded<int>(0, -1, [&]() {
+        TQ_REQUIRE(cache && cache->cache, "tq_kv_append: NULL cache");
+        cache->cache->append(layer, keys, values, dtype, tokens, static_cast<cudaStream_t>(stream));
+        return 0;
+    });
+}
+
+int tq_kv_get_fp16(tq_kv_cache_t cache, int layer, int values, int start, int end, void* out_fp16, void* stream) {
+    return guarded<int>(0, -1, [&]() {
+        TQ_REQUIRE(cache && cache->cache, "tq_kv_get_fp16: NULL cache");
+        cache->cache->get_fp16(layer, values != 0, start, end, out_fp16, static_cast<cudaStream_t>(stream));
+        return 0;
+    });
+}
+
+int tq_kv_export(tq_kv_cache_t cache, int layer, uint32_t* k_words, uint32_t* v_words, float* k_norms, float* v_norms,
+                 uint32_t* qjl_words, float* qjl_norms) {
+    return guarded<int>(0, -1, [&]() {
+        TQ_REQUIRE(cache && cache->cache, "tq_kv_export: NULL cache");
+        return cache->cache->export_layer(layer, k_words, v_words, k_norms, v_norms, qjl_words, qjl_norms);
+    });
+}
+
+int tq_kv_attention(const tq_kv_cache_t* caches, int n_seqs, int layer, const void* queries, int q_dtype, int q_heads,
+                    void* out_fp16, int start, int end, int use_qjl, void* stream) {
+    return guarded<int>(0, -1, [&]() {
+        TQ_REQUIRE(caches && n_seqs > 0, "tq_kv_attention: no caches");
+        std::vector<turboquant::TQKVCache*> cs(static_cast<size_t>(n_seqs));
+        std::vector<int> starts(static_cast<size_t>(n_seqs)), ends(static_cast<size_t>(n_seqs));
+        for (int i = 0; i < n_seqs; ++i) {
+            TQ_REQUIRE(caches[i] && caches[i]->cache, "tq_kv_attention: NULL cache");
+            cs[i] = caches[i]->cache;
+            starts[i] = start;
+            ends[i] = end < 0 ? caches[i]->cache->layer_tokens(layer) : end;
+        }
+        turboquant::attention_batched(cs.data(), n_seqs, layer, queries, q_dtype, q_heads, starts.data(), ends.data(),
+                                      use_qjl != 0, out_fp16, static_cast<cudaStream_t>(stream));
+        return 0;
+    });
+}
+
+}  // extern "C"

@@ -1,0 +1,297 @@
+// TurboQuantLinear on the device, and its C entry points.
+//
+// Mirrors the reference's turboquant::TurboQuantLinear (include/turboquant/linear.h:11-35)
+// and the dequantiser entry points (include/turboquant/dequantizer.h:11-39).  What the
+// reference recomputes on every call — packing mode, "residual present" scan, the
+// 256-entry centroid-sum table (src/dequantizer.cpp:619-643, 674-688) — is decided once
+// when the handle is built.
+#include <cmath>
+
+#include "tq_host.hpp"
+#include "tq_kernels.cuh"
+#include "turboquant_c/turboquant_b200.h"
+
+namespace turboquant {
+
+using tq::DeviceBuffer;
+using tq::Error;
+
+class TurboQuantLinear {
+public:
+    TurboQuantLinear(int in_features, int out_features, const uint8_t* packed_primary, int primary_cols,
+                     const uint8_t* packed_residual, const float* norms, const uint32_t* seeds, const float* cb_p,
+                     int n_p, const float* cb_r, int n_r, uint32_t block)
+        : in_(in_features), out_(out_features), block_(block) {
+        TQ_REQUIRE(in_ > 0 && out_ > 0, "TurboQuantLinear: dimensions must be positive");
+        TQ_REQUIRE(tq::is_pow2(block) && block >= 32 && block <= 1024,
+                   "TurboQuantLinear: block_size must be a power of two in [32, 1024]");
+        TQ_REQUIRE(in_ % static_cast<int>(block) == 0, "in_features must be divisible by block_size");
+        TQ_REQUIRE(static_cast<long>(in_) * out_ < (1L << 32), "TurboQuantLinear: weight too large for 32-bit offsets");
+        TQ_REQUIRE(packed_primary && packed_residual && norms && seeds && cb_p && cb_r, "TurboQuantLinear: NULL argument");
+        TQ_REQUIRE(n_p >= 1 && n_p <= 32 && n_r >= 1 && n_r <= 16, "TurboQuantLinear: bad codebook size");
+        // packing mode from the plane shapes (src/dequantizer.cpp:72-74)
+        if (primary_cols == in_ / 2) primary_5bit_ = false;
+        else if (primary_cols == in_) primary_5bit_ = true;
+        else throw Error("TurboQuantLinear: packed_primary must have in/2 or in columns");
+        device_ = tq::current_device();
+        sm_count_ = tq::sm_count(device_);
+
+        cudaStream_t st = nullptr;
+        uint32_t h_seeds[3];
+        TQ_CUDA(cudaMemcpy(h_seeds, seeds, sizeof h_seeds, cudaMemcpyDefault));
+        seed_p_ = h_seeds[0];
+        seed_r_ = h_seeds[1];
+
+        // codes: reference planes -> joint bytes
+        const size_t n_w = static_cast<size_t>(out_) * in_;
+        DeviceBuffer stage_p, stage_r, flags(2 * sizeof(unsigned int));
+        const uint8_t* d_pp = tq::device_view(packed_primary, static_cast<size_t>(out_) * primary_cols, stage_p, st);
+        const uint8_t* d_pr = tq::device_view(packed_residual, n_w / 2, stage_r, st);
+        codes_.resize(n_w);
+        TQ_CUDA(cudaMemsetAsync(flags.as<void>(), 0, 2 * sizeof(unsigned int), st));
+        tq::launch_relayout(d_pp, d_pr, codes_.as<uint8_t>(), out_, in_, primary_5bit_, flags.as<unsigned int>(), st);
+        unsigned int h_flags[2];
+        TQ_CUDA(cudaMemcpy(h_flags, flags.as<void>(), sizeof h_flags, cudaMemcpyDeviceToHost));
+        TQ_REQUIRE(h_flags[1] == 0, "TurboQuantLinear: 5-bit primary needs residual codes below 8 (5+3 mode)");
+        has_residual_ = h_flags[0] != 0;                 // src/dequantizer.cpp:118-128
+        shared_ = (seed_r_ == 0 && has_residual_);       // src/dequantizer.cpp:133
+        dual_ = has_residual_ && !shared_;
+
+        norms_.resize(static_cast<size_t>(out_) * sizeof(float));
+        TQ_CUDA(cudaMemcpy(norms_.as<void>(), norms, static_cast<size_t>(out_) * sizeof(float), cudaMemcpyDefault));
+
+        // lookup tables over the joint byte
+        std::vector<float> cp(n_p), cr(n_r);
+        TQ_CUDA(cudaMemcpy(cp.data(), cb_p, sizeof(float) * n_p, cudaMemcpyDefault));
+        TQ_CUDA(cudaMemcpy(cr.data(), cb_r, sizeof(float) * n_r, cudaMemcpyDefault));
+        std::vector<float> tables(512, 0.0f);
+        const int p_bits = primary_5bit_ ? 5 : 4;
+        const int p_mask = (1 << p_bits) - 1;
+        auto clamp_p = [&](int i) { return cp[i < n_p ? i : n_p - 1]; };  // src/dequantizer.cpp:92-104
+        auto clamp_r = [&](int i) { return cr[i < n_r ? i : n_r - 1]; };
+        for (int b = 0; b < 256; ++b) {
+            const int pi = b & p_mask, ri = b >> p_bits;
+            if (shared_) {
+                if (!primary_5bit_) {
+                    // the 256-entry table of src/dequantizer.cpp:144-150; entries whose primary
+                    // index lies beyond the codebook stay zero there as well
+                    tables[b] = (pi < n_p) ? cp[pi] + clamp_r(ri) : 0.0f;
+                } else {
+                    tables[b] = clamp_p(pi) + clamp_r(ri);  // src/dequantizer.cpp:192-199
+                }
+            } else {
+                tables[b] = clamp_p(pi);
+                tables[256 + b] = clamp_r(ri);
+            }
+        }
+        tables_.resize(512 * sizeof(float));
+        TQ_CUDA(cudaMemcpy(tables_.as<void>(), tables.data(), 512 * sizeof(float), cudaMemcpyHostToDevice));
+
+        const size_t sb = tq::gemv_scratch_bytes(out_, in_, dual_ ? 2 : 1);
+        if (sb) {
+            scratch_.resize(sb);
+            TQ_CUDA(cudaMemset(scratch_.as<void>(), 0, sb));
+        }
+        status_.resize(sizeof(unsigned int));
+        TQ_CUDA(cudaMemset(status_.as<void>(), 0, sizeof(unsigned int)));
+
+        // One launch on a zero activation: proves on this device, now, that the kernel's
+        // shared-memory layout holds, instead of failing on the first real forward.
+        DeviceBuffer x0(static_cast<size_t>(in_) * sizeof(__half)), y0(static_cast<size_t>(out_) * sizeof(__half));
+        TQ_CUDA(cudaMemset(x0.as<void>(), 0, x0.bytes()));
+        launch_forward(x0.as<__half>(), 1, y0.as<__half>(), nullptr);
+        TQ_CUDA(cudaDeviceSynchronize());
+        check_status();
+    }
+
+    int in_features() const { return in_; }
+    int out_features() const { return out_; }
+    bool shared_rotation() const { return shared_; }
+    bool has_residual() const { return has_residual_; }
+
+    // x: [batch, in] fp16 or fp32, host or device.  y: [batch, out] fp16, host or device.
+    void forward(const void* x, int x_dtype, int batch, void* y, cudaStream_t st) {
+        TQ_REQUIRE(x && y, "TurboQuantLinear::forward: NULL argument");
+        TQ_REQUIRE(batch >= 0, "TurboQuantLinear::forward: negative batch");
+        TQ_REQUIRE(x_dtype == TQ_F32 || x_dtype == TQ_F16, "TurboQuantLinear::forward: x must be fp32 or fp16");
+        if (batch == 0) return;
+        TQ_CUDA(cudaSetDevice(device_));
+        const size_t nx = static_cast<size_t>(batch) * in_, ny = static_cast<size_t>(batch) * out_;
+        const bool x_dev = tq::is_device_pointer(x), y_dev = tq::is_device_pointer(y);
+
+        const __half* d_x;
+        if (x_dtype == TQ_F16) {
+            if (x_dev) d_x = static_cast<const __half*>(x);
+            else {
+                x_f16_.reserve(nx * sizeof(__half));
+                TQ_CUDA(cudaMemcpyAsync(x_f16_.as<void>(), x, nx * sizeof(__half), cudaMemcpyHostToDevice, st));
+                d_x = x_f16_.as<__half>();
+            }
+        } else {
+            const float* d_xf;
+            if (x_dev) d_xf = static_cast<const float*>(x);
+            else {
+                x_f32_.reserve(nx * sizeof(float));
+                TQ_CUDA(cudaMemcpyAsync(x_f32_.as<void>(), x, nx * sizeof(float), cudaMemcpyHostToDevice, st));
+                d_xf = x_f32_.as<float>();
+            }
+            x_f16_.reserve(nx * sizeof(__half));
+            tq::launch_f32_to_f16(d_xf, x_f16_.as<__half>(), static_cast<long>(nx), st);  // src/dequantizer.cpp:691
+            d_x = x_f16_.as<__half>();
+        }
+        __half* d_y;
+        if (y_dev) d_y = static_cast<__half*>(y);
+        else {
+            y_f16_.reserve(ny * sizeof(__half));
+            d_y = y_f16_.as<__half>();
+        }
+        launch_forward(d_x, batch, d_y, st);
+        if (!y_dev) {
+            TQ_CUDA(cudaMemcpyAsync(y, d_y, ny * sizeof(__half), cudaMemcpyDeviceToHost, st));
+            TQ_CUDA(cudaStreamSynchronize(st));
+        }
+    }
+
+    // result: [out, in] fp32 or fp16, host or device.
+    void dequantize(void* result, int dtype, cudaStream_t st) {
+        TQ_REQUIRE(result, "dequantize: NULL result");
+        TQ_REQUIRE(dtype == TQ_F32 || dtype == TQ_F16, "dequantize: result must be fp32 or fp16");
+        TQ_CUDA(cudaSetDevice(device_));
+        const size_t n = static_cast<size_t>(out_) * in_;
+        const size_t es = dtype == TQ_F32 ? 4 : 2;
+        const bool dev = tq::is_device_pointer(result);
+        DeviceBuffer stage;
+        void* d_out = result;
+        if (!dev) {
+            stage.reserve(n * es);
+            d_out = stage.as<void>();
+        }
+        if (dtype == TQ_F32)
+            tq::launch_dequant_f32(codes_.as<uint8_t>(), norms_.as<float>(), tables_.as<float>(), static_cast<float*>(d_out),
+                                   out_, in_, block_, seed_p_, seed_r_, dual_, st);
+        else
+            tq::launch_dequant_f16(codes_.as<uint8_t>(), norms_.as<float>(), tables_.as<float>(), static_cast<__half*>(d_out),
+                                   out_, in_, block_, seed_p_, seed_r_, dual_, st);
+        if (!dev) {
+            TQ_CUDA(cudaMemcpyAsync(result, d_out, n * es, cudaMemcpyDeviceToHost, st));
+            TQ_CUDA(cudaStreamSynchronize(st));
+        }
+    }
+
+    void check_status() {
+        unsigned int h = 0;
+        TQ_CUDA(cudaMemcpy(&h, status_.as<void>(), sizeof h, cudaMemcpyDeviceToHost));
+        TQ_REQUIRE(h == 0, "tq8_gemv: unexpected shared-memory base address on this device; kernel did not run");
+    }
+
+private:
+    // Device pointers only.  Batches above 8 rows are issued as passes of 8.
+    void launch_forward(const __half* d_x, int batch, __half* d_y, cudaStream_t st) {
+        for (int b0 = 0; b0 < batch; b0 += 8) {
+            const int nb = batch - b0 < 8 ? batch - b0 : 8;
+            tq::launch_tq8_gemv(codes_.as<uint8_t>(), norms_.as<float>(), tables_.as<float>(),
+                                d_x + static_cast<size_t>(b0) * in_, d_y + static_cast<size_t>(b0) * out_, out_, in_, nb,
+                                block_, dual_ ? 2 : 1, seed_p_, seed_r_, scratch_.as<void>(),
+                                status_.as<unsigned int>(), sm_count_, st);
+        }
+    }
+
+    int in_, out_;
+    uint32_t block_;
+    int device_ = 0, sm_count_ = 0;
+    bool primary_5bit_ = false, has_residual_ = false, shared_ = false, dual_ = false;
+    uint32_t seed_p_ = 0, seed_r_ = 0;
+    DeviceBuffer codes_, norms_, tables_, scratch_, status_;
+    DeviceBuffer x_f16_, x_f32_, y_f16_;  // staging for host-side callers
+};
+
+}  // namespace turboquant
+
+struct tq_linear_s {
+    turboquant::TurboQuantLinear* impl;
+};
+
+using namespace tq;
+
+extern "C" {
+
+tq_linear_t tq_linear_create(int in_features, int out_features, const uint8_t* packed_primary, int primary_cols,
+                             const uint8_t* packed_residual, const float* norms, const uint32_t* seeds,
+                             const float* primary_centroids, int n_primary, const float* residual_centroids,
+                             int n_residual, uint32_t block) {
+    return guarded<tq_linear_t>(nullptr, nullptr, [&]() -> tq_linear_t {
+        auto* impl = new turboquant::TurboQuantLinear(in_features, out_features, packed_primary, primary_cols,
+                                                      packed_residual, norms, seeds, primary_centroids, n_primary,
+                                                      residual_centroids, n_residual, block);
+        return new tq_linear_s{impl};
+    });
+}
+
+int tq_linear_forward(tq_linear_t lin, const void* x, int x_dtype, int batch, void* y_fp16, void* stream) {
+    return guarded<int>(0, -1, [&]() {
+        TQ_REQUIRE(lin && lin->impl, "tq_linear_forward: NULL handle");
+        lin->impl->forward(x, x_dtype, batch, y_fp16, static_cast<cudaStream_t>(stream));
+        return 0;
+    });
+}
+
+int tq_linear_dequantize(tq_linear_t lin, void* result, int result_dtype, void* stream) {
+    return guarded<int>(0, -1, [&]() {
+        TQ_REQUIRE(lin && lin->impl, "tq_linear_dequantize: NULL handle");
+        lin->impl->dequantize(result, result_dtype, static_cast<cudaStream_t>(stream));
+        return 0;
+    });
+}
+
+int tq_quantize_weight(const float* weight, int out_features, int in_features, const float* primary_centroids,
+                       int n_primary, const float* residual_centroids, int n_residual, int primary_bits,
+                       int residual_bits, uint32_t block, int shared_rotation, uint8_t* packed_primary,
+                       uint8_t* packed_residual, float* norms, uint32_t* seeds, void* stream) {
+    return guarded<int>(0, -1, [&]() {
+        TQ_REQUIRE(weight && primary_centroids && residual_centroids && packed_primary && packed_residual && norms && seeds,
+                   "tq_quantize_weight: NULL argument");
+        TQ_REQUIRE(out_features >= 0 && in_features > 0 && (in_features % 2) == 0, "tq_quantize_weight: bad shape");
+        TQ_REQUIRE(n_primary >= 2 && n_primary <= 32 && n_residual >= 2 && n_residual <= 16, "tq_quantize_weight: bad codebook size");
+        auto st = static_cast<cudaStream_t>(stream);
+        const size_t n = static_cast<size_t>(out_features) * in_features;
+        const size_t pp_bytes = primary_bits <= 4 ? n / 2 : n, pr_bytes = n / 2;
+        std::vector<float> cp(n_primary), cr(n_residual);
+        TQ_CUDA(cudaMemcpy(cp.data(), primary_centroids, sizeof(float) * n_primary, cudaMemcpyDefault));
+        TQ_CUDA(cudaMemcpy(cr.data(), residual_centroids, sizeof(float) * n_residual, cudaMemcpyDefault));
+        DeviceBuffer w_stage, recon(n * sizeof(float)), orig(static_cast<size_t>(out_features) * sizeof(float) + 4);
+        const float* d_w = device_view(weight, n, w_stage, st);
+        const bool pp_dev = is_device_pointer(packed_primary), pr_dev = is_device_pointer(packed_residual),
+                   nm_dev = is_device_pointer(norms);
+        DeviceBuffer pp_stage, pr_stage, nm_stage;
+        uint8_t* d_pp = packed_primary;
+        uint8_t* d_pr = packed_residual;
+        float* d_nm = norms;
+        if (!pp_dev) { pp_stage.reserve(pp_bytes + 4); d_pp = pp_stage.as<uint8_t>(); }
+        if (!pr_dev) { pr_stage.reserve(pr_bytes + 4); d_pr = pr_stage.as<uint8_t>(); }
+        if (!nm_dev) { nm_stage.reserve(static_cast<size_t>(out_features) * 4 + 4); d_nm = nm_stage.as<float>(); }
+        uint32_t seed_p = 0, seed_r = 0;
+        derive_seeds(d_w, n, &seed_p, &seed_r, st);  // src/quantizer.cpp:69-70
+        launch_quantize_weight(d_w, out_features, in_features, cp.data(), n_primary, cr.data(), n_residual, primary_bits,
+                               residual_bits, block, shared_rotation != 0, seed_p, seed_r, d_pp, d_pr, d_nm,
+                               orig.as<float>(), recon.as<float>(), st);
+        if (!pp_dev && pp_bytes) TQ_CUDA(cudaMemcpyAsync(packed_primary, d_pp, pp_bytes, cudaMemcpyDeviceToHost, st));
+        if (!pr_dev && pr_bytes) TQ_CUDA(cudaMemcpyAsync(packed_residual, d_pr, pr_bytes, cudaMemcpyDeviceToHost, st));
+        if (!nm_dev && out_features) TQ_CUDA(cudaMemcpyAsync(norms, d_nm, static_cast<size_t>(out_features) * 4, cudaMemcpyDeviceToHost, st));
+        // seeds = {primary, residual or 0 under shared rotation, block}  (src/quantizer.cpp:255-258)
+        const uint32_t h_seeds[3] = {seed_p, (shared_rotation && residual_bits > 0) ? 0u : seed_r, block};
+        TQ_CUDA(cudaMemcpyAsync(seeds, h_seeds, sizeof h_seeds, cudaMemcpyDefault, st));
+        TQ_CUDA(cudaStreamSynchronize(st));  // scratch and staging buffers die here
+        return 0;
+    });
+}
+
+int tq_linear_in_features(tq_linear_t lin) { return (lin && lin->impl) ? lin->impl->in_features() : 0; }
+int tq_linear_out_features(tq_linear_t lin) { return (lin && lin->impl) ? lin->impl->out_features() : 0; }
+
+void tq_linear_free(tq_linear_t lin) {
+    if (!lin) return;
+    delete lin->impl;
+    delete lin;
+}
+
+}  // extern "C"

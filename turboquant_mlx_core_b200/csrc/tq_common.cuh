@@ -1,0 +1,95 @@
+// Shared device/host helpers for the TurboQuant sm_100a kernels.
+#pragma once
+
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <cstdint>
+#include <stdexcept>
+#include <string>
+
+namespace tq {
+
+// ---- errors --------------------------------------------------------------------
+// Host code throws; the C boundary catches and turns exceptions into status codes
+// plus a thread-local message (no exception crosses the ABI).
+struct Error : std::runtime_error {
+    using std::runtime_error::runtime_error;
+};
+
+inline void cuda_check(cudaError_t e, const char* what, const char* file, int line) {
+    if (e != cudaSuccess) {
+        throw Error(std::string(what) + ": " + cudaGetErrorString(e) + " (" + file + ":" + std::to_string(line) + ")");
+    }
+}
+#define TQ_CUDA(x) ::tq::cuda_check((x), #x, __FILE__, __LINE__)
+#define TQ_REQUIRE(cond, msg)                    \
+    do {                                         \
+        if (!(cond)) throw ::tq::Error(msg);     \
+    } while (0)
+
+// ---- sign hash -----------------------------------------------------------------
+// Same integer hash as the reference's make_signs (src/rotation.cpp:32-42): the index
+// is the position inside the WHT block, so one sign vector serves every block and row.
+__host__ __device__ __forceinline__ bool sign_is_positive(uint32_t seed, uint32_t i) {
+    uint32_t h = seed * 2654435761u + i * 2246822519u;
+    h ^= h >> 16;
+    h *= 0x45d9f3bu;
+    h ^= h >> 16;
+    return (h & 1u) != 0u;
+}
+__host__ __device__ __forceinline__ float sign_value(uint32_t seed, uint32_t i) {
+    return sign_is_positive(seed, i) ? 1.0f : -1.0f;
+}
+
+// QJL key-side sign (src/kv_cache.cpp:249-250): top bit of the un-avalanched hash.
+__host__ __device__ __forceinline__ bool qjl_sign_is_positive(uint32_t seed, uint32_t d) {
+    uint32_t h = seed * 2654435761u + d * 2246822519u;
+    return (h >> 31) != 0u;
+}
+
+// Per-layer KV seeds (src/kv_cache.cpp:32-42). which: 1 = K rotation, 2 = V rotation, 3 = QJL.
+__host__ __device__ __forceinline__ uint32_t kv_layer_seed(uint32_t layer, uint32_t which) {
+    uint32_t h = layer;
+    h ^= which + 0x9e3779b9u + (h << 6) + (h >> 2);
+    h = (h ^ (h >> 16)) * 0x45d9f3bu;
+    h = (h ^ (h >> 16)) * 0x45d9f3bu;
+    h ^= h >> 16;
+    return h;
+}
+
+// ---- warp-level Walsh-Hadamard butterfly -----------------------------------------
+// One warp transforms one block of 32*E values; lane l holds elements [l*E, (l+1)*E).
+// The add tree is the reference's (src/rotation.cpp:14-25): for h = 1, 2, 4, ... the
+// pair (j, j+h) becomes (a+b, a-b) with a the lower index.  Stages h < E stay in
+// registers; stages h >= E exchange with lane ^ (h/E).  Only __fadd_rn/__fsub_rn are
+// used so nothing can be contracted into an FMA: results are bit-identical to the
+// scalar loop.
+template <int E>
+__device__ __forceinline__ void warp_fwht(float (&v)[E], int lane) {
+#pragma unroll
+    for (int h = 1; h < E; h <<= 1) {
+#pragma unroll
+        for (int i = 0; i < E; i += 2 * h) {
+#pragma unroll
+            for (int j = i; j < i + h; ++j) {
+                float a = v[j], b = v[j + h];
+                v[j] = __fadd_rn(a, b);
+                v[j + h] = __fsub_rn(a, b);
+            }
+        }
+    }
+#pragma unroll
+    for (int m = 1; m < 32; m <<= 1) {
+        const bool upper = (lane & m) != 0;
+#pragma unroll
+        for (int j = 0; j < E; ++j) {
+            float other = __shfl_xor_sync(0xffffffffu, v[j], m);
+            // lower lane: mine + other; upper lane: other - mine  (a is the lower index)
+            v[j] = upper ? __fsub_rn(other, v[j]) : __fadd_rn(v[j], other);
+        }
+    }
+}
+
+__host__ __device__ __forceinline__ bool is_pow2(uint32_t v) { return v && !(v & (v - 1)); }
+
+}  // namespace tq

@@ -1,0 +1,197 @@
+// Weight-side kernels that must reproduce the reference bit for bit:
+//   * relayout: the reference's two nibble planes -> one "joint" byte per weight
+//     (primary code in the low bits, residual code above it), the layout every other
+//     kernel streams;
+//   * dequantize: joint codes -> fp32 / fp16 weights in the exact operation order of
+//     dequantize_weight_cpu (src/dequantizer.cpp:52-256):
+//        (centroid sum) * inv_scale -> butterfly -> * (inv_sqrt*sign) -> * norm.
+// Both are pure HBM streams (1 B read per weight; 2 or 4 B written).
+#include <cmath>
+
+#include "tq_common.cuh"
+#include "tq_kernels.cuh"
+
+namespace tq {
+
+// ---- relayout ---------------------------------------------------------------------
+// 4-bit primary: packed byte k of a row holds codes 2k (low nibble) and 2k+1 (high
+// nibble) in both planes (src/quantizer.cpp:33-39).  joint = p | r << 4.
+// 5-bit primary: one primary code per byte, residual still nibble-packed (3-bit codes);
+// joint = p | r << 5.
+__global__ void relayout_kernel(const uint8_t* __restrict__ pp, const uint8_t* __restrict__ pr,
+                                uint8_t* __restrict__ joint, long n_pairs, int primary_5bit,
+                                unsigned int* __restrict__ flags) {
+    unsigned int any_res = 0, bad = 0;
+    for (long i = static_cast<long>(blockIdx.x) * blockDim.x + threadIdx.x; i < n_pairs;
+         i += static_cast<long>(gridDim.x) * blockDim.x) {
+        const uint32_t r = pr[i];
+        any_res |= r;
+        uint32_t j0, j1;
+        if (!primary_5bit) {
+            const uint32_t p = pp[i];
+            j0 = (p & 0x0Fu) | ((r & 0x0Fu) << 4);
+            j1 = (p >> 4) | (r & 0xF0u);
+        } else {
+            const uint32_t p0 = pp[2 * i], p1 = pp[2 * i + 1];
+            // a residual code above 7 or a primary code above 31 does not fit the joint byte
+            bad |= (r & 0x88u) | ((p0 | p1) & 0xE0u);
+            j0 = (p0 & 0x1Fu) | ((r & 0x07u) << 5);
+            j1 = (p1 & 0x1Fu) | (((r >> 4) & 0x07u) << 5);
+        }
+        reinterpret_cast<uchar2*>(joint)[i] = make_uchar2(static_cast<unsigned char>(j0), static_cast<unsigned char>(j1));
+    }
+    if (__any_sync(0xffffffffu, any_res != 0) && (threadIdx.x & 31) == 0) atomicOr(&flags[0], 1u);
+    if (__any_sync(0xffffffffu, bad != 0) && (threadIdx.x & 31) == 0) atomicOr(&flags[1], 1u);
+}
+
+void launch_relayout(const uint8_t* packed_primary, const uint8_t* packed_residual, uint8_t* joint, long out, int in,
+                     bool primary_5bit, unsigned int* flags, cudaStream_t stream) {
+    const long n_pairs = out * (in / 2);
+    if (n_pairs == 0) return;
+    long want = (n_pairs + 255) / 256;
+    int grid = static_cast<int>(want < 148L * 16 ? want : 148L * 16);
+    relayout_kernel<<<grid, 256, 0, stream>>>(packed_primary, packed_residual, joint, n_pairs, primary_5bit ? 1 : 0, flags);
+    TQ_CUDA(cudaGetLastError());
+}
+
+// Inverse of relayout (joint bytes -> the reference's two planes), used when a handle
+// built on this device has to hand its codes back in the reference's format.
+__global__ void unrelayout_kernel(const uint8_t* __restrict__ joint, uint8_t* __restrict__ pp,
+                                  uint8_t* __restrict__ pr, long n_pairs, int primary_5bit) {
+    for (long i = static_cast<long>(blockIdx.x) * blockDim.x + threadIdx.x; i < n_pairs;
+         i += static_cast<long>(gridDim.x) * blockDim.x) {
+        const uchar2 j = reinterpret_cast<const uchar2*>(joint)[i];
+        if (!primary_5bit) {
+            pp[i] = static_cast<uint8_t>((j.x & 0x0F) | ((j.y & 0x0F) << 4));
+            pr[i] = static_cast<uint8_t>((j.x >> 4) | (j.y & 0xF0));
+        } else {
+            pp[2 * i] = j.x & 0x1F;
+            pp[2 * i + 1] = j.y & 0x1F;
+            pr[i] = static_cast<uint8_t>((j.x >> 5) | ((j.y >> 5) << 4));
+        }
+    }
+}
+
+void launch_unrelayout(const uint8_t* joint, uint8_t* packed_primary, uint8_t* packed_residual, long out, int in,
+                       bool primary_5bit, cudaStream_t stream) {
+    const long n_pairs = out * (in / 2);
+    if (n_pairs == 0) return;
+    long want = (n_pairs + 255) / 256;
+    int grid = static_cast<int>(want < 148L * 16 ? want : 148L * 16);
+    unrelayout_kernel<<<grid, 256, 0, stream>>>(joint, packed_primary, packed_residual, n_pairs, primary_5bit ? 1 : 0);
+    TQ_CUDA(cudaGetLastError());
+}
+
+// ---- dequantize ---------------------------------------------------------------------
+// One warp per (row, WHT block).  tables[0..255] is the single-rotation table
+// (centroid sums, or primary centroids alone when no residual is present);
+// for dual rotation tables[0..255] holds the primary centroid and tables[256..511]
+// the residual centroid of each joint byte, and the two chains are rotated with their
+// own sign vectors and added before the norm multiply (src/dequantizer.cpp:214-252).
+template <int E, typename OutT>
+__global__ void __launch_bounds__(256) dequant_kernel(const uint8_t* __restrict__ joint, const float* __restrict__ norms,
+                                                      const float* __restrict__ tables, OutT* __restrict__ out,
+                                                      long rows, int blocks_per_row, uint32_t seed_p, uint32_t seed_r,
+                                                      int dual, float inv_scale, float inv_sqrt) {
+    __shared__ float lut[512];
+    for (int i = threadIdx.x; i < (dual ? 512 : 256); i += blockDim.x) lut[i] = tables[i];
+    __syncthreads();
+
+    constexpr int BS = 32 * E;
+    const int lane = threadIdx.x & 31;
+    const long warp0 = (static_cast<long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+    const long n_warps = (static_cast<long>(gridDim.x) * blockDim.x) >> 5;
+    const long total = rows * blocks_per_row;
+
+    float sp[E], sr[E];
+#pragma unroll
+    for (int j = 0; j < E; ++j) {
+        sp[j] = __fmul_rn(inv_sqrt, sign_value(seed_p, static_cast<uint32_t>(lane * E + j)));
+        sr[j] = __fmul_rn(inv_sqrt, sign_value(seed_r, static_cast<uint32_t>(lane * E + j)));
+    }
+
+    for (long blk = warp0; blk < total; blk += n_warps) {
+        const long row = blk / blocks_per_row;
+        const uint8_t* src = joint + blk * BS + lane * E;
+        uint8_t code[E];
+        if constexpr (E >= 16) {
+#pragma unroll
+            for (int j = 0; j < E; j += 16) {
+                uint4 t = *reinterpret_cast<const uint4*>(src + j);
+                const uint32_t w[4] = {t.x, t.y, t.z, t.w};
+#pragma unroll
+                for (int k = 0; k < 16; ++k) code[j + k] = static_cast<uint8_t>(w[k >> 2] >> (8 * (k & 3)));
+            }
+        } else if constexpr (E == 8) {
+            uint2 t = *reinterpret_cast<const uint2*>(src);
+#pragma unroll
+            for (int k = 0; k < 8; ++k) code[k] = static_cast<uint8_t>((k < 4 ? t.x : t.y) >> (8 * (k & 3)));
+        } else if constexpr (E == 4) {
+            uint32_t t = *reinterpret_cast<const uint32_t*>(src);
+#pragma unroll
+            for (int k = 0; k < 4; ++k) code[k] = static_cast<uint8_t>(t >> (8 * k));
+        } else {
+#pragma unroll
+            for (int k = 0; k < E; ++k) code[k] = src[k];
+        }
+
+        const float norm = norms[row];
+        float v[E];
+#pragma unroll
+        for (int j = 0; j < E; ++j) v[j] = __fmul_rn(lut[code[j]], inv_scale);
+        warp_fwht<E>(v, lane);
+#pragma unroll
+        for (int j = 0; j < E; ++j) v[j] = __fmul_rn(v[j], sp[j]);
+        if (dual) {
+            float u[E];
+#pragma unroll
+            for (int j = 0; j < E; ++j) u[j] = __fmul_rn(lut[256 + code[j]], inv_scale);
+            warp_fwht<E>(u, lane);
+#pragma unroll
+            for (int j = 0; j < E; ++j) v[j] = __fadd_rn(v[j], __fmul_rn(u[j], sr[j]));
+        }
+        OutT* dst = out + blk * BS + lane * E;
+#pragma unroll
+        for (int j = 0; j < E; ++j) {
+            const float w = __fmul_rn(v[j], norm);
+            if constexpr (sizeof(OutT) == 4) dst[j] = w;
+            else dst[j] = __float2half_rn(w);
+        }
+    }
+}
+
+template <typename OutT>
+static void launch_dequant_t(const uint8_t* joint, const float* norms, const float* tables, OutT* out, long rows, int in,
+                             uint32_t block, uint32_t seed_p, uint32_t seed_r, bool dual, cudaStream_t stream) {
+    TQ_REQUIRE(is_pow2(block) && block >= 32 && block <= 1024, "WHT block size must be a power of two in [32, 1024]");
+    TQ_REQUIRE(in % static_cast<int>(block) == 0, "in_features must be divisible by block_size");
+    const int bpr = in / static_cast<int>(block);
+    const long total = rows * bpr;
+    if (total == 0) return;
+    const float inv_scale = 1.0f / std::sqrt(static_cast<float>(in));    // src/dequantizer.cpp:76
+    const float inv_sqrt = 1.0f / std::sqrt(static_cast<float>(block));  // src/rotation.cpp:333
+    long want = (total + 7) / 8;
+    int grid = static_cast<int>(want < 148L * 8 ? want : 148L * 8);
+#define TQ_DQ_CASE(EV)                                                                                            \
+    case 32 * EV:                                                                                                 \
+        dequant_kernel<EV, OutT><<<grid, 256, 0, stream>>>(joint, norms, tables, out, rows, bpr, seed_p, seed_r,  \
+                                                           dual ? 1 : 0, inv_scale, inv_sqrt);                    \
+        break;
+    switch (block) {
+        TQ_DQ_CASE(1) TQ_DQ_CASE(2) TQ_DQ_CASE(4) TQ_DQ_CASE(8) TQ_DQ_CASE(16) TQ_DQ_CASE(32)
+        default: throw Error("unsupported WHT block size");
+    }
+#undef TQ_DQ_CASE
+    TQ_CUDA(cudaGetLastError());
+}
+
+void launch_dequant_f32(const uint8_t* joint, const float* norms, const float* tables, float* out, long rows, int in,
+                        uint32_t block, uint32_t seed_p, uint32_t seed_r, bool dual, cudaStream_t stream) {
+    launch_dequant_t<float>(joint, norms, tables, out, rows, in, block, seed_p, seed_r, dual, stream);
+}
+void launch_dequant_f16(const uint8_t* joint, const float* norms, const float* tables, __half* out, long rows, int in,
+                        uint32_t block, uint32_t seed_p, uint32_t seed_r, bool dual, cudaStream_t stream) {
+    launch_dequant_t<__half>(joint, norms, tables, out, rows, in, block, seed_p, seed_r, dual, stream);
+}
+
+}  // namespace tq

@@ -1,0 +1,54 @@
+// Launchers of the sm_100a kernels (host-callable, asynchronous on `stream`).
+// All pointers are device pointers unless stated otherwise.
+#pragma once
+
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <cstddef>
+#include <cstdint>
+#include <vector>
+
+namespace tq {
+
+// tq_wht.cu — blocked WHT of an fp32 [rows, cols] matrix (forward or inverse), bit-exact.
+void launch_wht_rows(const float* in, float* out, long rows, int cols, uint32_t seed, uint32_t block, bool inverse,
+                     cudaStream_t stream);
+
+// tq_dequant.cu
+// flags[0] is OR-ed with 1 when any residual byte is non-zero, flags[1] when a 5-bit-mode
+// code does not fit the joint byte.
+void launch_relayout(const uint8_t* packed_primary, const uint8_t* packed_residual, uint8_t* joint, long out, int in,
+                     bool primary_5bit, unsigned int* flags, cudaStream_t stream);
+void launch_unrelayout(const uint8_t* joint, uint8_t* packed_primary, uint8_t* packed_residual, long out, int in,
+                       bool primary_5bit, cudaStream_t stream);
+// tables: 256 fp32 (single rotation) or 512 fp32 (dual rotation: primary then residual).
+void launch_dequant_f32(const uint8_t* joint, const float* norms, const float* tables, float* out, long rows, int in,
+                        uint32_t block, uint32_t seed_p, uint32_t seed_r, bool dual, cudaStream_t stream);
+void launch_dequant_f16(const uint8_t* joint, const float* norms, const float* tables, __half* out, long rows, int in,
+                        uint32_t block, uint32_t seed_p, uint32_t seed_r, bool dual, cudaStream_t stream);
+
+// tq_gemv.cu — fused dequantise + GEMV, 1..8 activation rows.  table: [n_planes, 256] fp32
+// (one plane for shared rotation / primary only, two for dual rotation).
+// scratch: gemv_scratch_bytes(out, in) bytes, zero-initialised once (the kernel leaves
+// its counters at zero); may be NULL when that size is 0.  status: one device word,
+// set non-zero by the kernel if its shared-memory layout assumption does not hold.
+size_t gemv_scratch_bytes(int out, int in, int n_planes);
+void launch_tq8_gemv(const uint8_t* codes, const float* norms, const float* table, const __half* x, __half* y,
+                     int out, int in, int batch, uint32_t block, int n_planes, uint32_t seed_p, uint32_t seed_r,
+                     void* scratch, unsigned int* status, int sm_count, cudaStream_t stream);
+
+// tq_quantize.cu — bit-exact weight quantiser.  derive_seeds hashes the sampled bytes
+// of the fp32 weight (synchronises the stream).  launch_quantize_weight: cb_p / cb_r are
+// HOST arrays; d_orig_norm_tmp is [out] fp32 and d_recon_tmp [out, in] fp32 scratch.
+void derive_seeds(const float* d_weight, size_t n_elems, uint32_t* seed_primary, uint32_t* seed_residual,
+                  cudaStream_t stream);
+void launch_quantize_weight(const float* d_weight, long out, int in, const float* cb_p, int n_p, const float* cb_r,
+                            int n_r, int primary_bits, int residual_bits, uint32_t block, bool shared_rotation,
+                            uint32_t seed_p, uint32_t seed_r, uint8_t* d_packed_primary, uint8_t* d_packed_residual,
+                            float* d_norms, float* d_orig_norm_tmp, float* d_recon_tmp, cudaStream_t stream);
+
+// tq_misc.cu — small element-wise helpers.
+void launch_f32_to_f16(const float* in, __half* out, long n, cudaStream_t stream);
+void launch_f16_to_f32(const __half* in, float* out, long n, cudaStream_t stream);
+
+}  // namespace tq
