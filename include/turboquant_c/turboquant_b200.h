@@ -108,6 +108,40 @@ tq_linear_t tq_linear_create(int in_features, int out_features, const uint8_t* p
  *  fp16 first) -> y fp16 [batch, out], fp32 accumulation. */
 int tq_linear_forward(tq_linear_t lin, const void* x, int x_dtype, int batch, void* y_fp16, void* stream);
 
+/** Forward pass that performs no device or host allocation of any kind.
+ *  (No counterpart in the reference: its forward allocates its output and temporaries
+ *  through MLX on every call.)
+ *
+ *  Who needs it: a serving process that, once its models are loaded, gives all remaining
+ *  device memory to its own pool — after that a cudaMalloc from inside a library can fail
+ *  or stall the whole device while the driver synchronises — and any caller that runs the
+ *  layer while a CUDA stream capture is open on the thread, where allocating calls are
+ *  rejected.  tq_linear_forward is unsuitable for both when it has to grow a staging
+ *  buffer; this entry never does.
+ *
+ *  x: DEVICE pointer, fp16 [batch, in]; y: DEVICE pointer, fp16 [batch, out]; batch 1..8.
+ *  Host pointers are refused (copying them would need staging memory).  Results are the
+ *  same as tq_linear_forward's.
+ *
+ *  The working memory the kernels need (rotated activation, partial sums of layers wider
+ *  than 4096 inputs, arrival counters) comes from one fixed array of
+ *  tq_linear_noalloc_scratch_limit() bytes (2 MiB) compiled into the library; each GPU
+ *  that loads the library holds that array until the process ends.  A layer whose need
+ *  8*4*in*planes + 8*4*ceil(in/4096)*planes*out (+ counters) exceeds the limit is refused
+ *  with an error; nothing is truncated.
+ *
+ *  All calls on a device share that array and it keeps the previous call's contents (the
+ *  part that must start at zero is cleared in stream order by each call).  Calls that can
+ *  run at the same time on one GPU — different streams, or different threads — would
+ *  overwrite each other's working memory: keep such calls on one stream or order them
+ *  with events.
+ *
+ *  The first call on each device looks up the array's device address; make that first
+ *  call before any stream capture begins. */
+int tq_linear_forward_noalloc(tq_linear_t lin, const void* x_fp16_device, int batch, void* y_fp16_device, void* stream);
+/** Size in bytes of the built-in working array used by tq_linear_forward_noalloc. */
+size_t tq_linear_noalloc_scratch_limit(void);
+
 /** dequantize_weight_cpu / dequantize_weight_gpu (src/dequantizer.cpp:52-256, 347-451):
  *  result [out, in] as TQ_F32 (bit-identical to the reference's CPU result) or TQ_F16
  *  (the same values rounded to nearest even, src/turboquant_c_dequant.cpp:156-167). */

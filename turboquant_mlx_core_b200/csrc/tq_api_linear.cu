@@ -178,6 +178,19 @@ public:
         }
     }
 
+    // Forward that allocates nothing: device fp16 in, device fp16 out, at most 8 rows, scratch
+    // from the library's built-in array.
+    void forward_static(const void* x, int batch, void* y, cudaStream_t st) {
+        TQ_REQUIRE(x && y, "allocation-free forward: NULL argument");
+        TQ_REQUIRE(batch >= 1 && batch <= 8, "allocation-free forward: batch must be 1..8");
+        TQ_REQUIRE(tq::is_device_pointer(x) && tq::is_device_pointer(y),
+                   "allocation-free forward: x and y must be device pointers (copying host memory would need a staging allocation)");
+        TQ_CUDA(cudaSetDevice(device_));
+        tq::launch_tq8_gemv_static(codes_.as<uint8_t>(), norms_.as<float>(), tables_.as<float>(),
+                                   static_cast<const __half*>(x), static_cast<__half*>(y), out_, in_, batch, block_,
+                                   dual_ ? 2 : 1, seed_p_, seed_r_, status_.as<unsigned int>(), sm_count_, st);
+    }
+
     void check_status() {
         unsigned int h = 0;
         TQ_CUDA(cudaMemcpy(&h, status_.as<void>(), sizeof h, cudaMemcpyDeviceToHost));
@@ -234,6 +247,16 @@ int tq_linear_forward(tq_linear_t lin, const void* x, int x_dtype, int batch, vo
         return 0;
     });
 }
+
+int tq_linear_forward_noalloc(tq_linear_t lin, const void* x_fp16_device, int batch, void* y_fp16_device, void* stream) {
+    return guarded<int>(0, -1, [&]() {
+        TQ_REQUIRE(lin && lin->impl, "tq_linear_forward_noalloc: NULL handle");
+        lin->impl->forward_static(x_fp16_device, batch, y_fp16_device, static_cast<cudaStream_t>(stream));
+        return 0;
+    });
+}
+
+size_t tq_linear_noalloc_scratch_limit(void) { return tq::gemv_static_scratch_capacity(); }
 
 int tq_linear_dequantize(tq_linear_t lin, void* result, int result_dtype, void* stream) {
     return guarded<int>(0, -1, [&]() {

@@ -435,4 +435,50 @@ void launch_tq8_gemv(const uint8_t* codes, const float* norms, const float* tabl
     }
 }
 
+// ---- allocation-free variant ---------------------------------------------------------------
+// Same two kernels, but the scratch (rotated activation, split-K partial sums, arrival
+// counters) lives in a fixed array inside the library image instead of a buffer the handle
+// allocated.  Every GPU that loads the library carries these bytes until the process exits.
+constexpr size_t kStaticScratchBytes = size_t(2) << 20;  // 2 MiB
+static __device__ __align__(256) unsigned char g_gemv_static_scratch[kStaticScratchBytes];
+
+size_t gemv_static_scratch_capacity() { return kStaticScratchBytes; }
+
+// Device address of the array on the current device.  In host code the array's name is only
+// a handle for the runtime, not an address a kernel could use, so the address is looked up
+// once per device (with that device current) and cached.
+static void* static_scratch_address() {
+    static void* cached[64] = {nullptr};
+    int dev = 0;
+    TQ_CUDA(cudaGetDevice(&dev));
+    if (dev >= 0 && dev < 64 && cached[dev]) return cached[dev];
+    void* ptr = nullptr;
+    TQ_CUDA(cudaGetSymbolAddress(&ptr, g_gemv_static_scratch));
+    TQ_REQUIRE(ptr != nullptr, "tq8_gemv: static scratch has no device address");
+    if (dev >= 0 && dev < 64) cached[dev] = ptr;
+    return ptr;
+}
+
+void launch_tq8_gemv_static(const uint8_t* codes, const float* norms, const float* table, const __half* x, __half* y,
+                            int out, int in, int batch, uint32_t block, int n_planes, uint32_t seed_p, uint32_t seed_r,
+                            unsigned int* status, int sm_count, cudaStream_t stream) {
+    const size_t need = gemv_scratch_bytes(out, in, n_planes);
+    if (need > kStaticScratchBytes)
+        throw Error("allocation-free forward: this layer needs " + std::to_string(need) +
+                    " bytes of scratch, the built-in array holds " + std::to_string(kStaticScratchBytes));
+    void* scratch = static_scratch_address();
+    // The array is shared by every call and keeps what the last one left.  The arrival
+    // counters are the only part that must read zero at kernel start; the kernels re-zero
+    // them on exit, but a call cut short (device error, aborted process sharing the context)
+    // would leave them dirty, so they are cleared here, in stream order.
+    const size_t xrot_bytes = align256(static_cast<size_t>(n_planes) * 8 * in * sizeof(float));
+    if (need > xrot_bytes) {
+        const int n_row_tiles = (out + 15) / 16;
+        const size_t counter_bytes = align256(static_cast<size_t>(n_row_tiles) * sizeof(unsigned int));
+        TQ_CUDA(cudaMemsetAsync(static_cast<uint8_t*>(scratch) + need - counter_bytes, 0, counter_bytes, stream));
+    }
+    launch_tq8_gemv(codes, norms, table, x, y, out, in, batch, block, n_planes, seed_p, seed_r, scratch, status, sm_count,
+                    stream);
+}
+
 }  // namespace tq

@@ -37,6 +37,13 @@ void launch_tq8_gemv(const uint8_t* codes, const float* norms, const float* tabl
                      int out, int in, int batch, uint32_t block, int n_planes, uint32_t seed_p, uint32_t seed_r,
                      void* scratch, unsigned int* status, int sm_count, cudaStream_t stream);
 
+// Allocation-free variant: scratch is a fixed array in the library image
+// (gemv_static_scratch_capacity() bytes); throws if the layer needs more.
+size_t gemv_static_scratch_capacity();
+void launch_tq8_gemv_static(const uint8_t* codes, const float* norms, const float* table, const __half* x, __half* y,
+                            int out, int in, int batch, uint32_t block, int n_planes, uint32_t seed_p, uint32_t seed_r,
+                            unsigned int* status, int sm_count, cudaStream_t stream);
+
 // tq_quantize.cu — bit-exact weight quantiser.  derive_seeds hashes the sampled bytes
 // of the fp32 weight (synchronises the stream).  launch_quantize_weight: cb_p / cb_r are
 // HOST arrays; d_orig_norm_tmp is [out] fp32 and d_recon_tmp [out, in] fp32 scratch.
