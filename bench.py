@@ -196,6 +196,8 @@ def run_cuda(args):
     stream.synchronize()
     launch_mode = "CUDA graph of one GEMV per layer"
     try:
+        if args.no_graph:
+            raise RuntimeError("graph disabled by flag")
         graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(graph, stream=stream):
             one_pass()
@@ -523,6 +525,7 @@ def main():
     ap.add_argument("--attn-ctx", type=int, default=32768)
     ap.add_argument("--no-extras", action="store_true", help="skip the attention and LM-head measurements")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-graph", action="store_true", help="time plain stream launches instead of a CUDA graph")
     a = ap.parse_args()
     if a.impl == "reference":
         a.steps = a.steps if a.steps is not None else 5

@@ -14,7 +14,8 @@
 // one's set-up overlaps whatever precedes it in the stream:
 //   rotate_x_kernel   x fp16 [b, in] -> xrot fp32 (TF32-rounded) [b, in] in scratch
 //   tq8_gemv_kernel   persistent, one CTA per SM, 16 warps:
-//     HBM --(128-bit loads, 16 codes each)--> registers --(byte -> address, 1 PRMT)-->
+//     HBM --(128-bit loads, 16 codes each, two 64-column steps ahead)--> registers
+//     --(byte -> address, 1 PRMT)-->
 //     shared-memory table (lane-private columns: bank-conflict free by construction)
 //     --> TF32 A fragments --> mma.sync m16n8k8 against xrot held in registers as B
 //     fragments --> fp32 accumulators --> cross-warp sum in shared memory --> y.
@@ -42,6 +43,7 @@
 // residual centroid against x rotated with the residual seed; planes are just further
 // partial-sum slots.
 #include <cmath>
+#include <cstdlib>
 
 #include "tq_common.cuh"
 #include "tq_kernels.cuh"
@@ -56,7 +58,8 @@ constexpr int kSlice = 256;               // columns per warp
 constexpr int kChunk = kWarps * kSlice;   // columns per unit
 constexpr uint32_t kLutAddr = 0x10000u;   // shared-window address of the table
 constexpr uint32_t kLutBytes = 0x10000u;  // 256 entries * 256 B
-constexpr int kRedFloats = kWarps * 128;  // one 16x8 tile per warp
+constexpr int kRedBytes = 16384;           // partial-sum ring: ring * 16 warps * 16 rows * bp floats
+constexpr int kMaxRing = 16;
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
 
@@ -75,19 +78,6 @@ __device__ __forceinline__ float to_tf32(float v) {
     uint32_t r;
     asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(v));
     return __uint_as_float(r);
-}
-__device__ __forceinline__ uint4 ldg_stream(const uint8_t* p) {
-    uint4 v;
-    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0, %1, %2, %3}, [%4];"
-                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
-                 : "l"(p));
-    return v;
-}
-__device__ __forceinline__ void mma_tf32(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
-                                         uint32_t b1) {
-    asm("mma.sync.aligned.m16n8k8.row.col.f32.tf32.tf32.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
-        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
-        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 // Wait for the kernel launched before this one in the stream (no-op without the
 // programmatic-serialization launch attribute).
@@ -142,7 +132,7 @@ struct GemvArgs {
     const float* xrot;      // [n_planes, batch, in] fp32 (TF32-rounded)
     __half* y;              // [batch, out]
     float* partial;         // [n_slots, 8, out_pad] (only when n_slots > 1)
-    unsigned int* counters; // [n_row_tiles]         (only when n_slots > 1)
+    unsigned int* counters; // [n_row_units]         (only when n_slots > 1)
     unsigned int* status;   // device error word (0 = ok)
     int out, in, batch;
     int n_row_units, n_chunks, n_slots, out_pad;  // n_slots = n_planes * n_chunks
@@ -150,86 +140,299 @@ struct GemvArgs {
     float inv_scale;
 };
 
-__global__ void __launch_bounds__(kThreads, 1) tq8_gemv_kernel(const GemvArgs p) {
+// Shared memory holds only the table and the partial-sum ring: the dynamic allocation ends at
+// the end of the table (128 KB).  Asking for much more than that shrinks the L1 side of the
+// SM's memory and with it the number of global loads the SM keeps in flight (measured: a
+// streaming read drops from 5.8 to 3.4 TB/s when a CTA holds 216 KB), so the codes are never
+// staged through shared memory: they go from HBM straight into registers.
+constexpr size_t kGemvSmem = kLutAddr + kLutBytes;  // dynamic bytes requested (window end)
+constexpr int kConsumerThreads = kThreads;
+constexpr int kCtaThreads = kThreads;
+constexpr unsigned long long kWaitLimitNs = 200ull * 1000 * 1000;  // bounded waits: give up after 0.2 s and flag it
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+// Returns false if the phase did not complete within the spin limit.
+__device__ __forceinline__ unsigned long long global_timer_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+#ifdef TQ_GEMV_TIMING
+// Cycle accounting for development builds: [0] waits for codes, [1] waits for "tiles written",
+// [2] waits for "buffer read", [3] whole kernel (per warp, summed over all warps).
+__device__ unsigned long long g_gemv_timing[8];
+#define TQ_TIMED_WAIT(slot, expr)                                     \
+    [&]() {                                                           \
+        const long long t_ = clock64();                               \
+        const bool ok_ = (expr);                                      \
+        if (lane == 0) atomicAdd(&g_gemv_timing[slot], static_cast<unsigned long long>(clock64() - t_)); \
+        return ok_;                                                   \
+    }()
+#else
+#define TQ_TIMED_WAIT(slot, expr) (expr)
+#endif
+
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+    unsigned long long t0 = 0;
+    for (uint32_t spin = 0;; ++spin) {
+        uint32_t done;
+        asm volatile(
+            "{ .reg .pred p; mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2; selp.u32 %0, 1, 0, p; }"
+            : "=r"(done)
+            : "r"(bar), "r"(parity)
+            : "memory");
+        if (done) return true;
+        if (spin == 64) t0 = global_timer_ns();
+        if (spin > 64 && (spin & 63) == 0 && global_timer_ns() - t0 > kWaitLimitNs) return false;
+    }
+}
+__device__ __forceinline__ uint4 ldg_stream(const uint8_t* p) {
+    uint4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                 : "l"(p));
+    return v;
+}
+__device__ __forceinline__ void named_barrier_sync(int id, int threads) {
+    asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
+}
+
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+// Table lookup.  Not volatile: the table is read-only while lookups run, so the compiler may
+// batch and reorder these loads freely (the address depends on codes loaded after the
+// barrier that publishes the table, which keeps them below it).
+__device__ __forceinline__ uint32_t lut_load(uint32_t addr) {
+#if defined(TQ_ABLATE) && (TQ_ABLATE == 2 || TQ_ABLATE >= 3)
+    return addr;  // development ablation: no table lookup
+#else
+    uint32_t v;
+    asm("ld.shared.b32 %0, [%1];" : "=r"(v) : "r"(addr));
+    return v;
+#endif
+}
+__device__ __forceinline__ void mma_tf32(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                         uint32_t b1) {
+#if defined(TQ_ABLATE) && (TQ_ABLATE == 1 || TQ_ABLATE >= 3)
+    // development ablation: no tensor-core instruction, keep the data dependencies
+    c[0] = __uint_as_float(__float_as_uint(c[0]) ^ a0 ^ b0);
+    c[1] = __uint_as_float(__float_as_uint(c[1]) ^ a1 ^ b1);
+    c[2] = __uint_as_float(__float_as_uint(c[2]) ^ a2);
+    c[3] = __uint_as_float(__float_as_uint(c[3]) ^ a3);
+#else
+    asm("mma.sync.aligned.m16n8k8.row.col.f32.tf32.tf32.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+#endif
+}
+
+// BP = activation rows padded to 1, 2, 4 or 8 (compile time, so that the partial-sum ring
+// geometry and the reduction need no runtime arithmetic).
+template <int BP>
+__global__ void __launch_bounds__(kCtaThreads, 1) tq8_gemv_kernel(const GemvArgs p) {
+    constexpr int kRing = (kRedBytes / (kWarps * 16 * BP * 4)) > kMaxRing ? kMaxRing : (kRedBytes / (kWarps * 16 * BP * 4));
+    constexpr int kLag = kRing / 2;                       // how many units behind the sums run
+    constexpr uint32_t kSlotBytes = kWarps * 16 * BP * 4;  // one ring slot: [warp][16 rows][BP] floats
+    constexpr int kPer = BP >= 2 ? BP / 2 : 1;            // floats a lane adds in the reduction
+
     extern __shared__ __align__(128) uint8_t smem_raw[];
-    __shared__ unsigned int s_last;
+    __shared__ unsigned int s_abort;
+    // [0..kRing) "tiles of ring slot written" (one arrival per warp), [kMaxRing..) "slot read"
+    __shared__ __align__(8) unsigned long long s_bars[2 * kMaxRing];
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int g = lane >> 2, q = lane & 3;
 
-    // ---- unit range of this CTA: unit = (slot, row tile), slot = plane * n_chunks + chunk ----
+    // ---- unit range of this CTA: unit = (slot, row unit), slot = plane * n_chunks + chunk ----
     const int n_units = p.n_row_units * p.n_slots;
     const int u_begin = static_cast<int>(static_cast<long>(n_units) * blockIdx.x / gridDim.x);
     const int u_end = static_cast<int>(static_cast<long>(n_units) * (blockIdx.x + 1) / gridDim.x);
     if (u_begin >= u_end) return;
+    const int n_local = u_end - u_begin;
 
-    // ---- shared-memory map: [reduction buffers | ... | table at 0x10000] ----
+    // ---- shared-memory map: [partial-sum ring | unused | table at 0x10000] ----
     const uint32_t base = smem_u32(smem_raw);
-    const uint32_t red_addr = (base + 127u) & ~127u;  // 2 buffers of kRedFloats
-    if (red_addr + 2u * kRedFloats * 4u > kLutAddr) {  // layout assumption broken: refuse to run
+    const uint32_t red_addr = (base + 127u) & ~127u;
+    if (red_addr + kRedBytes > kLutAddr) {  // layout assumption broken: refuse to run
         if (tid == 0) atomicExch(p.status, 1u);
         return;
     }
-
-    // ---- first unit's code loads go out before anything else (weights never depend on
-    //      the kernel that runs before this one) ----
-    const int tile_in_unit = warp / p.wpt;                 // which of the unit's row tiles this warp works on
-    const int slice0 = (warp - tile_in_unit * p.wpt) * kSlice;  // column of this warp's slice inside the chunk
-    // byte offset of (row g, this thread's 16 columns) inside a unit; matrices stay below 4 GiB
-    const uint32_t thread_off = static_cast<uint32_t>(g) * static_cast<uint32_t>(p.in) + static_cast<uint32_t>(slice0 + 16 * q);
-    const uint32_t row8_off = 8u * static_cast<uint32_t>(p.in);
-    uint4 a[4][2];
-    auto load_step = [&](int s, int kc, int ru) {
-        const int c = kc * kChunk + slice0 + 16 * q + 64 * s;
-        const int rt = ru * p.tpu + tile_in_unit;
-        const int r0 = rt * 16 + g;
-        const uint32_t off = static_cast<uint32_t>(rt) * 16u * static_cast<uint32_t>(p.in) +
-                             static_cast<uint32_t>(kc * kChunk + 64 * s) + thread_off;
-        const bool ok = c < p.in;
-        a[s][0] = (ok && r0 < p.out) ? ldg_stream(p.codes + off) : make_uint4(0, 0, 0, 0);
-        a[s][1] = (ok && r0 + 8 < p.out) ? ldg_stream(p.codes + off + row8_off) : make_uint4(0, 0, 0, 0);
-    };
-    {
-        const int slot0 = u_begin / p.n_row_units;
-        const int rt0 = u_begin - slot0 * p.n_row_units;
-#pragma unroll
-        for (int s = 0; s < 4; ++s) load_step(s, slot0 % p.n_chunks, rt0);
+    const uint32_t bar_written = smem_u32(&s_bars[0]), bar_read = smem_u32(&s_bars[kMaxRing]);
+    if (tid == 0) {
+        for (int i = 0; i < kRing; ++i) {
+            mbar_init(bar_written + 8u * i, kWarps);
+            mbar_init(bar_read + 8u * i, kWarps);
+        }
+        s_abort = 0u;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
 
+    const int g = lane >> 2, q = lane & 3;
+    const int tile_in_unit = warp / p.wpt;                      // which of the unit's row tiles this warp works on
+    const int slice0 = (warp - tile_in_unit * p.wpt) * kSlice;  // column of this warp's slice inside the chunk
     const uint32_t lane_const = 0x00010000u | static_cast<uint32_t>(lane * 4);
+    const size_t unit_stride = static_cast<size_t>(p.tpu) * 16 * p.in;  // bytes between consecutive row units
+    const size_t row8 = 8 * static_cast<size_t>(p.in);
+
+    // ---- position of a unit, kept incrementally (no divisions in the loop) ----
+    struct Pos {
+        int slot, ru;          // slot and row unit
+        const uint8_t* ptr;    // this thread's first 16 codes of the unit (row g)
+        uint32_t ok;           // bit s: columns of step s valid; bit 4: row g valid; bit 5: row g+8 valid
+    };
+    auto make_pos = [&](int unit) {
+        Pos u;
+        u.slot = unit / p.n_row_units;
+        u.ru = unit - u.slot * p.n_row_units;
+        const int c = (u.slot % p.n_chunks) * kChunk + slice0 + 16 * q;
+        const int r0 = (u.ru * p.tpu + tile_in_unit) * 16 + g;
+        u.ptr = p.codes + static_cast<size_t>(r0) * p.in + c;
+        u.ok = 0;
+#pragma unroll
+        for (int s = 0; s < 4; ++s) u.ok |= (c + 64 * s < p.in) ? (1u << s) : 0u;
+        u.ok |= (r0 < p.out ? 16u : 0u) | (r0 + 8 < p.out ? 32u : 0u);
+        return u;
+    };
+    auto next_pos = [&](const Pos& u) {
+        Pos n = u;
+        if (u.ru + 1 < p.n_row_units) {   // same slot, next row unit: only the rows move
+            n.ru = u.ru + 1;
+            n.ptr = u.ptr + unit_stride;
+            const int r0 = (n.ru * p.tpu + tile_in_unit) * 16 + g;
+            n.ok = (u.ok & 15u) | (r0 < p.out ? 16u : 0u) | (r0 + 8 < p.out ? 32u : 0u);
+            return n;
+        }
+        return make_pos((u.slot + 1) * p.n_row_units);
+    };
+    // Codes never depend on the kernel before this one, so the first loads go out before the
+    // dependency wait below.  Pieces outside the matrix read as zero.
+    auto load_step = [&](const Pos& u, int s, bool live, uint4& lo, uint4& hi) {
+        const bool c_ok = live && ((u.ok >> s) & 1u);
+        lo = (c_ok && (u.ok & 16u)) ? ldg_stream(u.ptr + 64 * s) : make_uint4(0, 0, 0, 0);
+        hi = (c_ok && (u.ok & 32u)) ? ldg_stream(u.ptr + 64 * s + row8) : make_uint4(0, 0, 0, 0);
+    };
+    Pos cur = make_pos(u_begin);
+    Pos nxt = (n_local > 1) ? next_pos(cur) : cur;
+    uint4 lo0, hi0, lo1, hi1;  // even / odd step, two steps in flight
+    load_step(cur, 0, true, lo0, hi0);
+    load_step(cur, 1, true, lo1, hi1);
+
     auto build_table = [&](int plane) {
         // 256 entries x 32 copies; a thread writes 4 consecutive copies per store
         const int copy4 = (tid & 7) * 4;
-        for (int e = tid >> 3; e < 256; e += kThreads / 8) {
+        for (int e = tid >> 3; e < 256; e += kConsumerThreads / 8) {
             const float v = to_tf32(__ldg(p.table + plane * 256 + e));
             sts_v4(kLutAddr + static_cast<uint32_t>(e) * 256u + static_cast<uint32_t>(copy4) * 4u, v, v, v, v);
         }
     };
-    int staged_plane = (u_begin / p.n_row_units) / p.n_chunks;
+    int staged_plane = cur.slot / p.n_chunks;
     build_table(staged_plane);
 
     // Everything below reads or writes data the preceding kernels produce or still use.
     grid_dependency_sync();
-    __syncthreads();  // table visible
+    __syncthreads();  // table and barriers visible
+
+    // ---- sum of one unit's per-warp partial tiles ----
+    // Ring slot layout: [warp][16 rows][BP] floats.  Warp w owns the (tile, row) pairs
+    // w*tpu .. w*tpu+tpu-1 of the unit; lane l reads what warp (l & 15) of that row tile's
+    // group wrote, activation columns (l >> 4) * kPer .., and a fixed shuffle tree adds the
+    // 16 (fixed order: results do not depend on timing).
+    const int pw = lane & 15, hv = lane >> 4;
+    const int n0 = BP >= 2 ? hv * kPer : 0;
+    const bool red_active = pw < p.wpt && (BP >= 2 || hv == 0);
+    const bool red_writer = pw == 0 && (BP >= 2 || hv == 0);
+    auto reduce_unit = [&](int slot, int ru, int rs, uint32_t parity) {
+        if (!mbar_wait(bar_written + 8u * rs, parity)) {
+            atomicExch(p.status, 5u);
+            atomicExch(&s_abort, 1u);
+        }
+        for (int j = 0; j < p.tpu; ++j) {
+            const int pi = warp * p.tpu + j, t = pi >> 4, r = pi & 15;
+            const int row = (ru * p.tpu + t) * 16 + r;
+            const bool wr = red_writer && row < p.out;
+            // the norm is fetched first so that its latency hides behind the shuffles
+            const float sc = wr ? __ldg(p.norms + row) * p.inv_scale : 0.f;
+            float v[kPer];
+#pragma unroll
+            for (int k = 0; k < kPer; ++k) v[k] = 0.f;
+            if (red_active) {
+                const uint32_t src = red_addr + static_cast<uint32_t>(rs) * kSlotBytes +
+                                     static_cast<uint32_t>(((t * p.wpt + pw) * 16 + r) * BP + n0) * 4u;
+                if constexpr (kPer == 4) asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v[0]), "=f"(v[1]), "=f"(v[2]), "=f"(v[3]) : "r"(src));
+                else if constexpr (kPer == 2) asm volatile("ld.shared.v2.f32 {%0, %1}, [%2];" : "=f"(v[0]), "=f"(v[1]) : "r"(src));
+                else asm volatile("ld.shared.f32 %0, [%1];" : "=f"(v[0]) : "r"(src));
+            }
+#pragma unroll
+            for (int o = 1; o < 16; o <<= 1) {
+#pragma unroll
+                for (int k = 0; k < kPer; ++k) v[k] += __shfl_xor_sync(0xffffffffu, v[k], o);
+            }
+            if (wr) {
+#pragma unroll
+                for (int k = 0; k < kPer; ++k) {
+                    const int n = n0 + k;
+                    if (p.n_slots == 1) {
+                        if (n < p.batch) p.y[static_cast<size_t>(n) * p.out + row] = __float2half_rn(v[k] * sc);
+                    } else {
+                        p.partial[(static_cast<size_t>(slot) * 8 + n) * p.out_pad + row] = v[k];
+                    }
+                }
+            }
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar_read + 8u * rs);
+        if (p.n_slots > 1) {
+            // Row units spread over several slots: every warp counts in; the warp that brings the
+            // count to n_slots * 16 adds the slots' partial sums in slot order and writes y.
+            __threadfence();
+            __syncwarp();
+            unsigned int last = 0;
+            if (lane == 0) {
+                const unsigned int target = static_cast<unsigned int>(p.n_slots * kWarps);
+                const unsigned int prev = atomicAdd(&p.counters[ru], 1u);
+                last = (prev == target - 1u) ? 1u : 0u;
+                if (last) p.counters[ru] = 0u;  // ready for the next launch
+            }
+            last = __shfl_sync(0xffffffffu, last, 0);
+            if (last) {
+                __threadfence();
+                const int n_out = p.tpu * 16 * BP;
+                for (int idx = lane; idx < n_out; idx += 32) {
+                    const int n = idx % BP, tr = idx / BP;
+                    const int row = ru * p.tpu * 16 + tr;
+                    if (row < p.out && n < p.batch) {
+                        float total = 0.f;
+                        for (int c = 0; c < p.n_slots; ++c)
+                            total += __ldcg(p.partial + (static_cast<size_t>(c) * 8 + n) * p.out_pad + row);
+                        p.y[static_cast<size_t>(n) * p.out + row] = __float2half_rn(total * (p.norms[row] * p.inv_scale));
+                    }
+                }
+            }
+        }
+    };
 
     uint32_t bfrag[4][16];
     int staged_slot = -1;
-    int buf = 0;
+    // ring bookkeeping: slot / parity for the unit being written and the unit being summed
+    int ws = 0;             // write slot = i % kRing
+    uint32_t wpar = 0;      // parity of the "read" phase the writer waits for = ((i / kRing) - 1) & 1
+    int rs = 0;             // slot of the unit being summed = (i - kLag) % kRing
+    uint32_t rpar = 0;      // parity of its "written" phase = ((i - kLag) / kRing) & 1
+    Pos red = cur;          // position of the unit being summed
 
-    for (int unit = u_begin; unit < u_end; ++unit) {
-        const int slot = unit / p.n_row_units;
-        const int rt = unit - slot * p.n_row_units;
-        const int plane = slot / p.n_chunks, kc = slot - plane * p.n_chunks;
-
-        if (slot != staged_slot) {
+    for (int i = 0; i < n_local; ++i) {
+        const int plane = cur.slot / p.n_chunks;
+        if (cur.slot != staged_slot) {
             if (plane != staged_plane) {
-                __syncthreads();  // nobody still reads the previous table
+                named_barrier_sync(1, kConsumerThreads);  // nobody still reads the previous table
                 build_table(plane);
-                __syncthreads();
+                named_barrier_sync(1, kConsumerThreads);
                 staged_plane = plane;
             }
             // B fragment of MMA (s, m): k = q -> column 64 s + 16 q + 2 m, k = q+4 -> the next column; n = g.
-            const int col0 = kc * kChunk + slice0 + 16 * q;
+            const int col0 = (cur.slot - plane * p.n_chunks) * kChunk + slice0 + 16 * q;
             const float* xr = p.xrot + (static_cast<size_t>(plane) * p.batch + g) * p.in + col0;
             const bool have_row = g < p.batch;
 #pragma unroll
@@ -244,94 +447,90 @@ __global__ void __launch_bounds__(kThreads, 1) tq8_gemv_kernel(const GemvArgs p)
                     bfrag[s][k + 3] = __float_as_uint(t.w);
                 }
             }
-            staged_slot = slot;
+            staged_slot = cur.slot;
         }
+        const bool has_next = i + 1 < n_local;
 
         float acc0[4] = {0.f, 0.f, 0.f, 0.f}, acc1[4] = {0.f, 0.f, 0.f, 0.f};
-        const bool has_next = (unit + 1) < u_end;
-        int nkc = kc, nrt = rt + 1;
-        if (nrt == p.n_row_units) { nrt = 0; nkc = (kc + 1 == p.n_chunks) ? 0 : kc + 1; }
 #pragma unroll
         for (int s = 0; s < 4; ++s) {
-            const uint32_t lo[4] = {a[s][0].x, a[s][0].y, a[s][0].z, a[s][0].w};
-            const uint32_t hi[4] = {a[s][1].x, a[s][1].y, a[s][1].z, a[s][1].w};
+            uint4& lo = (s & 1) ? lo1 : lo0;
+            uint4& hi = (s & 1) ? hi1 : hi0;
+            const uint32_t wl[4] = {lo.x, lo.y, lo.z, lo.w};
+            const uint32_t wh[4] = {hi.x, hi.y, hi.z, hi.w};
+            // the words are copied out: refill the pair with the step two ahead
+            if (s < 2) load_step(cur, s + 2, true, lo, hi);
+            else load_step(nxt, s - 2, has_next, lo, hi);
+            // 16 independent lookups, then the 4 MMAs they feed (bytes 0,1 of a word feed one
+            // MMA, bytes 2,3 the next); two accumulator chains.
 #pragma unroll
-            for (int w = 0; w < 4; ++w) {
-                // bytes 0,1 of the word feed one MMA, bytes 2,3 the next; two accumulator
-                // chains keep consecutive MMAs independent
-                {
-                    const float a0 = lds_f32(lut_addr<0>(lo[w], lane_const));
-                    const float a2 = lds_f32(lut_addr<1>(lo[w], lane_const));
-                    const float a1 = lds_f32(lut_addr<0>(hi[w], lane_const));
-                    const float a3 = lds_f32(lut_addr<1>(hi[w], lane_const));
-                    mma_tf32(acc0, __float_as_uint(a0), __float_as_uint(a1), __float_as_uint(a2), __float_as_uint(a3),
-                             bfrag[s][4 * w + 0], bfrag[s][4 * w + 1]);
+            for (int h = 0; h < 2; ++h) {
+                uint32_t av[16];
+#pragma unroll
+                for (int w2 = 0; w2 < 2; ++w2) {
+                    const uint32_t l = wl[2 * h + w2], u = wh[2 * h + w2];
+                    av[8 * w2 + 0] = lut_load(lut_addr<0>(l, lane_const));
+                    av[8 * w2 + 1] = lut_load(lut_addr<0>(u, lane_const));
+                    av[8 * w2 + 2] = lut_load(lut_addr<1>(l, lane_const));
+                    av[8 * w2 + 3] = lut_load(lut_addr<1>(u, lane_const));
+                    av[8 * w2 + 4] = lut_load(lut_addr<2>(l, lane_const));
+                    av[8 * w2 + 5] = lut_load(lut_addr<2>(u, lane_const));
+                    av[8 * w2 + 6] = lut_load(lut_addr<3>(l, lane_const));
+                    av[8 * w2 + 7] = lut_load(lut_addr<3>(u, lane_const));
                 }
-                {
-                    const float a0 = lds_f32(lut_addr<2>(lo[w], lane_const));
-                    const float a2 = lds_f32(lut_addr<3>(lo[w], lane_const));
-                    const float a1 = lds_f32(lut_addr<2>(hi[w], lane_const));
-                    const float a3 = lds_f32(lut_addr<3>(hi[w], lane_const));
-                    mma_tf32(acc1, __float_as_uint(a0), __float_as_uint(a1), __float_as_uint(a2), __float_as_uint(a3),
-                             bfrag[s][4 * w + 2], bfrag[s][4 * w + 3]);
+#pragma unroll
+                for (int w2 = 0; w2 < 2; ++w2) {
+                    const int w = 2 * h + w2;
+                    mma_tf32(acc0, av[8 * w2 + 0], av[8 * w2 + 1], av[8 * w2 + 2], av[8 * w2 + 3], bfrag[s][4 * w + 0],
+                             bfrag[s][4 * w + 1]);
+                    mma_tf32(acc1, av[8 * w2 + 4], av[8 * w2 + 5], av[8 * w2 + 6], av[8 * w2 + 7], bfrag[s][4 * w + 2],
+                             bfrag[s][4 * w + 3]);
                 }
             }
-            if (has_next) load_step(s, nkc, nrt);  // registers of step s are dead now: refill from the next unit
         }
-        if (!has_next) grid_launch_dependents();  // last unit's codes are in: the next kernel may start setting up
+        if (!has_next) grid_launch_dependents();  // the next kernel may start setting up
 
-        // ---- cross-warp sum of the 16 per-warp 16x8 tiles ----
-        const uint32_t red = red_addr + static_cast<uint32_t>(buf * kRedFloats + warp * 128) * 4u;
-        sts_f32(red + static_cast<uint32_t>(g * 8 + 2 * q) * 4u, acc0[0] + acc1[0]);
-        sts_f32(red + static_cast<uint32_t>(g * 8 + 2 * q + 1) * 4u, acc0[1] + acc1[1]);
-        sts_f32(red + static_cast<uint32_t>((g + 8) * 8 + 2 * q) * 4u, acc0[2] + acc1[2]);
-        sts_f32(red + static_cast<uint32_t>((g + 8) * 8 + 2 * q + 1) * 4u, acc0[3] + acc1[3]);
-        __syncthreads();
-        // thread idx -> (tile of the unit, row in tile, activation row n)
-        for (int idx = tid; idx < p.tpu * 128; idx += kThreads) {
-            const int t = idx >> 7, e = idx & 127;
-            const int n = e & 7;
-            const int row = (rt * p.tpu + t) * 16 + (e >> 3);
-            const uint32_t src = red_addr + static_cast<uint32_t>(buf * kRedFloats + t * p.wpt * 128 + e) * 4u;
-            float sum = 0.f;
-            for (int w = 0; w < p.wpt; ++w) sum += lds_f32(src + static_cast<uint32_t>(w * 128) * 4u);
-            if (row < p.out) {
-                if (p.n_slots == 1) {
-                    if (n < p.batch) p.y[static_cast<size_t>(n) * p.out + row] = __float2half_rn(sum * (p.norms[row] * p.inv_scale));
-                } else {
-                    p.partial[(static_cast<size_t>(slot) * 8 + n) * p.out_pad + row] = sum;
+        // ---- cross-warp sum without a CTA-wide barrier, kLag units behind ----
+        // Every warp drops its partial tile of unit i into ring slot i % kRing and signals
+        // "written"; the sum is done kLag units later by all warps symmetrically, followed by
+        // "read".  With a deep ring (16 slots for one activation row) warps drift apart by
+        // several units, so a slow memory response delays one warp, not the CTA.
+        if (i >= kLag) {
+            reduce_unit(red.slot, red.ru, rs, rpar);
+            red = next_pos(red);
+            if (++rs == kRing) { rs = 0; rpar ^= 1u; }
+        }
+        if (i >= kRing && !mbar_wait(bar_read + 8u * ws, wpar)) {
+            atomicExch(p.status, 4u);
+            atomicExch(&s_abort, 1u);
+        }
+        {
+            // C fragment: (row g, columns 2q, 2q+1) and (row g+8, same columns)
+            const uint32_t dst = red_addr + static_cast<uint32_t>(ws) * kSlotBytes + static_cast<uint32_t>(warp * 16 * BP) * 4u;
+            const int n = 2 * q;
+            if (n < BP) {
+                sts_f32(dst + static_cast<uint32_t>(g * BP + n) * 4u, acc0[0] + acc1[0]);
+                sts_f32(dst + static_cast<uint32_t>((g + 8) * BP + n) * 4u, acc0[2] + acc1[2]);
+                if (n + 1 < BP) {
+                    sts_f32(dst + static_cast<uint32_t>(g * BP + n + 1) * 4u, acc0[1] + acc1[1]);
+                    sts_f32(dst + static_cast<uint32_t>((g + 8) * BP + n + 1) * 4u, acc0[3] + acc1[3]);
                 }
             }
         }
-        if (p.n_slots > 1) {
-            __threadfence();
-            __syncthreads();
-            if (tid == 0) {
-                const unsigned int prev = atomicAdd(&p.counters[rt], 1u);
-                s_last = (prev == static_cast<unsigned int>(p.n_slots - 1)) ? 1u : 0u;
-                if (s_last) p.counters[rt] = 0u;  // ready for the next launch
-            }
-            __syncthreads();
-            if (s_last) {
-                __threadfence();
-                for (int idx = tid; idx < p.tpu * 128; idx += kThreads) {
-                    const int t = idx >> 7, e = idx & 127;
-                    const int n = e & 7;
-                    const int row = (rt * p.tpu + t) * 16 + (e >> 3);
-                    if (row < p.out && n < p.batch) {
-                        float total = 0.f;
-                        for (int c = 0; c < p.n_slots; ++c)
-                            total += __ldcg(p.partial + (static_cast<size_t>(c) * 8 + n) * p.out_pad + row);
-                        p.y[static_cast<size_t>(n) * p.out + row] = __float2half_rn(total * (p.norms[row] * p.inv_scale));
-                    }
-                }
-            }
-        }
-        buf ^= 1;
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar_written + 8u * ws);
+        if (++ws == kRing) { ws = 0; if (i >= kRing) wpar ^= 1u; }
+
+        cur = nxt;
+        if (i + 2 < n_local) nxt = next_pos(nxt);
+    }
+    // the last kLag units (or all of them, for a short range) are still to be summed
+    for (int k = (n_local > kLag ? n_local - kLag : 0); k < n_local; ++k) {
+        reduce_unit(red.slot, red.ru, rs, rpar);
+        red = next_pos(red);
+        if (++rs == kRing) { rs = 0; rpar ^= 1u; }
     }
 }
-
-constexpr size_t kGemvSmem = kLutAddr + kLutBytes;
 
 size_t align256(size_t v) { return (v + 255) & ~static_cast<size_t>(255); }
 
@@ -377,6 +576,7 @@ void launch_tq8_gemv(const uint8_t* codes, const float* norms, const float* tabl
     a.wpt = warps_per_tile(in);
     a.tpu = kWarps / a.wpt;
     a.n_row_units = (n_row_tiles + a.tpu - 1) / a.tpu;
+    const int bp = batch <= 1 ? 1 : (batch <= 2 ? 2 : (batch <= 4 ? 4 : 8));
     a.inv_scale = 1.0f / std::sqrt(static_cast<float>(in));
     uint8_t* sp = static_cast<uint8_t*>(scratch);
     float* xrot = reinterpret_cast<float*>(sp);
@@ -393,13 +593,17 @@ void launch_tq8_gemv(const uint8_t* codes, const float* norms, const float* tabl
     int dev = 0;
     TQ_CUDA(cudaGetDevice(&dev));
     if (dev >= 64 || !configured[dev]) {
-        TQ_CUDA(cudaFuncSetAttribute(tq8_gemv_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kGemvSmem)));
+        TQ_CUDA(cudaFuncSetAttribute(tq8_gemv_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kGemvSmem)));
+        TQ_CUDA(cudaFuncSetAttribute(tq8_gemv_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kGemvSmem)));
+        TQ_CUDA(cudaFuncSetAttribute(tq8_gemv_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kGemvSmem)));
+        TQ_CUDA(cudaFuncSetAttribute(tq8_gemv_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kGemvSmem)));
         if (dev < 64) configured[dev] = true;
     }
 
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = 1;
+    static const int n_attr = std::getenv("TQ_NO_PDL") ? 0 : 1;  // development switch
 
     // 1. rotate the activation (one warp per plane x row x block)
     {
@@ -410,7 +614,7 @@ void launch_tq8_gemv(const uint8_t* codes, const float* norms, const float* tabl
         cfg.blockDim = dim3(128);
         cfg.stream = stream;
         cfg.attrs = attr;
-        cfg.numAttrs = 1;
+        cfg.numAttrs = n_attr;
 #define TQ_ROT_CASE(EV)                                                                                            \
     case 32 * EV:                                                                                                  \
         TQ_CUDA(cudaLaunchKernelEx(&cfg, rotate_x_kernel<EV>, x, xrot, in, batch, n_planes, seed_p, seed_r, inv_sqrt)); \
@@ -426,12 +630,17 @@ void launch_tq8_gemv(const uint8_t* codes, const float* norms, const float* tabl
         const int n_units = a.n_row_units * a.n_slots;
         cudaLaunchConfig_t cfg{};
         cfg.gridDim = dim3(n_units < sm_count ? n_units : sm_count);
-        cfg.blockDim = dim3(kThreads);
+        cfg.blockDim = dim3(kCtaThreads);
         cfg.dynamicSmemBytes = kGemvSmem;
         cfg.stream = stream;
         cfg.attrs = attr;
-        cfg.numAttrs = 1;
-        TQ_CUDA(cudaLaunchKernelEx(&cfg, tq8_gemv_kernel, a));
+        cfg.numAttrs = n_attr;
+        switch (bp) {
+            case 1: TQ_CUDA(cudaLaunchKernelEx(&cfg, tq8_gemv_kernel<1>, a)); break;
+            case 2: TQ_CUDA(cudaLaunchKernelEx(&cfg, tq8_gemv_kernel<2>, a)); break;
+            case 4: TQ_CUDA(cudaLaunchKernelEx(&cfg, tq8_gemv_kernel<4>, a)); break;
+            default: TQ_CUDA(cudaLaunchKernelEx(&cfg, tq8_gemv_kernel<8>, a)); break;
+        }
     }
 }
 
@@ -480,5 +689,16 @@ void launch_tq8_gemv_static(const uint8_t* codes, const float* norms, const floa
     launch_tq8_gemv(codes, norms, table, x, y, out, in, batch, block, n_planes, seed_p, seed_r, scratch, status, sm_count,
                     stream);
 }
+
+#ifdef TQ_GEMV_TIMING
+extern "C" void tq_debug_gemv_timing(unsigned long long* out8, int reset) {
+    cudaDeviceSynchronize();
+    cudaMemcpyFromSymbol(out8, g_gemv_timing, sizeof(unsigned long long) * 8);
+    if (reset) {
+        unsigned long long z[8] = {0};
+        cudaMemcpyToSymbol(g_gemv_timing, z, sizeof z);
+    }
+}
+#endif
 
 }  // namespace tq
