@@ -322,6 +322,273 @@ __global__ void __launch_bounds__(128) attn_combine_kernel(const float* __restri
             __float2half_rn(v[j] * inv_sqrt * sign_value(v_seed, static_cast<uint32_t>(lane * E + j)) * invL);
 }
 
+// ---- decode attention on the tensor cores (head_dim 128) ------------------------------------------
+// One warp owns 16-token tiles.  Layouts (all mma.sync.m16n8k16, fp16 in, fp32 accumulate):
+//   S^T[16 tokens x 8 heads]  = K[16 x 128]   . Qrot^T[128 x 8]      (8 MMAs, centroid part)
+//   S2^T                       = Sgn[16 x 128] . Qsgn^T[128 x 8]      (8 MMAs, 1-bit residual part)
+//   O^T[128 dims x 8 heads]   += V^T[128 x 16] . P^T[16 x 8]           (8 MMAs)
+// so the 7 query heads of a GQA group fill the n = 8 side and no MMA row is wasted.
+// Codes become fp16 fragments through a 64-entry table indexed by a PAIR of 3-bit codes (the
+// reference packs ten codes per word, so pairs never straddle words); the table is replicated
+// per lane in shared memory so lookups never bank-conflict.  Thread q of a quad owns the pairs
+// of words q, q+4, q+8 and pair q of word 12; the resulting permutation of the 128 dims is
+// the same on both operands of each product and is undone when the partial result is written.
+// V tiles are looked up in [token x dim] order and transposed in registers (movmatrix).
+constexpr int kMmaThreads = 128;
+// The table holds kCentroidScale * centroid: with this factor all four centroid magnitudes
+// round to fp16 with a relative error below 1.4e-5 (unscaled: up to 3e-4, which the softmax
+// amplifies); the factor is divided out of the key and value norms.
+constexpr float kCentroidScale = 1.1979075f;
+
+__device__ __forceinline__ void mma_f16(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                        uint32_t b1) {
+    asm("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t movmatrix_trans(uint32_t a) {
+    uint32_t d;
+    asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;" : "=r"(d) : "r"(a));
+    return d;
+}
+__device__ __forceinline__ uint32_t pack_half2(float lo, float hi) {
+    const __half2 h = __floats2half2_rn(lo, hi);
+    return *reinterpret_cast<const uint32_t*>(&h);
+}
+// First dim of pair `pidx` (0..15) owned by quad-thread q.
+__host__ __device__ __forceinline__ int attn_pair_dim(int q, int pidx) {
+    return pidx < 15 ? 10 * (q + 4 * (pidx / 5)) + 2 * (pidx % 5) : 120 + 2 * q;
+}
+
+template <typename QT>
+__global__ void __launch_bounds__(kMmaThreads) attn_mma_kernel(const AttnSeq* __restrict__ seqs, const QT* __restrict__ qv,
+                                                               int q_heads, int kv_heads, int n_splits, uint32_t k_seed,
+                                                               uint32_t qjl_seed, int use_qjl, float inv_sqrt,
+                                                               float inv_scale_d, float attn_scale, float gamma,
+                                                               float* __restrict__ part_acc, float* __restrict__ part_ml) {
+    constexpr int D = 128, WPH = 13, QPH = 4;
+    __shared__ uint32_t s_lut[64 * 32];    // pair table, [pair index][lane]
+    __shared__ uint32_t s_sgn[4 * 32];     // two sign bits -> (+-1, +-1), [index][lane]
+    __shared__ float s_q[8][D];            // rotated queries of this KV head's group
+    __shared__ float s_m[4][8], s_l[4][8];
+    __shared__ float s_acc[4][8][D];
+
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int g = lane >> 2, q = lane & 3;
+    const int split = blockIdx.x, kvh = blockIdx.y % kv_heads, gchunk = blockIdx.y / kv_heads, seq = blockIdx.z;
+    const int G = q_heads / kv_heads;
+    const int g0 = gchunk * 8;
+    const int ng = min(8, G - g0);
+
+    for (int i = tid; i < 64 * 32; i += kMmaThreads) {
+        const int idx = i >> 5;
+        s_lut[i] = pack_half2(kCentroidScale * kC3[idx & 7], kCentroidScale * kC3[idx >> 3]);
+    }
+    for (int i = tid; i < 4 * 32; i += kMmaThreads) {
+        const int idx = i >> 5;
+        s_sgn[i] = pack_half2((idx & 1) ? 1.f : -1.f, (idx & 2) ? 1.f : -1.f);
+    }
+    // rotated queries: fp16-round, sign, butterfly, 1/sqrt(d)  (one warp per head)
+    for (int h = warp; h < 8; h += 4) {
+        float v[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            float t = 0.f;
+            if (h < ng) {
+                const size_t qi = (static_cast<size_t>(seq) * q_heads + kvh * G + g0 + h) * D + lane * 4 + j;
+                t = __half2float(__float2half_rn(static_cast<float>(qv[qi])));
+            }
+            v[j] = t * sign_value(k_seed, static_cast<uint32_t>(lane * 4 + j));
+        }
+        warp_fwht<4>(v, lane);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) s_q[h][lane * 4 + j] = v[j] * inv_sqrt;
+    }
+    __syncthreads();
+
+    // B fragments (head n = g): centroid product uses this thread's pair dims, the sign product
+    // uses dims 32 q + 2 p (sign word q of the token), with the key-side sign folded in.
+    // The rotated query is split into an fp16 head and an fp16 tail (two MMAs per step) so
+    // that its rounding does not limit the score accuracy.
+    uint32_t bq[16], bql[16], bs[16];
+#pragma unroll
+    for (int pidx = 0; pidx < 16; ++pidx) {
+        const int d = attn_pair_dim(q, pidx);
+        const float x0 = s_q[g][d], x1 = s_q[g][d + 1];
+        const float h0 = __half2float(__float2half_rn(x0)), h1 = __half2float(__float2half_rn(x1));
+        bq[pidx] = pack_half2(h0, h1);
+        bql[pidx] = pack_half2(x0 - h0, x1 - h1);
+        const int e = 32 * q + 2 * pidx;
+        const float s0 = qjl_sign_is_positive(qjl_seed, static_cast<uint32_t>(e)) ? 1.f : -1.f;
+        const float s1 = qjl_sign_is_positive(qjl_seed, static_cast<uint32_t>(e + 1)) ? 1.f : -1.f;
+        bs[pidx] = pack_half2(s_q[g][e] * s0, s_q[g][e + 1] * s1);
+    }
+
+    const AttnSeq S = seqs[seq];
+    const int n_tok = S.end - S.start;
+    const int t0 = S.start + static_cast<int>(static_cast<long>(n_tok) * split / n_splits);
+    const int t1 = S.start + static_cast<int>(static_cast<long>(n_tok) * (split + 1) / n_splits);
+
+    const uint32_t lut_base = static_cast<uint32_t>(__cvta_generic_to_shared(s_lut)) + static_cast<uint32_t>(lane) * 4u;
+    const uint32_t sgn_base = static_cast<uint32_t>(__cvta_generic_to_shared(s_sgn)) + static_cast<uint32_t>(lane) * 4u;
+    auto lut_pair = [&](uint32_t word, int bit) -> uint32_t {
+        // ((word >> bit) & 63) * 128 + lane * 4
+        const uint32_t sh = bit >= 7 ? (word >> (bit - 7)) : (word << (7 - bit));
+        uint32_t v;
+        asm("ld.shared.b32 %0, [%1];" : "=r"(v) : "r"(lut_base + (sh & (63u << 7))));
+        return v;
+    };
+    auto sgn_pair = [&](uint32_t word, int bit) -> uint32_t {
+        const uint32_t sh = bit >= 7 ? (word >> (bit - 7)) : (word << (7 - bit));
+        uint32_t v;
+        asm("ld.shared.b32 %0, [%1];" : "=r"(v) : "r"(sgn_base + (sh & (3u << 7))));
+        return v;
+    };
+    // the 16 pair fragments of one token's codes for this thread
+    auto dequant16 = [&](const uint32_t* rec, uint32_t (&out)[16]) {
+        const uint32_t w0 = __ldg(rec + q), w1 = __ldg(rec + q + 4), w2 = __ldg(rec + q + 8), w3 = __ldg(rec + 12);
+#pragma unroll
+        for (int j = 0; j < 5; ++j) {
+            out[j] = lut_pair(w0, 6 * j);
+            out[5 + j] = lut_pair(w1, 6 * j);
+            out[10 + j] = lut_pair(w2, 6 * j);
+        }
+        out[15] = lut_pair(w3 >> (6 * q), 0);
+    };
+
+    float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};  // heads 2q, 2q+1
+    float acc[8][4];
+#pragma unroll
+    for (int mt = 0; mt < 8; ++mt)
+#pragma unroll
+        for (int k = 0; k < 4; ++k) acc[mt][k] = 0.f;
+
+    for (int tb = t0 + warp * 16; tb < t1; tb += 64) {
+        // tokens of this thread's two rows (clamped so loads stay in range; masked below)
+        const int ta = tb + g, tbb = tb + g + 8;
+        const bool va = ta < t1, vb = tbb < t1;
+        const size_t ra = static_cast<size_t>(va ? ta : t1 - 1) * kv_heads + kvh;
+        const size_t rb = static_cast<size_t>(vb ? tbb : t1 - 1) * kv_heads + kvh;
+        const float kscale = inv_scale_d * attn_scale / kCentroidScale;
+        const float kna = S.k_norms[ra] * kscale, knb = S.k_norms[rb] * kscale;
+        const float vna = S.v_norms[ra] * (1.0f / kCentroidScale), vnb = S.v_norms[rb] * (1.0f / kCentroidScale);
+
+        // ---- scores ----
+        float c1[4] = {0.f, 0.f, 0.f, 0.f};
+        {
+            uint32_t ka[16], kb[16];
+            dequant16(S.k_words + ra * WPH, ka);
+            dequant16(S.k_words + rb * WPH, kb);
+#pragma unroll
+            for (int ks = 0; ks < 8; ++ks) {
+                mma_f16(c1, ka[2 * ks], kb[2 * ks], ka[2 * ks + 1], kb[2 * ks + 1], bq[2 * ks], bq[2 * ks + 1]);
+                mma_f16(c1, ka[2 * ks], kb[2 * ks], ka[2 * ks + 1], kb[2 * ks + 1], bql[2 * ks], bql[2 * ks + 1]);
+            }
+        }
+        if (use_qjl) {
+            float c2[4] = {0.f, 0.f, 0.f, 0.f};
+            const uint32_t wa = S.qjl_words[ra * QPH + q], wb = S.qjl_words[rb * QPH + q];
+#pragma unroll
+            for (int ks = 0; ks < 8; ++ks)
+                mma_f16(c2, sgn_pair(wa, 4 * ks), sgn_pair(wb, 4 * ks), sgn_pair(wa, 4 * ks + 2), sgn_pair(wb, 4 * ks + 2),
+                        bs[2 * ks], bs[2 * ks + 1]);
+            const float qa = S.qjl_norms[ra] * (gamma * kCentroidScale), qb = S.qjl_norms[rb] * (gamma * kCentroidScale);
+            c1[0] = fmaf(qa, c2[0], c1[0]);
+            c1[1] = fmaf(qa, c2[1], c1[1]);
+            c1[2] = fmaf(qb, c2[2], c1[2]);
+            c1[3] = fmaf(qb, c2[3], c1[3]);
+        }
+        // c1: (token g: heads 2q, 2q+1), (token g+8: heads 2q, 2q+1)
+        float s00 = va ? c1[0] * kna : -INFINITY, s01 = va ? c1[1] * kna : -INFINITY;
+        float s10 = vb ? c1[2] * knb : -INFINITY, s11 = vb ? c1[3] * knb : -INFINITY;
+
+        // ---- online softmax per head (reduce over the 16 tokens = over g) ----
+        float mx0 = fmaxf(s00, s10), mx1 = fmaxf(s01, s11);
+#pragma unroll
+        for (int o = 4; o < 32; o <<= 1) {
+            mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, o));
+            mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, o));
+        }
+        const float mn0 = fmaxf(m_run[0], mx0), mn1 = fmaxf(m_run[1], mx1);
+        const float cr0 = __expf(m_run[0] - mn0), cr1 = __expf(m_run[1] - mn1);
+        const float p00 = __expf(s00 - mn0), p01 = __expf(s01 - mn1), p10 = __expf(s10 - mn0), p11 = __expf(s11 - mn1);
+        float sum0 = p00 + p10, sum1 = p01 + p11;
+#pragma unroll
+        for (int o = 4; o < 32; o <<= 1) {
+            sum0 += __shfl_xor_sync(0xffffffffu, sum0, o);
+            sum1 += __shfl_xor_sync(0xffffffffu, sum1, o);
+        }
+        l_run[0] = fmaf(l_run[0], cr0, sum0);
+        l_run[1] = fmaf(l_run[1], cr1, sum1);
+        m_run[0] = mn0;
+        m_run[1] = mn1;
+#pragma unroll
+        for (int mt = 0; mt < 8; ++mt) {
+            acc[mt][0] *= cr0;
+            acc[mt][1] *= cr1;
+            acc[mt][2] *= cr0;
+            acc[mt][3] *= cr1;
+        }
+        // P^T fragment: (tokens 2q, 2q+1 | 2q+8, 2q+9 ; head g) from (token g | g+8 ; heads 2q, 2q+1)
+        const uint32_t pb0 = movmatrix_trans(pack_half2(p00 * vna, p01 * vna));
+        const uint32_t pb1 = movmatrix_trans(pack_half2(p10 * vnb, p11 * vnb));
+
+        // ---- values ----
+        {
+            uint32_t xa[16], xb[16];
+            dequant16(S.v_words + ra * WPH, xa);
+            dequant16(S.v_words + rb * WPH, xb);
+#pragma unroll
+            for (int ks = 0; ks < 8; ++ks) {
+                // V[token x dim] fragment of dim block ks -> V^T[dim x token] fragment
+                const uint32_t a0 = movmatrix_trans(xa[2 * ks]);      // dims 0-7  x tokens 0-7
+                const uint32_t a1 = movmatrix_trans(xa[2 * ks + 1]);  // dims 8-15 x tokens 0-7
+                const uint32_t a2 = movmatrix_trans(xb[2 * ks]);      // dims 0-7  x tokens 8-15
+                const uint32_t a3 = movmatrix_trans(xb[2 * ks + 1]);  // dims 8-15 x tokens 8-15
+                mma_f16(acc[ks], a0, a1, a2, a3, pb0, pb1);
+            }
+        }
+    }
+
+    // ---- publish this warp's state in natural dim order, merge the 4 warps, write the partial ----
+    // acc[mt]: (slot g: heads 2q, 2q+1), (slot g+8: heads 2q, 2q+1); slot -> dim through the pair map
+    if (g == 0) {
+        s_m[warp][2 * q] = m_run[0];
+        s_m[warp][2 * q + 1] = m_run[1];
+        s_l[warp][2 * q] = l_run[0];
+        s_l[warp][2 * q + 1] = l_run[1];
+    }
+#pragma unroll
+    for (int mt = 0; mt < 8; ++mt) {
+#pragma unroll
+        for (int hf = 0; hf < 2; ++hf) {
+            const int slot = g + 8 * hf;                   // row of the m-tile
+            const int qq = (slot & 7) >> 1, lowbit = slot & 1, half = slot >> 3;
+            const int d = attn_pair_dim(qq, 2 * mt + half) + lowbit;
+            s_acc[warp][2 * q][d] = acc[mt][2 * hf];
+            s_acc[warp][2 * q + 1][d] = acc[mt][2 * hf + 1];
+        }
+    }
+    __syncthreads();
+    for (int idx = tid; idx < ng * D; idx += kMmaThreads) {
+        const int h = idx / D, e = idx - h * D;
+        const float M = fmaxf(fmaxf(s_m[0][h], s_m[1][h]), fmaxf(s_m[2][h], s_m[3][h]));
+        float L = 0.f, A = 0.f;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) {
+            const float f = (s_m[w][h] == -INFINITY) ? 0.f : __expf(s_m[w][h] - M);
+            L = fmaf(s_l[w][h], f, L);
+            A = fmaf(s_acc[w][h][e], f, A);
+        }
+        const size_t slot = (static_cast<size_t>(seq) * q_heads + kvh * G + g0 + h) * n_splits + split;
+        part_acc[slot * D + e] = A;
+        if (e == 0) {
+            part_ml[slot * 2] = M;
+            part_ml[slot * 2 + 1] = L;
+        }
+    }
+}
+
 int grid_for_warps(long n_warp_items, int warps_per_block, int cap) {
     long want = (n_warp_items + warps_per_block - 1) / warps_per_block;
     if (want < 1) want = 1;
@@ -405,6 +672,22 @@ void launch_kv_attention(const void* d_seqs, int n_seqs, const void* q, bool q_i
                                                                  inv_scale_d, attn_scale, gamma, part_acc, part_ml);     \
     attn_combine_kernel<EV><<<static_cast<int>((n_rows + 3) / 4), 128, 0, stream>>>(part_acc, part_ml, n_rows, n_splits, \
                                                                                    v_seed, inv_sqrt, inv_scale_d, out);
+    if (head_dim == 128) {
+        if (q_is_f16)
+            attn_mma_kernel<__half><<<grid, kMmaThreads, 0, stream>>>(static_cast<const AttnSeq*>(d_seqs),
+                                                                        static_cast<const __half*>(q), q_heads, kv_heads,
+                                                                        n_splits, k_seed, qjl_seed, use_qjl ? 1 : 0, inv_sqrt,
+                                                                        inv_scale_d, attn_scale, gamma, part_acc, part_ml);
+        else
+            attn_mma_kernel<float><<<grid, kMmaThreads, 0, stream>>>(static_cast<const AttnSeq*>(d_seqs),
+                                                                       static_cast<const float*>(q), q_heads, kv_heads,
+                                                                       n_splits, k_seed, qjl_seed, use_qjl ? 1 : 0, inv_sqrt,
+                                                                       inv_scale_d, attn_scale, gamma, part_acc, part_ml);
+        attn_combine_kernel<4><<<static_cast<int>((n_rows + 3) / 4), 128, 0, stream>>>(part_acc, part_ml, n_rows, n_splits,
+                                                                                      v_seed, inv_sqrt, inv_scale_d, out);
+        TQ_CUDA(cudaGetLastError());
+        return;
+    }
     switch (head_dim) {
         case 32: TQ_ATT(1) break;
         case 64: TQ_ATT(2) break;
