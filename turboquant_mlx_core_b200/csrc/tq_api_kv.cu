@@ -223,8 +223,8 @@ void attention_batched(TQKVCache* const* caches, int n_seqs, int layer, const vo
     // enough context splits to fill the machine, at least ~256 tokens each
     const int G = q_heads / heads;
     const int ctas_per_split = n_seqs * heads * ((G + 7) / 8);
-    int n_splits = std::max(1, std::min((148 * 4 + ctas_per_split - 1) / ctas_per_split, (max_tok + 255) / 256));
-    n_splits = std::min(n_splits, 64);
+    int n_splits = std::max(1, std::min((148 * 12 + ctas_per_split - 1) / ctas_per_split, (max_tok + 255) / 256));
+    n_splits = std::min(n_splits, 128);
 
     c0->attn_desc().reserve(desc.size() * sizeof(SeqDesc));
     TQ_CUDA(cudaMemcpyAsync(c0->attn_desc().as<void>(), desc.data(), desc.size() * sizeof(SeqDesc), cudaMemcpyHostToDevice, st));

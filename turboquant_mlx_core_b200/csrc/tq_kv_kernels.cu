@@ -361,14 +361,17 @@ __host__ __device__ __forceinline__ int attn_pair_dim(int q, int pidx) {
 }
 
 template <typename QT>
-__global__ void __launch_bounds__(kMmaThreads) attn_mma_kernel(const AttnSeq* __restrict__ seqs, const QT* __restrict__ qv,
+__global__ void __launch_bounds__(kMmaThreads, 4) attn_mma_kernel(const AttnSeq* __restrict__ seqs, const QT* __restrict__ qv,
                                                                int q_heads, int kv_heads, int n_splits, uint32_t k_seed,
                                                                uint32_t qjl_seed, int use_qjl, float inv_sqrt,
                                                                float inv_scale_d, float attn_scale, float gamma,
                                                                float* __restrict__ part_acc, float* __restrict__ part_ml) {
     constexpr int D = 128, WPH = 13, QPH = 4;
-    __shared__ uint32_t s_lut[64 * 32];    // pair table, [pair index][lane]
-    __shared__ uint32_t s_sgn[4 * 32];     // two sign bits -> (+-1, +-1), [index][lane]
+    // The tables sit at shared-window addresses that are multiples of their size, so that
+    // "table base + lane offset" and the scaled index occupy disjoint bits and one logic op
+    // forms a lookup address.  The window offset of a static array is not under the program's
+    // control, so the aligned addresses are chosen at run time inside a buffer of twice the size.
+    __shared__ __align__(16) uint32_t s_tab[2 * 64 * 32];
     __shared__ float s_q[8][D];            // rotated queries of this KV head's group
     __shared__ float s_m[4][8], s_l[4][8];
     __shared__ float s_acc[4][8][D];
@@ -380,6 +383,11 @@ __global__ void __launch_bounds__(kMmaThreads) attn_mma_kernel(const AttnSeq* __
     const int g0 = gchunk * 8;
     const int ng = min(8, G - g0);
 
+    const uint32_t tab_addr = static_cast<uint32_t>(__cvta_generic_to_shared(s_tab));
+    const uint32_t lut_addr = (tab_addr + 8191u) & ~8191u;           // pair table, [pair index][lane]
+    const uint32_t sgn_addr = (lut_addr - tab_addr <= 8192u - 512u) ? lut_addr + 8192u : lut_addr - 512u;
+    uint32_t* const s_lut = s_tab + ((lut_addr - tab_addr) >> 2);
+    uint32_t* const s_sgn = s_tab + ((sgn_addr - tab_addr) >> 2);    // two sign bits -> (+-1, +-1), [index][lane]
     for (int i = tid; i < 64 * 32; i += kMmaThreads) {
         const int idx = i >> 5;
         s_lut[i] = pack_half2(kCentroidScale * kC3[idx & 7], kCentroidScale * kC3[idx >> 3]);
@@ -429,19 +437,19 @@ __global__ void __launch_bounds__(kMmaThreads) attn_mma_kernel(const AttnSeq* __
     const int t0 = S.start + static_cast<int>(static_cast<long>(n_tok) * split / n_splits);
     const int t1 = S.start + static_cast<int>(static_cast<long>(n_tok) * (split + 1) / n_splits);
 
-    const uint32_t lut_base = static_cast<uint32_t>(__cvta_generic_to_shared(s_lut)) + static_cast<uint32_t>(lane) * 4u;
-    const uint32_t sgn_base = static_cast<uint32_t>(__cvta_generic_to_shared(s_sgn)) + static_cast<uint32_t>(lane) * 4u;
+    const uint32_t lut_base = lut_addr + static_cast<uint32_t>(lane) * 4u;
+    const uint32_t sgn_base = sgn_addr + static_cast<uint32_t>(lane) * 4u;
     auto lut_pair = [&](uint32_t word, int bit) -> uint32_t {
         // ((word >> bit) & 63) * 128 + lane * 4
         const uint32_t sh = bit >= 7 ? (word >> (bit - 7)) : (word << (7 - bit));
         uint32_t v;
-        asm("ld.shared.b32 %0, [%1];" : "=r"(v) : "r"(lut_base + (sh & (63u << 7))));
+        asm("ld.shared.b32 %0, [%1];" : "=r"(v) : "r"(lut_base | (sh & (63u << 7))));
         return v;
     };
     auto sgn_pair = [&](uint32_t word, int bit) -> uint32_t {
         const uint32_t sh = bit >= 7 ? (word >> (bit - 7)) : (word << (7 - bit));
         uint32_t v;
-        asm("ld.shared.b32 %0, [%1];" : "=r"(v) : "r"(sgn_base + (sh & (3u << 7))));
+        asm("ld.shared.b32 %0, [%1];" : "=r"(v) : "r"(sgn_base | (sh & (3u << 7))));
         return v;
     };
     // the 16 pair fragments of one token's codes for this thread
@@ -470,8 +478,8 @@ __global__ void __launch_bounds__(kMmaThreads) attn_mma_kernel(const AttnSeq* __
         const size_t ra = static_cast<size_t>(va ? ta : t1 - 1) * kv_heads + kvh;
         const size_t rb = static_cast<size_t>(vb ? tbb : t1 - 1) * kv_heads + kvh;
         const float kscale = inv_scale_d * attn_scale / kCentroidScale;
-        const float kna = S.k_norms[ra] * kscale, knb = S.k_norms[rb] * kscale;
-        const float vna = S.v_norms[ra] * (1.0f / kCentroidScale), vnb = S.v_norms[rb] * (1.0f / kCentroidScale);
+        const float kna = __ldg(S.k_norms + ra) * kscale, knb = __ldg(S.k_norms + rb) * kscale;
+        const float vna = __ldg(S.v_norms + ra) * (1.0f / kCentroidScale), vnb = __ldg(S.v_norms + rb) * (1.0f / kCentroidScale);
 
         // ---- scores ----
         float c1[4] = {0.f, 0.f, 0.f, 0.f};
@@ -487,12 +495,12 @@ __global__ void __launch_bounds__(kMmaThreads) attn_mma_kernel(const AttnSeq* __
         }
         if (use_qjl) {
             float c2[4] = {0.f, 0.f, 0.f, 0.f};
-            const uint32_t wa = S.qjl_words[ra * QPH + q], wb = S.qjl_words[rb * QPH + q];
+            const uint32_t wa = __ldg(S.qjl_words + ra * QPH + q), wb = __ldg(S.qjl_words + rb * QPH + q);
 #pragma unroll
             for (int ks = 0; ks < 8; ++ks)
                 mma_f16(c2, sgn_pair(wa, 4 * ks), sgn_pair(wb, 4 * ks), sgn_pair(wa, 4 * ks + 2), sgn_pair(wb, 4 * ks + 2),
                         bs[2 * ks], bs[2 * ks + 1]);
-            const float qa = S.qjl_norms[ra] * (gamma * kCentroidScale), qb = S.qjl_norms[rb] * (gamma * kCentroidScale);
+            const float qa = __ldg(S.qjl_norms + ra) * (gamma * kCentroidScale), qb = __ldg(S.qjl_norms + rb) * (gamma * kCentroidScale);
             c1[0] = fmaf(qa, c2[0], c1[0]);
             c1[1] = fmaf(qa, c2[1], c1[1]);
             c1[2] = fmaf(qb, c2[2], c1[2]);
@@ -522,12 +530,15 @@ __global__ void __launch_bounds__(kMmaThreads) attn_mma_kernel(const AttnSeq* __
         l_run[1] = fmaf(l_run[1], cr1, sum1);
         m_run[0] = mn0;
         m_run[1] = mn1;
+        // once the running maxima have settled the correction is exactly 1: skip the rescale then
+        if (__any_sync(0xffffffffu, cr0 != 1.f || cr1 != 1.f)) {
 #pragma unroll
-        for (int mt = 0; mt < 8; ++mt) {
-            acc[mt][0] *= cr0;
-            acc[mt][1] *= cr1;
-            acc[mt][2] *= cr0;
-            acc[mt][3] *= cr1;
+            for (int mt = 0; mt < 8; ++mt) {
+                acc[mt][0] *= cr0;
+                acc[mt][1] *= cr1;
+                acc[mt][2] *= cr0;
+                acc[mt][3] *= cr1;
+            }
         }
         // P^T fragment: (tokens 2q, 2q+1 | 2q+8, 2q+9 ; head g) from (token g | g+8 ; heads 2q, 2q+1)
         const uint32_t pb0 = movmatrix_trans(pack_half2(p00 * vna, p01 * vna));
