@@ -22,7 +22,6 @@ import ctypes as C
 import json
 import os
 import statistics
-import subprocess
 import sys
 import time
 
@@ -35,8 +34,8 @@ OUT_F, IN_F, BLOCK = 4096, 4096, 128
 ALGO_BYTES = OUT_F * IN_F + 4 * OUT_F + 2 * IN_F + 2 * OUT_F   # codes + norms + x + y = 16 809 984
 PUBLISHED_TOK_S = 671.0   # reference README: 1.49 ms/token, Apple GPU, same shape, block 512
 # dram__bytes_read.sum + dram__bytes_write.sum of one tq8_gemv_kernel launch at this shape
-# (ncu capture summarised in profiles/); None until a capture exists.
-GEMV_DRAM_TRAFFIC = None
+# (ncu capture summarised in profiles/tq8_gemv_kernel_4096x4096_b1.md): reads only, no DRAM writes.
+GEMV_DRAM_TRAFFIC = 16852224
 
 
 def measured_peaks():
@@ -50,46 +49,58 @@ def measured_peaks():
 # ---- clocks --------------------------------------------------------------------------------
 
 class ClockSampler:
-    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
-         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
-         "clocks_event_reasons.sw_power_cap")
+    """Samples SM clock and clock-event reasons of one GPU from a thread while the timed region
+    runs (NVML reads only; nothing is set).  A timed region of a few milliseconds is shorter
+    than one nvidia-smi start-up, hence NVML in-process with a ~1 ms period."""
+    REASONS = (("hw_slowdown", 0x8), ("hw_thermal_slowdown", 0x40), ("sw_thermal_slowdown", 0x20),
+               ("sw_power_cap", 0x4))
 
-    def __init__(self, gpu_index: int):
-        self.proc = None
-        self.gpu = gpu_index
+    def __init__(self, device):
+        import threading
+        self.samples, self.bits, self.max_mhz, self.err = [], 0, None, None
+        self._stop = threading.Event()
+        self._thread = None
+        try:
+            import pynvml
+            import torch
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            uuid = str(torch.cuda.get_device_properties(device).uuid)
+            try:
+                self.h = pynvml.nvmlDeviceGetHandleByUUID(("GPU-" + uuid).encode())
+            except Exception:
+                self.h = pynvml.nvmlDeviceGetHandleByIndex(device.index or 0)
+            self.max_mhz = float(pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM))
+        except Exception as exc:  # no NVML: say so in the line instead of failing the bench
+            self.nv, self.err = None, f"NVML unavailable: {type(exc).__name__}"
+
+    def _run(self):
+        nv = self.nv
+        while not self._stop.is_set():
+            try:
+                self.samples.append(float(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM)))
+                self.bits |= int(nv.nvmlDeviceGetCurrentClocksEventReasons(self.h))
+            except Exception as exc:
+                self.err = f"NVML read failed: {type(exc).__name__}"
+                return
+            time.sleep(0.001)
 
     def start(self):
-        try:
-            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.gpu), "--query-gpu=" + self.Q,
-                                          "--format=csv,noheader,nounits", "-lms", "50"],
-                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
-        except OSError:
-            self.proc = None
+        if self.nv is None:
+            return
+        import threading
+        self._thread = threading.Thread(target=self._run, daemon=True)
+        self._thread.start()
 
     def stop(self):
-        if not self.proc:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
-        self.proc.terminate()
-        try:
-            out, _ = self.proc.communicate(timeout=5)
-        except subprocess.TimeoutExpired:
-            self.proc.kill()
-            out, _ = self.proc.communicate()
-        sm, mx, reasons = [], [], set()
-        for line in out.strip().splitlines():
-            f = [x.strip() for x in line.split(",")]
-            if len(f) < 9:
-                continue
-            try:
-                sm.append(float(f[1]))
-                mx.append(float(f[2]))
-            except ValueError:
-                continue
-            for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
-                if val.lower().startswith("active"):
-                    reasons.add(name)
-        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
-                "reasons": sorted(reasons), "samples": len(sm)}
+        if self._thread is not None:
+            self._stop.set()
+            self._thread.join(timeout=2)
+        reasons = [name for name, bit in self.REASONS if self.bits & bit]
+        if self.err:
+            reasons.append(self.err)
+        return {"sm_mhz": statistics.median(self.samples) if self.samples else None, "sm_max_mhz": self.max_mhz,
+                "reasons": reasons, "samples": len(self.samples)}
 
 
 # ---- synthetic inputs ------------------------------------------------------------------------
@@ -216,7 +227,7 @@ def run_cuda(args):
             dist.barrier()
         torch.cuda.synchronize()
 
-    sampler = ClockSampler(local_rank)
+    sampler = ClockSampler(device)
     with torch.cuda.stream(stream):
         for _ in range(args.warmup):
             graph.replay()
