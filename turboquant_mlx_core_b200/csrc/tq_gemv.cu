@@ -6,13 +6,17 @@
 //
 // Algebra.  A dequantised row block is  norm * (inv_sqrt*sign) o H(table[codes]*inv_scale)
 // and H is symmetric, so   <s o H(c), x> = <c, H(s o x)>.   The activation is therefore
-// rotated ONCE per call by a small kernel (forward WHT of every block of x) and the
-// weight side collapses to a table lookup per code:
+// rotated ONCE per call (forward WHT of every block of x) and the weight side collapses
+// to a table lookup per code:
 //   y[b, r] = norm[r] * inv_scale * sum_j table[code[r, j]] * xrot[b, j].
 //
-// Two kernels per call, chained with programmatic dependent launch so that the second
-// one's set-up overlaps whatever precedes it in the stream:
-//   rotate_x_kernel   x fp16 [b, in] -> xrot fp32 (TF32-rounded) [b, in] in scratch
+// Where the rotation happens.  A warp multiplies a fixed 256-column slice, so for WHT
+// blocks of up to 256 columns it rotates its own slice of x inside the GEMV kernel (16-byte
+// loads, butterflies in registers and lane exchanges, a 1 KB strip of shared memory to reach
+// the fragment layout): one kernel per call.  Larger blocks span several warps; for those
+// rotate_x_kernel writes xrot (fp32, TF32-rounded, [b, in]) to scratch first, chained with
+// programmatic dependent launch.  Either way the GEMV is launched with the programmatic
+// attribute: its set-up (table, first code loads) overlaps the tail of whatever precedes it.
 //   tq8_gemv_kernel   persistent, one CTA per SM, 16 warps:
 //     HBM --(128-bit loads, 16 codes each, two 64-column steps ahead)--> registers
 //     --(byte -> address, 1 PRMT)-->
@@ -43,7 +47,7 @@
 // residual centroid against x rotated with the residual seed; planes are just further
 // partial-sum slots.
 #include <cmath>
-#include <cstdlib>
+#include <cstdint>
 
 #include "tq_common.cuh"
 #include "tq_kernels.cuh"
@@ -63,11 +67,6 @@ constexpr int kMaxRing = 16;
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
 
-__device__ __forceinline__ float lds_f32(uint32_t addr) {
-    float v;
-    asm volatile("ld.shared.f32 %0, [%1];" : "=f"(v) : "r"(addr));
-    return v;
-}
 __device__ __forceinline__ void sts_f32(uint32_t addr, float v) {
     asm volatile("st.shared.f32 [%0], %1;" ::"r"(addr), "f"(v) : "memory");
 }
@@ -129,7 +128,8 @@ struct GemvArgs {
     const uint8_t* codes;   // [out, in] joint bytes
     const float* norms;     // [out]
     const float* table;     // [n_planes, 256] fp32
-    const float* xrot;      // [n_planes, batch, in] fp32 (TF32-rounded)
+    const float* xrot;      // [n_planes, batch, in] fp32 (TF32-rounded); used when x == nullptr
+    const __half* x;        // [batch, in] fp16: rotate inside the kernel (WHT block <= 256), else nullptr
     __half* y;              // [batch, out]
     float* partial;         // [n_slots, 8, out_pad] (only when n_slots > 1)
     unsigned int* counters; // [n_row_units]         (only when n_slots > 1)
@@ -138,6 +138,9 @@ struct GemvArgs {
     int n_row_units, n_chunks, n_slots, out_pad;  // n_slots = n_planes * n_chunks
     int wpt, tpu;           // warps per row tile, row tiles per unit (wpt * tpu = 16)
     float inv_scale;
+    uint32_t seed_p, seed_r;   // sign seeds of plane 0 / plane 1 (in-kernel rotation)
+    int block;                 // WHT block size                  (in-kernel rotation)
+    float inv_sqrt_block;
 };
 
 // Shared memory holds only the table and the partial-sum ring: the dynamic allocation ends at
@@ -159,21 +162,6 @@ __device__ __forceinline__ unsigned long long global_timer_ns() {
     asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
     return t;
 }
-#ifdef TQ_GEMV_TIMING
-// Cycle accounting for development builds: [0] waits for codes, [1] waits for "tiles written",
-// [2] waits for "buffer read", [3] whole kernel (per warp, summed over all warps).
-__device__ unsigned long long g_gemv_timing[8];
-#define TQ_TIMED_WAIT(slot, expr)                                     \
-    [&]() {                                                           \
-        const long long t_ = clock64();                               \
-        const bool ok_ = (expr);                                      \
-        if (lane == 0) atomicAdd(&g_gemv_timing[slot], static_cast<unsigned long long>(clock64() - t_)); \
-        return ok_;                                                   \
-    }()
-#else
-#define TQ_TIMED_WAIT(slot, expr) (expr)
-#endif
-
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
     unsigned long long t0 = 0;
     for (uint32_t spin = 0;; ++spin) {
@@ -188,12 +176,15 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
         if (spin > 64 && (spin & 63) == 0 && global_timer_ns() - t0 > kWaitLimitNs) return false;
     }
 }
-__device__ __forceinline__ uint4 ldg_stream(const uint8_t* p) {
-    uint4 v;
-    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0, %1, %2, %3}, [%4];"
-                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
-                 : "l"(p));
-    return v;
+// Streaming 16-byte load that leaves `v` untouched when `pred` is false.  Codes outside the
+// matrix are never zero-filled: whatever the registers hold indexes a valid table entry, and it
+// meets either a zero activation (columns past in_features) or a row that is never written.
+__device__ __forceinline__ void ldg_stream_if(uint4& v, const uint8_t* p, bool pred) {
+    asm volatile(
+        "{ .reg .pred p; setp.ne.u32 p, %5, 0;\n"
+        "  @p ld.global.nc.L1::no_allocate.v4.u32 {%0, %1, %2, %3}, [%4]; }"
+        : "+r"(v.x), "+r"(v.y), "+r"(v.z), "+r"(v.w)
+        : "l"(p), "r"(static_cast<uint32_t>(pred)));
 }
 __device__ __forceinline__ void named_barrier_sync(int id, int threads) {
     asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
@@ -206,27 +197,15 @@ __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
 // batch and reorder these loads freely (the address depends on codes loaded after the
 // barrier that publishes the table, which keeps them below it).
 __device__ __forceinline__ uint32_t lut_load(uint32_t addr) {
-#if defined(TQ_ABLATE) && (TQ_ABLATE == 2 || TQ_ABLATE >= 3)
-    return addr;  // development ablation: no table lookup
-#else
     uint32_t v;
     asm("ld.shared.b32 %0, [%1];" : "=r"(v) : "r"(addr));
     return v;
-#endif
 }
 __device__ __forceinline__ void mma_tf32(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
                                          uint32_t b1) {
-#if defined(TQ_ABLATE) && (TQ_ABLATE == 1 || TQ_ABLATE >= 3)
-    // development ablation: no tensor-core instruction, keep the data dependencies
-    c[0] = __uint_as_float(__float_as_uint(c[0]) ^ a0 ^ b0);
-    c[1] = __uint_as_float(__float_as_uint(c[1]) ^ a1 ^ b1);
-    c[2] = __uint_as_float(__float_as_uint(c[2]) ^ a2);
-    c[3] = __uint_as_float(__float_as_uint(c[3]) ^ a3);
-#else
     asm("mma.sync.aligned.m16n8k8.row.col.f32.tf32.tf32.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
         : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
-#endif
 }
 
 // BP = activation rows padded to 1, 2, 4 or 8 (compile time, so that the partial-sum ring
@@ -252,10 +231,11 @@ __global__ void __launch_bounds__(kCtaThreads, 1) tq8_gemv_kernel(const GemvArgs
     if (u_begin >= u_end) return;
     const int n_local = u_end - u_begin;
 
-    // ---- shared-memory map: [partial-sum ring | unused | table at 0x10000] ----
+    // ---- shared-memory map: [partial-sum ring | rotation strips | unused | table at 0x10000] ----
     const uint32_t base = smem_u32(smem_raw);
     const uint32_t red_addr = (base + 127u) & ~127u;
-    if (red_addr + kRedBytes > kLutAddr) {  // layout assumption broken: refuse to run
+    const uint32_t strip_addr = red_addr + kRedBytes + static_cast<uint32_t>(warp) * (kSlice * 4u);
+    if (red_addr + kRedBytes + kWarps * kSlice * 4u > kLutAddr) {  // layout assumption broken: refuse to run
         if (tid == 0) atomicExch(p.status, 1u);
         return;
     }
@@ -307,17 +287,24 @@ __global__ void __launch_bounds__(kCtaThreads, 1) tq8_gemv_kernel(const GemvArgs
         return make_pos((u.slot + 1) * p.n_row_units);
     };
     // Codes never depend on the kernel before this one, so the first loads go out before the
-    // dependency wait below.  Pieces outside the matrix read as zero.
+    // dependency wait below.  Pieces outside the matrix are simply not loaded.
     auto load_step = [&](const Pos& u, int s, bool live, uint4& lo, uint4& hi) {
         const bool c_ok = live && ((u.ok >> s) & 1u);
-        lo = (c_ok && (u.ok & 16u)) ? ldg_stream(u.ptr + 64 * s) : make_uint4(0, 0, 0, 0);
-        hi = (c_ok && (u.ok & 32u)) ? ldg_stream(u.ptr + 64 * s + row8) : make_uint4(0, 0, 0, 0);
+        ldg_stream_if(lo, u.ptr + 64 * s, c_ok && (u.ok & 16u));
+        ldg_stream_if(hi, u.ptr + 64 * s + row8, c_ok && (u.ok & 32u));
     };
     Pos cur = make_pos(u_begin);
     Pos nxt = (n_local > 1) ? next_pos(cur) : cur;
-    uint4 lo0, hi0, lo1, hi1;  // even / odd step, two steps in flight
-    load_step(cur, 0, true, lo0, hi0);
-    load_step(cur, 1, true, lo1, hi1);
+    // Two register buffers (even / odd step): two steps, 32 KB per SM, in flight.  Four buffers
+    // were measured and bought nothing: the kernel is bound by L1 data-pipe wavefronts (table
+    // lookups plus the 64-byte-granular code loads), not by the depth of the load queue.
+    uint4 blo[2], bhi[2];
+#pragma unroll
+    for (int s = 0; s < 2; ++s) {
+        blo[s] = make_uint4(0, 0, 0, 0);
+        bhi[s] = make_uint4(0, 0, 0, 0);
+        load_step(cur, s, true, blo[s], bhi[s]);
+    }
 
     auto build_table = [&](int plane) {
         // 256 entries x 32 copies; a thread writes 4 consecutive copies per store
@@ -432,7 +419,75 @@ __global__ void __launch_bounds__(kCtaThreads, 1) tq8_gemv_kernel(const GemvArgs
                 staged_plane = plane;
             }
             // B fragment of MMA (s, m): k = q -> column 64 s + 16 q + 2 m, k = q+4 -> the next column; n = g.
-            const int col0 = (cur.slot - plane * p.n_chunks) * kChunk + slice0 + 16 * q;
+            const int colw = (cur.slot - plane * p.n_chunks) * kChunk + slice0;  // first column of this warp's slice
+            const int col0 = colw + 16 * q;
+            if (p.x != nullptr) {
+                // Rotate this warp's 256 activation columns here: lane l holds columns 8l..8l+7 of
+                // the slice, stages below 8 stay in the lane, the rest are lane exchanges (same
+                // add tree as rotate_x_kernel).  A 1 KB strip of shared memory per warp turns the
+                // result into the fragment layout, one activation row at a time.
+                const uint32_t seed = plane ? p.seed_r : p.seed_p;
+                const int cl = colw + 8 * lane;
+                const bool c_ok = cl < p.in;
+                // bit j: the sign of this lane's column j is negative
+                uint32_t neg = 0;
+#pragma unroll
+                for (int j = 0; j < 8; ++j)
+                    neg |= sign_is_positive(seed, static_cast<uint32_t>((8 * lane + j) & (p.block - 1))) ? 0u : (1u << j);
+#pragma unroll
+                for (int s = 0; s < 4; ++s)
+#pragma unroll
+                    for (int k = 0; k < 16; ++k) bfrag[s][k] = 0u;
+                const int lane_steps = p.block >> 3;  // lanes per WHT block
+                uint4 xn = c_ok ? __ldg(reinterpret_cast<const uint4*>(p.x + cl)) : make_uint4(0, 0, 0, 0);
+                for (int n = 0; n < p.batch; ++n) {
+                    const uint4 xc = xn;
+                    if (n + 1 < p.batch && c_ok)
+                        xn = __ldg(reinterpret_cast<const uint4*>(p.x + static_cast<size_t>(n + 1) * p.in + cl));
+                    const uint32_t xw[4] = {xc.x, xc.y, xc.z, xc.w};
+                    float v[8];
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        const __half2 h2 = *reinterpret_cast<const __half2*>(&xw[j]);
+                        const float lo = __low2float(h2), hi = __high2float(h2);
+                        v[2 * j] = (neg >> (2 * j)) & 1u ? -lo : lo;
+                        v[2 * j + 1] = (neg >> (2 * j + 1)) & 1u ? -hi : hi;
+                    }
+#pragma unroll
+                    for (int h = 1; h < 8; h <<= 1)
+#pragma unroll
+                        for (int i = 0; i < 8; i += 2 * h)
+#pragma unroll
+                            for (int j = i; j < i + h; ++j) {
+                                const float a = v[j], b = v[j + h];
+                                v[j] = __fadd_rn(a, b);
+                                v[j + h] = __fsub_rn(a, b);
+                            }
+                    for (int m = 1; m < lane_steps; m <<= 1) {
+                        const bool upper = (lane & m) != 0;
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) {
+                            const float o = __shfl_xor_sync(0xffffffffu, v[j], m);
+                            v[j] = upper ? __fsub_rn(o, v[j]) : __fadd_rn(v[j], o);
+                        }
+                    }
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) v[j] = to_tf32(v[j] * p.inv_sqrt_block);
+                    sts_v4(strip_addr + static_cast<uint32_t>(lane) * 32u, v[0], v[1], v[2], v[3]);
+                    sts_v4(strip_addr + static_cast<uint32_t>(lane) * 32u + 16u, v[4], v[5], v[6], v[7]);
+                    __syncwarp();
+                    if (g == n) {
+#pragma unroll
+                        for (int s = 0; s < 4; ++s)
+#pragma unroll
+                            for (int k = 0; k < 16; k += 4)
+                                asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
+                                             : "=r"(bfrag[s][k]), "=r"(bfrag[s][k + 1]), "=r"(bfrag[s][k + 2]), "=r"(bfrag[s][k + 3])
+                                             : "r"(strip_addr + static_cast<uint32_t>(64 * s + 16 * q + k) * 4u));
+                    }
+                    __syncwarp();
+                }
+            } else {
             const float* xr = p.xrot + (static_cast<size_t>(plane) * p.batch + g) * p.in + col0;
             const bool have_row = g < p.batch;
 #pragma unroll
@@ -447,6 +502,7 @@ __global__ void __launch_bounds__(kCtaThreads, 1) tq8_gemv_kernel(const GemvArgs
                     bfrag[s][k + 3] = __float_as_uint(t.w);
                 }
             }
+            }
             staged_slot = cur.slot;
         }
         const bool has_next = i + 1 < n_local;
@@ -454,38 +510,33 @@ __global__ void __launch_bounds__(kCtaThreads, 1) tq8_gemv_kernel(const GemvArgs
         float acc0[4] = {0.f, 0.f, 0.f, 0.f}, acc1[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
         for (int s = 0; s < 4; ++s) {
-            uint4& lo = (s & 1) ? lo1 : lo0;
-            uint4& hi = (s & 1) ? hi1 : hi0;
-            const uint32_t wl[4] = {lo.x, lo.y, lo.z, lo.w};
-            const uint32_t wh[4] = {hi.x, hi.y, hi.z, hi.w};
-            // the words are copied out: refill the pair with the step two ahead
-            if (s < 2) load_step(cur, s + 2, true, lo, hi);
-            else load_step(nxt, s - 2, has_next, lo, hi);
+            uint4& lo = blo[s & 1];
+            uint4& hi = bhi[s & 1];
             // 16 independent lookups, then the 4 MMAs they feed (bytes 0,1 of a word feed one
-            // MMA, bytes 2,3 the next); two accumulator chains.
+            // MMA, bytes 2,3 the next); two accumulator chains.  Once the second half's addresses
+            // are formed the code registers are free: the step two ahead is loaded into them.
 #pragma unroll
-            for (int h = 0; h < 2; ++h) {
-                uint32_t av[16];
-#pragma unroll
-                for (int w2 = 0; w2 < 2; ++w2) {
-                    const uint32_t l = wl[2 * h + w2], u = wh[2 * h + w2];
-                    av[8 * w2 + 0] = lut_load(lut_addr<0>(l, lane_const));
-                    av[8 * w2 + 1] = lut_load(lut_addr<0>(u, lane_const));
-                    av[8 * w2 + 2] = lut_load(lut_addr<1>(l, lane_const));
-                    av[8 * w2 + 3] = lut_load(lut_addr<1>(u, lane_const));
-                    av[8 * w2 + 4] = lut_load(lut_addr<2>(l, lane_const));
-                    av[8 * w2 + 5] = lut_load(lut_addr<2>(u, lane_const));
-                    av[8 * w2 + 6] = lut_load(lut_addr<3>(l, lane_const));
-                    av[8 * w2 + 7] = lut_load(lut_addr<3>(u, lane_const));
+            for (int w = 0; w < 4; ++w) {
+                const uint32_t l = w == 0 ? lo.x : (w == 1 ? lo.y : (w == 2 ? lo.z : lo.w));
+                const uint32_t u = w == 0 ? hi.x : (w == 1 ? hi.y : (w == 2 ? hi.z : hi.w));
+                uint32_t ad[8];
+                ad[0] = lut_addr<0>(l, lane_const);
+                ad[1] = lut_addr<0>(u, lane_const);
+                ad[2] = lut_addr<1>(l, lane_const);
+                ad[3] = lut_addr<1>(u, lane_const);
+                ad[4] = lut_addr<2>(l, lane_const);
+                ad[5] = lut_addr<2>(u, lane_const);
+                ad[6] = lut_addr<3>(l, lane_const);
+                ad[7] = lut_addr<3>(u, lane_const);
+                if (w == 3) {
+                    if (s < 2) load_step(cur, s + 2, true, lo, hi);
+                    else load_step(nxt, s - 2, has_next, lo, hi);
                 }
+                uint32_t av[8];
 #pragma unroll
-                for (int w2 = 0; w2 < 2; ++w2) {
-                    const int w = 2 * h + w2;
-                    mma_tf32(acc0, av[8 * w2 + 0], av[8 * w2 + 1], av[8 * w2 + 2], av[8 * w2 + 3], bfrag[s][4 * w + 0],
-                             bfrag[s][4 * w + 1]);
-                    mma_tf32(acc1, av[8 * w2 + 4], av[8 * w2 + 5], av[8 * w2 + 6], av[8 * w2 + 7], bfrag[s][4 * w + 2],
-                             bfrag[s][4 * w + 3]);
-                }
+                for (int k = 0; k < 8; ++k) av[k] = lut_load(ad[k]);
+                mma_tf32(acc0, av[0], av[1], av[2], av[3], bfrag[s][4 * w + 0], bfrag[s][4 * w + 1]);
+                mma_tf32(acc1, av[4], av[5], av[6], av[7], bfrag[s][4 * w + 2], bfrag[s][4 * w + 3]);
             }
         }
         if (!has_next) grid_launch_dependents();  // the next kernel may start setting up
@@ -578,6 +629,14 @@ void launch_tq8_gemv(const uint8_t* codes, const float* norms, const float* tabl
     a.n_row_units = (n_row_tiles + a.tpu - 1) / a.tpu;
     const int bp = batch <= 1 ? 1 : (batch <= 2 ? 2 : (batch <= 4 ? 4 : 8));
     a.inv_scale = 1.0f / std::sqrt(static_cast<float>(in));
+    // Blocks that fit a warp's 256-column slice are rotated inside the GEMV kernel (16-byte
+    // activation loads); larger blocks, or an unaligned activation, go through rotate_x_kernel.
+    const bool fused_rotation = block <= static_cast<uint32_t>(kSlice) && in % 8 == 0 &&
+                                reinterpret_cast<uintptr_t>(x) % 16 == 0;
+    a.x = fused_rotation ? x : nullptr;
+    a.seed_p = seed_p; a.seed_r = seed_r;
+    a.block = static_cast<int>(block);
+    a.inv_sqrt_block = 1.0f / std::sqrt(static_cast<float>(block));
     uint8_t* sp = static_cast<uint8_t*>(scratch);
     float* xrot = reinterpret_cast<float*>(sp);
     a.xrot = xrot;
@@ -603,10 +662,10 @@ void launch_tq8_gemv(const uint8_t* codes, const float* norms, const float* tabl
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = 1;
-    static const int n_attr = std::getenv("TQ_NO_PDL") ? 0 : 1;  // development switch
+    const int n_attr = 1;
 
     // 1. rotate the activation (one warp per plane x row x block)
-    {
+    if (!fused_rotation) {
         const float inv_sqrt = 1.0f / std::sqrt(static_cast<float>(block));
         const int n_warps = n_planes * batch * (in / static_cast<int>(block));
         cudaLaunchConfig_t cfg{};
@@ -689,16 +748,5 @@ void launch_tq8_gemv_static(const uint8_t* codes, const float* norms, const floa
     launch_tq8_gemv(codes, norms, table, x, y, out, in, batch, block, n_planes, seed_p, seed_r, scratch, status, sm_count,
                     stream);
 }
-
-#ifdef TQ_GEMV_TIMING
-extern "C" void tq_debug_gemv_timing(unsigned long long* out8, int reset) {
-    cudaDeviceSynchronize();
-    cudaMemcpyFromSymbol(out8, g_gemv_timing, sizeof(unsigned long long) * 8);
-    if (reset) {
-        unsigned long long z[8] = {0};
-        cudaMemcpyToSymbol(g_gemv_timing, z, sizeof z);
-    }
-}
-#endif
 
 }  // namespace tq
