@@ -105,7 +105,10 @@ tq_linear_t tq_linear_create(int in_features, int out_features, const uint8_t* p
 
 /** TurboQuantLinear::forward / fused_dequant_matmul (src/linear.cpp:20-26,
  *  src/dequantizer.cpp:606-721): x [batch, in] of x_dtype (TQ_F32 or TQ_F16; cast to
- *  fp16 first) -> y fp16 [batch, out], fp32 accumulation. */
+ *  fp16 first) -> y fp16 [batch, out], fp32 accumulation.  Up to 32 rows run through the
+ *  decode kernel (passes of 8); more rows run through the tensor-core GEMM when in_features
+ *  is a multiple of 64 (its working memory, batch * in * 2 bytes per rotation plane, is
+ *  allocated on first use and kept). */
 int tq_linear_forward(tq_linear_t lin, const void* x, int x_dtype, int batch, void* y_fp16, void* stream);
 
 /** Forward pass that performs no device or host allocation of any kind.
@@ -146,6 +149,12 @@ size_t tq_linear_noalloc_scratch_limit(void);
  *  result [out, in] as TQ_F32 (bit-identical to the reference's CPU result) or TQ_F16
  *  (the same values rounded to nearest even, src/turboquant_c_dequant.cpp:156-167). */
 int tq_linear_dequantize(tq_linear_t lin, void* result, int result_dtype, void* stream);
+
+/** Waits for the device, then returns 0 if every kernel launched through this handle ran to
+ *  completion, non-zero (see tq_last_error) if one refused to run or gave up on a bounded wait.
+ *  Calls with host output check this themselves; callers that pass device pointers and
+ *  synchronise on their own can ask here.  No counterpart in the reference. */
+int tq_linear_status(tq_linear_t lin);
 
 int tq_linear_in_features(tq_linear_t lin);
 int tq_linear_out_features(tq_linear_t lin);

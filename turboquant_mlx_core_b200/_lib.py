@@ -75,6 +75,7 @@ def load() -> C.CDLL:
     sig("tq_linear_forward_noalloc", i, [vp, vp, i, vp, vp])
     sig("tq_linear_noalloc_scratch_limit", C.c_size_t, [])
     sig("tq_linear_dequantize", i, [vp, vp, i, vp])
+    sig("tq_linear_status", i, [vp])
     sig("tq_linear_in_features", i, [vp])
     sig("tq_linear_out_features", i, [vp])
     sig("tq_linear_free", None, [vp])

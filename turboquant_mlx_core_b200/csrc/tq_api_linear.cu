@@ -94,6 +94,8 @@ public:
         }
         status_.resize(sizeof(unsigned int));
         TQ_CUDA(cudaMemset(status_.as<void>(), 0, sizeof(unsigned int)));
+        TQ_CUDA(cudaMallocHost(&h_status_, sizeof(unsigned int)));
+        *h_status_ = 0;
 
         // One launch on a zero activation: proves on this device, now, that the kernel's
         // shared-memory layout holds, instead of failing on the first real forward.
@@ -148,8 +150,20 @@ public:
         launch_forward(d_x, batch, d_y, st);
         if (!y_dev) {
             TQ_CUDA(cudaMemcpyAsync(y, d_y, ny * sizeof(__half), cudaMemcpyDeviceToHost, st));
+            // the kernels' error word rides along with the result (no second synchronisation)
+            TQ_CUDA(cudaMemcpyAsync(h_status_, status_.as<void>(), sizeof(unsigned int), cudaMemcpyDeviceToHost, st));
             TQ_CUDA(cudaStreamSynchronize(st));
+            require_ok(*h_status_);
         }
+    }
+
+    // Waits for the device and reports whether any kernel of this handle refused to run or gave
+    // up on a bounded wait (the word is sticky).
+    void check_status() {
+        unsigned int h = 0;
+        TQ_CUDA(cudaSetDevice(device_));
+        TQ_CUDA(cudaMemcpy(&h, status_.as<void>(), sizeof h, cudaMemcpyDeviceToHost));
+        require_ok(h);
     }
 
     // result: [out, in] fp32 or fp16, host or device.
@@ -191,15 +205,32 @@ public:
                                    dual_ ? 2 : 1, seed_p_, seed_r_, status_.as<unsigned int>(), sm_count_, st);
     }
 
-    void check_status() {
-        unsigned int h = 0;
-        TQ_CUDA(cudaMemcpy(&h, status_.as<void>(), sizeof h, cudaMemcpyDeviceToHost));
-        TQ_REQUIRE(h == 0, "tq8_gemv: unexpected shared-memory base address on this device; kernel did not run");
+    ~TurboQuantLinear() {
+        if (h_status_) cudaFreeHost(h_status_);
     }
 
 private:
-    // Device pointers only.  Batches above 8 rows are issued as passes of 8.
+    static void require_ok(unsigned int h) {
+        if (h == 0) return;
+        const char* what = h == 1 ? "decode kernel: unexpected shared-memory base address, kernel did not run"
+                           : (h == 4 || h == 5) ? "decode kernel: a bounded wait on a partial-sum barrier gave up"
+                           : h == 9 ? "prefill kernel: shared-memory layout does not fit, kernel did not run"
+                           : (h >= 6 && h <= 8) ? "prefill kernel: a bounded wait on a pipeline barrier gave up"
+                                                : "kernel reported an unknown status";
+        throw Error(std::string("TurboQuantLinear: ") + what + " (status " + std::to_string(h) + ")");
+    }
+
+    // Device pointers only.  More than kGemmMinBatch rows go to the tensor-core GEMM (when the
+    // shape allows); otherwise batches above 8 rows are issued as passes of 8 through the GEMV.
+    static constexpr int kGemmMinBatch = 32;
     void launch_forward(const __half* d_x, int batch, __half* d_y, cudaStream_t st) {
+        if (batch > kGemmMinBatch && tq::gemm_supported(in_)) {
+            const int planes = dual_ ? 2 : 1;
+            gemm_scratch_.reserve(tq::gemm_scratch_bytes(in_, batch, planes));
+            tq::launch_tq8_gemm(codes_.as<uint8_t>(), norms_.as<float>(), tables_.as<float>(), d_x, d_y, out_, in_, batch,
+                                block_, planes, seed_p_, seed_r_, gemm_scratch_.as<void>(), status_.as<unsigned int>(), st);
+            return;
+        }
         for (int b0 = 0; b0 < batch; b0 += 8) {
             const int nb = batch - b0 < 8 ? batch - b0 : 8;
             tq::launch_tq8_gemv(codes_.as<uint8_t>(), norms_.as<float>(), tables_.as<float>(),
@@ -214,8 +245,9 @@ private:
     int device_ = 0, sm_count_ = 0;
     bool primary_5bit_ = false, has_residual_ = false, shared_ = false, dual_ = false;
     uint32_t seed_p_ = 0, seed_r_ = 0;
-    DeviceBuffer codes_, norms_, tables_, scratch_, status_;
+    DeviceBuffer codes_, norms_, tables_, scratch_, gemm_scratch_, status_;
     DeviceBuffer x_f16_, x_f32_, y_f16_;  // staging for host-side callers
+    unsigned int* h_status_ = nullptr;    // pinned host copy of the status word
 };
 
 }  // namespace turboquant
@@ -304,6 +336,14 @@ int tq_quantize_weight(const float* weight, int out_features, int in_features, c
         const uint32_t h_seeds[3] = {seed_p, (shared_rotation && residual_bits > 0) ? 0u : seed_r, block};
         TQ_CUDA(cudaMemcpyAsync(seeds, h_seeds, sizeof h_seeds, cudaMemcpyDefault, st));
         TQ_CUDA(cudaStreamSynchronize(st));  // scratch and staging buffers die here
+        return 0;
+    });
+}
+
+int tq_linear_status(tq_linear_t lin) {
+    return guarded<int>(0, -1, [&]() {
+        TQ_REQUIRE(lin && lin->impl, "tq_linear_status: NULL handle");
+        lin->impl->check_status();
         return 0;
     });
 }

@@ -1,0 +1,416 @@
+// Fused TQ8 dequantise + GEMM for prefill (tens to thousands of activation rows) on the
+// 5th-generation tensor cores: tcgen05.mma with the accumulator in tensor memory.
+//
+// Replaces, for large batches, the reference's tq_dequant_mm Metal kernel and its host wrapper
+// (metal/turboquant_dequant_mm.metal:152-313, src/dequantizer.cpp:606-721):
+//   y[m, r] = fp16( norm[r] * sum_j W~[r, j] * fp16(x[m, j]) ),  fp32 accumulate.
+//
+// Same algebra as the decode kernel: the activation is rotated once (forward WHT of every block
+// of every row, written as fp16 by rotate_rows_f16_kernel), and the weight side is a table
+// lookup per code:   y[m, r] = norm[r] * inv_scale * sum_j table[code[r, j]] * xrot[m, j].
+// Dual-rotation weights run as two passes over K into the same accumulator (primary table
+// against x rotated with the primary seed, residual table against x rotated with the residual
+// seed).
+//
+// One CTA computes a 128 (weight rows) x 256 (activation rows) tile of y^T:
+//   D[128 x 256] (TMEM, fp32) += A[128 x 64] (weights, fp16, smem) . B[256 x 64]^T (xrot, fp16, smem)
+// per 64-column K block, as four tcgen05.mma (M 128, N 256, K 16) issued by one thread.
+//   warps 0-7  producers: codes HBM -> registers -> lookup (lane-private fp16 table in shared
+//              memory) -> A tile in shared memory; xrot tile L2 -> shared memory with cp.async;
+//              three stages, full/empty mbarriers
+//   warp 8     waits for a full stage, issues the MMAs, commits to the stage's empty barrier
+//   warps 0-7  epilogue: tcgen05.ld the accumulator, scale by norm * inv_scale, store fp16
+// The dequantised weights never touch HBM; a weight tile is looked up once per 256 activation
+// rows.  Roofline: tensor pipe (2 * M * out * in flops), with the table lookups (one shared-memory
+// load per weight per 256 activation rows) as the competing pipe.
+//
+// Shared-memory operand layout (both operands K-major, no swizzle): 8 x 8 fp16 core matrices of
+// 128 contiguous bytes (8 rows of 16 bytes); core matrices adjacent in K are 128 bytes apart
+// (leading byte offset), 8-row groups are 1024 bytes apart (stride byte offset).
+//
+// Every wait is bounded: a barrier that does not complete within 0.2 s sets the status word and
+// an abort flag, after which all warps fall through to the exit path (which still frees the
+// tensor memory).
+#include <cmath>
+#include <cstdint>
+
+#include "tq_common.cuh"
+#include "tq_kernels.cuh"
+
+namespace tq {
+
+namespace {
+
+constexpr int kTileRows = 128;  // weight rows per CTA (MMA M)
+constexpr int kTileTok = 256;   // activation rows per CTA (MMA N)
+constexpr int kBlockK = 64;     // K columns per stage
+constexpr int kStages = 3;
+constexpr int kProducerWarps = 8;
+constexpr int kProducerThreads = kProducerWarps * 32;
+constexpr int kGemmThreads = kProducerThreads + 32;
+constexpr uint32_t kABytes = kTileRows * kBlockK * 2;  // 16 KB
+constexpr uint32_t kBBytes = kTileTok * kBlockK * 2;   // 32 KB
+constexpr uint32_t kLutBytes = 256 * 32 * 4;           // one plane: 256 entries x 32 lane copies x (fp16, fp16)
+constexpr uint32_t kTmemCols = 256;
+constexpr unsigned long long kGemmWaitLimitNs = 200ull * 1000 * 1000;
+
+// instruction descriptor: D fp32, A and B fp16, both K-major, N = 256, M = 128
+constexpr uint32_t kInstrDesc = (1u << 4) | (static_cast<uint32_t>(kTileTok >> 3) << 17) | (static_cast<uint32_t>(kTileRows >> 4) << 24);
+
+__device__ __forceinline__ uint32_t smem_addr(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
+
+__device__ __forceinline__ unsigned long long timer_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+__device__ __forceinline__ void bar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void bar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+// Bounded wait; gives up at once when another thread has already flagged a failure.
+__device__ __forceinline__ bool bar_wait(uint32_t bar, uint32_t parity, volatile unsigned int* abort_flag) {
+    unsigned long long t0 = 0;
+    for (uint32_t spin = 0;; ++spin) {
+        uint32_t done;
+        asm volatile(
+            "{ .reg .pred p; mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2; selp.u32 %0, 1, 0, p; }"
+            : "=r"(done)
+            : "r"(bar), "r"(parity)
+            : "memory");
+        if (done) return true;
+        if ((spin & 15) == 15 && *abort_flag) return false;
+        if (spin == 64) t0 = timer_ns();
+        if (spin > 64 && (spin & 63) == 0 && timer_ns() - t0 > kGemmWaitLimitNs) return false;
+    }
+}
+
+// shared-memory matrix descriptor: K-major, no swizzle, LBO 128 B, SBO 1024 B, descriptor version 1
+__device__ __forceinline__ uint64_t smem_desc(uint32_t addr) {
+    return static_cast<uint64_t>((addr >> 4) & 0x3FFFu) | (static_cast<uint64_t>(128u >> 4) << 16) |
+           (static_cast<uint64_t>(1024u >> 4) << 32) | (1ull << 46);
+}
+
+__device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t accumulate) {
+    asm volatile(
+        "{ .reg .pred p; setp.ne.b32 p, %4, 0;\n"
+        "  tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5}, p; }"
+        :
+        : "r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(kInstrDesc), "r"(accumulate), "r"(0u)
+        : "memory");
+}
+// Arrives on the barrier once every MMA issued so far by this thread has finished.
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&v)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
+          "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]), "=r"(v[16]),
+          "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]),
+          "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+        : "r"(taddr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// ---- activation rotation to fp16 ---------------------------------------------------------------
+// One warp per (plane, row, WHT block): xrot = fp16( FWHT(sign o fp16(x)) / sqrt(bs) ), [plane][row][in].
+template <int E>
+__global__ void __launch_bounds__(128) rotate_rows_f16_kernel(const __half* __restrict__ x, __half* __restrict__ xrot,
+                                                              int in, long rows, int n_planes, uint32_t seed_p,
+                                                              uint32_t seed_r, float inv_sqrt) {
+    constexpr int BS = 32 * E;
+    const int lane = threadIdx.x & 31;
+    const long blocks_per_row = in / BS;
+    const long total = static_cast<long>(n_planes) * rows * blocks_per_row;
+    const long warp = (static_cast<long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+    if (warp >= total) return;
+    const int plane = static_cast<int>(warp / (rows * blocks_per_row));
+    const long rem = warp - static_cast<long>(plane) * rows * blocks_per_row;
+    const long row = rem / blocks_per_row, blk = rem - row * blocks_per_row;
+    const uint32_t seed = plane ? seed_r : seed_p;
+    const __half* src = x + row * in + blk * BS + lane * E;
+    float v[E];
+#pragma unroll
+    for (int j = 0; j < E; ++j) v[j] = __half2float(src[j]) * sign_value(seed, static_cast<uint32_t>(lane * E + j));
+    warp_fwht<E>(v, lane);
+    __half* dst = xrot + (static_cast<long>(plane) * rows + row) * in + blk * BS + lane * E;
+#pragma unroll
+    for (int j = 0; j < E; ++j) dst[j] = __float2half_rn(v[j] * inv_sqrt);
+}
+
+struct GemmArgs {
+    const uint8_t* codes;   // [out, in] joint bytes
+    const float* norms;     // [out]
+    const float* table;     // [n_planes, 256] fp32
+    const __half* xrot;     // [n_planes, m, in] fp16
+    __half* y;              // [m, out]
+    unsigned int* status;   // device error word (0 = ok)
+    int out, in, m, n_planes;
+    float inv_scale;
+};
+
+__global__ void __launch_bounds__(kGemmThreads, 1) tq8_gemm_kernel(const GemmArgs p) {
+    extern __shared__ __align__(128) uint8_t gemm_smem[];
+    __shared__ __align__(8) unsigned long long s_full[kStages], s_empty[kStages], s_accum;
+    __shared__ uint32_t s_tmem_base;
+    __shared__ uint32_t s_stage[2 * kStages];  // A buffers, then B buffers
+    __shared__ unsigned int s_abort;
+
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int row0 = blockIdx.x * kTileRows;  // first weight row of the tile
+    const int tok0 = blockIdx.y * kTileTok;   // first activation row of the tile
+
+    // ---- shared-memory map -------------------------------------------------------------------
+    // The lookup tables sit at a 32 KB-aligned window address (so that table base, lane offset
+    // and scaled code occupy disjoint address bits); the 16 KB / 32 KB stage buffers are packed
+    // around them.
+    const uint32_t raw = smem_addr(gemm_smem);
+    const uint32_t base = (raw + 127u) & ~127u;
+    const uint32_t lut_addr = (base + 32767u) & ~32767u;
+    const uint32_t lut_end = lut_addr + kLutBytes * static_cast<uint32_t>(p.n_planes);
+    uint32_t dyn_bytes;
+    asm("mov.u32 %0, %%dynamic_smem_size;" : "=r"(dyn_bytes));
+    {
+        // Same arithmetic in every thread; thread 0 publishes the stage addresses.
+        uint32_t lo = base, hi = lut_end;  // bump pointers below and above the tables
+        uint32_t addr[2 * kStages];
+#pragma unroll
+        for (int s = 0; s < 2 * kStages; ++s) {
+            const uint32_t bytes = s < kStages ? kABytes : kBBytes;
+            if (lo + bytes <= lut_addr) { addr[s] = lo; lo += bytes; }
+            else { addr[s] = hi; hi += bytes; }
+        }
+        if (hi > raw + dyn_bytes || lut_end > raw + dyn_bytes) {  // layout does not fit: refuse to run (nothing allocated yet)
+            if (tid == 0) atomicExch(p.status, 9u);
+            return;
+        }
+        if (tid == 0) {
+#pragma unroll
+            for (int s = 0; s < 2 * kStages; ++s) s_stage[s] = addr[s];
+        }
+    }
+    const uint32_t bar_full = smem_addr(&s_full[0]), bar_empty = smem_addr(&s_empty[0]), bar_accum = smem_addr(&s_accum);
+
+    if (tid == 0) {
+        for (int s = 0; s < kStages; ++s) {
+            bar_init(bar_full + 8u * s, kProducerThreads);
+            bar_init(bar_empty + 8u * s, 1);
+        }
+        bar_init(bar_accum, 1);
+        s_abort = 0u;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == kProducerWarps) {  // the MMA warp owns the tensor-memory allocation
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_addr(&s_tmem_base)),
+                     "r"(kTmemCols)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    // lookup tables: entry e, lane copy l at lut + plane * 32 KB + e * 128 + l * 4, value (t, t) as fp16
+    for (int i = tid; i < 256 * 8 * p.n_planes; i += kGemmThreads) {
+        const int e = i >> 3, c4 = (i & 7) * 4;  // e counts across planes
+        const __half h = __float2half_rn(__ldg(p.table + e));
+        const uint32_t v = static_cast<uint32_t>(__half_as_ushort(h)) * 0x00010001u;
+        asm volatile("st.shared.v4.b32 [%0], {%1, %1, %1, %1};" ::"r"(lut_addr + static_cast<uint32_t>(e) * 128u + c4 * 4u), "r"(v)
+                     : "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem_d = s_tmem_base;
+    volatile unsigned int* abort_flag = &s_abort;
+
+    const int kb_per_plane = p.in / kBlockK;
+    const int n_kb = kb_per_plane * p.n_planes;
+
+    if (warp < kProducerWarps) {
+        // ---- producers ------------------------------------------------------------------------
+        // A tile: warp w owns rows 16w .. 16w+15; lane -> (row & 7) + 8 * half + 16 * (row >> 3 & 1),
+        // so that the 8 lanes of a store phase write one 128-byte core-matrix column.
+        const int ar = 16 * warp + (lane & 7) + 8 * (lane >> 4);  // row inside the tile
+        const int ah = (lane >> 3) & 1;                           // which 32 columns of the K block
+        const int grow = min(row0 + ar, p.out - 1);               // rows past the matrix repeat the last row (never stored)
+        const uint8_t* code_ptr = p.codes + static_cast<size_t>(grow) * p.in + 32 * ah;
+        const uint32_t a_off = static_cast<uint32_t>(ar >> 3) * 1024u + static_cast<uint32_t>(ar & 7) * 16u +
+                               static_cast<uint32_t>(4 * ah) * 128u;
+        // B tile: per k block 32 row groups x 8 core columns; a warp iteration copies one row
+        // group x 4 core columns (lane -> row lane & 7, core column lane >> 3).
+        const int br = lane & 7, bc = lane >> 3;
+        const uint32_t lut_lane = lut_addr + static_cast<uint32_t>(lane) * 4u;
+
+        uint4 c0 = __ldg(reinterpret_cast<const uint4*>(code_ptr));
+        uint4 c1 = __ldg(reinterpret_cast<const uint4*>(code_ptr + 16));
+        for (int kb = 0; kb < n_kb; ++kb) {
+            const int s = kb % kStages;
+            const int plane = kb >= kb_per_plane ? 1 : 0;
+            const int kcol = (kb - plane * kb_per_plane) * kBlockK;
+            if (kb >= kStages && !bar_wait(bar_empty + 8u * s, ((kb / kStages) - 1) & 1, abort_flag)) {
+                atomicExch(p.status, 6u);
+                atomicExch(&s_abort, 1u);
+                break;
+            }
+            const uint32_t a_stage = s_stage[s], b_stage = s_stage[kStages + s];
+            // activation tile: 8 x 16-byte cp.async per thread, rows past m zero-filled
+            const __half* xp = p.xrot + static_cast<size_t>(plane) * p.m * p.in + kcol;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const int combo = warp * 8 + i, rg = combo >> 1, kc = (combo & 1) * 4 + bc;
+                const int tok = tok0 + rg * 8 + br;
+                const bool ok = tok < p.m;
+                const __half* src = xp + static_cast<size_t>(ok ? tok : 0) * p.in + kc * 8;
+                const uint32_t dst = b_stage + static_cast<uint32_t>(rg) * 1024u + static_cast<uint32_t>(kc) * 128u +
+                                     static_cast<uint32_t>(br) * 16u;
+                asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(ok ? 16u : 0u) : "memory");
+            }
+            // weight tile: 32 codes -> 32 fp16 -> four 16-byte stores
+            const uint32_t w[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
+            if (kb + 1 < n_kb) {  // next block's codes (the same bytes again for the second plane)
+                const int nplane = (kb + 1) >= kb_per_plane ? 1 : 0;
+                const int ncol = (kb + 1 - nplane * kb_per_plane) * kBlockK;
+                c0 = __ldg(reinterpret_cast<const uint4*>(code_ptr + ncol));
+                c1 = __ldg(reinterpret_cast<const uint4*>(code_ptr + ncol + 16));
+            }
+            const uint32_t lut_p = lut_lane + static_cast<uint32_t>(plane) * kLutBytes;
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {  // core column 4 * ah + c : codes 8c .. 8c+7 of this thread
+                uint32_t packed[4];
+#pragma unroll
+                for (int h = 0; h < 4; ++h) {
+                    const uint32_t word = w[2 * c + (h >> 1)];
+                    const int b0 = (h & 1) * 2;  // bytes b0, b0 + 1 of the word
+                    const uint32_t i0 = b0 == 0 ? (word << 7) : (word >> 9);
+                    const uint32_t i1 = b0 == 0 ? (word >> 1) : (word >> 17);
+                    uint32_t v0, v1;
+                    asm("ld.shared.b32 %0, [%1];" : "=r"(v0) : "r"(lut_p | (i0 & (255u << 7))));
+                    asm("ld.shared.b32 %0, [%1];" : "=r"(v1) : "r"(lut_p | (i1 & (255u << 7))));
+                    packed[h] = __byte_perm(v0, v1, 0x5410);
+                }
+                asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(a_stage + a_off + static_cast<uint32_t>(c) * 128u),
+                             "r"(packed[0]), "r"(packed[1]), "r"(packed[2]), "r"(packed[3])
+                             : "memory");
+            }
+            asm volatile("cp.async.wait_all;" ::: "memory");
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic-proxy writes -> visible to the tensor core
+            bar_arrive(bar_full + 8u * s);
+        }
+    } else {
+        // ---- MMA issuer -----------------------------------------------------------------------
+        for (int kb = 0; kb < n_kb; ++kb) {
+            const int s = kb % kStages;
+            if (!bar_wait(bar_full + 8u * s, (kb / kStages) & 1, abort_flag)) {
+                if (lane == 0) {
+                    atomicExch(p.status, 7u);
+                    atomicExch(&s_abort, 1u);
+                }
+                break;
+            }
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            if (lane == 0) {
+                const uint32_t a_stage = s_stage[s], b_stage = s_stage[kStages + s];
+#pragma unroll
+                for (int j = 0; j < kBlockK / 16; ++j)
+                    umma_f16(tmem_d, smem_desc(a_stage + 256u * j), smem_desc(b_stage + 256u * j), (kb | j) != 0 ? 1u : 0u);
+                umma_commit(bar_empty + 8u * s);  // the stage may be refilled when these MMAs are done
+            }
+            __syncwarp();
+        }
+        if (lane == 0) umma_commit(bar_accum);
+        __syncwarp();
+    }
+
+    // ---- epilogue (warps 0-7): TMEM lanes 32 * (warp & 3), columns 128 * (warp >> 2) .. +127 ----
+    if (warp < kProducerWarps) {
+        const bool ok = !*abort_flag && bar_wait(bar_accum, 0, abort_flag);
+        if (!ok) {
+            atomicExch(p.status, 8u);
+            atomicExch(&s_abort, 1u);
+        } else {
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const int r = row0 + 32 * (warp & 3) + lane;
+            const bool r_ok = r < p.out;
+            const float scale = r_ok ? __ldg(p.norms + r) * p.inv_scale : 0.f;
+#pragma unroll 1
+            for (int cb = 0; cb < 4; ++cb) {
+                const int col0 = 128 * (warp >> 2) + 32 * cb;
+                uint32_t v[32];
+                tmem_ld32(tmem_d + (static_cast<uint32_t>(32 * (warp & 3)) << 16) + static_cast<uint32_t>(col0), v);
+#pragma unroll
+                for (int j = 0; j < 32; ++j) {
+                    const int tok = tok0 + col0 + j;
+                    if (r_ok && tok < p.m) p.y[static_cast<size_t>(tok) * p.out + r] = __float2half_rn(__uint_as_float(v[j]) * scale);
+                }
+            }
+        }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == kProducerWarps) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_d), "r"(kTmemCols) : "memory");
+    }
+}
+
+}  // namespace
+
+size_t gemm_scratch_bytes(int in, long m, int n_planes) {
+    return static_cast<size_t>(n_planes) * static_cast<size_t>(m) * static_cast<size_t>(in) * sizeof(__half);
+}
+
+bool gemm_supported(int in) { return in % kBlockK == 0; }
+
+void launch_tq8_gemm(const uint8_t* codes, const float* norms, const float* table, const __half* x, __half* y, int out,
+                     int in, long m, uint32_t block, int n_planes, uint32_t seed_p, uint32_t seed_r, void* scratch,
+                     unsigned int* status, cudaStream_t stream) {
+    TQ_REQUIRE(n_planes == 1 || n_planes == 2, "tq8_gemm: one or two rotation planes");
+    TQ_REQUIRE(gemm_supported(in), "tq8_gemm: in_features must be a multiple of 64");
+    TQ_REQUIRE(is_pow2(block) && block >= 32 && block <= 1024, "WHT block size must be a power of two in [32, 1024]");
+    TQ_REQUIRE(in % static_cast<int>(block) == 0, "in_features must be divisible by block_size");
+    TQ_REQUIRE(m >= 1 && m < (1L << 30), "tq8_gemm: bad number of activation rows");
+    TQ_REQUIRE(scratch != nullptr, "tq8_gemm needs its scratch buffer");
+    if (out == 0) return;
+    __half* xrot = static_cast<__half*>(scratch);
+
+    // 1. rotate every activation row (one warp per plane x row x block)
+    {
+        const float inv_sqrt = 1.0f / std::sqrt(static_cast<float>(block));
+        const long n_warps = static_cast<long>(n_planes) * m * (in / static_cast<int>(block));
+        const unsigned int grid = static_cast<unsigned int>((n_warps + 3) / 4);
+#define TQ_ROT16_CASE(EV)                                                                                          \
+    case 32 * EV:                                                                                                  \
+        rotate_rows_f16_kernel<EV><<<grid, 128, 0, stream>>>(x, xrot, in, m, n_planes, seed_p, seed_r, inv_sqrt);  \
+        break;
+        switch (block) {
+            TQ_ROT16_CASE(1) TQ_ROT16_CASE(2) TQ_ROT16_CASE(4) TQ_ROT16_CASE(8) TQ_ROT16_CASE(16) TQ_ROT16_CASE(32)
+            default: throw Error("unsupported WHT block size");
+        }
+#undef TQ_ROT16_CASE
+        TQ_CUDA(cudaGetLastError());
+    }
+    // 2. the GEMM
+    GemmArgs a{};
+    a.codes = codes; a.norms = norms; a.table = table; a.xrot = xrot; a.y = y; a.status = status;
+    a.out = out; a.in = in; a.m = static_cast<int>(m); a.n_planes = n_planes;
+    a.inv_scale = 1.0f / std::sqrt(static_cast<float>(in));
+    // stages + tables + worst-case padding in front of the 32 KB-aligned tables
+    const size_t smem = kStages * (kABytes + kBBytes) + static_cast<size_t>(n_planes) * kLutBytes + 16384 + 1024;
+    static bool configured[64] = {false};
+    int dev = 0;
+    TQ_CUDA(cudaGetDevice(&dev));
+    if (dev >= 64 || !configured[dev]) {
+        TQ_CUDA(cudaFuncSetAttribute(tq8_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     static_cast<int>(kStages * (kABytes + kBBytes) + 2 * kLutBytes + 16384 + 1024)));
+        if (dev < 64) configured[dev] = true;
+    }
+    const dim3 grid(static_cast<unsigned int>((out + kTileRows - 1) / kTileRows),
+                    static_cast<unsigned int>((m + kTileTok - 1) / kTileTok));
+    tq8_gemm_kernel<<<grid, kGemmThreads, smem, stream>>>(a);
+    TQ_CUDA(cudaGetLastError());
+}
+
+}  // namespace tq
