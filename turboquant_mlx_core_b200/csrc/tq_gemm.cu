@@ -15,10 +15,11 @@
 // One CTA computes a 128 (weight rows) x 256 (activation rows) tile of y^T:
 //   D[128 x 256] (TMEM, fp32) += A[128 x 64] (weights, fp16, smem) . B[256 x 64]^T (xrot, fp16, smem)
 // per 64-column K block, as four tcgen05.mma (M 128, N 256, K 16) issued by one thread.
-//   warps 0-7  producers: codes HBM -> registers -> lookup (lane-private fp16 table in shared
-//              memory) -> A tile in shared memory; xrot tile L2 -> shared memory with cp.async;
-//              three stages, full/empty mbarriers
-//   warp 8     waits for a full stage, issues the MMAs, commits to the stage's empty barrier
+//   warps 0-7  producers: codes HBM -> registers (four K blocks ahead) -> lookup (lane-private
+//              fp16 table in shared memory) -> weight tile in shared memory, ring of 3
+//   warp 9     activation tiles: the rotation kernel stores xrot in operand-tile order, so a tile
+//              is one contiguous 32 KB bulk copy (cp.async.bulk, mbarrier complete_tx), ring of 4
+//   warp 8     waits for both tiles of a K block, issues the MMAs, commits to the rings' empty barriers
 //   warps 0-7  epilogue: tcgen05.ld the accumulator, scale by norm * inv_scale, store fp16
 // The dequantised weights never touch HBM; a weight tile is looked up once per 256 activation
 // rows.  Roofline: tensor pipe (2 * M * out * in flops), with the table lookups (one shared-memory
@@ -44,14 +45,21 @@ namespace {
 constexpr int kTileRows = 128;  // weight rows per CTA (MMA M)
 constexpr int kTileTok = 256;   // activation rows per CTA (MMA N)
 constexpr int kBlockK = 64;     // K columns per stage
-constexpr int kStages = 3;
+constexpr int kAStages = 3;    // weight-tile ring (filled just in time by the lookups)
+constexpr int kBStagesMax = 4; // activation-tile ring (cp.async two K blocks ahead); 3 with two table planes
+constexpr int kFull = 4;       // "K block ready" barriers
 constexpr int kProducerWarps = 8;
 constexpr int kProducerThreads = kProducerWarps * 32;
-constexpr int kGemmThreads = kProducerThreads + 32;
+constexpr int kMmaWarp = kProducerWarps;       // issues the MMAs, owns the tensor-memory allocation
+constexpr int kCopyWarp = kProducerWarps + 1;  // issues the activation-tile bulk copies
+constexpr int kGemmThreads = kProducerThreads + 64;
 constexpr uint32_t kABytes = kTileRows * kBlockK * 2;  // 16 KB
 constexpr uint32_t kBBytes = kTileTok * kBlockK * 2;   // 32 KB
 constexpr uint32_t kLutBytes = 256 * 32 * 4;           // one plane: 256 entries x 32 lane copies x (fp16, fp16)
 constexpr uint32_t kTmemCols = 256;
+// rings + tables (4 activation stages with one table plane, 3 with two) + worst-case padding in
+// front of the 32 KB-aligned tables
+constexpr size_t kGemmSmemBytes = kAStages * kABytes + kBStagesMax * kBBytes + kLutBytes + 16384 + 1024;
 constexpr unsigned long long kGemmWaitLimitNs = 200ull * 1000 * 1000;
 
 // instruction descriptor: D fp32, A and B fp16, both K-major, N = 256, M = 128
@@ -118,37 +126,57 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&v)[32]) {
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
-// ---- activation rotation to fp16 ---------------------------------------------------------------
-// One warp per (plane, row, WHT block): xrot = fp16( FWHT(sign o fp16(x)) / sqrt(bs) ), [plane][row][in].
+// ---- activation rotation to fp16, written in operand-tile order --------------------------------
+// One warp per (plane, row, WHT block): xrot = fp16( FWHT(sign o fp16(x)) / sqrt(bs) ).
+// Output layout: [plane][row tile of 256][K block of 64][32 KB tile], the tile being exactly the
+// shared-memory image the GEMM wants (8 x 8 core matrices: [row group 32][core column 8][row 8][8 fp16]),
+// so that a CTA fetches an activation tile with ONE contiguous bulk copy.  Rows past the last
+// one are left as they are: they only feed accumulator columns that are never stored.
 template <int E>
 __global__ void __launch_bounds__(128) rotate_rows_f16_kernel(const __half* __restrict__ x, __half* __restrict__ xrot,
                                                               int in, long rows, int n_planes, uint32_t seed_p,
                                                               uint32_t seed_r, float inv_sqrt) {
     constexpr int BS = 32 * E;
+    constexpr int V = E < 8 ? E : 8;  // halves per vector store (one core-matrix row holds 8)
     const int lane = threadIdx.x & 31;
     const long blocks_per_row = in / BS;
     const long total = static_cast<long>(n_planes) * rows * blocks_per_row;
     const long warp = (static_cast<long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
     if (warp >= total) return;
+    // consecutive warps take consecutive rows of the same block: their stores fill whole lines
     const int plane = static_cast<int>(warp / (rows * blocks_per_row));
     const long rem = warp - static_cast<long>(plane) * rows * blocks_per_row;
-    const long row = rem / blocks_per_row, blk = rem - row * blocks_per_row;
+    const long blk = rem / rows, row = rem - blk * rows;
     const uint32_t seed = plane ? seed_r : seed_p;
     const __half* src = x + row * in + blk * BS + lane * E;
     float v[E];
 #pragma unroll
     for (int j = 0; j < E; ++j) v[j] = __half2float(src[j]) * sign_value(seed, static_cast<uint32_t>(lane * E + j));
     warp_fwht<E>(v, lane);
-    __half* dst = xrot + (static_cast<long>(plane) * rows + row) * in + blk * BS + lane * E;
+    const long n_row_tiles = (rows + kTileTok - 1) / kTileTok;
+    const long kb_per_plane = in / kBlockK;
+    const long rt = row / kTileTok, rin = row - rt * kTileTok;
 #pragma unroll
-    for (int j = 0; j < E; ++j) dst[j] = __float2half_rn(v[j] * inv_sqrt);
+    for (int j0 = 0; j0 < E; j0 += V) {
+        const long col = blk * BS + lane * E + j0;
+        const long kb = col / kBlockK, cin = col - kb * kBlockK;
+        const long tile = (static_cast<long>(plane) * n_row_tiles + rt) * kb_per_plane + kb;
+        __half* dst = xrot + tile * (kTileTok * kBlockK) + (((rin >> 3) * 8 + (cin >> 3)) * 8 + (rin & 7)) * 8 + (cin & 7);
+        __align__(16) __half h[V];
+#pragma unroll
+        for (int j = 0; j < V; ++j) h[j] = __float2half_rn(v[j0 + j] * inv_sqrt);
+        if constexpr (V == 8) *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<const uint4*>(h);
+        else if constexpr (V == 4) *reinterpret_cast<uint2*>(dst) = *reinterpret_cast<const uint2*>(h);
+        else if constexpr (V == 2) *reinterpret_cast<uint32_t*>(dst) = *reinterpret_cast<const uint32_t*>(h);
+        else dst[0] = h[0];
+    }
 }
 
 struct GemmArgs {
     const uint8_t* codes;   // [out, in] joint bytes
     const float* norms;     // [out]
     const float* table;     // [n_planes, 256] fp32
-    const __half* xrot;     // [n_planes, m, in] fp16
+    const __half* xrot;     // rotated activation in operand-tile order (see rotate_rows_f16_kernel)
     __half* y;              // [m, out]
     unsigned int* status;   // device error word (0 = ok)
     int out, in, m, n_planes;
@@ -157,9 +185,9 @@ struct GemmArgs {
 
 __global__ void __launch_bounds__(kGemmThreads, 1) tq8_gemm_kernel(const GemmArgs p) {
     extern __shared__ __align__(128) uint8_t gemm_smem[];
-    __shared__ __align__(8) unsigned long long s_full[kStages], s_empty[kStages], s_accum;
+    __shared__ __align__(8) unsigned long long s_full[kFull], s_full_b[kBStagesMax], s_empty_a[kAStages], s_empty_b[kBStagesMax], s_accum;
     __shared__ uint32_t s_tmem_base;
-    __shared__ uint32_t s_stage[2 * kStages];  // A buffers, then B buffers
+    __shared__ uint32_t s_stage[kAStages + kBStagesMax];  // A buffers, then B buffers
     __shared__ unsigned int s_abort;
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -170,6 +198,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) tq8_gemm_kernel(const GemmArg
     // The lookup tables sit at a 32 KB-aligned window address (so that table base, lane offset
     // and scaled code occupy disjoint address bits); the 16 KB / 32 KB stage buffers are packed
     // around them.
+    const int n_b = p.n_planes == 2 ? 3 : kBStagesMax;  // activation stages that fit beside the tables
     const uint32_t raw = smem_addr(gemm_smem);
     const uint32_t base = (raw + 127u) & ~127u;
     const uint32_t lut_addr = (base + 32767u) & ~32767u;
@@ -179,10 +208,11 @@ __global__ void __launch_bounds__(kGemmThreads, 1) tq8_gemm_kernel(const GemmArg
     {
         // Same arithmetic in every thread; thread 0 publishes the stage addresses.
         uint32_t lo = base, hi = lut_end;  // bump pointers below and above the tables
-        uint32_t addr[2 * kStages];
+        uint32_t addr[kAStages + kBStagesMax];
 #pragma unroll
-        for (int s = 0; s < 2 * kStages; ++s) {
-            const uint32_t bytes = s < kStages ? kABytes : kBBytes;
+        for (int s = 0; s < kAStages + kBStagesMax; ++s) {
+            const uint32_t bytes = s < kAStages ? kABytes : kBBytes;
+            if (s >= kAStages + n_b) { addr[s] = 0; continue; }
             if (lo + bytes <= lut_addr) { addr[s] = lo; lo += bytes; }
             else { addr[s] = hi; hi += bytes; }
         }
@@ -192,21 +222,25 @@ __global__ void __launch_bounds__(kGemmThreads, 1) tq8_gemm_kernel(const GemmArg
         }
         if (tid == 0) {
 #pragma unroll
-            for (int s = 0; s < 2 * kStages; ++s) s_stage[s] = addr[s];
+            for (int s = 0; s < kAStages + kBStagesMax; ++s) s_stage[s] = addr[s];
         }
     }
-    const uint32_t bar_full = smem_addr(&s_full[0]), bar_empty = smem_addr(&s_empty[0]), bar_accum = smem_addr(&s_accum);
+    const uint32_t bar_full = smem_addr(&s_full[0]), bar_full_b = smem_addr(&s_full_b[0]),
+                   bar_empty_a = smem_addr(&s_empty_a[0]), bar_empty_b = smem_addr(&s_empty_b[0]),
+                   bar_accum = smem_addr(&s_accum);
 
     if (tid == 0) {
-        for (int s = 0; s < kStages; ++s) {
-            bar_init(bar_full + 8u * s, kProducerThreads);
-            bar_init(bar_empty + 8u * s, 1);
+        for (int s = 0; s < kFull; ++s) bar_init(bar_full + 8u * s, kProducerThreads);
+        for (int s = 0; s < kAStages; ++s) bar_init(bar_empty_a + 8u * s, 1);
+        for (int s = 0; s < kBStagesMax; ++s) {
+            bar_init(bar_empty_b + 8u * s, 1);
+            bar_init(bar_full_b + 8u * s, 1);
         }
         bar_init(bar_accum, 1);
         s_abort = 0u;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    if (warp == kProducerWarps) {  // the MMA warp owns the tensor-memory allocation
+    if (warp == kMmaWarp) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_addr(&s_tmem_base)),
                      "r"(kTmemCols)
                      : "memory");
@@ -239,71 +273,97 @@ __global__ void __launch_bounds__(kGemmThreads, 1) tq8_gemm_kernel(const GemmArg
         const uint8_t* code_ptr = p.codes + static_cast<size_t>(grow) * p.in + 32 * ah;
         const uint32_t a_off = static_cast<uint32_t>(ar >> 3) * 1024u + static_cast<uint32_t>(ar & 7) * 16u +
                                static_cast<uint32_t>(4 * ah) * 128u;
-        // B tile: per k block 32 row groups x 8 core columns; a warp iteration copies one row
-        // group x 4 core columns (lane -> row lane & 7, core column lane >> 3).
-        const int br = lane & 7, bc = lane >> 3;
         const uint32_t lut_lane = lut_addr + static_cast<uint32_t>(lane) * 4u;
 
-        uint4 c0 = __ldg(reinterpret_cast<const uint4*>(code_ptr));
-        uint4 c1 = __ldg(reinterpret_cast<const uint4*>(code_ptr + 16));
+        // Codes are fetched kCodeAhead K blocks ahead into a register ring (a K block is consumed
+        // in well under the DRAM latency).  The second plane reads the same bytes again.
+        constexpr int kCodeAhead = 4;
+        auto load_codes = [&](int kb, uint4& lo, uint4& hi) {
+            if (kb < n_kb) {
+                const int plane = kb >= kb_per_plane ? 1 : 0;
+                const uint8_t* src = code_ptr + (kb - plane * kb_per_plane) * kBlockK;
+                lo = __ldg(reinterpret_cast<const uint4*>(src));
+                hi = __ldg(reinterpret_cast<const uint4*>(src + 16));
+            }
+        };
+        uint4 clo[kCodeAhead], chi[kCodeAhead];
+#pragma unroll
+        for (int u = 0; u < kCodeAhead; ++u) {
+            clo[u] = make_uint4(0, 0, 0, 0);
+            chi[u] = make_uint4(0, 0, 0, 0);
+            load_codes(u, clo[u], chi[u]);
+        }
+        bool alive = true;
+        for (int kb0 = 0; alive && kb0 < n_kb; kb0 += kCodeAhead) {
+#pragma unroll
+            for (int u = 0; u < kCodeAhead; ++u) {
+                const int kb = kb0 + u;
+                if (!alive || kb >= n_kb) break;
+                const int sa = kb % kAStages;
+                const int plane = kb >= kb_per_plane ? 1 : 0;
+                if (kb >= kAStages && !bar_wait(bar_empty_a + 8u * sa, ((kb / kAStages) - 1) & 1, abort_flag)) {
+                    atomicExch(p.status, 6u);
+                    atomicExch(&s_abort, 1u);
+                    alive = false;
+                    break;
+                }
+                const uint32_t a_stage = s_stage[sa];
+                // weight tile: 32 codes -> 32 fp16 -> four 16-byte stores
+                const uint32_t w[8] = {clo[u].x, clo[u].y, clo[u].z, clo[u].w, chi[u].x, chi[u].y, chi[u].z, chi[u].w};
+                load_codes(kb + kCodeAhead, clo[u], chi[u]);
+                const uint32_t lut_p = lut_lane + static_cast<uint32_t>(plane) * kLutBytes;
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {  // core column 4 * ah + c : codes 8c .. 8c+7 of this thread
+                    uint32_t packed[4];
+#pragma unroll
+                    for (int h = 0; h < 4; ++h) {
+                        const uint32_t word = w[2 * c + (h >> 1)];
+                        const int b0 = (h & 1) * 2;  // bytes b0, b0 + 1 of the word
+                        const uint32_t i0 = b0 == 0 ? (word << 7) : (word >> 9);
+                        const uint32_t i1 = b0 == 0 ? (word >> 1) : (word >> 17);
+                        uint32_t v0, v1;
+                        asm("ld.shared.b32 %0, [%1];" : "=r"(v0) : "r"(lut_p | (i0 & (255u << 7))));
+                        asm("ld.shared.b32 %0, [%1];" : "=r"(v1) : "r"(lut_p | (i1 & (255u << 7))));
+                        packed[h] = __byte_perm(v0, v1, 0x5410);
+                    }
+                    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(a_stage + a_off + static_cast<uint32_t>(c) * 128u),
+                                 "r"(packed[0]), "r"(packed[1]), "r"(packed[2]), "r"(packed[3])
+                                 : "memory");
+                }
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic-proxy writes -> visible to the tensor core
+                bar_arrive(bar_full + 8u * (kb % kFull));
+            }
+        }
+    } else if (warp == kCopyWarp) {
+        // ---- activation tiles: one 32 KB bulk copy per K block, n_b blocks ahead of the MMAs ----
+        const size_t n_tok_tiles = (static_cast<size_t>(p.m) + kTileTok - 1) / kTileTok;
         for (int kb = 0; kb < n_kb; ++kb) {
-            const int s = kb % kStages;
-            const int plane = kb >= kb_per_plane ? 1 : 0;
-            const int kcol = (kb - plane * kb_per_plane) * kBlockK;
-            if (kb >= kStages && !bar_wait(bar_empty + 8u * s, ((kb / kStages) - 1) & 1, abort_flag)) {
-                atomicExch(p.status, 6u);
-                atomicExch(&s_abort, 1u);
+            const int sb = kb % n_b;
+            if (kb >= n_b && !bar_wait(bar_empty_b + 8u * sb, ((kb / n_b) - 1) & 1, abort_flag)) {
+                if (lane == 0) {
+                    atomicExch(p.status, 6u);
+                    atomicExch(&s_abort, 1u);
+                }
                 break;
             }
-            const uint32_t a_stage = s_stage[s], b_stage = s_stage[kStages + s];
-            // activation tile: 8 x 16-byte cp.async per thread, rows past m zero-filled
-            const __half* xp = p.xrot + static_cast<size_t>(plane) * p.m * p.in + kcol;
-#pragma unroll
-            for (int i = 0; i < 8; ++i) {
-                const int combo = warp * 8 + i, rg = combo >> 1, kc = (combo & 1) * 4 + bc;
-                const int tok = tok0 + rg * 8 + br;
-                const bool ok = tok < p.m;
-                const __half* src = xp + static_cast<size_t>(ok ? tok : 0) * p.in + kc * 8;
-                const uint32_t dst = b_stage + static_cast<uint32_t>(rg) * 1024u + static_cast<uint32_t>(kc) * 128u +
-                                     static_cast<uint32_t>(br) * 16u;
-                asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(ok ? 16u : 0u) : "memory");
-            }
-            // weight tile: 32 codes -> 32 fp16 -> four 16-byte stores
-            const uint32_t w[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
-            if (kb + 1 < n_kb) {  // next block's codes (the same bytes again for the second plane)
-                const int nplane = (kb + 1) >= kb_per_plane ? 1 : 0;
-                const int ncol = (kb + 1 - nplane * kb_per_plane) * kBlockK;
-                c0 = __ldg(reinterpret_cast<const uint4*>(code_ptr + ncol));
-                c1 = __ldg(reinterpret_cast<const uint4*>(code_ptr + ncol + 16));
-            }
-            const uint32_t lut_p = lut_lane + static_cast<uint32_t>(plane) * kLutBytes;
-#pragma unroll
-            for (int c = 0; c < 4; ++c) {  // core column 4 * ah + c : codes 8c .. 8c+7 of this thread
-                uint32_t packed[4];
-#pragma unroll
-                for (int h = 0; h < 4; ++h) {
-                    const uint32_t word = w[2 * c + (h >> 1)];
-                    const int b0 = (h & 1) * 2;  // bytes b0, b0 + 1 of the word
-                    const uint32_t i0 = b0 == 0 ? (word << 7) : (word >> 9);
-                    const uint32_t i1 = b0 == 0 ? (word >> 1) : (word >> 17);
-                    uint32_t v0, v1;
-                    asm("ld.shared.b32 %0, [%1];" : "=r"(v0) : "r"(lut_p | (i0 & (255u << 7))));
-                    asm("ld.shared.b32 %0, [%1];" : "=r"(v1) : "r"(lut_p | (i1 & (255u << 7))));
-                    packed[h] = __byte_perm(v0, v1, 0x5410);
-                }
-                asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(a_stage + a_off + static_cast<uint32_t>(c) * 128u),
-                             "r"(packed[0]), "r"(packed[1]), "r"(packed[2]), "r"(packed[3])
+            if (lane == 0) {
+                const int plane = kb >= kb_per_plane ? 1 : 0;
+                const size_t tile = (static_cast<size_t>(plane) * n_tok_tiles + blockIdx.y) * kb_per_plane + (kb - plane * kb_per_plane);
+                const __half* src = p.xrot + tile * (kTileTok * kBlockK);
+                const uint32_t bar = bar_full_b + 8u * sb;
+                asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(kBBytes) : "memory");
+                asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                                 s_stage[kAStages + sb]),
+                             "l"(src), "r"(kBBytes), "r"(bar)
                              : "memory");
             }
-            asm volatile("cp.async.wait_all;" ::: "memory");
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic-proxy writes -> visible to the tensor core
-            bar_arrive(bar_full + 8u * s);
+            __syncwarp();
         }
     } else {
         // ---- MMA issuer -----------------------------------------------------------------------
         for (int kb = 0; kb < n_kb; ++kb) {
-            const int s = kb % kStages;
-            if (!bar_wait(bar_full + 8u * s, (kb / kStages) & 1, abort_flag)) {
+            if (!bar_wait(bar_full + 8u * (kb % kFull), (kb / kFull) & 1, abort_flag) ||
+                !bar_wait(bar_full_b + 8u * (kb % n_b), (kb / n_b) & 1, abort_flag)) {
                 if (lane == 0) {
                     atomicExch(p.status, 7u);
                     atomicExch(&s_abort, 1u);
@@ -312,11 +372,13 @@ __global__ void __launch_bounds__(kGemmThreads, 1) tq8_gemm_kernel(const GemmArg
             }
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             if (lane == 0) {
-                const uint32_t a_stage = s_stage[s], b_stage = s_stage[kStages + s];
+                const uint32_t a_stage = s_stage[kb % kAStages], b_stage = s_stage[kAStages + kb % n_b];
 #pragma unroll
                 for (int j = 0; j < kBlockK / 16; ++j)
                     umma_f16(tmem_d, smem_desc(a_stage + 256u * j), smem_desc(b_stage + 256u * j), (kb | j) != 0 ? 1u : 0u);
-                umma_commit(bar_empty + 8u * s);  // the stage may be refilled when these MMAs are done
+                // both ring slots may be refilled once these MMAs are done
+                umma_commit(bar_empty_a + 8u * (kb % kAStages));
+                umma_commit(bar_empty_b + 8u * (kb % n_b));
             }
             __syncwarp();
         }
@@ -350,7 +412,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) tq8_gemm_kernel(const GemmArg
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
-    if (warp == kProducerWarps) {
+    if (warp == kMmaWarp) {
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_d), "r"(kTmemCols) : "memory");
     }
@@ -359,7 +421,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1) tq8_gemm_kernel(const GemmArg
 }  // namespace
 
 size_t gemm_scratch_bytes(int in, long m, int n_planes) {
-    return static_cast<size_t>(n_planes) * static_cast<size_t>(m) * static_cast<size_t>(in) * sizeof(__half);
+    const size_t padded = (static_cast<size_t>(m) + kTileTok - 1) / kTileTok * kTileTok;  // whole operand tiles
+    return static_cast<size_t>(n_planes) * padded * static_cast<size_t>(in) * sizeof(__half);
 }
 
 bool gemm_supported(int in) { return in % kBlockK == 0; }
@@ -398,13 +461,13 @@ void launch_tq8_gemm(const uint8_t* codes, const float* norms, const float* tabl
     a.out = out; a.in = in; a.m = static_cast<int>(m); a.n_planes = n_planes;
     a.inv_scale = 1.0f / std::sqrt(static_cast<float>(in));
     // stages + tables + worst-case padding in front of the 32 KB-aligned tables
-    const size_t smem = kStages * (kABytes + kBBytes) + static_cast<size_t>(n_planes) * kLutBytes + 16384 + 1024;
+    const size_t smem = kGemmSmemBytes;
     static bool configured[64] = {false};
     int dev = 0;
     TQ_CUDA(cudaGetDevice(&dev));
     if (dev >= 64 || !configured[dev]) {
         TQ_CUDA(cudaFuncSetAttribute(tq8_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                     static_cast<int>(kStages * (kABytes + kBBytes) + 2 * kLutBytes + 16384 + 1024)));
+                                     static_cast<int>(kGemmSmemBytes)));
         if (dev < 64) configured[dev] = true;
     }
     const dim3 grid(static_cast<unsigned int>((out + kTileRows - 1) / kTileRows),
