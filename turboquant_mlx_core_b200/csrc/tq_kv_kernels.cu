@@ -361,20 +361,22 @@ __host__ __device__ __forceinline__ int attn_pair_dim(int q, int pidx) {
 }
 
 template <typename QT>
-__global__ void __launch_bounds__(kMmaThreads, 4) attn_mma_kernel(const AttnSeq* __restrict__ seqs, const QT* __restrict__ qv,
+__global__ void __launch_bounds__(kMmaThreads, 3) attn_mma_kernel(const AttnSeq* __restrict__ seqs, const QT* __restrict__ qv,
                                                                int q_heads, int kv_heads, int n_splits, uint32_t k_seed,
                                                                uint32_t qjl_seed, int use_qjl, float inv_sqrt,
                                                                float inv_scale_d, float attn_scale, float gamma,
                                                                float* __restrict__ part_acc, float* __restrict__ part_ml) {
     constexpr int D = 128, WPH = 13, QPH = 4;
-    // The tables sit at shared-window addresses that are multiples of their size, so that
+    // The pair table sits at a shared-window address that is a multiple of its size, so that
     // "table base + lane offset" and the scaled index occupy disjoint bits and one logic op
     // forms a lookup address.  The window offset of a static array is not under the program's
-    // control, so the aligned addresses are chosen at run time inside a buffer of twice the size.
+    // control, so the aligned address is chosen at run time inside a buffer of twice the size.
     __shared__ __align__(16) uint32_t s_tab[2 * 64 * 32];
-    __shared__ float s_q[8][D];            // rotated queries of this KV head's group
+    // rotated queries of this KV head's group, [head][32-dim word][dim in word], padded so that the
+    // fragment set-up below reads without bank conflicts (bank = 4 g + word + dim)
+    __shared__ float s_q[8][4][33];
     __shared__ float s_m[4][8], s_l[4][8];
-    __shared__ float s_acc[4][8][D];
+    __shared__ float s_acc[4][8][D + 4];   // row stride 132: the publishing stores below hit 32 distinct banks
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int g = lane >> 2, q = lane & 3;
@@ -385,16 +387,10 @@ __global__ void __launch_bounds__(kMmaThreads, 4) attn_mma_kernel(const AttnSeq*
 
     const uint32_t tab_addr = static_cast<uint32_t>(__cvta_generic_to_shared(s_tab));
     const uint32_t lut_addr = (tab_addr + 8191u) & ~8191u;           // pair table, [pair index][lane]
-    const uint32_t sgn_addr = (lut_addr - tab_addr <= 8192u - 512u) ? lut_addr + 8192u : lut_addr - 512u;
     uint32_t* const s_lut = s_tab + ((lut_addr - tab_addr) >> 2);
-    uint32_t* const s_sgn = s_tab + ((sgn_addr - tab_addr) >> 2);    // two sign bits -> (+-1, +-1), [index][lane]
     for (int i = tid; i < 64 * 32; i += kMmaThreads) {
         const int idx = i >> 5;
         s_lut[i] = pack_half2(kCentroidScale * kC3[idx & 7], kCentroidScale * kC3[idx >> 3]);
-    }
-    for (int i = tid; i < 4 * 32; i += kMmaThreads) {
-        const int idx = i >> 5;
-        s_sgn[i] = pack_half2((idx & 1) ? 1.f : -1.f, (idx & 2) ? 1.f : -1.f);
     }
     // rotated queries: fp16-round, sign, butterfly, 1/sqrt(d)  (one warp per head)
     for (int h = warp; h < 8; h += 4) {
@@ -410,26 +406,24 @@ __global__ void __launch_bounds__(kMmaThreads, 4) attn_mma_kernel(const AttnSeq*
         }
         warp_fwht<4>(v, lane);
 #pragma unroll
-        for (int j = 0; j < 4; ++j) s_q[h][lane * 4 + j] = v[j] * inv_sqrt;
+        for (int j = 0; j < 4; ++j) s_q[h][lane >> 3][(lane & 7) * 4 + j] = v[j] * inv_sqrt;
     }
     __syncthreads();
 
-    // B fragments (head n = g): centroid product uses this thread's pair dims, the sign product
-    // uses dims 32 q + 2 p (sign word q of the token), with the key-side sign folded in.
-    // The rotated query is split into an fp16 head and an fp16 tail (two MMAs per step) so
-    // that its rounding does not limit the score accuracy.
-    uint32_t bq[16], bql[16], bs[16];
+    // B fragments (head n = g): the centroid product uses this thread's pair dims; the sign
+    // product pairs bits p and p + 16 of sign word q (dims 32 q + p, 32 q + p + 16), with the
+    // key-side sign folded in.
+    uint32_t bq[16], bs[16];
 #pragma unroll
     for (int pidx = 0; pidx < 16; ++pidx) {
         const int d = attn_pair_dim(q, pidx);
-        const float x0 = s_q[g][d], x1 = s_q[g][d + 1];
+        const float x0 = s_q[g][d >> 5][d & 31], x1 = s_q[g][(d + 1) >> 5][(d + 1) & 31];
         const float h0 = __half2float(__float2half_rn(x0)), h1 = __half2float(__float2half_rn(x1));
         bq[pidx] = pack_half2(h0, h1);
-        bql[pidx] = pack_half2(x0 - h0, x1 - h1);
-        const int e = 32 * q + 2 * pidx;
+        const int e = 32 * q + pidx;
         const float s0 = qjl_sign_is_positive(qjl_seed, static_cast<uint32_t>(e)) ? 1.f : -1.f;
-        const float s1 = qjl_sign_is_positive(qjl_seed, static_cast<uint32_t>(e + 1)) ? 1.f : -1.f;
-        bs[pidx] = pack_half2(s_q[g][e] * s0, s_q[g][e + 1] * s1);
+        const float s1 = qjl_sign_is_positive(qjl_seed, static_cast<uint32_t>(e + 16)) ? 1.f : -1.f;
+        bs[pidx] = pack_half2(s_q[g][q][pidx] * s0, s_q[g][q][pidx + 16] * s1);
     }
 
     const AttnSeq S = seqs[seq];
@@ -438,7 +432,6 @@ __global__ void __launch_bounds__(kMmaThreads, 4) attn_mma_kernel(const AttnSeq*
     const int t1 = S.start + static_cast<int>(static_cast<long>(n_tok) * (split + 1) / n_splits);
 
     const uint32_t lut_base = lut_addr + static_cast<uint32_t>(lane) * 4u;
-    const uint32_t sgn_base = sgn_addr + static_cast<uint32_t>(lane) * 4u;
     auto lut_pair = [&](uint32_t word, int bit) -> uint32_t {
         // ((word >> bit) & 63) * 128 + lane * 4
         const uint32_t sh = bit >= 7 ? (word >> (bit - 7)) : (word << (7 - bit));
@@ -446,15 +439,21 @@ __global__ void __launch_bounds__(kMmaThreads, 4) attn_mma_kernel(const AttnSeq*
         asm("ld.shared.b32 %0, [%1];" : "=r"(v) : "r"(lut_base | (sh & (63u << 7))));
         return v;
     };
-    auto sgn_pair = [&](uint32_t word, int bit) -> uint32_t {
-        const uint32_t sh = bit >= 7 ? (word >> (bit - 7)) : (word << (7 - bit));
-        uint32_t v;
-        asm("ld.shared.b32 %0, [%1];" : "=r"(v) : "r"(sgn_base | (sh & (3u << 7))));
-        return v;
+    // Sign bits p and p + 16 of an INVERTED sign word -> fp16 pair (+-1, +-1) without a table:
+    // a set bit of the inverted word becomes the fp16 sign bit of 1.0.
+    auto sgn_pair = [&](uint32_t inv_word, int pp) -> uint32_t {
+        const uint32_t sh = pp == 15 ? inv_word : (inv_word << (15 - pp));
+        return (sh & 0x80008000u) | 0x3C003C00u;
     };
-    // the 16 pair fragments of one token's codes for this thread
-    auto dequant16 = [&](const uint32_t* rec, uint32_t (&out)[16]) {
-        const uint32_t w0 = __ldg(rec + q), w1 = __ldg(rec + q + 4), w2 = __ldg(rec + q + 8), w3 = __ldg(rec + 12);
+    // this thread's four code words of one token record, and the 16 pair fragments they hold
+    auto load_words = [&](const uint32_t* rec, uint32_t (&w)[4]) {
+        w[0] = __ldg(rec + q);
+        w[1] = __ldg(rec + q + 4);
+        w[2] = __ldg(rec + q + 8);
+        w[3] = __ldg(rec + 12);
+    };
+    auto dequant16 = [&](const uint32_t (&w)[4], uint32_t (&out)[16]) {
+        const uint32_t w0 = w[0], w1 = w[1], w2 = w[2], w3 = w[3];
 #pragma unroll
         for (int j = 0; j < 5; ++j) {
             out[j] = lut_pair(w0, 6 * j);
@@ -471,12 +470,32 @@ __global__ void __launch_bounds__(kMmaThreads, 4) attn_mma_kernel(const AttnSeq*
 #pragma unroll
         for (int k = 0; k < 4; ++k) acc[mt][k] = 0.f;
 
+    // Software pipeline over 16-token tiles: a tile's key words are fetched while the tile
+    // before it is in its value phase; its value words, sign words and norms are fetched at the
+    // top of the tile, a whole key phase ahead of their use.
+    // record index of this thread's two tokens of the tile starting at tb (clamped so loads stay
+    // in range; tokens past the end are masked out of the scores)
+    auto rec_of = [&](int tok) { return static_cast<size_t>(tok < t1 ? tok : t1 - 1) * kv_heads + kvh; };
+    uint32_t kwa[4] = {0, 0, 0, 0}, kwb[4] = {0, 0, 0, 0};
+    if (t0 + warp * 16 < t1) {
+        load_words(S.k_words + rec_of(t0 + warp * 16 + g) * WPH, kwa);
+        load_words(S.k_words + rec_of(t0 + warp * 16 + g + 8) * WPH, kwb);
+    }
     for (int tb = t0 + warp * 16; tb < t1; tb += 64) {
-        // tokens of this thread's two rows (clamped so loads stay in range; masked below)
         const int ta = tb + g, tbb = tb + g + 8;
         const bool va = ta < t1, vb = tbb < t1;
-        const size_t ra = static_cast<size_t>(va ? ta : t1 - 1) * kv_heads + kvh;
-        const size_t rb = static_cast<size_t>(vb ? tbb : t1 - 1) * kv_heads + kvh;
+        const size_t ra = rec_of(ta), rb = rec_of(tbb);
+        uint32_t vwa[4], vwb[4];
+        load_words(S.v_words + ra * WPH, vwa);
+        load_words(S.v_words + rb * WPH, vwb);
+        uint32_t wa = 0, wb = 0;
+        float qa = 0.f, qb = 0.f;
+        if (use_qjl) {
+            wa = __ldg(S.qjl_words + ra * QPH + q);
+            wb = __ldg(S.qjl_words + rb * QPH + q);
+            qa = __ldg(S.qjl_norms + ra);
+            qb = __ldg(S.qjl_norms + rb);
+        }
         const float kscale = inv_scale_d * attn_scale / kCentroidScale;
         const float kna = __ldg(S.k_norms + ra) * kscale, knb = __ldg(S.k_norms + rb) * kscale;
         const float vna = __ldg(S.v_norms + ra) * (1.0f / kCentroidScale), vnb = __ldg(S.v_norms + rb) * (1.0f / kCentroidScale);
@@ -485,22 +504,27 @@ __global__ void __launch_bounds__(kMmaThreads, 4) attn_mma_kernel(const AttnSeq*
         float c1[4] = {0.f, 0.f, 0.f, 0.f};
         {
             uint32_t ka[16], kb[16];
-            dequant16(S.k_words + ra * WPH, ka);
-            dequant16(S.k_words + rb * WPH, kb);
+            dequant16(kwa, ka);
+            dequant16(kwb, kb);
+            if (tb + 64 < t1) {  // the next tile's key words
+                load_words(S.k_words + rec_of(tb + 64 + g) * WPH, kwa);
+                load_words(S.k_words + rec_of(tb + 64 + g + 8) * WPH, kwb);
+            }
 #pragma unroll
             for (int ks = 0; ks < 8; ++ks) {
                 mma_f16(c1, ka[2 * ks], kb[2 * ks], ka[2 * ks + 1], kb[2 * ks + 1], bq[2 * ks], bq[2 * ks + 1]);
-                mma_f16(c1, ka[2 * ks], kb[2 * ks], ka[2 * ks + 1], kb[2 * ks + 1], bql[2 * ks], bql[2 * ks + 1]);
             }
         }
         if (use_qjl) {
             float c2[4] = {0.f, 0.f, 0.f, 0.f};
-            const uint32_t wa = __ldg(S.qjl_words + ra * QPH + q), wb = __ldg(S.qjl_words + rb * QPH + q);
+            wa = ~wa;
+            wb = ~wb;
+            qa *= gamma * kCentroidScale;
+            qb *= gamma * kCentroidScale;
 #pragma unroll
             for (int ks = 0; ks < 8; ++ks)
-                mma_f16(c2, sgn_pair(wa, 4 * ks), sgn_pair(wb, 4 * ks), sgn_pair(wa, 4 * ks + 2), sgn_pair(wb, 4 * ks + 2),
+                mma_f16(c2, sgn_pair(wa, 2 * ks), sgn_pair(wb, 2 * ks), sgn_pair(wa, 2 * ks + 1), sgn_pair(wb, 2 * ks + 1),
                         bs[2 * ks], bs[2 * ks + 1]);
-            const float qa = __ldg(S.qjl_norms + ra) * (gamma * kCentroidScale), qb = __ldg(S.qjl_norms + rb) * (gamma * kCentroidScale);
             c1[0] = fmaf(qa, c2[0], c1[0]);
             c1[1] = fmaf(qa, c2[1], c1[1]);
             c1[2] = fmaf(qb, c2[2], c1[2]);
@@ -520,14 +544,9 @@ __global__ void __launch_bounds__(kMmaThreads, 4) attn_mma_kernel(const AttnSeq*
         const float mn0 = fmaxf(m_run[0], mx0), mn1 = fmaxf(m_run[1], mx1);
         const float cr0 = __expf(m_run[0] - mn0), cr1 = __expf(m_run[1] - mn1);
         const float p00 = __expf(s00 - mn0), p01 = __expf(s01 - mn1), p10 = __expf(s10 - mn0), p11 = __expf(s11 - mn1);
-        float sum0 = p00 + p10, sum1 = p01 + p11;
-#pragma unroll
-        for (int o = 4; o < 32; o <<= 1) {
-            sum0 += __shfl_xor_sync(0xffffffffu, sum0, o);
-            sum1 += __shfl_xor_sync(0xffffffffu, sum1, o);
-        }
-        l_run[0] = fmaf(l_run[0], cr0, sum0);
-        l_run[1] = fmaf(l_run[1], cr1, sum1);
+        // this lane's share of the running sums (its two tokens); lanes are added up after the loop
+        l_run[0] = fmaf(l_run[0], cr0, p00 + p10);
+        l_run[1] = fmaf(l_run[1], cr1, p01 + p11);
         m_run[0] = mn0;
         m_run[1] = mn1;
         // once the running maxima have settled the correction is exactly 1: skip the rescale then
@@ -547,8 +566,8 @@ __global__ void __launch_bounds__(kMmaThreads, 4) attn_mma_kernel(const AttnSeq*
         // ---- values ----
         {
             uint32_t xa[16], xb[16];
-            dequant16(S.v_words + ra * WPH, xa);
-            dequant16(S.v_words + rb * WPH, xb);
+            dequant16(vwa, xa);
+            dequant16(vwb, xb);
 #pragma unroll
             for (int ks = 0; ks < 8; ++ks) {
                 // V[token x dim] fragment of dim block ks -> V^T[dim x token] fragment
@@ -563,6 +582,11 @@ __global__ void __launch_bounds__(kMmaThreads, 4) attn_mma_kernel(const AttnSeq*
 
     // ---- publish this warp's state in natural dim order, merge the 4 warps, write the partial ----
     // acc[mt]: (slot g: heads 2q, 2q+1), (slot g+8: heads 2q, 2q+1); slot -> dim through the pair map
+#pragma unroll
+    for (int o = 4; o < 32; o <<= 1) {
+        l_run[0] += __shfl_xor_sync(0xffffffffu, l_run[0], o);
+        l_run[1] += __shfl_xor_sync(0xffffffffu, l_run[1], o);
+    }
     if (g == 0) {
         s_m[warp][2 * q] = m_run[0];
         s_m[warp][2 * q + 1] = m_run[1];
