@@ -224,7 +224,9 @@ private:
     // shape allows); otherwise batches above 8 rows are issued as passes of 8 through the GEMV.
     static constexpr int kGemmMinBatch = 32;
     void launch_forward(const __half* d_x, int batch, __half* d_y, cudaStream_t st) {
-        if (batch > kGemmMinBatch && tq::gemm_supported(in_)) {
+        // (a tall matrix fills every SM with row tiles, so the GEMM already pays off at 17 rows)
+        const bool tall = (out_ + 127) / 128 >= 2 * sm_count_;
+        if ((batch > kGemmMinBatch || (tall && batch > 16)) && tq::gemm_supported(in_)) {
             const int planes = dual_ ? 2 : 1;
             gemm_scratch_.reserve(tq::gemm_scratch_bytes(in_, batch, planes));
             tq::launch_tq8_gemm(codes_.as<uint8_t>(), norms_.as<float>(), tables_.as<float>(), d_x, d_y, out_, in_, batch,

@@ -314,11 +314,27 @@ __global__ void __launch_bounds__(kCtaThreads, 1) tq8_gemv_kernel(const GemvArgs
             sts_v4(kLutAddr + static_cast<uint32_t>(e) * 256u + static_cast<uint32_t>(copy4) * 4u, v, v, v, v);
         }
     };
+    // Prologue order: table entries are fetched into registers (they do not depend on the
+    // preceding kernel), then comes the dependency wait, then this warp's activation slice of
+    // the first unit is requested, and only then are the table entries written to shared
+    // memory - so the activation's latency hides behind the table build.
     int staged_plane = cur.slot / p.n_chunks;
-    build_table(staged_plane);
+    float tab_first[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) tab_first[k] = __ldg(p.table + staged_plane * 256 + (tid >> 3) + 64 * k);
 
     // Everything below reads or writes data the preceding kernels produce or still use.
     grid_dependency_sync();
+    uint4 x_first = make_uint4(0, 0, 0, 0);
+    if (p.x != nullptr) {
+        const int cl0 = (cur.slot - staged_plane * p.n_chunks) * kChunk + slice0 + 8 * lane;
+        if (cl0 < p.in) x_first = __ldg(reinterpret_cast<const uint4*>(p.x + cl0));
+    }
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        const float v = to_tf32(tab_first[k]);
+        sts_v4(kLutAddr + static_cast<uint32_t>((tid >> 3) + 64 * k) * 256u + static_cast<uint32_t>((tid & 7) * 4) * 4u, v, v, v, v);
+    }
     __syncthreads();  // table and barriers visible
 
     // ---- sum of one unit's per-warp partial tiles ----
@@ -409,9 +425,11 @@ __global__ void __launch_bounds__(kCtaThreads, 1) tq8_gemv_kernel(const GemvArgs
     uint32_t rpar = 0;      // parity of its "written" phase = ((i - kLag) / kRing) & 1
     Pos red = cur;          // position of the unit being summed
 
-    for (int i = 0; i < n_local; ++i) {
-        const int plane = cur.slot / p.n_chunks;
-        if (cur.slot != staged_slot) {
+    // Makes `slot` the current one: switches the table when the plane changes and rebuilds this
+    // warp's B fragments.  x0 is this lane's first-row activation when the caller has already
+    // requested it (have_x0).
+    auto stage_slot = [&](int slot, const uint4& x0, bool have_x0) {
+        const int plane = slot / p.n_chunks;
             if (plane != staged_plane) {
                 named_barrier_sync(1, kConsumerThreads);  // nobody still reads the previous table
                 build_table(plane);
@@ -419,7 +437,7 @@ __global__ void __launch_bounds__(kCtaThreads, 1) tq8_gemv_kernel(const GemvArgs
                 staged_plane = plane;
             }
             // B fragment of MMA (s, m): k = q -> column 64 s + 16 q + 2 m, k = q+4 -> the next column; n = g.
-            const int colw = (cur.slot - plane * p.n_chunks) * kChunk + slice0;  // first column of this warp's slice
+            const int colw = (slot - plane * p.n_chunks) * kChunk + slice0;  // first column of this warp's slice
             const int col0 = colw + 16 * q;
             if (p.x != nullptr) {
                 // Rotate this warp's 256 activation columns here: lane l holds columns 8l..8l+7 of
@@ -439,7 +457,8 @@ __global__ void __launch_bounds__(kCtaThreads, 1) tq8_gemv_kernel(const GemvArgs
 #pragma unroll
                     for (int k = 0; k < 16; ++k) bfrag[s][k] = 0u;
                 const int lane_steps = p.block >> 3;  // lanes per WHT block
-                uint4 xn = c_ok ? __ldg(reinterpret_cast<const uint4*>(p.x + cl)) : make_uint4(0, 0, 0, 0);
+                uint4 xn = x0;
+                if (!have_x0 && c_ok) xn = __ldg(reinterpret_cast<const uint4*>(p.x + cl));
                 for (int n = 0; n < p.batch; ++n) {
                     const uint4 xc = xn;
                     if (n + 1 < p.batch && c_ok)
@@ -503,8 +522,14 @@ __global__ void __launch_bounds__(kCtaThreads, 1) tq8_gemv_kernel(const GemvArgs
                 }
             }
             }
-            staged_slot = cur.slot;
-        }
+        staged_slot = slot;
+    };
+    stage_slot(cur.slot, x_first, p.x != nullptr);
+
+    for (int i = 0; i < n_local; ++i) {
+        const int plane = cur.slot / p.n_chunks;
+        (void)plane;
+        if (cur.slot != staged_slot) stage_slot(cur.slot, make_uint4(0, 0, 0, 0), false);
         const bool has_next = i + 1 < n_local;
 
         float acc0[4] = {0.f, 0.f, 0.f, 0.f}, acc1[4] = {0.f, 0.f, 0.f, 0.f};
