@@ -45,21 +45,22 @@ namespace {
 constexpr int kTileRows = 128;  // weight rows per CTA (MMA M)
 constexpr int kTileTok = 256;   // activation rows per CTA (MMA N)
 constexpr int kBlockK = 64;     // K columns per stage
-constexpr int kAStages = 3;    // weight-tile ring (filled just in time by the lookups)
-constexpr int kBStagesMax = 4; // activation-tile ring (cp.async two K blocks ahead); 3 with two table planes
+constexpr int kAStages = 4;    // weight-tile ring in tensor memory (filled just in time by the lookups)
+constexpr int kBStagesMax = 4; // activation-tile ring in shared memory (bulk copies run this far ahead)
 constexpr int kFull = 4;       // "K block ready" barriers
 constexpr int kProducerWarps = 8;
 constexpr int kProducerThreads = kProducerWarps * 32;
 constexpr int kMmaWarp = kProducerWarps;       // issues the MMAs, owns the tensor-memory allocation
 constexpr int kCopyWarp = kProducerWarps + 1;  // issues the activation-tile bulk copies
 constexpr int kGemmThreads = kProducerThreads + 64;
-constexpr uint32_t kABytes = kTileRows * kBlockK * 2;  // 16 KB
 constexpr uint32_t kBBytes = kTileTok * kBlockK * 2;   // 32 KB
 constexpr uint32_t kLutBytes = 256 * 32 * 4;           // one plane: 256 entries x 32 lane copies x (fp16, fp16)
-constexpr uint32_t kTmemCols = 256;
+constexpr uint32_t kTmemCols = 512;   // accumulator: columns 0..255; weight tiles: 32 columns each from 256 on
+constexpr uint32_t kTmemAColumn = 256;
+constexpr uint32_t kTmemAStageCols = kBlockK / 2;  // two fp16 per 32-bit column
 // rings + tables (4 activation stages with one table plane, 3 with two) + worst-case padding in
 // front of the 32 KB-aligned tables
-constexpr size_t kGemmSmemBytes = kAStages * kABytes + kBStagesMax * kBBytes + kLutBytes + 16384 + 1024;
+constexpr size_t kGemmSmemBytes = kBStagesMax * kBBytes + 2 * kLutBytes + 32768 + 1024;
 constexpr unsigned long long kGemmWaitLimitNs = 200ull * 1000 * 1000;
 
 // instruction descriptor: D fp32, A and B fp16, both K-major, N = 256, M = 128
@@ -101,13 +102,26 @@ __device__ __forceinline__ uint64_t smem_desc(uint32_t addr) {
            (static_cast<uint64_t>(1024u >> 4) << 32) | (1ull << 46);
 }
 
-__device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t accumulate) {
+// D[tmem_d] (+)= A[tmem_a] . B[desc_b]^T : A from tensor memory (128 lanes x 8 columns of fp16 pairs),
+// B from shared memory.
+__device__ __forceinline__ void umma_f16_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t desc_b, uint32_t accumulate) {
     asm volatile(
         "{ .reg .pred p; setp.ne.b32 p, %4, 0;\n"
-        "  tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5}, p; }"
+        "  tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, {%5, %5, %5, %5}, p; }"
         :
-        : "r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(kInstrDesc), "r"(accumulate), "r"(0u)
+        : "r"(tmem_d), "r"(tmem_a), "l"(desc_b), "r"(kInstrDesc), "r"(accumulate), "r"(0u)
         : "memory");
+}
+// 16 consecutive 32-bit columns of this thread's tensor-memory lane.
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&v)[16]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
+        :
+        : "r"(taddr), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]), "r"(v[8]),
+          "r"(v[9]), "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15])
+        : "memory");
+    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
 }
 // Arrives on the barrier once every MMA issued so far by this thread has finished.
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
@@ -187,7 +201,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) tq8_gemm_kernel(const GemmArg
     extern __shared__ __align__(128) uint8_t gemm_smem[];
     __shared__ __align__(8) unsigned long long s_full[kFull], s_full_b[kBStagesMax], s_empty_a[kAStages], s_empty_b[kBStagesMax], s_accum;
     __shared__ uint32_t s_tmem_base;
-    __shared__ uint32_t s_stage[kAStages + kBStagesMax];  // A buffers, then B buffers
+    __shared__ uint32_t s_stage[kBStagesMax];  // activation-tile buffers
     __shared__ unsigned int s_abort;
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -198,7 +212,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) tq8_gemm_kernel(const GemmArg
     // The lookup tables sit at a 32 KB-aligned window address (so that table base, lane offset
     // and scaled code occupy disjoint address bits); the 16 KB / 32 KB stage buffers are packed
     // around them.
-    const int n_b = p.n_planes == 2 ? 3 : kBStagesMax;  // activation stages that fit beside the tables
+    const int n_b = kBStagesMax;
     const uint32_t raw = smem_addr(gemm_smem);
     const uint32_t base = (raw + 127u) & ~127u;
     const uint32_t lut_addr = (base + 32767u) & ~32767u;
@@ -208,13 +222,12 @@ __global__ void __launch_bounds__(kGemmThreads, 1) tq8_gemm_kernel(const GemmArg
     {
         // Same arithmetic in every thread; thread 0 publishes the stage addresses.
         uint32_t lo = base, hi = lut_end;  // bump pointers below and above the tables
-        uint32_t addr[kAStages + kBStagesMax];
+        uint32_t addr[kBStagesMax];
 #pragma unroll
-        for (int s = 0; s < kAStages + kBStagesMax; ++s) {
-            const uint32_t bytes = s < kAStages ? kABytes : kBBytes;
-            if (s >= kAStages + n_b) { addr[s] = 0; continue; }
-            if (lo + bytes <= lut_addr) { addr[s] = lo; lo += bytes; }
-            else { addr[s] = hi; hi += bytes; }
+        for (int s = 0; s < kBStagesMax; ++s) {
+            if (s >= n_b) { addr[s] = 0; continue; }
+            if (lo + kBBytes <= lut_addr) { addr[s] = lo; lo += kBBytes; }
+            else { addr[s] = hi; hi += kBBytes; }
         }
         if (hi > raw + dyn_bytes || lut_end > raw + dyn_bytes) {  // layout does not fit: refuse to run (nothing allocated yet)
             if (tid == 0) atomicExch(p.status, 9u);
@@ -222,7 +235,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) tq8_gemm_kernel(const GemmArg
         }
         if (tid == 0) {
 #pragma unroll
-            for (int s = 0; s < kAStages + kBStagesMax; ++s) s_stage[s] = addr[s];
+            for (int s = 0; s < kBStagesMax; ++s) s_stage[s] = addr[s];
         }
     }
     const uint32_t bar_full = smem_addr(&s_full[0]), bar_full_b = smem_addr(&s_full_b[0]),
@@ -265,14 +278,14 @@ __global__ void __launch_bounds__(kGemmThreads, 1) tq8_gemm_kernel(const GemmArg
 
     if (warp < kProducerWarps) {
         // ---- producers ------------------------------------------------------------------------
-        // A tile: warp w owns rows 16w .. 16w+15; lane -> (row & 7) + 8 * half + 16 * (row >> 3 & 1),
-        // so that the 8 lanes of a store phase write one 128-byte core-matrix column.
-        const int ar = 16 * warp + (lane & 7) + 8 * (lane >> 4);  // row inside the tile
-        const int ah = (lane >> 3) & 1;                           // which 32 columns of the K block
-        const int grow = min(row0 + ar, p.out - 1);               // rows past the matrix repeat the last row (never stored)
+        // Weight tile in tensor memory: lane = row of the tile, 32 columns per K block (two fp16 per
+        // column).  A warp may touch lanes 32 * (warp % 4) .. + 31: warp w owns those rows and the
+        // column half w / 4 (K 0..31 or 32..63 of the block); a thread dequantises 32 codes of its row.
+        const int ar = 32 * (warp & 3) + lane;       // row inside the tile
+        const int ah = warp >> 2;                    // which 32 columns of the K block
+        const int grow = min(row0 + ar, p.out - 1);  // rows past the matrix repeat the last row (never stored)
         const uint8_t* code_ptr = p.codes + static_cast<size_t>(grow) * p.in + 32 * ah;
-        const uint32_t a_off = static_cast<uint32_t>(ar >> 3) * 1024u + static_cast<uint32_t>(ar & 7) * 16u +
-                               static_cast<uint32_t>(4 * ah) * 128u;
+        const uint32_t a_taddr = tmem_d + (static_cast<uint32_t>(32 * (warp & 3)) << 16) + kTmemAColumn + 16u * ah;
         const uint32_t lut_lane = lut_addr + static_cast<uint32_t>(lane) * 4u;
 
         // Codes are fetched kCodeAhead K blocks ahead into a register ring (a K block is consumed
@@ -307,30 +320,24 @@ __global__ void __launch_bounds__(kGemmThreads, 1) tq8_gemm_kernel(const GemmArg
                     alive = false;
                     break;
                 }
-                const uint32_t a_stage = s_stage[sa];
-                // weight tile: 32 codes -> 32 fp16 -> four 16-byte stores
+                // weight tile: 32 codes -> 32 fp16 -> 16 tensor-memory columns of this thread's lane
                 const uint32_t w[8] = {clo[u].x, clo[u].y, clo[u].z, clo[u].w, chi[u].x, chi[u].y, chi[u].z, chi[u].w};
                 load_codes(kb + kCodeAhead, clo[u], chi[u]);
                 const uint32_t lut_p = lut_lane + static_cast<uint32_t>(plane) * kLutBytes;
+                uint32_t packed[16];
 #pragma unroll
-                for (int c = 0; c < 4; ++c) {  // core column 4 * ah + c : codes 8c .. 8c+7 of this thread
-                    uint32_t packed[4];
-#pragma unroll
-                    for (int h = 0; h < 4; ++h) {
-                        const uint32_t word = w[2 * c + (h >> 1)];
-                        const int b0 = (h & 1) * 2;  // bytes b0, b0 + 1 of the word
-                        const uint32_t i0 = b0 == 0 ? (word << 7) : (word >> 9);
-                        const uint32_t i1 = b0 == 0 ? (word >> 1) : (word >> 17);
-                        uint32_t v0, v1;
-                        asm("ld.shared.b32 %0, [%1];" : "=r"(v0) : "r"(lut_p | (i0 & (255u << 7))));
-                        asm("ld.shared.b32 %0, [%1];" : "=r"(v1) : "r"(lut_p | (i1 & (255u << 7))));
-                        packed[h] = __byte_perm(v0, v1, 0x5410);
-                    }
-                    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(a_stage + a_off + static_cast<uint32_t>(c) * 128u),
-                                 "r"(packed[0]), "r"(packed[1]), "r"(packed[2]), "r"(packed[3])
-                                 : "memory");
+                for (int h = 0; h < 16; ++h) {  // codes 2h, 2h + 1 -> column h
+                    const uint32_t word = w[h >> 1];
+                    const int b0 = (h & 1) * 2;  // bytes b0, b0 + 1 of the word
+                    const uint32_t i0 = b0 == 0 ? (word << 7) : (word >> 9);
+                    const uint32_t i1 = b0 == 0 ? (word >> 1) : (word >> 17);
+                    uint32_t v0, v1;
+                    asm("ld.shared.b32 %0, [%1];" : "=r"(v0) : "r"(lut_p | (i0 & (255u << 7))));
+                    asm("ld.shared.b32 %0, [%1];" : "=r"(v1) : "r"(lut_p | (i1 & (255u << 7))));
+                    packed[h] = __byte_perm(v0, v1, 0x5410);
                 }
-                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic-proxy writes -> visible to the tensor core
+                tmem_st16(a_taddr + kTmemAStageCols * static_cast<uint32_t>(sa), packed);
+                asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
                 bar_arrive(bar_full + 8u * (kb % kFull));
             }
         }
@@ -353,7 +360,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) tq8_gemm_kernel(const GemmArg
                 const uint32_t bar = bar_full_b + 8u * sb;
                 asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(kBBytes) : "memory");
                 asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
-                                 s_stage[kAStages + sb]),
+                                 s_stage[sb]),
                              "l"(src), "r"(kBBytes), "r"(bar)
                              : "memory");
             }
@@ -372,10 +379,11 @@ __global__ void __launch_bounds__(kGemmThreads, 1) tq8_gemm_kernel(const GemmArg
             }
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             if (lane == 0) {
-                const uint32_t a_stage = s_stage[kb % kAStages], b_stage = s_stage[kAStages + kb % n_b];
+                const uint32_t a_tmem = tmem_d + kTmemAColumn + kTmemAStageCols * static_cast<uint32_t>(kb % kAStages);
+                const uint32_t b_stage = s_stage[kb % n_b];
 #pragma unroll
                 for (int j = 0; j < kBlockK / 16; ++j)
-                    umma_f16(tmem_d, smem_desc(a_stage + 256u * j), smem_desc(b_stage + 256u * j), (kb | j) != 0 ? 1u : 0u);
+                    umma_f16_ts(tmem_d, a_tmem + 8u * j, smem_desc(b_stage + 256u * j), (kb | j) != 0 ? 1u : 0u);
                 // both ring slots may be refilled once these MMAs are done
                 umma_commit(bar_empty_a + 8u * (kb % kAStages));
                 umma_commit(bar_empty_b + 8u * (kb % n_b));
