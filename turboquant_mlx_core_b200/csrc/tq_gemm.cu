@@ -121,7 +121,11 @@ __device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&v)[16
         : "r"(taddr), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]), "r"(v[8]),
           "r"(v[9]), "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15])
         : "memory");
+}
+// Waits for this thread's tensor-memory stores and orders them before the barrier arrival that follows.
+__device__ __forceinline__ void tmem_st_publish() {
     asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
 }
 // Arrives on the barrier once every MMA issued so far by this thread has finished.
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
@@ -336,10 +340,18 @@ __global__ void __launch_bounds__(kGemmThreads, 1) tq8_gemm_kernel(const GemmArg
                     asm("ld.shared.b32 %0, [%1];" : "=r"(v1) : "r"(lut_p | (i1 & (255u << 7))));
                     packed[h] = __byte_perm(v0, v1, 0x5410);
                 }
+                // The previous K block's stores have had a whole block of lookups to land: publish
+                // them now, then queue this block's stores (published one iteration later).
+                if (kb > 0) {
+                    tmem_st_publish();
+                    bar_arrive(bar_full + 8u * ((kb - 1) % kFull));
+                }
                 tmem_st16(a_taddr + kTmemAStageCols * static_cast<uint32_t>(sa), packed);
-                asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-                bar_arrive(bar_full + 8u * (kb % kFull));
             }
+        }
+        if (alive && n_kb > 0) {
+            tmem_st_publish();
+            bar_arrive(bar_full + 8u * ((n_kb - 1) % kFull));
         }
     } else if (warp == kCopyWarp) {
         // ---- activation tiles: one 32 KB bulk copy per K block, n_b blocks ahead of the MMAs ----
