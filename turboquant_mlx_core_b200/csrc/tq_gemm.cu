@@ -13,10 +13,11 @@
 // seed).
 //
 // One CTA computes a 128 (weight rows) x 256 (activation rows) tile of y^T:
-//   D[128 x 256] (TMEM, fp32) += A[128 x 64] (weights, fp16, smem) . B[256 x 64]^T (xrot, fp16, smem)
+//   D[128 x 256] (TMEM, fp32) += A[128 x 64] (weights, fp16, TMEM) . B[256 x 64]^T (xrot, fp16, smem)
 // per 64-column K block, as four tcgen05.mma (M 128, N 256, K 16) issued by one thread.
 //   warps 0-7  producers: codes HBM -> registers (four K blocks ahead) -> lookup (lane-private
-//              fp16 table in shared memory) -> weight tile in shared memory, ring of 3
+//              fp16 table in shared memory) -> weight tile in TENSOR memory (tcgen05.st; lane = row,
+//              32 columns of fp16 pairs per K block), ring of 4, published one K block late
 //   warp 9     activation tiles: the rotation kernel stores xrot in operand-tile order, so a tile
 //              is one contiguous 32 KB bulk copy (cp.async.bulk, mbarrier complete_tx), ring of 4
 //   warp 8     waits for both tiles of a K block, issues the MMAs, commits to the rings' empty barriers
@@ -25,7 +26,7 @@
 // rows.  Roofline: tensor pipe (2 * M * out * in flops), with the table lookups (one shared-memory
 // load per weight per 256 activation rows) as the competing pipe.
 //
-// Shared-memory operand layout (both operands K-major, no swizzle): 8 x 8 fp16 core matrices of
+// Shared-memory layout of the activation operand (K-major, no swizzle): 8 x 8 fp16 core matrices of
 // 128 contiguous bytes (8 rows of 16 bytes); core matrices adjacent in K are 128 bytes apart
 // (leading byte offset), 8-row groups are 1024 bytes apart (stride byte offset).
 //
