@@ -311,9 +311,17 @@ def run_cuda(args):
         line["cpu_baseline"] = cpu_baseline(qw0, cbs, x_host[0].numpy(), y_dev[0].cpu().numpy(), budget_s=12.0)
     if not args.no_extras:
         try:
-            line["attention"] = bench_attention(tq, L, device, stream, rank, world, args)
+            line["attention"] = bench_attention(tq, L, device, stream, rank, world, args, args.attn_ctx)
+            if world == 1 and args.attn_ctx == 32768:
+                line["attention_ctx4k"] = bench_attention(tq, L, device, stream, rank, world, args, 4096)
+                line["attention_ctx128k"] = bench_attention(tq, L, device, stream, rank, world, args, 131072)
         except Exception as e:  # secondary measurement: report, do not hide the headline
             line["attention"] = {"error": str(e)}
+        if world == 1:
+            try:
+                line["decoder_layer"] = bench_decoder_layer(tq, L, device, stream, cbs, args)
+            except Exception as e:
+                line["decoder_layer"] = {"error": str(e)}
         try:
             line["prefill"] = bench_prefill(tq, L, layers, device, stream, args)
         except Exception as e:
@@ -331,11 +339,11 @@ def run_cuda(args):
 
 # ---- secondary: compressed-cache decode attention (BASELINE config 3) ---------------------------
 
-def bench_attention(tq, L, device, stream, rank, world, args):
+def bench_attention(tq, L, device, stream, rank, world, args, ctx):
     """16 sequences, 4 KV / 28 query heads, d 128, ctx 32768, QJL on.  KV heads are split across
     ranks when world <= 4 (heads are independent; outputs all-gathered by the caller)."""
     import torch
-    n_seqs, kv_heads, q_heads, dim, ctx = 16, 4, 28, 128, args.attn_ctx
+    n_seqs, kv_heads, q_heads, dim = 16, 4, 28, 128
     if world > kv_heads or kv_heads % world:
         return {"skipped": f"{world} ranks over {kv_heads} KV heads needs a context split"}
     heads_local = kv_heads // world
@@ -431,6 +439,54 @@ def bench_prefill(tq, L, layers, device, stream, args):
     return {"workload": f"{m} activation rows x 4096x4096 TQ8 layer (rotation + fused dequant GEMM, fp16 in, fp32 accumulate)",
             "us_per_layer": us, "tok_per_s": m / (us * 1e-6), "tflops": tf, "frac_of_tensor_peak": tf / peak,
             "peak_tflops": peak, "peak_kind": peak_kind}
+
+
+# ---- secondary: decoder-layer projections at decode batch sizes (BASELINE config 1) ----------------
+
+def bench_decoder_layer(tq, L, device, stream, cbs, args):
+    """The seven projections of a Qwen2.5-7B-shaped decoder layer (hidden 3584, intermediate 18944,
+    28 query / 4 KV heads of 128), TQ8, at batch 1, 8 and 64: one pass = q, k, v, o, gate, up, down
+    back to back (233 MB of codes per pass > L2).  Only the linears are timed (no attention, norms
+    or activations: those are outside the path)."""
+    import torch
+    hidden, inter, q_out, kv_out = 3584, 18944, 28 * 128, 4 * 128
+    shapes = [("q", q_out, hidden), ("k", kv_out, hidden), ("v", kv_out, hidden), ("o", hidden, q_out),
+              ("gate", inter, hidden), ("up", inter, hidden), ("down", hidden, inter)]
+    lins = []
+    for i, (_, out_f, in_f) in enumerate(shapes):
+        lins.append(make_layer(tq, 7000 + i, device, cbs, out_f=out_f, in_f=in_f)[0])
+    code_bytes = sum(o * i for _, o, i in shapes)
+    sp = C.c_void_p(stream.cuda_stream)
+    g = torch.Generator(device=device).manual_seed(77)
+    res = {"workload": "config 1: q/k/v/o/gate/up/down of a Qwen2.5-7B-shaped layer, TQ8, block 128",
+           "code_bytes_per_pass": code_bytes}
+    for batch in (1, 8, 64):
+        xs = [torch.randn((batch, in_f), generator=g, device=device).half() for _, _, in_f in shapes]
+        ys = [torch.empty((batch, out_f), device=device, dtype=torch.float16) for _, out_f, _ in shapes]
+
+        def one_pass():
+            for lin, x, y in zip(lins, xs, ys):
+                rc = L.tq_linear_forward(lin.handle, C.c_void_p(x.data_ptr()), tq.TQ_F16, batch, C.c_void_p(y.data_ptr()), sp)
+                if rc:
+                    raise RuntimeError(L.tq_last_error().decode())
+
+        with torch.cuda.stream(stream):
+            for _ in range(3):
+                one_pass()
+        torch.cuda.synchronize()
+        reps = 10
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        with torch.cuda.stream(stream):
+            e0.record(stream)
+            for _ in range(reps):
+                one_pass()
+            e1.record(stream)
+        torch.cuda.synchronize()
+        us = e0.elapsed_time(e1) * 1e3 / reps
+        res[f"b{batch}"] = {"us_per_layer": us, "tok_per_s": batch / (us * 1e-6), "code_gb_per_s": code_bytes / (us * 1e-6) / 1e9}
+    for lin in lins:
+        lin.close()
+    return res
 
 
 # ---- secondary: row-sharded LM head (BASELINE config 2) -------------------------------------------
