@@ -19,6 +19,9 @@ CASES = [
     (64, 896 + 128, 128, 77, 5, 3, True),  # 5+3-bit joint codes
     (48, 512, 512, 33, 4, 0, False),       # primary only, one WHT block spans several K blocks
     (384, 2048, 1024, 520, 4, 4, True),    # three row tiles x three activation tiles
+    (128, 4096, 128, 40, 4, 4, True),      # one output tile: K split over 8 CTAs, partial sums added in order
+    (130, 768, 64, 64, 4, 4, False),       # dual rotation with K split in 3: one split spans both planes
+    (3584, 2048, 128, 64, 4, 4, True),     # 28 row tiles, K split in 4
 ]
 
 

@@ -228,9 +228,10 @@ private:
         const bool tall = (out_ + 127) / 128 >= 2 * sm_count_;
         if ((batch > kGemmMinBatch || (tall && batch > 16)) && tq::gemm_supported(in_)) {
             const int planes = dual_ ? 2 : 1;
-            gemm_scratch_.reserve(tq::gemm_scratch_bytes(in_, batch, planes));
+            gemm_scratch_.reserve(tq::gemm_scratch_bytes(out_, in_, batch, planes, sm_count_));
             tq::launch_tq8_gemm(codes_.as<uint8_t>(), norms_.as<float>(), tables_.as<float>(), d_x, d_y, out_, in_, batch,
-                                block_, planes, seed_p_, seed_r_, gemm_scratch_.as<void>(), status_.as<unsigned int>(), st);
+                                block_, planes, seed_p_, seed_r_, gemm_scratch_.as<void>(), status_.as<unsigned int>(),
+                                sm_count_, st);
             return;
         }
         for (int b0 = 0; b0 < batch; b0 += 8) {

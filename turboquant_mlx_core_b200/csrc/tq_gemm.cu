@@ -33,6 +33,7 @@
 // Every wait is bounded: a barrier that does not complete within 0.2 s sets the status word and
 // an abort flag, after which all warps fall through to the exit path (which still frees the
 // tensor memory).
+#include <algorithm>
 #include <cmath>
 #include <cstdint>
 
@@ -197,8 +198,10 @@ struct GemmArgs {
     const float* table;     // [n_planes, 256] fp32
     const __half* xrot;     // rotated activation in operand-tile order (see rotate_rows_f16_kernel)
     __half* y;              // [m, out]
+    float* partial;         // [k_splits, m, out] fp32 un-scaled partial sums (only when k_splits > 1)
     unsigned int* status;   // device error word (0 = ok)
     int out, in, m, n_planes;
+    int k_splits;           // CTAs along K per output tile (gridDim.z)
     float inv_scale;
 };
 
@@ -278,8 +281,12 @@ __global__ void __launch_bounds__(kGemmThreads, 1) tq8_gemm_kernel(const GemmArg
     const uint32_t tmem_d = s_tmem_base;
     volatile unsigned int* abort_flag = &s_abort;
 
+    // K blocks of this CTA: a contiguous range of the (plane-major) list of all K blocks.  Ring
+    // slots and barrier phases count from the start of the range; kb_base maps back to columns.
     const int kb_per_plane = p.in / kBlockK;
-    const int n_kb = kb_per_plane * p.n_planes;
+    const int n_kb_total = kb_per_plane * p.n_planes;
+    const int kb_base = static_cast<int>(static_cast<long>(n_kb_total) * blockIdx.z / p.k_splits);
+    const int n_kb = static_cast<int>(static_cast<long>(n_kb_total) * (blockIdx.z + 1) / p.k_splits) - kb_base;
 
     if (warp < kProducerWarps) {
         // ---- producers ------------------------------------------------------------------------
@@ -298,8 +305,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1) tq8_gemm_kernel(const GemmArg
         constexpr int kCodeAhead = 4;
         auto load_codes = [&](int kb, uint4& lo, uint4& hi) {
             if (kb < n_kb) {
-                const int plane = kb >= kb_per_plane ? 1 : 0;
-                const uint8_t* src = code_ptr + (kb - plane * kb_per_plane) * kBlockK;
+                const int plane = (kb_base + kb) >= kb_per_plane ? 1 : 0;
+                const uint8_t* src = code_ptr + (kb_base + kb - plane * kb_per_plane) * kBlockK;
                 lo = __ldg(reinterpret_cast<const uint4*>(src));
                 hi = __ldg(reinterpret_cast<const uint4*>(src + 16));
             }
@@ -318,7 +325,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) tq8_gemm_kernel(const GemmArg
                 const int kb = kb0 + u;
                 if (!alive || kb >= n_kb) break;
                 const int sa = kb % kAStages;
-                const int plane = kb >= kb_per_plane ? 1 : 0;
+                const int plane = (kb_base + kb) >= kb_per_plane ? 1 : 0;
                 if (kb >= kAStages && !bar_wait(bar_empty_a + 8u * sa, ((kb / kAStages) - 1) & 1, abort_flag)) {
                     atomicExch(p.status, 6u);
                     atomicExch(&s_abort, 1u);
@@ -367,8 +374,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1) tq8_gemm_kernel(const GemmArg
                 break;
             }
             if (lane == 0) {
-                const int plane = kb >= kb_per_plane ? 1 : 0;
-                const size_t tile = (static_cast<size_t>(plane) * n_tok_tiles + blockIdx.y) * kb_per_plane + (kb - plane * kb_per_plane);
+                const int plane = (kb_base + kb) >= kb_per_plane ? 1 : 0;
+                const size_t tile = (static_cast<size_t>(plane) * n_tok_tiles + blockIdx.y) * kb_per_plane + (kb_base + kb - plane * kb_per_plane);
                 const __half* src = p.xrot + tile * (kTileTok * kBlockK);
                 const uint32_t bar = bar_full_b + 8u * sb;
                 asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(kBBytes) : "memory");
@@ -426,7 +433,10 @@ __global__ void __launch_bounds__(kGemmThreads, 1) tq8_gemm_kernel(const GemmArg
 #pragma unroll
                 for (int j = 0; j < 32; ++j) {
                     const int tok = tok0 + col0 + j;
-                    if (r_ok && tok < p.m) p.y[static_cast<size_t>(tok) * p.out + r] = __float2half_rn(__uint_as_float(v[j]) * scale);
+                    if (r_ok && tok < p.m) {
+                        if (p.k_splits == 1) p.y[static_cast<size_t>(tok) * p.out + r] = __float2half_rn(__uint_as_float(v[j]) * scale);
+                        else p.partial[(static_cast<size_t>(blockIdx.z) * p.m + tok) * p.out + r] = __uint_as_float(v[j]);
+                    }
                 }
             }
         }
@@ -439,18 +449,47 @@ __global__ void __launch_bounds__(kGemmThreads, 1) tq8_gemm_kernel(const GemmArg
     }
 }
 
+// y = fp16(norm * inv_scale * sum over K splits, in split order) — fixed order, run-to-run identical.
+__global__ void __launch_bounds__(256) gemm_finish_kernel(const float* __restrict__ partial, const float* __restrict__ norms,
+                                                          __half* __restrict__ y, long m, int out, int k_splits,
+                                                          float inv_scale) {
+    const long n = m * out;
+    for (long i = static_cast<long>(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += static_cast<long>(gridDim.x) * blockDim.x) {
+        float acc = 0.f;
+        for (int z = 0; z < k_splits; ++z) acc += partial[static_cast<long>(z) * n + i];
+        y[i] = __float2half_rn(acc * (__ldg(norms + i % out) * inv_scale));
+    }
+}
+
+size_t xrot_bytes(int in, long m, int n_planes) {
+    const size_t padded = (static_cast<size_t>(m) + kTileTok - 1) / kTileTok * kTileTok;  // whole operand tiles
+    return (static_cast<size_t>(n_planes) * padded * static_cast<size_t>(in) * sizeof(__half) + 255) & ~static_cast<size_t>(255);
+}
+
 }  // namespace
 
-size_t gemm_scratch_bytes(int in, long m, int n_planes) {
-    const size_t padded = (static_cast<size_t>(m) + kTileTok - 1) / kTileTok * kTileTok;  // whole operand tiles
-    return static_cast<size_t>(n_planes) * padded * static_cast<size_t>(in) * sizeof(__half);
+// When the output has too few tiles to occupy the SMs (few activation rows on a matrix with few
+// rows and many columns), K is split over several CTAs per tile; every split keeps at least 8 K blocks.
+int gemm_k_splits(int out, int in, long m, int n_planes, int sm_count) {
+    const long tiles = static_cast<long>((out + kTileRows - 1) / kTileRows) * ((m + kTileTok - 1) / kTileTok);
+    const int n_kb = in / kBlockK * n_planes;
+    long s = sm_count / (tiles > 0 ? tiles : 1);
+    if (s > n_kb / 8) s = n_kb / 8;
+    return s < 1 ? 1 : static_cast<int>(s);
+}
+
+size_t gemm_scratch_bytes(int out, int in, long m, int n_planes, int sm_count) {
+    const int splits = gemm_k_splits(out, in, m, n_planes, sm_count);
+    size_t bytes = xrot_bytes(in, m, n_planes);
+    if (splits > 1) bytes += static_cast<size_t>(splits) * static_cast<size_t>(m) * out * sizeof(float);
+    return bytes;
 }
 
 bool gemm_supported(int in) { return in % kBlockK == 0; }
 
 void launch_tq8_gemm(const uint8_t* codes, const float* norms, const float* table, const __half* x, __half* y, int out,
                      int in, long m, uint32_t block, int n_planes, uint32_t seed_p, uint32_t seed_r, void* scratch,
-                     unsigned int* status, cudaStream_t stream) {
+                     unsigned int* status, int sm_count, cudaStream_t stream) {
     TQ_REQUIRE(n_planes == 1 || n_planes == 2, "tq8_gemm: one or two rotation planes");
     TQ_REQUIRE(gemm_supported(in), "tq8_gemm: in_features must be a multiple of 64");
     TQ_REQUIRE(is_pow2(block) && block >= 32 && block <= 1024, "WHT block size must be a power of two in [32, 1024]");
@@ -481,6 +520,8 @@ void launch_tq8_gemm(const uint8_t* codes, const float* norms, const float* tabl
     a.codes = codes; a.norms = norms; a.table = table; a.xrot = xrot; a.y = y; a.status = status;
     a.out = out; a.in = in; a.m = static_cast<int>(m); a.n_planes = n_planes;
     a.inv_scale = 1.0f / std::sqrt(static_cast<float>(in));
+    a.k_splits = gemm_k_splits(out, in, m, n_planes, sm_count);
+    a.partial = a.k_splits > 1 ? reinterpret_cast<float*>(static_cast<uint8_t*>(scratch) + xrot_bytes(in, m, n_planes)) : nullptr;
     // stages + tables + worst-case padding in front of the 32 KB-aligned tables
     const size_t smem = kGemmSmemBytes;
     static bool configured[64] = {false};
@@ -492,9 +533,15 @@ void launch_tq8_gemm(const uint8_t* codes, const float* norms, const float* tabl
         if (dev < 64) configured[dev] = true;
     }
     const dim3 grid(static_cast<unsigned int>((out + kTileRows - 1) / kTileRows),
-                    static_cast<unsigned int>((m + kTileTok - 1) / kTileTok));
+                    static_cast<unsigned int>((m + kTileTok - 1) / kTileTok), static_cast<unsigned int>(a.k_splits));
     tq8_gemm_kernel<<<grid, kGemmThreads, smem, stream>>>(a);
     TQ_CUDA(cudaGetLastError());
+    if (a.k_splits > 1) {
+        const long n = m * out;
+        const unsigned int blocks = static_cast<unsigned int>(std::min<long>((n + 255) / 256, 148L * 8));
+        gemm_finish_kernel<<<blocks, 256, 0, stream>>>(a.partial, norms, y, m, out, a.k_splits, a.inv_scale);
+        TQ_CUDA(cudaGetLastError());
+    }
 }
 
 }  // namespace tq

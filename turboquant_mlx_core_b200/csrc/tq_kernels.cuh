@@ -45,14 +45,15 @@ void launch_tq8_gemv_static(const uint8_t* codes, const float* norms, const floa
                             unsigned int* status, int sm_count, cudaStream_t stream);
 
 // tq_gemm.cu — fused dequantise + GEMM on tcgen05 / tensor memory for many activation rows
-// (prefill).  x: [m, in] fp16, y: [m, out] fp16.  scratch: gemm_scratch_bytes(in, m, n_planes)
-// bytes (the rotated activation, fp16).  Needs in % 64 == 0 (gemm_supported).  status: one
+// (prefill).  x: [m, in] fp16, y: [m, out] fp16.  scratch: gemm_scratch_bytes(...) bytes (the
+// rotated activation in fp16, plus fp32 partial sums when K is split over CTAs).  Needs in % 64 == 0 (gemm_supported).  status: one
 // device word, set non-zero if the kernel refused to run or a bounded wait gave up.
 bool gemm_supported(int in);
-size_t gemm_scratch_bytes(int in, long m, int n_planes);
+int gemm_k_splits(int out, int in, long m, int n_planes, int sm_count);
+size_t gemm_scratch_bytes(int out, int in, long m, int n_planes, int sm_count);
 void launch_tq8_gemm(const uint8_t* codes, const float* norms, const float* table, const __half* x, __half* y, int out,
                      int in, long m, uint32_t block, int n_planes, uint32_t seed_p, uint32_t seed_r, void* scratch,
-                     unsigned int* status, cudaStream_t stream);
+                     unsigned int* status, int sm_count, cudaStream_t stream);
 
 // tq_quantize.cu — bit-exact weight quantiser.  derive_seeds hashes the sampled bytes
 // of the fp32 weight (synchronises the stream).  launch_quantize_weight: cb_p / cb_r are
