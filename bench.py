@@ -340,20 +340,27 @@ def run_cuda(args):
 # ---- secondary: compressed-cache decode attention (BASELINE config 3) ---------------------------
 
 def bench_attention(tq, L, device, stream, rank, world, args, ctx):
-    """16 sequences, 4 KV / 28 query heads, d 128, ctx 32768, QJL on.  KV heads are split across
-    ranks when world <= 4 (heads are independent; outputs all-gathered by the caller)."""
+    """16 sequences, 4 KV / 28 query heads, d 128, QJL on.  Up to 4 ranks split the KV heads (heads
+    are independent).  With more ranks than KV heads the ranks sharing a head split the context
+    range, each computes a partial result with its log-sum-exp, and an all-gather over the
+    world followed by a merge gives every rank the full result (timed inside the region)."""
     import torch
+    import torch.distributed as dist
+    from turboquant_mlx_core_b200.sharding import attention_grid, context_range, merge_attention_parts
     n_seqs, kv_heads, q_heads, dim = 16, 4, 28, 128
-    if world > kv_heads or kv_heads % world:
-        return {"skipped": f"{world} ranks over {kv_heads} KV heads needs a context split"}
-    heads_local = kv_heads // world
-    qh_local = q_heads // world
+    if world > kv_heads and world % kv_heads:
+        return {"skipped": f"{world} ranks over {kv_heads} KV heads: rank count must be a multiple of the heads"}
+    h0, h1, part, parts = attention_grid(kv_heads, rank, world)
+    heads_local = h1 - h0
+    qh_local = q_heads // kv_heads * heads_local
+    c0, c1 = context_range(0, ctx, part, parts)
+    ctx_local = c1 - c0
     g = torch.Generator(device=device).manual_seed(100 + rank)
     caches = []
     for s in range(n_seqs):
         c = tq.TQKVCache(1, heads_local, dim)
-        for t0 in range(0, ctx, 8192):
-            n = min(8192, ctx - t0)
+        for t0 in range(0, ctx_local, 8192):
+            n = min(8192, ctx_local - t0)
             k = torch.randn((n, heads_local, dim), generator=g, device=device)
             v = torch.randn((n, heads_local, dim), generator=g, device=device)
             k[:, :, ::20] *= 8.0          # ~5 % outlier channels
@@ -362,19 +369,32 @@ def bench_attention(tq, L, device, stream, rank, world, args, ctx):
         caches.append(c)
     q = torch.randn((n_seqs, qh_local, dim), generator=g, device=device).half()
     out = torch.empty_like(q)
+    lse = torch.empty((n_seqs, qh_local), device=device, dtype=torch.float32)
     arr = (C.c_void_p * n_seqs)(*[c.handle for c in caches])
     sp = C.c_void_p(stream.cuda_stream)
+    gathered_o = torch.empty((world,) + tuple(out.shape), device=device, dtype=out.dtype) if parts > 1 else None
+    gathered_l = torch.empty((world,) + tuple(lse.shape), device=device, dtype=lse.dtype) if parts > 1 else None
 
     def call():
-        rc = L.tq_kv_attention(arr, n_seqs, 0, C.c_void_p(q.data_ptr()), tq.TQ_F16, qh_local,
-                               C.c_void_p(out.data_ptr()), 0, -1, 1, sp)
+        rc = L.tq_kv_attention_lse(arr, n_seqs, 0, C.c_void_p(q.data_ptr()), tq.TQ_F16, qh_local,
+                                   C.c_void_p(out.data_ptr()), C.c_void_p(lse.data_ptr()), 0, -1, 1, sp)
         if rc:
             raise RuntimeError(L.tq_last_error().decode())
+        if parts > 1:
+            # every rank receives all (head, part) results; rows of ranks r, r + kv_heads, ... share a head
+            dist.all_gather_into_tensor(gathered_o.view(-1, qh_local, dim), out)
+            dist.all_gather_into_tensor(gathered_l.view(-1, qh_local), lse)
+            o = gathered_o.view(parts, kv_heads, n_seqs, qh_local, dim)
+            l_ = gathered_l.view(parts, kv_heads, n_seqs, qh_local)
+            return merge_attention_parts(o, l_)
+        return out
 
     with torch.cuda.stream(stream):
         for _ in range(3):
             call()
     torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
     reps = 10
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     with torch.cuda.stream(stream):
@@ -383,62 +403,20 @@ def bench_attention(tq, L, device, stream, rank, world, args, ctx):
             call()
         e1.record(stream)
     torch.cuda.synchronize()
-    us = e0.elapsed_time(e1) * 1e3 / reps
-    algo = n_seqs * heads_local * ctx * 118          # compact bytes per (token, KV head) with QJL
+    t = torch.tensor([e0.elapsed_time(e1) * 1e3 / reps], device=device, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    us = float(t.item())
+    algo = n_seqs * heads_local * ctx_local * 118          # compact bytes per (token, KV head) with QJL
     peak, kind = measured_peaks()
     for c in caches:
         c.close()
     return {"workload": f"config 3: {n_seqs} seqs x ctx {ctx}, {kv_heads} KV / {q_heads} query heads, d {dim}, QJL on",
             "us_per_layer_step": us, "tok_per_s": n_seqs / (us * 1e-6), "gb_per_s_per_gpu": algo / (us * 1e-6) / 1e9,
             "frac_of_peak": algo / (us * 1e-6) / 1e9 / peak, "peak_kind": kind, "kv_heads_per_gpu": heads_local,
-            "l2_policy": f"cache {n_seqs * heads_local * ctx * 132 / 1e6:.0f} MB > L2"}
-
-
-# ---- secondary: prefill through the tensor-core GEMM (BASELINE config 1, prefill part) -------------
-
-def bench_prefill(tq, L, layers, device, stream, args):
-    """2048 activation rows through 4096x4096 TQ8 layers (distinct layers back to back, as in the
-    headline loop): fused dequantise + tcgen05 GEMM, activation rotation included."""
-    import torch
-    m = 2048
-    n_layers = min(len(layers), 8)
-    g = torch.Generator(device=device).manual_seed(900)
-    x = torch.randn((m, IN_F), generator=g, device=device).half()
-    y = torch.empty((m, OUT_F), device=device, dtype=torch.float16)
-    sp = C.c_void_p(stream.cuda_stream)
-
-    def call(lin):
-        rc = L.tq_linear_forward(lin.handle, C.c_void_p(x.data_ptr()), tq.TQ_F16, m, C.c_void_p(y.data_ptr()), sp)
-        if rc:
-            raise RuntimeError(L.tq_last_error().decode())
-
-    with torch.cuda.stream(stream):
-        for lin in layers[:n_layers]:
-            call(lin)
-    torch.cuda.synchronize()
-    reps = 5
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    with torch.cuda.stream(stream):
-        e0.record(stream)
-        for _ in range(reps):
-            for lin in layers[:n_layers]:
-                call(lin)
-        e1.record(stream)
-    torch.cuda.synchronize()
-    if L.tq_linear_status(layers[0].handle):
-        raise RuntimeError(L.tq_last_error().decode())
-    us = e0.elapsed_time(e1) * 1e3 / (reps * n_layers)
-    flops = 2.0 * m * OUT_F * IN_F
-    peak = None
-    pth = os.path.join(ROOT, "MEASURED_PEAKS.json")
-    if os.path.exists(pth):
-        peak = float(json.load(open(pth)).get("bf16_tflops", 0)) or None
-    peak_kind = "measured cuBLAS bf16 burst" if peak else "fallback"
-    peak = peak or 1590.0
-    tf = flops / (us * 1e-6) / 1e12
-    return {"workload": f"{m} activation rows x 4096x4096 TQ8 layer (rotation + fused dequant GEMM, fp16 in, fp32 accumulate)",
-            "us_per_layer": us, "tok_per_s": m / (us * 1e-6), "tflops": tf, "frac_of_tensor_peak": tf / peak,
-            "peak_tflops": peak, "peak_kind": peak_kind}
+            "context_parts": parts,
+            "l2_policy": f"cache {n_seqs * heads_local * ctx_local * 132 / 1e6:.0f} MB per GPU "
+                         + ("> L2" if n_seqs * heads_local * ctx_local * 132 > 126e6 else "<= L2 (126 MB)")}
 
 
 # ---- secondary: decoder-layer projections at decode batch sizes (BASELINE config 1) ----------------

@@ -197,6 +197,15 @@ int tq_kv_export(tq_kv_cache_t cache, int layer, uint32_t* k_words, uint32_t* v_
 int tq_kv_attention(const tq_kv_cache_t* caches, int n_seqs, int layer, const void* queries, int q_dtype,
                     int q_heads, void* out_fp16, int start, int end, int use_qjl, void* stream);
 
+/** The same, and additionally lse_out[n_seqs, q_heads] (fp32, host or device; may be NULL): the
+ *  natural log of each row's softmax denominator over the scaled scores of tokens
+ *  [start, end).  Two results (out_a, lse_a), (out_b, lse_b) over disjoint token ranges of one
+ *  sequence merge exactly as  out = (out_a e^{lse_a - m} + out_b e^{lse_b - m}) /
+ *  (e^{lse_a - m} + e^{lse_b - m}),  m = max(lse_a, lse_b) — which is how a sequence's context is
+ *  split across GPUs.  No counterpart in the reference. */
+int tq_kv_attention_lse(const tq_kv_cache_t* caches, int n_seqs, int layer, const void* queries, int q_dtype,
+                        int q_heads, void* out_fp16, float* lse_out, int start, int end, int use_qjl, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -127,3 +127,34 @@ def test_reference_c_api_with_arrays(tq, golden):
     for a in (oa, qa, ka, va):
         L.tq_array_free(a)
     L.tq_kv_cache_free(cache)
+
+
+def test_attention_lse_merges_context_parts(tq):
+    """Attention over [0, n) equals the merge of attention over three disjoint token ranges using
+    the log-sum-exp output: the rule by which a sequence's context is split across GPUs."""
+    from turboquant_mlx_core_b200.sharding import context_range, merge_attention_parts
+    rng = np.random.default_rng(21)
+    heads, dim, tokens, q_heads = 4, 128, 700, 28
+    caches = []
+    for s_ in range(2):
+        c = tq.TQKVCache(1, heads, dim)
+        c.append(0, rng.standard_normal((tokens, heads, dim)).astype(np.float16),
+                 rng.standard_normal((tokens, heads, dim)).astype(np.float16))
+        caches.append(c)
+    q = rng.standard_normal((2, q_heads, dim)).astype(np.float16)
+    for use_qjl in (False, True):
+        full, lse_full = tq.compressed_attention(caches, 0, q, use_qjl=use_qjl, return_lse=True)
+        assert lse_full.shape == (2, q_heads) and np.all(np.isfinite(lse_full))
+        outs, lses = [], []
+        for part in range(3):
+            a, b = context_range(0, tokens, part, 3)
+            o, l = tq.compressed_attention(caches, 0, q, start=a, end=b, use_qjl=use_qjl, return_lse=True)
+            outs.append(o.astype(np.float32))
+            lses.append(l)
+        merged = merge_attention_parts(np.stack(outs), np.stack(lses))
+        assert rel_l2(merged, full.astype(np.float32)) < ATTN_TOL
+        # the parts' denominators add up to the whole
+        m = np.max(np.stack(lses), axis=0)
+        assert np.allclose(m + np.log(np.sum(np.exp(np.stack(lses) - m), axis=0)), lse_full, rtol=0, atol=2e-3)
+    for c in caches:
+        c.close()

@@ -71,3 +71,71 @@ def test_all_gather_of_row_shards_gloo():
     for p in procs:
         p.join(60)
     assert res == [(0, True), (1, True)]
+
+
+def test_attention_grid_and_context_range():
+    from turboquant_mlx_core_b200.sharding import attention_grid, context_range
+    assert [attention_grid(4, r, 2) for r in range(2)] == [(0, 2, 0, 1), (2, 4, 0, 1)]
+    assert [attention_grid(4, r, 8) for r in range(8)] == [(r % 4, r % 4 + 1, r // 4, 2) for r in range(8)]
+    with pytest.raises(ValueError):
+        attention_grid(4, 0, 6)
+    spans = [context_range(5, 1005, p, 3) for p in range(3)]
+    assert spans[0][0] == 5 and spans[-1][1] == 1005 and all(a[1] == b[0] for a, b in zip(spans, spans[1:]))
+
+
+def _softmax_parts(rng, parts, rows, toks, dim):
+    """Per-part attention outputs and log-sum-exps of one random problem, plus the full answer."""
+    s = rng.standard_normal((rows, toks)).astype(np.float64) * 3
+    v = rng.standard_normal((toks, dim)).astype(np.float64)
+    w = np.exp(s - s.max(axis=1, keepdims=True))
+    full = (w / w.sum(axis=1, keepdims=True)) @ v
+    outs, lses = [], []
+    for p in range(parts):
+        a, b = toks * p // parts, toks * (p + 1) // parts
+        sp = s[:, a:b]
+        m = sp.max(axis=1, keepdims=True)
+        e = np.exp(sp - m)
+        outs.append((e / e.sum(axis=1, keepdims=True)) @ v[a:b])
+        lses.append((m[:, 0] + np.log(e.sum(axis=1))))
+    return np.stack(outs).astype(np.float32), np.stack(lses).astype(np.float32), full
+
+
+def test_merge_attention_parts_is_exact():
+    from turboquant_mlx_core_b200.sharding import merge_attention_parts
+    rng = np.random.default_rng(4)
+    outs, lses, full = _softmax_parts(rng, 3, 7, 50, 16)
+    got = merge_attention_parts(outs, lses)
+    assert np.allclose(got, full, rtol=1e-5, atol=1e-6)
+    import torch
+    got_t = merge_attention_parts(torch.tensor(outs), torch.tensor(lses)).numpy()
+    assert np.allclose(got_t, full, rtol=1e-5, atol=1e-6)
+    # a part with no tokens (lse = -inf) contributes nothing
+    outs2 = np.concatenate([outs, np.zeros_like(outs[:1])])
+    lses2 = np.concatenate([lses, np.full_like(lses[:1], -np.inf)])
+    assert np.allclose(merge_attention_parts(outs2, lses2), full, rtol=1e-5, atol=1e-6)
+
+
+def _worker_attn(rank, world, port, q):
+    import torch
+    import torch.distributed as dist
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    from turboquant_mlx_core_b200.sharding import all_gather_attention_parts
+    outs, lses, full = _softmax_parts(np.random.default_rng(9), world, 6, 40, 8)
+    got = all_gather_attention_parts(torch.tensor(outs[rank]), torch.tensor(lses[rank]))
+    q.put((rank, bool(np.allclose(got.numpy(), full, rtol=1e-5, atol=1e-6))))
+    dist.destroy_process_group()
+
+
+def test_context_split_merge_gloo():
+    import torch.multiprocessing as mp
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_worker_attn, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    res = sorted(q.get(timeout=120) for _ in procs)
+    for p in procs:
+        p.join(60)
+    assert res == [(0, True), (1, True)]

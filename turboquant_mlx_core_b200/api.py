@@ -308,10 +308,12 @@ class TQKVCache:
 
 
 def compressed_attention(caches, layer: int, queries, start: int = 0, end: int = -1, use_qjl: bool = False,
-                         out=None, stream=None):
+                         out=None, stream=None, return_lse: bool = False):
     """Decode attention over the compressed caches of a batch of sequences: the long-context
     branch of hybrid_attention (src/attention_dispatch.cpp:58-73) without materialising K/V.
-    queries: [n_seqs, q_heads, head_dim] -> fp16 of the same shape."""
+    queries: [n_seqs, q_heads, head_dim] -> fp16 of the same shape.  With return_lse the result
+    is (out, lse): lse[n_seqs, q_heads] fp32 is the log of each row's softmax denominator, which
+    lets results over disjoint token ranges be merged (sharding.merge_attention_parts)."""
     L = _lib.load()
     if isinstance(caches, TQKVCache):
         caches = [caches]
@@ -328,6 +330,15 @@ def compressed_attention(caches, layer: int, queries, start: int = 0, end: int =
         else:
             out = np.empty(queries.shape, np.float16)
     arr = (C.c_void_p * n)(*[c.handle for c in caches])
-    check(L.tq_kv_attention(arr, n, layer, _ptr(queries), _dtype_tag(queries), q_heads, _ptr(out), start, end,
-                            int(use_qjl), _stream_ptr(stream)), "compressed_attention")
-    return out
+    if not return_lse:
+        check(L.tq_kv_attention(arr, n, layer, _ptr(queries), _dtype_tag(queries), q_heads, _ptr(out), start, end,
+                                int(use_qjl), _stream_ptr(stream)), "compressed_attention")
+        return out
+    if _is_torch(queries):
+        import torch
+        lse = torch.empty((n, q_heads), dtype=torch.float32, device=queries.device)
+    else:
+        lse = np.empty((n, q_heads), np.float32)
+    check(L.tq_kv_attention_lse(arr, n, layer, _ptr(queries), _dtype_tag(queries), q_heads, _ptr(out), _ptr(lse), start,
+                                end, int(use_qjl), _stream_ptr(stream)), "compressed_attention")
+    return out, lse

@@ -23,7 +23,7 @@ void launch_kv_decode_f16(const uint32_t* words, const float* norms, long n_vec,
 size_t attn_scratch_bytes(int n_seqs, int q_heads, int head_dim, int n_splits);
 void launch_kv_attention(const void* d_seqs, int n_seqs, const void* q, bool q_is_f16, int q_heads, int kv_heads,
                          int head_dim, int n_splits, uint32_t k_seed, uint32_t v_seed, uint32_t qjl_seed, bool use_qjl,
-                         void* scratch, __half* out, cudaStream_t stream);
+                         void* scratch, __half* out, float* lse, cudaStream_t stream);
 }  // namespace tq
 
 namespace turboquant {
@@ -168,6 +168,7 @@ public:
     DeviceBuffer& attn_desc() { return attn_desc_; }
     DeviceBuffer& attn_q() { return attn_q_; }
     DeviceBuffer& attn_out() { return attn_out_; }
+    DeviceBuffer& attn_lse() { return attn_lse_; }
 
 private:
     // Grow a layer's buffers to hold `tokens` tokens (capacity doubles; old contents kept).
@@ -196,13 +197,13 @@ private:
     int seq_length_ = 0;
     std::vector<LayerKVStorage> layers_;
     DeviceBuffer stage_k_, stage_v_;
-    DeviceBuffer attn_scratch_, attn_desc_, attn_q_, attn_out_;
+    DeviceBuffer attn_scratch_, attn_desc_, attn_q_, attn_out_, attn_lse_;
 };
 
 // Attention of one query position per sequence over [start, end) of each cache.
 // q: [n_seqs, q_heads, dim] fp32/fp16, out: fp16 same shape; host or device.
 void attention_batched(TQKVCache* const* caches, int n_seqs, int layer, const void* q, int q_dtype, int q_heads,
-                       const int* starts, const int* ends, bool use_qjl, void* out, cudaStream_t st) {
+                       const int* starts, const int* ends, bool use_qjl, void* out, float* lse_out, cudaStream_t st) {
     TQ_REQUIRE(caches && n_seqs > 0 && q && out, "attention: bad argument");
     TQ_REQUIRE(q_dtype == TQ_F32 || q_dtype == TQ_F16, "attention: queries must be fp32 or fp16");
     TQKVCache* c0 = caches[0];
@@ -242,16 +243,23 @@ void attention_batched(TQKVCache* const* caches, int n_seqs, int layer, const vo
         c0->attn_out().reserve(n_q * sizeof(__half));
         d_out = c0->attn_out().as<__half>();
     }
+    // optional log-sum-exp per (sequence, query head), fp32, host or device
+    const size_t n_lse = static_cast<size_t>(n_seqs) * q_heads;
+    float* d_lse = lse_out;
+    if (lse_out != nullptr && !tq::is_device_pointer(lse_out)) {
+        c0->attn_lse().reserve(n_lse * sizeof(float));
+        d_lse = c0->attn_lse().as<float>();
+    }
     c0->attn_scratch().reserve(tq::attn_scratch_bytes(n_seqs, q_heads, dim, n_splits));
     tq::launch_kv_attention(c0->attn_desc().as<void>(), n_seqs, d_q, q_dtype == TQ_F16, q_heads, heads, dim, n_splits,
                             tq::kv_layer_seed(static_cast<uint32_t>(layer), 1), tq::kv_layer_seed(static_cast<uint32_t>(layer), 2),
-                            tq::kv_layer_seed(static_cast<uint32_t>(layer), 3), use_qjl, c0->attn_scratch().as<void>(), d_out, st);
+                            tq::kv_layer_seed(static_cast<uint32_t>(layer), 3), use_qjl, c0->attn_scratch().as<void>(), d_out, d_lse, st);
     // desc was copied from pageable host memory: the copy has been staged by the time
     // cudaMemcpyAsync returned, so `desc` may die here.
-    if (!out_dev) {
-        TQ_CUDA(cudaMemcpyAsync(out, d_out, n_q * sizeof(__half), cudaMemcpyDeviceToHost, st));
-        TQ_CUDA(cudaStreamSynchronize(st));
-    }
+    const bool lse_host = lse_out != nullptr && d_lse != lse_out;
+    if (lse_host) TQ_CUDA(cudaMemcpyAsync(lse_out, d_lse, n_lse * sizeof(float), cudaMemcpyDeviceToHost, st));
+    if (!out_dev) TQ_CUDA(cudaMemcpyAsync(out, d_out, n_q * sizeof(__half), cudaMemcpyDeviceToHost, st));
+    if (!out_dev || lse_host) TQ_CUDA(cudaStreamSynchronize(st));
 }
 
 }  // namespace turboquant
@@ -356,7 +364,7 @@ void* tq_kv_cache_attention(tq_kv_cache_t cache, int layer, const void* queries_
         try {
             turboquant::TQKVCache* one[1] = {cache->cache};
             turboquant::attention_batched(one, 1, layer, q->data, q->dtype, q_heads, &compressed_start, &compressed_end,
-                                          false, out->data, nullptr);
+                                          false, out->data, nullptr, nullptr);
         } catch (...) {
             tq_array_free(out);
             throw;
@@ -402,6 +410,11 @@ int tq_kv_export(tq_kv_cache_t cache, int layer, uint32_t* k_words, uint32_t* v_
 
 int tq_kv_attention(const tq_kv_cache_t* caches, int n_seqs, int layer, const void* queries, int q_dtype, int q_heads,
                     void* out_fp16, int start, int end, int use_qjl, void* stream) {
+    return tq_kv_attention_lse(caches, n_seqs, layer, queries, q_dtype, q_heads, out_fp16, nullptr, start, end, use_qjl, stream);
+}
+
+int tq_kv_attention_lse(const tq_kv_cache_t* caches, int n_seqs, int layer, const void* queries, int q_dtype, int q_heads,
+                        void* out_fp16, float* lse_out, int start, int end, int use_qjl, void* stream) {
     return guarded<int>(0, -1, [&]() {
         TQ_REQUIRE(caches && n_seqs > 0, "tq_kv_attention: no caches");
         std::vector<turboquant::TQKVCache*> cs(static_cast<size_t>(n_seqs));
@@ -413,7 +426,7 @@ int tq_kv_attention(const tq_kv_cache_t* caches, int n_seqs, int layer, const vo
             ends[i] = end < 0 ? caches[i]->cache->layer_tokens(layer) : end;
         }
         turboquant::attention_batched(cs.data(), n_seqs, layer, queries, q_dtype, q_heads, starts.data(), ends.data(),
-                                      use_qjl != 0, out_fp16, static_cast<cudaStream_t>(stream));
+                                      use_qjl != 0, out_fp16, lse_out, static_cast<cudaStream_t>(stream));
         return 0;
     });
 }

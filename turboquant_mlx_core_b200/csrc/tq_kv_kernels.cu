@@ -295,7 +295,8 @@ __global__ void __launch_bounds__(128) attn_partial_kernel(const AttnSeq* __rest
 template <int E>
 __global__ void __launch_bounds__(128) attn_combine_kernel(const float* __restrict__ part_acc, const float* __restrict__ part_ml,
                                                            long n_rows, int n_splits, uint32_t v_seed, float inv_sqrt,
-                                                           float inv_scale_d, __half* __restrict__ out) {
+                                                           float inv_scale_d, __half* __restrict__ out,
+                                                           float* __restrict__ lse) {
     constexpr int D = 32 * E;
     const int lane = threadIdx.x & 31;
     const long row = (static_cast<long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
@@ -316,6 +317,8 @@ __global__ void __launch_bounds__(128) attn_combine_kernel(const float* __restri
     for (int j = 0; j < E; ++j) v[j] *= inv_scale_d;
     warp_fwht<E>(v, lane);
     const float invL = (L > 0.0f) ? 1.0f / L : 0.0f;
+    // log of the softmax denominator: lets a caller merge results over disjoint token ranges
+    if (lse != nullptr && lane == 0) lse[row] = (L > 0.0f) ? M + __logf(L) : -INFINITY;
 #pragma unroll
     for (int j = 0; j < E; ++j)
         out[row * D + lane * E + j] =
@@ -681,7 +684,7 @@ size_t attn_scratch_bytes(int n_seqs, int q_heads, int head_dim, int n_splits) {
 
 void launch_kv_attention(const void* d_seqs, int n_seqs, const void* q, bool q_is_f16, int q_heads, int kv_heads,
                          int head_dim, int n_splits, uint32_t k_seed, uint32_t v_seed, uint32_t qjl_seed, bool use_qjl,
-                         void* scratch, __half* out, cudaStream_t stream) {
+                         void* scratch, __half* out, float* lse, cudaStream_t stream) {
     if (n_seqs == 0) return;
     TQ_REQUIRE(q_heads % kv_heads == 0, "query heads must be a multiple of KV heads");
     const int G = q_heads / kv_heads;
@@ -706,7 +709,7 @@ void launch_kv_attention(const void* d_seqs, int n_seqs, const void* q, bool q_i
                                                                  n_splits, k_seed, qjl_seed, use_qjl ? 1 : 0, inv_sqrt,   \
                                                                  inv_scale_d, attn_scale, gamma, part_acc, part_ml);     \
     attn_combine_kernel<EV><<<static_cast<int>((n_rows + 3) / 4), 128, 0, stream>>>(part_acc, part_ml, n_rows, n_splits, \
-                                                                                   v_seed, inv_sqrt, inv_scale_d, out);
+                                                                                   v_seed, inv_sqrt, inv_scale_d, out, lse);
     if (head_dim == 128) {
         if (q_is_f16)
             attn_mma_kernel<__half><<<grid, kMmaThreads, 0, stream>>>(static_cast<const AttnSeq*>(d_seqs),
@@ -719,7 +722,7 @@ void launch_kv_attention(const void* d_seqs, int n_seqs, const void* q, bool q_i
                                                                        n_splits, k_seed, qjl_seed, use_qjl ? 1 : 0, inv_sqrt,
                                                                        inv_scale_d, attn_scale, gamma, part_acc, part_ml);
         attn_combine_kernel<4><<<static_cast<int>((n_rows + 3) / 4), 128, 0, stream>>>(part_acc, part_ml, n_rows, n_splits,
-                                                                                      v_seed, inv_sqrt, inv_scale_d, out);
+                                                                                      v_seed, inv_sqrt, inv_scale_d, out, lse);
         TQ_CUDA(cudaGetLastError());
         return;
     }

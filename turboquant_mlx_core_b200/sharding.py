@@ -49,3 +49,59 @@ def all_gather_rows(local, out_features: int, world: int):
     for r, (s, e) in enumerate(spans):
         out[:, s:e] = gathered[r, :, : e - s]
     return out
+
+
+def attention_grid(kv_heads: int, rank: int, world: int) -> tuple[int, int, int, int]:
+    """Placement of `rank` for decode attention: (first KV head, one-past-last KV head, context
+    part, number of context parts).  Up to kv_heads ranks split the heads; beyond that each head
+    is shared by world / kv_heads ranks which split the context range in equal parts and merge
+    their partial results (merge_attention_parts)."""
+    if world <= kv_heads:
+        s, e = head_range(kv_heads, rank, world)
+        return s, e, 0, 1
+    if world % kv_heads:
+        raise ValueError("more ranks than KV heads: the rank count must be a multiple of the KV heads")
+    parts = world // kv_heads
+    head = rank % kv_heads
+    return head, head + 1, rank // kv_heads, parts
+
+
+def context_range(start: int, end: int, part: int, parts: int) -> tuple[int, int]:
+    """Token range of context part `part` of [start, end)."""
+    n = end - start
+    return start + n * part // parts, start + n * (part + 1) // parts
+
+
+def merge_attention_parts(outs, lses):
+    """Merge attention results computed over disjoint token ranges of the same sequences.
+    outs: [parts, ..., head_dim], lses: [parts, ...] (log of each part's softmax denominator).
+    Returns the attention over the union, fp32.  Works on numpy arrays and torch tensors."""
+    if hasattr(outs, "detach"):
+        import torch
+        m = lses.max(dim=0, keepdim=True).values
+        m = torch.where(torch.isfinite(m), m, torch.zeros_like(m))
+        w = torch.exp(lses - m)
+        den = w.sum(dim=0)
+        num = (outs.float() * w.unsqueeze(-1)).sum(dim=0)
+        return num / den.clamp_min(1e-38).unsqueeze(-1)
+    import numpy as np
+    outs = np.asarray(outs, np.float32)
+    lses = np.asarray(lses, np.float32)
+    m = lses.max(axis=0, keepdims=True)
+    m = np.where(np.isfinite(m), m, 0.0)
+    w = np.exp(lses - m)
+    den = w.sum(axis=0)
+    num = (outs * w[..., None]).sum(axis=0)
+    return num / np.maximum(den, 1e-38)[..., None]
+
+
+def all_gather_attention_parts(out_local, lse_local, group=None):
+    """All-gather (out, lse) over the ranks that share a KV head and merge them."""
+    import torch
+    import torch.distributed as dist
+    world = dist.get_world_size(group)
+    outs = torch.empty((world,) + tuple(out_local.shape), dtype=out_local.dtype, device=out_local.device)
+    lses = torch.empty((world,) + tuple(lse_local.shape), dtype=lse_local.dtype, device=lse_local.device)
+    dist.all_gather_into_tensor(outs.view(world * out_local.shape[0], *out_local.shape[1:]), out_local.contiguous(), group=group)
+    dist.all_gather_into_tensor(lses.view(world * lse_local.shape[0], *lse_local.shape[1:]), lse_local.contiguous(), group=group)
+    return merge_attention_parts(outs, lses)
