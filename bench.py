@@ -419,6 +419,53 @@ def bench_attention(tq, L, device, stream, rank, world, args, ctx):
                          + ("> L2" if n_seqs * heads_local * ctx_local * 132 > 126e6 else "<= L2 (126 MB)")}
 
 
+# ---- secondary: prefill through the tensor-core GEMM (BASELINE config 1, prefill part) -------------
+
+def bench_prefill(tq, L, layers, device, stream, args):
+    """2048 activation rows through 4096x4096 TQ8 layers (distinct layers back to back, as in the
+    headline loop): fused dequantise + tcgen05 GEMM, activation rotation included."""
+    import torch
+    m = 2048
+    n_layers = min(len(layers), 8)
+    g = torch.Generator(device=device).manual_seed(900)
+    x = torch.randn((m, IN_F), generator=g, device=device).half()
+    y = torch.empty((m, OUT_F), device=device, dtype=torch.float16)
+    sp = C.c_void_p(stream.cuda_stream)
+
+    def call(lin):
+        rc = L.tq_linear_forward(lin.handle, C.c_void_p(x.data_ptr()), tq.TQ_F16, m, C.c_void_p(y.data_ptr()), sp)
+        if rc:
+            raise RuntimeError(L.tq_last_error().decode())
+
+    with torch.cuda.stream(stream):
+        for lin in layers[:n_layers]:
+            call(lin)
+    torch.cuda.synchronize()
+    reps = 5
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with torch.cuda.stream(stream):
+        e0.record(stream)
+        for _ in range(reps):
+            for lin in layers[:n_layers]:
+                call(lin)
+        e1.record(stream)
+    torch.cuda.synchronize()
+    if L.tq_linear_status(layers[0].handle):
+        raise RuntimeError(L.tq_last_error().decode())
+    us = e0.elapsed_time(e1) * 1e3 / (reps * n_layers)
+    flops = 2.0 * m * OUT_F * IN_F
+    peak = None
+    pth = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(pth):
+        peak = float(json.load(open(pth)).get("bf16_tflops", 0)) or None
+    peak_kind = "measured cuBLAS bf16 burst" if peak else "fallback"
+    peak = peak or 1590.0
+    tf = flops / (us * 1e-6) / 1e12
+    return {"workload": f"{m} activation rows x 4096x4096 TQ8 layer (rotation + fused dequant GEMM, fp16 in, fp32 accumulate)",
+            "us_per_layer": us, "tok_per_s": m / (us * 1e-6), "tflops": tf, "frac_of_tensor_peak": tf / peak,
+            "peak_tflops": peak, "peak_kind": peak_kind}
+
+
 # ---- secondary: decoder-layer projections at decode batch sizes (BASELINE config 1) ----------------
 
 def bench_decoder_layer(tq, L, device, stream, cbs, args):

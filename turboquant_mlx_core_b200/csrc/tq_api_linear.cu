@@ -47,7 +47,7 @@ public:
         DeviceBuffer stage_p, stage_r, flags(2 * sizeof(unsigned int));
         const uint8_t* d_pp = tq::device_view(packed_primary, static_cast<size_t>(out_) * primary_cols, stage_p, st);
         const uint8_t* d_pr = tq::device_view(packed_residual, n_w / 2, stage_r, st);
-        codes_.resize(n_w);
+        codes_.resize(tq::code_bytes(out_, in_));
         TQ_CUDA(cudaMemsetAsync(flags.as<void>(), 0, 2 * sizeof(unsigned int), st));
         tq::launch_relayout(d_pp, d_pr, codes_.as<uint8_t>(), out_, in_, primary_5bit_, flags.as<unsigned int>(), st);
         unsigned int h_flags[2];

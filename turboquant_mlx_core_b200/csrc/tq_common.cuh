@@ -92,4 +92,21 @@ __device__ __forceinline__ void warp_fwht(float (&v)[E], int lane) {
 
 __host__ __device__ __forceinline__ bool is_pow2(uint32_t v) { return v && !(v & (v - 1)); }
 
+// ---- layout of the weight codes in HBM ------------------------------------------------
+// One "joint" byte per weight, stored in tiles of 16 rows x 64 columns (1 KB, rows of a tile
+// contiguous, 64 bytes each); tiles are row-major over the matrix, and the matrix is padded with
+// zero bytes to whole tiles.  A warp of the decode kernel reads 16 rows x 16 bytes per load: in
+// this order that is 2 x 512 contiguous bytes instead of 16 pieces of 64; a row's 64 columns of
+// one tile stay contiguous for the row-wise readers (dequantiser, prefill GEMM).
+constexpr int kCodeTileRows = 16, kCodeTileCols = 64, kCodeTileBytes = kCodeTileRows * kCodeTileCols;
+__host__ __device__ __forceinline__ size_t code_tiles_per_row(int in) { return (static_cast<size_t>(in) + kCodeTileCols - 1) / kCodeTileCols; }
+__host__ __device__ __forceinline__ size_t code_bytes(long out, int in) {
+    return (static_cast<size_t>(out) + kCodeTileRows - 1) / kCodeTileRows * code_tiles_per_row(in) * kCodeTileBytes;
+}
+// Byte offset of (row, col); `tiles_per_row` = code_tiles_per_row(in).
+__host__ __device__ __forceinline__ size_t code_offset(long row, int col, size_t tiles_per_row) {
+    return ((static_cast<size_t>(row) >> 4) * tiles_per_row + (static_cast<size_t>(col) >> 6)) * kCodeTileBytes +
+           (static_cast<size_t>(row) & 15) * kCodeTileCols + (static_cast<size_t>(col) & 63);
+}
+
 }  // namespace tq

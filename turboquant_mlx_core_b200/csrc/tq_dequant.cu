@@ -19,8 +19,9 @@ namespace tq {
 // 5-bit primary: one primary code per byte, residual still nibble-packed (3-bit codes);
 // joint = p | r << 5.
 __global__ void relayout_kernel(const uint8_t* __restrict__ pp, const uint8_t* __restrict__ pr,
-                                uint8_t* __restrict__ joint, long n_pairs, int primary_5bit,
+                                uint8_t* __restrict__ joint, long n_pairs, int pairs_per_row, int primary_5bit,
                                 unsigned int* __restrict__ flags) {
+    const size_t tpr = code_tiles_per_row(2 * pairs_per_row);
     unsigned int any_res = 0, bad = 0;
     for (long i = static_cast<long>(blockIdx.x) * blockDim.x + threadIdx.x; i < n_pairs;
          i += static_cast<long>(gridDim.x) * blockDim.x) {
@@ -38,7 +39,10 @@ __global__ void relayout_kernel(const uint8_t* __restrict__ pp, const uint8_t* _
             j0 = (p0 & 0x1Fu) | ((r & 0x07u) << 5);
             j1 = (p1 & 0x1Fu) | (((r >> 4) & 0x07u) << 5);
         }
-        reinterpret_cast<uchar2*>(joint)[i] = make_uchar2(static_cast<unsigned char>(j0), static_cast<unsigned char>(j1));
+        const long row = i / pairs_per_row;
+        const int col = 2 * static_cast<int>(i - row * pairs_per_row);
+        *reinterpret_cast<uchar2*>(joint + code_offset(row, col, tpr)) =
+            make_uchar2(static_cast<unsigned char>(j0), static_cast<unsigned char>(j1));
     }
     if (__any_sync(0xffffffffu, any_res != 0) && (threadIdx.x & 31) == 0) atomicOr(&flags[0], 1u);
     if (__any_sync(0xffffffffu, bad != 0) && (threadIdx.x & 31) == 0) atomicOr(&flags[1], 1u);
@@ -50,17 +54,22 @@ void launch_relayout(const uint8_t* packed_primary, const uint8_t* packed_residu
     if (n_pairs == 0) return;
     long want = (n_pairs + 255) / 256;
     int grid = static_cast<int>(want < 148L * 16 ? want : 148L * 16);
-    relayout_kernel<<<grid, 256, 0, stream>>>(packed_primary, packed_residual, joint, n_pairs, primary_5bit ? 1 : 0, flags);
+    // padding bytes of the tiled layout read as code 0
+    TQ_CUDA(cudaMemsetAsync(joint, 0, code_bytes(out, in), stream));
+    relayout_kernel<<<grid, 256, 0, stream>>>(packed_primary, packed_residual, joint, n_pairs, in / 2, primary_5bit ? 1 : 0, flags);
     TQ_CUDA(cudaGetLastError());
 }
 
 // Inverse of relayout (joint bytes -> the reference's two planes), used when a handle
 // built on this device has to hand its codes back in the reference's format.
 __global__ void unrelayout_kernel(const uint8_t* __restrict__ joint, uint8_t* __restrict__ pp,
-                                  uint8_t* __restrict__ pr, long n_pairs, int primary_5bit) {
+                                  uint8_t* __restrict__ pr, long n_pairs, int pairs_per_row, int primary_5bit) {
+    const size_t tpr = code_tiles_per_row(2 * pairs_per_row);
     for (long i = static_cast<long>(blockIdx.x) * blockDim.x + threadIdx.x; i < n_pairs;
          i += static_cast<long>(gridDim.x) * blockDim.x) {
-        const uchar2 j = reinterpret_cast<const uchar2*>(joint)[i];
+        const long row = i / pairs_per_row;
+        const int col = 2 * static_cast<int>(i - row * pairs_per_row);
+        const uchar2 j = *reinterpret_cast<const uchar2*>(joint + code_offset(row, col, tpr));
         if (!primary_5bit) {
             pp[i] = static_cast<uint8_t>((j.x & 0x0F) | ((j.y & 0x0F) << 4));
             pr[i] = static_cast<uint8_t>((j.x >> 4) | (j.y & 0xF0));
@@ -78,7 +87,7 @@ void launch_unrelayout(const uint8_t* joint, uint8_t* packed_primary, uint8_t* p
     if (n_pairs == 0) return;
     long want = (n_pairs + 255) / 256;
     int grid = static_cast<int>(want < 148L * 16 ? want : 148L * 16);
-    unrelayout_kernel<<<grid, 256, 0, stream>>>(joint, packed_primary, packed_residual, n_pairs, primary_5bit ? 1 : 0);
+    unrelayout_kernel<<<grid, 256, 0, stream>>>(joint, packed_primary, packed_residual, n_pairs, in / 2, primary_5bit ? 1 : 0);
     TQ_CUDA(cudaGetLastError());
 }
 
@@ -112,7 +121,8 @@ __global__ void __launch_bounds__(256) dequant_kernel(const uint8_t* __restrict_
 
     for (long blk = warp0; blk < total; blk += n_warps) {
         const long row = blk / blocks_per_row;
-        const uint8_t* src = joint + blk * BS + lane * E;
+        const int col = static_cast<int>(blk - row * blocks_per_row) * BS + lane * E;
+        const uint8_t* src = joint + code_offset(row, col, code_tiles_per_row(blocks_per_row * BS));
         uint8_t code[E];
         if constexpr (E >= 16) {
 #pragma unroll

@@ -193,7 +193,7 @@ __global__ void __launch_bounds__(128) rotate_rows_f16_kernel(const __half* __re
 }
 
 struct GemmArgs {
-    const uint8_t* codes;   // [out, in] joint bytes
+    const uint8_t* codes;   // joint bytes in 16 x 64 tiles (code_offset)
     const float* norms;     // [out]
     const float* table;     // [n_planes, 256] fp32
     const __half* xrot;     // rotated activation in operand-tile order (see rotate_rows_f16_kernel)
@@ -296,7 +296,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1) tq8_gemm_kernel(const GemmArg
         const int ar = 32 * (warp & 3) + lane;       // row inside the tile
         const int ah = warp >> 2;                    // which 32 columns of the K block
         const int grow = min(row0 + ar, p.out - 1);  // rows past the matrix repeat the last row (never stored)
-        const uint8_t* code_ptr = p.codes + static_cast<size_t>(grow) * p.in + 32 * ah;
+        // a row's 64 columns of K block kb are 64 contiguous bytes of code tile (row / 16, kb)
+        const uint8_t* code_ptr = p.codes + code_offset(grow, 32 * ah, code_tiles_per_row(p.in));
         const uint32_t a_taddr = tmem_d + (static_cast<uint32_t>(32 * (warp & 3)) << 16) + kTmemAColumn + 16u * ah;
         const uint32_t lut_lane = lut_addr + static_cast<uint32_t>(lane) * 4u;
 
@@ -306,7 +307,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) tq8_gemm_kernel(const GemmArg
         auto load_codes = [&](int kb, uint4& lo, uint4& hi) {
             if (kb < n_kb) {
                 const int plane = (kb_base + kb) >= kb_per_plane ? 1 : 0;
-                const uint8_t* src = code_ptr + (kb_base + kb - plane * kb_per_plane) * kBlockK;
+                const uint8_t* src = code_ptr + static_cast<size_t>(kb_base + kb - plane * kb_per_plane) * kCodeTileBytes;
                 lo = __ldg(reinterpret_cast<const uint4*>(src));
                 hi = __ldg(reinterpret_cast<const uint4*>(src + 16));
             }

@@ -125,7 +125,7 @@ __global__ void __launch_bounds__(128) rotate_x_kernel(const __half* __restrict_
 }
 
 struct GemvArgs {
-    const uint8_t* codes;   // [out, in] joint bytes
+    const uint8_t* codes;   // joint bytes in 16 x 64 tiles (code_offset)
     const float* norms;     // [out]
     const float* table;     // [n_planes, 256] fp32
     const float* xrot;      // [n_planes, batch, in] fp32 (TF32-rounded); used when x == nullptr
@@ -253,26 +253,29 @@ __global__ void __launch_bounds__(kCtaThreads, 1) tq8_gemv_kernel(const GemvArgs
     const int tile_in_unit = warp / p.wpt;                      // which of the unit's row tiles this warp works on
     const int slice0 = (warp - tile_in_unit * p.wpt) * kSlice;  // column of this warp's slice inside the chunk
     const uint32_t lane_const = 0x00010000u | static_cast<uint32_t>(lane * 4);
-    const size_t unit_stride = static_cast<size_t>(p.tpu) * 16 * p.in;  // bytes between consecutive row units
-    const size_t row8 = 8 * static_cast<size_t>(p.in);
+    // Codes are stored in 16-row x 64-column tiles of 1 KB (code_offset): a step of a warp is one
+    // tile, of which lane (g, q) reads bytes g*64 + 16q (row g) and 512 + g*64 + 16q (row g + 8) -
+    // 512 contiguous bytes per warp load.  Consecutive steps are consecutive tiles.
+    const size_t tiles_per_row = code_tiles_per_row(p.in);
+    const size_t unit_stride = static_cast<size_t>(p.tpu) * tiles_per_row * kCodeTileBytes;  // bytes between consecutive row units
 
     // ---- position of a unit, kept incrementally (no divisions in the loop) ----
     struct Pos {
         int slot, ru;          // slot and row unit
         const uint8_t* ptr;    // this thread's first 16 codes of the unit (row g)
-        uint32_t ok;           // bit s: columns of step s valid; bit 4: row g valid; bit 5: row g+8 valid
+        uint32_t ok;           // bit s: columns of step s exist; bits 4, 5: the row tile exists (padded rows are stored)
     };
     auto make_pos = [&](int unit) {
         Pos u;
         u.slot = unit / p.n_row_units;
         u.ru = unit - u.slot * p.n_row_units;
-        const int c = (u.slot % p.n_chunks) * kChunk + slice0 + 16 * q;
-        const int r0 = (u.ru * p.tpu + tile_in_unit) * 16 + g;
-        u.ptr = p.codes + static_cast<size_t>(r0) * p.in + c;
+        const int c = (u.slot % p.n_chunks) * kChunk + slice0;  // first column of this warp's slice
+        const int tile = u.ru * p.tpu + tile_in_unit;
+        u.ptr = p.codes + (static_cast<size_t>(tile) * tiles_per_row + static_cast<size_t>(c >> 6)) * kCodeTileBytes + g * 64 + 16 * q;
         u.ok = 0;
 #pragma unroll
         for (int s = 0; s < 4; ++s) u.ok |= (c + 64 * s < p.in) ? (1u << s) : 0u;
-        u.ok |= (r0 < p.out ? 16u : 0u) | (r0 + 8 < p.out ? 32u : 0u);
+        u.ok |= (tile * 16 < p.out) ? 48u : 0u;
         return u;
     };
     auto next_pos = [&](const Pos& u) {
@@ -280,8 +283,7 @@ __global__ void __launch_bounds__(kCtaThreads, 1) tq8_gemv_kernel(const GemvArgs
         if (u.ru + 1 < p.n_row_units) {   // same slot, next row unit: only the rows move
             n.ru = u.ru + 1;
             n.ptr = u.ptr + unit_stride;
-            const int r0 = (n.ru * p.tpu + tile_in_unit) * 16 + g;
-            n.ok = (u.ok & 15u) | (r0 < p.out ? 16u : 0u) | (r0 + 8 < p.out ? 32u : 0u);
+            n.ok = (u.ok & 15u) | (((n.ru * p.tpu + tile_in_unit) * 16 < p.out) ? 48u : 0u);
             return n;
         }
         return make_pos((u.slot + 1) * p.n_row_units);
@@ -290,14 +292,14 @@ __global__ void __launch_bounds__(kCtaThreads, 1) tq8_gemv_kernel(const GemvArgs
     // dependency wait below.  Pieces outside the matrix are simply not loaded.
     auto load_step = [&](const Pos& u, int s, bool live, uint4& lo, uint4& hi) {
         const bool c_ok = live && ((u.ok >> s) & 1u);
-        ldg_stream_if(lo, u.ptr + 64 * s, c_ok && (u.ok & 16u));
-        ldg_stream_if(hi, u.ptr + 64 * s + row8, c_ok && (u.ok & 32u));
+        ldg_stream_if(lo, u.ptr + kCodeTileBytes * s, c_ok && (u.ok & 16u));
+        ldg_stream_if(hi, u.ptr + kCodeTileBytes * s + 512, c_ok && (u.ok & 32u));
     };
     Pos cur = make_pos(u_begin);
     Pos nxt = (n_local > 1) ? next_pos(cur) : cur;
     // Two register buffers (even / odd step): two steps, 32 KB per SM, in flight.  Four buffers
     // were measured and bought nothing: the kernel is bound by L1 data-pipe wavefronts (table
-    // lookups plus the 64-byte-granular code loads), not by the depth of the load queue.
+    // lookups plus the code loads), not by the depth of the load queue.
     uint4 blo[2], bhi[2];
 #pragma unroll
     for (int s = 0; s < 2; ++s) {

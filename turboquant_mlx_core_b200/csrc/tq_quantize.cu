@@ -25,31 +25,33 @@ namespace tq {
 namespace {
 
 // sum_j m[r][j]^2, accumulated strictly left to right in fp32; out[r] = sqrt(sum).
-// A warp owns 32 rows: it stages 32x32 tiles through shared memory (coalesced reads)
-// and lane l then walks row l of the tile in order.
-__global__ void __launch_bounds__(128) row_norm_seq_kernel(const float* __restrict__ m, float* __restrict__ out,
+// One warp per row: lanes read 32 consecutive columns (coalesced, four such pieces in flight) and
+// square them; the running sum then takes the 32 squares in column order through lane
+// broadcasts, every lane carrying the same sum.  Columns past the end contribute +0.0, which
+// leaves a non-negative sum unchanged.  All rows run at once, so the matrix streams from HBM
+// while each row's add chain (the order that makes the result bit-exact) stays serial.
+__global__ void __launch_bounds__(256) row_norm_seq_kernel(const float* __restrict__ m, float* __restrict__ out,
                                                            long rows, int cols) {
-    __shared__ float tile[4][32][33];
-    const int lane = threadIdx.x & 31, wib = threadIdx.x >> 5;
-    const long row0 = (static_cast<long>(blockIdx.x) * 4 + wib) * 32;
-    if (row0 >= rows) return;
+    const int lane = threadIdx.x & 31;
+    const long row = (static_cast<long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+    if (row >= rows) return;
+    const float* src = m + row * cols;
     float acc = 0.0f;
-    for (int c0 = 0; c0 < cols; c0 += 32) {
-        const int c = c0 + lane;
-#pragma unroll 4
-        for (int i = 0; i < 32; ++i) {
-            const long r = row0 + i;
-            tile[wib][i][lane] = (r < rows && c < cols) ? m[r * cols + c] : 0.0f;
+    for (int c0 = 0; c0 < cols; c0 += 128) {
+        float sq[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const int c = c0 + 32 * u + lane;
+            const float v = c < cols ? __ldg(src + c) : 0.0f;
+            sq[u] = __fmul_rn(v, v);
         }
-        __syncwarp();
-        const int n = min(32, cols - c0);
-        for (int j = 0; j < n; ++j) {
-            const float v = tile[wib][lane][j];
-            acc = __fadd_rn(acc, __fmul_rn(v, v));
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) acc = __fadd_rn(acc, __shfl_sync(0xffffffffu, sq[u], j));
         }
-        __syncwarp();
     }
-    if (row0 + lane < rows) out[row0 + lane] = __fsqrt_rn(acc);
+    if (lane == 0) out[row] = __fsqrt_rn(acc);
 }
 
 __global__ void corrected_norm_kernel(const float* __restrict__ orig, float* __restrict__ recon_inout, long rows) {
@@ -243,8 +245,8 @@ void launch_quantize_weight(const float* d_weight, long out, int in, const float
     const int bpr = in / static_cast<int>(block);
     const long total = out * bpr;
 
-    const int norm_grid = static_cast<int>((out + 127) / 128);
-    row_norm_seq_kernel<<<norm_grid, 128, 0, stream>>>(d_weight, d_orig_norm_tmp, out, in);
+    const int norm_grid = static_cast<int>((out + 7) / 8);  // 8 warps (rows) per CTA
+    row_norm_seq_kernel<<<norm_grid, 256, 0, stream>>>(d_weight, d_orig_norm_tmp, out, in);
     TQ_CUDA(cudaGetLastError());
     if (residual_bits == 0) TQ_CUDA(cudaMemsetAsync(d_packed_residual, 0, static_cast<size_t>(out) * (in / 2), stream));
     long want = (total + 3) / 4;
@@ -262,7 +264,7 @@ void launch_quantize_weight(const float* d_weight, long out, int in, const float
     }
 #undef TQ_Q_CASE
     TQ_CUDA(cudaGetLastError());
-    row_norm_seq_kernel<<<norm_grid, 128, 0, stream>>>(d_recon_tmp, d_norms, out, in);
+    row_norm_seq_kernel<<<norm_grid, 256, 0, stream>>>(d_recon_tmp, d_norms, out, in);
     TQ_CUDA(cudaGetLastError());
     corrected_norm_kernel<<<static_cast<int>((out + 255) / 256), 256, 0, stream>>>(d_orig_norm_tmp, d_norms, out);
     TQ_CUDA(cudaGetLastError());
