@@ -309,7 +309,10 @@ def run_cuda(args):
 
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         line["cpu_baseline"] = cpu_baseline(qw0, cbs, x_host[0].numpy(), y_dev[0].cpu().numpy(), budget_s=12.0)
-    if not args.no_extras:
+    legs = set(args.legs.split(",")) if args.legs else {"attention", "decoder_layer", "prefill", "lm_head"}
+    if args.no_extras:
+        legs = set()
+    if "attention" in legs:
         try:
             line["attention"] = bench_attention(tq, L, device, stream, rank, world, args, args.attn_ctx)
             if world == 1 and args.attn_ctx == 32768:
@@ -317,15 +320,17 @@ def run_cuda(args):
                 line["attention_ctx128k"] = bench_attention(tq, L, device, stream, rank, world, args, 131072)
         except Exception as e:  # secondary measurement: report, do not hide the headline
             line["attention"] = {"error": str(e)}
-        if world == 1:
-            try:
-                line["decoder_layer"] = bench_decoder_layer(tq, L, device, stream, cbs, args)
-            except Exception as e:
-                line["decoder_layer"] = {"error": str(e)}
+    if "decoder_layer" in legs and world == 1:
+        try:
+            line["decoder_layer"] = bench_decoder_layer(tq, L, device, stream, cbs, args)
+        except Exception as e:
+            line["decoder_layer"] = {"error": str(e)}
+    if "prefill" in legs:
         try:
             line["prefill"] = bench_prefill(tq, L, layers, device, stream, args)
         except Exception as e:
             line["prefill"] = {"error": str(e)}
+    if "lm_head" in legs:
         try:
             line["lm_head"] = bench_lm_head(tq, L, device, stream, rank, world, cbs, args)
         except Exception as e:
@@ -667,7 +672,9 @@ def main():
     ap.add_argument("--impl", default="cuda", choices=["cuda", "reference"])
     ap.add_argument("--nbuf", type=int, default=64, help="distinct 4096x4096 layers per step")
     ap.add_argument("--attn-ctx", type=int, default=32768)
-    ap.add_argument("--no-extras", action="store_true", help="skip the attention and LM-head measurements")
+    ap.add_argument("--no-extras", action="store_true", help="skip the secondary measurements")
+    ap.add_argument("--legs", default="", help="comma list of secondary measurements to run "
+                                               "(attention, decoder_layer, prefill, lm_head); default all")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-graph", action="store_true", help="time plain stream launches instead of a CUDA graph")
     a = ap.parse_args()

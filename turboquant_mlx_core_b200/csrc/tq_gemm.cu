@@ -192,6 +192,68 @@ __global__ void __launch_bounds__(128) rotate_rows_f16_kernel(const __half* __re
     }
 }
 
+// The same for WHT blocks of up to 256 columns, with 16-byte accesses: a warp takes 256 columns
+// of one row, lane l the 8 columns 8l..8l+7 (one core-matrix row of the output tile); butterfly
+// stages below 8 stay in the lane, the rest are lane exchanges (the add tree of warp_fwht).  The
+// 8 warps of a CTA take 8 consecutive rows, so their stores complete whole 128-byte core matrices.
+__global__ void __launch_bounds__(256) rotate_rows_f16_wide_kernel(const __half* __restrict__ x, __half* __restrict__ xrot,
+                                                                   int in, long rows, int n_planes, int block,
+                                                                   uint32_t seed_p, uint32_t seed_r, float inv_sqrt) {
+    const int lane = threadIdx.x & 31, wib = threadIdx.x >> 5;
+    const long groups_per_row = (in + 255) / 256;
+    const long row_groups = (rows + 7) / 8;
+    // blockIdx.x -> (plane, column group, group of 8 rows); warp -> row inside the group
+    long b = blockIdx.x;
+    const long rg = b % row_groups;
+    b /= row_groups;
+    const long cg = b % groups_per_row;
+    const int plane = static_cast<int>(b / groups_per_row);
+    if (plane >= n_planes) return;
+    const long row = rg * 8 + wib;
+    const int col = static_cast<int>(cg) * 256 + 8 * lane;
+    if (row >= rows || col >= in) return;  // in is a multiple of 32 >= block: whole lanes only; exchanges stay inside a block
+    const uint32_t seed = plane ? seed_r : seed_p;
+    const uint4 raw = __ldg(reinterpret_cast<const uint4*>(x + row * in + col));
+    const uint32_t xw[4] = {raw.x, raw.y, raw.z, raw.w};
+    float v[8];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        const __half2 h2 = *reinterpret_cast<const __half2*>(&xw[j]);
+        v[2 * j] = __low2float(h2) * sign_value(seed, static_cast<uint32_t>((col + 2 * j) & (block - 1)));
+        v[2 * j + 1] = __high2float(h2) * sign_value(seed, static_cast<uint32_t>((col + 2 * j + 1) & (block - 1)));
+    }
+#pragma unroll
+    for (int h = 1; h < 8; h <<= 1)
+#pragma unroll
+        for (int i = 0; i < 8; i += 2 * h)
+#pragma unroll
+            for (int j = i; j < i + h; ++j) {
+                const float a0 = v[j], b0 = v[j + h];
+                v[j] = __fadd_rn(a0, b0);
+                v[j + h] = __fsub_rn(a0, b0);
+            }
+    // lanes of an incomplete trailing group (in % 256 != 0) have returned: exchange only among the live ones
+    const unsigned live = __activemask();
+    for (int m = 1; m < (block >> 3); m <<= 1) {
+        const bool upper = (lane & m) != 0;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const float o = __shfl_xor_sync(live, v[j], m);
+            v[j] = upper ? __fsub_rn(o, v[j]) : __fadd_rn(v[j], o);
+        }
+    }
+    const long n_row_tiles = (rows + kTileTok - 1) / kTileTok;
+    const long kb_per_plane = in / kBlockK;
+    const long rt = row / kTileTok, rin = row - rt * kTileTok;
+    const long kb = col / kBlockK, cin = col - kb * kBlockK;
+    const long tile = (static_cast<long>(plane) * n_row_tiles + rt) * kb_per_plane + kb;
+    __half* dst = xrot + tile * (kTileTok * kBlockK) + (((rin >> 3) * 8 + (cin >> 3)) * 8 + (rin & 7)) * 8;
+    __align__(16) __half hv[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) hv[j] = __float2half_rn(v[j] * inv_sqrt);
+    *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<const uint4*>(hv);
+}
+
 struct GemmArgs {
     const uint8_t* codes;   // joint bytes in 16 x 64 tiles (code_offset)
     const float* norms;     // [out]
@@ -505,6 +567,11 @@ void launch_tq8_gemm(const uint8_t* codes, const float* norms, const float* tabl
         const float inv_sqrt = 1.0f / std::sqrt(static_cast<float>(block));
         const long n_warps = static_cast<long>(n_planes) * m * (in / static_cast<int>(block));
         const unsigned int grid = static_cast<unsigned int>((n_warps + 3) / 4);
+        const long wide_blocks = static_cast<long>(n_planes) * ((in + 255) / 256) * ((m + 7) / 8);
+        if (block <= 256 && reinterpret_cast<uintptr_t>(x) % 16 == 0 && wide_blocks < (1L << 31)) {
+            rotate_rows_f16_wide_kernel<<<static_cast<unsigned int>(wide_blocks), 256, 0, stream>>>(
+                x, xrot, in, m, n_planes, static_cast<int>(block), seed_p, seed_r, inv_sqrt);
+        } else
 #define TQ_ROT16_CASE(EV)                                                                                          \
     case 32 * EV:                                                                                                  \
         rotate_rows_f16_kernel<EV><<<grid, 128, 0, stream>>>(x, xrot, in, m, n_planes, seed_p, seed_r, inv_sqrt);  \
