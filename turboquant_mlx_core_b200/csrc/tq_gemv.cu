@@ -62,7 +62,7 @@ constexpr int kSlice = 256;               // columns per warp
 constexpr int kChunk = kWarps * kSlice;   // columns per unit
 constexpr uint32_t kLutAddr = 0x10000u;   // shared-window address of the table
 constexpr uint32_t kLutBytes = 0x10000u;  // 256 entries * 256 B
-constexpr int kRedBytes = 16384;           // partial-sum ring: ring * 16 warps * 16 rows * bp floats
+constexpr int kRedBytes = 32768;           // partial-sum ring: ring * 16 warps * (16 rows * bp + 4) floats
 constexpr int kMaxRing = 16;
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
@@ -212,9 +212,13 @@ __device__ __forceinline__ void mma_tf32(float (&c)[4], uint32_t a0, uint32_t a1
 // geometry and the reduction need no runtime arithmetic).
 template <int BP>
 __global__ void __launch_bounds__(kCtaThreads, 1) tq8_gemv_kernel(const GemvArgs p) {
-    constexpr int kRing = (kRedBytes / (kWarps * 16 * BP * 4)) > kMaxRing ? kMaxRing : (kRedBytes / (kWarps * 16 * BP * 4));
+    // A warp's partial tile is [16 rows][BP] floats plus 4 floats of padding: the 16 tiles a
+    // reduction reads side by side then start 4 banks apart instead of in the same bank.
+    constexpr int kTileFloats = 16 * BP + 4;
+    constexpr int kRing = (kRedBytes / (kWarps * kTileFloats * 4)) > kMaxRing ? kMaxRing : (kRedBytes / (kWarps * kTileFloats * 4));
+    static_assert(kRing >= 2, "the ring needs a slot to write while another is summed");
     constexpr int kLag = kRing / 2;                       // how many units behind the sums run
-    constexpr uint32_t kSlotBytes = kWarps * 16 * BP * 4;  // one ring slot: [warp][16 rows][BP] floats
+    constexpr uint32_t kSlotBytes = kWarps * kTileFloats * 4;  // one ring slot: [warp][16 rows][BP] floats (+ padding)
     constexpr int kPer = BP >= 2 ? BP / 2 : 1;            // floats a lane adds in the reduction
 
     extern __shared__ __align__(128) uint8_t smem_raw[];
@@ -340,7 +344,7 @@ __global__ void __launch_bounds__(kCtaThreads, 1) tq8_gemv_kernel(const GemvArgs
     __syncthreads();  // table and barriers visible
 
     // ---- sum of one unit's per-warp partial tiles ----
-    // Ring slot layout: [warp][16 rows][BP] floats.  Warp w owns the (tile, row) pairs
+    // Ring slot layout: [warp][16 rows][BP] floats (+ 4 floats of padding per warp).  Warp w owns the (tile, row) pairs
     // w*tpu .. w*tpu+tpu-1 of the unit; lane l reads what warp (l & 15) of that row tile's
     // group wrote, activation columns (l >> 4) * kPer .., and a fixed shuffle tree adds the
     // 16 (fixed order: results do not depend on timing).
@@ -364,7 +368,7 @@ __global__ void __launch_bounds__(kCtaThreads, 1) tq8_gemv_kernel(const GemvArgs
             for (int k = 0; k < kPer; ++k) v[k] = 0.f;
             if (red_active) {
                 const uint32_t src = red_addr + static_cast<uint32_t>(rs) * kSlotBytes +
-                                     static_cast<uint32_t>(((t * p.wpt + pw) * 16 + r) * BP + n0) * 4u;
+                                     static_cast<uint32_t>((t * p.wpt + pw) * kTileFloats + r * BP + n0) * 4u;
                 if constexpr (kPer == 4) asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v[0]), "=f"(v[1]), "=f"(v[2]), "=f"(v[3]) : "r"(src));
                 else if constexpr (kPer == 2) asm volatile("ld.shared.v2.f32 {%0, %1}, [%2];" : "=f"(v[0]), "=f"(v[1]) : "r"(src));
                 else asm volatile("ld.shared.f32 %0, [%1];" : "=f"(v[0]) : "r"(src));
@@ -584,7 +588,7 @@ __global__ void __launch_bounds__(kCtaThreads, 1) tq8_gemv_kernel(const GemvArgs
         }
         {
             // C fragment: (row g, columns 2q, 2q+1) and (row g+8, same columns)
-            const uint32_t dst = red_addr + static_cast<uint32_t>(ws) * kSlotBytes + static_cast<uint32_t>(warp * 16 * BP) * 4u;
+            const uint32_t dst = red_addr + static_cast<uint32_t>(ws) * kSlotBytes + static_cast<uint32_t>(warp * kTileFloats) * 4u;
             const int n = 2 * q;
             if (n < BP) {
                 sts_f32(dst + static_cast<uint32_t>(g * BP + n) * 4u, acc0[0] + acc1[0]);
