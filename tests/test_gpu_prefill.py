@@ -68,3 +68,27 @@ def test_prefill_falls_back_when_k_is_not_a_multiple_of_64(tq, oracle):
     y = lin.forward(x)
     assert rel_l2(y, oracle.linear_from_dequant(deq, x.astype(np.float32))) < LINEAR_TOL
     lin.close()
+
+
+def test_prefill_device_tensors_and_status(tq, oracle):
+    """Device-resident x and y on a side stream (no host round trip), then the status query."""
+    import torch
+    rng = np.random.default_rng(5)
+    cb = oracle.codebook(4)[0]
+    rows, cols, m = 256, 1024, 384
+    w = (rng.standard_normal((rows, cols)) * 0.02).astype(np.float16).astype(np.float32)
+    pp, pr, norms, seeds = oracle.quantize_weight(w, cb, cb, 4, 4, 128, True)
+    deq = oracle.dequantize_weight(pp, pr, norms, seeds, cb, cb, 128)
+    lin = tq.TurboQuantLinear(cols, rows, tq.QuantizedWeight(pp, pr, norms, seeds), tq.codebook_from_centroids(cb),
+                              tq.codebook_from_centroids(cb), 128)
+    xh = rng.standard_normal((m, cols)).astype(np.float16)
+    x = torch.from_numpy(xh).cuda()
+    y = torch.empty((m, rows), dtype=torch.float16, device="cuda")
+    st = torch.cuda.Stream()
+    with torch.cuda.stream(st):
+        lin.forward(x, out=y, stream=st)
+        lin.forward(x, out=y, stream=st)      # scratch reuse on the second call
+    st.synchronize()
+    lin.check_status()
+    assert rel_l2(y.cpu().numpy(), oracle.linear_from_dequant(deq, xh.astype(np.float32))) < LINEAR_TOL
+    lin.close()

@@ -208,6 +208,11 @@ class TurboQuantLinear:
         check(self._L.tq_linear_dequantize(self._h, _ptr(out), _dtype_tag(out), _stream_ptr(stream)), "dequantize")
         return out
 
+    def check_status(self):
+        """Waits for the device and raises if any kernel launched through this layer refused to
+        run or gave up on a bounded wait (calls with host output check this themselves)."""
+        check(self._L.tq_linear_status(self._h), "TurboQuantLinear.check_status")
+
     def close(self):
         if getattr(self, "_h", None):
             self._L.tq_linear_free(self._h)
