@@ -567,6 +567,49 @@ def bench_lm_head(tq, L, device, stream, rank, world, cbs, args):
         us = float(t.item())
         algo = vocab * hidden + 4 * vocab + 2 * batch * hidden + 2 * batch * vocab
         res[f"b{batch}"] = {"us": us, "tok_per_s": batch / (us * 1e-6), "gb_per_s_aggregate": algo / (us * 1e-6) / 1e9}
+    if world > 1:
+        # the same without the all-gather: the GEMV's epilogue stores every logit into every
+        # rank's buffer over NVLink (peer-mapped memory, plain stores); one tiny all-reduce is the
+        # barrier after which each rank may read the full logits
+        from turboquant_mlx_core_b200.sharding import SharedBuffer
+        try:
+            shared = SharedBuffer(8 * vocab * 2)
+            logits = shared.tensor((8, vocab), torch.float16)
+            flag = torch.zeros(1, device=device)
+            x = torch.randn((1, hidden), generator=g, device=device).half()
+            y_ref = torch.empty((1, rows), device=device, dtype=torch.float16)
+
+            def call_scatter():
+                lin.forward_scatter(x, shared.ptrs, vocab, s, stream=stream)
+                dist.all_reduce(flag)
+
+            with torch.cuda.stream(stream):
+                for _ in range(3):
+                    call_scatter()
+                rc = L.tq_linear_forward(lin.handle, C.c_void_p(x.data_ptr()), tq.TQ_F16, 1, C.c_void_p(y_ref.data_ptr()), sp)
+                full = all_gather_rows(y_ref, vocab, world)
+            torch.cuda.synchronize()
+            dist.barrier()
+            same = bool(torch.equal(full[0], logits[0]))
+            reps = 20
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            with torch.cuda.stream(stream):
+                e0.record(stream)
+                for _ in range(reps):
+                    call_scatter()
+                e1.record(stream)
+            torch.cuda.synchronize()
+            t = torch.tensor([e0.elapsed_time(e1) * 1e3 / reps], device=device, dtype=torch.float64)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            us = float(t.item())
+            same_t = torch.tensor([1.0 if same else 0.0], device=device)
+            dist.all_reduce(same_t, op=dist.ReduceOp.MIN)
+            res["b1_scatter"] = {"us": us, "tok_per_s": 1 / (us * 1e-6),
+                                 "path": "tq_linear_forward_scatter (peer stores from the GEMV epilogue) + 1-element all-reduce as barrier",
+                                 "identical_to_all_gather_on_every_rank": bool(same_t.item() == 1.0)}
+            shared.close()
+        except Exception as e:
+            res["b1_scatter"] = {"error": str(e)}
     lin.close()
     res["workload"] = f"config 2: LM head {vocab}x{hidden}, rows sharded over {world} GPU(s), fp16 logits all-gather"
     return res

@@ -150,6 +150,27 @@ size_t tq_linear_noalloc_scratch_limit(void);
  *  (the same values rounded to nearest even, src/turboquant_c_dequant.cpp:156-167). */
 int tq_linear_dequantize(tq_linear_t lin, void* result, int result_dtype, void* stream);
 
+/** Decode forward (x: DEVICE fp16 [batch, in], batch 1..8) whose result is written to n_dst
+ *  (1..8) buffers at once: destination d receives output row r of activation row n at
+ *  dst[d][n * dst_row_stride + row_offset + r] (fp16).  For a layer whose rows are sharded over
+ *  GPUs (an LM head), dst holds the same logits buffer of every rank (the local one and the
+ *  peers' mapped with tq_shared_open), dst_row_stride = vocabulary size, row_offset = this rank's
+ *  first row: the kernel's epilogue stores each value into every rank's buffer over NVLink and no
+ *  all-gather follows, only a barrier among the ranks before the logits are read.  Plain peer
+ *  stores: no multicast, and the kernel waits on nobody.  No counterpart in the reference. */
+int tq_linear_forward_scatter(tq_linear_t lin, const void* x_fp16_device, int batch, void* const* dst, int n_dst,
+                              long dst_row_stride, long row_offset, void* stream);
+
+/** Device memory that other processes on the same machine can map: tq_shared_alloc (cudaMalloc,
+ *  zero-filled) on the owner, tq_shared_export writes a 64-byte handle to send to the peers
+ *  (any channel), tq_shared_open maps it there (CUDA IPC with lazy peer access; the pointer is
+ *  valid on the opener's current device), tq_shared_close unmaps, tq_shared_free releases. */
+void* tq_shared_alloc(size_t bytes);
+void tq_shared_free(void* ptr);
+int tq_shared_export(void* ptr, void* handle_out, size_t handle_bytes);
+void* tq_shared_open(const void* handle, size_t handle_bytes);
+int tq_shared_close(void* peer_ptr);
+
 /** Waits for the device, then returns 0 if every kernel launched through this handle ran to
  *  completion, non-zero (see tq_last_error) if one refused to run or gave up on a bounded wait.
  *  Calls with host output check this themselves; callers that pass device pointers and

@@ -167,3 +167,39 @@ def test_zero_row_and_all_zero_residual(tq, oracle):
     assert bits_equal(qw.packed_primary, pp) and bits_equal(qw.packed_residual, pr) and bits_equal(qw.norms, norms)
     got = tq.dequantize_weight(qw, c, c, 128)
     assert bits_equal(got, deq) and np.all(got[3] == 0)
+
+
+def test_forward_scatter_writes_every_destination(tq, oracle):
+    """tq_linear_forward_scatter with two local destinations (what a row-sharded LM head does
+    with peer-mapped buffers): both receive exactly forward()'s values at the row offset, and
+    nothing outside that window is touched."""
+    import ctypes as C
+    import torch
+    rng = np.random.default_rng(12)
+    cb = oracle.codebook(4)[0]
+    rows, cols, total, off = 200, 512, 1000, 333
+    w = (rng.standard_normal((rows, cols)) * 0.02).astype(np.float16).astype(np.float32)
+    pp, pr, norms, seeds = oracle.quantize_weight(w, cb, cb, 4, 4, 128, True)
+    lin = tq.TurboQuantLinear(cols, rows, tq.QuantizedWeight(pp, pr, norms, seeds), tq.codebook_from_centroids(cb),
+                              tq.codebook_from_centroids(cb), 128)
+    for batch in (1, 3):
+        x = torch.from_numpy(rng.standard_normal((batch, cols)).astype(np.float16)).cuda()
+        want = lin.forward(x)
+        a = torch.full((batch, total), 7.0, dtype=torch.float16, device="cuda")
+        b = torch.full((batch, total), 7.0, dtype=torch.float16, device="cuda")
+        lin.forward_scatter(x, [a.data_ptr(), b.data_ptr()], total, off)
+        torch.cuda.synchronize()
+        for buf in (a, b):
+            assert torch.equal(buf[:, off:off + rows], want)
+            assert bool((buf[:, :off] == 7.0).all()) and bool((buf[:, off + rows:] == 7.0).all())
+    with pytest.raises(tq.TQError):
+        lin.forward_scatter(x, [a.data_ptr()], total, total - rows + 1)     # window does not fit
+    lin.close()
+    # shared-buffer bookkeeping that needs no second process
+    L = tq.load()
+    p = L.tq_shared_alloc(4096)
+    assert p
+    h = C.create_string_buffer(64)
+    assert L.tq_shared_export(C.c_void_p(p), h, 64) == 0 and any(h.raw)
+    assert L.tq_shared_export(C.c_void_p(p), h, 8) != 0                    # handle buffer too small
+    L.tq_shared_free(C.c_void_p(p))

@@ -76,6 +76,12 @@ def load() -> C.CDLL:
     sig("tq_linear_noalloc_scratch_limit", C.c_size_t, [])
     sig("tq_linear_dequantize", i, [vp, vp, i, vp])
     sig("tq_linear_status", i, [vp])
+    sig("tq_linear_forward_scatter", i, [vp, vp, i, C.POINTER(C.c_void_p), i, C.c_long, C.c_long, vp])
+    sig("tq_shared_alloc", vp, [C.c_size_t])
+    sig("tq_shared_free", None, [vp])
+    sig("tq_shared_export", i, [vp, vp, C.c_size_t])
+    sig("tq_shared_open", vp, [vp, C.c_size_t])
+    sig("tq_shared_close", i, [vp])
     sig("tq_linear_in_features", i, [vp])
     sig("tq_linear_out_features", i, [vp])
     sig("tq_linear_free", None, [vp])

@@ -208,6 +208,16 @@ class TurboQuantLinear:
         check(self._L.tq_linear_dequantize(self._h, _ptr(out), _dtype_tag(out), _stream_ptr(stream)), "dequantize")
         return out
 
+    def forward_scatter(self, x, dst_ptrs, dst_row_stride: int, row_offset: int, stream=None):
+        """Decode forward (device fp16 x, at most 8 rows) written straight into several buffers:
+        output row r of activation row n lands at dst[d][n * dst_row_stride + row_offset + r] for
+        every raw device pointer d in dst_ptrs (this rank's buffer and the peers' mapped ones:
+        sharding.SharedBuffer).  Replaces "forward, then all-gather" for row-sharded layers."""
+        batch = int(np.prod(x.shape[:-1])) if len(x.shape) > 1 else 1
+        arr = (C.c_void_p * len(dst_ptrs))(*[int(d) for d in dst_ptrs])
+        check(self._L.tq_linear_forward_scatter(self._h, _ptr(x), batch, arr, len(dst_ptrs), int(dst_row_stride),
+                                                int(row_offset), _stream_ptr(stream)), "TurboQuantLinear.forward_scatter")
+
     def check_status(self):
         """Waits for the device and raises if any kernel launched through this layer refused to
         run or gave up on a bounded wait (calls with host output check this themselves)."""

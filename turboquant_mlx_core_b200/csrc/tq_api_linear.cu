@@ -7,6 +7,8 @@
 // when the handle is built.
 #include <cmath>
 
+#include <cstring>
+
 #include "tq_host.hpp"
 #include "tq_kernels.cuh"
 #include "turboquant_c/turboquant_b200.h"
@@ -159,6 +161,28 @@ public:
 
     // Waits for the device and reports whether any kernel of this handle refused to run or gave
     // up on a bounded wait (the word is sticky).
+    // Decode forward (device fp16 in, at most 8 rows) whose result goes to several buffers at
+    // once: destination d receives row r of activation row n at dst[d][n * dst_stride + row_offset + r].
+    void forward_scatter(const void* x, int batch, void* const* dst, int n_dst, long dst_stride, long row_offset,
+                         cudaStream_t st) {
+        TQ_REQUIRE(x && dst, "forward_scatter: NULL argument");
+        TQ_REQUIRE(batch >= 1 && batch <= 8, "forward_scatter: batch must be 1..8");
+        TQ_REQUIRE(n_dst >= 1 && n_dst <= 8, "forward_scatter: 1..8 destinations");
+        TQ_REQUIRE(row_offset >= 0 && row_offset + out_ <= dst_stride,
+                   "forward_scatter: rows [row_offset, row_offset + out) must fit the destination row stride");
+        TQ_REQUIRE(tq::is_device_pointer(x), "forward_scatter: x must be a device pointer");
+        TQ_CUDA(cudaSetDevice(device_));
+        __half* d[8];
+        for (int i = 0; i < n_dst; ++i) {
+            TQ_REQUIRE(dst[i] != nullptr, "forward_scatter: NULL destination");
+            d[i] = static_cast<__half*>(dst[i]) + row_offset;
+        }
+        tq::launch_tq8_gemv_scatter(codes_.as<uint8_t>(), norms_.as<float>(), tables_.as<float>(),
+                                    static_cast<const __half*>(x), d, n_dst, dst_stride, out_, in_, batch, block_,
+                                    dual_ ? 2 : 1, seed_p_, seed_r_, scratch_.as<void>(), status_.as<unsigned int>(),
+                                    sm_count_, st);
+    }
+
     void check_status() {
         unsigned int h = 0;
         TQ_CUDA(cudaSetDevice(device_));
@@ -339,6 +363,59 @@ int tq_quantize_weight(const float* weight, int out_features, int in_features, c
         const uint32_t h_seeds[3] = {seed_p, (shared_rotation && residual_bits > 0) ? 0u : seed_r, block};
         TQ_CUDA(cudaMemcpyAsync(seeds, h_seeds, sizeof h_seeds, cudaMemcpyDefault, st));
         TQ_CUDA(cudaStreamSynchronize(st));  // scratch and staging buffers die here
+        return 0;
+    });
+}
+
+int tq_linear_forward_scatter(tq_linear_t lin, const void* x_fp16_device, int batch, void* const* dst, int n_dst,
+                              long dst_row_stride, long row_offset, void* stream) {
+    return guarded<int>(0, -1, [&]() {
+        TQ_REQUIRE(lin && lin->impl, "tq_linear_forward_scatter: NULL handle");
+        lin->impl->forward_scatter(x_fp16_device, batch, dst, n_dst, dst_row_stride, row_offset,
+                                   static_cast<cudaStream_t>(stream));
+        return 0;
+    });
+}
+
+void* tq_shared_alloc(size_t bytes) {
+    return guarded<void*>(nullptr, nullptr, [&]() -> void* {
+        TQ_REQUIRE(bytes > 0, "tq_shared_alloc: zero bytes");
+        void* p = nullptr;
+        TQ_CUDA(cudaMalloc(&p, bytes));
+        TQ_CUDA(cudaMemset(p, 0, bytes));
+        return p;
+    });
+}
+
+void tq_shared_free(void* ptr) {
+    if (ptr) cudaFree(ptr);
+}
+
+int tq_shared_export(void* ptr, void* handle_out, size_t handle_bytes) {
+    return guarded<int>(0, -1, [&]() {
+        TQ_REQUIRE(ptr && handle_out, "tq_shared_export: NULL argument");
+        TQ_REQUIRE(handle_bytes >= sizeof(cudaIpcMemHandle_t), "tq_shared_export: handle buffer too small (64 bytes)");
+        cudaIpcMemHandle_t h;
+        TQ_CUDA(cudaIpcGetMemHandle(&h, ptr));
+        std::memcpy(handle_out, &h, sizeof h);
+        return 0;
+    });
+}
+
+void* tq_shared_open(const void* handle, size_t handle_bytes) {
+    return guarded<void*>(nullptr, nullptr, [&]() -> void* {
+        TQ_REQUIRE(handle && handle_bytes >= sizeof(cudaIpcMemHandle_t), "tq_shared_open: bad handle");
+        cudaIpcMemHandle_t h;
+        std::memcpy(&h, handle, sizeof h);
+        void* p = nullptr;
+        TQ_CUDA(cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess));
+        return p;
+    });
+}
+
+int tq_shared_close(void* peer_ptr) {
+    return guarded<int>(0, -1, [&]() {
+        if (peer_ptr) TQ_CUDA(cudaIpcCloseMemHandle(peer_ptr));
         return 0;
     });
 }

@@ -130,7 +130,10 @@ struct GemvArgs {
     const float* table;     // [n_planes, 256] fp32
     const float* xrot;      // [n_planes, batch, in] fp32 (TF32-rounded); used when x == nullptr
     const __half* x;        // [batch, in] fp16: rotate inside the kernel (WHT block <= 256), else nullptr
-    __half* y;              // [batch, out]
+    __half* y;              // [batch, y_stride]: row r of activation row n at y[n * y_stride + r]
+    __half* y_peer[7];      // further destinations written with the same values (other GPUs' buffers)
+    int n_peer;
+    long y_stride;
     float* partial;         // [n_slots, 8, out_pad] (only when n_slots > 1)
     unsigned int* counters; // [n_row_units]         (only when n_slots > 1)
     unsigned int* status;   // device error word (0 = ok)
@@ -142,6 +145,17 @@ struct GemvArgs {
     int block;                 // WHT block size                  (in-kernel rotation)
     float inv_sqrt_block;
 };
+
+// One output element goes to the caller's buffer and, when the call scatters, to the same
+// position of up to 7 further buffers (peer GPUs' memory mapped into this process: plain stores
+// over NVLink, no multicast).
+__device__ __forceinline__ void store_y(const GemvArgs& p, int n, int row, __half h) {
+    const size_t o = static_cast<size_t>(n) * p.y_stride + row;
+    p.y[o] = h;
+#pragma unroll
+    for (int d = 0; d < 7; ++d)
+        if (d < p.n_peer) p.y_peer[d][o] = h;
+}
 
 // Shared memory holds only the table and the partial-sum ring: the dynamic allocation ends at
 // the end of the table (128 KB).  Asking for much more than that shrinks the L1 side of the
@@ -383,7 +397,7 @@ __global__ void __launch_bounds__(kCtaThreads, 1) tq8_gemv_kernel(const GemvArgs
                 for (int k = 0; k < kPer; ++k) {
                     const int n = n0 + k;
                     if (p.n_slots == 1) {
-                        if (n < p.batch) p.y[static_cast<size_t>(n) * p.out + row] = __float2half_rn(v[k] * sc);
+                        if (n < p.batch) store_y(p, n, row, __float2half_rn(v[k] * sc));
                     } else {
                         p.partial[(static_cast<size_t>(slot) * 8 + n) * p.out_pad + row] = v[k];
                     }
@@ -415,7 +429,7 @@ __global__ void __launch_bounds__(kCtaThreads, 1) tq8_gemv_kernel(const GemvArgs
                         float total = 0.f;
                         for (int c = 0; c < p.n_slots; ++c)
                             total += __ldcg(p.partial + (static_cast<size_t>(c) * 8 + n) * p.out_pad + row);
-                        p.y[static_cast<size_t>(n) * p.out + row] = __float2half_rn(total * (p.norms[row] * p.inv_scale));
+                        store_y(p, n, row, __float2half_rn(total * (p.norms[row] * p.inv_scale)));
                     }
                 }
             }
@@ -641,6 +655,17 @@ size_t gemv_scratch_bytes(int out, int in, int n_planes) {
 void launch_tq8_gemv(const uint8_t* codes, const float* norms, const float* table, const __half* x, __half* y,
                      int out, int in, int batch, uint32_t block, int n_planes, uint32_t seed_p, uint32_t seed_r,
                      void* scratch, unsigned int* status, int sm_count, cudaStream_t stream) {
+    launch_tq8_gemv_scatter(codes, norms, table, x, &y, 1, out, out, in, batch, block, n_planes, seed_p, seed_r, scratch,
+                            status, sm_count, stream);
+}
+
+void launch_tq8_gemv_scatter(const uint8_t* codes, const float* norms, const float* table, const __half* x,
+                             __half* const* dst, int n_dst, long dst_stride, int out, int in, int batch, uint32_t block,
+                             int n_planes, uint32_t seed_p, uint32_t seed_r, void* scratch, unsigned int* status,
+                             int sm_count, cudaStream_t stream) {
+    TQ_REQUIRE(dst != nullptr && n_dst >= 1 && n_dst <= 8, "tq8_gemv: 1..8 destinations");
+    TQ_REQUIRE(dst_stride >= out, "tq8_gemv: destination row stride smaller than the layer's rows");
+    __half* y = dst[0];
     TQ_REQUIRE(n_planes == 1 || n_planes == 2, "tq8_gemv: one or two rotation planes");
     TQ_REQUIRE(batch >= 1 && batch <= 8, "tq8_gemv handles 1..8 activation rows per launch");
     TQ_REQUIRE(is_pow2(block) && block >= 32 && block <= 1024, "WHT block size must be a power of two in [32, 1024]");
@@ -650,6 +675,12 @@ void launch_tq8_gemv(const uint8_t* codes, const float* norms, const float* tabl
 
     GemvArgs a{};
     a.codes = codes; a.norms = norms; a.table = table; a.y = y; a.status = status;
+    a.n_peer = n_dst - 1;
+    for (int d = 1; d < n_dst; ++d) {
+        TQ_REQUIRE(dst[d] != nullptr, "tq8_gemv: NULL destination");
+        a.y_peer[d - 1] = dst[d];
+    }
+    a.y_stride = dst_stride;
     a.out = out; a.in = in; a.batch = batch;
     const int n_row_tiles = (out + 15) / 16;
     a.n_chunks = (in + kChunk - 1) / kChunk;

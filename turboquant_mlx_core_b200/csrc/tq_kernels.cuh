@@ -37,6 +37,14 @@ void launch_tq8_gemv(const uint8_t* codes, const float* norms, const float* tabl
                      int out, int in, int batch, uint32_t block, int n_planes, uint32_t seed_p, uint32_t seed_r,
                      void* scratch, unsigned int* status, int sm_count, cudaStream_t stream);
 
+// The same with the fp16 result written to n_dst (1..8) buffers at once: destination d receives
+// activation row n, output row r at dst[d][n * dst_stride + r].  Destinations may be other GPUs'
+// memory mapped into this process (peer access / CUDA IPC): plain stores, no multicast.
+void launch_tq8_gemv_scatter(const uint8_t* codes, const float* norms, const float* table, const __half* x,
+                             __half* const* dst, int n_dst, long dst_stride, int out, int in, int batch, uint32_t block,
+                             int n_planes, uint32_t seed_p, uint32_t seed_r, void* scratch, unsigned int* status,
+                             int sm_count, cudaStream_t stream);
+
 // Allocation-free variant: scratch is a fixed array in the library image
 // (gemv_static_scratch_capacity() bytes); throws if the layer needs more.
 size_t gemv_static_scratch_capacity();

@@ -105,3 +105,63 @@ def all_gather_attention_parts(out_local, lse_local, group=None):
     dist.all_gather_into_tensor(outs.view(world * out_local.shape[0], *out_local.shape[1:]), out_local.contiguous(), group=group)
     dist.all_gather_into_tensor(lses.view(world * lse_local.shape[0], *lse_local.shape[1:]), lse_local.contiguous(), group=group)
     return merge_attention_parts(outs, lses)
+
+
+class SharedBuffer:
+    """One device buffer per rank that every rank of the job (one node) can write with plain
+    stores: allocated by the library (cudaMalloc), its CUDA IPC handle exchanged through
+    torch.distributed, mapped on the peers.  ptrs[0] is this rank's own buffer, the others follow
+    in rank order (skipping this rank) - the order TurboQuantLinear.forward_scatter wants.  No
+    multicast object is created anywhere."""
+
+    def __init__(self, nbytes: int, group=None):
+        import ctypes as C
+        import torch.distributed as dist
+        from . import _lib
+        self._L = _lib.load()
+        self.nbytes = int(nbytes)
+        self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
+        self.local = self._L.tq_shared_alloc(self.nbytes)
+        if not self.local:
+            raise _lib.TQError("tq_shared_alloc: " + _lib.last_error())
+        handle = C.create_string_buffer(64)
+        _lib.check(self._L.tq_shared_export(C.c_void_p(self.local), handle, 64), "tq_shared_export")
+        handles = [None] * self.world
+        dist.all_gather_object(handles, bytes(handle.raw), group=group)
+        self._peers = []
+        self.ptrs = [self.local]
+        for r in range(self.world):
+            if r == self.rank:
+                continue
+            h = C.create_string_buffer(handles[r], 64)
+            p = self._L.tq_shared_open(h, 64)
+            if not p:
+                raise _lib.TQError("tq_shared_open: " + _lib.last_error())
+            self._peers.append(p)
+            self.ptrs.append(p)
+        self._group = group
+
+    def tensor(self, shape, dtype):
+        """A torch view of this rank's own buffer (zero-copy)."""
+        import torch
+        typestr = {torch.float16: "<f2", torch.float32: "<f4", torch.uint8: "|u1"}[dtype]
+
+        class _View:
+            pass
+        v = _View()
+        v.__cuda_array_interface__ = {"shape": tuple(shape), "typestr": typestr, "data": (int(self.local), False),
+                                      "version": 2, "strides": None}
+        return torch.as_tensor(v, device="cuda")
+
+    def close(self):
+        import ctypes as C
+        import torch
+        import torch.distributed as dist
+        if getattr(self, "local", None) is None:
+            return
+        torch.cuda.synchronize()
+        dist.barrier(group=self._group)        # nobody may still be writing into a buffer about to go
+        for p in self._peers:
+            self._L.tq_shared_close(C.c_void_p(p))
+        self._L.tq_shared_free(C.c_void_p(self.local))
+        self.local, self._peers, self.ptrs = None, [], []
