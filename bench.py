@@ -602,9 +602,41 @@ def bench_lm_head(tq, L, device, stream, rank, world, cbs, args):
             t = torch.tensor([e0.elapsed_time(e1) * 1e3 / reps], device=device, dtype=torch.float64)
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
             us = float(t.item())
+
+            def timed(fn):
+                with torch.cuda.stream(stream):
+                    fn()
+                    a0, a1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    a0.record(stream)
+                    for _ in range(reps):
+                        fn()
+                    a1.record(stream)
+                torch.cuda.synchronize()
+                tt = torch.tensor([a0.elapsed_time(a1) * 1e3 / reps], device=device, dtype=torch.float64)
+                dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+                return float(tt.item())
+            us_gemv = timed(lambda: lin.forward_scatter(x, shared.ptrs, vocab, s, stream=stream))
+            us_barrier = timed(lambda: dist.all_reduce(flag))
+            # fused barrier: the GEMV's tail raises this rank's flag on every rank; a one-warp
+            # kernel waits for all flags (no collective library call at all)
+            epoch = [0]
+
+            def call_signal():
+                epoch[0] += 1
+                lin.forward_scatter(x, shared.ptrs, vocab, s, stream=stream, signal_ptrs=shared.flag_ptrs,
+                                    signal_slot=rank, signal_value=epoch[0])
+                lin.wait_peers(shared.local_flags, world, epoch[0], stream=stream)
+            logits.zero_()
+            torch.cuda.synchronize()
+            dist.barrier()
+            us_signal = timed(call_signal)
+            lin.check_status()
+            same = same and bool(torch.equal(full[0], logits[0]))
             same_t = torch.tensor([1.0 if same else 0.0], device=device)
             dist.all_reduce(same_t, op=dist.ReduceOp.MIN)
-            res["b1_scatter"] = {"us": us, "tok_per_s": 1 / (us * 1e-6),
+            res["b1_scatter"] = {"us": us, "tok_per_s": 1 / (us * 1e-6), "us_gemv_with_peer_stores_alone": us_gemv,
+                                 "us_one_element_all_reduce_alone": us_barrier,
+                                 "us_with_fused_flag_barrier": us_signal,
                                  "path": "tq_linear_forward_scatter (peer stores from the GEMV epilogue) + 1-element all-reduce as barrier",
                                  "identical_to_all_gather_on_every_rank": bool(same_t.item() == 1.0)}
             shared.close()

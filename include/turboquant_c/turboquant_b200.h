@@ -161,6 +161,22 @@ int tq_linear_dequantize(tq_linear_t lin, void* result, int result_dtype, void* 
 int tq_linear_forward_scatter(tq_linear_t lin, const void* x_fp16_device, int batch, void* const* dst, int n_dst,
                               long dst_row_stride, long row_offset, void* stream);
 
+/** The same, followed by a completion signal: signal[d] points to an array of 32-bit flags in
+ *  destination d's memory (e.g. at the end of its shared buffer); when every result of this
+ *  call has been stored, flag signal_slot (0..31, normally this rank) of every destination is
+ *  set to signal_value (release, system scope).  tq_linear_wait_peers enqueues one small kernel
+ *  on this GPU that waits until flags [0, n_flags) of the LOCAL array have all reached `value`
+ *  (callers pass a value that grows with every step): after it, on that stream, the results of
+ *  all ranks are visible here — a rank-to-rank barrier costing one flag store and one kernel
+ *  launch, fused into the GEMV's tail instead of a separate collective.  The wait gives up after
+ *  one second and records it in the handle's status (tq_linear_status).  A buffer must not be
+ *  scattered into again before every rank has read the previous results (alternate two buffers).
+ *  No counterpart in the reference. */
+int tq_linear_forward_scatter_signal(tq_linear_t lin, const void* x_fp16_device, int batch, void* const* dst, int n_dst,
+                                     long dst_row_stride, long row_offset, void* const* signal, int signal_slot,
+                                     unsigned int signal_value, void* stream);
+int tq_linear_wait_peers(tq_linear_t lin, const void* local_flags, int n_flags, unsigned int value, void* stream);
+
 /** Device memory that other processes on the same machine can map: tq_shared_alloc (cudaMalloc,
  *  zero-filled) on the owner, tq_shared_export writes a 64-byte handle to send to the peers
  *  (any channel), tq_shared_open maps it there (CUDA IPC with lazy peer access; the pointer is

@@ -203,3 +203,43 @@ def test_forward_scatter_writes_every_destination(tq, oracle):
     assert L.tq_shared_export(C.c_void_p(p), h, 64) == 0 and any(h.raw)
     assert L.tq_shared_export(C.c_void_p(p), h, 8) != 0                    # handle buffer too small
     L.tq_shared_free(C.c_void_p(p))
+
+
+def test_scatter_completion_signal_and_bounded_wait(tq, oracle):
+    """The completion flag of a scattering call reaches every destination's flag array, the wait
+    kernel returns once the flags are there, and a flag that nobody raises makes the wait give up
+    after its limit with an error status (the context stays usable)."""
+    import torch
+    rng = np.random.default_rng(13)
+    cb = oracle.codebook(4)[0]
+    rows, cols = 96, 256
+    w = (rng.standard_normal((rows, cols)) * 0.02).astype(np.float16).astype(np.float32)
+    pp, pr, norms, seeds = oracle.quantize_weight(w, cb, cb, 4, 4, 128, True)
+
+    def make():
+        return tq.TurboQuantLinear(cols, rows, tq.QuantizedWeight(pp, pr, norms, seeds), tq.codebook_from_centroids(cb),
+                                   tq.codebook_from_centroids(cb), 128)
+    lin = make()
+    x = torch.from_numpy(rng.standard_normal((2, cols)).astype(np.float16)).cuda()
+    want = lin.forward(x)
+    a = torch.zeros((2, rows), dtype=torch.float16, device="cuda")
+    b = torch.zeros((2, rows), dtype=torch.float16, device="cuda")
+    fa = torch.zeros(32, dtype=torch.int32, device="cuda")
+    fb = torch.zeros(32, dtype=torch.int32, device="cuda")
+    for step in (1, 2, 3):
+        lin.forward_scatter(x, [a.data_ptr(), b.data_ptr()], rows, 0, signal_ptrs=[fa.data_ptr(), fb.data_ptr()],
+                            signal_slot=3, signal_value=step)
+        lin.wait_peers(fa.data_ptr() + 4 * 3, 1, step)
+        torch.cuda.synchronize()
+        assert int(fa[3]) == step and int(fb[3]) == step and int(fa.sum()) == step
+        assert torch.equal(a, want) and torch.equal(b, want)
+    lin.check_status()
+    # a flag nobody raises: the wait runs out (about a second) and says so
+    lin.wait_peers(fa.data_ptr(), 1, 1)
+    torch.cuda.synchronize()
+    with pytest.raises(tq.TQError):
+        lin.check_status()
+    lin.close()
+    lin2 = make()                                   # the device is fine afterwards
+    assert torch.equal(lin2.forward(x), want)
+    lin2.close()

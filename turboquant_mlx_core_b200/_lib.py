@@ -77,6 +77,9 @@ def load() -> C.CDLL:
     sig("tq_linear_dequantize", i, [vp, vp, i, vp])
     sig("tq_linear_status", i, [vp])
     sig("tq_linear_forward_scatter", i, [vp, vp, i, C.POINTER(C.c_void_p), i, C.c_long, C.c_long, vp])
+    sig("tq_linear_forward_scatter_signal", i, [vp, vp, i, C.POINTER(C.c_void_p), i, C.c_long, C.c_long,
+                                                C.POINTER(C.c_void_p), i, C.c_uint, vp])
+    sig("tq_linear_wait_peers", i, [vp, vp, i, C.c_uint, vp])
     sig("tq_shared_alloc", vp, [C.c_size_t])
     sig("tq_shared_free", None, [vp])
     sig("tq_shared_export", i, [vp, vp, C.c_size_t])

@@ -208,15 +208,31 @@ class TurboQuantLinear:
         check(self._L.tq_linear_dequantize(self._h, _ptr(out), _dtype_tag(out), _stream_ptr(stream)), "dequantize")
         return out
 
-    def forward_scatter(self, x, dst_ptrs, dst_row_stride: int, row_offset: int, stream=None):
+    def forward_scatter(self, x, dst_ptrs, dst_row_stride: int, row_offset: int, stream=None, signal_ptrs=None,
+                        signal_slot: int = 0, signal_value: int = 0):
         """Decode forward (device fp16 x, at most 8 rows) written straight into several buffers:
         output row r of activation row n lands at dst[d][n * dst_row_stride + row_offset + r] for
         every raw device pointer d in dst_ptrs (this rank's buffer and the peers' mapped ones:
         sharding.SharedBuffer).  Replaces "forward, then all-gather" for row-sharded layers."""
         batch = int(np.prod(x.shape[:-1])) if len(x.shape) > 1 else 1
         arr = (C.c_void_p * len(dst_ptrs))(*[int(d) for d in dst_ptrs])
-        check(self._L.tq_linear_forward_scatter(self._h, _ptr(x), batch, arr, len(dst_ptrs), int(dst_row_stride),
-                                                int(row_offset), _stream_ptr(stream)), "TurboQuantLinear.forward_scatter")
+        if signal_ptrs is None:
+            check(self._L.tq_linear_forward_scatter(self._h, _ptr(x), batch, arr, len(dst_ptrs), int(dst_row_stride),
+                                                    int(row_offset), _stream_ptr(stream)), "TurboQuantLinear.forward_scatter")
+            return
+        # with a completion signal: flag `signal_slot` of every destination's flag array is set to
+        # signal_value once all results are stored (see wait_peers)
+        sig = (C.c_void_p * len(signal_ptrs))(*[int(d) for d in signal_ptrs])
+        check(self._L.tq_linear_forward_scatter_signal(self._h, _ptr(x), batch, arr, len(dst_ptrs), int(dst_row_stride),
+                                                       int(row_offset), sig, int(signal_slot), int(signal_value) & 0xFFFFFFFF,
+                                                       _stream_ptr(stream)), "TurboQuantLinear.forward_scatter")
+
+    def wait_peers(self, local_flags_ptr: int, n_flags: int, value: int, stream=None):
+        """Enqueue the (bounded) wait for the completion flags of n_flags ranks in this rank's own
+        flag array to reach `value`; afterwards, on that stream, every rank's scattered results are
+        visible here.  A timeout shows up in check_status()."""
+        check(self._L.tq_linear_wait_peers(self._h, C.c_void_p(int(local_flags_ptr)), int(n_flags), int(value) & 0xFFFFFFFF,
+                                           _stream_ptr(stream)), "TurboQuantLinear.wait_peers")
 
     def check_status(self):
         """Waits for the device and raises if any kernel launched through this layer refused to

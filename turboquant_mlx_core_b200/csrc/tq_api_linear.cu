@@ -94,8 +94,8 @@ public:
             scratch_.resize(sb);
             TQ_CUDA(cudaMemset(scratch_.as<void>(), 0, sb));
         }
-        status_.resize(sizeof(unsigned int));
-        TQ_CUDA(cudaMemset(status_.as<void>(), 0, sizeof(unsigned int)));
+        status_.resize(2 * sizeof(unsigned int));  // [0] error word, [1] grid completion counter of scattering calls
+        TQ_CUDA(cudaMemset(status_.as<void>(), 0, 2 * sizeof(unsigned int)));
         TQ_CUDA(cudaMallocHost(&h_status_, sizeof(unsigned int)));
         *h_status_ = 0;
 
@@ -164,7 +164,7 @@ public:
     // Decode forward (device fp16 in, at most 8 rows) whose result goes to several buffers at
     // once: destination d receives row r of activation row n at dst[d][n * dst_stride + row_offset + r].
     void forward_scatter(const void* x, int batch, void* const* dst, int n_dst, long dst_stride, long row_offset,
-                         cudaStream_t st) {
+                         cudaStream_t st, void* const* signal = nullptr, int signal_slot = 0, unsigned int signal_value = 0) {
         TQ_REQUIRE(x && dst, "forward_scatter: NULL argument");
         TQ_REQUIRE(batch >= 1 && batch <= 8, "forward_scatter: batch must be 1..8");
         TQ_REQUIRE(n_dst >= 1 && n_dst <= 8, "forward_scatter: 1..8 destinations");
@@ -177,10 +177,20 @@ public:
             TQ_REQUIRE(dst[i] != nullptr, "forward_scatter: NULL destination");
             d[i] = static_cast<__half*>(dst[i]) + row_offset;
         }
+        unsigned int* sig[8];
+        if (signal != nullptr) {
+            TQ_REQUIRE(signal_slot >= 0 && signal_slot < 32, "forward_scatter: signal slot must be 0..31");
+            for (int i = 0; i < n_dst; ++i) sig[i] = static_cast<unsigned int*>(signal[i]);
+        }
         tq::launch_tq8_gemv_scatter(codes_.as<uint8_t>(), norms_.as<float>(), tables_.as<float>(),
                                     static_cast<const __half*>(x), d, n_dst, dst_stride, out_, in_, batch, block_,
                                     dual_ ? 2 : 1, seed_p_, seed_r_, scratch_.as<void>(), status_.as<unsigned int>(),
-                                    sm_count_, st);
+                                    sm_count_, st, signal ? sig : nullptr, signal_slot, signal_value);
+    }
+
+    void wait_peers(const void* flags, int n, unsigned int value, cudaStream_t st) {
+        TQ_CUDA(cudaSetDevice(device_));
+        tq::launch_peer_wait(static_cast<const unsigned int*>(flags), n, value, status_.as<unsigned int>(), st);
     }
 
     void check_status() {
@@ -239,6 +249,7 @@ private:
         const char* what = h == 1 ? "decode kernel: unexpected shared-memory base address, kernel did not run"
                            : (h == 4 || h == 5) ? "decode kernel: a bounded wait on a partial-sum barrier gave up"
                            : h == 9 ? "prefill kernel: shared-memory layout does not fit, kernel did not run"
+                           : h == 10 ? "peer wait: a rank's completion flag did not arrive within a second"
                            : (h >= 6 && h <= 8) ? "prefill kernel: a bounded wait on a pipeline barrier gave up"
                                                 : "kernel reported an unknown status";
         throw Error(std::string("TurboQuantLinear: ") + what + " (status " + std::to_string(h) + ")");
@@ -373,6 +384,26 @@ int tq_linear_forward_scatter(tq_linear_t lin, const void* x_fp16_device, int ba
         TQ_REQUIRE(lin && lin->impl, "tq_linear_forward_scatter: NULL handle");
         lin->impl->forward_scatter(x_fp16_device, batch, dst, n_dst, dst_row_stride, row_offset,
                                    static_cast<cudaStream_t>(stream));
+        return 0;
+    });
+}
+
+int tq_linear_forward_scatter_signal(tq_linear_t lin, const void* x_fp16_device, int batch, void* const* dst, int n_dst,
+                                     long dst_row_stride, long row_offset, void* const* signal, int signal_slot,
+                                     unsigned int signal_value, void* stream) {
+    return guarded<int>(0, -1, [&]() {
+        TQ_REQUIRE(lin && lin->impl, "tq_linear_forward_scatter_signal: NULL handle");
+        TQ_REQUIRE(signal != nullptr, "tq_linear_forward_scatter_signal: NULL signal list");
+        lin->impl->forward_scatter(x_fp16_device, batch, dst, n_dst, dst_row_stride, row_offset,
+                                   static_cast<cudaStream_t>(stream), signal, signal_slot, signal_value);
+        return 0;
+    });
+}
+
+int tq_linear_wait_peers(tq_linear_t lin, const void* local_flags, int n_flags, unsigned int value, void* stream) {
+    return guarded<int>(0, -1, [&]() {
+        TQ_REQUIRE(lin && lin->impl, "tq_linear_wait_peers: NULL handle");
+        lin->impl->wait_peers(local_flags, n_flags, value, static_cast<cudaStream_t>(stream));
         return 0;
     });
 }

@@ -134,6 +134,13 @@ struct GemvArgs {
     __half* y_peer[7];      // further destinations written with the same values (other GPUs' buffers)
     int n_peer;
     long y_stride;
+    // Completion signal of a scattering call (n_signal = 0: none): when the whole grid has
+    // stored its results, word `signal_slot` of every destination's flag array is set to
+    // `signal_value`.  done_counter is a zero-initialised device word owned by the layer.
+    unsigned int* signal[8];
+    int n_signal, signal_slot;
+    unsigned int signal_value;
+    unsigned int* done_counter;
     float* partial;         // [n_slots, 8, out_pad] (only when n_slots > 1)
     unsigned int* counters; // [n_row_units]         (only when n_slots > 1)
     unsigned int* status;   // device error word (0 = ok)
@@ -626,6 +633,43 @@ __global__ void __launch_bounds__(kCtaThreads, 1) tq8_gemv_kernel(const GemvArgs
         red = next_pos(red);
         if (++rs == kRing) { rs = 0; rpar ^= 1u; }
     }
+
+    // ---- completion signal to the destinations' owners ----
+    // Every thread orders its (possibly remote) result stores system-wide, the CTA counts in, and
+    // the CTA that completes the grid publishes the flag everywhere.  Whoever then reads the flag
+    // with acquire semantics sees all of this launch's results.
+    if (p.n_signal > 0) {
+        __threadfence_system();
+        __syncthreads();
+        if (tid == 0) {
+            const unsigned int prev = atomicAdd(p.done_counter, 1u);
+            if (prev == gridDim.x - 1) {
+                *p.done_counter = 0u;  // ready for the next launch (stream order)
+                __threadfence_system();
+#pragma unroll
+                for (int d = 0; d < 8; ++d)
+                    if (d < p.n_signal)
+                        asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p.signal[d] + p.signal_slot), "r"(p.signal_value) : "memory");
+            }
+        }
+    }
+}
+
+// Waits (bounded) until flags[0..n) have all reached `value`: the receiving side of the completion
+// signal above.  Runs on the GPU that owns the flags; the writers are kernels on other GPUs.
+__global__ void peer_wait_kernel(const unsigned int* __restrict__ flags, int n, unsigned int value, unsigned int* status) {
+    const int lane = threadIdx.x;
+    if (lane >= n) return;
+    const unsigned long long t0 = global_timer_ns();
+    for (unsigned int spin = 0;; ++spin) {
+        unsigned int v;
+        asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(flags + lane) : "memory");
+        if (static_cast<int>(v - value) >= 0) return;
+        if ((spin & 255u) == 255u && global_timer_ns() - t0 > 5ull * kWaitLimitNs) {  // 1 s: a peer is gone
+            atomicExch(status, 10u);
+            return;
+        }
+    }
 }
 
 size_t align256(size_t v) { return (v + 255) & ~static_cast<size_t>(255); }
@@ -659,10 +703,17 @@ void launch_tq8_gemv(const uint8_t* codes, const float* norms, const float* tabl
                             status, sm_count, stream);
 }
 
+void launch_peer_wait(const unsigned int* flags, int n, unsigned int value, unsigned int* status, cudaStream_t stream) {
+    TQ_REQUIRE(flags != nullptr && n >= 1 && n <= 32, "peer wait: 1..32 flags");
+    peer_wait_kernel<<<1, 32, 0, stream>>>(flags, n, value, status);
+    TQ_CUDA(cudaGetLastError());
+}
+
 void launch_tq8_gemv_scatter(const uint8_t* codes, const float* norms, const float* table, const __half* x,
                              __half* const* dst, int n_dst, long dst_stride, int out, int in, int batch, uint32_t block,
                              int n_planes, uint32_t seed_p, uint32_t seed_r, void* scratch, unsigned int* status,
-                             int sm_count, cudaStream_t stream) {
+                             int sm_count, cudaStream_t stream, unsigned int* const* signal, int signal_slot,
+                             unsigned int signal_value) {
     TQ_REQUIRE(dst != nullptr && n_dst >= 1 && n_dst <= 8, "tq8_gemv: 1..8 destinations");
     TQ_REQUIRE(dst_stride >= out, "tq8_gemv: destination row stride smaller than the layer's rows");
     __half* y = dst[0];
@@ -681,6 +732,17 @@ void launch_tq8_gemv_scatter(const uint8_t* codes, const float* norms, const flo
         a.y_peer[d - 1] = dst[d];
     }
     a.y_stride = dst_stride;
+    a.n_signal = 0;
+    if (signal != nullptr) {
+        a.n_signal = n_dst;
+        for (int d = 0; d < n_dst; ++d) {
+            TQ_REQUIRE(signal[d] != nullptr, "tq8_gemv: NULL signal array");
+            a.signal[d] = signal[d];
+        }
+        a.signal_slot = signal_slot;
+        a.signal_value = signal_value;
+        a.done_counter = status + 1;  // the layer's second status word
+    }
     a.out = out; a.in = in; a.batch = batch;
     const int n_row_tiles = (out + 15) / 16;
     a.n_chunks = (in + kChunk - 1) / kChunk;

@@ -121,7 +121,9 @@ class SharedBuffer:
         self._L = _lib.load()
         self.nbytes = int(nbytes)
         self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
-        self.local = self._L.tq_shared_alloc(self.nbytes)
+        # 32 completion flags (one per rank) live behind the payload, 256-byte aligned
+        self.flag_offset = (self.nbytes + 255) // 256 * 256
+        self.local = self._L.tq_shared_alloc(self.flag_offset + 256)
         if not self.local:
             raise _lib.TQError("tq_shared_alloc: " + _lib.last_error())
         handle = C.create_string_buffer(64)
@@ -140,6 +142,8 @@ class SharedBuffer:
             self._peers.append(p)
             self.ptrs.append(p)
         self._group = group
+        self.flag_ptrs = [p + self.flag_offset for p in self.ptrs]   # same order as ptrs
+        self.local_flags = self.local + self.flag_offset
 
     def tensor(self, shape, dtype):
         """A torch view of this rank's own buffer (zero-copy)."""
