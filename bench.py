@@ -309,7 +309,7 @@ def run_cuda(args):
 
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         line["cpu_baseline"] = cpu_baseline(qw0, cbs, x_host[0].numpy(), y_dev[0].cpu().numpy(), budget_s=12.0)
-    legs = set(args.legs.split(",")) if args.legs else {"attention", "decoder_layer", "prefill", "lm_head"}
+    legs = set(args.legs.split(",")) if args.legs else {"attention", "decoder_layer", "prefill", "lm_head", "side_kernels"}
     if args.no_extras:
         legs = set()
     if "attention" in legs:
@@ -325,6 +325,11 @@ def run_cuda(args):
             line["decoder_layer"] = bench_decoder_layer(tq, L, device, stream, cbs, args)
         except Exception as e:
             line["decoder_layer"] = {"error": str(e)}
+    if "side_kernels" in legs and world == 1:
+        try:
+            line["side_kernels"] = bench_side_kernels(tq, L, layers, device, stream, args)
+        except Exception as e:
+            line["side_kernels"] = {"error": str(e)}
     if "prefill" in legs:
         try:
             line["prefill"] = bench_prefill(tq, L, layers, device, stream, args)
@@ -422,6 +427,97 @@ def bench_attention(tq, L, device, stream, rank, world, args, ctx):
             "context_parts": parts,
             "l2_policy": f"cache {n_seqs * heads_local * ctx_local * 132 / 1e6:.0f} MB per GPU "
                          + ("> L2" if n_seqs * heads_local * ctx_local * 132 > 126e6 else "<= L2 (126 MB)")}
+
+
+# ---- secondary: the memory-bound side kernels of the path (dequantise, rotation, KV encode / decode) ---
+
+def bench_side_kernels(tq, L, layers, device, stream, args):
+    """Device-resident inputs and outputs, CUDA events, inputs larger than L2 where the kernel
+    streams (8 distinct layers / matrices per pass)."""
+    import torch
+    sp = C.c_void_p(stream.cuda_stream)
+    peak, kind = measured_peaks()
+    res = {"peak_kind": kind}
+
+    def timed(fn, reps=5):
+        with torch.cuda.stream(stream):
+            fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        with torch.cuda.stream(stream):
+            e0.record(stream)
+            for _ in range(reps):
+                fn()
+            e1.record(stream)
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) * 1e3 / reps
+
+    n = min(len(layers), 8)
+    # dequantise to fp16: 1 B read + 2 B written per weight
+    outs = [torch.empty((OUT_F, IN_F), dtype=torch.float16, device=device) for _ in range(n)]
+
+    def deq():
+        for lin, o in zip(layers[:n], outs):
+            if L.tq_linear_dequantize(lin.handle, C.c_void_p(o.data_ptr()), tq.TQ_F16, sp):
+                raise RuntimeError(L.tq_last_error().decode())
+    us = timed(deq) / n
+    b = OUT_F * IN_F * 3
+    res["dequantize_f16_4096x4096"] = {"us": us, "gb_per_s": b / (us * 1e-6) / 1e9, "frac_of_peak": b / (us * 1e-6) / 1e9 / peak}
+    del outs
+    # blocked WHT rotation of an fp32 matrix: 4 B read + 4 B written per element
+    ms = [torch.randn((OUT_F, IN_F), device=device) for _ in range(n)]
+    rot = torch.empty((OUT_F, IN_F), device=device)
+
+    def wht():
+        for m_ in ms:
+            if L.tq_wht_rotate(C.c_void_p(m_.data_ptr()), C.c_void_p(rot.data_ptr()), OUT_F, IN_F, 1234, BLOCK, 0, sp):
+                raise RuntimeError(L.tq_last_error().decode())
+    us = timed(wht) / n
+    b = OUT_F * IN_F * 8
+    res["wht_rotate_f32_4096x4096"] = {"us": us, "gb_per_s": b / (us * 1e-6) / 1e9, "frac_of_peak": b / (us * 1e-6) / 1e9 / peak}
+    del ms, rot
+    # KV encode (append): bulk 8192 tokens x 4 heads x 128, and one token for 16 sequences
+    heads, dim = 4, 128
+    k = torch.randn((8192, heads, dim), device=device).half()
+    v = torch.randn((8192, heads, dim), device=device).half()
+    cache = tq.TQKVCache(1, heads, dim)
+    t0 = time.perf_counter()
+    with torch.cuda.stream(stream):
+        for _ in range(8):
+            cache.append(0, k, v, stream=stream)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with torch.cuda.stream(stream):
+        e0.record(stream)
+        for _ in range(8):
+            cache.append(0, k, v, stream=stream)
+        e1.record(stream)
+    torch.cuda.synchronize()
+    us = e0.elapsed_time(e1) * 1e3 / 8
+    b = 8192 * heads * (2 * dim * 2 + 132)
+    res["kv_append_8192_tokens"] = {"us": us, "tok_per_s": 8192 / (us * 1e-6), "gb_per_s": b / (us * 1e-6) / 1e9,
+                                    "frac_of_peak": b / (us * 1e-6) / 1e9 / peak}
+    # decode of the compressed keys back to fp16 (get_keys_fp16): 56 B read + 256 B written per vector
+    out = torch.empty((65536, heads, dim), dtype=torch.float16, device=device)
+
+    def dec():
+        if L.tq_kv_get_fp16(cache.handle, 0, 0, 0, 65536, C.c_void_p(out.data_ptr()), sp):
+            raise RuntimeError(L.tq_last_error().decode())
+    us = timed(dec)
+    b = 65536 * heads * (56 + 2 * dim)
+    res["kv_get_keys_fp16_65536_tokens"] = {"us": us, "gb_per_s": b / (us * 1e-6) / 1e9, "frac_of_peak": b / (us * 1e-6) / 1e9 / peak}
+    cache.close()
+    seqs = [tq.TQKVCache(1, heads, dim) for _ in range(16)]
+    k1 = torch.randn((1, heads, dim), device=device).half()
+
+    def step():
+        for c in seqs:
+            c.append(0, k1, k1, stream=stream)
+    us = timed(step, reps=20)
+    res["kv_append_1_token_x16_seqs"] = {"us_per_step": us, "us_per_sequence": us / 16}
+    for c in seqs:
+        c.close()
+    return res
 
 
 # ---- secondary: prefill through the tensor-core GEMM (BASELINE config 1, prefill part) -------------
@@ -572,8 +668,21 @@ def bench_lm_head(tq, L, device, stream, rank, world, cbs, args):
         # rank's buffer over NVLink (peer-mapped memory, plain stores); one tiny all-reduce is the
         # barrier after which each rank may read the full logits
         from turboquant_mlx_core_b200.sharding import SharedBuffer
+        # set-up errors must not leave some ranks inside collectives the others never join:
+        # every rank reports whether its buffers are mapped, and all skip together otherwise
+        shared, setup_error = None, None
         try:
             shared = SharedBuffer(8 * vocab * 2)
+        except Exception as e:
+            setup_error = str(e)
+        ok_t = torch.tensor([0.0 if setup_error else 1.0], device=device)
+        dist.all_reduce(ok_t, op=dist.ReduceOp.MIN)
+        if ok_t.item() != 1.0:
+            res["b1_scatter"] = {"skipped": "shared buffers could not be mapped on every rank", "local_error": setup_error}
+            lin.close()
+            res["workload"] = f"config 2: LM head {vocab}x{hidden}, rows sharded over {world} GPU(s), fp16 logits all-gather"
+            return res
+        try:
             logits = shared.tensor((8, vocab), torch.float16)
             flag = torch.zeros(1, device=device)
             x = torch.randn((1, hidden), generator=g, device=device).half()
@@ -749,7 +858,7 @@ def main():
     ap.add_argument("--attn-ctx", type=int, default=32768)
     ap.add_argument("--no-extras", action="store_true", help="skip the secondary measurements")
     ap.add_argument("--legs", default="", help="comma list of secondary measurements to run "
-                                               "(attention, decoder_layer, prefill, lm_head); default all")
+                                               "(attention, decoder_layer, prefill, lm_head, side_kernels); default all")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-graph", action="store_true", help="time plain stream launches instead of a CUDA graph")
     a = ap.parse_args()

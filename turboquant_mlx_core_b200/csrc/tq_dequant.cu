@@ -161,12 +161,34 @@ __global__ void __launch_bounds__(256) dequant_kernel(const uint8_t* __restrict_
             for (int j = 0; j < E; ++j) v[j] = __fadd_rn(v[j], __fmul_rn(u[j], sr[j]));
         }
         OutT* dst = out + blk * BS + lane * E;
+        // a lane's E results are contiguous: store them with the widest aligned vector available
+        __align__(16) OutT w[E];
 #pragma unroll
         for (int j = 0; j < E; ++j) {
-            const float w = __fmul_rn(v[j], norm);
-            if constexpr (sizeof(OutT) == 4) dst[j] = w;
-            else dst[j] = __float2half_rn(w);
+            const float f = __fmul_rn(v[j], norm);
+            if constexpr (sizeof(OutT) == 4) w[j] = f;
+            else w[j] = __float2half_rn(f);
         }
+        constexpr int kBytes = E * static_cast<int>(sizeof(OutT));
+        if constexpr (kBytes % 16 == 0) {
+            if (reinterpret_cast<uintptr_t>(dst) % 16 == 0) {
+#pragma unroll
+                for (int c = 0; c < kBytes / 16; ++c) reinterpret_cast<uint4*>(dst)[c] = reinterpret_cast<const uint4*>(w)[c];
+                continue;
+            }
+        } else if constexpr (kBytes == 8) {
+            if (reinterpret_cast<uintptr_t>(dst) % 8 == 0) {
+                *reinterpret_cast<uint2*>(dst) = *reinterpret_cast<const uint2*>(w);
+                continue;
+            }
+        } else if constexpr (kBytes == 4) {
+            if (reinterpret_cast<uintptr_t>(dst) % 4 == 0) {
+                *reinterpret_cast<uint32_t*>(dst) = *reinterpret_cast<const uint32_t*>(w);
+                continue;
+            }
+        }
+#pragma unroll
+        for (int j = 0; j < E; ++j) dst[j] = w[j];
     }
 }
 

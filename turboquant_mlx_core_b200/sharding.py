@@ -123,13 +123,25 @@ class SharedBuffer:
         self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
         # 32 completion flags (one per rank) live behind the payload, 256-byte aligned
         self.flag_offset = (self.nbytes + 255) // 256 * 256
+        # A rank whose allocation fails still takes part in the exchange (with None), so that all
+        # ranks raise together instead of leaving the others inside the collective.
         self.local = self._L.tq_shared_alloc(self.flag_offset + 256)
+        mine, err = None, None
         if not self.local:
-            raise _lib.TQError("tq_shared_alloc: " + _lib.last_error())
-        handle = C.create_string_buffer(64)
-        _lib.check(self._L.tq_shared_export(C.c_void_p(self.local), handle, 64), "tq_shared_export")
+            err = "tq_shared_alloc: " + _lib.last_error()
+        else:
+            handle = C.create_string_buffer(64)
+            if self._L.tq_shared_export(C.c_void_p(self.local), handle, 64) != 0:
+                err = "tq_shared_export: " + _lib.last_error()
+            else:
+                mine = bytes(handle.raw)
         handles = [None] * self.world
-        dist.all_gather_object(handles, bytes(handle.raw), group=group)
+        dist.all_gather_object(handles, mine, group=group)
+        if any(h is None for h in handles):
+            if self.local:
+                self._L.tq_shared_free(C.c_void_p(self.local))
+            self.local = None
+            raise _lib.TQError(err or "a peer could not allocate or export its shared buffer")
         self._peers = []
         self.ptrs = [self.local]
         for r in range(self.world):
