@@ -473,35 +473,50 @@ __global__ void __launch_bounds__(kMmaThreads, 3) attn_mma_kernel(const AttnSeq*
 #pragma unroll
         for (int k = 0; k < 4; ++k) acc[mt][k] = 0.f;
 
-    // Software pipeline over 16-token tiles: a tile's key words are fetched while the tile
-    // before it is in its value phase; its value words, sign words and norms are fetched at the
-    // top of the tile, a whole key phase ahead of their use.
+    // Software pipeline over 16-token tiles: everything a tile reads from the cache (key words,
+    // sign words, value words, the four norms) sits in registers when the tile starts, and each
+    // register group is refilled for the NEXT tile right after its last use in this one, so every
+    // load has a whole tile of work to hide behind and no extra registers are needed.  The refill
+    // addresses are clamped, so the last tile's refills read valid (unused) records.
     // record index of this thread's two tokens of the tile starting at tb (clamped so loads stay
     // in range; tokens past the end are masked out of the scores)
     auto rec_of = [&](int tok) { return static_cast<size_t>(tok < t1 ? tok : t1 - 1) * kv_heads + kvh; };
-    uint32_t kwa[4] = {0, 0, 0, 0}, kwb[4] = {0, 0, 0, 0};
+    uint32_t kwa[4] = {0, 0, 0, 0}, kwb[4] = {0, 0, 0, 0}, vwa[4] = {0, 0, 0, 0}, vwb[4] = {0, 0, 0, 0};
+    uint32_t wa_n = 0, wb_n = 0;
+    float qa_n = 0.f, qb_n = 0.f, kna_n = 0.f, knb_n = 0.f, vna_n = 0.f, vnb_n = 0.f;
     if (t0 + warp * 16 < t1) {
-        load_words(S.k_words + rec_of(t0 + warp * 16 + g) * WPH, kwa);
-        load_words(S.k_words + rec_of(t0 + warp * 16 + g + 8) * WPH, kwb);
+        const size_t r0 = rec_of(t0 + warp * 16 + g), r1 = rec_of(t0 + warp * 16 + g + 8);
+        load_words(S.k_words + r0 * WPH, kwa);
+        load_words(S.k_words + r1 * WPH, kwb);
+        load_words(S.v_words + r0 * WPH, vwa);
+        load_words(S.v_words + r1 * WPH, vwb);
+        if (use_qjl) {
+            wa_n = __ldg(S.qjl_words + r0 * QPH + q);
+            wb_n = __ldg(S.qjl_words + r1 * QPH + q);
+            qa_n = __ldg(S.qjl_norms + r0);
+            qb_n = __ldg(S.qjl_norms + r1);
+        }
+        kna_n = __ldg(S.k_norms + r0);
+        knb_n = __ldg(S.k_norms + r1);
+        vna_n = __ldg(S.v_norms + r0);
+        vnb_n = __ldg(S.v_norms + r1);
     }
     for (int tb = t0 + warp * 16; tb < t1; tb += 64) {
         const int ta = tb + g, tbb = tb + g + 8;
         const bool va = ta < t1, vb = tbb < t1;
-        const size_t ra = rec_of(ta), rb = rec_of(tbb);
-        uint32_t vwa[4], vwb[4];
-        load_words(S.v_words + ra * WPH, vwa);
-        load_words(S.v_words + rb * WPH, vwb);
-        uint32_t wa = 0, wb = 0;
-        float qa = 0.f, qb = 0.f;
-        if (use_qjl) {
-            wa = __ldg(S.qjl_words + ra * QPH + q);
-            wb = __ldg(S.qjl_words + rb * QPH + q);
-            qa = __ldg(S.qjl_norms + ra);
-            qb = __ldg(S.qjl_norms + rb);
-        }
+        const size_t na = rec_of(tb + 64 + g), nb = rec_of(tb + 64 + g + 8);  // this thread's records of the next tile
         const float kscale = inv_scale_d * attn_scale / kCentroidScale;
-        const float kna = __ldg(S.k_norms + ra) * kscale, knb = __ldg(S.k_norms + rb) * kscale;
-        const float vna = __ldg(S.v_norms + ra) * (1.0f / kCentroidScale), vnb = __ldg(S.v_norms + rb) * (1.0f / kCentroidScale);
+        const float kna = kna_n * kscale, knb = knb_n * kscale;
+        kna_n = __ldg(S.k_norms + na);
+        knb_n = __ldg(S.k_norms + nb);
+        uint32_t wa = wa_n, wb = wb_n;
+        float qa = qa_n, qb = qb_n;
+        if (use_qjl) {
+            wa_n = __ldg(S.qjl_words + na * QPH + q);
+            wb_n = __ldg(S.qjl_words + nb * QPH + q);
+            qa_n = __ldg(S.qjl_norms + na);
+            qb_n = __ldg(S.qjl_norms + nb);
+        }
 
         // ---- scores ----
         float c1[4] = {0.f, 0.f, 0.f, 0.f};
@@ -509,10 +524,8 @@ __global__ void __launch_bounds__(kMmaThreads, 3) attn_mma_kernel(const AttnSeq*
             uint32_t ka[16], kb[16];
             dequant16(kwa, ka);
             dequant16(kwb, kb);
-            if (tb + 64 < t1) {  // the next tile's key words
-                load_words(S.k_words + rec_of(tb + 64 + g) * WPH, kwa);
-                load_words(S.k_words + rec_of(tb + 64 + g + 8) * WPH, kwb);
-            }
+            load_words(S.k_words + na * WPH, kwa);  // the next tile's key words
+            load_words(S.k_words + nb * WPH, kwb);
 #pragma unroll
             for (int ks = 0; ks < 8; ++ks) {
                 mma_f16(c1, ka[2 * ks], kb[2 * ks], ka[2 * ks + 1], kb[2 * ks + 1], bq[2 * ks], bq[2 * ks + 1]);
@@ -563,6 +576,9 @@ __global__ void __launch_bounds__(kMmaThreads, 3) attn_mma_kernel(const AttnSeq*
             }
         }
         // P^T fragment: (tokens 2q, 2q+1 | 2q+8, 2q+9 ; head g) from (token g | g+8 ; heads 2q, 2q+1)
+        const float vna = vna_n * (1.0f / kCentroidScale), vnb = vnb_n * (1.0f / kCentroidScale);
+        vna_n = __ldg(S.v_norms + na);
+        vnb_n = __ldg(S.v_norms + nb);
         const uint32_t pb0 = movmatrix_trans(pack_half2(p00 * vna, p01 * vna));
         const uint32_t pb1 = movmatrix_trans(pack_half2(p10 * vnb, p11 * vnb));
 
@@ -571,6 +587,8 @@ __global__ void __launch_bounds__(kMmaThreads, 3) attn_mma_kernel(const AttnSeq*
             uint32_t xa[16], xb[16];
             dequant16(vwa, xa);
             dequant16(vwb, xb);
+            load_words(S.v_words + na * WPH, vwa);  // the next tile's value words
+            load_words(S.v_words + nb * WPH, vwb);
 #pragma unroll
             for (int ks = 0; ks < 8; ++ks) {
                 // V[token x dim] fragment of dim block ks -> V^T[dim x token] fragment
