@@ -224,6 +224,17 @@ int tq_kv_get_fp16(tq_kv_cache_t cache, int layer, int values, int start, int en
 int tq_kv_export(tq_kv_cache_t cache, int layer, uint32_t* k_words, uint32_t* v_words, float* k_norms,
                  float* v_norms, uint32_t* qjl_words, float* qjl_norms);
 
+/** Room for `tokens` tokens of `layer` without further allocation (storage otherwise grows by
+ *  doubling, which copies and synchronises): call once with the expected context length. */
+int tq_kv_reserve(tq_kv_cache_t cache, int layer, int tokens, void* stream);
+
+/** One decode step of a batch: keys / values [n_seqs, heads, head_dim] (DEVICE memory, TQ_F32 or
+ *  TQ_F16), row i appended as one token to caches[i] (same results as n_seqs calls of
+ *  tq_kv_append with one token each, in two kernel launches per 32 sequences).  No counterpart in
+ *  the reference, whose cache holds one sequence. */
+int tq_kv_append_batch(const tq_kv_cache_t* caches, int n_seqs, int layer, const void* keys, const void* values,
+                       int dtype, void* stream);
+
 /** Decode attention for a batch of sequences: hybrid_attention's long-context branch
  *  (src/attention_dispatch.cpp:58-73) computed directly on the compressed cache.
  *  queries [n_seqs, q_heads, head_dim] (TQ_F32 / TQ_F16, rounded to fp16 first) ->

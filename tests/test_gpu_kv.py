@@ -158,3 +158,32 @@ def test_attention_lse_merges_context_parts(tq):
         assert np.allclose(m + np.log(np.sum(np.exp(np.stack(lses) - m), axis=0)), lse_full, rtol=0, atol=2e-3)
     for c in caches:
         c.close()
+
+
+def test_append_batch_equals_single_appends(tq):
+    """A decode step appended to many caches at once stores exactly what one-token appends store,
+    also across the 32-sequence launch boundary and after a reserve()."""
+    import torch
+    rng = np.random.default_rng(31)
+    heads, dim, n = 2, 128, 37
+    a = [tq.TQKVCache(1, heads, dim) for _ in range(n)]
+    b = [tq.TQKVCache(1, heads, dim) for _ in range(n)]
+    for c in a[:5]:
+        c.reserve(0, 1000)
+    prefix = rng.standard_normal((3, heads, dim)).astype(np.float16)
+    for c in a + b:
+        c.append(0, prefix, prefix)
+    for step in range(3):
+        k = rng.standard_normal((n, heads, dim)).astype(np.float16)
+        v = rng.standard_normal((n, heads, dim)).astype(np.float16)
+        tq.append_batch(a, 0, torch.from_numpy(k).cuda(), torch.from_numpy(v).cuda())
+        for i, c in enumerate(b):
+            c.append(0, k[i:i + 1], v[i:i + 1])
+    torch.cuda.synchronize()
+    for ca, cb in zip(a, b):
+        ea, eb = ca.export(0), cb.export(0)
+        assert ea["tokens"] == eb["tokens"] == 6
+        for key in ("k_words", "v_words", "k_norms", "v_norms", "qjl_words", "qjl_norms"):
+            assert bits_equal(ea[key], eb[key]), key
+    for c in a + b:
+        c.close()

@@ -6,5 +6,5 @@ library; the first call does, and raises if it is missing.
 """
 from ._lib import LIB_PATH, TQ_F16, TQ_F32, LibraryMissing, TQError, load  # noqa: F401
 from .api import (Codebook, QuantizedWeight, QuantizerConfig, TQKVCache, TurboQuantLinear,  # noqa: F401
-                  apply_inverse_wht_rotation, apply_wht_rotation, codebook_from_centroids, compressed_attention,
+                  append_batch, apply_inverse_wht_rotation, apply_wht_rotation, codebook_from_centroids, compressed_attention,
                   dequantize_weight, generate_codebook, quantize_weight)

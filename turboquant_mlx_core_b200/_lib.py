@@ -105,6 +105,8 @@ def load() -> C.CDLL:
     sig("tq_kv_append", i, [vp, i, vp, vp, i, i, vp])
     sig("tq_kv_get_fp16", i, [vp, i, i, i, i, vp, vp])
     sig("tq_kv_export", i, [vp, i, vp, vp, vp, vp, vp, vp])
+    sig("tq_kv_reserve", i, [vp, i, i, vp])
+    sig("tq_kv_append_batch", i, [C.POINTER(C.c_void_p), i, i, vp, vp, i, vp])
     sig("tq_kv_attention", i, [C.POINTER(C.c_void_p), i, i, vp, i, i, vp, i, i, i, vp])
     sig("tq_kv_attention_lse", i, [C.POINTER(C.c_void_p), i, i, vp, i, i, vp, vp, i, i, i, vp])
 

@@ -292,6 +292,10 @@ class TQKVCache:
         check(self._L.tq_kv_append(self._h, layer, _ptr(keys), _ptr(values), _dtype_tag(keys), int(keys.shape[0]),
                                    _stream_ptr(stream)), "TQKVCache.append")
 
+    def reserve(self, layer: int, tokens: int, stream=None):
+        """Make room for `tokens` tokens of `layer` up front (growth otherwise doubles and copies)."""
+        check(self._L.tq_kv_reserve(self._h, layer, int(tokens), _stream_ptr(stream)), "TQKVCache.reserve")
+
     def seq_length(self) -> int:
         return self._L.tq_kv_cache_seq_length(self._h)
 
@@ -336,6 +340,17 @@ class TQKVCache:
             self.close()
         except Exception:
             pass
+
+
+def append_batch(caches, layer: int, keys, values, stream=None):
+    """One decode step of a batch: row i of keys / values ([n_seqs, heads, head_dim], device
+    tensors) is appended as one token to caches[i]; two kernel launches per 32 sequences."""
+    L = _lib.load()
+    n = len(caches)
+    if int(keys.shape[0]) != n or int(values.shape[0]) != n:
+        raise ValueError("keys and values must have one row per cache")
+    arr = (C.c_void_p * n)(*[c.handle for c in caches])
+    check(L.tq_kv_append_batch(arr, n, layer, _ptr(keys), _ptr(values), _dtype_tag(keys), _stream_ptr(stream)), "append_batch")
 
 
 def compressed_attention(caches, layer: int, queries, start: int = 0, end: int = -1, use_qjl: bool = False,

@@ -107,6 +107,62 @@ public:
         seq_length_ = std::max(seq_length_, L.num_tokens);
     }
 
+    // Room for `tokens` tokens in `layer` without further allocation (growth otherwise doubles).
+    void reserve_tokens(int layer, int tokens, cudaStream_t st) {
+        TQ_REQUIRE(layer >= 0 && layer < layers_n_, "Layer index out of range");
+        TQ_REQUIRE(tokens >= 0, "reserve: negative token count");
+        TQ_CUDA(cudaSetDevice(device_));
+        LayerKVStorage& L = layers_[static_cast<size_t>(layer)];
+        if (tokens > L.capacity) reserve_exact(L, tokens, st);
+    }
+
+    // One decode step of a batch: token i of keys / values ([n, heads, dim], device memory) is
+    // appended to caches[i].  All caches must share shape and device; one encoder launch for the
+    // keys and one for the values per 32 sequences.
+    static void append_batch(TQKVCache* const* caches, int n, int layer, const void* keys, const void* values, int dtype,
+                             cudaStream_t st) {
+        TQ_REQUIRE(caches && n > 0 && keys && values, "append_batch: bad argument");
+        TQ_REQUIRE(dtype == TQ_F32 || dtype == TQ_F16, "append_batch: keys/values must be fp32 or fp16");
+        TQ_REQUIRE(tq::is_device_pointer(keys) && tq::is_device_pointer(values), "append_batch: keys and values must be device pointers");
+        TQKVCache* c0 = caches[0];
+        TQ_REQUIRE(c0, "append_batch: NULL cache");
+        TQ_REQUIRE(layer >= 0 && layer < c0->layers_n_, "Layer index out of range");
+        TQ_CUDA(cudaSetDevice(c0->device_));
+        const int wph = c0->words_per_head(), qph = c0->qjl_words_per_head();
+        const uint32_t ks = tq::kv_layer_seed(static_cast<uint32_t>(layer), 1);
+        const uint32_t vs = tq::kv_layer_seed(static_cast<uint32_t>(layer), 2);
+        const uint32_t qs = tq::kv_layer_seed(static_cast<uint32_t>(layer), 3);
+        const size_t es = dtype == TQ_F32 ? 4 : 2;
+        const size_t vec_bytes = static_cast<size_t>(c0->heads_) * c0->dim_ * es;
+        for (int b0 = 0; b0 < n; b0 += 32) {
+            const int nb = std::min(32, n - b0);
+            tq::KvEncodeSegment kseg[32], vseg[32];
+            for (int i = 0; i < nb; ++i) {
+                TQKVCache* c = caches[b0 + i];
+                TQ_REQUIRE(c && c->heads_ == c0->heads_ && c->dim_ == c0->dim_ && c->device_ == c0->device_ &&
+                               c->layers_n_ == c0->layers_n_,
+                           "append_batch: caches of one call must share shape and device");
+                LayerKVStorage& L = c->layers_[static_cast<size_t>(layer)];
+                c->reserve(L, L.num_tokens + 1, st);
+                const size_t off = static_cast<size_t>(L.num_tokens) * c->heads_;
+                kseg[i] = {L.k_words.as<uint32_t>() + off * wph, L.k_norms.as<float>() + off,
+                           L.qjl_words.as<uint32_t>() + off * qph, L.qjl_norms.as<float>() + off};
+                vseg[i] = {L.v_words.as<uint32_t>() + off * wph, L.v_norms.as<float>() + off, nullptr, nullptr};
+            }
+            const long n_vec = static_cast<long>(nb) * c0->heads_;
+            const char* kp = static_cast<const char*>(keys) + static_cast<size_t>(b0) * vec_bytes;
+            const char* vp = static_cast<const char*>(values) + static_cast<size_t>(b0) * vec_bytes;
+            tq::launch_kv_encode_segments(kp, dtype == TQ_F16, n_vec, c0->heads_, c0->dim_, ks, qs, true, kseg, nb, st);
+            tq::launch_kv_encode_segments(vp, dtype == TQ_F16, n_vec, c0->heads_, c0->dim_, vs, 0u, false, vseg, nb, st);
+            for (int i = 0; i < nb; ++i) {
+                TQKVCache* c = caches[b0 + i];
+                LayerKVStorage& L = c->layers_[static_cast<size_t>(layer)];
+                L.num_tokens += 1;
+                c->seq_length_ = std::max(c->seq_length_, L.num_tokens);
+            }
+        }
+    }
+
     // fp16 [end-start, heads, dim] into `out` (host or device).
     void get_fp16(int layer, bool values, int start, int end, void* out, cudaStream_t st) {
         TQ_REQUIRE(layer >= 0 && layer < layers_n_, "Layer index out of range");
@@ -174,7 +230,9 @@ private:
     // Grow a layer's buffers to hold `tokens` tokens (capacity doubles; old contents kept).
     void reserve(LayerKVStorage& L, int tokens, cudaStream_t st) {
         if (tokens <= L.capacity) return;
-        int cap = std::max(L.capacity * 2, std::max(tokens, 256));
+        reserve_exact(L, std::max(L.capacity * 2, std::max(tokens, 256)), st);
+    }
+    void reserve_exact(LayerKVStorage& L, int cap, cudaStream_t st) {
         const size_t per = static_cast<size_t>(heads_);
         const size_t old_n = static_cast<size_t>(L.num_tokens) * per;
         auto grow = [&](DeviceBuffer& b, size_t elem_bytes_per_vec) {
@@ -405,6 +463,28 @@ int tq_kv_export(tq_kv_cache_t cache, int layer, uint32_t* k_words, uint32_t* v_
     return guarded<int>(0, -1, [&]() {
         TQ_REQUIRE(cache && cache->cache, "tq_kv_export: NULL cache");
         return cache->cache->export_layer(layer, k_words, v_words, k_norms, v_norms, qjl_words, qjl_norms);
+    });
+}
+
+int tq_kv_reserve(tq_kv_cache_t cache, int layer, int tokens, void* stream) {
+    return guarded<int>(0, -1, [&]() {
+        TQ_REQUIRE(cache && cache->cache, "tq_kv_reserve: NULL cache");
+        cache->cache->reserve_tokens(layer, tokens, static_cast<cudaStream_t>(stream));
+        return 0;
+    });
+}
+
+int tq_kv_append_batch(const tq_kv_cache_t* caches, int n_seqs, int layer, const void* keys, const void* values, int dtype,
+                       void* stream) {
+    return guarded<int>(0, -1, [&]() {
+        TQ_REQUIRE(caches && n_seqs > 0, "tq_kv_append_batch: no caches");
+        std::vector<turboquant::TQKVCache*> cs(static_cast<size_t>(n_seqs));
+        for (int i = 0; i < n_seqs; ++i) {
+            TQ_REQUIRE(caches[i] && caches[i]->cache, "tq_kv_append_batch: NULL cache");
+            cs[i] = caches[i]->cache;
+        }
+        turboquant::TQKVCache::append_batch(cs.data(), n_seqs, layer, keys, values, dtype, static_cast<cudaStream_t>(stream));
+        return 0;
     });
 }
 

@@ -119,33 +119,53 @@ __global__ void __launch_bounds__(256) dequant_kernel(const uint8_t* __restrict_
         sr[j] = __fmul_rn(inv_sqrt, sign_value(seed_r, static_cast<uint32_t>(lane * E + j)));
     }
 
-    for (long blk = warp0; blk < total; blk += n_warps) {
-        const long row = blk / blocks_per_row;
-        const int col = static_cast<int>(blk - row * blocks_per_row) * BS + lane * E;
-        const uint8_t* src = joint + code_offset(row, col, code_tiles_per_row(blocks_per_row * BS));
-        uint8_t code[E];
-        if constexpr (E >= 16) {
+    // A warp takes kAhead consecutive blocks per round and requests all their codes (and norms)
+    // before it transforms the first one: with one 128-byte request per warp in flight the kernel
+    // would be bound by load latency, not bandwidth.
+    constexpr int kAhead = 4;
+    constexpr int W = (E + 3) / 4;  // 32-bit words of codes per lane and block
+    const size_t tiles_per_row = code_tiles_per_row(blocks_per_row * BS);
+    for (long blk0 = warp0 * kAhead; blk0 < total; blk0 += n_warps * kAhead) {
+        uint32_t raw[kAhead][W];
+        float nrm[kAhead];
 #pragma unroll
-            for (int j = 0; j < E; j += 16) {
-                uint4 t = *reinterpret_cast<const uint4*>(src + j);
-                const uint32_t w[4] = {t.x, t.y, t.z, t.w};
+        for (int u = 0; u < kAhead; ++u) {
+            const long blk = blk0 + u;
+            nrm[u] = 0.f;
 #pragma unroll
-                for (int k = 0; k < 16; ++k) code[j + k] = static_cast<uint8_t>(w[k >> 2] >> (8 * (k & 3)));
+            for (int k = 0; k < W; ++k) raw[u][k] = 0u;
+            if (blk < total) {
+                const long row = blk / blocks_per_row;
+                const int col = static_cast<int>(blk - row * blocks_per_row) * BS + lane * E;
+                const uint8_t* src = joint + code_offset(row, col, tiles_per_row);
+                nrm[u] = __ldg(norms + row);
+                if constexpr (E >= 16) {
+#pragma unroll
+                    for (int j = 0; j < E / 16; ++j) {
+                        const uint4 t = __ldg(reinterpret_cast<const uint4*>(src) + j);
+                        raw[u][4 * j] = t.x; raw[u][4 * j + 1] = t.y; raw[u][4 * j + 2] = t.z; raw[u][4 * j + 3] = t.w;
+                    }
+                } else if constexpr (E == 8) {
+                    const uint2 t = __ldg(reinterpret_cast<const uint2*>(src));
+                    raw[u][0] = t.x; raw[u][1] = t.y;
+                } else if constexpr (E == 4) {
+                    raw[u][0] = __ldg(reinterpret_cast<const uint32_t*>(src));
+                } else if constexpr (E == 2) {
+                    raw[u][0] = __ldg(reinterpret_cast<const unsigned short*>(src));
+                } else {
+                    raw[u][0] = src[0];
+                }
             }
-        } else if constexpr (E == 8) {
-            uint2 t = *reinterpret_cast<const uint2*>(src);
-#pragma unroll
-            for (int k = 0; k < 8; ++k) code[k] = static_cast<uint8_t>((k < 4 ? t.x : t.y) >> (8 * (k & 3)));
-        } else if constexpr (E == 4) {
-            uint32_t t = *reinterpret_cast<const uint32_t*>(src);
-#pragma unroll
-            for (int k = 0; k < 4; ++k) code[k] = static_cast<uint8_t>(t >> (8 * k));
-        } else {
-#pragma unroll
-            for (int k = 0; k < E; ++k) code[k] = src[k];
         }
+#pragma unroll
+        for (int u = 0; u < kAhead; ++u) {
+        const long blk = blk0 + u;
+        if (blk >= total) break;
+        uint8_t code[E];
+#pragma unroll
+        for (int k = 0; k < E; ++k) code[k] = static_cast<uint8_t>(raw[u][k >> 2] >> (8 * (k & 3)));
 
-        const float norm = norms[row];
+        const float norm = nrm[u];
         float v[E];
 #pragma unroll
         for (int j = 0; j < E; ++j) v[j] = __fmul_rn(lut[code[j]], inv_scale);
@@ -189,6 +209,7 @@ __global__ void __launch_bounds__(256) dequant_kernel(const uint8_t* __restrict_
         }
 #pragma unroll
         for (int j = 0; j < E; ++j) dst[j] = w[j];
+        }
     }
 }
 

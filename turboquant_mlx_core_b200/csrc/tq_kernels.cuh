@@ -80,6 +80,20 @@ void launch_quantize_weight(const float* d_weight, long out, int in, const float
                             uint32_t seed_p, uint32_t seed_r, uint8_t* d_packed_primary, uint8_t* d_packed_residual,
                             float* d_norms, float* d_orig_norm_tmp, float* d_recon_tmp, cudaStream_t stream);
 
+// tq_kv_kernels.cu — KV-cache encoder with several destinations: the n_vec input vectors
+// ([n_vec, head_dim], contiguous) are cut into segments of vec_per_seg vectors and segment s is
+// written to segs[s] (at most 32 segments per launch).  A decode step that appends one token to
+// many sequences' caches is one launch for the keys and one for the values.
+struct KvEncodeSegment {
+    uint32_t* words;
+    float* norms;
+    uint32_t* qjl_words;  // may be NULL when with_qjl is false
+    float* qjl_norms;
+};
+void launch_kv_encode_segments(const void* x, bool x_is_f16, long n_vec, long vec_per_seg, int head_dim, uint32_t wht_seed,
+                               uint32_t qjl_seed, bool with_qjl, const KvEncodeSegment* segs, int n_segs,
+                               cudaStream_t stream);
+
 // tq_misc.cu — small element-wise helpers.
 void launch_f32_to_f16(const float* in, __half* out, long n, cudaStream_t stream);
 void launch_f16_to_f32(const __half* in, float* out, long n, cudaStream_t stream);

@@ -25,11 +25,24 @@ __device__ __forceinline__ float load_as_f32(const __half* p, size_t i) { return
 // One warp per (token, head) vector of d = 32*E values.  Bit-exact: the two sums of
 // squares are accumulated left to right by one lane, everything else is element-wise
 // or the shared butterfly.
+// Where the encoder writes: the input vectors are cut into segments of vec_per_seg consecutive
+// vectors and segment s goes to seg[s] (one segment for an ordinary append; one per sequence when
+// a decode step appends a token to many caches at once).
+struct KvEncodeDst {
+    uint32_t* words;
+    float* norms;
+    uint32_t* qjl_words;
+    float* qjl_norms;
+};
+constexpr int kKvEncodeMaxSegments = 32;
+struct KvEncodeTable {
+    KvEncodeDst seg[kKvEncodeMaxSegments];
+};
+
 template <int E, typename InT>
 __global__ void __launch_bounds__(128) kv_encode_kernel(const InT* __restrict__ x, long n_vec, uint32_t wht_seed,
                                                         uint32_t qjl_seed, int with_qjl, float scale, float inv_sqrt,
-                                                        uint32_t* __restrict__ words, float* __restrict__ norms,
-                                                        uint32_t* __restrict__ qjl_words, float* __restrict__ qjl_norms) {
+                                                        const __grid_constant__ KvEncodeTable tab, long vec_per_seg) {
     constexpr int D = 32 * E;
     constexpr int WPH = (D + 9) / 10;
     constexpr int QPH = D / 32;
@@ -49,11 +62,19 @@ __global__ void __launch_bounds__(128) kv_encode_kernel(const InT* __restrict__ 
 #pragma unroll
     for (int j = 0; j < E; ++j) sgn[j] = sign_value(wht_seed, static_cast<uint32_t>(lane * E + j));
 
-    for (long vec = warp0; vec < n_vec; vec += n_warps) {
+    for (long gvec = warp0; gvec < n_vec; gvec += n_warps) {
+        // destination of this vector: segment and position inside it
+        const long sidx = gvec / vec_per_seg;
+        const long vec = gvec - sidx * vec_per_seg;
+        const KvEncodeDst& dst = tab.seg[sidx];
+        uint32_t* const words = dst.words;
+        float* const norms = dst.norms;
+        uint32_t* const qjl_words = dst.qjl_words;
+        float* const qjl_norms = dst.qjl_norms;
         float v[E];
 #pragma unroll
         for (int j = 0; j < E; ++j) {
-            v[j] = load_as_f32(x, static_cast<size_t>(vec) * D + lane * E + j);
+            v[j] = load_as_f32(x, static_cast<size_t>(gvec) * D + lane * E + j);
             s_val[wib][lane * E + j] = v[j];
         }
         __syncwarp();
@@ -139,9 +160,22 @@ __global__ void __launch_bounds__(128) kv_decode_kernel(const uint32_t* __restri
         }
         warp_fwht<E>(v, lane);
         const float norm = norms[vec];
+        __align__(16) __half h[E];
 #pragma unroll
-        for (int j = 0; j < E; ++j)
-            out[static_cast<size_t>(vec) * D + lane * E + j] = __float2half_rn(__fmul_rn(__fmul_rn(v[j], sg[j]), norm));
+        for (int j = 0; j < E; ++j) h[j] = __float2half_rn(__fmul_rn(__fmul_rn(v[j], sg[j]), norm));
+        __half* dst = out + static_cast<size_t>(vec) * D + lane * E;
+        constexpr int kBytes = E * 2;
+        if (kBytes % 16 == 0 && reinterpret_cast<uintptr_t>(dst) % 16 == 0) {
+#pragma unroll
+            for (int c = 0; c < (kBytes >= 16 ? kBytes / 16 : 1); ++c) reinterpret_cast<uint4*>(dst)[c] = reinterpret_cast<const uint4*>(h)[c];
+        } else if (kBytes == 8 && reinterpret_cast<uintptr_t>(dst) % 8 == 0) {
+            *reinterpret_cast<uint2*>(dst) = *reinterpret_cast<const uint2*>(h);
+        } else if (kBytes == 4 && reinterpret_cast<uintptr_t>(dst) % 4 == 0) {
+            *reinterpret_cast<uint32_t*>(dst) = *reinterpret_cast<const uint32_t*>(h);
+        } else {
+#pragma unroll
+            for (int j = 0; j < E; ++j) dst[j] = h[j];
+        }
     }
 }
 
@@ -667,18 +701,28 @@ void launch_kv_encode(const void* x, bool x_is_f16, long n_vec, int head_dim, ui
                       bool with_qjl, uint32_t* words, float* norms, uint32_t* qjl_words, float* qjl_norms,
                       cudaStream_t stream) {
     if (n_vec == 0) return;
+    KvEncodeSegment one{words, norms, qjl_words, qjl_norms};
+    launch_kv_encode_segments(x, x_is_f16, n_vec, n_vec, head_dim, wht_seed, qjl_seed, with_qjl, &one, 1, stream);
+}
+
+void launch_kv_encode_segments(const void* x, bool x_is_f16, long n_vec, long vec_per_seg, int head_dim, uint32_t wht_seed,
+                               uint32_t qjl_seed, bool with_qjl, const KvEncodeSegment* segs, int n_segs,
+                               cudaStream_t stream) {
+    if (n_vec == 0) return;
+    TQ_REQUIRE(n_segs >= 1 && n_segs <= kKvEncodeMaxSegments, "kv encode: 1..32 segments per launch");
+    TQ_REQUIRE(vec_per_seg > 0 && (n_vec + vec_per_seg - 1) / vec_per_seg <= n_segs, "kv encode: segments do not cover the input");
+    KvEncodeTable tab{};
+    for (int i = 0; i < n_segs; ++i) tab.seg[i] = KvEncodeDst{segs[i].words, segs[i].norms, segs[i].qjl_words, segs[i].qjl_norms};
     const float scale = std::sqrt(static_cast<float>(head_dim));             // src/kv_cache.cpp:72
     const float inv_sqrt = 1.0f / std::sqrt(static_cast<float>(head_dim));   // src/rotation.cpp:301
     const int grid = grid_for_warps(n_vec, 4, 148 * 16);
 #define TQ_ENC(EV)                                                                                                      \
     if (x_is_f16)                                                                                                       \
         kv_encode_kernel<EV, __half><<<grid, 128, 0, stream>>>(static_cast<const __half*>(x), n_vec, wht_seed, qjl_seed, \
-                                                               with_qjl ? 1 : 0, scale, inv_sqrt, words, norms,          \
-                                                               qjl_words, qjl_norms);                                    \
+                                                               with_qjl ? 1 : 0, scale, inv_sqrt, tab, vec_per_seg);    \
     else                                                                                                                \
         kv_encode_kernel<EV, float><<<grid, 128, 0, stream>>>(static_cast<const float*>(x), n_vec, wht_seed, qjl_seed,   \
-                                                              with_qjl ? 1 : 0, scale, inv_sqrt, words, norms,           \
-                                                              qjl_words, qjl_norms);
+                                                              with_qjl ? 1 : 0, scale, inv_sqrt, tab, vec_per_seg);
     TQ_D_SWITCH(head_dim, TQ_ENC)
 #undef TQ_ENC
     TQ_CUDA(cudaGetLastError());
