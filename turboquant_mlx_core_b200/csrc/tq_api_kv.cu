@@ -279,11 +279,24 @@ void attention_batched(TQKVCache* const* caches, int n_seqs, int layer, const vo
         desc[i] = caches[i]->describe(layer, starts[i], ends[i]);
         max_tok = std::max(max_tok, ends[i] - starts[i]);
     }
-    // enough context splits to fill the machine, at least ~256 tokens each
+    // Context splits.  A CTA handles one (sequence, KV head, query-head group, split); the SMs
+    // hold three such CTAs each, so the launch runs in ceil(CTAs / resident) waves and a wave costs
+    // about (tokens per split + a fixed set-up cost of ~160 tokens' worth).  Pick the split count
+    // that minimises waves x cost, with at least ~256 tokens per split.
     const int G = q_heads / heads;
     const int ctas_per_split = n_seqs * heads * ((G + 7) / 8);
-    int n_splits = std::max(1, std::min((148 * 12 + ctas_per_split - 1) / ctas_per_split, (max_tok + 255) / 256));
-    n_splits = std::min(n_splits, 128);
+    const long resident = static_cast<long>(tq::sm_count(c0->device())) * 3;
+    const int max_splits = std::max(1, std::min(128, max_tok / 256));
+    int n_splits = 1;
+    double best = 1e300;
+    for (int n = 1; n <= max_splits; ++n) {
+        const long waves = (static_cast<long>(ctas_per_split) * n + resident - 1) / resident;
+        const double cost = static_cast<double>(waves) * (static_cast<double>(max_tok) / n + 160.0);
+        if (cost < best * 0.999) {
+            best = cost;
+            n_splits = n;
+        }
+    }
 
     c0->attn_desc().reserve(desc.size() * sizeof(SeqDesc));
     TQ_CUDA(cudaMemcpyAsync(c0->attn_desc().as<void>(), desc.data(), desc.size() * sizeof(SeqDesc), cudaMemcpyHostToDevice, st));
