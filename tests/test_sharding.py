@@ -139,3 +139,31 @@ def test_context_split_merge_gloo():
     for p in procs:
         p.join(60)
     assert res == [(0, True), (1, True)]
+
+
+def test_row_parallel_column_shards_sum_to_the_full_layer(oracle):
+    """Row-parallel split (input features in whole WHT blocks): the dequantised column shards,
+    built with the rescaled norms, multiply the matching slices of x to partial outputs whose sum
+    is the full layer's output."""
+    from turboquant_mlx_core_b200.sharding import col_range, shard_quantized_cols
+    rng = np.random.default_rng(2)
+    rows, cols, bs, world = 24, 768, 128, 3
+    cb = oracle.codebook(4)[0]
+    w = (rng.standard_normal((rows, cols)) * 0.02).astype(np.float16).astype(np.float32)
+    pp, pr, norms, seeds = oracle.quantize_weight(w, cb, cb, 4, 4, bs, True)
+    full = oracle.dequantize_weight(pp, pr, norms, seeds, cb, cb, bs)
+    x = rng.standard_normal((2, cols)).astype(np.float16).astype(np.float32)
+    want = x @ full.T
+    got = np.zeros_like(want)
+    spans = []
+    for r in range(world):
+        spp, spr, snorms, (c0, c1) = shard_quantized_cols(pp, pr, norms, cols, bs, r, world)
+        spans.append((c0, c1))
+        part = oracle.dequantize_weight(np.ascontiguousarray(spp), np.ascontiguousarray(spr), snorms, seeds, cb, cb, bs)
+        assert part.shape == (rows, c1 - c0)
+        # same weights up to fp32 rounding of the rescaled norm and inverse scale (a few 1e-8 on values of 0.08)
+        assert np.max(np.abs(part - full[:, c0:c1])) < 1e-6 * np.max(np.abs(full))
+        got += x[:, c0:c1] @ part.T
+    assert spans[0][0] == 0 and spans[-1][1] == cols and all(a[1] == b[0] for a, b in zip(spans, spans[1:]))
+    assert np.allclose(got, want, rtol=1e-4, atol=1e-6)
+    assert col_range(27648, 128, 7, 8) == (7 * 3456, 8 * 3456)

@@ -181,3 +181,30 @@ class SharedBuffer:
             self._L.tq_shared_close(C.c_void_p(p))
         self._L.tq_shared_free(C.c_void_p(self.local))
         self.local, self._peers, self.ptrs = None, [], []
+
+
+def col_range(in_features: int, block_size: int, rank: int, world: int) -> tuple[int, int]:
+    """Contiguous input-feature range of `rank` for a ROW-parallel linear (o_proj, down_proj):
+    whole WHT blocks, as even as possible, so every rank rotates only its own slice of x."""
+    blocks = in_features // block_size
+    b0 = blocks * rank // world
+    b1 = blocks * (rank + 1) // world
+    return b0 * block_size, b1 * block_size
+
+
+def shard_quantized_cols(packed_primary, packed_residual, norms, in_features: int, block_size: int, rank: int,
+                         world: int):
+    """Column slice of a QuantizedWeight for a row-parallel linear.  The codes of columns
+    [c0, c1) are cut out of both planes (two codes per byte; 5-bit primaries one per byte); the
+    per-row norm is a plain factor of the row, so every rank keeps it - multiplied by
+    sqrt((c1 - c0) / in_features), because a TurboQuantLinear over the slice divides by the
+    square root of ITS in_features.  Each rank then runs an ordinary forward on x[:, c0:c1] and the
+    partial outputs are summed (all-reduce).  Seeds and codebooks are unchanged: the sign pattern
+    repeats per WHT block, so whole blocks carry over."""
+    import numpy as np
+    c0, c1 = col_range(in_features, block_size, rank, world)
+    primary_per_byte = 2 if packed_primary.shape[1] == in_features // 2 else 1
+    pp = packed_primary[:, c0 // primary_per_byte: c1 // primary_per_byte]
+    pr = packed_residual[:, c0 // 2: c1 // 2]
+    scale = np.float32(np.sqrt(np.float32(c1 - c0) / np.float32(in_features)))
+    return pp, pr, (norms * scale).astype(np.float32), (c0, c1)
