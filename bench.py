@@ -12,8 +12,16 @@ HBM.  metric = layer-forwards ("tokens" through this layer) per second.
   python bench.py --impl reference [...]                       the reference's CPU path
 
 Prints ONE JSON line (rank 0).  With N > 1 (torchrun, one rank per GPU) every rank runs
-its own NBUF matrices (independent layers, no collective on this path: weak scaling);
-the row-sharded LM head with its NCCL all-gather is reported under "lm_head".
+its own NBUF matrices (independent layers, no collective on this path: weak scaling).
+
+Secondary measurements ride in the same line (--legs selects, --no-extras drops them):
+  attention      decode attention over the compressed cache, 16 sequences, 4k / 32k / 128k context;
+                 KV heads split over ranks, the context range as well beyond 4 ranks
+  decoder_layer  the seven projections of a Qwen2.5-7B-shaped layer at batch 1 / 8 / 64
+  prefill        2048 activation rows through the tcgen05 GEMM
+  lm_head        151936 x 2048 at batch 1 / 32, rows sharded over the ranks: NCCL all-gather of the
+                 logits, and the fused variant (peer stores from the GEMV + completion flags)
+  side_kernels   dequantise, blocked WHT, KV append (bulk, one token x 16 sequences), KV decode
 """
 from __future__ import annotations
 

@@ -143,15 +143,19 @@ public:
             tq::launch_f32_to_f16(d_xf, x_f16_.as<__half>(), static_cast<long>(nx), st);  // src/dequantizer.cpp:691
             d_x = x_f16_.as<__half>();
         }
+        // A few rows into page-locked host memory: the decode kernel stores them there itself
+        // (8 KB of posted writes cost less than a separate copy); anything larger or pageable is staged.
+        void* y_alias = (!y_dev && batch <= 8) ? tq::pinned_host_device_alias(y) : nullptr;
         __half* d_y;
         if (y_dev) d_y = static_cast<__half*>(y);
+        else if (y_alias) d_y = static_cast<__half*>(y_alias);
         else {
             y_f16_.reserve(ny * sizeof(__half));
             d_y = y_f16_.as<__half>();
         }
         launch_forward(d_x, batch, d_y, st);
         if (!y_dev) {
-            TQ_CUDA(cudaMemcpyAsync(y, d_y, ny * sizeof(__half), cudaMemcpyDeviceToHost, st));
+            if (!y_alias) TQ_CUDA(cudaMemcpyAsync(y, d_y, ny * sizeof(__half), cudaMemcpyDeviceToHost, st));
             // the kernels' error word rides along with the result (no second synchronisation)
             TQ_CUDA(cudaMemcpyAsync(h_status_, status_.as<void>(), sizeof(unsigned int), cudaMemcpyDeviceToHost, st));
             TQ_CUDA(cudaStreamSynchronize(st));

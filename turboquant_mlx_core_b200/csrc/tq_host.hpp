@@ -50,6 +50,18 @@ inline bool is_device_pointer(const void* p) {
     return attr.type == cudaMemoryTypeDevice || attr.type == cudaMemoryTypeManaged;
 }
 
+// For page-locked host memory (cudaHostAlloc / cudaHostRegister, mapped as usual under unified
+// addressing) returns the address a kernel can use for it, else NULL.
+inline void* pinned_host_device_alias(const void* p) {
+    if (!p) return nullptr;
+    cudaPointerAttributes attr{};
+    if (cudaPointerGetAttributes(&attr, p) != cudaSuccess) {
+        cudaGetLastError();
+        return nullptr;
+    }
+    return attr.type == cudaMemoryTypeHost ? attr.devicePointer : nullptr;
+}
+
 class DeviceBuffer {
 public:
     DeviceBuffer() = default;
