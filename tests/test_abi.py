@@ -118,3 +118,23 @@ def test_library_is_standalone():
     out = subprocess.run(["ldd", LIB_PATH], capture_output=True, text=True).stdout
     for banned in ("torch", "mlx", "tq_oracle", "tq_ref", "c10"):
         assert banned not in out
+
+
+def test_headers_are_plain_c(tmp_path):
+    """Both public headers compile as C99 with nothing but the standard headers, and a C
+    translation unit can take the address of every declared function (the drop-in boundary is
+    a C ABI: no C++ and no CUDA types in the signatures)."""
+    import shutil
+    import subprocess
+    gcc = shutil.which("gcc")
+    if gcc is None:
+        pytest.skip("no C compiler")
+    inc = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "include")
+    syms = declared_symbols()
+    src = tmp_path / "abi.c"
+    src.write_text('#include "turboquant_c/turboquant_c.h"\n#include "turboquant_c/turboquant_b200.h"\n'
+                   "const void* table[] = {\n" + "".join(f"    (const void*)&{s},\n" for s in syms) + "};\n"
+                   "int n_symbols(void) { return (int)(sizeof table / sizeof table[0]); }\n")
+    r = subprocess.run([gcc, "-std=c99", "-Wall", "-Werror", "-pedantic", "-Wno-pedantic", "-I", inc, "-c", str(src), "-o",
+                        str(tmp_path / "abi.o")], capture_output=True, text=True)
+    assert r.returncode == 0, r.stderr
