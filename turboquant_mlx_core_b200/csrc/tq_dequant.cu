@@ -213,6 +213,119 @@ __global__ void __launch_bounds__(256) dequant_kernel(const uint8_t* __restrict_
     }
 }
 
+// The same for WHT blocks of up to 256 columns with 8 weights per lane: a warp takes 256
+// consecutive columns of a row (lane l the columns 8l..8l+7: one 8-byte code load, one 16- or
+// 32-byte store), butterfly stages below 8 stay in the lane, the rest are lane exchanges.  Same
+// operations on the same operands in the same order as dequant_kernel, hence the same bits, at
+// less than half the instructions per weight.
+template <typename OutT>
+__global__ void __launch_bounds__(256) dequant_wide_kernel(const uint8_t* __restrict__ joint, const float* __restrict__ norms,
+                                                           const float* __restrict__ tables, OutT* __restrict__ out,
+                                                           long rows, int in, int block, uint32_t seed_p, uint32_t seed_r,
+                                                           int dual, float inv_scale, float inv_sqrt) {
+    __shared__ float lut[512];
+    for (int i = threadIdx.x; i < (dual ? 512 : 256); i += blockDim.x) lut[i] = tables[i];
+    __syncthreads();
+
+    const int lane = threadIdx.x & 31;
+    const long warp0 = (static_cast<long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+    const long n_warps = (static_cast<long>(gridDim.x) * blockDim.x) >> 5;
+    const long groups_per_row = (in + 255) / 256;
+    const long total = rows * groups_per_row;
+    const size_t tiles_per_row = code_tiles_per_row(in);
+
+    // the sign pattern repeats per block and blocks divide 256: it does not depend on the group
+    float sp[8], sr[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        const uint32_t idx = static_cast<uint32_t>((8 * lane + j) & (block - 1));
+        sp[j] = __fmul_rn(inv_sqrt, sign_value(seed_p, idx));
+        sr[j] = __fmul_rn(inv_sqrt, sign_value(seed_r, idx));
+    }
+    const int lane_steps = block >> 3;  // lanes per WHT block
+
+    auto fwht8 = [&](float (&v)[8], unsigned live) {
+#pragma unroll
+        for (int h = 1; h < 8; h <<= 1)
+#pragma unroll
+            for (int i = 0; i < 8; i += 2 * h)
+#pragma unroll
+                for (int j = i; j < i + h; ++j) {
+                    const float a = v[j], b = v[j + h];
+                    v[j] = __fadd_rn(a, b);
+                    v[j + h] = __fsub_rn(a, b);
+                }
+        for (int m = 1; m < lane_steps; m <<= 1) {
+            const bool upper = (lane & m) != 0;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const float o = __shfl_xor_sync(live, v[j], m);
+                v[j] = upper ? __fsub_rn(o, v[j]) : __fadd_rn(v[j], o);
+            }
+        }
+    };
+
+    constexpr int kAhead = 4;
+    for (long g0 = warp0 * kAhead; g0 < total; g0 += n_warps * kAhead) {
+        uint2 raw[kAhead];
+        float nrm[kAhead];
+#pragma unroll
+        for (int u = 0; u < kAhead; ++u) {
+            raw[u] = make_uint2(0u, 0u);
+            nrm[u] = 0.f;
+            const long grp = g0 + u;
+            if (grp < total) {
+                const long row = grp / groups_per_row;
+                const int col = static_cast<int>(grp - row * groups_per_row) * 256 + 8 * lane;
+                nrm[u] = __ldg(norms + row);
+                if (col < in) raw[u] = __ldg(reinterpret_cast<const uint2*>(joint + code_offset(row, col, tiles_per_row)));
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < kAhead; ++u) {
+            const long grp = g0 + u;
+            if (grp >= total) break;
+            const long row = grp / groups_per_row;
+            const int col = static_cast<int>(grp - row * groups_per_row) * 256 + 8 * lane;
+            const unsigned live = __ballot_sync(0xffffffffu, col < in);
+            if (col >= in) continue;  // lanes past the row's end (whole blocks: their partners are out too)
+            uint32_t code[8];
+#pragma unroll
+            for (int k = 0; k < 8; ++k) code[k] = ((k < 4 ? raw[u].x : raw[u].y) >> (8 * (k & 3))) & 0xFFu;
+            float v[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) v[j] = __fmul_rn(lut[code[j]], inv_scale);
+            fwht8(v, live);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) v[j] = __fmul_rn(v[j], sp[j]);
+            if (dual) {
+                float w2[8];
+#pragma unroll
+                for (int j = 0; j < 8; ++j) w2[j] = __fmul_rn(lut[256 + code[j]], inv_scale);
+                fwht8(w2, live);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) v[j] = __fadd_rn(v[j], __fmul_rn(w2[j], sr[j]));
+            }
+            OutT* dst = out + row * in + col;
+            __align__(16) OutT w[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const float f = __fmul_rn(v[j], nrm[u]);
+                if constexpr (sizeof(OutT) == 4) w[j] = f;
+                else w[j] = __float2half_rn(f);
+            }
+            if (reinterpret_cast<uintptr_t>(dst) % 16 == 0) {
+#pragma unroll
+                for (int c = 0; c < static_cast<int>(8 * sizeof(OutT) / 16); ++c)
+                    reinterpret_cast<uint4*>(dst)[c] = reinterpret_cast<const uint4*>(w)[c];
+            } else {
+#pragma unroll
+                for (int j = 0; j < 8; ++j) dst[j] = w[j];
+            }
+        }
+    }
+}
+
 template <typename OutT>
 static void launch_dequant_t(const uint8_t* joint, const float* norms, const float* tables, OutT* out, long rows, int in,
                              uint32_t block, uint32_t seed_p, uint32_t seed_r, bool dual, cudaStream_t stream) {
@@ -223,6 +336,15 @@ static void launch_dequant_t(const uint8_t* joint, const float* norms, const flo
     if (total == 0) return;
     const float inv_scale = 1.0f / std::sqrt(static_cast<float>(in));    // src/dequantizer.cpp:76
     const float inv_sqrt = 1.0f / std::sqrt(static_cast<float>(block));  // src/rotation.cpp:333
+    if (block <= 256) {
+        const long groups = rows * ((in + 255) / 256);
+        const long want_w = (groups + 4 * 8 - 1) / (4 * 8);  // 8 warps per CTA, 4 groups per warp and round
+        const int grid_w = static_cast<int>(want_w < 148L * 8 ? (want_w < 1 ? 1 : want_w) : 148L * 8);
+        dequant_wide_kernel<OutT><<<grid_w, 256, 0, stream>>>(joint, norms, tables, out, rows, in, static_cast<int>(block),
+                                                              seed_p, seed_r, dual ? 1 : 0, inv_scale, inv_sqrt);
+        TQ_CUDA(cudaGetLastError());
+        return;
+    }
     long want = (total + 7) / 8;
     int grid = static_cast<int>(want < 148L * 8 ? want : 148L * 8);
 #define TQ_DQ_CASE(EV)                                                                                            \
