@@ -224,6 +224,18 @@ int tq_kv_get_fp16(tq_kv_cache_t cache, int layer, int values, int start, int en
 int tq_kv_export(tq_kv_cache_t cache, int layer, uint32_t* k_words, uint32_t* v_words, float* k_norms,
                  float* v_norms, uint32_t* qjl_words, float* qjl_norms);
 
+/** TQKVCache::snapshot + snapshot_serialize (src/kv_cache.cpp:509-524, src/cache_snapshot.cpp:62-83):
+ *  the cache's transferable byte stream ("TQCS" header, then one length-prefixed blob per layer
+ *  holding the token count and the six storage arrays), byte-identical to the reference's for the
+ *  same appended data.  Returns the stream's size in bytes (or -1); the stream is written to the
+ *  HOST buffer `out` only when capacity is large enough, so a first call with out = NULL sizes it. */
+long tq_kv_snapshot(tq_kv_cache_t cache, void* out, size_t capacity, uint32_t model_hash, uint32_t codebook_hash);
+/** snapshot_deserialize + TQKVCache::restore (src/cache_snapshot.cpp:85-110, src/kv_cache.cpp:526-545):
+ *  replaces the cache's contents with a stream from tq_kv_snapshot or from the reference.  The
+ *  stream's layer count, head count and head_dim must match the cache; malformed input is refused
+ *  (non-zero) before anything changes. */
+int tq_kv_restore(tq_kv_cache_t cache, const void* data, size_t size);
+
 /** Room for `tokens` tokens of `layer` without further allocation (storage otherwise grows by
  *  doubling, which copies and synchronises): call once with the expected context length. */
 int tq_kv_reserve(tq_kv_cache_t cache, int layer, int tokens, void* stream);

@@ -227,6 +227,9 @@ class Ref(_Base):
         L.ref_kv_seq_length.argtypes = [C.c_void_p]
         L.ref_kv_get_fp16.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, _u16p]
         L.ref_kv_export.argtypes = [C.c_void_p, C.c_int] + [C.c_void_p] * 6
+        L.ref_kv_snapshot.argtypes = [C.c_void_p, C.c_void_p, C.c_long, C.c_uint32, C.c_uint32]
+        L.ref_kv_snapshot.restype = C.c_long
+        L.ref_kv_restore.argtypes = [C.c_void_p, C.c_void_p, C.c_long]
 
     def codebook(self, bits: int):
         c = np.zeros(1 << bits, np.float32)
@@ -317,6 +320,20 @@ class Ref(_Base):
             self.ref.lib.ref_kv_export(self.h, layer, kw.ctypes.data, vw.ctypes.data, kn.ctypes.data,
                                        vn.ctypes.data, qw.ctypes.data, qn.ctypes.data)
             return dict(k_words=kw, v_words=vw, k_norms=kn, v_norms=vn, qjl_words=qw, qjl_norms=qn, tokens=n)
+
+        def snapshot(self, model_hash=0, codebook_hash=0) -> np.ndarray:
+            """The reference's serialized cache snapshot (snapshot() + snapshot_serialize) as bytes."""
+            n = self.ref.lib.ref_kv_snapshot(self.h, None, 0, model_hash, codebook_hash)
+            if n < 0:
+                raise RuntimeError("ref snapshot failed")
+            out = np.zeros(n, np.uint8)
+            self.ref.lib.ref_kv_snapshot(self.h, out.ctypes.data, n, model_hash, codebook_hash)
+            return out
+
+        def restore(self, data: np.ndarray):
+            data = np.ascontiguousarray(data, np.uint8)
+            if self.ref.lib.ref_kv_restore(self.h, data.ctypes.data, data.size):
+                raise ValueError("ref restore failed")
 
     def kv(self, layers, heads, dim):
         return Ref.KV(self, layers, heads, dim)

@@ -255,4 +255,30 @@ int ref_kv_export(void* h, int layer, uint32_t* key_words, uint32_t* value_words
     } catch (...) { return -1; }
 }
 
+// TQKVCache::snapshot + snapshot_serialize (src/kv_cache.cpp:509-524, src/cache_snapshot.cpp:62-83):
+// the transferable byte stream.  Returns the stream's size; writes it when `out` has room.
+long ref_kv_snapshot(void* h, uint8_t* out, long capacity, uint32_t model_hash, uint32_t codebook_hash) {
+    try {
+        auto* k = static_cast<KVHandle*>(h);
+        TQCacheSnapshot snap = k->cache->snapshot();
+        snap.model_hash = model_hash;
+        snap.codebook_hash = codebook_hash;
+        const std::vector<uint8_t> bytes = snapshot_serialize(snap);
+        if (out && capacity >= static_cast<long>(bytes.size())) std::memcpy(out, bytes.data(), bytes.size());
+        return static_cast<long>(bytes.size());
+    } catch (...) { return -1; }
+}
+
+// snapshot_deserialize + TQKVCache::restore (src/cache_snapshot.cpp:85-110, src/kv_cache.cpp:526-545).
+int ref_kv_restore(void* h, const uint8_t* data, long size) {
+    try {
+        auto* k = static_cast<KVHandle*>(h);
+        const std::vector<uint8_t> bytes(data, data + size);
+        const TQCacheSnapshot snap = snapshot_deserialize(bytes);
+        if (snap.num_layers == 0) return 1;
+        k->cache->restore(snap);
+        return 0;
+    } catch (...) { return -1; }
+}
+
 }  // extern "C"

@@ -99,6 +99,8 @@ def main():
             out[f"{name}_{key}"] = ex[key]
         out[f"{name}_keys_fp16"] = kv.get_fp16(lay, False, 0, tokens).view(np.uint16)
         out[f"{name}_values_fp16"] = kv.get_fp16(lay, True, 0, tokens).view(np.uint16)
+        # the reference's serialized snapshot of the whole cache (TQCS stream), with fixed identity hashes
+        out[f"{name}_snapshot"] = kv.snapshot(model_hash=0x1234ABCD, codebook_hash=0x0BADF00D)
         # attention (C restatement; GQA group 7 for the 4x128 case, 1 otherwise)
         q_heads = heads * (7 if heads == 4 else 1)
         rng = np.random.default_rng(seed + 100)

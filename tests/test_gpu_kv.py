@@ -187,3 +187,39 @@ def test_append_batch_equals_single_appends(tq):
             assert bits_equal(ea[key], eb[key]), key
     for c in a + b:
         c.close()
+
+
+def test_snapshot_is_byte_identical_and_restores(tq, golden):
+    """tq_kv_snapshot writes the reference's serialized snapshot byte for byte; restoring it (or
+    the reference's own stream) into a fresh cache reproduces storage and attention."""
+    name, layers, heads, dim, tokens, seed = KV_CASES[0]
+    k, v = kv_inputs(seed, tokens, heads, dim)
+    cache = tq.TQKVCache(layers, heads, dim)
+    cache.append(layers - 1, k[: tokens // 2], v[: tokens // 2])
+    cache.append(layers - 1, k[tokens // 2:], v[tokens // 2:])
+    snap = cache.snapshot(model_hash=0x1234ABCD, codebook_hash=0x0BADF00D)
+    assert bits_equal(snap, golden[f"{name}_snapshot"])
+    other = tq.TQKVCache(layers, heads, dim)
+    other.append(0, k[:3], v[:3])                     # replaced by the restore
+    other.restore(golden[f"{name}_snapshot"])
+    assert other.seq_length() == tokens
+    ea, eb = cache.export(layers - 1), other.export(layers - 1)
+    for key in ("k_words", "v_words", "k_norms", "v_norms", "qjl_words", "qjl_norms"):
+        assert bits_equal(ea[key], eb[key]), key
+    assert other.export(0)["tokens"] == 0
+    q = np.random.default_rng(1).standard_normal((1, heads * 7, dim)).astype(np.float16)
+    a = tq.compressed_attention([cache], layers - 1, q, use_qjl=True)
+    b = tq.compressed_attention([other], layers - 1, q, use_qjl=True)
+    assert bits_equal(a, b)
+    other.append(layers - 1, k[:1], v[:1])            # still appendable
+    assert other.seq_length() == tokens + 1
+    # malformed streams are refused and leave the cache as it was
+    for bad in (snap[:40], np.concatenate([snap[:8], snap[8:] ^ 0]).astype(np.uint8)[:-5], np.zeros(64, np.uint8)):
+        with pytest.raises(ValueError):
+            other.restore(bad)
+    wrong = tq.TQKVCache(layers, heads * 2, dim)
+    with pytest.raises(ValueError):
+        wrong.restore(snap)
+    assert other.seq_length() == tokens + 1
+    for c in (cache, other, wrong):
+        c.close()

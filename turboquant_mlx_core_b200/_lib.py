@@ -105,6 +105,8 @@ def load() -> C.CDLL:
     sig("tq_kv_append", i, [vp, i, vp, vp, i, i, vp])
     sig("tq_kv_get_fp16", i, [vp, i, i, i, i, vp, vp])
     sig("tq_kv_export", i, [vp, i, vp, vp, vp, vp, vp, vp])
+    sig("tq_kv_snapshot", C.c_long, [vp, vp, C.c_size_t, u32, u32])
+    sig("tq_kv_restore", i, [vp, vp, C.c_size_t])
     sig("tq_kv_reserve", i, [vp, i, i, vp])
     sig("tq_kv_append_batch", i, [C.POINTER(C.c_void_p), i, i, vp, vp, i, vp])
     sig("tq_kv_attention", i, [C.POINTER(C.c_void_p), i, i, vp, i, i, vp, i, i, i, vp])

@@ -292,6 +292,23 @@ class TQKVCache:
         check(self._L.tq_kv_append(self._h, layer, _ptr(keys), _ptr(values), _dtype_tag(keys), int(keys.shape[0]),
                                    _stream_ptr(stream)), "TQKVCache.append")
 
+    def snapshot(self, model_hash: int = 0, codebook_hash: int = 0) -> np.ndarray:
+        """The transferable byte stream of the whole cache (TQKVCache::snapshot + snapshot_serialize,
+        src/kv_cache.cpp:509-524, src/cache_snapshot.cpp:62-83), as a uint8 array."""
+        n = self._L.tq_kv_snapshot(self._h, None, 0, model_hash, codebook_hash)
+        if n < 0:
+            raise _lib.TQError("TQKVCache.snapshot: " + _lib.last_error())
+        out = np.zeros(n, np.uint8)
+        if self._L.tq_kv_snapshot(self._h, _ptr(out), n, model_hash, codebook_hash) != n:
+            raise _lib.TQError("TQKVCache.snapshot: " + _lib.last_error())
+        return out
+
+    def restore(self, data):
+        """Replace the contents with a snapshot stream (ours or the reference's)."""
+        data = np.ascontiguousarray(data, np.uint8)
+        if self._L.tq_kv_restore(self._h, _ptr(data), data.size) != 0:
+            raise ValueError("TQKVCache.restore: " + _lib.last_error())
+
     def reserve(self, layer: int, tokens: int, stream=None):
         """Make room for `tokens` tokens of `layer` up front (growth otherwise doubles and copies)."""
         check(self._L.tq_kv_reserve(self._h, layer, int(tokens), _stream_ptr(stream)), "TQKVCache.reserve")

@@ -6,7 +6,9 @@
 // (src/attention_dispatch.cpp:58-73).  One cache = one sequence, as in the reference;
 // a decode batch is a set of caches attended in one launch.
 #include <algorithm>
+#include <array>
 #include <cmath>
+#include <cstring>
 
 #include "tq_host.hpp"
 #include "tq_kernels.cuh"
@@ -209,6 +211,102 @@ public:
         copy(qjl_words, L.qjl_words, n * qjl_words_per_head() * 4);
         copy(qjl_norms, L.qjl_norms, n * 4);
         return L.num_tokens;
+    }
+
+    // ---- snapshot stream (src/cache_snapshot.cpp:5-31, src/kv_cache.cpp:401-412) ----
+    // header: "TQCS", layers, positions, head_dim, heads, kv_bits (as u32), model hash, codebook hash;
+    // per layer: blob bytes, then the blob = token count followed by six length-prefixed arrays
+    // (key words, value words, key norms, value norms, sign words, sign norms) in storage order.
+    size_t snapshot_bytes() const {
+        size_t total = 8 * 4;
+        for (const LayerKVStorage& L : layers_) total += 4 + layer_blob_bytes(L);
+        return total;
+    }
+    size_t layer_blob_bytes(const LayerKVStorage& L) const {
+        const size_t n = static_cast<size_t>(L.num_tokens) * heads_;
+        return 4 + 6 * 4 + n * (2 * static_cast<size_t>(words_per_head()) + qjl_words_per_head() + 3) * 4;
+    }
+    // Writes the stream into host memory `out` (snapshot_bytes() bytes).
+    void snapshot_to(uint8_t* out, uint32_t model_hash, uint32_t codebook_hash) {
+        TQ_CUDA(cudaSetDevice(device_));
+        TQ_CUDA(cudaDeviceSynchronize());
+        size_t pos = 0;
+        auto put = [&](uint32_t v) { std::memcpy(out + pos, &v, 4); pos += 4; };
+        put(0x53435154u);  // 'T','Q','C','S'
+        put(static_cast<uint32_t>(layers_n_));
+        put(static_cast<uint32_t>(seq_length_));
+        put(static_cast<uint32_t>(dim_));
+        put(static_cast<uint32_t>(heads_));
+        put(static_cast<uint32_t>(kv_bits_) & 0xFFu);
+        put(model_hash);
+        put(codebook_hash);
+        for (const LayerKVStorage& L : layers_) {
+            put(static_cast<uint32_t>(layer_blob_bytes(L)));
+            put(static_cast<uint32_t>(L.num_tokens));
+            const size_t n = static_cast<size_t>(L.num_tokens) * heads_;
+            auto span = [&](const DeviceBuffer& src, size_t bytes) {
+                put(static_cast<uint32_t>(bytes));
+                if (bytes) TQ_CUDA(cudaMemcpy(out + pos, src.as<void>(), bytes, cudaMemcpyDeviceToHost));
+                pos += bytes;
+            };
+            span(L.k_words, n * words_per_head() * 4);
+            span(L.v_words, n * words_per_head() * 4);
+            span(L.k_norms, n * 4);
+            span(L.v_norms, n * 4);
+            span(L.qjl_words, n * qjl_words_per_head() * 4);
+            span(L.qjl_norms, n * 4);
+        }
+    }
+    // Replaces the cache contents with a stream written by snapshot_to (or by the reference's
+    // snapshot_serialize).  The geometry must match this cache; malformed input is refused before
+    // anything is changed.
+    void restore_from(const uint8_t* data, size_t size) {
+        size_t pos = 0;
+        auto get = [&](uint32_t& v) {
+            TQ_REQUIRE(pos + 4 <= size, "restore: truncated snapshot");
+            std::memcpy(&v, data + pos, 4);
+            pos += 4;
+        };
+        uint32_t magic, layers, positions, dim, heads, bits, mh, ch;
+        get(magic); get(layers); get(positions); get(dim); get(heads); get(bits); get(mh); get(ch);
+        TQ_REQUIRE(magic == 0x53435154u, "restore: not a cache snapshot");
+        TQ_REQUIRE(static_cast<int>(layers) == layers_n_ && static_cast<int>(dim) == dim_ && static_cast<int>(heads) == heads_,
+                   "restore: snapshot geometry differs from this cache");
+        struct Span { size_t off, bytes; };
+        std::vector<std::array<Span, 6>> spans(layers);
+        std::vector<uint32_t> tokens(layers);
+        for (uint32_t l = 0; l < layers; ++l) {
+            uint32_t blob;
+            get(blob);
+            TQ_REQUIRE(pos + blob <= size, "restore: truncated layer blob");
+            const size_t end = pos + blob;
+            get(tokens[l]);
+            const size_t n = static_cast<size_t>(tokens[l]) * heads_;
+            const size_t want[6] = {n * words_per_head() * 4, n * words_per_head() * 4, n * 4, n * 4,
+                                    n * qjl_words_per_head() * 4, n * 4};
+            for (int i = 0; i < 6; ++i) {
+                uint32_t bytes;
+                get(bytes);
+                TQ_REQUIRE(bytes == want[i] && pos + bytes <= end, "restore: array size does not match the token count");
+                spans[l][i] = Span{pos, bytes};
+                pos += bytes;
+            }
+            TQ_REQUIRE(pos == end, "restore: trailing bytes in a layer blob");
+        }
+        TQ_CUDA(cudaSetDevice(device_));
+        TQ_CUDA(cudaDeviceSynchronize());
+        seq_length_ = 0;
+        for (uint32_t l = 0; l < layers; ++l) {
+            LayerKVStorage& L = layers_[l];
+            L.num_tokens = 0;
+            reserve(L, static_cast<int>(tokens[l]), nullptr);
+            DeviceBuffer* dst[6] = {&L.k_words, &L.v_words, &L.k_norms, &L.v_norms, &L.qjl_words, &L.qjl_norms};
+            for (int i = 0; i < 6; ++i)
+                if (spans[l][i].bytes)
+                    TQ_CUDA(cudaMemcpy(dst[i]->as<void>(), data + spans[l][i].off, spans[l][i].bytes, cudaMemcpyHostToDevice));
+            L.num_tokens = static_cast<int>(tokens[l]);
+            seq_length_ = std::max(seq_length_, L.num_tokens);
+        }
     }
 
     SeqDesc describe(int layer, int start, int end) const {
@@ -476,6 +574,27 @@ int tq_kv_export(tq_kv_cache_t cache, int layer, uint32_t* k_words, uint32_t* v_
     return guarded<int>(0, -1, [&]() {
         TQ_REQUIRE(cache && cache->cache, "tq_kv_export: NULL cache");
         return cache->cache->export_layer(layer, k_words, v_words, k_norms, v_norms, qjl_words, qjl_norms);
+    });
+}
+
+long tq_kv_snapshot(tq_kv_cache_t cache, void* out, size_t capacity, uint32_t model_hash, uint32_t codebook_hash) {
+    return guarded<long>(0, -1, [&]() -> long {
+        TQ_REQUIRE(cache && cache->cache, "tq_kv_snapshot: NULL cache");
+        const size_t need = cache->cache->snapshot_bytes();
+        if (out != nullptr && capacity >= need) {
+            TQ_REQUIRE(!tq::is_device_pointer(out), "tq_kv_snapshot: the stream is written to host memory");
+            cache->cache->snapshot_to(static_cast<uint8_t*>(out), model_hash, codebook_hash);
+        }
+        return static_cast<long>(need);
+    });
+}
+
+int tq_kv_restore(tq_kv_cache_t cache, const void* data, size_t size) {
+    return guarded<int>(0, -1, [&]() {
+        TQ_REQUIRE(cache && cache->cache, "tq_kv_restore: NULL cache");
+        TQ_REQUIRE(data != nullptr && !tq::is_device_pointer(data), "tq_kv_restore: the stream is read from host memory");
+        cache->cache->restore_from(static_cast<const uint8_t*>(data), size);
+        return 0;
     });
 }
 
