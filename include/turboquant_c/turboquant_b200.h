@@ -236,6 +236,17 @@ long tq_kv_snapshot(tq_kv_cache_t cache, void* out, size_t capacity, uint32_t mo
  *  (non-zero) before anything changes. */
 int tq_kv_restore(tq_kv_cache_t cache, const void* data, size_t size);
 
+/** Which decode-attention kernel calls that name this cache FIRST use for head_dim 128:
+ *  0 chooses by job size (default), 1 the load-based kernel, 2 the bulk-copy pipeline (cp.async.bulk
+ *  + mbarrier ring; applies to 1, 2 or a multiple of 4 KV heads, otherwise 1 is used).  Results of
+ *  the two agree to rounding (different split of the context); the knob exists for tuning and tests. */
+int tq_kv_set_attention_kernel(tq_kv_cache_t cache, int kernel);
+/** Non-zero (message via tq_last_error) if an attention call on this cache that has finished
+ *  reported a device-side failure (a bounded wait of the pipeline kernel ran out); clears the
+ *  report.  Calls with host outputs check this themselves; callers with device outputs call it
+ *  after synchronising their stream. */
+int tq_kv_attention_status(tq_kv_cache_t cache);
+
 /** Room for `tokens` tokens of `layer` without further allocation (storage otherwise grows by
  *  doubling, which copies and synchronises): call once with the expected context length. */
 int tq_kv_reserve(tq_kv_cache_t cache, int layer, int tokens, void* stream);

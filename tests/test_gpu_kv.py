@@ -223,3 +223,53 @@ def test_snapshot_is_byte_identical_and_restores(tq, golden):
     assert other.seq_length() == tokens + 1
     for c in (cache, other, wrong):
         c.close()
+
+
+@pytest.mark.parametrize("heads,q_heads", [(1, 4), (2, 14), (4, 28), (8, 32), (3, 6), (12, 12)])
+def test_attention_head_counts_and_ragged_ranges(tq, oracle, heads, q_heads):
+    """head_dim 128 over every way the cache is fetched: all heads of a 16-token tile as one slab
+    (1, 2, 4 KV heads), a group of four heads as per-token rows (8, 12), and the load-based kernel
+    (3); token ranges that start and end inside a tile, and shorter than one tile."""
+    rng = np.random.default_rng(heads * 100 + q_heads)
+    dim, n = 128, 333
+    k, v = kv_inputs(int(rng.integers(1 << 30)), n, heads, dim)
+    c = tq.TQKVCache(1, heads, dim)
+    c.append(0, k, v)
+    ex = c.export(0)
+    q = rng.standard_normal((1, q_heads, dim)).astype(np.float16)
+    for start, end, use_qjl in [(0, n, True), (0, n, False), (5, 330, True), (17, 30, True), (32, 48, False), (331, 333, True)]:
+        # the automatic choice would run a job this small on the load-based kernel: ask for the pipeline
+        c.set_attention_kernel(c.ATTENTION_PIPELINE)
+        out = tq.compressed_attention([c], 0, q, start=start, end=end, use_qjl=use_qjl)
+        c.set_attention_kernel(c.ATTENTION_LOADS)
+        other = tq.compressed_attention([c], 0, q, start=start, end=end, use_qjl=use_qjl)
+        assert rel_l2(out[0], other[0].astype(np.float32)) < ATTN_TOL
+        want = oracle.attention(q[0].astype(np.float32), heads, ex["k_words"], ex["k_norms"], ex["v_words"], ex["v_norms"],
+                                ex["qjl_words"], ex["qjl_norms"], layer=0, start=start, end=end, use_qjl=use_qjl)
+        assert np.all(np.isfinite(out.astype(np.float32)))
+        assert rel_l2(out[0], want) < ATTN_TOL, (start, end, use_qjl, rel_l2(out[0], want))
+    c.close()
+
+
+def test_attention_kernel_choice_is_automatic_for_long_batches(tq):
+    """40 sequences x 8192 tokens fill every CTA slot with 512 tokens or more: the automatic choice is the
+    pipeline kernel; it agrees with the load-based kernel, leaves the status clean, and the knob refuses
+    unknown values."""
+    heads, dim, q_heads, n, n_seqs = 4, 128, 28, 8192, 40
+    rng = np.random.default_rng(21)
+    k, v = kv_inputs(77, n, heads, dim)
+    c = tq.TQKVCache(1, heads, dim)
+    c.append(0, k, v)
+    caches = [c] * n_seqs                      # the same storage read by every sequence of the batch
+    q = rng.standard_normal((n_seqs, q_heads, dim)).astype(np.float16)
+    auto = tq.compressed_attention(caches, 0, q)
+    c.set_attention_kernel(c.ATTENTION_LOADS)
+    loads = tq.compressed_attention(caches, 0, q)
+    c.set_attention_kernel(c.ATTENTION_PIPELINE)
+    pipe = tq.compressed_attention(caches, 0, q)
+    c.check_attention_status()
+    assert rel_l2(auto, loads.astype(np.float32)) < ATTN_TOL
+    assert np.array_equal(auto.view(np.uint16), pipe.view(np.uint16))    # automatic == pipeline here
+    with pytest.raises(tq.TQError):
+        c.set_attention_kernel(7)
+    c.close()

@@ -108,6 +108,8 @@ def load() -> C.CDLL:
     sig("tq_kv_snapshot", C.c_long, [vp, vp, C.c_size_t, u32, u32])
     sig("tq_kv_restore", i, [vp, vp, C.c_size_t])
     sig("tq_kv_reserve", i, [vp, i, i, vp])
+    sig("tq_kv_set_attention_kernel", i, [vp, i])
+    sig("tq_kv_attention_status", i, [vp])
     sig("tq_kv_append_batch", i, [C.POINTER(C.c_void_p), i, i, vp, vp, i, vp])
     sig("tq_kv_attention", i, [C.POINTER(C.c_void_p), i, i, vp, i, i, vp, i, i, i, vp])
     sig("tq_kv_attention_lse", i, [C.POINTER(C.c_void_p), i, i, vp, i, i, vp, vp, i, i, i, vp])

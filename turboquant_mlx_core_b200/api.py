@@ -313,6 +313,17 @@ class TQKVCache:
         """Make room for `tokens` tokens of `layer` up front (growth otherwise doubles and copies)."""
         check(self._L.tq_kv_reserve(self._h, layer, int(tokens), _stream_ptr(stream)), "TQKVCache.reserve")
 
+    ATTENTION_AUTO, ATTENTION_LOADS, ATTENTION_PIPELINE = 0, 1, 2
+
+    def set_attention_kernel(self, kernel: int):
+        """Decode-attention kernel for calls that name this cache first: automatic (by job size),
+        the load-based kernel, or the bulk-copy pipeline."""
+        check(self._L.tq_kv_set_attention_kernel(self._h, int(kernel)), "TQKVCache.set_attention_kernel")
+
+    def check_attention_status(self):
+        """Raise if a finished attention call on this cache reported a device-side failure."""
+        check(self._L.tq_kv_attention_status(self._h), "TQKVCache.check_attention_status")
+
     def seq_length(self) -> int:
         return self._L.tq_kv_cache_seq_length(self._h)
 

@@ -9,6 +9,7 @@
 #include <array>
 #include <cmath>
 #include <cstring>
+#include <string>
 
 #include "tq_host.hpp"
 #include "tq_kernels.cuh"
@@ -24,8 +25,9 @@ void launch_kv_decode_f16(const uint32_t* words, const float* norms, long n_vec,
                           __half* out, cudaStream_t stream);
 size_t attn_scratch_bytes(int n_seqs, int q_heads, int head_dim, int n_splits);
 void launch_kv_attention(const void* d_seqs, int n_seqs, const void* q, bool q_is_f16, int q_heads, int kv_heads,
-                         int head_dim, int n_splits, uint32_t k_seed, uint32_t v_seed, uint32_t qjl_seed, bool use_qjl,
-                         void* scratch, __half* out, float* lse, cudaStream_t stream);
+                         int head_dim, AttnPlan plan, uint32_t k_seed, uint32_t v_seed, uint32_t qjl_seed, bool use_qjl,
+                         void* scratch, __half* out, float* lse, unsigned int* status, cudaStream_t stream);
+AttnPlan attn_make_plan(int n_seqs, int q_heads, int kv_heads, int head_dim, int max_tok, int sm_count, int kernel);
 }  // namespace tq
 
 namespace turboquant {
@@ -323,6 +325,36 @@ public:
     DeviceBuffer& attn_q() { return attn_q_; }
     DeviceBuffer& attn_out() { return attn_out_; }
     DeviceBuffer& attn_lse() { return attn_lse_; }
+    int attention_kernel() const { return attention_kernel_; }
+    void set_attention_kernel(int k) {
+        TQ_REQUIRE(k >= 0 && k <= 2, "attention kernel: 0 (automatic), 1 (load-based) or 2 (bulk-copy pipeline)");
+        attention_kernel_ = k;
+    }
+    // Status word of the attention kernels: page-locked host memory that the device writes
+    // directly (only when a bounded wait ran out), so reading it costs the host nothing.
+    unsigned int* attn_status_device() {
+        if (!h_attn_status_) {
+            TQ_CUDA(cudaMallocHost(&h_attn_status_, sizeof(unsigned int)));
+            *h_attn_status_ = 0u;
+        }
+        void* alias = tq::pinned_host_device_alias(h_attn_status_);
+        TQ_REQUIRE(alias != nullptr, "attention: the status word is not mapped for the device");
+        return static_cast<unsigned int*>(alias);
+    }
+    // Throws when an attention launch that has finished reported a failure (and clears the report).
+    ~TQKVCache() {
+        if (h_attn_status_) cudaFreeHost(h_attn_status_);
+    }
+    TQKVCache(const TQKVCache&) = delete;
+    TQKVCache& operator=(const TQKVCache&) = delete;
+    void check_attention_status() {
+        if (h_attn_status_ && *static_cast<volatile unsigned int*>(h_attn_status_) != 0u) {
+            const unsigned int code = *h_attn_status_;
+            *h_attn_status_ = 0u;
+            throw Error("attention: a bounded wait in the kernel ran out (device status " + std::to_string(code) +
+                        "); the output of that call is not valid");
+        }
+    }
 
 private:
     // Grow a layer's buffers to hold `tokens` tokens (capacity doubles; old contents kept).
@@ -331,6 +363,8 @@ private:
         reserve_exact(L, std::max(L.capacity * 2, std::max(tokens, 256)), st);
     }
     void reserve_exact(LayerKVStorage& L, int cap, cudaStream_t st) {
+        // whole 16-token tiles: the attention kernel fetches the cache a tile at a time
+        cap = (cap + 15) / 16 * 16;
         const size_t per = static_cast<size_t>(heads_);
         const size_t old_n = static_cast<size_t>(L.num_tokens) * per;
         auto grow = [&](DeviceBuffer& b, size_t elem_bytes_per_vec) {
@@ -354,6 +388,8 @@ private:
     std::vector<LayerKVStorage> layers_;
     DeviceBuffer stage_k_, stage_v_;
     DeviceBuffer attn_scratch_, attn_desc_, attn_q_, attn_out_, attn_lse_;
+    unsigned int* h_attn_status_ = nullptr;
+    int attention_kernel_ = 0;
 };
 
 // Attention of one query position per sequence over [start, end) of each cache.
@@ -368,6 +404,7 @@ void attention_batched(TQKVCache* const* caches, int n_seqs, int layer, const vo
     TQ_REQUIRE(q_heads > 0 && q_heads % heads == 0, "attention: query heads must be a multiple of KV heads");
     TQ_REQUIRE(dim <= 256, "attention: head_dim above 256 is not supported");
     TQ_CUDA(cudaSetDevice(c0->device()));
+    c0->check_attention_status();   // a failure of an earlier asynchronous call
     std::vector<SeqDesc> desc(static_cast<size_t>(n_seqs));
     int max_tok = 0;
     for (int i = 0; i < n_seqs; ++i) {
@@ -377,24 +414,8 @@ void attention_batched(TQKVCache* const* caches, int n_seqs, int layer, const vo
         desc[i] = caches[i]->describe(layer, starts[i], ends[i]);
         max_tok = std::max(max_tok, ends[i] - starts[i]);
     }
-    // Context splits.  A CTA handles one (sequence, KV head, query-head group, split); the SMs
-    // hold three such CTAs each, so the launch runs in ceil(CTAs / resident) waves and a wave costs
-    // about (tokens per split + a fixed set-up cost of ~160 tokens' worth).  Pick the split count
-    // that minimises waves x cost, with at least ~256 tokens per split.
-    const int G = q_heads / heads;
-    const int ctas_per_split = n_seqs * heads * ((G + 7) / 8);
-    const long resident = static_cast<long>(tq::sm_count(c0->device())) * 3;
-    const int max_splits = std::max(1, std::min(128, max_tok / 256));
-    int n_splits = 1;
-    double best = 1e300;
-    for (int n = 1; n <= max_splits; ++n) {
-        const long waves = (static_cast<long>(ctas_per_split) * n + resident - 1) / resident;
-        const double cost = static_cast<double>(waves) * (static_cast<double>(max_tok) / n + 160.0);
-        if (cost < best * 0.999) {
-            best = cost;
-            n_splits = n;
-        }
-    }
+    const tq::AttnPlan plan = tq::attn_make_plan(n_seqs, q_heads, heads, dim, max_tok, tq::sm_count(c0->device()), c0->attention_kernel());
+    const int n_splits = plan.n_splits;
 
     c0->attn_desc().reserve(desc.size() * sizeof(SeqDesc));
     TQ_CUDA(cudaMemcpyAsync(c0->attn_desc().as<void>(), desc.data(), desc.size() * sizeof(SeqDesc), cudaMemcpyHostToDevice, st));
@@ -420,15 +441,19 @@ void attention_batched(TQKVCache* const* caches, int n_seqs, int layer, const vo
         d_lse = c0->attn_lse().as<float>();
     }
     c0->attn_scratch().reserve(tq::attn_scratch_bytes(n_seqs, q_heads, dim, n_splits));
-    tq::launch_kv_attention(c0->attn_desc().as<void>(), n_seqs, d_q, q_dtype == TQ_F16, q_heads, heads, dim, n_splits,
+    tq::launch_kv_attention(c0->attn_desc().as<void>(), n_seqs, d_q, q_dtype == TQ_F16, q_heads, heads, dim, plan,
                             tq::kv_layer_seed(static_cast<uint32_t>(layer), 1), tq::kv_layer_seed(static_cast<uint32_t>(layer), 2),
-                            tq::kv_layer_seed(static_cast<uint32_t>(layer), 3), use_qjl, c0->attn_scratch().as<void>(), d_out, d_lse, st);
+                            tq::kv_layer_seed(static_cast<uint32_t>(layer), 3), use_qjl, c0->attn_scratch().as<void>(), d_out, d_lse,
+                            c0->attn_status_device(), st);
     // desc was copied from pageable host memory: the copy has been staged by the time
     // cudaMemcpyAsync returned, so `desc` may die here.
     const bool lse_host = lse_out != nullptr && d_lse != lse_out;
     if (lse_host) TQ_CUDA(cudaMemcpyAsync(lse_out, d_lse, n_lse * sizeof(float), cudaMemcpyDeviceToHost, st));
     if (!out_dev) TQ_CUDA(cudaMemcpyAsync(out, d_out, n_q * sizeof(__half), cudaMemcpyDeviceToHost, st));
-    if (!out_dev || lse_host) TQ_CUDA(cudaStreamSynchronize(st));
+    if (!out_dev || lse_host) {
+        TQ_CUDA(cudaStreamSynchronize(st));
+        c0->check_attention_status();
+    }
 }
 
 }  // namespace turboquant
@@ -594,6 +619,22 @@ int tq_kv_restore(tq_kv_cache_t cache, const void* data, size_t size) {
         TQ_REQUIRE(cache && cache->cache, "tq_kv_restore: NULL cache");
         TQ_REQUIRE(data != nullptr && !tq::is_device_pointer(data), "tq_kv_restore: the stream is read from host memory");
         cache->cache->restore_from(static_cast<const uint8_t*>(data), size);
+        return 0;
+    });
+}
+
+int tq_kv_set_attention_kernel(tq_kv_cache_t cache, int kernel) {
+    return guarded<int>(0, -1, [&]() {
+        TQ_REQUIRE(cache && cache->cache, "tq_kv_set_attention_kernel: NULL cache");
+        cache->cache->set_attention_kernel(kernel);
+        return 0;
+    });
+}
+
+int tq_kv_attention_status(tq_kv_cache_t cache) {
+    return guarded<int>(0, -1, [&]() {
+        TQ_REQUIRE(cache && cache->cache, "tq_kv_attention_status: NULL cache");
+        cache->cache->check_attention_status();
         return 0;
     });
 }

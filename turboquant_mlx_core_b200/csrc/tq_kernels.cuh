@@ -84,6 +84,12 @@ void launch_quantize_weight(const float* d_weight, long out, int in, const float
 // ([n_vec, head_dim], contiguous) are cut into segments of vec_per_seg vectors and segment s is
 // written to segs[s] (at most 32 segments per launch).  A decode step that appends one token to
 // many sequences' caches is one launch for the keys and one for the values.
+// How one decode-attention call runs (attn_make_plan in tq_kv_kernels.cu).
+struct AttnPlan {
+    int n_splits;     // context splits per sequence
+    int pipe_heads;   // KV heads per CTA of the bulk-copy pipeline kernel; 0: load-based kernels
+};
+
 struct KvEncodeSegment {
     uint32_t* words;
     float* norms;

@@ -679,6 +679,394 @@ __global__ void __launch_bounds__(kMmaThreads, 3) attn_mma_kernel(const AttnSeq*
     }
 }
 
+// ---- decode attention, bulk-copy pipeline (head_dim 128) ----------------------------------------
+// Same arithmetic as attn_mma_kernel, different data movement: a CTA owns a token range for GH KV heads at once,
+// one warp per head.  The token-major storage makes the records of 16 tokens x all heads one
+// contiguous slab per array, so a tile is fetched by six cp.async.bulk copies (key words, value
+// words, sign words, three norm arrays) that complete on an mbarrier; a ring of kPipeStages tiles
+// is in flight, no cache word passes through a register on its way in, and the warps read their
+// records from shared memory without bank conflicts (token stride GH*13 words = 20 mod 32 for
+// four heads).  With more KV heads than GH a CTA takes a group of GH heads and the tile is fetched
+// as 16 per-token rows per array instead (16 lanes issue them).  Tiles are aligned to multiples
+// of 16 tokens from the start of the layer's storage, whose capacity is a multiple of 16 tokens,
+// so every copy source is 16-byte aligned and inside the allocation; tokens outside [start, end)
+// are masked.  Every mbarrier wait is bounded: on a time-out the CTA raises *status, lets the
+// copies in flight land, and returns without writing a result.
+constexpr int kPipeStages = 4;
+constexpr float kSoftmaxSlack = 2.0f;
+constexpr int kPipeWarpsPerSm = 16;   // 128 registers per thread
+constexpr unsigned long long kPipeWaitLimitNs = 200ull * 1000 * 1000;
+
+__device__ __forceinline__ unsigned long long pipe_timer_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+__device__ __forceinline__ bool pipe_wait(uint32_t bar, uint32_t parity, volatile unsigned int* abort_flag) {
+    unsigned long long t0 = 0;
+    for (uint32_t spin = 0;; ++spin) {
+        uint32_t done;
+        asm volatile("{ .reg .pred p; mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2; selp.u32 %0, 1, 0, p; }"
+                     : "=r"(done)
+                     : "r"(bar), "r"(parity)
+                     : "memory");
+        if (done) return true;
+        if ((spin & 15) == 15 && *abort_flag) return false;
+        if (spin == 64) t0 = pipe_timer_ns();
+        if (spin > 64 && (spin & 63) == 0 && pipe_timer_ns() - t0 > kPipeWaitLimitNs) return false;
+    }
+}
+__device__ __forceinline__ void pipe_copy(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
+                 "l"(src), "r"(bytes), "r"(bar)
+                 : "memory");
+}
+
+template <int GH>
+struct PipeLayout {
+    static constexpr int kKBytes = 16 * GH * 52;     // key (and value) words of a tile
+    static constexpr int kSBytes = 16 * GH * 16;     // sign words
+    static constexpr int kNBytes = 16 * GH * 4;      // one norm array
+    static constexpr int kOffV = kKBytes, kOffS = 2 * kKBytes, kOffKN = kOffS + kSBytes, kOffVN = kOffKN + kNBytes,
+                         kOffQN = kOffVN + kNBytes;
+    static constexpr int kStageBytes = kOffQN + kNBytes;
+    static constexpr int kQStride = 136;             // halves per rotated query row
+    static constexpr int kOffStages = 0;             // offsets into the dynamic shared memory
+    static constexpr int kOffQ = kOffStages + kPipeStages * kStageBytes;
+    static constexpr int kOffBars = kOffQ + GH * 8 * kQStride * 2;
+    static constexpr int kSmemBytes = kOffBars + 2 * kPipeStages * 8;
+    static_assert(kStageBytes % 16 == 0 && kKBytes % 16 == 0, "bulk copies move multiples of 16 bytes");
+    static_assert(kPipeStages * kStageBytes >= GH * 8 * (128 + 4) * 4, "the result staging reuses the ring");
+};
+
+template <int GH, typename QT>
+__global__ void __launch_bounds__(32 * GH, kPipeWarpsPerSm / GH) attn_pipe_kernel(const AttnSeq* __restrict__ seqs, const QT* __restrict__ qv,
+                                                                    int q_heads, int kv_heads, int n_splits, uint32_t k_seed,
+                                                                    uint32_t qjl_seed, int use_qjl, float inv_sqrt,
+                                                                    float inv_scale_d, float attn_scale, float gamma,
+                                                                    float* __restrict__ part_acc, float* __restrict__ part_ml,
+                                                                    unsigned int* __restrict__ status) {
+    using LY = PipeLayout<GH>;
+    constexpr int D = 128;
+    extern __shared__ __align__(16) unsigned char pipe_smem[];
+    // pair table [pair index][lane]: static, so its window address is an immediate of the lookup loads
+    __shared__ __align__(16) uint32_t s_lut[64 * 32];
+    __shared__ unsigned int s_abort;
+
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int g = lane >> 2, q = lane & 3;
+    const int G = q_heads / kv_heads;
+    const int gchunks = (G + 7) / 8;
+    const int split = blockIdx.x, grp = blockIdx.y / gchunks, gchunk = blockIdx.y - grp * gchunks, seq = blockIdx.z;
+    const int kvh = grp * GH + warp;
+    const int g0 = gchunk * 8;
+    const int ng = min(8, G - g0);
+    const bool rows_mode = kv_heads > GH;            // a head group of a wider cache: per-token rows
+
+    const uint32_t raw_addr = static_cast<uint32_t>(__cvta_generic_to_shared(pipe_smem));
+    unsigned char* const base = pipe_smem;
+    __half* const s_q = reinterpret_cast<__half*>(base + LY::kOffQ) + warp * 8 * LY::kQStride;
+    const uint32_t stage_addr = raw_addr + LY::kOffStages;
+    const uint32_t bar_full = raw_addr + LY::kOffBars, bar_empty = bar_full + 8u * kPipeStages;
+
+    const AttnSeq S = seqs[seq];
+    const int first_tile = S.start >> 4, end_tile = (S.end + 15) >> 4;
+    const int all_tiles = S.end > S.start ? end_tile - first_tile : 0;
+    const int tile0 = first_tile + static_cast<int>(static_cast<long>(all_tiles) * split / n_splits);
+    const int tile1 = first_tile + static_cast<int>(static_cast<long>(all_tiles) * (split + 1) / n_splits);
+    const int n_tiles = tile1 - tile0;
+
+    // one tile of the ring: expected bytes, then the copies (warp 0 only; all its lanes call)
+    auto issue_tile = [&](int it) {
+        const uint32_t dst = stage_addr + static_cast<uint32_t>(it % kPipeStages) * LY::kStageBytes;
+        const uint32_t bar = bar_full + 8u * static_cast<uint32_t>(it % kPipeStages);
+        const size_t tok = static_cast<size_t>(tile0 + it) * 16;
+        if (lane == 0)
+            asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(LY::kStageBytes) : "memory");
+        __syncwarp();
+        if (!rows_mode) {
+            if (lane == 0) {
+                const size_t rec = tok * GH;
+                pipe_copy(dst, S.k_words + rec * 13, LY::kKBytes, bar);
+                pipe_copy(dst + LY::kOffV, S.v_words + rec * 13, LY::kKBytes, bar);
+                pipe_copy(dst + LY::kOffS, S.qjl_words + rec * 4, LY::kSBytes, bar);
+                pipe_copy(dst + LY::kOffKN, S.k_norms + rec, LY::kNBytes, bar);
+                pipe_copy(dst + LY::kOffVN, S.v_norms + rec, LY::kNBytes, bar);
+                pipe_copy(dst + LY::kOffQN, S.qjl_norms + rec, LY::kNBytes, bar);
+            }
+        } else if (lane < 16) {
+            const size_t rec = (tok + lane) * kv_heads + static_cast<size_t>(grp) * GH;
+            pipe_copy(dst + lane * (GH * 52), S.k_words + rec * 13, GH * 52, bar);
+            pipe_copy(dst + LY::kOffV + lane * (GH * 52), S.v_words + rec * 13, GH * 52, bar);
+            pipe_copy(dst + LY::kOffS + lane * (GH * 16), S.qjl_words + rec * 4, GH * 16, bar);
+            pipe_copy(dst + LY::kOffKN + lane * (GH * 4), S.k_norms + rec, GH * 4, bar);
+            pipe_copy(dst + LY::kOffVN + lane * (GH * 4), S.v_norms + rec, GH * 4, bar);
+            pipe_copy(dst + LY::kOffQN + lane * (GH * 4), S.qjl_norms + rec, GH * 4, bar);
+        }
+    };
+
+    if (warp == 0) {
+        if (lane == 0) {
+            s_abort = 0u;
+            for (int s = 0; s < kPipeStages; ++s) {
+                asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar_full + 8u * s), "r"(1) : "memory");
+                asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar_empty + 8u * s), "r"(GH) : "memory");
+            }
+            asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        }
+        __syncwarp();
+        // the first tiles start moving while the tables below are set up
+        for (int it = 0; it < min(kPipeStages, n_tiles); ++it) issue_tile(it);
+    }
+    for (int i = tid; i < 64 * 32; i += 32 * GH) {
+        const int idx = i >> 5;
+        s_lut[i] = pack_half2(kCentroidScale * kC3[idx & 7], kCentroidScale * kC3[idx >> 3]);
+    }
+    // rotated queries of this warp's KV head: fp16-round, sign, butterfly, 1/sqrt(d), fp16-round
+    for (int h = 0; h < 8; ++h) {
+        float v[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            float t = 0.f;
+            if (h < ng) {
+                const size_t qi = (static_cast<size_t>(seq) * q_heads + kvh * G + g0 + h) * D + lane * 4 + j;
+                t = __half2float(__float2half_rn(static_cast<float>(qv[qi])));
+            }
+            v[j] = t * sign_value(k_seed, static_cast<uint32_t>(lane * 4 + j));
+        }
+        warp_fwht<4>(v, lane);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) s_q[h * LY::kQStride + lane * 4 + j] = __float2half_rn(v[j] * inv_sqrt);
+    }
+    __syncthreads();
+    volatile unsigned int* abort_flag = &s_abort;
+
+    // B fragments, as in attn_mma_kernel
+    uint32_t bq[16], bs[16];
+#pragma unroll
+    for (int pidx = 0; pidx < 16; ++pidx) {
+        const int d = attn_pair_dim(q, pidx);
+        const __half2 hq = __halves2half2(s_q[g * LY::kQStride + d], s_q[g * LY::kQStride + d + 1]);
+        bq[pidx] = *reinterpret_cast<const uint32_t*>(&hq);
+        const int e = 32 * q + pidx;
+        const float s0 = qjl_sign_is_positive(qjl_seed, static_cast<uint32_t>(e)) ? 1.f : -1.f;
+        const float s1 = qjl_sign_is_positive(qjl_seed, static_cast<uint32_t>(e + 16)) ? 1.f : -1.f;
+        bs[pidx] = pack_half2(__half2float(s_q[g * LY::kQStride + e]) * s0, __half2float(s_q[g * LY::kQStride + e + 16]) * s1);
+    }
+
+    const uint32_t lane_off = static_cast<uint32_t>(lane) * 4u;
+    auto lut_pair = [&](uint32_t word, int bit) -> uint32_t {
+        // byte offset ((word >> bit) & 63) * 128 + lane * 4: one shift, one logic op; the table's address is an immediate
+        const uint32_t sh = bit >= 7 ? (word >> (bit - 7)) : (word << (7 - bit));
+        return *reinterpret_cast<const uint32_t*>(reinterpret_cast<const unsigned char*>(s_lut) + ((sh & (63u << 7)) | lane_off));
+    };
+    auto sgn_pair = [&](uint32_t inv_word, int pp) -> uint32_t {
+        const uint32_t sh = pp == 15 ? inv_word : (inv_word << (15 - pp));
+        return (sh & 0x80008000u) | 0x3C003C00u;
+    };
+    auto dequant16 = [&](const uint32_t (&w)[4], uint32_t (&out)[16]) {
+        const uint32_t w0 = w[0], w1 = w[1], w2 = w[2], w3 = w[3];
+#pragma unroll
+        for (int j = 0; j < 5; ++j) {
+            out[j] = lut_pair(w0, 6 * j);
+            out[5 + j] = lut_pair(w1, 6 * j);
+            out[10 + j] = lut_pair(w2, 6 * j);
+        }
+        out[15] = lut_pair(w3 >> (6 * q), 0);
+    };
+
+    float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+    float acc[8][4];
+#pragma unroll
+    for (int mt = 0; mt < 8; ++mt)
+#pragma unroll
+        for (int k = 0; k < 4; ++k) acc[mt][k] = 0.f;
+
+    // this thread's two records of a tile: tokens g and g + 8 of head `warp` of the group
+    const int ra = g * GH + warp, rb = ra + 8 * GH;
+    const float kscale = inv_scale_d * attn_scale / kCentroidScale;
+    const float qscale = gamma * kCentroidScale;
+    bool ok = true;
+    for (int it = 0; it < n_tiles; ++it) {
+        const int s = it % kPipeStages;
+        const uint32_t ph = static_cast<uint32_t>(it / kPipeStages) & 1u;
+        if (warp == 0 && it > 0 && it - 1 + kPipeStages < n_tiles) {
+            // the stage of the previous tile is free once every warp has read it: refill it
+            if (!pipe_wait(bar_empty + 8u * ((it - 1) % kPipeStages), static_cast<uint32_t>((it - 1) / kPipeStages) & 1u, abort_flag)) {
+                ok = false;
+                break;
+            }
+            issue_tile(it - 1 + kPipeStages);
+        }
+        if (!pipe_wait(bar_full + 8u * s, ph, abort_flag)) {
+            ok = false;
+            break;
+        }
+        const unsigned char* st = base + LY::kOffStages + s * LY::kStageBytes;
+        const uint32_t* sk = reinterpret_cast<const uint32_t*>(st);
+        const uint32_t* sv = reinterpret_cast<const uint32_t*>(st + LY::kOffV);
+        const uint32_t* ss = reinterpret_cast<const uint32_t*>(st + LY::kOffS);
+        const float* skn = reinterpret_cast<const float*>(st + LY::kOffKN);
+        const float* svn = reinterpret_cast<const float*>(st + LY::kOffVN);
+        const float* sqn = reinterpret_cast<const float*>(st + LY::kOffQN);
+        uint32_t kwa[4], kwb[4], vwa[4], vwb[4];
+#pragma unroll
+        for (int j = 0; j < 3; ++j) {
+            kwa[j] = sk[ra * 13 + q + 4 * j];
+            kwb[j] = sk[rb * 13 + q + 4 * j];
+            vwa[j] = sv[ra * 13 + q + 4 * j];
+            vwb[j] = sv[rb * 13 + q + 4 * j];
+        }
+        kwa[3] = sk[ra * 13 + 12];
+        kwb[3] = sk[rb * 13 + 12];
+        vwa[3] = sv[ra * 13 + 12];
+        vwb[3] = sv[rb * 13 + 12];
+        uint32_t wa = 0, wb = 0;
+        float qa = 0.f, qb = 0.f;
+        if (use_qjl) {
+            wa = ~ss[ra * 4 + q];
+            wb = ~ss[rb * 4 + q];
+            qa = sqn[ra] * qscale;
+            qb = sqn[rb] * qscale;
+        }
+        const int ta = (tile0 + it) * 16 + g, tb = ta + 8;
+        const bool va = ta >= S.start && ta < S.end, vb = tb >= S.start && tb < S.end;
+        const float kna = skn[ra] * kscale, knb = skn[rb] * kscale;
+        const float vna = va ? svn[ra] * (1.0f / kCentroidScale) : 0.f, vnb = vb ? svn[rb] * (1.0f / kCentroidScale) : 0.f;
+        __syncwarp();
+        if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar_empty + 8u * s) : "memory");
+
+        // ---- scores (two accumulators per product: dependent chains of four MMAs, not eight) ----
+        float c1[4] = {0.f, 0.f, 0.f, 0.f}, c1b[4] = {0.f, 0.f, 0.f, 0.f};
+        {
+            uint32_t ka[16], kb[16];
+            dequant16(kwa, ka);
+            dequant16(kwb, kb);
+#pragma unroll
+            for (int ks = 0; ks < 8; ks += 2) {
+                mma_f16(c1, ka[2 * ks], kb[2 * ks], ka[2 * ks + 1], kb[2 * ks + 1], bq[2 * ks], bq[2 * ks + 1]);
+                mma_f16(c1b, ka[2 * ks + 2], kb[2 * ks + 2], ka[2 * ks + 3], kb[2 * ks + 3], bq[2 * ks + 2], bq[2 * ks + 3]);
+            }
+        }
+#pragma unroll
+        for (int k = 0; k < 4; ++k) c1[k] += c1b[k];
+        if (use_qjl) {
+            float c2[4] = {0.f, 0.f, 0.f, 0.f}, c2b[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+            for (int ks = 0; ks < 8; ks += 2) {
+                mma_f16(c2, sgn_pair(wa, 2 * ks), sgn_pair(wb, 2 * ks), sgn_pair(wa, 2 * ks + 1), sgn_pair(wb, 2 * ks + 1),
+                        bs[2 * ks], bs[2 * ks + 1]);
+                mma_f16(c2b, sgn_pair(wa, 2 * ks + 2), sgn_pair(wb, 2 * ks + 2), sgn_pair(wa, 2 * ks + 3), sgn_pair(wb, 2 * ks + 3),
+                        bs[2 * ks + 2], bs[2 * ks + 3]);
+            }
+            c1[0] = fmaf(qa, c2[0] + c2b[0], c1[0]);
+            c1[1] = fmaf(qa, c2[1] + c2b[1], c1[1]);
+            c1[2] = fmaf(qb, c2[2] + c2b[2], c1[2]);
+            c1[3] = fmaf(qb, c2[3] + c2b[3], c1[3]);
+        }
+        const float s00 = va ? c1[0] * kna : -INFINITY, s01 = va ? c1[1] * kna : -INFINITY;
+        const float s10 = vb ? c1[2] * knb : -INFINITY, s11 = vb ? c1[3] * knb : -INFINITY;
+
+        // ---- online softmax per head, with a lazy reference: the running reference m_run only moves
+        // (and the sums are only rescaled) when some score of the tile exceeds it by more than
+        // kSoftmaxSlack, so the usual tile needs one vote instead of a reduction over the tokens.
+        // Probabilities are then at most e^slack (7.4), still far from the fp16 range once
+        // multiplied by a value norm.  Every tile of [tile0, tile1) holds a token of [start, end),
+        // so the reference is finite from the first tile on.
+        const float tm0 = fmaxf(s00, s10), tm1 = fmaxf(s01, s11);
+        if (__any_sync(0xffffffffu, tm0 > m_run[0] + kSoftmaxSlack || tm1 > m_run[1] + kSoftmaxSlack)) {
+            float mx0 = tm0, mx1 = tm1;
+#pragma unroll
+            for (int o = 4; o < 32; o <<= 1) {
+                mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, o));
+                mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, o));
+            }
+            const float mn0 = fmaxf(m_run[0], mx0), mn1 = fmaxf(m_run[1], mx1);
+            const float cr0 = __expf(m_run[0] - mn0), cr1 = __expf(m_run[1] - mn1);
+            l_run[0] *= cr0;
+            l_run[1] *= cr1;
+            m_run[0] = mn0;
+            m_run[1] = mn1;
+#pragma unroll
+            for (int mt = 0; mt < 8; ++mt) {
+                acc[mt][0] *= cr0;
+                acc[mt][1] *= cr1;
+                acc[mt][2] *= cr0;
+                acc[mt][3] *= cr1;
+            }
+        }
+        const float p00 = __expf(s00 - m_run[0]), p01 = __expf(s01 - m_run[1]);
+        const float p10 = __expf(s10 - m_run[0]), p11 = __expf(s11 - m_run[1]);
+        l_run[0] += p00 + p10;
+        l_run[1] += p01 + p11;
+        const uint32_t pb0 = movmatrix_trans(pack_half2(p00 * vna, p01 * vna));
+        const uint32_t pb1 = movmatrix_trans(pack_half2(p10 * vnb, p11 * vnb));
+
+        // ---- values ----
+        {
+            uint32_t xa[16], xb[16];
+            dequant16(vwa, xa);
+            dequant16(vwb, xb);
+#pragma unroll
+            for (int ks = 0; ks < 8; ++ks) {
+                const uint32_t a0 = movmatrix_trans(xa[2 * ks]);
+                const uint32_t a1 = movmatrix_trans(xa[2 * ks + 1]);
+                const uint32_t a2 = movmatrix_trans(xb[2 * ks]);
+                const uint32_t a3 = movmatrix_trans(xb[2 * ks + 1]);
+                mma_f16(acc[ks], a0, a1, a2, a3, pb0, pb1);
+            }
+        }
+    }
+    if (!ok) atomicExch(&s_abort, 1u);
+    __syncthreads();   // every warp is past its last read of the ring (or has given up)
+    if (s_abort) {
+        // let whatever was requested land before the shared memory is released
+        if (tid == 0) {
+            *reinterpret_cast<volatile unsigned int*>(status) = 11u;   // may be host memory: a plain store, then a system fence
+            __threadfence_system();
+            const unsigned long long t0 = pipe_timer_ns();
+            while (pipe_timer_ns() - t0 < 2000000ull) __nanosleep(1000);
+        }
+        __syncthreads();
+        return;
+    }
+
+    // ---- publish: natural dim order through the (now idle) ring, one region per warp ----
+#pragma unroll
+    for (int o = 4; o < 32; o <<= 1) {
+        l_run[0] += __shfl_xor_sync(0xffffffffu, l_run[0], o);
+        l_run[1] += __shfl_xor_sync(0xffffffffu, l_run[1], o);
+    }
+    float* const s_acc = reinterpret_cast<float*>(base + LY::kOffStages) + warp * 8 * (D + 4);
+#pragma unroll
+    for (int mt = 0; mt < 8; ++mt) {
+#pragma unroll
+        for (int hf = 0; hf < 2; ++hf) {
+            const int slot = g + 8 * hf;
+            const int qq = (slot & 7) >> 1, lowbit = slot & 1, half = slot >> 3;
+            const int d = attn_pair_dim(qq, 2 * mt + half) + lowbit;
+            s_acc[(2 * q) * (D + 4) + d] = acc[mt][2 * hf];
+            s_acc[(2 * q + 1) * (D + 4) + d] = acc[mt][2 * hf + 1];
+        }
+    }
+    __syncwarp();
+    const size_t slot0 = (static_cast<size_t>(seq) * q_heads + kvh * G + g0) * n_splits + split;
+    for (int idx = lane; idx < ng * D; idx += 32) {
+        const int h = idx >> 7, e = idx & (D - 1);
+        part_acc[(slot0 + static_cast<size_t>(h) * n_splits) * D + e] = s_acc[h * (D + 4) + e];
+    }
+    if (g == 0) {
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+            const int h = 2 * q + j;
+            if (h < ng) {
+                part_ml[(slot0 + static_cast<size_t>(h) * n_splits) * 2] = m_run[j];
+                part_ml[(slot0 + static_cast<size_t>(h) * n_splits) * 2 + 1] = l_run[j];
+            }
+        }
+    }
+}
+
 int grid_for_warps(long n_warp_items, int warps_per_block, int cap) {
     long want = (n_warp_items + warps_per_block - 1) / warps_per_block;
     if (want < 1) want = 1;
@@ -744,10 +1132,72 @@ size_t attn_scratch_bytes(int n_seqs, int q_heads, int head_dim, int n_splits) {
     return static_cast<size_t>(n_seqs) * q_heads * n_splits * (head_dim + 2) * sizeof(float);
 }
 
+// KV heads one CTA of the bulk-copy pipeline kernel takes (0: that kernel does not apply).
+static int attn_pipe_heads(int head_dim, int kv_heads) {
+    if (head_dim != 128) return 0;
+    if (kv_heads % 4 == 0) return 4;
+    return (kv_heads == 1 || kv_heads == 2) ? kv_heads : 0;
+}
+
+// Plan of one attention call: which kernel, and how many context splits.
+// kernel: 0 chooses, 1 forces the load-based kernels, 2 forces the bulk-copy pipeline (where it
+// applies).  The pipeline pays a heavier per-CTA set-up (each warp rotates its own query group)
+// and writes one partial per (head, split) for four heads per CTA, so it is chosen when every
+// resident CTA slot still gets at least 512 tokens to walk; shorter jobs run the load-based
+// kernel, whose four warps share one head's set-up.
+// Splits: the launch runs in ceil(CTAs / resident CTAs) waves and a wave costs about (tokens a
+// warp walks + a fixed set-up cost expressed in tokens); pick the count that minimises waves x
+// cost.  Pipeline: a CTA is (sequence, group of KV heads, query-head group, split) and every warp
+// walks the whole range of the split.  Load-based: a CTA is (sequence, KV head, query-head group,
+// split) and its four warps share the range.
+AttnPlan attn_make_plan(int n_seqs, int q_heads, int kv_heads, int head_dim, int max_tok, int sm_count, int kernel) {
+    const int G = q_heads / kv_heads;
+    const int gchunks = (G + kAttnGMax - 1) / kAttnGMax;
+    int gh = kernel == 1 ? 0 : attn_pipe_heads(head_dim, kv_heads);
+    if (gh && kernel == 0) {
+        const long slots = static_cast<long>(sm_count) * (kPipeWarpsPerSm / gh);
+        const long ctas_at_512 = static_cast<long>(n_seqs) * (kv_heads / gh) * gchunks * (max_tok / 512);
+        if (ctas_at_512 < slots) gh = 0;
+    }
+    const long ctas_per_split = gh ? static_cast<long>(n_seqs) * (kv_heads / gh) * gchunks : static_cast<long>(n_seqs) * kv_heads * gchunks;
+    const long resident = static_cast<long>(sm_count) * (gh ? kPipeWarpsPerSm / gh : 3);
+    const double walk = gh ? 1.0 : 0.25, setup = gh ? 96.0 : 40.0;
+    const int min_tok = gh ? 128 : 256;
+    const int max_splits = std::max(1, std::min(gh ? 512 : 128, max_tok / min_tok));
+    AttnPlan plan{1, gh};
+    double best = 1e300;
+    for (int n = 1; n <= max_splits; ++n) {
+        const long waves = (ctas_per_split * n + resident - 1) / resident;
+        const double cost = static_cast<double>(waves) * (walk * static_cast<double>(max_tok) / n + setup);
+        if (cost < best * 0.999) {
+            best = cost;
+            plan.n_splits = n;
+        }
+    }
+    return plan;
+}
+
+template <int GH, typename QT>
+static void launch_attn_pipe(const AttnSeq* seqs, int n_seqs, const QT* q, int q_heads, int kv_heads, int n_splits, uint32_t k_seed,
+                             uint32_t qjl_seed, bool use_qjl, float inv_sqrt, float inv_scale_d, float attn_scale, float gamma,
+                             float* part_acc, float* part_ml, unsigned int* status, cudaStream_t stream) {
+    static bool configured = false;   // per instantiation; the attribute is per function and idempotent
+    if (!configured) {
+        TQ_CUDA(cudaFuncSetAttribute(attn_pipe_kernel<GH, QT>, cudaFuncAttributeMaxDynamicSharedMemorySize, PipeLayout<GH>::kSmemBytes));
+        configured = true;
+    }
+    const int gchunks = (q_heads / kv_heads + kAttnGMax - 1) / kAttnGMax;
+    const dim3 grid(n_splits, (kv_heads / GH) * gchunks, n_seqs);
+    attn_pipe_kernel<GH, QT><<<grid, 32 * GH, PipeLayout<GH>::kSmemBytes, stream>>>(seqs, q, q_heads, kv_heads, n_splits, k_seed, qjl_seed,
+                                                                                  use_qjl ? 1 : 0, inv_sqrt, inv_scale_d, attn_scale,
+                                                                                  gamma, part_acc, part_ml, status);
+}
+
 void launch_kv_attention(const void* d_seqs, int n_seqs, const void* q, bool q_is_f16, int q_heads, int kv_heads,
-                         int head_dim, int n_splits, uint32_t k_seed, uint32_t v_seed, uint32_t qjl_seed, bool use_qjl,
-                         void* scratch, __half* out, float* lse, cudaStream_t stream) {
+                         int head_dim, AttnPlan plan, uint32_t k_seed, uint32_t v_seed, uint32_t qjl_seed, bool use_qjl,
+                         void* scratch, __half* out, float* lse, unsigned int* status, cudaStream_t stream) {
     if (n_seqs == 0) return;
+    const int n_splits = plan.n_splits;
     TQ_REQUIRE(q_heads % kv_heads == 0, "query heads must be a multiple of KV heads");
     const int G = q_heads / kv_heads;
     const int gchunks = (G + kAttnGMax - 1) / kAttnGMax;
@@ -772,6 +1222,29 @@ void launch_kv_attention(const void* d_seqs, int n_seqs, const void* q, bool q_i
                                                                  inv_scale_d, attn_scale, gamma, part_acc, part_ml);     \
     attn_combine_kernel<EV><<<static_cast<int>((n_rows + 3) / 4), 128, 0, stream>>>(part_acc, part_ml, n_rows, n_splits, \
                                                                                    v_seed, inv_sqrt, inv_scale_d, out, lse);
+    if (const int gh = plan.pipe_heads) {
+        TQ_REQUIRE(gh == attn_pipe_heads(head_dim, kv_heads), "attention: plan does not match the cache shape");
+        const AttnSeq* seqs = static_cast<const AttnSeq*>(d_seqs);
+#define TQ_PIPE(GHV)                                                                                                            \
+    if (q_is_f16)                                                                                                               \
+        launch_attn_pipe<GHV, __half>(seqs, n_seqs, static_cast<const __half*>(q), q_heads, kv_heads, n_splits, k_seed, qjl_seed, \
+                                      use_qjl, inv_sqrt, inv_scale_d, attn_scale, gamma, part_acc, part_ml, status, stream);    \
+    else                                                                                                                        \
+        launch_attn_pipe<GHV, float>(seqs, n_seqs, static_cast<const float*>(q), q_heads, kv_heads, n_splits, k_seed, qjl_seed,  \
+                                     use_qjl, inv_sqrt, inv_scale_d, attn_scale, gamma, part_acc, part_ml, status, stream);
+        if (gh == 4) {
+            TQ_PIPE(4)
+        } else if (gh == 2) {
+            TQ_PIPE(2)
+        } else {
+            TQ_PIPE(1)
+        }
+#undef TQ_PIPE
+        attn_combine_kernel<4><<<static_cast<int>((n_rows + 3) / 4), 128, 0, stream>>>(part_acc, part_ml, n_rows, n_splits,
+                                                                                      v_seed, inv_sqrt, inv_scale_d, out, lse);
+        TQ_CUDA(cudaGetLastError());
+        return;
+    }
     if (head_dim == 128) {
         if (q_is_f16)
             attn_mma_kernel<__half><<<grid, kMmaThreads, 0, stream>>>(static_cast<const AttnSeq*>(d_seqs),
