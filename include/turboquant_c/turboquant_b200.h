@@ -236,6 +236,16 @@ long tq_kv_snapshot(tq_kv_cache_t cache, void* out, size_t capacity, uint32_t mo
  *  (non-zero) before anything changes. */
 int tq_kv_restore(tq_kv_cache_t cache, const void* data, size_t size);
 
+/** TQKVCache::delta + delta_serialize (src/kv_cache.cpp:566-581, src/cache_snapshot.cpp:110-123):
+ *  positions [from, to) of every layer (clamped to each layer's length) as the reference's "TQCD"
+ *  byte stream.  Returns the size needed (negative on error) and writes the stream when `out`
+ *  (HOST memory) has `capacity` >= that size; call with out = NULL to size the buffer. */
+long tq_kv_delta(tq_kv_cache_t cache, void* out, size_t capacity, uint32_t from, uint32_t to);
+/** delta_deserialize + TQKVCache::apply_delta (src/cache_snapshot.cpp:125-140, src/kv_cache.cpp:583-594):
+ *  appends a stream from tq_kv_delta or from the reference to every layer.  The layer count must
+ *  match; malformed input is refused (non-zero) before anything changes. */
+int tq_kv_apply_delta(tq_kv_cache_t cache, const void* data, size_t size);
+
 /** Which decode-attention kernel calls that name this cache FIRST use for head_dim 128:
  *  0 chooses by job size (default), 1 the load-based kernel, 2 the bulk-copy pipeline (cp.async.bulk
  *  + mbarrier ring; applies to 1, 2 or a multiple of 4 KV heads, otherwise 1 is used).  Results of

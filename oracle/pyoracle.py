@@ -230,6 +230,9 @@ class Ref(_Base):
         L.ref_kv_snapshot.argtypes = [C.c_void_p, C.c_void_p, C.c_long, C.c_uint32, C.c_uint32]
         L.ref_kv_snapshot.restype = C.c_long
         L.ref_kv_restore.argtypes = [C.c_void_p, C.c_void_p, C.c_long]
+        L.ref_kv_delta.argtypes = [C.c_void_p, C.c_void_p, C.c_long, C.c_uint32, C.c_uint32]
+        L.ref_kv_delta.restype = C.c_long
+        L.ref_kv_apply_delta.argtypes = [C.c_void_p, C.c_void_p, C.c_long]
 
     def codebook(self, bits: int):
         c = np.zeros(1 << bits, np.float32)
@@ -334,6 +337,20 @@ class Ref(_Base):
             data = np.ascontiguousarray(data, np.uint8)
             if self.ref.lib.ref_kv_restore(self.h, data.ctypes.data, data.size):
                 raise ValueError("ref restore failed")
+
+        def delta(self, start: int, end: int) -> np.ndarray:
+            """The reference's serialized delta of positions [start, end) (delta() + delta_serialize)."""
+            n = self.ref.lib.ref_kv_delta(self.h, None, 0, start, end)
+            if n < 0:
+                raise RuntimeError("ref delta failed")
+            out = np.zeros(n, np.uint8)
+            self.ref.lib.ref_kv_delta(self.h, out.ctypes.data, n, start, end)
+            return out
+
+        def apply_delta(self, data: np.ndarray):
+            data = np.ascontiguousarray(data, np.uint8)
+            if self.ref.lib.ref_kv_apply_delta(self.h, data.ctypes.data, data.size):
+                raise ValueError("ref apply_delta failed")
 
     def kv(self, layers, heads, dim):
         return Ref.KV(self, layers, heads, dim)

@@ -281,4 +281,27 @@ int ref_kv_restore(void* h, const uint8_t* data, long size) {
     } catch (...) { return -1; }
 }
 
+// TQKVCache::delta + delta_serialize (src/kv_cache.cpp:566-581, src/cache_snapshot.cpp:110-123):
+// positions [from, to) of every layer as a byte stream.  Returns its size; writes it when `out` has room.
+long ref_kv_delta(void* h, uint8_t* out, long capacity, uint32_t from, uint32_t to) {
+    try {
+        auto* k = static_cast<KVHandle*>(h);
+        const std::vector<uint8_t> bytes = delta_serialize(k->cache->delta(from, to));
+        if (out && capacity >= static_cast<long>(bytes.size())) std::memcpy(out, bytes.data(), bytes.size());
+        return static_cast<long>(bytes.size());
+    } catch (...) { return -1; }
+}
+
+// delta_deserialize + TQKVCache::apply_delta (src/cache_snapshot.cpp:125-140, src/kv_cache.cpp:583-594).
+int ref_kv_apply_delta(void* h, const uint8_t* data, long size) {
+    try {
+        auto* k = static_cast<KVHandle*>(h);
+        const std::vector<uint8_t> bytes(data, data + size);
+        const TQCacheDelta d = delta_deserialize(bytes);
+        if (d.num_layers == 0) return 1;
+        k->cache->apply_delta(d);
+        return 0;
+    } catch (...) { return -1; }
+}
+
 }  // extern "C"

@@ -101,6 +101,8 @@ def main():
         out[f"{name}_values_fp16"] = kv.get_fp16(lay, True, 0, tokens).view(np.uint16)
         # the reference's serialized snapshot of the whole cache (TQCS stream), with fixed identity hashes
         out[f"{name}_snapshot"] = kv.snapshot(model_hash=0x1234ABCD, codebook_hash=0x0BADF00D)
+        # ... and its delta of positions [3, tokens - 2) (TQCD stream)
+        out[f"{name}_delta"] = kv.delta(3, tokens - 2)
         # attention (C restatement; GQA group 7 for the 4x128 case, 1 otherwise)
         q_heads = heads * (7 if heads == 4 else 1)
         rng = np.random.default_rng(seed + 100)

@@ -273,3 +273,39 @@ def test_attention_kernel_choice_is_automatic_for_long_batches(tq):
     with pytest.raises(tq.TQError):
         c.set_attention_kernel(7)
     c.close()
+
+
+@pytest.mark.parametrize("case", KV_CASES, ids=[c[0] for c in KV_CASES])
+def test_delta_is_byte_identical_and_applies(tq, golden, case):
+    """tq_kv_delta writes the reference's serialized delta byte for byte; a cache holding the first
+    tokens plus the delta of the rest equals the cache that appended everything."""
+    name, layers, heads, dim, tokens, seed = case
+    k, v = kv_inputs(seed, tokens, heads, dim)
+    full = tq.TQKVCache(layers, heads, dim)
+    full.append(layers - 1, k[: tokens // 2], v[: tokens // 2])
+    full.append(layers - 1, k[tokens // 2:], v[tokens // 2:])
+    assert bits_equal(full.delta(3, tokens - 2), golden[f"{name}_delta"])
+    # ranges are clamped to each layer's length (the header keeps the positions as asked, as the
+    # reference's does), an empty range is a valid stream
+    assert bits_equal(full.delta(3, tokens + 50)[16:], full.delta(3, tokens)[16:])
+    assert full.delta(tokens, tokens).size == 16 + layers * (4 + 4 + 6 * 4)
+    part = tq.TQKVCache(layers, heads, dim)
+    part.append(layers - 1, k[:3], v[:3])
+    part.apply_delta(golden[f"{name}_delta"])          # the reference's own stream
+    part.apply_delta(full.delta(tokens - 2, tokens))
+    assert part.seq_length() == tokens
+    ea, eb = full.export(layers - 1), part.export(layers - 1)
+    for key in ("k_words", "v_words", "k_norms", "v_norms", "qjl_words", "qjl_norms"):
+        assert bits_equal(ea[key], eb[key]), key
+    d = full.delta(0, tokens)
+    for bad in (d[:20], d[:-3], np.zeros(40, np.uint8), full.snapshot()):
+        with pytest.raises(ValueError):
+            part.apply_delta(bad)
+    assert part.seq_length() == tokens
+    if layers > 1:
+        other = tq.TQKVCache(layers + 1, heads, dim)
+        with pytest.raises(ValueError):
+            other.apply_delta(d)
+        other.close()
+    full.close()
+    part.close()

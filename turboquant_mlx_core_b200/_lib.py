@@ -107,6 +107,8 @@ def load() -> C.CDLL:
     sig("tq_kv_export", i, [vp, i, vp, vp, vp, vp, vp, vp])
     sig("tq_kv_snapshot", C.c_long, [vp, vp, C.c_size_t, u32, u32])
     sig("tq_kv_restore", i, [vp, vp, C.c_size_t])
+    sig("tq_kv_delta", C.c_long, [vp, vp, C.c_size_t, C.c_uint32, C.c_uint32])
+    sig("tq_kv_apply_delta", i, [vp, vp, C.c_size_t])
     sig("tq_kv_reserve", i, [vp, i, i, vp])
     sig("tq_kv_set_attention_kernel", i, [vp, i])
     sig("tq_kv_attention_status", i, [vp])

@@ -309,6 +309,23 @@ class TQKVCache:
         if self._L.tq_kv_restore(self._h, _ptr(data), data.size) != 0:
             raise ValueError("TQKVCache.restore: " + _lib.last_error())
 
+    def delta(self, start: int, end: int) -> np.ndarray:
+        """Positions [start, end) of every layer as the reference's delta byte stream (TQKVCache::delta +
+        delta_serialize, src/kv_cache.cpp:566-581, src/cache_snapshot.cpp:110-123)."""
+        n = self._L.tq_kv_delta(self._h, None, 0, int(start), int(end))
+        if n < 0:
+            raise _lib.TQError("TQKVCache.delta: " + _lib.last_error())
+        out = np.zeros(n, np.uint8)
+        if self._L.tq_kv_delta(self._h, _ptr(out), n, int(start), int(end)) != n:
+            raise _lib.TQError("TQKVCache.delta: " + _lib.last_error())
+        return out
+
+    def apply_delta(self, data):
+        """Append a delta stream (ours or the reference's) to every layer."""
+        data = np.ascontiguousarray(data, np.uint8)
+        if self._L.tq_kv_apply_delta(self._h, _ptr(data), data.size) != 0:
+            raise ValueError("TQKVCache.apply_delta: " + _lib.last_error())
+
     def reserve(self, layer: int, tokens: int, stream=None):
         """Make room for `tokens` tokens of `layer` up front (growth otherwise doubles and copies)."""
         check(self._L.tq_kv_reserve(self._h, layer, int(tokens), _stream_ptr(stream)), "TQKVCache.reserve")

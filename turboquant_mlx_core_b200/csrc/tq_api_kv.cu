@@ -311,6 +311,109 @@ public:
         }
     }
 
+    // ---- delta stream (src/cache_snapshot.cpp:18-31, 110-140; src/kv_cache.cpp:566-594) ----
+    // header: "TQCD", from, to, layers; per layer: blob bytes, then the same blob as in a snapshot
+    // holding positions [from, to) clamped to the layer's token count.
+    static void clamp_range(const LayerKVStorage& L, long from, long to, int& a, int& b) {
+        a = static_cast<int>(std::max<long>(from, 0));
+        b = static_cast<int>(std::min<long>(to, L.num_tokens));
+        if (b < a) b = a;
+    }
+    size_t range_blob_bytes(int tokens) const {
+        const size_t n = static_cast<size_t>(tokens) * heads_;
+        return 4 + 6 * 4 + n * (2 * static_cast<size_t>(words_per_head()) + qjl_words_per_head() + 3) * 4;
+    }
+    size_t delta_bytes(uint32_t from, uint32_t to) const {
+        size_t total = 4 * 4;
+        for (const LayerKVStorage& L : layers_) {
+            int a, b;
+            clamp_range(L, from, to, a, b);
+            total += 4 + range_blob_bytes(b - a);
+        }
+        return total;
+    }
+    void delta_to(uint8_t* out, uint32_t from, uint32_t to) {
+        TQ_CUDA(cudaSetDevice(device_));
+        TQ_CUDA(cudaDeviceSynchronize());
+        size_t pos = 0;
+        auto put = [&](uint32_t v) { std::memcpy(out + pos, &v, 4); pos += 4; };
+        put(0x44435154u);  // 'T','Q','C','D'
+        put(from);
+        put(to);
+        put(static_cast<uint32_t>(layers_n_));
+        for (const LayerKVStorage& L : layers_) {
+            int a, b;
+            clamp_range(L, from, to, a, b);
+            put(static_cast<uint32_t>(range_blob_bytes(b - a)));
+            put(static_cast<uint32_t>(b - a));
+            const size_t n = static_cast<size_t>(b - a) * heads_, first = static_cast<size_t>(a) * heads_;
+            auto span = [&](const DeviceBuffer& src, size_t elem_bytes) {
+                const size_t bytes = n * elem_bytes;
+                put(static_cast<uint32_t>(bytes));
+                if (bytes) TQ_CUDA(cudaMemcpy(out + pos, src.as<uint8_t>() + first * elem_bytes, bytes, cudaMemcpyDeviceToHost));
+                pos += bytes;
+            };
+            span(L.k_words, static_cast<size_t>(words_per_head()) * 4);
+            span(L.v_words, static_cast<size_t>(words_per_head()) * 4);
+            span(L.k_norms, 4);
+            span(L.v_norms, 4);
+            span(L.qjl_words, static_cast<size_t>(qjl_words_per_head()) * 4);
+            span(L.qjl_norms, 4);
+        }
+    }
+    // Appends a delta stream (ours or the reference's delta_serialize) to every layer.  The layer
+    // count must match; malformed input is refused before anything is changed.  As in the
+    // reference, the positions in the header are not checked against the cache's length.
+    void apply_delta_from(const uint8_t* data, size_t size) {
+        size_t pos = 0;
+        auto get = [&](uint32_t& v) {
+            TQ_REQUIRE(pos + 4 <= size, "apply_delta: truncated stream");
+            std::memcpy(&v, data + pos, 4);
+            pos += 4;
+        };
+        uint32_t magic, from, to, layers;
+        get(magic); get(from); get(to); get(layers);
+        TQ_REQUIRE(magic == 0x44435154u, "apply_delta: not a cache delta");
+        TQ_REQUIRE(static_cast<int>(layers) == layers_n_, "apply_delta: layer count differs from this cache");
+        struct Span { size_t off, bytes; };
+        std::vector<std::array<Span, 6>> spans(layers);
+        std::vector<uint32_t> tokens(layers);
+        for (uint32_t l = 0; l < layers; ++l) {
+            uint32_t blob;
+            get(blob);
+            TQ_REQUIRE(pos + blob <= size, "apply_delta: truncated layer blob");
+            const size_t end = pos + blob;
+            get(tokens[l]);
+            const size_t n = static_cast<size_t>(tokens[l]) * heads_;
+            const size_t want[6] = {n * words_per_head() * 4, n * words_per_head() * 4, n * 4, n * 4,
+                                    n * qjl_words_per_head() * 4, n * 4};
+            for (int i = 0; i < 6; ++i) {
+                uint32_t bytes;
+                get(bytes);
+                TQ_REQUIRE(bytes == want[i] && pos + bytes <= end, "apply_delta: array size does not match the token count");
+                spans[l][i] = Span{pos, bytes};
+                pos += bytes;
+            }
+            TQ_REQUIRE(pos == end, "apply_delta: trailing bytes in a layer blob");
+        }
+        TQ_CUDA(cudaSetDevice(device_));
+        TQ_CUDA(cudaDeviceSynchronize());
+        for (uint32_t l = 0; l < layers; ++l) {
+            LayerKVStorage& L = layers_[l];
+            reserve(L, L.num_tokens + static_cast<int>(tokens[l]), nullptr);
+            const size_t first = static_cast<size_t>(L.num_tokens) * heads_;
+            DeviceBuffer* dst[6] = {&L.k_words, &L.v_words, &L.k_norms, &L.v_norms, &L.qjl_words, &L.qjl_norms};
+            const size_t elem[6] = {static_cast<size_t>(words_per_head()) * 4, static_cast<size_t>(words_per_head()) * 4, 4, 4,
+                                    static_cast<size_t>(qjl_words_per_head()) * 4, 4};
+            for (int i = 0; i < 6; ++i)
+                if (spans[l][i].bytes)
+                    TQ_CUDA(cudaMemcpy(dst[i]->as<uint8_t>() + first * elem[i], data + spans[l][i].off, spans[l][i].bytes,
+                                       cudaMemcpyHostToDevice));
+            L.num_tokens += static_cast<int>(tokens[l]);
+            seq_length_ = std::max(seq_length_, L.num_tokens);
+        }
+    }
+
     SeqDesc describe(int layer, int start, int end) const {
         TQ_REQUIRE(layer >= 0 && layer < layers_n_, "Layer index out of range");
         const LayerKVStorage& L = layers_[static_cast<size_t>(layer)];
@@ -619,6 +722,27 @@ int tq_kv_restore(tq_kv_cache_t cache, const void* data, size_t size) {
         TQ_REQUIRE(cache && cache->cache, "tq_kv_restore: NULL cache");
         TQ_REQUIRE(data != nullptr && !tq::is_device_pointer(data), "tq_kv_restore: the stream is read from host memory");
         cache->cache->restore_from(static_cast<const uint8_t*>(data), size);
+        return 0;
+    });
+}
+
+long tq_kv_delta(tq_kv_cache_t cache, void* out, size_t capacity, uint32_t from, uint32_t to) {
+    return guarded<long>(0, -1, [&]() -> long {
+        TQ_REQUIRE(cache && cache->cache, "tq_kv_delta: NULL cache");
+        const size_t need = cache->cache->delta_bytes(from, to);
+        if (out != nullptr && capacity >= need) {
+            TQ_REQUIRE(!tq::is_device_pointer(out), "tq_kv_delta: the stream is written to host memory");
+            cache->cache->delta_to(static_cast<uint8_t*>(out), from, to);
+        }
+        return static_cast<long>(need);
+    });
+}
+
+int tq_kv_apply_delta(tq_kv_cache_t cache, const void* data, size_t size) {
+    return guarded<int>(0, -1, [&]() {
+        TQ_REQUIRE(cache && cache->cache && data, "tq_kv_apply_delta: NULL argument");
+        TQ_REQUIRE(!tq::is_device_pointer(data), "tq_kv_apply_delta: the stream is read from host memory");
+        cache->cache->apply_delta_from(static_cast<const uint8_t*>(data), size);
         return 0;
     });
 }

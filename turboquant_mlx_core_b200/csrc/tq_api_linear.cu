@@ -94,10 +94,14 @@ public:
             scratch_.resize(sb);
             TQ_CUDA(cudaMemset(scratch_.as<void>(), 0, sb));
         }
-        status_.resize(2 * sizeof(unsigned int));  // [0] error word, [1] grid completion counter of scattering calls
-        TQ_CUDA(cudaMemset(status_.as<void>(), 0, 2 * sizeof(unsigned int)));
+        counter_.resize(sizeof(unsigned int));  // grid completion counter of scattering calls
+        TQ_CUDA(cudaMemset(counter_.as<void>(), 0, sizeof(unsigned int)));
+        // The kernels' error word is page-locked host memory that they store to directly (only on
+        // a failure), so the host checks it after a synchronisation without a copy.
         TQ_CUDA(cudaMallocHost(&h_status_, sizeof(unsigned int)));
         *h_status_ = 0;
+        d_status_ = static_cast<unsigned int*>(tq::pinned_host_device_alias(h_status_));
+        TQ_REQUIRE(d_status_ != nullptr, "TurboQuantLinear: the status word is not mapped for the device");
 
         // One launch on a zero activation: proves on this device, now, that the kernel's
         // shared-memory layout holds, instead of failing on the first real forward.
@@ -156,10 +160,8 @@ public:
         launch_forward(d_x, batch, d_y, st);
         if (!y_dev) {
             if (!y_alias) TQ_CUDA(cudaMemcpyAsync(y, d_y, ny * sizeof(__half), cudaMemcpyDeviceToHost, st));
-            // the kernels' error word rides along with the result (no second synchronisation)
-            TQ_CUDA(cudaMemcpyAsync(h_status_, status_.as<void>(), sizeof(unsigned int), cudaMemcpyDeviceToHost, st));
             TQ_CUDA(cudaStreamSynchronize(st));
-            require_ok(*h_status_);
+            require_ok(*static_cast<volatile unsigned int*>(h_status_));
         }
     }
 
@@ -188,20 +190,19 @@ public:
         }
         tq::launch_tq8_gemv_scatter(codes_.as<uint8_t>(), norms_.as<float>(), tables_.as<float>(),
                                     static_cast<const __half*>(x), d, n_dst, dst_stride, out_, in_, batch, block_,
-                                    dual_ ? 2 : 1, seed_p_, seed_r_, scratch_.as<void>(), status_.as<unsigned int>(),
-                                    sm_count_, st, signal ? sig : nullptr, signal_slot, signal_value);
+                                    dual_ ? 2 : 1, seed_p_, seed_r_, scratch_.as<void>(), d_status_,
+                                    sm_count_, st, signal ? sig : nullptr, signal_slot, signal_value, counter_.as<unsigned int>());
     }
 
     void wait_peers(const void* flags, int n, unsigned int value, cudaStream_t st) {
         TQ_CUDA(cudaSetDevice(device_));
-        tq::launch_peer_wait(static_cast<const unsigned int*>(flags), n, value, status_.as<unsigned int>(), st);
+        tq::launch_peer_wait(static_cast<const unsigned int*>(flags), n, value, d_status_, st);
     }
 
     void check_status() {
-        unsigned int h = 0;
         TQ_CUDA(cudaSetDevice(device_));
-        TQ_CUDA(cudaMemcpy(&h, status_.as<void>(), sizeof h, cudaMemcpyDeviceToHost));
-        require_ok(h);
+        TQ_CUDA(cudaDeviceSynchronize());
+        require_ok(*static_cast<volatile unsigned int*>(h_status_));
     }
 
     // result: [out, in] fp32 or fp16, host or device.
@@ -240,7 +241,7 @@ public:
         TQ_CUDA(cudaSetDevice(device_));
         tq::launch_tq8_gemv_static(codes_.as<uint8_t>(), norms_.as<float>(), tables_.as<float>(),
                                    static_cast<const __half*>(x), static_cast<__half*>(y), out_, in_, batch, block_,
-                                   dual_ ? 2 : 1, seed_p_, seed_r_, status_.as<unsigned int>(), sm_count_, st);
+                                   dual_ ? 2 : 1, seed_p_, seed_r_, d_status_, sm_count_, st);
     }
 
     ~TurboQuantLinear() {
@@ -269,7 +270,7 @@ private:
             const int planes = dual_ ? 2 : 1;
             gemm_scratch_.reserve(tq::gemm_scratch_bytes(out_, in_, batch, planes, sm_count_));
             tq::launch_tq8_gemm(codes_.as<uint8_t>(), norms_.as<float>(), tables_.as<float>(), d_x, d_y, out_, in_, batch,
-                                block_, planes, seed_p_, seed_r_, gemm_scratch_.as<void>(), status_.as<unsigned int>(),
+                                block_, planes, seed_p_, seed_r_, gemm_scratch_.as<void>(), d_status_,
                                 sm_count_, st);
             return;
         }
@@ -278,7 +279,7 @@ private:
             tq::launch_tq8_gemv(codes_.as<uint8_t>(), norms_.as<float>(), tables_.as<float>(),
                                 d_x + static_cast<size_t>(b0) * in_, d_y + static_cast<size_t>(b0) * out_, out_, in_, nb,
                                 block_, dual_ ? 2 : 1, seed_p_, seed_r_, scratch_.as<void>(),
-                                status_.as<unsigned int>(), sm_count_, st);
+                                d_status_, sm_count_, st);
         }
     }
 
@@ -287,9 +288,10 @@ private:
     int device_ = 0, sm_count_ = 0;
     bool primary_5bit_ = false, has_residual_ = false, shared_ = false, dual_ = false;
     uint32_t seed_p_ = 0, seed_r_ = 0;
-    DeviceBuffer codes_, norms_, tables_, scratch_, gemm_scratch_, status_;
+    DeviceBuffer codes_, norms_, tables_, scratch_, gemm_scratch_, counter_;
     DeviceBuffer x_f16_, x_f32_, y_f16_;  // staging for host-side callers
-    unsigned int* h_status_ = nullptr;    // pinned host copy of the status word
+    unsigned int* h_status_ = nullptr;    // the kernels' error word: page-locked host memory
+    unsigned int* d_status_ = nullptr;    // its address for kernels
 };
 
 }  // namespace turboquant

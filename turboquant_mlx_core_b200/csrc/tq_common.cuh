@@ -109,4 +109,11 @@ __host__ __device__ __forceinline__ size_t code_offset(long row, int col, size_t
            (static_cast<size_t>(row) & 15) * kCodeTileCols + (static_cast<size_t>(col) & 63);
 }
 
+// Report a failure from a kernel.  The status word may live in page-locked HOST memory (so that
+// the host reads it without a copy): a plain store followed by a system-scope fence, no atomic.
+__device__ __forceinline__ void raise_status(unsigned int* status, unsigned int code) {
+    *reinterpret_cast<volatile unsigned int*>(status) = code;
+    __threadfence_system();
+}
+
 }  // namespace tq

@@ -300,7 +300,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) tq8_gemm_kernel(const GemmArg
             else { addr[s] = hi; hi += kBBytes; }
         }
         if (hi > raw + dyn_bytes || lut_end > raw + dyn_bytes) {  // layout does not fit: refuse to run (nothing allocated yet)
-            if (tid == 0) atomicExch(p.status, 9u);
+            if (tid == 0) raise_status(p.status, 9u);
             return;
         }
         if (tid == 0) {
@@ -390,7 +390,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) tq8_gemm_kernel(const GemmArg
                 const int sa = kb % kAStages;
                 const int plane = (kb_base + kb) >= kb_per_plane ? 1 : 0;
                 if (kb >= kAStages && !bar_wait(bar_empty_a + 8u * sa, ((kb / kAStages) - 1) & 1, abort_flag)) {
-                    atomicExch(p.status, 6u);
+                    raise_status(p.status, 6u);
                     atomicExch(&s_abort, 1u);
                     alive = false;
                     break;
@@ -431,7 +431,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) tq8_gemm_kernel(const GemmArg
             const int sb = kb % n_b;
             if (kb >= n_b && !bar_wait(bar_empty_b + 8u * sb, ((kb / n_b) - 1) & 1, abort_flag)) {
                 if (lane == 0) {
-                    atomicExch(p.status, 6u);
+                    raise_status(p.status, 6u);
                     atomicExch(&s_abort, 1u);
                 }
                 break;
@@ -455,7 +455,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) tq8_gemm_kernel(const GemmArg
             if (!bar_wait(bar_full + 8u * (kb % kFull), (kb / kFull) & 1, abort_flag) ||
                 !bar_wait(bar_full_b + 8u * (kb % n_b), (kb / n_b) & 1, abort_flag)) {
                 if (lane == 0) {
-                    atomicExch(p.status, 7u);
+                    raise_status(p.status, 7u);
                     atomicExch(&s_abort, 1u);
                 }
                 break;
@@ -481,7 +481,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) tq8_gemm_kernel(const GemmArg
     if (warp < kProducerWarps) {
         const bool ok = !*abort_flag && bar_wait(bar_accum, 0, abort_flag);
         if (!ok) {
-            atomicExch(p.status, 8u);
+            raise_status(p.status, 8u);
             atomicExch(&s_abort, 1u);
         } else {
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");

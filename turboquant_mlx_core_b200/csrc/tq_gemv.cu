@@ -261,7 +261,7 @@ __global__ void __launch_bounds__(kCtaThreads, 1) tq8_gemv_kernel(const GemvArgs
     const uint32_t red_addr = (base + 127u) & ~127u;
     const uint32_t strip_addr = red_addr + kRedBytes + static_cast<uint32_t>(warp) * (kSlice * 4u);
     if (red_addr + kRedBytes + kWarps * kSlice * 4u > kLutAddr) {  // layout assumption broken: refuse to run
-        if (tid == 0) atomicExch(p.status, 1u);
+        if (tid == 0) raise_status(p.status, 1u);
         return;
     }
     const uint32_t bar_written = smem_u32(&s_bars[0]), bar_read = smem_u32(&s_bars[kMaxRing]);
@@ -375,7 +375,7 @@ __global__ void __launch_bounds__(kCtaThreads, 1) tq8_gemv_kernel(const GemvArgs
     const bool red_writer = pw == 0 && (BP >= 2 || hv == 0);
     auto reduce_unit = [&](int slot, int ru, int rs, uint32_t parity) {
         if (!mbar_wait(bar_written + 8u * rs, parity)) {
-            atomicExch(p.status, 5u);
+            raise_status(p.status, 5u);
             atomicExch(&s_abort, 1u);
         }
         for (int j = 0; j < p.tpu; ++j) {
@@ -604,7 +604,7 @@ __global__ void __launch_bounds__(kCtaThreads, 1) tq8_gemv_kernel(const GemvArgs
             if (++rs == kRing) { rs = 0; rpar ^= 1u; }
         }
         if (i >= kRing && !mbar_wait(bar_read + 8u * ws, wpar)) {
-            atomicExch(p.status, 4u);
+            raise_status(p.status, 4u);
             atomicExch(&s_abort, 1u);
         }
         {
@@ -666,7 +666,7 @@ __global__ void peer_wait_kernel(const unsigned int* __restrict__ flags, int n, 
         asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(flags + lane) : "memory");
         if (static_cast<int>(v - value) >= 0) return;
         if ((spin & 255u) == 255u && global_timer_ns() - t0 > 5ull * kWaitLimitNs) {  // 1 s: a peer is gone
-            atomicExch(status, 10u);
+            raise_status(status, 10u);
             return;
         }
     }
@@ -713,7 +713,7 @@ void launch_tq8_gemv_scatter(const uint8_t* codes, const float* norms, const flo
                              __half* const* dst, int n_dst, long dst_stride, int out, int in, int batch, uint32_t block,
                              int n_planes, uint32_t seed_p, uint32_t seed_r, void* scratch, unsigned int* status,
                              int sm_count, cudaStream_t stream, unsigned int* const* signal, int signal_slot,
-                             unsigned int signal_value) {
+                             unsigned int signal_value, unsigned int* done_counter) {
     TQ_REQUIRE(dst != nullptr && n_dst >= 1 && n_dst <= 8, "tq8_gemv: 1..8 destinations");
     TQ_REQUIRE(dst_stride >= out, "tq8_gemv: destination row stride smaller than the layer's rows");
     __half* y = dst[0];
@@ -741,7 +741,8 @@ void launch_tq8_gemv_scatter(const uint8_t* codes, const float* norms, const flo
         }
         a.signal_slot = signal_slot;
         a.signal_value = signal_value;
-        a.done_counter = status + 1;  // the layer's second status word
+        TQ_REQUIRE(done_counter != nullptr, "tq8_gemv: signalling needs a completion counter in device memory");
+        a.done_counter = done_counter;
     }
     a.out = out; a.in = in; a.batch = batch;
     const int n_row_tiles = (out + 15) / 16;

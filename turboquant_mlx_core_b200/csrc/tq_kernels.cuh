@@ -44,10 +44,11 @@ void launch_tq8_gemv_scatter(const uint8_t* codes, const float* norms, const flo
                              __half* const* dst, int n_dst, long dst_stride, int out, int in, int batch, uint32_t block,
                              int n_planes, uint32_t seed_p, uint32_t seed_r, void* scratch, unsigned int* status,
                              int sm_count, cudaStream_t stream, unsigned int* const* signal = nullptr, int signal_slot = 0,
-                             unsigned int signal_value = 0);
+                             unsigned int signal_value = 0, unsigned int* done_counter = nullptr);
 // With `signal` (one flag array per destination): once the whole grid has stored its results,
-// signal[d][signal_slot] = signal_value on every destination (release, system scope); status[1]
-// must be a zero-initialised word (grid completion counter).  launch_peer_wait: one small kernel
+// signal[d][signal_slot] = signal_value on every destination (release, system scope); `done_counter`
+// must be a zero-initialised word in device memory (grid completion counter).  `status` may be
+// page-locked host memory in every launcher of this file (kernels only store to it).  launch_peer_wait: one small kernel
 // that waits, for at most a second, until flags[0..n) have all reached `value` (sets *status to
 // 10 otherwise).
 void launch_peer_wait(const unsigned int* flags, int n, unsigned int value, unsigned int* status, cudaStream_t stream);
