@@ -1,5 +1,5 @@
 #!/usr/bin/env python
-"""Benchmark of the TurboQuant hot path on B200 ("Measurement").
+"""Benchmark of the TurboQuant hot path on B200.
 
 Headline workload (BASELINE config 0): TQ8 fused dequant-GEMV, weight 4096x4096 drawn
 N(0, 0.02^2) in fp16, row-normalised, blocked WHT (block 128) after a seeded sign
