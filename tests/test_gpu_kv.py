@@ -309,3 +309,38 @@ def test_delta_is_byte_identical_and_applies(tq, golden, case):
         other.close()
     full.close()
     part.close()
+
+
+def test_kv_edge_cases(tq):
+    """Empty appends, empty layers and empty or reversed ranges: nothing changes, nothing faults,
+    and the calls that cannot be served say so."""
+    heads, dim = 2, 128
+    c = tq.TQKVCache(2, heads, dim)
+    assert c.seq_length() == 0 and c.export(0)["tokens"] == 0
+    empty = np.zeros((0, heads, dim), np.float16)
+    c.append(0, empty, empty)                              # zero tokens: a no-op
+    assert c.seq_length() == 0
+    q = np.ones((1, heads, dim), np.float16)
+    with pytest.raises(tq.TQError):
+        tq.compressed_attention([c], 0, q)                 # nothing to attend to
+    assert c.snapshot().size == 32 + 2 * (4 + 4 + 6 * 4)   # a snapshot of an empty cache is just headers
+    k, v = kv_inputs(3, 17, heads, dim)
+    c.append(1, k, v)
+    assert c.seq_length() == 17 and c.export(0)["tokens"] == 0
+    for start, end in [(5, 5), (9, 4), (-1, 3), (0, 18)]:
+        with pytest.raises((tq.TQError, ValueError, IndexError)):
+            tq.compressed_attention([c], 1, q, start=start, end=end)
+    with pytest.raises((tq.TQError, ValueError, IndexError)):
+        tq.compressed_attention([c], 0, q)                 # layer 0 is still empty
+    with pytest.raises((tq.TQError, ValueError, IndexError)):
+        c.append(2, k, v)                                  # no such layer
+    with pytest.raises(ValueError):
+        c.append(1, k[:, :1], v[:, :1])                    # wrong head count
+    c.reserve(1, 4)                                        # smaller than what is stored: a no-op
+    c.append(1, empty, empty)
+    assert c.seq_length() == 17
+    one = tq.compressed_attention([c], 1, q, start=16, end=17)   # a single token: the output is that value vector
+    vals = np.asarray(c.get_values_fp16(1, 16, 17)).astype(np.float32).reshape(heads, dim)
+    assert np.all(np.isfinite(one.astype(np.float32)))
+    assert rel_l2(one[0], vals) < 2e-3
+    c.close()

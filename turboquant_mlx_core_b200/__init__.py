@@ -8,3 +8,4 @@ from ._lib import LIB_PATH, TQ_F16, TQ_F32, LibraryMissing, TQError, load  # noq
 from .api import (Codebook, QuantizedWeight, QuantizerConfig, TQKVCache, TurboQuantLinear,  # noqa: F401
                   append_batch, apply_inverse_wht_rotation, apply_wht_rotation, codebook_from_centroids, compressed_attention,
                   dequantize_weight, generate_codebook, quantize_weight)
+from . import checkpoint  # noqa: F401,E402  (TurboQuant safetensors reader / writer)
