@@ -92,6 +92,21 @@ int tq_quantize_weight(const float* weight, int out_features, int in_features, c
 
 typedef struct tq_linear_s* tq_linear_t;
 
+/* ---- layers of a model loaded by tq_model_load (turboquant_c.h) ----
+ * tq_model_load(dir) reads every TurboQuant safetensors shard of a converted model directory
+ * (tensor names and metadata of src/serialization.cpp:19-97, loading rules of
+ * src/turboquant_c_dequant.cpp:68-150) and uploads each quantised weight as a linear handle; a
+ * directory without such shards gives a model with no layers, as the reference's handle has.  The
+ * handles below stay owned by the model (tq_model_free frees them). */
+#ifndef TURBOQUANT_C_H
+typedef struct tq_model_s* tq_model_t;   /* as in turboquant_c.h */
+#endif
+int tq_model_layer_count(tq_model_t model);
+/** Name of layer `index` (the tensor-name prefix, e.g. "model.layers.0.mlp.down_proj"), NULL if out of range. */
+const char* tq_model_layer_name(tq_model_t model, int index);
+/** The linear handle of the layer called `name`, NULL (see tq_last_error) if there is none. */
+tq_linear_t tq_model_layer(tq_model_t model, const char* name);
+
 /** Build a device-resident linear layer from a QuantizedWeight
  *  (include/turboquant/quantizer.h:22-27) plus its two codebooks.
  *  primary_cols is in/2 (4-bit primary) or in (5-bit primary); the residual plane is

@@ -64,7 +64,27 @@ def test_model_handle(lib):
         m = lib.tq_model_load(d.encode())
         assert m
         assert lib.tq_model_forward(m, None) is None               # stub in the reference as well
+        assert lib.tq_model_layer_count(m) == 0 and lib.tq_model_layer_name(m, 0) is None
+        assert lib.tq_model_layer(m, b"nope") is None
         lib.tq_model_free(m)
+        # shards that are not TurboQuant shards (or passthrough companions) are skipped; a malformed
+        # header is refused with a message, not a crash
+        import struct
+        with open(os.path.join(d, "plain.safetensors"), "wb") as f:
+            h = b'{"x":{"dtype":"F32","shape":[2],"data_offsets":[0,8]}}'
+            f.write(struct.pack("<Q", len(h)) + h + b"\0" * 8)
+        with open(os.path.join(d, "m_passthrough.safetensors"), "wb") as f:
+            f.write(b"garbage that is never parsed")
+        m = lib.tq_model_load(d.encode())
+        assert m and lib.tq_model_layer_count(m) == 0
+        lib.tq_model_free(m)
+        for bad in (b"short", struct.pack("<Q", 1 << 40) + b"{}", struct.pack("<Q", 5) + b'{"a":',
+                    struct.pack("<Q", 62) + b'{"x":{"dtype":"F32","shape":[2],"data_offsets":[0,800000000]}}'):
+            with open(os.path.join(d, "bad.safetensors"), "wb") as f:
+                f.write(bad)
+            assert lib.tq_model_load(d.encode()) is None
+            assert b"tq_model_load" in lib.tq_last_error()
+        os.remove(os.path.join(d, "bad.safetensors"))
         assert lib.tq_model_dequant(d.encode(), d.encode()) != 0
     assert lib.tq_model_dequant(None, None) != 0
 

@@ -119,3 +119,33 @@ def test_load_linears_runs_the_loaded_layers(tq, oracle, tmp_path):
             assert rel_l2(lins[name].forward(x), want) < 1e-3, name      # the linear layer's stated tolerance
         for l in lins.values():
             l.close()
+
+
+@pytest.mark.gpu
+def test_c_model_load_uploads_every_layer(tq, oracle, tmp_path):
+    """tq_model_load over a model directory (C++ safetensors reader): layer names, shapes, and the
+    forward of each loaded handle against the oracle; files written by the `safetensors` package load too."""
+    import ctypes as C
+    from safetensors.numpy import load_file, save_file
+    from turboquant_mlx_core_b200 import checkpoint as ckpt
+    rng = np.random.default_rng(4)
+    layers, shard, _ = _write_model(tq, ckpt, oracle, str(tmp_path), rng)
+    L = tq.load()
+    for rewrite in (False, True):
+        if rewrite:   # the same shard as the safetensors package lays it out (different header order and padding)
+            save_file(load_file(shard), shard, metadata=ckpt.read_tq_metadata(shard))
+        m = L.tq_model_load(str(tmp_path).encode())
+        assert m, L.tq_last_error()
+        n = L.tq_model_layer_count(m)
+        names = sorted(L.tq_model_layer_name(m, i).decode() for i in range(n))
+        assert names == sorted(layers)
+        for name, (pp, pr, norms, seeds, cbp, cbr, bs) in layers.items():
+            h = L.tq_model_layer(m, name.encode())
+            assert h and L.tq_linear_in_features(h) == pr.shape[1] * 2 and L.tq_linear_out_features(h) == pp.shape[0]
+            x = rng.standard_normal((2, pr.shape[1] * 2)).astype(np.float16)
+            y = np.zeros((2, pp.shape[0]), np.float16)
+            assert L.tq_linear_forward(h, x.ctypes.data_as(C.c_void_p), tq.TQ_F16, 2, y.ctypes.data_as(C.c_void_p), None) == 0
+            want = oracle.linear_from_dequant(oracle.dequantize_weight(pp, pr, norms, seeds, cbp, cbr, bs), x.astype(np.float32))
+            assert rel_l2(y, want) < 1e-3, name
+        assert L.tq_model_layer(m, b"missing") is None
+        L.tq_model_free(m)

@@ -93,6 +93,9 @@ def load() -> C.CDLL:
     sig("tq_model_forward", vp, [vp, vp])
     sig("tq_model_free", None, [vp])
     sig("tq_model_dequant", i, [C.c_char_p, C.c_char_p])
+    sig("tq_model_layer_count", i, [vp])
+    sig("tq_model_layer_name", C.c_char_p, [vp, i])
+    sig("tq_model_layer", vp, [vp, C.c_char_p])
 
     sig("tq_kv_cache_create", vp, [i, i, i, i, i, i])
     sig("tq_kv_cache_append", None, [vp, i, vp, vp])

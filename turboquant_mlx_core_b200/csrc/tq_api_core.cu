@@ -60,9 +60,6 @@ const float* analytic_centroids(int bits) {
 
 using namespace tq;
 
-struct tq_model_s {
-    std::string path;
-};
 struct tq_coordinator_s {
     int rank = 0, world = 1;
 };
@@ -202,28 +199,7 @@ int tq_wht_rotate(const float* in, float* out, int rows, int cols, uint32_t seed
     });
 }
 
-// ---- model / coordinator / cluster ------------------------------------------------------------
-
-tq_model_t tq_model_load(const char* model_path) {
-    if (!model_path) return nullptr;
-    struct stat sb;
-    if (stat(model_path, &sb) != 0 || !S_ISDIR(sb.st_mode)) return nullptr;
-    try {
-        auto* m = new tq_model_s();
-        m->path = model_path;
-        return m;
-    } catch (...) {
-        return nullptr;
-    }
-}
-void* tq_model_forward(tq_model_t, const void*) { return nullptr; }
-void tq_model_free(tq_model_t model) { delete model; }
-
-int tq_model_dequant(const char* tq_model_path, const char* output_path) {
-    if (!tq_model_path || !output_path) return 1;
-    set_last_error("tq_model_dequant: safetensors model directories are outside this build; use tq_linear_dequantize per tensor");
-    return 1;
-}
+// ---- coordinator / cluster (the model handle lives in tq_api_model.cu) ------------------------------------------------------------
 
 tq_coordinator_t tq_distributed_init(const char* hostfile, const char*) {
     (void)hostfile;
