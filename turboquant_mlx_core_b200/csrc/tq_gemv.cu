@@ -131,16 +131,6 @@ struct GemvArgs {
     const float* xrot;      // [n_planes, batch, in] fp32 (TF32-rounded); used when x == nullptr
     const __half* x;        // [batch, in] fp16: rotate inside the kernel (WHT block <= 256), else nullptr
     __half* y;              // [batch, y_stride]: row r of activation row n at y[n * y_stride + r]
-    __half* y_peer[7];      // further destinations written with the same values (other GPUs' buffers)
-    int n_peer;
-    long y_stride;
-    // Completion signal of a scattering call (n_signal = 0: none): when the whole grid has
-    // stored its results, word `signal_slot` of every destination's flag array is set to
-    // `signal_value`.  done_counter is a zero-initialised device word owned by the layer.
-    unsigned int* signal[8];
-    int n_signal, signal_slot;
-    unsigned int signal_value;
-    unsigned int* done_counter;
     float* partial;         // [n_slots, 8, out_pad] (only when n_slots > 1)
     unsigned int* counters; // [n_row_units]         (only when n_slots > 1)
     unsigned int* status;   // device error word (0 = ok)
@@ -153,15 +143,37 @@ struct GemvArgs {
     float inv_sqrt_block;
 };
 
+// Arguments of scattering calls, a kernel parameter of their own: with these fields inside
+// GemvArgs the plain kernel (same code otherwise) needed spills within its 128 registers.
+struct ScatterArgs {
+    __half* y_peer[7];      // further destinations written with the same values (other GPUs' buffers)
+    int n_peer;
+    long y_stride;
+    // Completion signal of a scattering call (n_signal = 0: none): when the whole grid has
+    // stored its results, word `signal_slot` of every destination's flag array is set to
+    // `signal_value`.  done_counter is a zero-initialised device word owned by the layer.
+    unsigned int* signal[8];
+    int n_signal, signal_slot;
+    unsigned int signal_value;
+    unsigned int* done_counter;
+};
+
 // One output element goes to the caller's buffer and, when the call scatters, to the same
 // position of up to 7 further buffers (peer GPUs' memory mapped into this process: plain stores
 // over NVLink, no multicast).
-__device__ __forceinline__ void store_y(const GemvArgs& p, int n, int row, __half h) {
-    const size_t o = static_cast<size_t>(n) * p.y_stride + row;
-    p.y[o] = h;
+// SCATTER is a compile-time variant: the plain kernel keeps the register budget it had before the
+// scattering code existed (with it in the same instantiation the kernel spilled).
+template <bool SCATTER>
+__device__ __forceinline__ void store_y(const GemvArgs& p, const ScatterArgs& sc, int n, int row, __half h) {
+    if constexpr (SCATTER) {
+        const size_t o = static_cast<size_t>(n) * sc.y_stride + row;
+        p.y[o] = h;
 #pragma unroll
-    for (int d = 0; d < 7; ++d)
-        if (d < p.n_peer) p.y_peer[d][o] = h;
+        for (int d = 0; d < 7; ++d)
+            if (d < sc.n_peer) sc.y_peer[d][o] = h;
+    } else {
+        p.y[static_cast<size_t>(n) * p.out + row] = h;
+    }
 }
 
 // Shared memory holds only the table and the partial-sum ring: the dynamic allocation ends at
@@ -231,8 +243,8 @@ __device__ __forceinline__ void mma_tf32(float (&c)[4], uint32_t a0, uint32_t a1
 
 // BP = activation rows padded to 1, 2, 4 or 8 (compile time, so that the partial-sum ring
 // geometry and the reduction need no runtime arithmetic).
-template <int BP>
-__global__ void __launch_bounds__(kCtaThreads, 1) tq8_gemv_kernel(const GemvArgs p) {
+template <int BP, bool SCATTER>
+__device__ __forceinline__ void gemv_body(const GemvArgs& p, const ScatterArgs& sargs) {
     // A warp's partial tile is [16 rows][BP] floats plus 4 floats of padding: the 16 tiles a
     // reduction reads side by side then start 4 banks apart instead of in the same bank.
     constexpr int kTileFloats = 16 * BP + 4;
@@ -404,7 +416,7 @@ __global__ void __launch_bounds__(kCtaThreads, 1) tq8_gemv_kernel(const GemvArgs
                 for (int k = 0; k < kPer; ++k) {
                     const int n = n0 + k;
                     if (p.n_slots == 1) {
-                        if (n < p.batch) store_y(p, n, row, __float2half_rn(v[k] * sc));
+                        if (n < p.batch) store_y<SCATTER>(p, sargs, n, row, __float2half_rn(v[k] * sc));
                     } else {
                         p.partial[(static_cast<size_t>(slot) * 8 + n) * p.out_pad + row] = v[k];
                     }
@@ -436,7 +448,7 @@ __global__ void __launch_bounds__(kCtaThreads, 1) tq8_gemv_kernel(const GemvArgs
                         float total = 0.f;
                         for (int c = 0; c < p.n_slots; ++c)
                             total += __ldcg(p.partial + (static_cast<size_t>(c) * 8 + n) * p.out_pad + row);
-                        store_y(p, n, row, __float2half_rn(total * (p.norms[row] * p.inv_scale)));
+                        store_y<SCATTER>(p, sargs, n, row, __float2half_rn(total * (p.norms[row] * p.inv_scale)));
                     }
                 }
             }
@@ -638,21 +650,32 @@ __global__ void __launch_bounds__(kCtaThreads, 1) tq8_gemv_kernel(const GemvArgs
     // Every thread orders its (possibly remote) result stores system-wide, the CTA counts in, and
     // the CTA that completes the grid publishes the flag everywhere.  Whoever then reads the flag
     // with acquire semantics sees all of this launch's results.
-    if (p.n_signal > 0) {
+    if constexpr (SCATTER) {
+    if (sargs.n_signal > 0) {
         __threadfence_system();
         __syncthreads();
         if (tid == 0) {
-            const unsigned int prev = atomicAdd(p.done_counter, 1u);
+            const unsigned int prev = atomicAdd(sargs.done_counter, 1u);
             if (prev == gridDim.x - 1) {
-                *p.done_counter = 0u;  // ready for the next launch (stream order)
+                *sargs.done_counter = 0u;  // ready for the next launch (stream order)
                 __threadfence_system();
 #pragma unroll
                 for (int d = 0; d < 8; ++d)
-                    if (d < p.n_signal)
-                        asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p.signal[d] + p.signal_slot), "r"(p.signal_value) : "memory");
+                    if (d < sargs.n_signal)
+                        asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(sargs.signal[d] + sargs.signal_slot), "r"(sargs.signal_value) : "memory");
             }
         }
     }
+    }
+}
+
+template <int BP>
+__global__ void __launch_bounds__(kCtaThreads, 1) tq8_gemv_kernel(const GemvArgs p) {
+    gemv_body<BP, false>(p, ScatterArgs{});
+}
+template <int BP>
+__global__ void __launch_bounds__(kCtaThreads, 1) tq8_gemv_scatter_kernel(const GemvArgs p, const ScatterArgs sc) {
+    gemv_body<BP, true>(p, sc);
 }
 
 // Waits (bounded) until flags[0..n) have all reached `value`: the receiving side of the completion
@@ -726,23 +749,24 @@ void launch_tq8_gemv_scatter(const uint8_t* codes, const float* norms, const flo
 
     GemvArgs a{};
     a.codes = codes; a.norms = norms; a.table = table; a.y = y; a.status = status;
-    a.n_peer = n_dst - 1;
+    ScatterArgs sa{};
+    sa.n_peer = n_dst - 1;
     for (int d = 1; d < n_dst; ++d) {
         TQ_REQUIRE(dst[d] != nullptr, "tq8_gemv: NULL destination");
-        a.y_peer[d - 1] = dst[d];
+        sa.y_peer[d - 1] = dst[d];
     }
-    a.y_stride = dst_stride;
-    a.n_signal = 0;
+    sa.y_stride = dst_stride;
+    sa.n_signal = 0;
     if (signal != nullptr) {
-        a.n_signal = n_dst;
+        sa.n_signal = n_dst;
         for (int d = 0; d < n_dst; ++d) {
             TQ_REQUIRE(signal[d] != nullptr, "tq8_gemv: NULL signal array");
-            a.signal[d] = signal[d];
+            sa.signal[d] = signal[d];
         }
-        a.signal_slot = signal_slot;
-        a.signal_value = signal_value;
+        sa.signal_slot = signal_slot;
+        sa.signal_value = signal_value;
         TQ_REQUIRE(done_counter != nullptr, "tq8_gemv: signalling needs a completion counter in device memory");
-        a.done_counter = done_counter;
+        sa.done_counter = done_counter;
     }
     a.out = out; a.in = in; a.batch = batch;
     const int n_row_tiles = (out + 15) / 16;
@@ -777,10 +801,14 @@ void launch_tq8_gemv_scatter(const uint8_t* codes, const float* norms, const flo
     int dev = 0;
     TQ_CUDA(cudaGetDevice(&dev));
     if (dev >= 64 || !configured[dev]) {
-        TQ_CUDA(cudaFuncSetAttribute(tq8_gemv_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kGemvSmem)));
-        TQ_CUDA(cudaFuncSetAttribute(tq8_gemv_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kGemvSmem)));
-        TQ_CUDA(cudaFuncSetAttribute(tq8_gemv_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kGemvSmem)));
-        TQ_CUDA(cudaFuncSetAttribute(tq8_gemv_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kGemvSmem)));
+#define TQ_GEMV_ATTR(BPV)                                                                                                          \
+    TQ_CUDA(cudaFuncSetAttribute(tq8_gemv_kernel<BPV>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kGemvSmem))); \
+    TQ_CUDA(cudaFuncSetAttribute(tq8_gemv_scatter_kernel<BPV>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kGemvSmem)));
+        TQ_GEMV_ATTR(1)
+        TQ_GEMV_ATTR(2)
+        TQ_GEMV_ATTR(4)
+        TQ_GEMV_ATTR(8)
+#undef TQ_GEMV_ATTR
         if (dev < 64) configured[dev] = true;
     }
 
@@ -819,12 +847,18 @@ void launch_tq8_gemv_scatter(const uint8_t* codes, const float* norms, const flo
         cfg.stream = stream;
         cfg.attrs = attr;
         cfg.numAttrs = n_attr;
+        // one destination with the layer's own row stride and no signal: the plain variant
+        const bool scatter = sa.n_peer > 0 || sa.n_signal > 0 || sa.y_stride != a.out;
+#define TQ_GEMV_LAUNCH(BPV)                                                   \
+    if (scatter) TQ_CUDA(cudaLaunchKernelEx(&cfg, tq8_gemv_scatter_kernel<BPV>, a, sa)); \
+    else TQ_CUDA(cudaLaunchKernelEx(&cfg, tq8_gemv_kernel<BPV>, a));
         switch (bp) {
-            case 1: TQ_CUDA(cudaLaunchKernelEx(&cfg, tq8_gemv_kernel<1>, a)); break;
-            case 2: TQ_CUDA(cudaLaunchKernelEx(&cfg, tq8_gemv_kernel<2>, a)); break;
-            case 4: TQ_CUDA(cudaLaunchKernelEx(&cfg, tq8_gemv_kernel<4>, a)); break;
-            default: TQ_CUDA(cudaLaunchKernelEx(&cfg, tq8_gemv_kernel<8>, a)); break;
+            case 1: TQ_GEMV_LAUNCH(1) break;
+            case 2: TQ_GEMV_LAUNCH(2) break;
+            case 4: TQ_GEMV_LAUNCH(4) break;
+            default: TQ_GEMV_LAUNCH(8) break;
         }
+#undef TQ_GEMV_LAUNCH
     }
 }
 
