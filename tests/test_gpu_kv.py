@@ -251,6 +251,31 @@ def test_attention_head_counts_and_ragged_ranges(tq, oracle, heads, q_heads):
     c.close()
 
 
+@pytest.mark.parametrize("tokens", [4096, 32768])
+def test_attention_at_benchmark_contexts_matches_oracle(tq, oracle, tokens):
+    """One sequence, 4 KV / 28 query heads, at the context lengths the throughput figures are quoted
+    on: both CUDA kernels (bulk-copy pipeline and load-based), residual bits off and on, each against
+    the CPU checker (mirrors src/attention_dispatch.cpp:58-73 over the fp16 keys and values that
+    src/kv_cache.cpp:292-365 would hand it).  At these lengths the context is cut into dozens of
+    splits, the softmax reference moves lazily and the parts are merged in fixed order."""
+    heads, dim, q_heads = 4, 128, 28
+    k, v = kv_inputs(1000 + tokens, tokens, heads, dim)
+    c = tq.TQKVCache(1, heads, dim)
+    c.append(0, k, v)
+    ex = c.export(0)
+    q = np.random.default_rng(tokens).standard_normal((1, q_heads, dim)).astype(np.float16)
+    for use_qjl in (False, True):
+        want = oracle.attention(q[0].astype(np.float32), heads, ex["k_words"], ex["k_norms"], ex["v_words"], ex["v_norms"],
+                                ex["qjl_words"], ex["qjl_norms"], layer=0, use_qjl=use_qjl)
+        for kernel in (c.ATTENTION_PIPELINE, c.ATTENTION_LOADS):
+            c.set_attention_kernel(kernel)
+            out = tq.compressed_attention([c], 0, q, use_qjl=use_qjl)
+            c.check_attention_status()
+            assert np.all(np.isfinite(out.astype(np.float32)))
+            assert rel_l2(out[0], want) < ATTN_TOL, (tokens, use_qjl, kernel, rel_l2(out[0], want))
+    c.close()
+
+
 def test_attention_kernel_choice_is_automatic_for_long_batches(tq):
     """40 sequences x 8192 tokens fill every CTA slot with 512 tokens or more: the automatic choice is the
     pipeline kernel; it agrees with the load-based kernel, leaves the status clean, and the knob refuses
@@ -289,6 +314,9 @@ def test_delta_is_byte_identical_and_applies(tq, golden, case):
     # reference's does), an empty range is a valid stream
     assert bits_equal(full.delta(3, tokens + 50)[16:], full.delta(3, tokens)[16:])
     assert full.delta(tokens, tokens).size == 16 + layers * (4 + 4 + 6 * 4)
+    # positions of 2^31 and above are narrowed to int as in the reference (src/kv_cache.cpp:571-572):
+    # such an end position is negative, so every layer's range is empty
+    assert full.delta(0, 0xFFFFFFFF).size == 16 + layers * (4 + 4 + 6 * 4)
     part = tq.TQKVCache(layers, heads, dim)
     part.append(layers - 1, k[:3], v[:3])
     part.apply_delta(golden[f"{name}_delta"])          # the reference's own stream

@@ -123,6 +123,37 @@ def test_linear_large_and_split_k(tq, oracle):
         lin.close()
 
 
+@pytest.mark.parametrize("cols", [18944, 27648])
+def test_linear_widest_layers_match_oracle(tq, oracle, cols):
+    """The widest input dimensions of the decoder shapes the throughput figures are quoted on (the
+    7B and 32B down-projections): the dot products are longest here, so this is where 10-bit-mantissa
+    operands use most of the 1e-3 budget.  Fitted (non-analytic) codebooks, ragged row count; 1 and
+    8 activation rows (decode kernel), 9..64 and 2048 (tensor-core kernels), each against
+    dequantize_weight_cpu + matmul (tests/integration/test_linear.cpp:82-145)."""
+    rng = np.random.default_rng(cols)
+    rows, bs = 272, 128
+    cbp = oracle.fit_codebook(rng.standard_normal(100_000).astype(np.float32), 4, 40)[0]
+    cbr = oracle.fit_codebook((rng.standard_normal(100_000) * 0.1).astype(np.float32), 4, 40)[0]
+    w = (rng.standard_normal((rows, cols)) * 0.02).astype(np.float16).astype(np.float32)
+    pp, pr, norms, seeds = oracle.quantize_weight(w, cbp, cbr, 4, 4, bs, True)
+    deq = oracle.dequantize_weight(pp, pr, norms, seeds, cbp, cbr, bs)
+    lin = tq.TurboQuantLinear(cols, rows, tq.QuantizedWeight(pp, pr, norms, seeds), tq.codebook_from_centroids(cbp),
+                              tq.codebook_from_centroids(cbr), bs)
+    assert bits_equal(lin.dequantize(np.float32), deq)
+    deq64 = deq.astype(np.float64)
+    for batch in (1, 8, 9, 33, 64, 2048):
+        x = rng.standard_normal((batch, cols)).astype(np.float16)
+        want = x.astype(np.float64) @ deq64.T
+        y = lin.forward(x)
+        assert np.all(np.isfinite(y.astype(np.float32)))
+        assert rel_l2(y, want) < LINEAR_TOL, (cols, batch, rel_l2(y, want))
+        num = np.linalg.norm(y.astype(np.float64) - want, axis=1)
+        den = np.linalg.norm(want, axis=1) + 1e-30
+        assert np.max(num / den) < 2 * LINEAR_TOL, (cols, batch, float(np.max(num / den)))
+    lin.check_status()
+    lin.close()
+
+
 def test_linear_device_tensors_and_stream(tq, oracle):
     torch = pytest.importorskip("torch")
     rng = np.random.default_rng(2)

@@ -4,9 +4,11 @@ It is for callers that cannot let a library allocate: a server that has handed t
 the GPU's memory to its own pool, or code running inside an open stream capture.  The entry
 takes device pointers only and draws its working memory from a fixed 2 MiB array built into
 the library, shared by all calls on the device — so the test calls it twice in a row (the
-second call finds the first one's leftovers in that array) and compares both results with the
-ordinary tq_linear_forward on the same inputs.  Collected last on purpose: a run that stops
-at the first failure has then already run every other test.
+second call finds the first one's leftovers in that array) and checks both results bit for bit
+against the ordinary tq_linear_forward on the same inputs and, within the linear tolerance,
+against the CPU checker; it also checks that the device's free memory did not shrink.
+Collected last on purpose: a run that stops at the first failure has then already run every
+other test.
 """
 import ctypes as C
 
@@ -20,34 +22,48 @@ pytestmark = pytest.mark.gpu
 LINEAR_TOL = 1e-3   # the tolerance of the linear-forward parity tests
 
 
-def _layer(tq, oracle, rows, cols, block, shared, seed):
+def _layer(tq, oracle, rows, cols, block, shared, seed, with_dequant=False):
     rng = np.random.default_rng(seed)
     cb = oracle.codebook(4)[0]
     w = (rng.standard_normal((rows, cols)) * 0.02).astype(np.float16).astype(np.float32)
     pp, pr, norms, seeds = oracle.quantize_weight(w, cb, cb, 4, 4, block, shared)
     c = tq.codebook_from_centroids(cb)
-    return tq.TurboQuantLinear(cols, rows, tq.QuantizedWeight(pp, pr, norms, seeds), c, c, block)
+    lin = tq.TurboQuantLinear(cols, rows, tq.QuantizedWeight(pp, pr, norms, seeds), c, c, block)
+    if with_dequant:
+        return lin, oracle.dequantize_weight(pp, pr, norms, seeds, cb, cb, block)
+    return lin
 
 
 @pytest.mark.parametrize("rows,cols,block,shared,batch", [
     (300, 8192, 128, True, 3),     # two column chunks: partial sums and arrival counters in the array
     (512, 1024, 256, False, 8),    # dual rotation: two planes
     (4096, 4096, 128, True, 1),    # the headline shape
+    (96, 2048, 512, True, 2),      # WHT block above 256: the rotated activation goes through the array too
+    (40, 5120, 1024, False, 5),    # the same with two planes and two column chunks
 ])
 def test_noalloc_forward_matches_ordinary_forward_twice(tq, oracle, rows, cols, block, shared, batch):
     torch = pytest.importorskip("torch")
     L = tq.load()
-    lin = _layer(tq, oracle, rows, cols, block, shared, seed=rows + cols)
+    lin, deq = _layer(tq, oracle, rows, cols, block, shared, seed=rows + cols, with_dequant=True)
     g = torch.Generator(device="cuda").manual_seed(3)
     xs = [torch.randn((batch, cols), generator=g, device="cuda").half() for _ in range(2)]
+    free_before = None
     for x in xs:                                   # two calls in a row share the built-in array
         want = lin.forward(x)
         got = torch.full((batch, rows), float("nan"), device="cuda", dtype=torch.float16)
+        torch.cuda.synchronize()
+        if free_before is None:
+            free_before = torch.cuda.mem_get_info()[0]
         rc = L.tq_linear_forward_noalloc(lin.handle, C.c_void_p(x.data_ptr()), batch, C.c_void_p(got.data_ptr()), None)
         assert rc == 0, L.tq_last_error().decode()
         torch.cuda.synchronize()
         assert torch.isfinite(got).all()
-        assert rel_l2(got.float().cpu().numpy(), want.float().cpu().numpy()) < LINEAR_TOL
+        # same kernels, same summation order, only the scratch pointer differs: the bits must agree
+        assert torch.equal(got, want)
+        ref = oracle.linear_from_dequant(deq, x.float().cpu().numpy())
+        assert rel_l2(got.float().cpu().numpy(), ref) < LINEAR_TOL
+    # neither call took memory from the device (the first one only looked up the array's address)
+    assert torch.cuda.mem_get_info()[0] >= free_before
     lin.close()
 
 

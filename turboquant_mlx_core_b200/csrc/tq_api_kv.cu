@@ -314,9 +314,13 @@ public:
     // ---- delta stream (src/cache_snapshot.cpp:18-31, 110-140; src/kv_cache.cpp:566-594) ----
     // header: "TQCD", from, to, layers; per layer: blob bytes, then the same blob as in a snapshot
     // holding positions [from, to) clamped to the layer's token count.
-    static void clamp_range(const LayerKVStorage& L, long from, long to, int& a, int& b) {
-        a = static_cast<int>(std::max<long>(from, 0));
-        b = static_cast<int>(std::min<long>(to, L.num_tokens));
+    // Positions arrive as uint32 and are narrowed to int first, as the reference does
+    // (src/kv_cache.cpp:571-572): values of 2^31 and above turn negative, so such a `to` gives an
+    // empty range and such a `from` starts at 0.
+    static void clamp_range(const LayerKVStorage& L, uint32_t from_u, uint32_t to_u, int& a, int& b) {
+        const int from = static_cast<int>(from_u), to = static_cast<int>(to_u);
+        a = std::max(from, 0);
+        b = std::min(to, L.num_tokens);
         if (b < a) b = a;
     }
     size_t range_blob_bytes(int tokens) const {

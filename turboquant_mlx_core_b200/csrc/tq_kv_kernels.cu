@@ -1181,10 +1181,13 @@ template <int GH, typename QT>
 static void launch_attn_pipe(const AttnSeq* seqs, int n_seqs, const QT* q, int q_heads, int kv_heads, int n_splits, uint32_t k_seed,
                              uint32_t qjl_seed, bool use_qjl, float inv_sqrt, float inv_scale_d, float attn_scale, float gamma,
                              float* part_acc, float* part_ml, unsigned int* status, cudaStream_t stream) {
-    static bool configured = false;   // per instantiation; the attribute is per function and idempotent
-    if (!configured) {
+    // the opt-in shared-memory size is a per-device attribute of each instantiation
+    static bool configured[64] = {false};
+    int dev = 0;
+    TQ_CUDA(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64 || !configured[dev]) {
         TQ_CUDA(cudaFuncSetAttribute(attn_pipe_kernel<GH, QT>, cudaFuncAttributeMaxDynamicSharedMemorySize, PipeLayout<GH>::kSmemBytes));
-        configured = true;
+        if (dev >= 0 && dev < 64) configured[dev] = true;
     }
     const int gchunks = (q_heads / kv_heads + kAttnGMax - 1) / kAttnGMax;
     const dim3 grid(n_splits, (kv_heads / GH) * gchunks, n_seqs);
