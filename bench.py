@@ -1,7 +1,7 @@
 #!/usr/bin/env python
 """Benchmark of the TurboQuant hot path on B200.
 
-Headline workload (BASELINE config 0): TQ8 fused dequant-GEMV, weight 4096x4096 drawn
+Headline workload: TQ8 fused dequant-GEMV, weight 4096x4096 drawn
 N(0, 0.02^2) in fp16, row-normalised, blocked WHT (block 128) after a seeded sign
 diagonal, 4-bit Lloyd-Max primary + 4-bit Lloyd-Max residual codebooks fitted to the
 data, batch-1 fp16 activation ~ N(0,1).  A step is one pass over NBUF distinct weight
@@ -295,7 +295,7 @@ def run_cuda(args):
         "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_max / args.steps,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": value / world / PUBLISHED_TOK_S if world == 1 else None,
         "dtype": "tf32 multiply, fp32 accumulate (fp16 activations in, fp16 out)", "data": "synthetic",
-        "config": {"workload": "BASELINE config 0: TQ8 4+4-bit fused dequant-GEMV, 4096x4096, block 128, shared rotation, "
+        "config": {"workload": "TQ8 4+4-bit fused dequant-GEMV, 4096x4096, block 128, shared rotation, "
                                "fitted Lloyd-Max codebooks, batch 1",
                    "layers_per_step": nbuf, "l2_policy": f"{nbuf} distinct weight matrices per step "
                                                          f"({nbuf * OUT_F * IN_F / 1e6:.0f} MB) "
@@ -355,7 +355,7 @@ def run_cuda(args):
         print(json.dumps(line))
 
 
-# ---- secondary: compressed-cache decode attention (BASELINE config 3) ---------------------------
+# ---- secondary: compressed-cache decode attention (16 sequences, 4 KV / 28 query heads) ---------------------------
 
 def bench_attention(tq, L, device, stream, rank, world, args, ctx):
     """16 sequences, 4 KV / 28 query heads, d 128, QJL on.  Up to 4 ranks split the KV heads (heads
@@ -533,7 +533,7 @@ def bench_side_kernels(tq, L, layers, device, stream, args):
     return res
 
 
-# ---- secondary: prefill through the tensor-core GEMM (BASELINE config 1, prefill part) -------------
+# ---- secondary: prefill through the tensor-core GEMM (2048 activation rows) -------------
 
 def bench_prefill(tq, L, layers, device, stream, args):
     """2048 activation rows through 4096x4096 TQ8 layers (distinct layers back to back, as in the
@@ -580,7 +580,7 @@ def bench_prefill(tq, L, layers, device, stream, args):
             "peak_tflops": peak, "peak_kind": peak_kind}
 
 
-# ---- secondary: decoder-layer projections at decode batch sizes (BASELINE config 1) ----------------
+# ---- secondary: decoder-layer projections at decode batch sizes (Qwen2.5-7B shapes) ----------------
 
 def bench_decoder_layer(tq, L, device, stream, cbs, args):
     """The seven projections of a Qwen2.5-7B-shaped decoder layer (hidden 3584, intermediate 18944,
@@ -628,7 +628,7 @@ def bench_decoder_layer(tq, L, device, stream, cbs, args):
     return res
 
 
-# ---- secondary: row-sharded LM head (BASELINE config 2) -------------------------------------------
+# ---- secondary: row-sharded LM head (151936 x 2048) -------------------------------------------
 
 def bench_lm_head(tq, L, device, stream, rank, world, cbs, args):
     import torch
@@ -852,7 +852,7 @@ def run_reference(args):
         "impl": "reference", "metric": "tq8_dequant_gemv_4096x4096_b1_tok_per_s", "value": value, "unit": "tok/s",
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "fp32", "data": "synthetic",
-        "config": {"workload": "BASELINE config 0: TQ8 4+4-bit linear, 4096x4096, block 128, shared rotation, batch 1; "
+        "config": {"workload": "TQ8 4+4-bit linear, 4096x4096, block 128, shared rotation, batch 1; "
                                "each step = one layer forward on the host cores"},
         "cpu_baseline": {"value": value, "unit": "tok/s", "cores": threads, "kind": kind,
                          "sample": "one 4096x4096 layer forward per step: the reference's dequantize_weight_cpu "

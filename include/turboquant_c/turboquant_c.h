@@ -63,7 +63,8 @@ void tq_kv_cache_free(tq_kv_cache_t cache);
 /* ---- coordinator (reference :74-86) ------------------------------------------------ */
 
 /* Multi-host bring-up from a hostfile is not part of this build: returns NULL.
- * Multi-GPU runs use one process per GPU with NCCL. */
+ * Multi-GPU runs use one process per GPU; the caller's launcher (e.g. torchrun) assigns the
+ * ranks and the sharded entry points of turboquant_b200.h take peer-mapped buffers. */
 tq_coordinator_t tq_distributed_init(const char* hostfile, const char* backend);
 /* Single-process coordinator: rank 0 of 1. */
 tq_coordinator_t tq_distributed_init_local(void);

@@ -21,7 +21,8 @@ import sys
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 REF_SOURCES = ["codebook", "rotation", "quantizer", "dequantizer", "kv_cache", "cache_snapshot"]
-DEFAULT_REFERENCE_ROOT = os.environ.get("TQ_REFERENCE_ROOT", "/root/reference")
+# The reference source tree: $TQ_REFERENCE_ROOT, else a folder named "reference" beside the repository.
+DEFAULT_REFERENCE_ROOT = os.environ.get("TQ_REFERENCE_ROOT") or os.path.join(os.path.dirname(os.path.dirname(HERE)), "reference")
 
 
 def _newer(target: str, deps: list[str]) -> bool:

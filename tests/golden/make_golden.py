@@ -71,7 +71,7 @@ def main():
         for inv in (0, 1):
             out[name + f"_wht{inv}"] = ref.wht(w, 12345 + rows, bs, bool(inv))
 
-    # fitted codebooks on Gaussian weights (the recipe of BASELINE config 0, small)
+    # fitted codebooks on Gaussian weights (the recipe of the headline 4096 x 4096 benchmark layer, small)
     w = gauss_weight(0, 64, 512)
     cb4, _ = ref.codebook(4)
     pp, pr, norms, seeds = ref.quantize_weight(w, cb4, cb4, 4, 4, 128, True)

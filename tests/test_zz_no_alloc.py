@@ -81,7 +81,7 @@ def test_noalloc_refuses_what_it_cannot_serve(tq, oracle):
     assert L.tq_linear_forward_noalloc(None, C.c_void_p(x.data_ptr()), 1, C.c_void_p(y.data_ptr()), None) != 0
     lin.close()
     # a layer whose working set exceeds the built-in array is refused, with the sizes in the message
-    rows, cols = 13000, 8192                      # dual rotation: 4 partial-sum slots of 8 x 13008 floats
+    rows, cols = 64, 32768                        # dual rotation: the rotated activation alone fills the 2 MiB
     rng = np.random.default_rng(5)
     planes = [rng.integers(0, 256, (rows, cols // 2), dtype=np.uint8) for _ in range(2)]
     cb = tq.generate_codebook(4)

@@ -6,7 +6,7 @@
 // 256-entry centroid-sum table (src/dequantizer.cpp:619-643, 674-688) — is decided once
 // when the handle is built.
 #include <cmath>
-
+#include <cstdlib>
 #include <cstring>
 
 #include "tq_host.hpp"
@@ -93,6 +93,13 @@ public:
         if (sb) {
             scratch_.resize(sb);
             TQ_CUDA(cudaMemset(scratch_.as<void>(), 0, sb));
+        }
+        const size_t ssb = tq::gemv_staged_scratch_bytes(out_, in_, dual_ ? 2 : 1, sm_count_);
+        staged_scratch_.resize(ssb);
+        TQ_CUDA(cudaMemset(staged_scratch_.as<void>(), 0, ssb));
+        if (const char* env = std::getenv("TQ_DECODE_KERNEL")) {
+            if (std::strcmp(env, "classic") == 0) decode_kernel_ = 1;
+            else if (std::strcmp(env, "staged") == 0) decode_kernel_ = 2;
         }
         counter_.resize(sizeof(unsigned int));  // grid completion counter of scattering calls
         TQ_CUDA(cudaMemset(counter_.as<void>(), 0, sizeof(unsigned int)));
@@ -239,9 +246,15 @@ public:
         TQ_REQUIRE(tq::is_device_pointer(x) && tq::is_device_pointer(y),
                    "allocation-free forward: x and y must be device pointers (copying host memory would need a staging allocation)");
         TQ_CUDA(cudaSetDevice(device_));
-        tq::launch_tq8_gemv_static(codes_.as<uint8_t>(), norms_.as<float>(), tables_.as<float>(),
-                                   static_cast<const __half*>(x), static_cast<__half*>(y), out_, in_, batch, block_,
-                                   dual_ ? 2 : 1, seed_p_, seed_r_, d_status_, sm_count_, st);
+        // the kernel forward() would run, when its working set fits the array; else the other one
+        if (decode_kernel_ == 2 && tq::gemv_staged_fits_static(out_, in_, batch, dual_ ? 2 : 1, sm_count_))
+            tq::launch_tq8_gemv_staged_static(codes_.as<uint8_t>(), norms_.as<float>(), tables_.as<float>(),
+                                              static_cast<const __half*>(x), static_cast<__half*>(y), out_, in_, batch, block_,
+                                              dual_ ? 2 : 1, seed_p_, seed_r_, d_status_, sm_count_, st);
+        else
+            tq::launch_tq8_gemv_static(codes_.as<uint8_t>(), norms_.as<float>(), tables_.as<float>(),
+                                       static_cast<const __half*>(x), static_cast<__half*>(y), out_, in_, batch, block_,
+                                       dual_ ? 2 : 1, seed_p_, seed_r_, d_status_, sm_count_, st);
     }
 
     ~TurboQuantLinear() {
@@ -262,11 +275,11 @@ private:
 
     // Device pointers only.  More than kGemmMinBatch rows go to the tensor-core GEMM (when the
     // shape allows); otherwise batches above 8 rows are issued as passes of 8 through the GEMV.
-    static constexpr int kGemmMinBatch = 32;
+    static constexpr int kGemmMinBatch = 8;
     void launch_forward(const __half* d_x, int batch, __half* d_y, cudaStream_t st) {
-        // (a tall matrix fills every SM with row tiles, so the GEMM already pays off at 17 rows)
-        const bool tall = (out_ + 127) / 128 >= 2 * sm_count_;
-        if ((batch > kGemmMinBatch || (tall && batch > 16)) && tq::gemm_supported(in_)) {
+        // From 9 rows on the tensor-memory kernel streams the codes once whatever the batch (its
+        // activation tile is as narrow as the batch, in steps of 16 rows).
+        if (batch > kGemmMinBatch && tq::gemm_supported(in_)) {
             const int planes = dual_ ? 2 : 1;
             gemm_scratch_.reserve(tq::gemm_scratch_bytes(out_, in_, batch, planes, sm_count_));
             tq::launch_tq8_gemm(codes_.as<uint8_t>(), norms_.as<float>(), tables_.as<float>(), d_x, d_y, out_, in_, batch,
@@ -276,10 +289,16 @@ private:
         }
         for (int b0 = 0; b0 < batch; b0 += 8) {
             const int nb = batch - b0 < 8 ? batch - b0 : 8;
-            tq::launch_tq8_gemv(codes_.as<uint8_t>(), norms_.as<float>(), tables_.as<float>(),
-                                d_x + static_cast<size_t>(b0) * in_, d_y + static_cast<size_t>(b0) * out_, out_, in_, nb,
-                                block_, dual_ ? 2 : 1, seed_p_, seed_r_, scratch_.as<void>(),
-                                d_status_, sm_count_, st);
+            if (decode_kernel_ == 2)
+                tq::launch_tq8_gemv_staged(codes_.as<uint8_t>(), norms_.as<float>(), tables_.as<float>(),
+                                           d_x + static_cast<size_t>(b0) * in_, d_y + static_cast<size_t>(b0) * out_, out_, in_,
+                                           nb, block_, dual_ ? 2 : 1, seed_p_, seed_r_, staged_scratch_.as<void>(), d_status_,
+                                           sm_count_, st);
+            else
+                tq::launch_tq8_gemv(codes_.as<uint8_t>(), norms_.as<float>(), tables_.as<float>(),
+                                    d_x + static_cast<size_t>(b0) * in_, d_y + static_cast<size_t>(b0) * out_, out_, in_, nb,
+                                    block_, dual_ ? 2 : 1, seed_p_, seed_r_, scratch_.as<void>(),
+                                    d_status_, sm_count_, st);
         }
     }
 
@@ -288,7 +307,8 @@ private:
     int device_ = 0, sm_count_ = 0;
     bool primary_5bit_ = false, has_residual_ = false, shared_ = false, dual_ = false;
     uint32_t seed_p_ = 0, seed_r_ = 0;
-    DeviceBuffer codes_, norms_, tables_, scratch_, gemm_scratch_, counter_;
+    DeviceBuffer codes_, norms_, tables_, scratch_, staged_scratch_, gemm_scratch_, counter_;
+    int decode_kernel_ = 0;               // 0 / 1: register-streamed kernel (the default), 2: bulk-copy staged kernel (TQ_DECODE_KERNEL=staged)
     DeviceBuffer x_f16_, x_f32_, y_f16_;  // staging for host-side callers
     unsigned int* h_status_ = nullptr;    // the kernels' error word: page-locked host memory
     unsigned int* d_status_ = nullptr;    // its address for kernels

@@ -12,16 +12,20 @@
 // against x rotated with the primary seed, residual table against x rotated with the residual
 // seed).
 //
-// One CTA computes a 128 (weight rows) x 256 (activation rows) tile of y^T:
+// One CTA computes a 128 (weight rows) x 256 (activation rows, or fewer) tile of y^T:
 //   D[128 x 256] (TMEM, fp32) += A[128 x 64] (weights, fp16, TMEM) . B[256 x 64]^T (xrot, fp16, smem)
 // per 64-column K block, as four tcgen05.mma (M 128, N 256, K 16) issued by one thread.
-//   warps 0-7  producers: codes HBM -> registers (four K blocks ahead) -> lookup (lane-private
-//              fp16 table in shared memory) -> weight tile in TENSOR memory (tcgen05.st; lane = row,
-//              32 columns of fp16 pairs per K block), ring of 4, published one K block late
-//   warp 9     activation tiles: the rotation kernel stores xrot in operand-tile order, so a tile
-//              is one contiguous 32 KB bulk copy (cp.async.bulk, mbarrier complete_tx), ring of 4
-//   warp 8     waits for both tiles of a K block, issues the MMAs, commits to the rings' empty barriers
-//   warps 0-7  epilogue: tcgen05.ld the accumulator, scale by norm * inv_scale, store fp16
+//   warps 0-15 producers in four groups; group j takes the K blocks j, j + 4, ...: codes HBM ->
+//              registers (two of the group's K blocks ahead) -> lookup (lane-private fp16 table in
+//              shared memory) -> weight tile in TENSOR memory (tcgen05.st; lane = row, 32 columns of
+//              fp16 pairs per K block), ring of 8 stages (two per group)
+//   warp 17    activation tiles: the rotation kernel stores xrot in operand-tile order, so a tile
+//              is one contiguous bulk copy (cp.async.bulk, mbarrier complete_tx) of 128 bytes per
+//              activation row of the tile; the ring has as many stages as fit (4 for 256 rows)
+//   warp 16    waits for both tiles of a K block, issues the MMAs, commits to the rings' empty barriers
+//   warps 0-15 epilogue: tcgen05.ld the accumulator, scale by norm * inv_scale, store fp16
+// The activation tile is as tall as the rows it really has (in steps of 16): a decode batch of 9..64
+// rows costs a short MMA and a short copy, so the codes are streamed once whatever the batch.
 // The dequantised weights never touch HBM; a weight tile is looked up once per 256 activation
 // rows.  Roofline: tensor pipe (2 * M * out * in flops), with the table lookups (one shared-memory
 // load per weight per 256 activation rows) as the competing pipe.
@@ -47,26 +51,29 @@ namespace {
 constexpr int kTileRows = 128;  // weight rows per CTA (MMA M)
 constexpr int kTileTok = 256;   // activation rows per CTA (MMA N)
 constexpr int kBlockK = 64;     // K columns per stage
-constexpr int kAStages = 4;    // weight-tile ring in tensor memory (filled just in time by the lookups)
-constexpr int kBStagesMax = 4; // activation-tile ring in shared memory (bulk copies run this far ahead)
-constexpr int kFull = 4;       // "K block ready" barriers
-constexpr int kProducerWarps = 8;
+constexpr int kAStages = 8;    // weight-tile ring in tensor memory: two stages per producer group
+constexpr int kBStagesMax = 16; // activation-tile ring in shared memory: as many stages as fit, up to this
+constexpr int kFull = kAStages;  // "K block ready" barriers, one per weight-tile stage
+constexpr int kGroups = 4;     // producer groups: group j dequantises the K blocks j, j + 4, j + 8, ...
+constexpr int kProducerWarps = 4 * kGroups;
 constexpr int kProducerThreads = kProducerWarps * 32;
 constexpr int kMmaWarp = kProducerWarps;       // issues the MMAs, owns the tensor-memory allocation
 constexpr int kCopyWarp = kProducerWarps + 1;  // issues the activation-tile bulk copies
 constexpr int kGemmThreads = kProducerThreads + 64;
 constexpr uint32_t kBBytes = kTileTok * kBlockK * 2;   // 32 KB
 constexpr uint32_t kLutBytes = 256 * 32 * 4;           // one plane: 256 entries x 32 lane copies x (fp16, fp16)
-constexpr uint32_t kTmemCols = 512;   // accumulator: columns 0..255; weight tiles: 32 columns each from 256 on
+constexpr uint32_t kTmemCols = 512;   // accumulator: columns 0..255; weight tiles: 8 x 32 columns from 256 on
 constexpr uint32_t kTmemAColumn = 256;
 constexpr uint32_t kTmemAStageCols = kBlockK / 2;  // two fp16 per 32-bit column
 // rings + tables (4 activation stages with one table plane, 3 with two) + worst-case padding in
 // front of the 32 KB-aligned tables
-constexpr size_t kGemmSmemBytes = kBStagesMax * kBBytes + 2 * kLutBytes + 32768 + 1024;
+constexpr size_t kGemmSmemBytes = 4 * kBBytes + 2 * kLutBytes + 32768 + 1024;
 constexpr unsigned long long kGemmWaitLimitNs = 200ull * 1000 * 1000;
 
-// instruction descriptor: D fp32, A and B fp16, both K-major, N = 256, M = 128
-constexpr uint32_t kInstrDesc = (1u << 4) | (static_cast<uint32_t>(kTileTok >> 3) << 17) | (static_cast<uint32_t>(kTileRows >> 4) << 24);
+// instruction descriptor: D fp32, A and B fp16, both K-major, M = 128, N = n (a multiple of 16 up to 256)
+__host__ __device__ constexpr uint32_t instr_desc(uint32_t n) {
+    return (1u << 4) | ((n >> 3) << 17) | (static_cast<uint32_t>(kTileRows >> 4) << 24);
+}
 
 __device__ __forceinline__ uint32_t smem_addr(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
 
@@ -106,12 +113,13 @@ __device__ __forceinline__ uint64_t smem_desc(uint32_t addr) {
 
 // D[tmem_d] (+)= A[tmem_a] . B[desc_b]^T : A from tensor memory (128 lanes x 8 columns of fp16 pairs),
 // B from shared memory.
-__device__ __forceinline__ void umma_f16_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t desc_b, uint32_t accumulate) {
+__device__ __forceinline__ void umma_f16_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t desc_b, uint32_t idesc,
+                                            uint32_t accumulate) {
     asm volatile(
         "{ .reg .pred p; setp.ne.b32 p, %4, 0;\n"
         "  tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, {%5, %5, %5, %5}, p; }"
         :
-        : "r"(tmem_d), "r"(tmem_a), "l"(desc_b), "r"(kInstrDesc), "r"(accumulate), "r"(0u)
+        : "r"(tmem_d), "r"(tmem_a), "l"(desc_b), "r"(idesc), "r"(accumulate), "r"(0u)
         : "memory");
 }
 // 16 consecutive 32-bit columns of this thread's tensor-memory lane.
@@ -277,29 +285,37 @@ __global__ void __launch_bounds__(kGemmThreads, 1) tq8_gemm_kernel(const GemmArg
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int row0 = blockIdx.x * kTileRows;  // first weight row of the tile
     const int tok0 = blockIdx.y * kTileTok;   // first activation row of the tile
+    // Activation rows this tile really has, rounded up to the MMA's granularity of 16: a short tile
+    // (a decode batch of 9..64 rows, or the tail of a prefill) costs a short MMA and a short copy.
+    const int n_tile = min(kTileTok, ((p.m - tok0) + 15) & ~15);
+    const uint32_t b_bytes = static_cast<uint32_t>(n_tile) * (kBlockK * 2);   // the tile's first n_tile rows are contiguous
+    const uint32_t idesc = instr_desc(static_cast<uint32_t>(n_tile));
 
     // ---- shared-memory map -------------------------------------------------------------------
     // The lookup tables sit at a 32 KB-aligned window address (so that table base, lane offset
     // and scaled code occupy disjoint address bits); the 16 KB / 32 KB stage buffers are packed
     // around them.
-    const int n_b = kBStagesMax;
     const uint32_t raw = smem_addr(gemm_smem);
     const uint32_t base = (raw + 127u) & ~127u;
     const uint32_t lut_addr = (base + 32767u) & ~32767u;
     const uint32_t lut_end = lut_addr + kLutBytes * static_cast<uint32_t>(p.n_planes);
     uint32_t dyn_bytes;
     asm("mov.u32 %0, %%dynamic_smem_size;" : "=r"(dyn_bytes));
+    // A stage holds the tile's real rows only, so a short tile gets a deep ring.
+    int n_b = 0;
     {
         // Same arithmetic in every thread; thread 0 publishes the stage addresses.
         uint32_t lo = base, hi = lut_end;  // bump pointers below and above the tables
+        const uint32_t end = raw + dyn_bytes;
         uint32_t addr[kBStagesMax];
 #pragma unroll
         for (int s = 0; s < kBStagesMax; ++s) {
-            if (s >= n_b) { addr[s] = 0; continue; }
-            if (lo + kBBytes <= lut_addr) { addr[s] = lo; lo += kBBytes; }
-            else { addr[s] = hi; hi += kBBytes; }
+            addr[s] = 0;
+            if (n_b != s) continue;   // an earlier stage did not fit: stop
+            if (lo + b_bytes <= lut_addr) { addr[s] = lo; lo += b_bytes; n_b = s + 1; }
+            else if (hi + b_bytes <= end) { addr[s] = hi; hi += b_bytes; n_b = s + 1; }
         }
-        if (hi > raw + dyn_bytes || lut_end > raw + dyn_bytes) {  // layout does not fit: refuse to run (nothing allocated yet)
+        if (n_b < 2 || lut_end > end) {  // layout does not fit: refuse to run (nothing allocated yet)
             if (tid == 0) raise_status(p.status, 9u);
             return;
         }
@@ -313,7 +329,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) tq8_gemm_kernel(const GemmArg
                    bar_accum = smem_addr(&s_accum);
 
     if (tid == 0) {
-        for (int s = 0; s < kFull; ++s) bar_init(bar_full + 8u * s, kProducerThreads);
+        for (int s = 0; s < kFull; ++s) bar_init(bar_full + 8u * s, kProducerWarps / kGroups);   // one arrival per warp of the group
         for (int s = 0; s < kAStages; ++s) bar_init(bar_empty_a + 8u * s, 1);
         for (int s = 0; s < kBStagesMax; ++s) {
             bar_init(bar_empty_b + 8u * s, 1);
@@ -353,52 +369,47 @@ __global__ void __launch_bounds__(kGemmThreads, 1) tq8_gemm_kernel(const GemmArg
     if (warp < kProducerWarps) {
         // ---- producers ------------------------------------------------------------------------
         // Weight tile in tensor memory: lane = row of the tile, 32 columns per K block (two fp16 per
-        // column).  A warp may touch lanes 32 * (warp % 4) .. + 31: warp w owns those rows and the
-        // column half w / 4 (K 0..31 or 32..63 of the block); a thread dequantises 32 codes of its row.
+        // column).  A warp may touch lanes 32 * (warp % 4) .. + 31.  The 16 producer warps form four
+        // groups (warp / 4); group j dequantises the K blocks j, j + 4, ... whole (a thread: the 64
+        // codes of its row) into the stages j and j + 4 alternately, so four K blocks are in the
+        // making at any time and a group's chain (codes -> lookups -> tensor-memory stores -> publish)
+        // has four K-block times to complete.
         const int ar = 32 * (warp & 3) + lane;       // row inside the tile
-        const int ah = warp >> 2;                    // which 32 columns of the K block
+        const int grp = warp >> 2;
         const int grow = min(row0 + ar, p.out - 1);  // rows past the matrix repeat the last row (never stored)
         // a row's 64 columns of K block kb are 64 contiguous bytes of code tile (row / 16, kb)
-        const uint8_t* code_ptr = p.codes + code_offset(grow, 32 * ah, code_tiles_per_row(p.in));
-        const uint32_t a_taddr = tmem_d + (static_cast<uint32_t>(32 * (warp & 3)) << 16) + kTmemAColumn + 16u * ah;
+        const uint8_t* code_ptr = p.codes + code_offset(grow, 0, code_tiles_per_row(p.in));
+        const uint32_t a_taddr = tmem_d + (static_cast<uint32_t>(32 * (warp & 3)) << 16) + kTmemAColumn;
         const uint32_t lut_lane = lut_addr + static_cast<uint32_t>(lane) * 4u;
 
-        // Codes are fetched kCodeAhead K blocks ahead into a register ring (a K block is consumed
-        // in well under the DRAM latency).  The second plane reads the same bytes again.
-        constexpr int kCodeAhead = 4;
-        auto load_codes = [&](int kb, uint4& lo, uint4& hi) {
+        // Codes are fetched two of the group's K blocks ahead into registers.  The second plane
+        // reads the same bytes again.
+        auto load_codes = [&](int kb, uint4 (&c)[4]) {
             if (kb < n_kb) {
                 const int plane = (kb_base + kb) >= kb_per_plane ? 1 : 0;
-                const uint8_t* src = code_ptr + static_cast<size_t>(kb_base + kb - plane * kb_per_plane) * kCodeTileBytes;
-                lo = __ldg(reinterpret_cast<const uint4*>(src));
-                hi = __ldg(reinterpret_cast<const uint4*>(src + 16));
+                const uint4* src = reinterpret_cast<const uint4*>(
+                    code_ptr + static_cast<size_t>(kb_base + kb - plane * kb_per_plane) * kCodeTileBytes);
+#pragma unroll
+                for (int i = 0; i < 4; ++i) c[i] = __ldg(src + i);
             }
         };
-        uint4 clo[kCodeAhead], chi[kCodeAhead];
+        uint4 c0[4], c1[4], c2[4];
 #pragma unroll
-        for (int u = 0; u < kCodeAhead; ++u) {
-            clo[u] = make_uint4(0, 0, 0, 0);
-            chi[u] = make_uint4(0, 0, 0, 0);
-            load_codes(u, clo[u], chi[u]);
-        }
+        for (int i = 0; i < 4; ++i) c0[i] = c1[i] = c2[i] = make_uint4(0, 0, 0, 0);
+        load_codes(grp, c0);
+        load_codes(grp + kGroups, c1);
         bool alive = true;
-        for (int kb0 = 0; alive && kb0 < n_kb; kb0 += kCodeAhead) {
+        for (int kb = grp; alive && kb < n_kb; kb += kGroups) {
+            load_codes(kb + 2 * kGroups, c2);
+            const int sa = kb % kAStages;
+            const int plane = (kb_base + kb) >= kb_per_plane ? 1 : 0;
+            const uint32_t lut_p = lut_lane + static_cast<uint32_t>(plane) * kLutBytes;
+            const uint32_t st_addr = a_taddr + kTmemAStageCols * static_cast<uint32_t>(sa);
 #pragma unroll
-            for (int u = 0; u < kCodeAhead; ++u) {
-                const int kb = kb0 + u;
-                if (!alive || kb >= n_kb) break;
-                const int sa = kb % kAStages;
-                const int plane = (kb_base + kb) >= kb_per_plane ? 1 : 0;
-                if (kb >= kAStages && !bar_wait(bar_empty_a + 8u * sa, ((kb / kAStages) - 1) & 1, abort_flag)) {
-                    raise_status(p.status, 6u);
-                    atomicExch(&s_abort, 1u);
-                    alive = false;
-                    break;
-                }
-                // weight tile: 32 codes -> 32 fp16 -> 16 tensor-memory columns of this thread's lane
-                const uint32_t w[8] = {clo[u].x, clo[u].y, clo[u].z, clo[u].w, chi[u].x, chi[u].y, chi[u].z, chi[u].w};
-                load_codes(kb + kCodeAhead, clo[u], chi[u]);
-                const uint32_t lut_p = lut_lane + static_cast<uint32_t>(plane) * kLutBytes;
+            for (int half = 0; half < 2; ++half) {
+                // 32 codes -> 32 fp16 -> 16 tensor-memory columns of this thread's lane
+                const uint32_t w[8] = {c0[2 * half].x, c0[2 * half].y, c0[2 * half].z, c0[2 * half].w,
+                                       c0[2 * half + 1].x, c0[2 * half + 1].y, c0[2 * half + 1].z, c0[2 * half + 1].w};
                 uint32_t packed[16];
 #pragma unroll
                 for (int h = 0; h < 16; ++h) {  // codes 2h, 2h + 1 -> column h
@@ -411,73 +422,85 @@ __global__ void __launch_bounds__(kGemmThreads, 1) tq8_gemm_kernel(const GemmArg
                     asm("ld.shared.b32 %0, [%1];" : "=r"(v1) : "r"(lut_p | (i1 & (255u << 7))));
                     packed[h] = __byte_perm(v0, v1, 0x5410);
                 }
-                // The previous K block's stores have had a whole block of lookups to land: publish
-                // them now, then queue this block's stores (published one iteration later).
-                if (kb > 0) {
-                    tmem_st_publish();
-                    bar_arrive(bar_full + 8u * ((kb - 1) % kFull));
-                }
-                tmem_st16(a_taddr + kTmemAStageCols * static_cast<uint32_t>(sa), packed);
-            }
-        }
-        if (alive && n_kb > 0) {
-            tmem_st_publish();
-            bar_arrive(bar_full + 8u * ((n_kb - 1) % kFull));
-        }
-    } else if (warp == kCopyWarp) {
-        // ---- activation tiles: one 32 KB bulk copy per K block, n_b blocks ahead of the MMAs ----
-        const size_t n_tok_tiles = (static_cast<size_t>(p.m) + kTileTok - 1) / kTileTok;
-        for (int kb = 0; kb < n_kb; ++kb) {
-            const int sb = kb % n_b;
-            if (kb >= n_b && !bar_wait(bar_empty_b + 8u * sb, ((kb / n_b) - 1) & 1, abort_flag)) {
-                if (lane == 0) {
+                // the stage must have been read by the MMAs of its previous K block (8 K blocks ago)
+                if (half == 0 && kb >= kAStages && !bar_wait(bar_empty_a + 8u * sa, ((kb / kAStages) - 1) & 1, abort_flag)) {
                     raise_status(p.status, 6u);
                     atomicExch(&s_abort, 1u);
+                    alive = false;
                 }
-                break;
+                if (!alive) break;
+                tmem_st16(st_addr + 16u * half, packed);
             }
-            if (lane == 0) {
+            if (!alive) break;
+            // every lane waits for its own stores, then one arrival per warp
+            tmem_st_publish();
+            __syncwarp();
+            if (lane == 0) bar_arrive(bar_full + 8u * sa);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                c0[i] = c1[i];
+                c1[i] = c2[i];
+            }
+        }
+    } else if (warp == kCopyWarp) {
+        // ---- activation tiles: one bulk copy per K block, n_b blocks ahead of the MMAs -------------
+        // One thread runs the whole loop; ring slot and phase are kept incrementally (no divisions on
+        // this serial path).
+        if (lane == 0) {
+            const size_t n_tok_tiles = (static_cast<size_t>(p.m) + kTileTok - 1) / kTileTok;
+            int sb = 0;
+            uint32_t par = 1u;   // parity of the "empty" phase to wait for: (kb / n_b - 1) & 1
+            for (int kb = 0; kb < n_kb; ++kb) {
+                if (kb >= n_b && !bar_wait(bar_empty_b + 8u * sb, par, abort_flag)) {
+                    raise_status(p.status, 6u);
+                    atomicExch(&s_abort, 1u);
+                    break;
+                }
                 const int plane = (kb_base + kb) >= kb_per_plane ? 1 : 0;
                 const size_t tile = (static_cast<size_t>(plane) * n_tok_tiles + blockIdx.y) * kb_per_plane + (kb_base + kb - plane * kb_per_plane);
                 const __half* src = p.xrot + tile * (kTileTok * kBlockK);
                 const uint32_t bar = bar_full_b + 8u * sb;
-                asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(kBBytes) : "memory");
+                asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(b_bytes) : "memory");
                 asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
                                  s_stage[sb]),
-                             "l"(src), "r"(kBBytes), "r"(bar)
+                             "l"(src), "r"(b_bytes), "r"(bar)
                              : "memory");
+                if (++sb == n_b) { sb = 0; par ^= 1u; }
             }
-            __syncwarp();
         }
+        __syncwarp();
     } else {
-        // ---- MMA issuer -----------------------------------------------------------------------
-        for (int kb = 0; kb < n_kb; ++kb) {
-            if (!bar_wait(bar_full + 8u * (kb % kFull), (kb / kFull) & 1, abort_flag) ||
-                !bar_wait(bar_full_b + 8u * (kb % n_b), (kb / n_b) & 1, abort_flag)) {
-                if (lane == 0) {
+        // ---- MMA issuer (one thread) ----------------------------------------------------------------
+        if (lane == 0) {
+            int sb = 0;
+            uint32_t par_b = 0u;   // (kb / n_b) & 1
+            bool ok = true;
+            for (int kb = 0; kb < n_kb; ++kb) {
+                const int sa = kb & (kAStages - 1);
+                if (!bar_wait(bar_full + 8u * sa, (kb / kAStages) & 1, abort_flag) ||
+                    !bar_wait(bar_full_b + 8u * sb, par_b, abort_flag)) {
                     raise_status(p.status, 7u);
                     atomicExch(&s_abort, 1u);
+                    ok = false;
+                    break;
                 }
-                break;
-            }
-            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            if (lane == 0) {
-                const uint32_t a_tmem = tmem_d + kTmemAColumn + kTmemAStageCols * static_cast<uint32_t>(kb % kAStages);
-                const uint32_t b_stage = s_stage[kb % n_b];
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint32_t a_tmem = tmem_d + kTmemAColumn + kTmemAStageCols * static_cast<uint32_t>(sa);
+                const uint64_t desc0 = smem_desc(s_stage[sb]);
 #pragma unroll
-                for (int j = 0; j < kBlockK / 16; ++j)
-                    umma_f16_ts(tmem_d, a_tmem + 8u * j, smem_desc(b_stage + 256u * j), (kb | j) != 0 ? 1u : 0u);
+                for (int j = 0; j < kBlockK / 16; ++j)   // 256 bytes further along K per step: +16 in the address field
+                    umma_f16_ts(tmem_d, a_tmem + 8u * j, desc0 + static_cast<uint64_t>(16 * j), idesc, (kb | j) != 0 ? 1u : 0u);
                 // both ring slots may be refilled once these MMAs are done
-                umma_commit(bar_empty_a + 8u * (kb % kAStages));
-                umma_commit(bar_empty_b + 8u * (kb % n_b));
+                umma_commit(bar_empty_a + 8u * sa);
+                umma_commit(bar_empty_b + 8u * sb);
+                if (++sb == n_b) { sb = 0; par_b ^= 1u; }
             }
-            __syncwarp();
+            if (ok) umma_commit(bar_accum);
         }
-        if (lane == 0) umma_commit(bar_accum);
         __syncwarp();
     }
 
-    // ---- epilogue (warps 0-7): TMEM lanes 32 * (warp & 3), columns 128 * (warp >> 2) .. +127 ----
+    // ---- epilogue (the producer warps): TMEM lanes 32 * (warp & 3), columns 64 * (warp >> 2) .. +63 ----
     if (warp < kProducerWarps) {
         const bool ok = !*abort_flag && bar_wait(bar_accum, 0, abort_flag);
         if (!ok) {
@@ -489,8 +512,9 @@ __global__ void __launch_bounds__(kGemmThreads, 1) tq8_gemm_kernel(const GemmArg
             const bool r_ok = r < p.out;
             const float scale = r_ok ? __ldg(p.norms + r) * p.inv_scale : 0.f;
 #pragma unroll 1
-            for (int cb = 0; cb < 4; ++cb) {
-                const int col0 = 128 * (warp >> 2) + 32 * cb;
+            for (int cb = 0; cb < 2; ++cb) {
+                const int col0 = (kTileTok / kGroups) * (warp >> 2) + 32 * cb;
+                if (col0 >= n_tile) break;   // warp-uniform: columns the MMA never wrote
                 uint32_t v[32];
                 tmem_ld32(tmem_d + (static_cast<uint32_t>(32 * (warp & 3)) << 16) + static_cast<uint32_t>(col0), v);
 #pragma unroll

@@ -862,6 +862,32 @@ void launch_tq8_gemv_scatter(const uint8_t* codes, const float* norms, const flo
     }
 }
 
+// The activation rotation alone (the pre-kernel of WHT blocks above 256 columns), for the other
+// decode kernels: xrot = [n_planes, batch, in] fp32.
+void launch_rotate_x(const __half* x, float* xrot, int in, int batch, uint32_t block, int n_planes, uint32_t seed_p,
+                     uint32_t seed_r, cudaStream_t stream) {
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    const float inv_sqrt = 1.0f / std::sqrt(static_cast<float>(block));
+    const int n_warps = n_planes * batch * (in / static_cast<int>(block));
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3((n_warps + 3) / 4);
+    cfg.blockDim = dim3(128);
+    cfg.stream = stream;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+#define TQ_ROT_CASE(EV)                                                                                            \
+    case 32 * EV:                                                                                                  \
+        TQ_CUDA(cudaLaunchKernelEx(&cfg, rotate_x_kernel<EV>, x, xrot, in, batch, n_planes, seed_p, seed_r, inv_sqrt)); \
+        break;
+    switch (block) {
+        TQ_ROT_CASE(1) TQ_ROT_CASE(2) TQ_ROT_CASE(4) TQ_ROT_CASE(8) TQ_ROT_CASE(16) TQ_ROT_CASE(32)
+        default: throw Error("unsupported WHT block size");
+    }
+#undef TQ_ROT_CASE
+}
+
 // ---- allocation-free variant ---------------------------------------------------------------
 // Same two kernels, but the scratch (rotated activation, split-K partial sums, arrival
 // counters) lives in a fixed array inside the library image instead of a buffer the handle
@@ -885,6 +911,9 @@ static void* static_scratch_address() {
     if (dev >= 0 && dev < 64) cached[dev] = ptr;
     return ptr;
 }
+
+// The same address for the other decode kernel's allocation-free variant.
+void* gemv_static_scratch_address() { return static_scratch_address(); }
 
 void launch_tq8_gemv_static(const uint8_t* codes, const float* norms, const float* table, const __half* x, __half* y,
                             int out, int in, int batch, uint32_t block, int n_planes, uint32_t seed_p, uint32_t seed_r,

@@ -53,6 +53,24 @@ void launch_tq8_gemv_scatter(const uint8_t* codes, const float* norms, const flo
 // 10 otherwise).
 void launch_peer_wait(const unsigned int* flags, int n, unsigned int value, unsigned int* status, cudaStream_t stream);
 
+// tq_gemv_staged.cu — the same operation with the codes staged through shared memory by bulk
+// copies (cp.async.bulk + mbarrier), work balanced over CTAs to 4 KB, two CTAs per SM.
+// scratch: gemv_staged_scratch_bytes(...) bytes, zero-initialised once.
+size_t gemv_staged_scratch_bytes(int out, int in, int n_planes, int sm_count);
+void launch_tq8_gemv_staged(const uint8_t* codes, const float* norms, const float* table, const __half* x, __half* y,
+                            int out, int in, int batch, uint32_t block, int n_planes, uint32_t seed_p, uint32_t seed_r,
+                            void* scratch, unsigned int* status, int sm_count, cudaStream_t stream);
+size_t gemv_staged_scratch_need(int out, int in, int batch, int n_planes, int sm_count);
+// Allocation-free variant over the library's built-in array (see launch_tq8_gemv_static).
+bool gemv_staged_fits_static(int out, int in, int batch, int n_planes, int sm_count);
+void launch_tq8_gemv_staged_static(const uint8_t* codes, const float* norms, const float* table, const __half* x, __half* y,
+                                   int out, int in, int batch, uint32_t block, int n_planes, uint32_t seed_p, uint32_t seed_r,
+                                   unsigned int* status, int sm_count, cudaStream_t stream);
+void* gemv_static_scratch_address();   // device address of that array on the current device (tq_gemv.cu)
+// The activation rotation of tq_gemv.cu alone: xrot = [n_planes, batch, in] fp32 (TF32-rounded).
+void launch_rotate_x(const __half* x, float* xrot, int in, int batch, uint32_t block, int n_planes, uint32_t seed_p,
+                     uint32_t seed_r, cudaStream_t stream);
+
 // Allocation-free variant: scratch is a fixed array in the library image
 // (gemv_static_scratch_capacity() bytes); throws if the layer needs more.
 size_t gemv_static_scratch_capacity();
