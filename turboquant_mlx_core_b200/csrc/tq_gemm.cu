@@ -15,14 +15,18 @@
 // One CTA computes a 128 (weight rows) x 256 (activation rows, or fewer) tile of y^T:
 //   D[128 x 256] (TMEM, fp32) += A[128 x 64] (weights, fp16, TMEM) . B[256 x 64]^T (xrot, fp16, smem)
 // per 64-column K block, as four tcgen05.mma (M 128, N 256, K 16) issued by one thread.
-//   warps 0-15 producers in four groups; group j takes the K blocks j, j + 4, ...: codes HBM ->
-//              registers (two of the group's K blocks ahead) -> lookup (lane-private fp16 table in
-//              shared memory) -> weight tile in TENSOR memory (tcgen05.st; lane = row, 32 columns of
-//              fp16 pairs per K block), ring of 8 stages (two per group)
-//   warp 17    activation tiles: the rotation kernel stores xrot in operand-tile order, so a tile
-//              is one contiguous bulk copy (cp.async.bulk, mbarrier complete_tx) of 128 bytes per
-//              activation row of the tile; the ring has as many stages as fit (4 for 256 rows)
-//   warp 16    waits for both tiles of a K block, issues the MMAs, commits to the rings' empty barriers
+//   A pipeline stage is 128 K columns (two 64-column K blocks), the ring has up to four stages.
+//   warps 0-15 producers in two groups of eight; group g takes the stages g, g + 2, ...: codes HBM ->
+//              registers (two of the group's stages ahead) -> lookup (lane-private fp16 table in
+//              shared memory) -> weight tile in TENSOR memory (tcgen05.st; lane = row, 64 columns of
+//              fp16 pairs per stage)
+//   warp 17    activation tiles: the rotation kernel stores xrot in operand-tile order, so a K block
+//              of a tile is one contiguous bulk copy (cp.async.bulk, mbarrier complete_tx) of 128
+//              bytes per activation row of the tile
+//   warp 16    one thread: waits for a stage (ONE barrier collects the producers' arrivals and the
+//              copies' bytes), issues its eight MMAs, commits to the stage's "empty" barrier.  The
+//              serial chain of this thread (wait, fence, issue, commit) is what bounds the kernel when
+//              the MMAs are short, hence few and long stages.
 //   warps 0-15 epilogue: tcgen05.ld the accumulator, scale by norm * inv_scale, store fp16
 // The activation tile is as tall as the rows it really has (in steps of 16): a decode batch of 9..64
 // rows costs a short MMA and a short copy, so the codes are streamed once whatever the batch.
@@ -51,23 +55,24 @@ namespace {
 constexpr int kTileRows = 128;  // weight rows per CTA (MMA M)
 constexpr int kTileTok = 256;   // activation rows per CTA (MMA N)
 constexpr int kBlockK = 64;     // K columns per stage
-constexpr int kAStages = 8;    // weight-tile ring in tensor memory: two stages per producer group
-constexpr int kBStagesMax = 16; // activation-tile ring in shared memory: as many stages as fit, up to this
-constexpr int kFull = kAStages;  // "K block ready" barriers, one per weight-tile stage
-constexpr int kGroups = 4;     // producer groups: group j dequantises the K blocks j, j + 4, j + 8, ...
-constexpr int kProducerWarps = 4 * kGroups;
+constexpr int kSubPerStage = 2; // K blocks per pipeline stage: a stage is 128 K columns
+constexpr int kStagesMax = 4;   // ring of stages: weight tiles in tensor memory (4 x 64 columns), activation tiles in shared memory (as many as fit)
+constexpr int kGroups = 2;      // producer groups of eight warps: group g dequantises the stages g, g + 2, ...
+constexpr int kProducerWarps = 8 * kGroups;
 constexpr int kProducerThreads = kProducerWarps * 32;
 constexpr int kMmaWarp = kProducerWarps;       // issues the MMAs, owns the tensor-memory allocation
 constexpr int kCopyWarp = kProducerWarps + 1;  // issues the activation-tile bulk copies
 constexpr int kGemmThreads = kProducerThreads + 64;
-constexpr uint32_t kBBytes = kTileTok * kBlockK * 2;   // 32 KB
 constexpr uint32_t kLutBytes = 256 * 32 * 4;           // one plane: 256 entries x 32 lane copies x (fp16, fp16)
-constexpr uint32_t kTmemCols = 512;   // accumulator: columns 0..255; weight tiles: 8 x 32 columns from 256 on
+constexpr uint32_t kTmemCols = 512;   // accumulator: columns 0..255; weight tiles: 4 stages x 64 columns from 256 on
 constexpr uint32_t kTmemAColumn = 256;
-constexpr uint32_t kTmemAStageCols = kBlockK / 2;  // two fp16 per 32-bit column
+constexpr uint32_t kTmemASubCols = kBlockK / 2;                    // one K block: two fp16 per 32-bit column
+constexpr uint32_t kTmemAStageCols = kSubPerStage * kTmemASubCols;
+constexpr uint32_t kLutWin = 0x800u;  // window address of the lookup tables (an immediate of the lookup's load)
 // rings + tables (4 activation stages with one table plane, 3 with two) + worst-case padding in
 // front of the 32 KB-aligned tables
-constexpr size_t kGemmSmemBytes = 4 * kBBytes + 2 * kLutBytes + 32768 + 1024;
+// Everything an SM can give one CTA: tables at kLutWin, then three 64 KB stages for a 256-row tile.
+constexpr size_t kGemmSmemBytes = 232448 - 512;
 constexpr unsigned long long kGemmWaitLimitNs = 200ull * 1000 * 1000;
 
 // instruction descriptor: D fp32, A and B fp16, both K-major, M = 128, N = n (a multiple of 16 up to 256)
@@ -110,6 +115,14 @@ __device__ __forceinline__ uint64_t smem_desc(uint32_t addr) {
     return static_cast<uint64_t>((addr >> 4) & 0x3FFFu) | (static_cast<uint64_t>(128u >> 4) << 16) |
            (static_cast<uint64_t>(1024u >> 4) << 32) | (1ull << 46);
 }
+
+// Table lookup: `offset` = scaled code | lane offset | plane offset; the table's window address is the immediate.
+__device__ __forceinline__ uint32_t lut_load(uint32_t offset) {
+    uint32_t v;
+    asm("ld.shared.b32 %0, [%1 + 2048];" : "=r"(v) : "r"(offset));
+    return v;
+}
+static_assert(kLutWin == 2048u, "lut_load's immediate is the tables' window address");
 
 // D[tmem_d] (+)= A[tmem_a] . B[desc_b]^T : A from tensor memory (128 lanes x 8 columns of fp16 pairs),
 // B from shared memory.
@@ -277,9 +290,8 @@ struct GemmArgs {
 
 __global__ void __launch_bounds__(kGemmThreads, 1) tq8_gemm_kernel(const GemmArgs p) {
     extern __shared__ __align__(128) uint8_t gemm_smem[];
-    __shared__ __align__(8) unsigned long long s_full[kFull], s_full_b[kBStagesMax], s_empty_a[kAStages], s_empty_b[kBStagesMax], s_accum;
+    __shared__ __align__(8) unsigned long long s_full[kStagesMax], s_empty[kStagesMax], s_accum;
     __shared__ uint32_t s_tmem_base;
-    __shared__ uint32_t s_stage[kBStagesMax];  // activation-tile buffers
     __shared__ unsigned int s_abort;
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -288,52 +300,32 @@ __global__ void __launch_bounds__(kGemmThreads, 1) tq8_gemm_kernel(const GemmArg
     // Activation rows this tile really has, rounded up to the MMA's granularity of 16: a short tile
     // (a decode batch of 9..64 rows, or the tail of a prefill) costs a short MMA and a short copy.
     const int n_tile = min(kTileTok, ((p.m - tok0) + 15) & ~15);
-    const uint32_t b_bytes = static_cast<uint32_t>(n_tile) * (kBlockK * 2);   // the tile's first n_tile rows are contiguous
+    const uint32_t b_bytes = static_cast<uint32_t>(n_tile) * (kBlockK * 2);   // one 64-column piece: the tile's first n_tile rows are contiguous
     const uint32_t idesc = instr_desc(static_cast<uint32_t>(n_tile));
 
     // ---- shared-memory map -------------------------------------------------------------------
-    // The lookup tables sit at a 32 KB-aligned window address (so that table base, lane offset
-    // and scaled code occupy disjoint address bits); the 16 KB / 32 KB stage buffers are packed
-    // around them.
+    // [kLutWin, + 32 KB per plane)  lookup tables, at a fixed window address (it is an immediate of
+    //                               the lookup's load instruction)
+    // [after the tables, end)       activation stages of 2 * b_bytes (two 64-column pieces), as many
+    //                               as fit, at most kStagesMax
     const uint32_t raw = smem_addr(gemm_smem);
-    const uint32_t base = (raw + 127u) & ~127u;
-    const uint32_t lut_addr = (base + 32767u) & ~32767u;
-    const uint32_t lut_end = lut_addr + kLutBytes * static_cast<uint32_t>(p.n_planes);
     uint32_t dyn_bytes;
     asm("mov.u32 %0, %%dynamic_smem_size;" : "=r"(dyn_bytes));
-    // A stage holds the tile's real rows only, so a short tile gets a deep ring.
-    int n_b = 0;
-    {
-        // Same arithmetic in every thread; thread 0 publishes the stage addresses.
-        uint32_t lo = base, hi = lut_end;  // bump pointers below and above the tables
-        const uint32_t end = raw + dyn_bytes;
-        uint32_t addr[kBStagesMax];
-#pragma unroll
-        for (int s = 0; s < kBStagesMax; ++s) {
-            addr[s] = 0;
-            if (n_b != s) continue;   // an earlier stage did not fit: stop
-            if (lo + b_bytes <= lut_addr) { addr[s] = lo; lo += b_bytes; n_b = s + 1; }
-            else if (hi + b_bytes <= end) { addr[s] = hi; hi += b_bytes; n_b = s + 1; }
-        }
-        if (n_b < 2 || lut_end > end) {  // layout does not fit: refuse to run (nothing allocated yet)
-            if (tid == 0) raise_status(p.status, 9u);
-            return;
-        }
-        if (tid == 0) {
-#pragma unroll
-            for (int s = 0; s < kBStagesMax; ++s) s_stage[s] = addr[s];
-        }
+    const uint32_t stage0 = kLutWin + kLutBytes * static_cast<uint32_t>(p.n_planes);
+    const uint32_t stage_bytes = kSubPerStage * b_bytes;
+    const uint32_t smem_end = raw + dyn_bytes;
+    int n_st = smem_end > stage0 ? static_cast<int>((smem_end - stage0) / stage_bytes) : 0;
+    if (n_st > kStagesMax) n_st = kStagesMax;
+    if (raw > kLutWin || n_st < 2) {  // layout does not fit: refuse to run (nothing allocated yet)
+        if (tid == 0) raise_status(p.status, 9u);
+        return;
     }
-    const uint32_t bar_full = smem_addr(&s_full[0]), bar_full_b = smem_addr(&s_full_b[0]),
-                   bar_empty_a = smem_addr(&s_empty_a[0]), bar_empty_b = smem_addr(&s_empty_b[0]),
-                   bar_accum = smem_addr(&s_accum);
+    const uint32_t bar_full = smem_addr(&s_full[0]), bar_empty = smem_addr(&s_empty[0]), bar_accum = smem_addr(&s_accum);
 
     if (tid == 0) {
-        for (int s = 0; s < kFull; ++s) bar_init(bar_full + 8u * s, kProducerWarps / kGroups);   // one arrival per warp of the group
-        for (int s = 0; s < kAStages; ++s) bar_init(bar_empty_a + 8u * s, 1);
-        for (int s = 0; s < kBStagesMax; ++s) {
-            bar_init(bar_empty_b + 8u * s, 1);
-            bar_init(bar_full_b + 8u * s, 1);
+        for (int s = 0; s < kStagesMax; ++s) {
+            bar_init(bar_full + 8u * s, kProducerWarps / kGroups + 1);   // one arrival per producer warp of the group + the copy thread
+            bar_init(bar_empty + 8u * s, 1);
         }
         bar_init(bar_accum, 1);
         s_abort = 0u;
@@ -345,12 +337,12 @@ __global__ void __launch_bounds__(kGemmThreads, 1) tq8_gemm_kernel(const GemmArg
                      : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
-    // lookup tables: entry e, lane copy l at lut + plane * 32 KB + e * 128 + l * 4, value (t, t) as fp16
+    // lookup tables: entry e, lane copy l at kLutWin + plane * 32 KB + e * 128 + l * 4, value (t, t) as fp16
     for (int i = tid; i < 256 * 8 * p.n_planes; i += kGemmThreads) {
         const int e = i >> 3, c4 = (i & 7) * 4;  // e counts across planes
         const __half h = __float2half_rn(__ldg(p.table + e));
         const uint32_t v = static_cast<uint32_t>(__half_as_ushort(h)) * 0x00010001u;
-        asm volatile("st.shared.v4.b32 [%0], {%1, %1, %1, %1};" ::"r"(lut_addr + static_cast<uint32_t>(e) * 128u + c4 * 4u), "r"(v)
+        asm volatile("st.shared.v4.b32 [%0], {%1, %1, %1, %1};" ::"r"(kLutWin + static_cast<uint32_t>(e) * 128u + c4 * 4u), "r"(v)
                      : "memory");
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -359,32 +351,33 @@ __global__ void __launch_bounds__(kGemmThreads, 1) tq8_gemm_kernel(const GemmArg
     const uint32_t tmem_d = s_tmem_base;
     volatile unsigned int* abort_flag = &s_abort;
 
-    // K blocks of this CTA: a contiguous range of the (plane-major) list of all K blocks.  Ring
-    // slots and barrier phases count from the start of the range; kb_base maps back to columns.
+    // K blocks (64 columns) of this CTA: a contiguous range of the (plane-major) list of all K blocks.
+    // A stage is two consecutive K blocks of the range (the last one may hold a single block).
     const int kb_per_plane = p.in / kBlockK;
     const int n_kb_total = kb_per_plane * p.n_planes;
     const int kb_base = static_cast<int>(static_cast<long>(n_kb_total) * blockIdx.z / p.k_splits);
     const int n_kb = static_cast<int>(static_cast<long>(n_kb_total) * (blockIdx.z + 1) / p.k_splits) - kb_base;
+    const int n_it = (n_kb + kSubPerStage - 1) / kSubPerStage;
 
     if (warp < kProducerWarps) {
         // ---- producers ------------------------------------------------------------------------
-        // Weight tile in tensor memory: lane = row of the tile, 32 columns per K block (two fp16 per
-        // column).  A warp may touch lanes 32 * (warp % 4) .. + 31.  The 16 producer warps form four
-        // groups (warp / 4); group j dequantises the K blocks j, j + 4, ... whole (a thread: the 64
-        // codes of its row) into the stages j and j + 4 alternately, so four K blocks are in the
-        // making at any time and a group's chain (codes -> lookups -> tensor-memory stores -> publish)
-        // has four K-block times to complete.
+        // Weight tile in tensor memory: lane = row of the tile, 64 columns per stage (two fp16 per
+        // column, 128 K columns).  A warp may touch lanes 32 * (warp % 4) .. + 31.  The 16 producer
+        // warps form two groups of eight (warp / 8); inside a group warp w takes the rows of lane
+        // quarter w % 4 and the K block (w / 4) % 2 of the stage; group g dequantises the stages g,
+        // g + 2, ...  A thread turns the 64 codes of its row and K block into 32 columns.
         const int ar = 32 * (warp & 3) + lane;       // row inside the tile
-        const int grp = warp >> 2;
+        const int sub = (warp >> 2) & 1;             // which K block of the stage
+        const int grp = warp >> 3;
         const int grow = min(row0 + ar, p.out - 1);  // rows past the matrix repeat the last row (never stored)
         // a row's 64 columns of K block kb are 64 contiguous bytes of code tile (row / 16, kb)
         const uint8_t* code_ptr = p.codes + code_offset(grow, 0, code_tiles_per_row(p.in));
-        const uint32_t a_taddr = tmem_d + (static_cast<uint32_t>(32 * (warp & 3)) << 16) + kTmemAColumn;
-        const uint32_t lut_lane = lut_addr + static_cast<uint32_t>(lane) * 4u;
+        const uint32_t a_taddr = tmem_d + (static_cast<uint32_t>(32 * (warp & 3)) << 16) + kTmemAColumn + kTmemASubCols * static_cast<uint32_t>(sub);
 
-        // Codes are fetched two of the group's K blocks ahead into registers.  The second plane
-        // reads the same bytes again.
-        auto load_codes = [&](int kb, uint4 (&c)[4]) {
+        // Codes are fetched two of the group's stages ahead into registers.  The second plane reads
+        // the same bytes again.
+        auto load_codes = [&](int it, uint4 (&c)[4]) {
+            const int kb = kSubPerStage * it + sub;
             if (kb < n_kb) {
                 const int plane = (kb_base + kb) >= kb_per_plane ? 1 : 0;
                 const uint4* src = reinterpret_cast<const uint4*>(
@@ -398,13 +391,16 @@ __global__ void __launch_bounds__(kGemmThreads, 1) tq8_gemm_kernel(const GemmArg
         for (int i = 0; i < 4; ++i) c0[i] = c1[i] = c2[i] = make_uint4(0, 0, 0, 0);
         load_codes(grp, c0);
         load_codes(grp + kGroups, c1);
+        int slot = grp % n_st, use = grp / n_st;     // ring slot of stage `it` and how often it has been used before
         bool alive = true;
-        for (int kb = grp; alive && kb < n_kb; kb += kGroups) {
-            load_codes(kb + 2 * kGroups, c2);
-            const int sa = kb % kAStages;
+        for (int it = grp; alive && it < n_it; it += kGroups) {
+            load_codes(it + 2 * kGroups, c2);
+            const int kb = kSubPerStage * it + sub;
+            const bool have = kb < n_kb;             // the last stage may lack its second K block
             const int plane = (kb_base + kb) >= kb_per_plane ? 1 : 0;
-            const uint32_t lut_p = lut_lane + static_cast<uint32_t>(plane) * kLutBytes;
-            const uint32_t st_addr = a_taddr + kTmemAStageCols * static_cast<uint32_t>(sa);
+            // lane offset, plus 32 KB for the second plane's table: bits outside the scaled code (7..14)
+            const uint32_t lane_c = static_cast<uint32_t>(lane) * 4u + static_cast<uint32_t>(plane) * kLutBytes;
+            const uint32_t st_addr = a_taddr + kTmemAStageCols * static_cast<uint32_t>(slot);
 #pragma unroll
             for (int half = 0; half < 2; ++half) {
                 // 32 codes -> 32 fp16 -> 16 tensor-memory columns of this thread's lane
@@ -417,83 +413,90 @@ __global__ void __launch_bounds__(kGemmThreads, 1) tq8_gemm_kernel(const GemmArg
                     const int b0 = (h & 1) * 2;  // bytes b0, b0 + 1 of the word
                     const uint32_t i0 = b0 == 0 ? (word << 7) : (word >> 9);
                     const uint32_t i1 = b0 == 0 ? (word >> 1) : (word >> 17);
-                    uint32_t v0, v1;
-                    asm("ld.shared.b32 %0, [%1];" : "=r"(v0) : "r"(lut_p | (i0 & (255u << 7))));
-                    asm("ld.shared.b32 %0, [%1];" : "=r"(v1) : "r"(lut_p | (i1 & (255u << 7))));
-                    packed[h] = __byte_perm(v0, v1, 0x5410);
+                    packed[h] = __byte_perm(lut_load((i0 & (255u << 7)) | lane_c), lut_load((i1 & (255u << 7)) | lane_c), 0x5410);
                 }
-                // the stage must have been read by the MMAs of its previous K block (8 K blocks ago)
-                if (half == 0 && kb >= kAStages && !bar_wait(bar_empty_a + 8u * sa, ((kb / kAStages) - 1) & 1, abort_flag)) {
+                // the slot must have been read by the MMAs of its previous stage
+                if (half == 0 && use > 0 && !bar_wait(bar_empty + 8u * slot, static_cast<uint32_t>(use - 1) & 1u, abort_flag)) {
                     raise_status(p.status, 6u);
                     atomicExch(&s_abort, 1u);
                     alive = false;
                 }
                 if (!alive) break;
-                tmem_st16(st_addr + 16u * half, packed);
+                if (have) tmem_st16(st_addr + 16u * half, packed);
             }
             if (!alive) break;
             // every lane waits for its own stores, then one arrival per warp
             tmem_st_publish();
             __syncwarp();
-            if (lane == 0) bar_arrive(bar_full + 8u * sa);
+            if (lane == 0) bar_arrive(bar_full + 8u * slot);
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
                 c0[i] = c1[i];
                 c1[i] = c2[i];
             }
+            slot += kGroups;
+            if (slot >= n_st) { slot -= n_st; ++use; }
         }
     } else if (warp == kCopyWarp) {
-        // ---- activation tiles: one bulk copy per K block, n_b blocks ahead of the MMAs -------------
+        // ---- activation tiles: one bulk copy per K block of the stage, as far ahead as the ring allows ----
         // One thread runs the whole loop; ring slot and phase are kept incrementally (no divisions on
         // this serial path).
         if (lane == 0) {
             const size_t n_tok_tiles = (static_cast<size_t>(p.m) + kTileTok - 1) / kTileTok;
-            int sb = 0;
-            uint32_t par = 1u;   // parity of the "empty" phase to wait for: (kb / n_b - 1) & 1
-            for (int kb = 0; kb < n_kb; ++kb) {
-                if (kb >= n_b && !bar_wait(bar_empty_b + 8u * sb, par, abort_flag)) {
+            int slot = 0;
+            uint32_t par = 1u;   // parity of the "empty" phase to wait for
+            for (int it = 0; it < n_it; ++it) {
+                if (it >= n_st && !bar_wait(bar_empty + 8u * slot, par, abort_flag)) {
                     raise_status(p.status, 6u);
                     atomicExch(&s_abort, 1u);
                     break;
                 }
-                const int plane = (kb_base + kb) >= kb_per_plane ? 1 : 0;
-                const size_t tile = (static_cast<size_t>(plane) * n_tok_tiles + blockIdx.y) * kb_per_plane + (kb_base + kb - plane * kb_per_plane);
-                const __half* src = p.xrot + tile * (kTileTok * kBlockK);
-                const uint32_t bar = bar_full_b + 8u * sb;
-                asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(b_bytes) : "memory");
-                asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
-                                 s_stage[sb]),
-                             "l"(src), "r"(b_bytes), "r"(bar)
-                             : "memory");
-                if (++sb == n_b) { sb = 0; par ^= 1u; }
+                const int nsub = min(kSubPerStage, n_kb - kSubPerStage * it);
+                const uint32_t bar = bar_full + 8u * slot;
+                asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(b_bytes * nsub) : "memory");
+                for (int sb = 0; sb < nsub; ++sb) {
+                    const int kb = kSubPerStage * it + sb;
+                    const int plane = (kb_base + kb) >= kb_per_plane ? 1 : 0;
+                    const size_t tile = (static_cast<size_t>(plane) * n_tok_tiles + blockIdx.y) * kb_per_plane + (kb_base + kb - plane * kb_per_plane);
+                    const __half* src = p.xrot + tile * (kTileTok * kBlockK);
+                    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                                     stage0 + static_cast<uint32_t>(slot) * stage_bytes + static_cast<uint32_t>(sb) * b_bytes),
+                                 "l"(src), "r"(b_bytes), "r"(bar)
+                                 : "memory");
+                }
+                if (++slot == n_st) { slot = 0; par ^= 1u; }
             }
         }
         __syncwarp();
     } else {
-        // ---- MMA issuer (one thread) ----------------------------------------------------------------
+        // ---- MMA issuer (one thread): one wait and one commit per stage ---------------------------------
         if (lane == 0) {
-            int sb = 0;
-            uint32_t par_b = 0u;   // (kb / n_b) & 1
+            int slot = 0;
+            uint32_t par = 0u;
             bool ok = true;
-            for (int kb = 0; kb < n_kb; ++kb) {
-                const int sa = kb & (kAStages - 1);
-                if (!bar_wait(bar_full + 8u * sa, (kb / kAStages) & 1, abort_flag) ||
-                    !bar_wait(bar_full_b + 8u * sb, par_b, abort_flag)) {
+            for (int it = 0; it < n_it; ++it) {
+                if (!bar_wait(bar_full + 8u * slot, par, abort_flag)) {
                     raise_status(p.status, 7u);
                     atomicExch(&s_abort, 1u);
                     ok = false;
                     break;
                 }
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                const uint32_t a_tmem = tmem_d + kTmemAColumn + kTmemAStageCols * static_cast<uint32_t>(sa);
-                const uint64_t desc0 = smem_desc(s_stage[sb]);
+                const int nsub = min(kSubPerStage, n_kb - kSubPerStage * it);
+                const uint32_t a_tmem = tmem_d + kTmemAColumn + kTmemAStageCols * static_cast<uint32_t>(slot);
+                const uint32_t b_stage = stage0 + static_cast<uint32_t>(slot) * stage_bytes;
 #pragma unroll
-                for (int j = 0; j < kBlockK / 16; ++j)   // 256 bytes further along K per step: +16 in the address field
-                    umma_f16_ts(tmem_d, a_tmem + 8u * j, desc0 + static_cast<uint64_t>(16 * j), idesc, (kb | j) != 0 ? 1u : 0u);
-                // both ring slots may be refilled once these MMAs are done
-                umma_commit(bar_empty_a + 8u * sa);
-                umma_commit(bar_empty_b + 8u * sb);
-                if (++sb == n_b) { sb = 0; par_b ^= 1u; }
+                for (int sb = 0; sb < kSubPerStage; ++sb) {
+                    if (sb < nsub) {
+                        const uint64_t desc0 = smem_desc(b_stage + static_cast<uint32_t>(sb) * b_bytes);
+#pragma unroll
+                        for (int j = 0; j < kBlockK / 16; ++j)   // 256 bytes further along K per step: +16 in the address field
+                            umma_f16_ts(tmem_d, a_tmem + kTmemASubCols * sb + 8u * j, desc0 + static_cast<uint64_t>(16 * j), idesc,
+                                        (it | sb | j) != 0 ? 1u : 0u);
+                    }
+                }
+                umma_commit(bar_empty + 8u * slot);   // the slot (weights and activation) may be refilled once these MMAs are done
+                if (++slot == n_st) { slot = 0; par ^= 1u; }
             }
             if (ok) umma_commit(bar_accum);
         }
@@ -513,7 +516,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) tq8_gemm_kernel(const GemmArg
             const float scale = r_ok ? __ldg(p.norms + r) * p.inv_scale : 0.f;
 #pragma unroll 1
             for (int cb = 0; cb < 2; ++cb) {
-                const int col0 = (kTileTok / kGroups) * (warp >> 2) + 32 * cb;
+                const int col0 = 64 * (warp >> 2) + 32 * cb;
                 if (col0 >= n_tile) break;   // warp-uniform: columns the MMA never wrote
                 uint32_t v[32];
                 tmem_ld32(tmem_d + (static_cast<uint32_t>(32 * (warp & 3)) << 16) + static_cast<uint32_t>(col0), v);
