@@ -202,6 +202,43 @@ int tq_shared_export(void* ptr, void* handle_out, size_t handle_bytes);
 void* tq_shared_open(const void* handle, size_t handle_bytes);
 int tq_shared_close(void* peer_ptr);
 
+/* ---- rank-to-rank exchange for the sharded paths ---------------------------------------
+ * One process per GPU; every rank allocates a buffer with tq_shared_alloc, the handles travel by
+ * the caller's own channel, and each rank maps the others' buffers with tq_shared_open.  The
+ * reference plans a layer split and ships no data plane between devices
+ * (src/distributed.cpp:201-253, benchmarks/bench_distributed.cpp:9-12): no counterpart there.
+ *
+ * tq_exchange_broadcast copies a block of this rank's device memory (rows x row_bytes, row_bytes
+ * a multiple of 16) to dst[0..n_dst): the same block's place in the other ranks' buffers (and in
+ * the local one, if the block was computed elsewhere) - plain 16-byte stores over NVLink, no
+ * multicast, no collective library - and then stores this exchange's broadcast count into flag
+ * `rank` of every flags[0..n_flags) (arrays of 32 words, one in every rank's memory, the local
+ * one included), release at system scope.  tq_exchange_wait enqueues a
+ * one-warp kernel that waits until flags [0, n_flags) of the LOCAL array have reached this
+ * exchange's wait count; it gives up after one second (tq_exchange_status then fails).  Both counts
+ * live in device memory and advance by one per call, so every rank must issue the same sequence of
+ * broadcasts and waits - and a captured CUDA graph of that sequence can be replayed.  A block must
+ * not be broadcast into again before every rank has read the previous one: alternate two buffers.
+ *   all-gather of row shards  = broadcast(own shard)               ; wait
+ *   all-reduce of partial sums = broadcast(partial into slot rank) ; wait ; tq_exchange_sum_f16
+ *   merge of attention parts  = broadcast(out, lse into slot part) ; wait ; tq_exchange_merge_attention */
+typedef struct tq_exchange_s* tq_exchange_t;
+tq_exchange_t tq_exchange_create(int rank, int world);
+int tq_exchange_broadcast(tq_exchange_t ex, const void* src, void* const* dst, int n_dst, int rows, long row_bytes,
+                          long src_stride_bytes, long dst_stride_bytes, void* const* flags, int n_flags, void* stream);
+int tq_exchange_wait(tq_exchange_t ex, const void* local_flags, int n_flags, void* stream);
+/** out[i] = fp16( sum over s = 0..n_slots-1, in that order, of slots[s * slot_stride + i] ), fp32
+ *  accumulate: every rank adds the same values in the same order and gets the same bits. */
+int tq_exchange_sum_f16(const void* slots_fp16, int n_slots, long slot_stride, long count, void* out_fp16, void* stream);
+/** Attention over the union of disjoint token ranges from each range's output and log-sum-exp
+ *  (tq_kv_attention_lse): outs [parts][rows][head_dim] fp16, lses [parts][rows] fp32, parts
+ *  part_stride_out / part_stride_lse elements apart. */
+int tq_exchange_merge_attention(const void* outs_fp16, const void* lses_fp32, int parts, long rows, int head_dim,
+                                long part_stride_out, long part_stride_lse, void* out_fp16, void* stream);
+/** Waits for the device; non-zero if a wait of this exchange gave up. */
+int tq_exchange_status(tq_exchange_t ex);
+void tq_exchange_free(tq_exchange_t ex);
+
 /** Waits for the device, then returns 0 if every kernel launched through this handle ran to
  *  completion, non-zero (see tq_last_error) if one refused to run or gave up on a bounded wait.
  *  Calls with host output check this themselves; callers that pass device pointers and

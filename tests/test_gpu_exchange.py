@@ -1,0 +1,89 @@
+"""GPU tests of the rank-to-rank exchange kernels on ONE device: two "ranks" are two exchange handles
+and two buffers in this process, and every broadcast is enqueued before the wait that consumes it (a
+kernel never waits here for one that has not been launched).  The multi-process use over CUDA IPC is
+exercised by bench.py's sharded legs on 2 or more GPUs; the partition rules and the merge formula are
+covered on CPU in tests/test_sharding.py."""
+import ctypes as C
+
+import numpy as np
+import pytest
+
+from tests.conftest import rel_l2
+
+pytestmark = pytest.mark.gpu
+
+
+def _ptrs(items):
+    return (C.c_void_p * len(items))(*items)
+
+
+def test_broadcast_wait_sum_and_merge(tq):
+    torch = pytest.importorskip("torch")
+    from turboquant_mlx_core_b200.sharding import merge_attention_parts
+    L = tq.load()
+    world, batch, hidden = 2, 3, 1024
+    slot = batch * hidden                                   # fp16 elements per rank's slot
+    nbytes = world * slot * 2
+    bufs = [torch.zeros(nbytes + 256, dtype=torch.uint8, device="cuda") for _ in range(world)]
+    flags = [b.data_ptr() + nbytes for b in bufs]           # 32 words behind the payload
+    ex = [L.tq_exchange_create(r, world) for r in range(world)]
+    assert all(ex)
+    g = torch.Generator(device="cuda").manual_seed(0)
+    for step in range(3):                                   # epochs advance on both sides
+        parts = [torch.randn((batch, hidden), generator=g, device="cuda").half() for _ in range(world)]
+        for r in range(world):                              # rank r computes its partial into slot r of its own buffer
+            bufs[r][r * slot * 2:(r + 1) * slot * 2].view(torch.float16).copy_(parts[r].reshape(-1))
+        for r in range(world):                              # ... and sends it to slot r of the other rank
+            other = 1 - r
+            dst = _ptrs([bufs[other].data_ptr() + r * slot * 2])
+            rc = L.tq_exchange_broadcast(ex[r], C.c_void_p(bufs[r].data_ptr() + r * slot * 2), dst, 1, batch, hidden * 2,
+                                         hidden * 2, hidden * 2, _ptrs(flags), world, None)
+            assert rc == 0, L.tq_last_error().decode()
+        outs = []
+        for r in range(world):
+            assert L.tq_exchange_wait(ex[r], C.c_void_p(flags[r]), world, None) == 0
+            out = torch.empty((batch, hidden), dtype=torch.float16, device="cuda")
+            assert L.tq_exchange_sum_f16(C.c_void_p(bufs[r].data_ptr()), world, slot, slot, C.c_void_p(out.data_ptr()), None) == 0
+            outs.append(out)
+        torch.cuda.synchronize()
+        want = (parts[0].float() + parts[1].float()).half()           # rank order, fp32 accumulate
+        assert torch.equal(outs[0], want) and torch.equal(outs[1], want)
+        for r in range(world):
+            assert L.tq_exchange_status(ex[r]) == 0
+            assert bufs[r][nbytes:nbytes + 8].view(torch.int32).tolist() == [step + 1, step + 1]
+
+    # merge of softmax parts against the numpy rule
+    rows, dim, nparts = 37, 128, 3
+    o = torch.randn((nparts, rows, dim), generator=g, device="cuda").half()
+    lse = torch.randn((nparts, rows), generator=g, device="cuda") * 3
+    lse[1, 5] = float("-inf")                               # a part that saw no token
+    merged = torch.empty((rows, dim), dtype=torch.float16, device="cuda")
+    assert L.tq_exchange_merge_attention(C.c_void_p(o.data_ptr()), C.c_void_p(lse.data_ptr()), nparts, rows, dim, rows * dim, rows,
+                                         C.c_void_p(merged.data_ptr()), None) == 0
+    torch.cuda.synchronize()
+    want = merge_attention_parts(o.float().cpu().numpy(), lse.cpu().numpy())
+    assert rel_l2(merged.float().cpu().numpy(), want) < 1e-3
+    for h in ex:
+        L.tq_exchange_free(h)
+
+
+def test_wait_for_a_flag_nobody_raises_gives_up(tq):
+    """A rank that never broadcasts: the wait runs out after its limit (about a second) and the
+    status says so; the device stays usable."""
+    torch = pytest.importorskip("torch")
+    L = tq.load()
+    flags = torch.zeros(32, dtype=torch.int32, device="cuda")
+    ex = L.tq_exchange_create(0, 2)
+    assert L.tq_exchange_wait(ex, C.c_void_p(flags.data_ptr()), 2, None) == 0
+    assert L.tq_exchange_status(ex) != 0
+    assert b"did not arrive" in L.tq_last_error()
+    L.tq_exchange_free(ex)
+    assert int(torch.ones(4, device="cuda").sum()) == 4
+    # argument checks
+    ex = L.tq_exchange_create(0, 1)
+    buf = torch.zeros(1024, dtype=torch.uint8, device="cuda")
+    bad = L.tq_exchange_broadcast(ex, C.c_void_p(buf.data_ptr()), _ptrs([buf.data_ptr()]), 1, 1, 24, 24, 24,
+                                  _ptrs([flags.data_ptr()]), 1, None)
+    assert bad != 0                                         # rows must be a multiple of 16 bytes
+    assert L.tq_exchange_create(3, 2) is None
+    L.tq_exchange_free(ex)

@@ -85,6 +85,13 @@ def load() -> C.CDLL:
     sig("tq_shared_export", i, [vp, vp, C.c_size_t])
     sig("tq_shared_open", vp, [vp, C.c_size_t])
     sig("tq_shared_close", i, [vp])
+    sig("tq_exchange_create", vp, [i, i])
+    sig("tq_exchange_broadcast", i, [vp, vp, C.POINTER(C.c_void_p), i, i, C.c_long, C.c_long, C.c_long, C.POINTER(C.c_void_p), i, vp])
+    sig("tq_exchange_wait", i, [vp, vp, i, vp])
+    sig("tq_exchange_sum_f16", i, [vp, i, C.c_long, C.c_long, vp, vp])
+    sig("tq_exchange_merge_attention", i, [vp, vp, i, C.c_long, i, C.c_long, C.c_long, vp, vp])
+    sig("tq_exchange_status", i, [vp])
+    sig("tq_exchange_free", None, [vp])
     sig("tq_linear_in_features", i, [vp])
     sig("tq_linear_out_features", i, [vp])
     sig("tq_linear_free", None, [vp])

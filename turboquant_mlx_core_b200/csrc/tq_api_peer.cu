@@ -1,0 +1,100 @@
+// C entry points of the rank-to-rank exchange (tq_peer.cu): the data plane of the sharded paths.
+// The reference plans a layer split (src/distributed.cpp:201-253) and ships no collective
+// (benchmarks/bench_distributed.cpp:9-12), so these calls have no counterpart there.
+#include "tq_host.hpp"
+#include "tq_kernels.cuh"
+#include "turboquant_c/turboquant_b200.h"
+
+struct tq_exchange_s {
+    int rank = 0, world = 1, device = 0;
+    tq::DeviceBuffer words;               // [0] CTAs finished, [1] broadcasts completed, [2] waits started
+    unsigned int* h_status = nullptr;     // page-locked: a wait that gave up stores 10 here
+    unsigned int* d_status = nullptr;
+    ~tq_exchange_s() {
+        if (h_status) cudaFreeHost(h_status);
+    }
+};
+
+using namespace tq;
+
+extern "C" {
+
+tq_exchange_t tq_exchange_create(int rank, int world) {
+    return guarded<tq_exchange_t>(nullptr, nullptr, [&]() -> tq_exchange_t {
+        TQ_REQUIRE(world >= 1 && world <= 8 && rank >= 0 && rank < world, "tq_exchange_create: rank / world out of range (1..8 ranks)");
+        auto* ex = new tq_exchange_s;
+        try {
+            ex->rank = rank;
+            ex->world = world;
+            ex->device = current_device();
+            ex->words.resize(256);
+            TQ_CUDA(cudaMemset(ex->words.as<void>(), 0, 256));
+            TQ_CUDA(cudaMallocHost(&ex->h_status, sizeof(unsigned int)));
+            *ex->h_status = 0;
+            ex->d_status = static_cast<unsigned int*>(pinned_host_device_alias(ex->h_status));
+            TQ_REQUIRE(ex->d_status != nullptr, "tq_exchange_create: the status word is not mapped for the device");
+        } catch (...) {
+            delete ex;
+            throw;
+        }
+        return ex;
+    });
+}
+
+int tq_exchange_broadcast(tq_exchange_t ex, const void* src, void* const* dst, int n_dst, int rows, long row_bytes,
+                          long src_stride_bytes, long dst_stride_bytes, void* const* flags, int n_flags, void* stream) {
+    return guarded<int>(0, -1, [&]() {
+        TQ_REQUIRE(ex != nullptr, "tq_exchange_broadcast: NULL handle");
+        TQ_REQUIRE(flags != nullptr, "tq_exchange_broadcast: NULL flag list");
+        unsigned int* sig[8];
+        TQ_REQUIRE(n_flags >= 1 && n_flags <= 8, "tq_exchange_broadcast: 1..8 flag arrays");
+        for (int d = 0; d < n_flags; ++d) sig[d] = static_cast<unsigned int*>(flags[d]);
+        unsigned int* w = ex->words.as<unsigned int>();
+        launch_exchange_broadcast(src, dst, n_dst, rows, row_bytes, src_stride_bytes, dst_stride_bytes, sig, n_flags, ex->rank, w, w + 1,
+                                  static_cast<cudaStream_t>(stream));
+        return 0;
+    });
+}
+
+int tq_exchange_wait(tq_exchange_t ex, const void* local_flags, int n_flags, void* stream) {
+    return guarded<int>(0, -1, [&]() {
+        TQ_REQUIRE(ex != nullptr, "tq_exchange_wait: NULL handle");
+        launch_exchange_wait(static_cast<const unsigned int*>(local_flags), n_flags, ex->words.as<unsigned int>() + 2, ex->d_status,
+                             static_cast<cudaStream_t>(stream));
+        return 0;
+    });
+}
+
+int tq_exchange_sum_f16(const void* slots_fp16, int n_slots, long slot_stride, long count, void* out_fp16, void* stream) {
+    return guarded<int>(0, -1, [&]() {
+        launch_exchange_sum_f16(static_cast<const __half*>(slots_fp16), n_slots, slot_stride, count, static_cast<__half*>(out_fp16),
+                                static_cast<cudaStream_t>(stream));
+        return 0;
+    });
+}
+
+int tq_exchange_merge_attention(const void* outs_fp16, const void* lses_fp32, int parts, long rows, int head_dim,
+                                long part_stride_out, long part_stride_lse, void* out_fp16, void* stream) {
+    return guarded<int>(0, -1, [&]() {
+        launch_exchange_merge_attention(static_cast<const __half*>(outs_fp16), static_cast<const float*>(lses_fp32), parts, rows,
+                                        head_dim, part_stride_out, part_stride_lse, static_cast<__half*>(out_fp16),
+                                        static_cast<cudaStream_t>(stream));
+        return 0;
+    });
+}
+
+int tq_exchange_status(tq_exchange_t ex) {
+    return guarded<int>(0, -1, [&]() {
+        TQ_REQUIRE(ex != nullptr, "tq_exchange_status: NULL handle");
+        TQ_CUDA(cudaSetDevice(ex->device));
+        TQ_CUDA(cudaDeviceSynchronize());
+        const unsigned int h = *static_cast<volatile unsigned int*>(ex->h_status);
+        if (h != 0)
+            throw Error("exchange: a rank's completion flag did not arrive within a second (status " + std::to_string(h) + ")");
+        return 0;
+    });
+}
+
+void tq_exchange_free(tq_exchange_t ex) { delete ex; }
+
+}  // extern "C"

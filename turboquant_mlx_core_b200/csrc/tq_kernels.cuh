@@ -119,6 +119,15 @@ void launch_kv_encode_segments(const void* x, bool x_is_f16, long n_vec, long ve
                                uint32_t qjl_seed, bool with_qjl, const KvEncodeSegment* segs, int n_segs,
                                cudaStream_t stream);
 
+// tq_peer.cu — exchange between ranks over peer-mapped memory (plain stores, flags with epochs).
+void launch_exchange_broadcast(const void* src, void* const* dst, int n_dst, int rows, long row_bytes, long src_stride,
+                               long dst_stride, unsigned int* const* signal, int n_signal, int slot, unsigned int* done,
+                               unsigned int* epoch, cudaStream_t stream);
+void launch_exchange_wait(const unsigned int* flags, int n, unsigned int* epoch, unsigned int* status, cudaStream_t stream);
+void launch_exchange_sum_f16(const __half* slots, int n_slots, long slot_stride, long count, __half* out, cudaStream_t stream);
+void launch_exchange_merge_attention(const __half* outs, const float* lses, int parts, long rows, int dim, long part_stride_o,
+                                     long part_stride_l, __half* out, cudaStream_t stream);
+
 // tq_misc.cu — small element-wise helpers.
 void launch_f32_to_f16(const float* in, __half* out, long n, cudaStream_t stream);
 void launch_f16_to_f32(const __half* in, float* out, long n, cudaStream_t stream);

@@ -183,6 +183,87 @@ class SharedBuffer:
         self.local, self._peers, self.ptrs = None, [], []
 
 
+class Exchange:
+    """The data plane of the sharded paths for one rank: a SharedBuffer every rank can write, plus the
+    library's exchange handle (tq_exchange_*: broadcast a block to all ranks with plain 16-byte
+    peer stores and raise this rank's flag; wait for every rank's flag; epochs live in device
+    memory, so the sequence can be captured in a CUDA graph).  Every rank must issue the same
+    sequence of broadcast() and wait() calls.
+
+      all-gather of row shards   : compute the shard in place in self.buf, broadcast(offset, ...); wait()
+      all-reduce of partial sums : compute the partial into slot `rank`, broadcast; wait(); sum_f16()
+      merge of attention parts   : compute (out | lse) into slot `part`, broadcast; wait(); merge_attention()
+    """
+
+    def __init__(self, nbytes: int, group=None):
+        import ctypes as C
+        from . import _lib
+        self._L = _lib.load()
+        self.buf = SharedBuffer(nbytes, group)
+        self.rank, self.world = self.buf.rank, self.buf.world
+        self._h = self._L.tq_exchange_create(self.rank, self.world)
+        if not self._h:
+            raise _lib.TQError("tq_exchange_create: " + _lib.last_error())
+        n_peers = self.world - 1
+        self._flags = (C.c_void_p * self.world)(*self.buf.flag_ptrs)
+        self._n_peers = n_peers
+
+    @property
+    def local(self) -> int:
+        return self.buf.local
+
+    def broadcast(self, offset: int, rows: int, row_bytes: int, stride_bytes: int, stream=None, peers=None):
+        """Copy the block at byte `offset` of this rank's buffer (rows x row_bytes, rows stride_bytes
+        apart) to the same place of the buffers of `peers` (indices into buf.ptrs; default: all other
+        ranks) and raise this rank's flag on every rank."""
+        import ctypes as C
+        from . import _lib
+        idx = list(range(1, self.world)) if peers is None else list(peers)
+        if not idx:                       # a single rank: only the flag is raised (copy onto itself)
+            idx = [0]
+        dst = (C.c_void_p * len(idx))(*[self.buf.ptrs[i] + offset for i in idx])
+        _lib.check(self._L.tq_exchange_broadcast(self._h, C.c_void_p(self.buf.local + offset), dst, len(idx), rows, row_bytes,
+                                                  stride_bytes, stride_bytes, self._flags, self.world, _stream_ptr(stream)),
+                   "tq_exchange_broadcast")
+
+    def wait(self, stream=None):
+        import ctypes as C
+        from . import _lib
+        _lib.check(self._L.tq_exchange_wait(self._h, C.c_void_p(self.buf.local_flags), self.world, _stream_ptr(stream)),
+                   "tq_exchange_wait")
+
+    def sum_f16(self, slots_offset: int, n_slots: int, slot_stride_elems: int, count: int, out_ptr: int, stream=None):
+        import ctypes as C
+        from . import _lib
+        _lib.check(self._L.tq_exchange_sum_f16(C.c_void_p(self.buf.local + slots_offset), n_slots, slot_stride_elems, count,
+                                                C.c_void_p(out_ptr), _stream_ptr(stream)), "tq_exchange_sum_f16")
+
+    def merge_attention(self, outs_offset: int, lses_offset: int, parts: int, rows: int, head_dim: int, part_stride_out: int,
+                        part_stride_lse: int, out_ptr: int, stream=None):
+        import ctypes as C
+        from . import _lib
+        _lib.check(self._L.tq_exchange_merge_attention(C.c_void_p(self.buf.local + outs_offset), C.c_void_p(self.buf.local + lses_offset),
+                                                        parts, rows, head_dim, part_stride_out, part_stride_lse, C.c_void_p(out_ptr),
+                                                        _stream_ptr(stream)), "tq_exchange_merge_attention")
+
+    def check_status(self):
+        from . import _lib
+        _lib.check(self._L.tq_exchange_status(self._h), "tq_exchange_status")
+
+    def close(self):
+        if getattr(self, "_h", None):
+            self._L.tq_exchange_free(self._h)
+            self._h = None
+        self.buf.close()
+
+
+def _stream_ptr(stream):
+    import ctypes as C
+    if stream is None:
+        return None
+    return C.c_void_p(stream.cuda_stream if hasattr(stream, "cuda_stream") else int(stream))
+
+
 def col_range(in_features: int, block_size: int, rank: int, world: int) -> tuple[int, int]:
     """Contiguous input-feature range of `rank` for a ROW-parallel linear (o_proj, down_proj):
     whole WHT blocks, as even as possible, so every rank rotates only its own slice of x."""
