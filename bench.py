@@ -202,18 +202,46 @@ def run_cuda(args):
     stream = torch.cuda.Stream(device=device)
     sp = C.c_void_p(stream.cuda_stream)
 
+    # With more than one rank the headline is the row-sharded layer of the sharded paths: every rank
+    # holds a 4096 x 4096 row shard of a (4096 * N) x 4096 layer, and after every layer-forward the
+    # fp16 output shards are all-gathered (each rank stores its 8 KB into every rank's buffer over
+    # NVLink and raises its flag; a one-warp kernel waits for all flags).  Two gather buffers
+    # alternate.  If the shared buffers cannot be mapped on every rank, the ranks run independent
+    # layers and the line says so.
+    exchange, exchange_note = None, None
+    if world > 1:
+        from turboquant_mlx_core_b200.sharding import Exchange
+        err = None
+        try:
+            exchange = Exchange(2 * world * OUT_F * 2)
+        except Exception as exc:
+            err = str(exc)
+        ok_t = torch.tensor([0.0 if err else 1.0], device=device)
+        dist.all_reduce(ok_t, op=dist.ReduceOp.MIN)
+        if ok_t.item() != 1.0:
+            if exchange is not None:
+                exchange.close()
+            exchange, exchange_note = None, "shared buffers could not be mapped on every rank: independent layers, no exchange"
+
     def one_pass():
         for i, lin in enumerate(layers):
-            rc = L.tq_linear_forward(lin.handle, C.c_void_p(x_dev[i].data_ptr()), tq.TQ_F16, 1,
-                                     C.c_void_p(y_dev[i].data_ptr()), sp)
+            if exchange is None:
+                y_ptr = y_dev[i].data_ptr()
+            else:
+                off = ((i & 1) * world + rank) * OUT_F * 2
+                y_ptr = exchange.local + off
+            rc = L.tq_linear_forward(lin.handle, C.c_void_p(x_dev[i].data_ptr()), tq.TQ_F16, 1, C.c_void_p(y_ptr), sp)
             if rc:
                 raise RuntimeError(L.tq_last_error().decode())
+            if exchange is not None:
+                exchange.broadcast(off, 1, OUT_F * 2, OUT_F * 2, stream=stream)
+                exchange.wait(stream=stream)
 
     # the launch-bound inner loop is captured once and replayed
     with torch.cuda.stream(stream):
         one_pass()
     stream.synchronize()
-    launch_mode = "CUDA graph of one GEMV per layer"
+    launch_mode = "CUDA graph of one GEMV per layer" + (" + output all-gather by peer stores and flag wait" if exchange is not None else "")
     try:
         if args.no_graph:
             raise RuntimeError("graph disabled by flag")
@@ -285,7 +313,21 @@ def run_cuda(args):
 
     # parity guard on what was timed: the device and host paths must agree bit for bit
     torch.cuda.synchronize()
-    same = bool(torch.equal(y_dev.cpu(), y_host))
+    gathered_ok = None
+    if exchange is None:
+        same = bool(torch.equal(y_dev.cpu(), y_host))
+    else:
+        # the last two layers' gathered outputs sit in the two buffers: this rank's slots must equal
+        # the host path's results, and every rank must hold the same gathered bytes
+        exchange.check_status()
+        gath = exchange.buf.tensor((2, world, OUT_F), torch.float16).clone()
+        same = all(bool(torch.equal(gath[i & 1, rank].cpu(), y_host[i])) for i in (nbuf - 2, nbuf - 1))
+        # layers differ per rank, so compare every rank's copy of the gathered block with rank 0's
+        ref = gath.clone()
+        dist.broadcast(ref, src=0)
+        ok = torch.tensor([1.0 if torch.equal(ref, gath) else 0.0], device=device)
+        dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+        gathered_ok = bool(ok.item() == 1.0)
 
     peak, peak_kind = measured_peaks()
     per_launch_s = ms_max * 1e-3 / launches
@@ -300,7 +342,11 @@ def run_cuda(args):
                    "layers_per_step": nbuf, "l2_policy": f"{nbuf} distinct weight matrices per step "
                                                          f"({nbuf * OUT_F * IN_F / 1e6:.0f} MB) "
                                                          + ("> L2" if nbuf * OUT_F * IN_F > 126e6 else "<= L2 (126 MB): not a valid HBM measurement"),
-                   "launch": launch_mode, "per_gpu": "independent layers, no collective",
+                   "launch": launch_mode,
+                   "per_gpu": ("independent layers, no collective" if exchange is None else
+                               "one 4096 x 4096 row shard of a (4096 N) x 4096 layer per launch; after every layer the fp16 output "
+                               "shards are all-gathered over NVLink (peer stores + flags, no collective library)"),
+                   "exchange_note": exchange_note,
                    "vs_baseline_note": "published 671 tok/s is the reference on an Apple GPU at block 512"},
         "gb_per_s": achieved * world,
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
@@ -314,6 +360,10 @@ def run_cuda(args):
         "clocks": clocks,
         "device_host_paths_bit_identical": same,
     }
+    if gathered_ok is not None:
+        line["gathered_outputs_identical_on_every_rank"] = gathered_ok
+    if exchange is not None:
+        exchange.close()
 
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         line["cpu_baseline"] = cpu_baseline(qw0, cbs, x_host[0].numpy(), y_dev[0].cpu().numpy(), budget_s=12.0)
@@ -365,7 +415,8 @@ def bench_attention(tq, L, device, stream, rank, world, args, ctx):
     import torch
     import torch.distributed as dist
     from turboquant_mlx_core_b200.sharding import attention_grid, context_range, merge_attention_parts
-    n_seqs, kv_heads, q_heads, dim = 16, 4, 28, 128
+    kv_heads = args.attn_kv_heads
+    n_seqs, q_heads, dim = 16, 7 * kv_heads, 128
     if world > kv_heads and world % kv_heads:
         return {"skipped": f"{world} ranks over {kv_heads} KV heads: rank count must be a multiple of the heads"}
     h0, h1, part, parts = attention_grid(kv_heads, rank, world)
@@ -390,22 +441,52 @@ def bench_attention(tq, L, device, stream, rank, world, args, ctx):
     lse = torch.empty((n_seqs, qh_local), device=device, dtype=torch.float32)
     arr = (C.c_void_p * n_seqs)(*[c.handle for c in caches])
     sp = C.c_void_p(stream.cuda_stream)
-    gathered_o = torch.empty((world,) + tuple(out.shape), device=device, dtype=out.dtype) if parts > 1 else None
-    gathered_l = torch.empty((world,) + tuple(lse.shape), device=device, dtype=lse.dtype) if parts > 1 else None
+    # Ranks that share a KV head (more ranks than heads) exchange their (output | log-sum-exp) parts by
+    # peer stores and merge them with one small kernel: slot `part` of the buffer of every rank that
+    # shares the head; two buffers alternate.
+    rows = n_seqs * qh_local
+    out_bytes, slot_bytes = rows * dim * 2, rows * dim * 2 + rows * 4
+    exchange, merge_path = None, None
+    if parts > 1:
+        from turboquant_mlx_core_b200.sharding import Exchange
+        err = None
+        try:
+            exchange = Exchange(2 * parts * slot_bytes)
+        except Exception as exc:
+            err = str(exc)
+        ok_t = torch.tensor([0.0 if err else 1.0], device=device)
+        dist.all_reduce(ok_t, op=dist.ReduceOp.MIN)
+        if ok_t.item() != 1.0:
+            if exchange is not None:
+                exchange.close()
+            return {"skipped": "shared buffers could not be mapped on every rank", "local_error": err}
+        sharing = [h0 + kv_heads * p for p in range(parts) if h0 + kv_heads * p != rank]
+        peer_idx = [1 + (r if r < rank else r - 1) for r in sharing]
+        merge_path = "parts exchanged by tq_exchange_broadcast (peer stores + flags), merged by tq_exchange_merge_attention"
+    step = [0]
 
     def call():
+        if exchange is None:
+            o_ptr, l_ptr = out.data_ptr(), lse.data_ptr()
+        else:
+            base = (step[0] & 1) * parts * slot_bytes
+            step[0] += 1
+            o_ptr = exchange.local + base + part * slot_bytes
+            l_ptr = o_ptr + out_bytes
         rc = L.tq_kv_attention_lse(arr, n_seqs, 0, C.c_void_p(q.data_ptr()), tq.TQ_F16, qh_local,
-                                   C.c_void_p(out.data_ptr()), C.c_void_p(lse.data_ptr()), 0, -1, 1, sp)
+                                   C.c_void_p(o_ptr), C.c_void_p(l_ptr), 0, -1, 1, sp)
         if rc:
             raise RuntimeError(L.tq_last_error().decode())
-        if parts > 1:
-            # every rank receives all (head, part) results; rows of ranks r, r + kv_heads, ... share a head
-            dist.all_gather_into_tensor(gathered_o.view(-1, qh_local, dim), out)
-            dist.all_gather_into_tensor(gathered_l.view(-1, qh_local), lse)
-            o = gathered_o.view(parts, kv_heads, n_seqs, qh_local, dim)
-            l_ = gathered_l.view(parts, kv_heads, n_seqs, qh_local)
-            return merge_attention_parts(o, l_)
+        if exchange is not None:
+            exchange.broadcast(base + part * slot_bytes, 1, slot_bytes, slot_bytes, stream=stream, peers=peer_idx)
+            exchange.wait(stream=stream)
+            exchange.merge_attention(base, base + out_bytes, parts, rows, dim, slot_bytes // 2, slot_bytes // 4, out.data_ptr(),
+                                     stream=stream)
         return out
+
+    # (launched eagerly: the attention entry point stages its per-sequence descriptors from host memory
+    # on every call, so it cannot be captured in a CUDA graph)
+    per_call = 1
 
     with torch.cuda.stream(stream):
         for _ in range(3):
@@ -421,15 +502,29 @@ def bench_attention(tq, L, device, stream, rank, world, args, ctx):
             call()
         e1.record(stream)
     torch.cuda.synchronize()
-    t = torch.tensor([e0.elapsed_time(e1) * 1e3 / reps], device=device, dtype=torch.float64)
+    t = torch.tensor([e0.elapsed_time(e1) * 1e3 / (reps * per_call)], device=device, dtype=torch.float64)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     us = float(t.item())
     algo = n_seqs * heads_local * ctx_local * 118          # compact bytes per (token, KV head) with QJL
     peak, kind = measured_peaks()
+    merged_ok = None
+    if exchange is not None:
+        # the merged result must equal what the torch-side rule gives on all-gathered parts
+        exchange.check_status()
+        mine = exchange.buf.tensor((2, parts, slot_bytes), torch.uint8)[0].clone()
+        o_parts = mine[:, :out_bytes].contiguous().view(torch.float16).view(parts, rows, dim)
+        l_parts = mine[:, out_bytes:].contiguous().view(torch.float32).view(parts, rows)
+        want = merge_attention_parts(o_parts, l_parts)
+        err = float((out.float().view(rows, dim) - want).norm() / want.norm().clamp_min(1e-30))
+        ok = torch.tensor([1.0 if err < 1e-3 else 0.0], device=device)
+        dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+        merged_ok = bool(ok.item() == 1.0)
+        exchange.close()
     for c in caches:
         c.close()
-    return {"workload": f"config 3: {n_seqs} seqs x ctx {ctx}, {kv_heads} KV / {q_heads} query heads, d {dim}, QJL on",
+    return {"workload": f"{n_seqs} seqs x ctx {ctx}, {kv_heads} KV / {q_heads} query heads, d {dim}, QJL on",
+            "merge_of_context_parts": merge_path, "merged_result_matches_rule_on_every_rank": merged_ok,
             "us_per_layer_step": us, "tok_per_s": n_seqs / (us * 1e-6), "gb_per_s_per_gpu": algo / (us * 1e-6) / 1e9,
             "frac_of_peak": algo / (us * 1e-6) / 1e9 / peak, "peak_kind": kind, "kv_heads_per_gpu": heads_local,
             "context_parts": parts,
@@ -631,9 +726,14 @@ def bench_decoder_layer(tq, L, device, stream, cbs, args):
 # ---- secondary: row-sharded LM head (151936 x 2048) -------------------------------------------
 
 def bench_lm_head(tq, L, device, stream, rank, world, cbs, args):
+    """Rows sharded over the ranks (whole 16-row tiles).  Two ways to give every rank the full logits:
+    (a) forward into a private shard, then an NCCL all-gather (torch.distributed); (b) forward straight
+    into this rank's rows of the shared logits buffer, then tq_exchange_broadcast of that block to
+    every rank (16-byte peer stores, flag) and tq_exchange_wait - no collective library.  (b) is
+    captured in a CUDA graph (two alternating logits buffers) and compared bit for bit with (a)."""
     import torch
     import torch.distributed as dist
-    from turboquant_mlx_core_b200.sharding import all_gather_rows, row_range
+    from turboquant_mlx_core_b200.sharding import Exchange, all_gather_rows, row_range
     vocab, hidden = 151936, 2048
     s, e = row_range(vocab, rank, world)
     rows = e - s
@@ -642,11 +742,60 @@ def bench_lm_head(tq, L, device, stream, rank, world, cbs, args):
     qw = tq.quantize_weight(w, cbs[0], cbs[1], tq.QuantizerConfig(4, 4, BLOCK, True))
     del w
     lin = tq.TurboQuantLinear(hidden, rows, qw, cbs[0], cbs[1], BLOCK)
-    res = {}
+    res = {"workload": f"LM head {vocab}x{hidden}, rows sharded over {world} GPU(s)"}
     sp = C.c_void_p(stream.cuda_stream)
+    reps = 20
+
+    def timed(fn, graph=False):
+        """(device us per call, host us per call when issued eagerly)"""
+        with torch.cuda.stream(stream):
+            for _ in range(3):
+                fn()
+        torch.cuda.synchronize()
+        run, per = fn, 1
+        if graph:
+            gr = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(gr, stream=stream):
+                fn()
+                fn()                      # both gather buffers
+            run, per = gr.replay, 2
+            with torch.cuda.stream(stream):
+                run()
+            torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t0 = time.perf_counter()
+        with torch.cuda.stream(stream):
+            e0.record(stream)
+            for _ in range(reps):
+                run()
+            e1.record(stream)
+        host_us = (time.perf_counter() - t0) * 1e6 / (reps * per)
+        torch.cuda.synchronize()
+        t = torch.tensor([e0.elapsed_time(e1) * 1e3 / (reps * per)], device=device, dtype=torch.float64)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item()), host_us
+
+    exchange, setup_error = None, None
+    if world > 1:
+        try:
+            exchange = Exchange(2 * 32 * vocab * 2)
+        except Exception as exc:
+            setup_error = str(exc)
+        ok_t = torch.tensor([0.0 if setup_error else 1.0], device=device)
+        dist.all_reduce(ok_t, op=dist.ReduceOp.MIN)
+        if ok_t.item() != 1.0:
+            if exchange is not None:
+                exchange.close()
+            exchange = None
+            res["exchange"] = {"skipped": "shared buffers could not be mapped on every rank", "local_error": setup_error}
+
     for batch in (1, 32):
         x = torch.randn((batch, hidden), generator=g, device=device).half()
         y = torch.empty((batch, rows), device=device, dtype=torch.float16)
+        algo = vocab * hidden + 4 * vocab + 2 * batch * hidden + 2 * batch * vocab
 
         def call():
             rc = L.tq_linear_forward(lin.handle, C.c_void_p(x.data_ptr()), tq.TQ_F16, batch, C.c_void_p(y.data_ptr()), sp)
@@ -656,116 +805,43 @@ def bench_lm_head(tq, L, device, stream, rank, world, cbs, args):
                 return all_gather_rows(y, vocab, world)
             return y
 
-        with torch.cuda.stream(stream):
-            for _ in range(3):
-                call()
-        torch.cuda.synchronize()
-        if world > 1:
-            dist.barrier()
-        reps = 20
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        with torch.cuda.stream(stream):
-            e0.record(stream)
-            for _ in range(reps):
-                call()
-            e1.record(stream)
-        torch.cuda.synchronize()
-        t = torch.tensor([e0.elapsed_time(e1) * 1e3 / reps], device=device, dtype=torch.float64)
-        if world > 1:
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        us = float(t.item())
-        algo = vocab * hidden + 4 * vocab + 2 * batch * hidden + 2 * batch * vocab
-        res[f"b{batch}"] = {"us": us, "tok_per_s": batch / (us * 1e-6), "gb_per_s_aggregate": algo / (us * 1e-6) / 1e9}
-    if world > 1:
-        # the same without the all-gather: the GEMV's epilogue stores every logit into every
-        # rank's buffer over NVLink (peer-mapped memory, plain stores); one tiny all-reduce is the
-        # barrier after which each rank may read the full logits
-        from turboquant_mlx_core_b200.sharding import SharedBuffer
-        # set-up errors must not leave some ranks inside collectives the others never join:
-        # every rank reports whether its buffers are mapped, and all skip together otherwise
-        shared, setup_error = None, None
+        us, host_us = timed(call, graph=(world == 1))
+        key = f"b{batch}"
+        res[key] = {"us": us, "tok_per_s": batch / (us * 1e-6), "gb_per_s_aggregate": algo / (us * 1e-6) / 1e9,
+                    "host_us_per_call_eager": host_us,
+                    "path": "forward" + (" + NCCL all-gather of the fp16 shards (eager launches)" if world > 1 else " (CUDA graph)")}
+        if exchange is None:
+            continue
         try:
-            shared = SharedBuffer(8 * vocab * 2)
-        except Exception as e:
-            setup_error = str(e)
-        ok_t = torch.tensor([0.0 if setup_error else 1.0], device=device)
-        dist.all_reduce(ok_t, op=dist.ReduceOp.MIN)
-        if ok_t.item() != 1.0:
-            res["b1_scatter"] = {"skipped": "shared buffers could not be mapped on every rank", "local_error": setup_error}
-            lin.close()
-            res["workload"] = f"config 2: LM head {vocab}x{hidden}, rows sharded over {world} GPU(s), fp16 logits all-gather"
-            return res
-        try:
-            logits = shared.tensor((8, vocab), torch.float16)
-            flag = torch.zeros(1, device=device)
-            x = torch.randn((1, hidden), generator=g, device=device).half()
-            y_ref = torch.empty((1, rows), device=device, dtype=torch.float16)
+            step = [0]
 
-            def call_scatter():
-                lin.forward_scatter(x, shared.ptrs, vocab, s, stream=stream)
-                dist.all_reduce(flag)
+            def call_exchange():
+                half = step[0] & 1
+                step[0] += 1
+                base = half * batch * vocab * 2                    # byte offset of this buffer's [batch, vocab] logits
+                # rows [s, e) of every activation row, at the vocabulary's stride
+                lin.forward_strided(x, exchange.local + base + s * 2, vocab, stream=stream)
+                exchange.broadcast(base + s * 2, batch, rows * 2, vocab * 2, stream=stream)
+                exchange.wait(stream=stream)
 
+            us_x, host_x = timed(call_exchange, graph=True)
+            exchange.check_status()
             with torch.cuda.stream(stream):
-                for _ in range(3):
-                    call_scatter()
-                rc = L.tq_linear_forward(lin.handle, C.c_void_p(x.data_ptr()), tq.TQ_F16, 1, C.c_void_p(y_ref.data_ptr()), sp)
-                full = all_gather_rows(y_ref, vocab, world)
+                full = call()
             torch.cuda.synchronize()
-            dist.barrier()
-            same = bool(torch.equal(full[0], logits[0]))
-            reps = 20
-            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            with torch.cuda.stream(stream):
-                e0.record(stream)
-                for _ in range(reps):
-                    call_scatter()
-                e1.record(stream)
-            torch.cuda.synchronize()
-            t = torch.tensor([e0.elapsed_time(e1) * 1e3 / reps], device=device, dtype=torch.float64)
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-            us = float(t.item())
-
-            def timed(fn):
-                with torch.cuda.stream(stream):
-                    fn()
-                    a0, a1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-                    a0.record(stream)
-                    for _ in range(reps):
-                        fn()
-                    a1.record(stream)
-                torch.cuda.synchronize()
-                tt = torch.tensor([a0.elapsed_time(a1) * 1e3 / reps], device=device, dtype=torch.float64)
-                dist.all_reduce(tt, op=dist.ReduceOp.MAX)
-                return float(tt.item())
-            us_gemv = timed(lambda: lin.forward_scatter(x, shared.ptrs, vocab, s, stream=stream))
-            us_barrier = timed(lambda: dist.all_reduce(flag))
-            # fused barrier: the GEMV's tail raises this rank's flag on every rank; a one-warp
-            # kernel waits for all flags (no collective library call at all)
-            epoch = [0]
-
-            def call_signal():
-                epoch[0] += 1
-                lin.forward_scatter(x, shared.ptrs, vocab, s, stream=stream, signal_ptrs=shared.flag_ptrs,
-                                    signal_slot=rank, signal_value=epoch[0])
-                lin.wait_peers(shared.local_flags, world, epoch[0], stream=stream)
-            logits.zero_()
-            torch.cuda.synchronize()
-            dist.barrier()
-            us_signal = timed(call_signal)
-            lin.check_status()
-            same = same and bool(torch.equal(full[0], logits[0]))
+            logits = exchange.buf.tensor((2, batch, vocab), torch.float16)
+            same = bool(torch.equal(full, logits[0])) and bool(torch.equal(full, logits[1]))
             same_t = torch.tensor([1.0 if same else 0.0], device=device)
             dist.all_reduce(same_t, op=dist.ReduceOp.MIN)
-            res["b1_scatter"] = {"us": us, "tok_per_s": 1 / (us * 1e-6), "us_gemv_with_peer_stores_alone": us_gemv,
-                                 "us_one_element_all_reduce_alone": us_barrier,
-                                 "us_with_fused_flag_barrier": us_signal,
-                                 "path": "tq_linear_forward_scatter (peer stores from the GEMV epilogue) + 1-element all-reduce as barrier",
-                                 "identical_to_all_gather_on_every_rank": bool(same_t.item() == 1.0)}
-            shared.close()
-        except Exception as e:
-            res["b1_scatter"] = {"error": str(e)}
+            res[key + "_exchange"] = {"us": us_x, "tok_per_s": batch / (us_x * 1e-6), "gb_per_s_aggregate": algo / (us_x * 1e-6) / 1e9,
+                                      "host_us_per_call_eager": host_x,
+                                      "path": "forward into the shared logits + tq_exchange_broadcast + tq_exchange_wait (CUDA graph)",
+                                      "identical_to_all_gather_on_every_rank": bool(same_t.item() == 1.0)}
+        except Exception as exc:
+            res[key + "_exchange"] = {"error": str(exc)}
+    if exchange is not None:
+        exchange.close()
     lin.close()
-    res["workload"] = f"config 2: LM head {vocab}x{hidden}, rows sharded over {world} GPU(s), fp16 logits all-gather"
     return res
 
 
@@ -869,6 +945,7 @@ def main():
     ap.add_argument("--impl", default="cuda", choices=["cuda", "reference"])
     ap.add_argument("--nbuf", type=int, default=64, help="distinct 4096x4096 layers per step")
     ap.add_argument("--attn-ctx", type=int, default=32768)
+    ap.add_argument("--attn-kv-heads", type=int, default=4, help="KV heads of the attention leg (7 query heads each)")
     ap.add_argument("--no-extras", action="store_true", help="skip the secondary measurements")
     ap.add_argument("--legs", default="", help="comma list of secondary measurements to run "
                                                "(attention, decoder_layer, prefill, lm_head, side_kernels); default all")

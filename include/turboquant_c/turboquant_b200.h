@@ -176,6 +176,15 @@ int tq_linear_dequantize(tq_linear_t lin, void* result, int result_dtype, void* 
 int tq_linear_forward_scatter(tq_linear_t lin, const void* x_fp16_device, int batch, void* const* dst, int n_dst,
                               long dst_row_stride, long row_offset, void* stream);
 
+/** Forward whose fp16 result is this layer's rows inside a wider buffer: activation row n goes to
+ *  y_fp16_device[n * y_row_stride ...] (y_row_stride >= out_features, in elements).  x and y are
+ *  device pointers; any batch size (decode kernel up to 8 rows, tensor-memory kernel above).  A
+ *  rank of a row-sharded layer passes its first row's address inside the full [batch, total_rows]
+ *  buffer and total_rows as the stride.  Stands in for the reference's forward
+ *  (src/linear.cpp:19-28) followed by a copy into place. */
+int tq_linear_forward_strided(tq_linear_t lin, const void* x_fp16_device, int batch, void* y_fp16_device, long y_row_stride,
+                              void* stream);
+
 /** The same, followed by a completion signal: signal[d] points to an array of 32-bit flags in
  *  destination d's memory (e.g. at the end of its shared buffer); when every result of this
  *  call has been stored, flag signal_slot (0..31, normally this rank) of every destination is
@@ -326,7 +335,10 @@ int tq_kv_append_batch(const tq_kv_cache_t* caches, int n_seqs, int layer, const
  *  out fp16 [n_seqs, q_heads, head_dim]; tokens [start, end) of every cache, end < 0
  *  meaning "all tokens of that cache"; q_heads a multiple of the cache's heads
  *  (grouped-query attention).  use_qjl != 0 adds the 1-bit residual correction to the
- *  key scores (an extension: the reference stores those bits but never reads them). */
+ *  key scores (an extension: the reference stores those bits but never reads them).
+ *  The call copies a table of per-sequence descriptors from host memory on every invocation and
+ *  keeps its staging buffers in caches[0]: do not capture it in a CUDA graph, and issue the calls
+ *  that share a first cache on one stream. */
 int tq_kv_attention(const tq_kv_cache_t* caches, int n_seqs, int layer, const void* queries, int q_dtype,
                     int q_heads, void* out_fp16, int start, int end, int use_qjl, void* stream);
 

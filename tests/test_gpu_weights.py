@@ -236,6 +236,31 @@ def test_forward_scatter_writes_every_destination(tq, oracle):
     L.tq_shared_free(C.c_void_p(p))
 
 
+def test_forward_strided_writes_rows_inside_a_wider_buffer(tq, oracle):
+    """tq_linear_forward_strided (a rank's shard of full logits): the same bits as forward(), at the
+    given row stride, nothing else touched - decode kernel (1..8 rows) and tensor-memory kernel."""
+    import torch
+    rng = np.random.default_rng(14)
+    cb = oracle.codebook(4)[0]
+    rows, cols, total, off = 208, 512, 1000, 304
+    w = (rng.standard_normal((rows, cols)) * 0.02).astype(np.float16).astype(np.float32)
+    pp, pr, norms, seeds = oracle.quantize_weight(w, cb, cb, 4, 4, 128, True)
+    lin = tq.TurboQuantLinear(cols, rows, tq.QuantizedWeight(pp, pr, norms, seeds), tq.codebook_from_centroids(cb),
+                              tq.codebook_from_centroids(cb), 128)
+    for batch in (1, 5, 8, 9, 40):
+        x = torch.from_numpy(rng.standard_normal((batch, cols)).astype(np.float16)).cuda()
+        want = lin.forward(x)
+        buf = torch.full((batch, total), 7.0, dtype=torch.float16, device="cuda")
+        lin.forward_strided(x, buf.data_ptr() + off * 2, total)
+        torch.cuda.synchronize()
+        assert torch.equal(buf[:, off:off + rows], want), batch
+        assert bool((buf[:, :off] == 7.0).all()) and bool((buf[:, off + rows:] == 7.0).all())
+    lin.check_status()
+    with pytest.raises(tq.TQError):
+        lin.forward_strided(x, buf.data_ptr(), rows - 1)          # stride smaller than the layer's rows
+    lin.close()
+
+
 def test_scatter_completion_signal_and_bounded_wait(tq, oracle):
     """The completion flag of a scattering call reaches every destination's flag array, the wait
     kernel returns once the flags are there, and a flag that nobody raises makes the wait give up

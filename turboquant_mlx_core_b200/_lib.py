@@ -73,6 +73,7 @@ def load() -> C.CDLL:
     sig("tq_linear_create", vp, [i, i, vp, i, vp, vp, vp, vp, i, vp, i, u32])
     sig("tq_linear_forward", i, [vp, vp, i, i, vp, vp])
     sig("tq_linear_forward_noalloc", i, [vp, vp, i, vp, vp])
+    sig("tq_linear_forward_strided", i, [vp, vp, i, vp, C.c_long, vp])
     sig("tq_linear_noalloc_scratch_limit", C.c_size_t, [])
     sig("tq_linear_dequantize", i, [vp, vp, i, vp])
     sig("tq_linear_status", i, [vp])

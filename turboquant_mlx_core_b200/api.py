@@ -227,6 +227,13 @@ class TurboQuantLinear:
                                                        int(row_offset), sig, int(signal_slot), int(signal_value) & 0xFFFFFFFF,
                                                        _stream_ptr(stream)), "TurboQuantLinear.forward_scatter")
 
+    def forward_strided(self, x, y_ptr: int, y_row_stride: int, stream=None):
+        """Device fp16 x [batch, in]; the fp16 result goes to raw device address y_ptr with
+        activation rows y_row_stride elements apart (this layer's rows inside a wider buffer)."""
+        batch = int(np.prod(x.shape[:-1])) if len(x.shape) > 1 else 1
+        check(self._L.tq_linear_forward_strided(self._h, _ptr(x), batch, C.c_void_p(int(y_ptr)), int(y_row_stride),
+                                                _stream_ptr(stream)), "TurboQuantLinear.forward_strided")
+
     def wait_peers(self, local_flags_ptr: int, n_flags: int, value: int, stream=None):
         """Enqueue the (bounded) wait for the completion flags of n_flags ranks in this rank's own
         flag array to reach `value`; afterwards, on that stream, every rank's scattered results are

@@ -201,6 +201,17 @@ public:
                                     sm_count_, st, signal ? sig : nullptr, signal_slot, signal_value, counter_.as<unsigned int>());
     }
 
+    // Device fp16 in, device fp16 out whose activation rows are y_stride elements apart (this layer's
+    // rows inside a wider buffer, e.g. a rank's shard of the full logits).
+    void forward_strided(const void* x, int batch, void* y, long y_stride, cudaStream_t st) {
+        TQ_REQUIRE(x && y, "forward_strided: NULL argument");
+        TQ_REQUIRE(batch >= 1, "forward_strided: batch must be positive");
+        TQ_REQUIRE(y_stride >= out_, "forward_strided: row stride smaller than out_features");
+        TQ_REQUIRE(tq::is_device_pointer(x) && tq::is_device_pointer(y), "forward_strided: x and y must be device pointers");
+        TQ_CUDA(cudaSetDevice(device_));
+        launch_forward(static_cast<const __half*>(x), batch, static_cast<__half*>(y), st, y_stride);
+    }
+
     void wait_peers(const void* flags, int n, unsigned int value, cudaStream_t st) {
         TQ_CUDA(cudaSetDevice(device_));
         tq::launch_peer_wait(static_cast<const unsigned int*>(flags), n, value, d_status_, st);
@@ -276,7 +287,9 @@ private:
     // Device pointers only.  More than kGemmMinBatch rows go to the tensor-core GEMM (when the
     // shape allows); otherwise batches above 8 rows are issued as passes of 8 through the GEMV.
     static constexpr int kGemmMinBatch = 8;
-    void launch_forward(const __half* d_x, int batch, __half* d_y, cudaStream_t st) {
+    // y_stride: elements between activation rows of y (0 = out_features: a dense [batch, out] result).
+    void launch_forward(const __half* d_x, int batch, __half* d_y, cudaStream_t st, long y_stride = 0) {
+        if (y_stride <= 0) y_stride = out_;
         // From 9 rows on the tensor-memory kernel streams the codes once whatever the batch (its
         // activation tile is as narrow as the batch, in steps of 16 rows).
         if (batch > kGemmMinBatch && tq::gemm_supported(in_)) {
@@ -284,7 +297,18 @@ private:
             gemm_scratch_.reserve(tq::gemm_scratch_bytes(out_, in_, batch, planes, sm_count_));
             tq::launch_tq8_gemm(codes_.as<uint8_t>(), norms_.as<float>(), tables_.as<float>(), d_x, d_y, out_, in_, batch,
                                 block_, planes, seed_p_, seed_r_, gemm_scratch_.as<void>(), d_status_,
-                                sm_count_, st);
+                                sm_count_, st, y_stride);
+            return;
+        }
+        if (y_stride != out_) {
+            // rows of a wider buffer: the decode kernel's variant with an explicit destination stride
+            for (int b0 = 0; b0 < batch; b0 += 8) {
+                const int nb = batch - b0 < 8 ? batch - b0 : 8;
+                __half* dst = d_y + static_cast<size_t>(b0) * y_stride;
+                tq::launch_tq8_gemv_scatter(codes_.as<uint8_t>(), norms_.as<float>(), tables_.as<float>(),
+                                            d_x + static_cast<size_t>(b0) * in_, &dst, 1, y_stride, out_, in_, nb, block_,
+                                            dual_ ? 2 : 1, seed_p_, seed_r_, scratch_.as<void>(), d_status_, sm_count_, st);
+            }
             return;
         }
         for (int b0 = 0; b0 < batch; b0 += 8) {
@@ -340,6 +364,15 @@ int tq_linear_forward(tq_linear_t lin, const void* x, int x_dtype, int batch, vo
     return guarded<int>(0, -1, [&]() {
         TQ_REQUIRE(lin && lin->impl, "tq_linear_forward: NULL handle");
         lin->impl->forward(x, x_dtype, batch, y_fp16, static_cast<cudaStream_t>(stream));
+        return 0;
+    });
+}
+
+int tq_linear_forward_strided(tq_linear_t lin, const void* x_fp16_device, int batch, void* y_fp16_device, long y_row_stride,
+                              void* stream) {
+    return guarded<int>(0, -1, [&]() {
+        TQ_REQUIRE(lin && lin->impl, "tq_linear_forward_strided: NULL handle");
+        lin->impl->forward_strided(x_fp16_device, batch, y_fp16_device, y_row_stride, static_cast<cudaStream_t>(stream));
         return 0;
     });
 }

@@ -280,7 +280,8 @@ struct GemmArgs {
     const float* norms;     // [out]
     const float* table;     // [n_planes, 256] fp32
     const __half* xrot;     // rotated activation in operand-tile order (see rotate_rows_f16_kernel)
-    __half* y;              // [m, out]
+    __half* y;              // [m, out], activation rows y_stride elements apart
+    long y_stride;
     float* partial;         // [k_splits, m, out] fp32 un-scaled partial sums (only when k_splits > 1)
     unsigned int* status;   // device error word (0 = ok)
     int out, in, m, n_planes;
@@ -524,7 +525,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) tq8_gemm_kernel(const GemmArg
                 for (int j = 0; j < 32; ++j) {
                     const int tok = tok0 + col0 + j;
                     if (r_ok && tok < p.m) {
-                        if (p.k_splits == 1) p.y[static_cast<size_t>(tok) * p.out + r] = __float2half_rn(__uint_as_float(v[j]) * scale);
+                        if (p.k_splits == 1) p.y[static_cast<size_t>(tok) * p.y_stride + r] = __float2half_rn(__uint_as_float(v[j]) * scale);
                         else p.partial[(static_cast<size_t>(blockIdx.z) * p.m + tok) * p.out + r] = __uint_as_float(v[j]);
                     }
                 }
@@ -541,13 +542,13 @@ __global__ void __launch_bounds__(kGemmThreads, 1) tq8_gemm_kernel(const GemmArg
 
 // y = fp16(norm * inv_scale * sum over K splits, in split order) — fixed order, run-to-run identical.
 __global__ void __launch_bounds__(256) gemm_finish_kernel(const float* __restrict__ partial, const float* __restrict__ norms,
-                                                          __half* __restrict__ y, long m, int out, int k_splits,
+                                                          __half* __restrict__ y, long y_stride, long m, int out, int k_splits,
                                                           float inv_scale) {
     const long n = m * out;
     for (long i = static_cast<long>(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += static_cast<long>(gridDim.x) * blockDim.x) {
         float acc = 0.f;
         for (int z = 0; z < k_splits; ++z) acc += partial[static_cast<long>(z) * n + i];
-        y[i] = __float2half_rn(acc * (__ldg(norms + i % out) * inv_scale));
+        y[(i / out) * y_stride + i % out] = __float2half_rn(acc * (__ldg(norms + i % out) * inv_scale));
     }
 }
 
@@ -579,7 +580,9 @@ bool gemm_supported(int in) { return in % kBlockK == 0; }
 
 void launch_tq8_gemm(const uint8_t* codes, const float* norms, const float* table, const __half* x, __half* y, int out,
                      int in, long m, uint32_t block, int n_planes, uint32_t seed_p, uint32_t seed_r, void* scratch,
-                     unsigned int* status, int sm_count, cudaStream_t stream) {
+                     unsigned int* status, int sm_count, cudaStream_t stream, long y_stride) {
+    if (y_stride <= 0) y_stride = out;
+    TQ_REQUIRE(y_stride >= out, "tq8_gemm: output row stride smaller than the layer's rows");
     TQ_REQUIRE(n_planes == 1 || n_planes == 2, "tq8_gemm: one or two rotation planes");
     TQ_REQUIRE(gemm_supported(in), "tq8_gemm: in_features must be a multiple of 64");
     TQ_REQUIRE(is_pow2(block) && block >= 32 && block <= 1024, "WHT block size must be a power of two in [32, 1024]");
@@ -612,7 +615,7 @@ void launch_tq8_gemm(const uint8_t* codes, const float* norms, const float* tabl
     }
     // 2. the GEMM
     GemmArgs a{};
-    a.codes = codes; a.norms = norms; a.table = table; a.xrot = xrot; a.y = y; a.status = status;
+    a.codes = codes; a.norms = norms; a.table = table; a.xrot = xrot; a.y = y; a.y_stride = y_stride; a.status = status;
     a.out = out; a.in = in; a.m = static_cast<int>(m); a.n_planes = n_planes;
     a.inv_scale = 1.0f / std::sqrt(static_cast<float>(in));
     a.k_splits = gemm_k_splits(out, in, m, n_planes, sm_count);
@@ -634,7 +637,7 @@ void launch_tq8_gemm(const uint8_t* codes, const float* norms, const float* tabl
     if (a.k_splits > 1) {
         const long n = m * out;
         const unsigned int blocks = static_cast<unsigned int>(std::min<long>((n + 255) / 256, 148L * 8));
-        gemm_finish_kernel<<<blocks, 256, 0, stream>>>(a.partial, norms, y, m, out, a.k_splits, a.inv_scale);
+        gemm_finish_kernel<<<blocks, 256, 0, stream>>>(a.partial, norms, y, y_stride, m, out, a.k_splits, a.inv_scale);
         TQ_CUDA(cudaGetLastError());
     }
 }

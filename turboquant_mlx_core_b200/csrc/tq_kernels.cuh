@@ -85,9 +85,10 @@ void launch_tq8_gemv_static(const uint8_t* codes, const float* norms, const floa
 bool gemm_supported(int in);
 int gemm_k_splits(int out, int in, long m, int n_planes, int sm_count);
 size_t gemm_scratch_bytes(int out, int in, long m, int n_planes, int sm_count);
+// y_stride: elements between consecutive activation rows of y (0 = out).
 void launch_tq8_gemm(const uint8_t* codes, const float* norms, const float* table, const __half* x, __half* y, int out,
                      int in, long m, uint32_t block, int n_planes, uint32_t seed_p, uint32_t seed_r, void* scratch,
-                     unsigned int* status, int sm_count, cudaStream_t stream);
+                     unsigned int* status, int sm_count, cudaStream_t stream, long y_stride = 0);
 
 // tq_quantize.cu — bit-exact weight quantiser.  derive_seeds hashes the sampled bytes
 // of the fp32 weight (synchronises the stream).  launch_quantize_weight: cb_p / cb_r are

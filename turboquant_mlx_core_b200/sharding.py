@@ -40,6 +40,17 @@ def all_gather_rows(local, out_features: int, world: int):
     spans = [row_range(out_features, r, world) for r in range(world)]
     width = max(e - s for s, e in spans)
     batch = local.shape[0]
+    if all(e - s == width for s, e in spans):
+        # equal shards need no padding: one collective straight into the result (one activation
+        # row), or into [world, batch, width] followed by a single permuting copy
+        out = torch.empty((batch, out_features), dtype=local.dtype, device=local.device)
+        if batch == 1:
+            dist.all_gather_into_tensor(out.view(world, width), local.contiguous().view(1, width))
+            return out
+        flat = torch.empty((world, batch, width), dtype=local.dtype, device=local.device)
+        dist.all_gather_into_tensor(flat.view(world * batch, width), local.contiguous())
+        out.view(batch, world, width).copy_(flat.permute(1, 0, 2))
+        return out
     padded = torch.zeros((batch, width), dtype=local.dtype, device=local.device)
     padded[:, : local.shape[1]] = local
     flat = torch.empty((world * batch, width), dtype=local.dtype, device=local.device)
