@@ -223,25 +223,42 @@ def run_cuda(args):
                 exchange.close()
             exchange, exchange_note = None, "shared buffers could not be mapped on every rank: independent layers, no exchange"
 
+    if exchange is not None:
+        # every fused call below waits for the exchange before it; this one is there for the first
+        with torch.cuda.stream(stream):
+            exchange.broadcast(0, 1, 16, 16, stream=stream)
+
+    fused_gather = os.environ.get("TQ_BENCH_GATHER", "fused") != "split"
+
     def one_pass():
         for i, lin in enumerate(layers):
             if exchange is None:
-                y_ptr = y_dev[i].data_ptr()
+                rc = L.tq_linear_forward(lin.handle, C.c_void_p(x_dev[i].data_ptr()), tq.TQ_F16, 1,
+                                         C.c_void_p(y_dev[i].data_ptr()), sp)
+                if rc:
+                    raise RuntimeError(L.tq_last_error().decode())
+            elif fused_gather:
+                # ONE kernel per layer: wait for the previous layer's gather, GEMV into this rank's rows of
+                # the gathered output, copy them to the peers, raise the flags
+                exchange.forward_allgather(lin, x_dev[i:i + 1], world * OUT_F, rank * OUT_F,
+                                           buffer_offset=(i & 1) * world * OUT_F * 2, wait=True, stream=stream)
             else:
+                # three kernels per layer: wait for the previous gather, GEMV in place, copy + flags
                 off = ((i & 1) * world + rank) * OUT_F * 2
-                y_ptr = exchange.local + off
-            rc = L.tq_linear_forward(lin.handle, C.c_void_p(x_dev[i].data_ptr()), tq.TQ_F16, 1, C.c_void_p(y_ptr), sp)
-            if rc:
-                raise RuntimeError(L.tq_last_error().decode())
-            if exchange is not None:
-                exchange.broadcast(off, 1, OUT_F * 2, OUT_F * 2, stream=stream)
                 exchange.wait(stream=stream)
+                rc = L.tq_linear_forward(lin.handle, C.c_void_p(x_dev[i].data_ptr()), tq.TQ_F16, 1,
+                                         C.c_void_p(exchange.local + off), sp)
+                if rc:
+                    raise RuntimeError(L.tq_last_error().decode())
+                exchange.broadcast(off, 1, OUT_F * 2, OUT_F * 2, stream=stream)
 
     # the launch-bound inner loop is captured once and replayed
     with torch.cuda.stream(stream):
         one_pass()
     stream.synchronize()
-    launch_mode = "CUDA graph of one GEMV per layer" + (" + output all-gather by peer stores and flag wait" if exchange is not None else "")
+    launch_mode = "CUDA graph of one GEMV per layer" + ("" if exchange is None else
+                                                         " fused with the wait for the previous gather, the peer copy of its output and the flags"
+                                                         if fused_gather else " + tq_exchange_wait before and tq_exchange_broadcast after it")
     try:
         if args.no_graph:
             raise RuntimeError("graph disabled by flag")
@@ -319,7 +336,11 @@ def run_cuda(args):
     else:
         # the last two layers' gathered outputs sit in the two buffers: this rank's slots must equal
         # the host path's results, and every rank must hold the same gathered bytes
+        with torch.cuda.stream(stream):
+            exchange.wait(stream=stream)          # the last layer's gather
         exchange.check_status()
+        for lin in layers:
+            lin.check_status()
         gath = exchange.buf.tensor((2, world, OUT_F), torch.float16).clone()
         same = all(bool(torch.equal(gath[i & 1, rank].cpu(), y_host[i])) for i in (nbuf - 2, nbuf - 1))
         # layers differ per rank, so compare every rank's copy of the gathered block with rank 0's
@@ -824,6 +845,24 @@ def bench_lm_head(tq, L, device, stream, rank, world, cbs, args):
                 exchange.broadcast(base + s * 2, batch, rows * 2, vocab * 2, stream=stream)
                 exchange.wait(stream=stream)
 
+            us_f = None
+            if batch <= 8:
+                with torch.cuda.stream(stream):
+                    exchange.broadcast(0, 1, 16, 16, stream=stream)      # something for the first fused call to wait for
+                fstep = [0]
+
+                def call_fused():
+                    half = fstep[0] & 1
+                    fstep[0] += 1
+                    exchange.forward_allgather(lin, x, vocab, s, buffer_offset=half * batch * vocab * 2, wait=True, stream=stream)
+
+                us_f, host_f = timed(call_fused, graph=True)
+                with torch.cuda.stream(stream):
+                    exchange.wait(stream=stream)
+                torch.cuda.synchronize()
+                exchange.check_status()
+                lin.check_status()
+                fused_logits = exchange.buf.tensor((2, batch, vocab), torch.float16).clone()
             us_x, host_x = timed(call_exchange, graph=True)
             exchange.check_status()
             with torch.cuda.stream(stream):
@@ -833,6 +872,15 @@ def bench_lm_head(tq, L, device, stream, rank, world, cbs, args):
             same = bool(torch.equal(full, logits[0])) and bool(torch.equal(full, logits[1]))
             same_t = torch.tensor([1.0 if same else 0.0], device=device)
             dist.all_reduce(same_t, op=dist.ReduceOp.MIN)
+            if us_f is not None:
+                same_f = bool(torch.equal(full, fused_logits[0])) and bool(torch.equal(full, fused_logits[1]))
+                sf = torch.tensor([1.0 if same_f else 0.0], device=device)
+                dist.all_reduce(sf, op=dist.ReduceOp.MIN)
+                res[key + "_fused"] = {"us": us_f, "tok_per_s": batch / (us_f * 1e-6), "gb_per_s_aggregate": algo / (us_f * 1e-6) / 1e9,
+                                       "host_us_per_call_eager": host_f,
+                                       "path": "tq_linear_forward_allgather: one kernel waits for the previous gather, computes the "
+                                               "shard, copies it to the peers and raises the flags (CUDA graph)",
+                                       "identical_to_all_gather_on_every_rank": bool(sf.item() == 1.0)}
             res[key + "_exchange"] = {"us": us_x, "tok_per_s": batch / (us_x * 1e-6), "gb_per_s_aggregate": algo / (us_x * 1e-6) / 1e9,
                                       "host_us_per_call_eager": host_x,
                                       "path": "forward into the shared logits + tq_exchange_broadcast + tq_exchange_wait (CUDA graph)",

@@ -244,6 +244,19 @@ int tq_exchange_sum_f16(const void* slots_fp16, int n_slots, long slot_stride, l
  *  part_stride_out / part_stride_lse elements apart. */
 int tq_exchange_merge_attention(const void* outs_fp16, const void* lses_fp32, int parts, long rows, int head_dim,
                                 long part_stride_out, long part_stride_lse, void* out_fp16, void* stream);
+/** A row-sharded layer's forward fused with the all-gather of its result, for 1..8 activation rows:
+ *  ONE kernel computes this rank's rows into dst[0] (its own buffer; row r of activation row n at
+ *  dst[d][n * dst_row_stride + row_offset + r]), the CTA that finishes last copies the block to
+ *  dst[1..n_dst) with 16-byte peer stores and raises this rank's flag in flags[0..n_flags) (counts as
+ *  one tq_exchange_broadcast of `ex`).  With wait_local_flags != NULL every CTA first waits - for
+ *  at most a second - until the n_wait local flags have reached the exchange's next wait count
+ *  (counts as one tq_exchange_wait): the activation x may then be the result of the previous
+ *  exchange, and a chain of sharded layers runs without any separate exchange kernel.  The first
+ *  fused call of a chain must find an earlier broadcast to wait for, or pass NULL.  Replaces the
+ *  reference's forward (src/linear.cpp:19-28) plus the collective the reference does not have. */
+int tq_linear_forward_allgather(tq_linear_t lin, tq_exchange_t ex, const void* x_fp16_device, int batch, void* const* dst,
+                                int n_dst, long dst_row_stride, long row_offset, void* const* flags, int n_flags,
+                                const void* wait_local_flags, int n_wait, void* stream);
 /** Waits for the device; non-zero if a wait of this exchange gave up. */
 int tq_exchange_status(tq_exchange_t ex);
 void tq_exchange_free(tq_exchange_t ex);

@@ -67,6 +67,52 @@ def test_broadcast_wait_sum_and_merge(tq):
         L.tq_exchange_free(h)
 
 
+def test_forward_fused_with_all_gather(tq, oracle):
+    """tq_linear_forward_allgather with two ranks emulated on one stream: each rank's kernel computes its
+    rows into its own buffer, its last CTA copies them into the other rank's buffer and raises the
+    flags, and the next kernel's CTAs find the previous exchange complete when they wait for it."""
+    torch = pytest.importorskip("torch")
+    L = tq.load()
+    rng = np.random.default_rng(21)
+    cb = oracle.codebook(4)[0]
+    world, rows, cols = 2, 208, 512           # per-rank rows; the gathered layer has world * rows
+    total = world * rows
+    lins = []
+    for r in range(world):
+        w = (rng.standard_normal((rows, cols)) * 0.02).astype(np.float16).astype(np.float32)
+        pp, pr, norms, seeds = oracle.quantize_weight(w, cb, cb, 4, 4, 128, True)
+        lins.append(tq.TurboQuantLinear(cols, rows, tq.QuantizedWeight(pp, pr, norms, seeds), tq.codebook_from_centroids(cb),
+                                        tq.codebook_from_centroids(cb), 128))
+    for batch in (1, 3):
+        nbytes = batch * total * 2
+        bufs = [torch.zeros(nbytes + 256, dtype=torch.uint8, device="cuda") for _ in range(world)]
+        flags = [b.data_ptr() + nbytes for b in bufs]
+        ex = [L.tq_exchange_create(r, world) for r in range(world)]
+        x = torch.from_numpy(rng.standard_normal((batch, cols)).astype(np.float16)).cuda()
+        want = torch.cat([lin.forward(x) for lin in lins], dim=1)
+        for step in range(3):
+            for r in range(world):
+                dst = _ptrs([bufs[r].data_ptr(), bufs[1 - r].data_ptr()])       # own buffer first
+                wait = C.c_void_p(flags[r]) if step > 0 else None             # nothing to wait for before the first exchange
+                rc = L.tq_linear_forward_allgather(lins[r].handle, ex[r], C.c_void_p(x.data_ptr()), batch, dst, world, total, r * rows,
+                                                   _ptrs(flags), world, wait, world, None)
+                assert rc == 0, L.tq_last_error().decode()
+            torch.cuda.synchronize()
+            for r in range(world):
+                got = bufs[r][:nbytes].view(torch.float16).view(batch, total)
+                assert torch.equal(got, want), (batch, step, r)
+                assert bufs[r][nbytes:nbytes + 8].view(torch.int32).tolist() == [step + 1, step + 1]
+            for b in bufs:
+                b[:nbytes].zero_()
+        for r in range(world):
+            assert L.tq_exchange_wait(ex[r], C.c_void_p(flags[r]), world, None) == 0   # the last exchange
+            assert L.tq_exchange_status(ex[r]) == 0
+            lins[r].check_status()
+            L.tq_exchange_free(ex[r])
+    for lin in lins:
+        lin.close()
+
+
 def test_wait_for_a_flag_nobody_raises_gives_up(tq):
     """A rank that never broadcasts: the wait runs out after its limit (about a second) and the
     status says so; the device stays usable."""

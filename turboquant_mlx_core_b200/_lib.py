@@ -91,6 +91,8 @@ def load() -> C.CDLL:
     sig("tq_exchange_wait", i, [vp, vp, i, vp])
     sig("tq_exchange_sum_f16", i, [vp, i, C.c_long, C.c_long, vp, vp])
     sig("tq_exchange_merge_attention", i, [vp, vp, i, C.c_long, i, C.c_long, C.c_long, vp, vp])
+    sig("tq_linear_forward_allgather", i, [vp, vp, vp, i, C.POINTER(C.c_void_p), i, C.c_long, C.c_long, C.POINTER(C.c_void_p), i,
+                                            vp, i, vp])
     sig("tq_exchange_status", i, [vp])
     sig("tq_exchange_free", None, [vp])
     sig("tq_linear_in_features", i, [vp])

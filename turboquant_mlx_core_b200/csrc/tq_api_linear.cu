@@ -212,6 +212,31 @@ public:
         launch_forward(static_cast<const __half*>(x), batch, static_cast<__half*>(y), st, y_stride);
     }
 
+    // Fused all-gather for a row-sharded layer at decode batch sizes (see GemvGather).
+    void forward_allgather(const void* x, int batch, void* const* dst, int n_dst, long dst_stride, long row_offset,
+                           void* const* flags, int n_flags, int slot, unsigned int* epoch, const void* wait_flags, int n_wait,
+                           unsigned int* wait_epoch, cudaStream_t st) {
+        TQ_REQUIRE(x && dst && flags, "forward_allgather: NULL argument");
+        TQ_REQUIRE(batch >= 1 && batch <= 8, "forward_allgather: batch must be 1..8");
+        TQ_REQUIRE(n_dst >= 1 && n_dst <= 8 && n_flags >= 1 && n_flags <= 8, "forward_allgather: 1..8 destinations and flag arrays");
+        TQ_REQUIRE(row_offset >= 0 && row_offset + out_ <= dst_stride,
+                   "forward_allgather: rows [row_offset, row_offset + out) must fit the destination row stride");
+        TQ_REQUIRE(slot >= 0 && slot < 32, "forward_allgather: flag slot must be 0..31");
+        TQ_REQUIRE(tq::is_device_pointer(x), "forward_allgather: x must be a device pointer");
+        TQ_CUDA(cudaSetDevice(device_));
+        __half* d[8];
+        for (int i = 0; i < n_dst; ++i) {
+            TQ_REQUIRE(dst[i] != nullptr, "forward_allgather: NULL destination");
+            d[i] = static_cast<__half*>(dst[i]) + row_offset;
+        }
+        unsigned int* sig[8];
+        for (int i = 0; i < n_flags; ++i) sig[i] = static_cast<unsigned int*>(flags[i]);
+        tq::GemvGather g{epoch, static_cast<const unsigned int*>(wait_flags), wait_flags ? n_wait : 0, wait_epoch};
+        tq::launch_tq8_gemv_scatter(codes_.as<uint8_t>(), norms_.as<float>(), tables_.as<float>(), static_cast<const __half*>(x), d,
+                                    n_dst, dst_stride, out_, in_, batch, block_, dual_ ? 2 : 1, seed_p_, seed_r_, scratch_.as<void>(),
+                                    d_status_, sm_count_, st, sig, slot, 0u, counter_.as<unsigned int>(), &g, n_flags);
+    }
+
     void wait_peers(const void* flags, int n, unsigned int value, cudaStream_t st) {
         TQ_CUDA(cudaSetDevice(device_));
         tq::launch_peer_wait(static_cast<const unsigned int*>(flags), n, value, d_status_, st);
@@ -455,6 +480,23 @@ int tq_linear_forward_scatter_signal(tq_linear_t lin, const void* x_fp16_device,
         TQ_REQUIRE(signal != nullptr, "tq_linear_forward_scatter_signal: NULL signal list");
         lin->impl->forward_scatter(x_fp16_device, batch, dst, n_dst, dst_row_stride, row_offset,
                                    static_cast<cudaStream_t>(stream), signal, signal_slot, signal_value);
+        return 0;
+    });
+}
+
+// (tq_exchange_s is defined in tq_api_peer.cu; only its counters are needed here)
+extern "C" unsigned int* tq_exchange_words(tq_exchange_t ex, int* rank);
+
+int tq_linear_forward_allgather(tq_linear_t lin, tq_exchange_t ex, const void* x_fp16_device, int batch, void* const* dst,
+                                int n_dst, long dst_row_stride, long row_offset, void* const* flags, int n_flags,
+                                const void* wait_local_flags, int n_wait, void* stream) {
+    return guarded<int>(0, -1, [&]() {
+        TQ_REQUIRE(lin && lin->impl, "tq_linear_forward_allgather: NULL handle");
+        TQ_REQUIRE(ex != nullptr, "tq_linear_forward_allgather: NULL exchange");
+        int rank = 0;
+        unsigned int* w = tq_exchange_words(ex, &rank);
+        lin->impl->forward_allgather(x_fp16_device, batch, dst, n_dst, dst_row_stride, row_offset, flags, n_flags, rank, w + 1,
+                                     wait_local_flags, n_wait, w + 2, static_cast<cudaStream_t>(stream));
         return 0;
     });
 }

@@ -97,4 +97,11 @@ int tq_exchange_status(tq_exchange_t ex) {
 
 void tq_exchange_free(tq_exchange_t ex) { delete ex; }
 
+// The exchange's device counters for the fused kernels of tq_api_linear.cu:
+// [0] CTAs finished, [1] broadcasts completed, [2] waits started.
+unsigned int* tq_exchange_words(tq_exchange_t ex, int* rank) {
+    if (rank) *rank = ex->rank;
+    return ex->words.as<unsigned int>();
+}
+
 }  // extern "C"

@@ -156,6 +156,16 @@ struct ScatterArgs {
     int n_signal, signal_slot;
     unsigned int signal_value;
     unsigned int* done_counter;
+    // Fused all-gather (bulk != 0): results are stored locally only; the CTA that completes the grid
+    // copies the whole block to the peers with 16-byte stores and then raises the flags with the value
+    // ++(*epoch) (signal_value is not used).  With n_wait > 0 every CTA first waits - bounded - until
+    // wait_flags[0..n_wait) have reached *wait_epoch + 1 before it reads the activation (the previous
+    // exchange has arrived); the completing CTA then advances *wait_epoch.
+    int bulk;
+    unsigned int* epoch;
+    const unsigned int* wait_flags;
+    int n_wait;
+    unsigned int* wait_epoch;
 };
 
 // One output element goes to the caller's buffer and, when the call scatters, to the same
@@ -168,9 +178,11 @@ __device__ __forceinline__ void store_y(const GemvArgs& p, const ScatterArgs& sc
     if constexpr (SCATTER) {
         const size_t o = static_cast<size_t>(n) * sc.y_stride + row;
         p.y[o] = h;
+        if (!sc.bulk) {
 #pragma unroll
-        for (int d = 0; d < 7; ++d)
-            if (d < sc.n_peer) sc.y_peer[d][o] = h;
+            for (int d = 0; d < 7; ++d)
+                if (d < sc.n_peer) sc.y_peer[d][o] = h;
+        }
     } else {
         p.y[static_cast<size_t>(n) * p.out + row] = h;
     }
@@ -364,6 +376,25 @@ __device__ __forceinline__ void gemv_body(const GemvArgs& p, const ScatterArgs& 
 
     // Everything below reads or writes data the preceding kernels produce or still use.
     grid_dependency_sync();
+    if constexpr (SCATTER) {
+        if (sargs.n_wait > 0) {
+            // the activation comes out of an exchange: wait until every rank's part has arrived
+            if (tid < sargs.n_wait) {
+                const unsigned int want = *reinterpret_cast<volatile unsigned int*>(sargs.wait_epoch) + 1u;
+                const unsigned long long t0 = global_timer_ns();
+                for (unsigned int spin = 0;; ++spin) {
+                    unsigned int v;
+                    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(sargs.wait_flags + tid) : "memory");
+                    if (static_cast<int>(v - want) >= 0) break;
+                    if ((spin & 255u) == 255u && global_timer_ns() - t0 > 5ull * kWaitLimitNs) {   // 1 s: a peer is gone
+                        raise_status(p.status, 10u);
+                        break;
+                    }
+                }
+            }
+            __syncthreads();
+        }
+    }
     uint4 x_first = make_uint4(0, 0, 0, 0);
     if (p.x != nullptr) {
         const int cl0 = (cur.slot - staged_plane * p.n_chunks) * kChunk + slice0 + 8 * lane;
@@ -652,17 +683,56 @@ __device__ __forceinline__ void gemv_body(const GemvArgs& p, const ScatterArgs& 
     // with acquire semantics sees all of this launch's results.
     if constexpr (SCATTER) {
     if (sargs.n_signal > 0) {
-        __threadfence_system();
+        __shared__ unsigned int s_last;
+        // results that went to other GPUs need a system-scope fence; with the bulk copy every CTA's
+        // results are local and only the copying CTA pays for one
+        if (sargs.bulk) __threadfence();
+        else __threadfence_system();
         __syncthreads();
         if (tid == 0) {
             const unsigned int prev = atomicAdd(sargs.done_counter, 1u);
-            if (prev == gridDim.x - 1) {
+            s_last = (prev == gridDim.x - 1) ? 1u : 0u;
+        }
+        __syncthreads();
+        if (s_last) {
+            __threadfence();
+            if (sargs.bulk && sargs.n_peer > 0) {
+                // the whole block (batch rows of `out` halves, y_stride apart) to every peer: 16-byte
+                // pieces where the rows allow it
+                const bool vec = (p.out % 8 == 0) && (sargs.y_stride % 8 == 0) && (reinterpret_cast<uintptr_t>(p.y) % 16 == 0);
+                if (vec) {
+                    const int per_row = p.out / 8;
+                    for (int i = tid; i < per_row * p.batch; i += kCtaThreads) {
+                        const int n = i / per_row, c = i - n * per_row;
+                        const size_t o = static_cast<size_t>(n) * sargs.y_stride + static_cast<size_t>(c) * 8;
+                        const uint4 v = __ldcg(reinterpret_cast<const uint4*>(p.y + o));
+#pragma unroll
+                        for (int d = 0; d < 7; ++d)
+                            if (d < sargs.n_peer) *reinterpret_cast<uint4*>(sargs.y_peer[d] + o) = v;
+                    }
+                } else {
+                    for (int i = tid; i < p.out * p.batch; i += kCtaThreads) {
+                        const int n = i / p.out, c = i - n * p.out;
+                        const size_t o = static_cast<size_t>(n) * sargs.y_stride + c;
+                        const __half v = __ldcg(p.y + o);
+#pragma unroll
+                        for (int d = 0; d < 7; ++d)
+                            if (d < sargs.n_peer) sargs.y_peer[d][o] = v;
+                    }
+                }
+                __threadfence_system();
+                __syncthreads();
+            }
+            if (tid == 0) {
                 *sargs.done_counter = 0u;  // ready for the next launch (stream order)
+                unsigned int value = sargs.signal_value;
+                if (sargs.bulk) value = atomicAdd(sargs.epoch, 1u) + 1u;
+                if (sargs.n_wait > 0) atomicAdd(sargs.wait_epoch, 1u);   // every CTA has read it by now
                 __threadfence_system();
 #pragma unroll
                 for (int d = 0; d < 8; ++d)
                     if (d < sargs.n_signal)
-                        asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(sargs.signal[d] + sargs.signal_slot), "r"(sargs.signal_value) : "memory");
+                        asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(sargs.signal[d] + sargs.signal_slot), "r"(value) : "memory");
             }
         }
     }
@@ -736,7 +806,7 @@ void launch_tq8_gemv_scatter(const uint8_t* codes, const float* norms, const flo
                              __half* const* dst, int n_dst, long dst_stride, int out, int in, int batch, uint32_t block,
                              int n_planes, uint32_t seed_p, uint32_t seed_r, void* scratch, unsigned int* status,
                              int sm_count, cudaStream_t stream, unsigned int* const* signal, int signal_slot,
-                             unsigned int signal_value, unsigned int* done_counter) {
+                             unsigned int signal_value, unsigned int* done_counter, const GemvGather* gather, int n_signal) {
     TQ_REQUIRE(dst != nullptr && n_dst >= 1 && n_dst <= 8, "tq8_gemv: 1..8 destinations");
     TQ_REQUIRE(dst_stride >= out, "tq8_gemv: destination row stride smaller than the layer's rows");
     __half* y = dst[0];
@@ -758,8 +828,9 @@ void launch_tq8_gemv_scatter(const uint8_t* codes, const float* norms, const flo
     sa.y_stride = dst_stride;
     sa.n_signal = 0;
     if (signal != nullptr) {
-        sa.n_signal = n_dst;
-        for (int d = 0; d < n_dst; ++d) {
+        sa.n_signal = n_signal > 0 ? n_signal : n_dst;
+        TQ_REQUIRE(sa.n_signal <= 8, "tq8_gemv: at most 8 flag arrays");
+        for (int d = 0; d < sa.n_signal; ++d) {
             TQ_REQUIRE(signal[d] != nullptr, "tq8_gemv: NULL signal array");
             sa.signal[d] = signal[d];
         }
@@ -767,6 +838,17 @@ void launch_tq8_gemv_scatter(const uint8_t* codes, const float* norms, const flo
         sa.signal_value = signal_value;
         TQ_REQUIRE(done_counter != nullptr, "tq8_gemv: signalling needs a completion counter in device memory");
         sa.done_counter = done_counter;
+    }
+    if (gather != nullptr) {
+        TQ_REQUIRE(signal != nullptr && gather->epoch != nullptr, "tq8_gemv: the fused all-gather needs flags and an epoch counter");
+        TQ_REQUIRE(gather->n_wait >= 0 && gather->n_wait <= 32, "tq8_gemv: 0..32 flags to wait for");
+        TQ_REQUIRE(gather->n_wait == 0 || (gather->wait_flags != nullptr && gather->wait_epoch != nullptr),
+                   "tq8_gemv: waiting needs the local flag array and the wait counter");
+        sa.bulk = 1;
+        sa.epoch = gather->epoch;
+        sa.wait_flags = gather->wait_flags;
+        sa.n_wait = gather->n_wait;
+        sa.wait_epoch = gather->wait_epoch;
     }
     a.out = out; a.in = in; a.batch = batch;
     const int n_row_tiles = (out + 15) / 16;

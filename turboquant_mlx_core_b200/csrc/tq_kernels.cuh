@@ -40,11 +40,23 @@ void launch_tq8_gemv(const uint8_t* codes, const float* norms, const float* tabl
 // The same with the fp16 result written to n_dst (1..8) buffers at once: destination d receives
 // activation row n, output row r at dst[d][n * dst_stride + r].  Destinations may be other GPUs'
 // memory mapped into this process (peer access / CUDA IPC): plain stores, no multicast.
+// Fused all-gather of a row-sharded layer (gather != nullptr): the results are stored into dst[0]
+// only; the CTA that completes the grid copies the block to dst[1..n_dst) with 16-byte stores and
+// raises flag `signal_slot` of signal[0..n_signal) with the value ++(*epoch).  With n_wait > 0 every
+// CTA waits (bounded) for wait_flags[0..n_wait) to reach *wait_epoch + 1 before it reads x, and the
+// completing CTA advances *wait_epoch: a chain of such layers needs no separate exchange kernel.
+struct GemvGather {
+    unsigned int* epoch;
+    const unsigned int* wait_flags;
+    int n_wait;
+    unsigned int* wait_epoch;
+};
 void launch_tq8_gemv_scatter(const uint8_t* codes, const float* norms, const float* table, const __half* x,
                              __half* const* dst, int n_dst, long dst_stride, int out, int in, int batch, uint32_t block,
                              int n_planes, uint32_t seed_p, uint32_t seed_r, void* scratch, unsigned int* status,
                              int sm_count, cudaStream_t stream, unsigned int* const* signal = nullptr, int signal_slot = 0,
-                             unsigned int signal_value = 0, unsigned int* done_counter = nullptr);
+                             unsigned int signal_value = 0, unsigned int* done_counter = nullptr,
+                             const GemvGather* gather = nullptr, int n_signal = 0);
 // With `signal` (one flag array per destination): once the whole grid has stored its results,
 // signal[d][signal_slot] = signal_value on every destination (release, system scope); `done_counter`
 // must be a zero-initialised word in device memory (grid completion counter).  `status` may be

@@ -237,6 +237,24 @@ class Exchange:
                                                   stride_bytes, stride_bytes, self._flags, self.world, _stream_ptr(stream)),
                    "tq_exchange_broadcast")
 
+    def forward_allgather(self, lin, x, dst_row_stride: int, row_offset: int, buffer_offset: int = 0, wait: bool = True,
+                          stream=None):
+        """A row-sharded layer's decode forward fused with the all-gather of its result
+        (tq_linear_forward_allgather): this rank's rows go to its own buffer at byte `buffer_offset`
+        (+ row_offset elements), the kernel's last CTA copies them to the same place of every other
+        rank's buffer and raises this rank's flag; with wait=True every CTA first waits for the
+        previous exchange (counts as one wait())."""
+        import ctypes as C
+        import numpy as np
+        from . import _lib
+        from .api import _ptr
+        batch = int(np.prod(x.shape[:-1])) if len(x.shape) > 1 else 1
+        dst = (C.c_void_p * self.world)(*[p + buffer_offset for p in self.buf.ptrs])
+        _lib.check(self._L.tq_linear_forward_allgather(lin.handle, self._h, _ptr(x), batch, dst, self.world, int(dst_row_stride),
+                                                        int(row_offset), self._flags, self.world,
+                                                        C.c_void_p(self.buf.local_flags) if wait else None, self.world,
+                                                        _stream_ptr(stream)), "tq_linear_forward_allgather")
+
     def wait(self, stream=None):
         import ctypes as C
         from . import _lib
