@@ -388,7 +388,7 @@ def run_cuda(args):
 
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         line["cpu_baseline"] = cpu_baseline(qw0, cbs, x_host[0].numpy(), y_dev[0].cpu().numpy(), budget_s=12.0)
-    legs = set(args.legs.split(",")) if args.legs else {"attention", "decoder_layer", "prefill", "lm_head", "side_kernels"}
+    legs = set(args.legs.split(",")) if args.legs else {"attention", "decoder_layer", "prefill", "lm_head", "side_kernels", "c4_decode_step"}
     if args.no_extras:
         legs = set()
     if "attention" in legs:
@@ -419,6 +419,11 @@ def run_cuda(args):
             line["lm_head"] = bench_lm_head(tq, L, device, stream, rank, world, cbs, args)
         except Exception as e:
             line["lm_head"] = {"error": str(e)}
+    if "c4_decode_step" in legs:
+        try:
+            line["c4_decode_step"] = bench_c4_decode_step(tq, L, device, stream, rank, world, cbs, args)
+        except Exception as e:
+            line["c4_decode_step"] = {"error": str(e)}
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
@@ -890,6 +895,235 @@ def bench_lm_head(tq, L, device, stream, rank, world, cbs, args):
     if exchange is not None:
         exchange.close()
     lin.close()
+    return res
+
+
+# ---- secondary: tensor-parallel decode step of a Qwen2.5-32B-shaped layer -------------------------------
+
+def bench_c4_decode_step(tq, L, device, stream, rank, world, cbs, args):
+    """One decoder layer per step, Qwen2.5-32B shapes (hidden 5120, intermediate 27648, 40 query / 8 KV
+    heads of 128, context 8192), tensor-parallel over the ranks as the sharded paths prescribe:
+    q / k / v / gate-up split by output rows (no exchange), o_proj and down_proj split by input columns
+    on WHT-block boundaries, their partial outputs exchanged by peer stores and added in rank order
+    (tq_exchange_broadcast / _wait / _sum_f16: the all-reduce), KV heads split for the compressed cache
+    and the decode attention; RMSNorm, rotary embedding, SwiGLU and the residual adds run as this
+    library's small kernels.  TQ8 (4+4 bit, block 128) weights with random codes for every layer (the
+    model's first and last four layers would stay fp16), one token appended per sequence per step.  The
+    whole step is one CUDA graph; enough distinct layers are cycled that the weights come from HBM.
+    Also checks a small row-parallel linear against the unsharded layer (1e-3) and across ranks (bits)."""
+    import torch
+    import torch.distributed as dist
+    from turboquant_mlx_core_b200.sharding import Exchange, col_range, shard_quantized_cols
+    hidden, inter, q_heads, kv_heads, dim, ctx, n_model_layers = 5120, 27648, 40, 8, 128, 8192, 64
+    if kv_heads % world:
+        return {"skipped": f"{world} ranks do not divide {kv_heads} KV heads"}
+    qh, kvh, il = q_heads // world, kv_heads // world, inter // world
+    sp = C.c_void_p(stream.cuda_stream)
+    res = {"workload": f"Qwen2.5-32B-shaped decoder layer, TQ8, tensor-parallel over {world} GPU(s), context {ctx}, 3.5-bit KV cache"}
+    cp, cr = cbs[0].centroids.astype(np.float32), cbs[1].centroids.astype(np.float32)
+    g = torch.Generator(device=device).manual_seed(900 + rank)
+    handles = []
+
+    def rand_linear(rows, cols, seed):
+        pp = torch.randint(0, 256, (rows, cols // 2), generator=g, device=device, dtype=torch.uint8)
+        pr = torch.randint(0, 256, (rows, cols // 2), generator=g, device=device, dtype=torch.uint8)
+        norms = torch.ones(rows, device=device, dtype=torch.float32)
+        seeds = np.array([seed, 0, BLOCK], np.uint32)
+        h = L.tq_linear_create(cols, rows, C.c_void_p(pp.data_ptr()), cols // 2, C.c_void_p(pr.data_ptr()), C.c_void_p(norms.data_ptr()),
+                               seeds.ctypes.data, cp.ctypes.data, cp.size, cr.ctypes.data, cr.size, BLOCK)
+        if not h:
+            raise RuntimeError(L.tq_last_error().decode())
+        handles.append(h)
+        return h
+
+    def fwd(h, x, batch, y):
+        if L.tq_linear_forward(h, C.c_void_p(x), tq.TQ_F16, batch, C.c_void_p(y), sp):
+            raise RuntimeError(L.tq_last_error().decode())
+
+    def chk(rc):
+        if rc:
+            raise RuntimeError(L.tq_last_error().decode())
+
+    bytes_per_layer = ((qh + 2 * kvh) * dim * hidden + hidden * qh * dim + 2 * il * hidden + hidden * il)
+    n_layers = max(2, -(-300_000_000 // bytes_per_layer))
+    layers = []
+    for li in range(n_layers):
+        layers.append({"q": rand_linear(qh * dim, hidden, 10 * li + 1), "k": rand_linear(kvh * dim, hidden, 10 * li + 2),
+                       "v": rand_linear(kvh * dim, hidden, 10 * li + 3), "o": rand_linear(hidden, qh * dim, 10 * li + 4),
+                       "gu": rand_linear(2 * il, hidden, 10 * li + 5), "down": rand_linear(hidden, il, 10 * li + 6),
+                       "n1": torch.ones(hidden, device=device, dtype=torch.float16),
+                       "n2": torch.ones(hidden, device=device, dtype=torch.float16)})
+
+    exchange = None
+    if world > 1:
+        err = None
+        try:
+            exchange = Exchange(2 * world * 32 * hidden * 2)
+        except Exception as exc:
+            err = str(exc)
+        ok_t = torch.tensor([0.0 if err else 1.0], device=device)
+        dist.all_reduce(ok_t, op=dist.ReduceOp.MIN)
+        if ok_t.item() != 1.0:
+            if exchange is not None:
+                exchange.close()
+            for h in handles:
+                L.tq_linear_free(h)
+            return {"skipped": "shared buffers could not be mapped on every rank", "local_error": err}
+
+    for batch in (1, 32):
+        caches = [tq.TQKVCache(n_layers, kvh, dim) for _ in range(batch)]
+        for c in caches:
+            for li in range(n_layers):
+                c.reserve(li, ctx + 16)
+                kk = torch.randn((ctx, kvh, dim), generator=g, device=device).half()
+                c.append(li, kk, kk)
+        arr = (C.c_void_p * batch)(*[c.handle for c in caches])
+        x = torch.randn((batch, hidden), generator=g, device=device).half() * 0.1
+        x0 = x.clone()
+        h1 = torch.empty_like(x)
+        q = torch.empty((batch, qh, dim), device=device, dtype=torch.float16)
+        k = torch.empty((batch, kvh, dim), device=device, dtype=torch.float16)
+        v = torch.empty_like(k)
+        attn = torch.empty_like(q)
+        part = torch.empty((batch, hidden), device=device, dtype=torch.float16)   # world == 1: the "exchange" is local
+        x1 = torch.empty_like(x)
+        gu = torch.empty((batch, 2 * il), device=device, dtype=torch.float16)
+        act = torch.empty((batch, il), device=device, dtype=torch.float16)
+        pos = torch.full((batch,), ctx, device=device, dtype=torch.int32)
+        count = batch * hidden
+        toggle = [0]
+
+        def all_reduce_add(partial_of, residual, out):
+            """partial_of(ptr) writes this rank's partial [batch, hidden] at ptr; out = residual + sum over ranks."""
+            if exchange is None:
+                partial_of(part.data_ptr())
+                chk(L.tq_exchange_sum_f16(C.c_void_p(part.data_ptr()), 1, count, count, C.c_void_p(residual.data_ptr()),
+                                          C.c_void_p(out.data_ptr()), sp))
+                return
+            base = (toggle[0] & 1) * world * count * 2
+            toggle[0] += 1
+            partial_of(exchange.local + base + rank * count * 2)
+            exchange.broadcast(base + rank * count * 2, 1, count * 2, count * 2, stream=stream)
+            exchange.wait(stream=stream)
+            exchange.sum_f16(base, world, count, count, out.data_ptr(), residual_ptr=residual.data_ptr(), stream=stream)
+
+        def layer_step(li):
+            w = layers[li]
+            chk(L.tq_rmsnorm_f16(C.c_void_p(x.data_ptr()), C.c_void_p(w["n1"].data_ptr()), C.c_void_p(h1.data_ptr()), batch, hidden, 1e-6, sp))
+            fwd(w["q"], h1.data_ptr(), batch, q.data_ptr())
+            fwd(w["k"], h1.data_ptr(), batch, k.data_ptr())
+            fwd(w["v"], h1.data_ptr(), batch, v.data_ptr())
+            chk(L.tq_rope_f16(C.c_void_p(q.data_ptr()), C.c_void_p(pos.data_ptr()), batch, qh, dim, 1e6, sp))
+            chk(L.tq_rope_f16(C.c_void_p(k.data_ptr()), C.c_void_p(pos.data_ptr()), batch, kvh, dim, 1e6, sp))
+            chk(L.tq_kv_append_batch(arr, batch, li, C.c_void_p(k.data_ptr()), C.c_void_p(v.data_ptr()), tq.TQ_F16, sp))
+            chk(L.tq_kv_attention(arr, batch, li, C.c_void_p(q.data_ptr()), tq.TQ_F16, qh, C.c_void_p(attn.data_ptr()), 0, ctx, 1, sp))
+            all_reduce_add(lambda ptr: fwd(w["o"], attn.data_ptr(), batch, ptr), x, x1)
+            chk(L.tq_rmsnorm_f16(C.c_void_p(x1.data_ptr()), C.c_void_p(w["n2"].data_ptr()), C.c_void_p(h1.data_ptr()), batch, hidden, 1e-6, sp))
+            fwd(w["gu"], h1.data_ptr(), batch, gu.data_ptr())
+            chk(L.tq_swiglu_f16(C.c_void_p(gu.data_ptr()), C.c_void_p(act.data_ptr()), batch, il, sp))
+            all_reduce_add(lambda ptr: fwd(w["down"], act.data_ptr(), batch, ptr), x1, x)
+
+        def one_pass():
+            for li in range(n_layers):
+                layer_step(li)
+
+        with torch.cuda.stream(stream):
+            one_pass()                     # allocates scratch, uploads attention descriptors per layer
+            x.copy_(x0)
+            one_pass()
+        torch.cuda.synchronize()
+        # the cache grew by two tokens per layer during the eager passes; the captured step re-appends
+        # at a fixed position and attends to [0, ctx), so its descriptors repeat the eager call's
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.stream(stream):
+            x.copy_(x0)
+        with torch.cuda.graph(graph, stream=stream):
+            one_pass()
+        with torch.cuda.stream(stream):
+            for _ in range(2):
+                graph.replay()
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        reps = 5
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        with torch.cuda.stream(stream):
+            e0.record(stream)
+            for _ in range(reps):
+                graph.replay()
+            e1.record(stream)
+        torch.cuda.synchronize()
+        t = torch.tensor([e0.elapsed_time(e1) * 1e3 / (reps * n_layers)], device=device, dtype=torch.float64)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        us = float(t.item())
+        # the residual stream must be finite and identical on every rank (fixed-order sums)
+        finite = bool(torch.isfinite(x.float()).all())
+        same = True
+        if world > 1:
+            ref = x.clone()
+            dist.broadcast(ref, src=0)
+            ok = torch.tensor([1.0 if torch.equal(ref, x) else 0.0], device=device)
+            dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+            same = bool(ok.item() == 1.0)
+            exchange.check_status()
+        weight_bytes = bytes_per_layer
+        kv_bytes = batch * kvh * ctx * 118
+        res[f"b{batch}"] = {"us_per_layer": us, "tok_per_s_64_layers": batch / (us * 1e-6 * n_model_layers),
+                            "gb_per_s_per_gpu": (weight_bytes + kv_bytes) / (us * 1e-6) / 1e9,
+                            "bytes_per_layer_per_gpu": weight_bytes + kv_bytes, "distinct_layers_cycled": n_layers,
+                            "kernels_per_layer": "rmsnorm, q, k, v, rope x2, kv append x2, attention, o_proj, [copy to peers, wait,] "
+                                                 "sum + residual, rmsnorm, gate-up, swiglu, down, [copy to peers, wait,] sum + residual",
+                            "residual_stream_finite": finite, "identical_on_every_rank": same}
+        for c in caches:
+            c.close()
+
+    # ---- row-parallel linear against the unsharded layer (small, real quantised weights) ----
+    try:
+        rows, cols, batch = 512, 2048, 3
+        gq = torch.Generator(device=device).manual_seed(4242)            # the same on every rank
+        wfull = (torch.randn((rows, cols), generator=gq, device=device) * 0.02).half().float()
+        qwf = tq.quantize_weight(wfull, cbs[0], cbs[1], tq.QuantizerConfig(4, 4, BLOCK, True))
+        full = tq.TurboQuantLinear(cols, rows, qwf, cbs[0], cbs[1], BLOCK)
+        xs = torch.randn((batch, cols), generator=gq, device=device).half()
+        want = full.forward(xs)
+        pp, pr, nrm, (c0, c1) = shard_quantized_cols(qwf.packed_primary, qwf.packed_residual, qwf.norms, cols, BLOCK, rank, world)
+        shard = tq.TurboQuantLinear(c1 - c0, rows, tq.QuantizedWeight(np.ascontiguousarray(pp), np.ascontiguousarray(pr), nrm, qwf.seeds),
+                                    cbs[0], cbs[1], BLOCK)
+        xl = xs[:, c0:c1].contiguous()
+        got = torch.empty((batch, rows), device=device, dtype=torch.float16)
+        cnt = batch * rows
+        with torch.cuda.stream(stream):
+            if exchange is None:
+                tmp = shard.forward(xl, stream=stream)
+                chk(L.tq_exchange_sum_f16(C.c_void_p(tmp.data_ptr()), 1, cnt, cnt, None, C.c_void_p(got.data_ptr()), sp))
+            else:
+                base = (toggle[0] & 1) * world * 32 * hidden * 2
+                toggle[0] += 1
+                off = base + rank * cnt * 2
+                fwd(shard.handle, xl.data_ptr(), batch, exchange.local + off)
+                exchange.broadcast(off, 1, cnt * 2, cnt * 2, stream=stream)
+                exchange.wait(stream=stream)
+                exchange.sum_f16(base, world, cnt, cnt, got.data_ptr(), stream=stream)
+        torch.cuda.synchronize()
+        rel = float((got.float() - want.float()).norm() / want.float().norm())
+        same = True
+        if world > 1:
+            ref = got.clone()
+            dist.broadcast(ref, src=0)
+            ok = torch.tensor([1.0 if torch.equal(ref, got) else 0.0], device=device)
+            dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+            same = bool(ok.item() == 1.0)
+        res["row_parallel_check"] = {"shape": f"{rows}x{cols}, batch {batch}, columns split over {world} rank(s) on WHT-block boundaries",
+                                     "rel_l2_vs_unsharded_layer": rel, "within_1e-3": rel < 1e-3, "identical_on_every_rank": same}
+        full.close()
+        shard.close()
+    except Exception as exc:
+        res["row_parallel_check"] = {"error": str(exc)}
+    if exchange is not None:
+        exchange.close()
+    for h in handles:
+        L.tq_linear_free(h)
     return res
 
 

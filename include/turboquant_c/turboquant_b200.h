@@ -236,9 +236,11 @@ tq_exchange_t tq_exchange_create(int rank, int world);
 int tq_exchange_broadcast(tq_exchange_t ex, const void* src, void* const* dst, int n_dst, int rows, long row_bytes,
                           long src_stride_bytes, long dst_stride_bytes, void* const* flags, int n_flags, void* stream);
 int tq_exchange_wait(tq_exchange_t ex, const void* local_flags, int n_flags, void* stream);
-/** out[i] = fp16( sum over s = 0..n_slots-1, in that order, of slots[s * slot_stride + i] ), fp32
- *  accumulate: every rank adds the same values in the same order and gets the same bits. */
-int tq_exchange_sum_f16(const void* slots_fp16, int n_slots, long slot_stride, long count, void* out_fp16, void* stream);
+/** out[i] = fp16( residual[i] + sum over s = 0..n_slots-1, in that order, of slots[s * slot_stride + i] ),
+ *  fp32 accumulate (residual_fp16 may be NULL): every rank adds the same values in the same order
+ *  and gets the same bits. */
+int tq_exchange_sum_f16(const void* slots_fp16, int n_slots, long slot_stride, long count, const void* residual_fp16,
+                        void* out_fp16, void* stream);
 /** Attention over the union of disjoint token ranges from each range's output and log-sum-exp
  *  (tq_kv_attention_lse): outs [parts][rows][head_dim] fp16, lses [parts][rows] fp32, parts
  *  part_stride_out / part_stride_lse elements apart. */
@@ -257,6 +259,17 @@ int tq_exchange_merge_attention(const void* outs_fp16, const void* lses_fp32, in
 int tq_linear_forward_allgather(tq_linear_t lin, tq_exchange_t ex, const void* x_fp16_device, int batch, void* const* dst,
                                 int n_dst, long dst_row_stride, long row_offset, void* const* flags, int n_flags,
                                 const void* wait_local_flags, int n_wait, void* stream);
+/* Element-wise glue of a decoder layer, device fp16 in and out, fp32 arithmetic.  The reference
+ * leaves these to MLX in the host application (no file of its own computes them); they are here so
+ * that a whole tensor-parallel decode step runs on this library's stream without a framework.
+ *   tq_rmsnorm_f16: y[r,:] = x[r,:] * rsqrt(mean(x[r,:]^2) + eps) * weight
+ *   tq_rope_f16   : in place on x [rows, heads, head_dim]; element i pairs with i + head_dim/2,
+ *                   angle = positions[row] * theta^(-2i/head_dim)
+ *   tq_swiglu_f16 : act[r,j] = silu(gate_up[r,j]) * gate_up[r, intermediate + j] */
+int tq_rmsnorm_f16(const void* x_fp16, const void* weight_fp16, void* y_fp16, long rows, int cols, float eps, void* stream);
+int tq_rope_f16(void* x_fp16, const int* positions, long rows, int heads, int head_dim, float theta, void* stream);
+int tq_swiglu_f16(const void* gate_up_fp16, void* act_fp16, long rows, int intermediate, void* stream);
+
 /** Waits for the device; non-zero if a wait of this exchange gave up. */
 int tq_exchange_status(tq_exchange_t ex);
 void tq_exchange_free(tq_exchange_t ex);
@@ -349,9 +362,11 @@ int tq_kv_append_batch(const tq_kv_cache_t* caches, int n_seqs, int layer, const
  *  meaning "all tokens of that cache"; q_heads a multiple of the cache's heads
  *  (grouped-query attention).  use_qjl != 0 adds the 1-bit residual correction to the
  *  key scores (an extension: the reference stores those bits but never reads them).
- *  The call copies a table of per-sequence descriptors from host memory on every invocation and
- *  keeps its staging buffers in caches[0]: do not capture it in a CUDA graph, and issue the calls
- *  that share a first cache on one stream. */
+ *  The call keeps a table of per-sequence descriptors and its staging buffers in caches[0]: issue
+ *  the calls that share a first cache on one stream.  The table is uploaded (from pageable host
+ *  memory) only when it changed - another set of caches, ranges or token counts; a call that
+ *  repeats the previous descriptors enqueues kernels only and can be captured in a CUDA graph
+ *  (run the same call once before the capture; do not capture a call whose descriptors change). */
 int tq_kv_attention(const tq_kv_cache_t* caches, int n_seqs, int layer, const void* queries, int q_dtype,
                     int q_heads, void* out_fp16, int start, int end, int use_qjl, void* stream);
 

@@ -43,7 +43,7 @@ def test_broadcast_wait_sum_and_merge(tq):
         for r in range(world):
             assert L.tq_exchange_wait(ex[r], C.c_void_p(flags[r]), world, None) == 0
             out = torch.empty((batch, hidden), dtype=torch.float16, device="cuda")
-            assert L.tq_exchange_sum_f16(C.c_void_p(bufs[r].data_ptr()), world, slot, slot, C.c_void_p(out.data_ptr()), None) == 0
+            assert L.tq_exchange_sum_f16(C.c_void_p(bufs[r].data_ptr()), world, slot, slot, None, C.c_void_p(out.data_ptr()), None) == 0
             outs.append(out)
         torch.cuda.synchronize()
         want = (parts[0].float() + parts[1].float()).half()           # rank order, fp32 accumulate

@@ -89,7 +89,10 @@ def load() -> C.CDLL:
     sig("tq_exchange_create", vp, [i, i])
     sig("tq_exchange_broadcast", i, [vp, vp, C.POINTER(C.c_void_p), i, i, C.c_long, C.c_long, C.c_long, C.POINTER(C.c_void_p), i, vp])
     sig("tq_exchange_wait", i, [vp, vp, i, vp])
-    sig("tq_exchange_sum_f16", i, [vp, i, C.c_long, C.c_long, vp, vp])
+    sig("tq_exchange_sum_f16", i, [vp, i, C.c_long, C.c_long, vp, vp, vp])
+    sig("tq_rmsnorm_f16", i, [vp, vp, vp, C.c_long, i, C.c_float, vp])
+    sig("tq_rope_f16", i, [vp, vp, C.c_long, i, i, C.c_float, vp])
+    sig("tq_swiglu_f16", i, [vp, vp, C.c_long, i, vp])
     sig("tq_exchange_merge_attention", i, [vp, vp, i, C.c_long, i, C.c_long, C.c_long, vp, vp])
     sig("tq_linear_forward_allgather", i, [vp, vp, vp, i, C.POINTER(C.c_void_p), i, C.c_long, C.c_long, C.POINTER(C.c_void_p), i,
                                             vp, i, vp])

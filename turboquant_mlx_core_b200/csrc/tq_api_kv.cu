@@ -448,6 +448,26 @@ public:
         TQ_REQUIRE(alias != nullptr, "attention: the status word is not mapped for the device");
         return static_cast<unsigned int*>(alias);
     }
+    // Device copy of the descriptor table of `layer`; uploaded only when it differs from what is there.
+    const void* upload_descriptors(int layer, const void* table, size_t bytes, cudaStream_t st) {
+        if (desc_dev_.size() < static_cast<size_t>(layers_n_)) {
+            desc_dev_.resize(static_cast<size_t>(layers_n_));
+            desc_host_.resize(static_cast<size_t>(layers_n_));
+        }
+        DeviceBuffer& dev = desc_dev_[static_cast<size_t>(layer)];
+        std::vector<uint8_t>& host = desc_host_[static_cast<size_t>(layer)];
+        if (bytes == host.size() && bytes > 0 && std::memcmp(host.data(), table, bytes) == 0) return dev.as<void>();
+        cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+        TQ_CUDA(cudaStreamIsCapturing(st, &cap));
+        TQ_REQUIRE(cap == cudaStreamCaptureStatusNone,
+                   "attention: the sequences or ranges of this call differ from the previous call for this layer; run it once "
+                   "outside the stream capture first (the descriptor upload cannot be captured)");
+        dev.reserve(bytes);
+        // from pageable memory: staged by the driver before the call returns, so `table` may die
+        TQ_CUDA(cudaMemcpyAsync(dev.as<void>(), table, bytes, cudaMemcpyHostToDevice, st));
+        host.assign(static_cast<const uint8_t*>(table), static_cast<const uint8_t*>(table) + bytes);
+        return dev.as<void>();
+    }
     // Throws when an attention launch that has finished reported a failure (and clears the report).
     ~TQKVCache() {
         if (h_attn_status_) cudaFreeHost(h_attn_status_);
@@ -496,6 +516,8 @@ private:
     DeviceBuffer stage_k_, stage_v_;
     DeviceBuffer attn_scratch_, attn_desc_, attn_q_, attn_out_, attn_lse_;
     unsigned int* h_attn_status_ = nullptr;
+    std::vector<DeviceBuffer> desc_dev_;            // per layer: the descriptor table of the last attention call
+    std::vector<std::vector<uint8_t>> desc_host_;   // ... and its host copy, to tell whether an upload is needed
     int attention_kernel_ = 0;
 };
 
@@ -524,8 +546,9 @@ void attention_batched(TQKVCache* const* caches, int n_seqs, int layer, const vo
     const tq::AttnPlan plan = tq::attn_make_plan(n_seqs, q_heads, heads, dim, max_tok, tq::sm_count(c0->device()), c0->attention_kernel());
     const int n_splits = plan.n_splits;
 
-    c0->attn_desc().reserve(desc.size() * sizeof(SeqDesc));
-    TQ_CUDA(cudaMemcpyAsync(c0->attn_desc().as<void>(), desc.data(), desc.size() * sizeof(SeqDesc), cudaMemcpyHostToDevice, st));
+    // The descriptor table goes up only when it differs from the one already on the device: a call
+    // that repeats the previous ranges enqueues kernels only (and can then be captured in a graph).
+    const void* d_desc = c0->upload_descriptors(layer, desc.data(), desc.size() * sizeof(SeqDesc), st);
     const size_t n_q = static_cast<size_t>(n_seqs) * q_heads * dim;
     const size_t q_es = q_dtype == TQ_F32 ? 4 : 2;
     const void* d_q = q;
@@ -548,7 +571,7 @@ void attention_batched(TQKVCache* const* caches, int n_seqs, int layer, const vo
         d_lse = c0->attn_lse().as<float>();
     }
     c0->attn_scratch().reserve(tq::attn_scratch_bytes(n_seqs, q_heads, dim, n_splits));
-    tq::launch_kv_attention(c0->attn_desc().as<void>(), n_seqs, d_q, q_dtype == TQ_F16, q_heads, heads, dim, plan,
+    tq::launch_kv_attention(d_desc, n_seqs, d_q, q_dtype == TQ_F16, q_heads, heads, dim, plan,
                             tq::kv_layer_seed(static_cast<uint32_t>(layer), 1), tq::kv_layer_seed(static_cast<uint32_t>(layer), 2),
                             tq::kv_layer_seed(static_cast<uint32_t>(layer), 3), use_qjl, c0->attn_scratch().as<void>(), d_out, d_lse,
                             c0->attn_status_device(), st);

@@ -65,10 +65,35 @@ int tq_exchange_wait(tq_exchange_t ex, const void* local_flags, int n_flags, voi
     });
 }
 
-int tq_exchange_sum_f16(const void* slots_fp16, int n_slots, long slot_stride, long count, void* out_fp16, void* stream) {
+int tq_exchange_sum_f16(const void* slots_fp16, int n_slots, long slot_stride, long count, const void* residual_fp16,
+                        void* out_fp16, void* stream) {
     return guarded<int>(0, -1, [&]() {
-        launch_exchange_sum_f16(static_cast<const __half*>(slots_fp16), n_slots, slot_stride, count, static_cast<__half*>(out_fp16),
+        launch_exchange_sum_f16(static_cast<const __half*>(slots_fp16), n_slots, slot_stride, count,
+                                static_cast<const __half*>(residual_fp16), static_cast<__half*>(out_fp16),
                                 static_cast<cudaStream_t>(stream));
+        return 0;
+    });
+}
+
+int tq_rmsnorm_f16(const void* x_fp16, const void* weight_fp16, void* y_fp16, long rows, int cols, float eps, void* stream) {
+    return guarded<int>(0, -1, [&]() {
+        launch_rmsnorm_f16(static_cast<const __half*>(x_fp16), static_cast<const __half*>(weight_fp16), static_cast<__half*>(y_fp16),
+                           rows, cols, eps, static_cast<cudaStream_t>(stream));
+        return 0;
+    });
+}
+
+int tq_rope_f16(void* x_fp16, const int* positions, long rows, int heads, int head_dim, float theta, void* stream) {
+    return guarded<int>(0, -1, [&]() {
+        launch_rope_f16(static_cast<__half*>(x_fp16), positions, rows, heads, head_dim, theta, static_cast<cudaStream_t>(stream));
+        return 0;
+    });
+}
+
+int tq_swiglu_f16(const void* gate_up_fp16, void* act_fp16, long rows, int intermediate, void* stream) {
+    return guarded<int>(0, -1, [&]() {
+        launch_swiglu_f16(static_cast<const __half*>(gate_up_fp16), static_cast<__half*>(act_fp16), rows, intermediate,
+                          static_cast<cudaStream_t>(stream));
         return 0;
     });
 }

@@ -137,9 +137,15 @@ void launch_exchange_broadcast(const void* src, void* const* dst, int n_dst, int
                                long dst_stride, unsigned int* const* signal, int n_signal, int slot, unsigned int* done,
                                unsigned int* epoch, cudaStream_t stream);
 void launch_exchange_wait(const unsigned int* flags, int n, unsigned int* epoch, unsigned int* status, cudaStream_t stream);
-void launch_exchange_sum_f16(const __half* slots, int n_slots, long slot_stride, long count, __half* out, cudaStream_t stream);
+void launch_exchange_sum_f16(const __half* slots, int n_slots, long slot_stride, long count, const __half* residual, __half* out,
+                             cudaStream_t stream);
 void launch_exchange_merge_attention(const __half* outs, const float* lses, int parts, long rows, int dim, long part_stride_o,
                                      long part_stride_l, __half* out, cudaStream_t stream);
+
+// tq_decoder_ops.cu — element-wise glue of a decoder layer (fp16 in / out, fp32 arithmetic).
+void launch_rmsnorm_f16(const __half* x, const __half* weight, __half* y, long rows, int cols, float eps, cudaStream_t stream);
+void launch_rope_f16(__half* x, const int* positions, long rows, int heads, int dim, float theta, cudaStream_t stream);
+void launch_swiglu_f16(const __half* gate_up, __half* act, long rows, int inter, cudaStream_t stream);
 
 // tq_misc.cu — small element-wise helpers.
 void launch_f32_to_f16(const float* in, __half* out, long n, cudaStream_t stream);

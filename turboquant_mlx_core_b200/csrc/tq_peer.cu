@@ -101,14 +101,19 @@ __global__ void exchange_wait_kernel(const unsigned int* __restrict__ flags, int
     }
 }
 
-// out[i] = fp16( sum over slots s, in slot order, of fp32(slots[s][i]) )
+// out[i] = fp16( residual[i] + sum over slots s, in slot order, of fp32(slots[s][i]) )   (residual may be NULL)
 __global__ void __launch_bounds__(256) exchange_sum_f16_kernel(const __half* __restrict__ slots, int n_slots, long slot_stride,
-                                                               long count, __half* __restrict__ out) {
+                                                               long count, const __half* __restrict__ residual, __half* __restrict__ out) {
     asm volatile("griddepcontrol.wait;" ::: "memory");
     asm volatile("griddepcontrol.launch_dependents;");
     for (long i = (static_cast<long>(blockIdx.x) * blockDim.x + threadIdx.x) * 2; i < count;
          i += static_cast<long>(gridDim.x) * blockDim.x * 2) {
         float a = 0.f, b = 0.f;
+        if (residual != nullptr) {
+            const __half2 h = *reinterpret_cast<const __half2*>(residual + i);
+            a = __low2float(h);
+            b = __high2float(h);
+        }
         for (int s = 0; s < n_slots; ++s) {
             const __half2 h = *reinterpret_cast<const __half2*>(slots + s * slot_stride + i);   // written by other GPUs: plain loads after the acquire of the wait kernel
             a += __low2float(h);
@@ -196,7 +201,8 @@ void launch_exchange_wait(const unsigned int* flags, int n, unsigned int* epoch,
     TQ_CUDA(cudaLaunchKernelEx(&cfg, exchange_wait_kernel, flags, n, epoch, status));
 }
 
-void launch_exchange_sum_f16(const __half* slots, int n_slots, long slot_stride, long count, __half* out, cudaStream_t stream) {
+void launch_exchange_sum_f16(const __half* slots, int n_slots, long slot_stride, long count, const __half* residual, __half* out,
+                             cudaStream_t stream) {
     TQ_REQUIRE(slots != nullptr && out != nullptr && n_slots >= 1, "exchange sum: NULL argument");
     TQ_REQUIRE(count % 2 == 0 && slot_stride % 2 == 0 && reinterpret_cast<uintptr_t>(slots) % 4 == 0 &&
                    reinterpret_cast<uintptr_t>(out) % 4 == 0,
@@ -206,7 +212,7 @@ void launch_exchange_sum_f16(const __half* slots, int n_slots, long slot_stride,
     if (blocks > 296) blocks = 296;
     cudaLaunchAttribute attr[1];
     cudaLaunchConfig_t cfg = pdl_config(dim3(static_cast<unsigned>(blocks)), dim3(256), stream, attr);
-    TQ_CUDA(cudaLaunchKernelEx(&cfg, exchange_sum_f16_kernel, slots, n_slots, slot_stride, count, out));
+    TQ_CUDA(cudaLaunchKernelEx(&cfg, exchange_sum_f16_kernel, slots, n_slots, slot_stride, count, residual, out));
 }
 
 void launch_exchange_merge_attention(const __half* outs, const float* lses, int parts, long rows, int dim, long part_stride_o,

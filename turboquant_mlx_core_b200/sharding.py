@@ -261,11 +261,13 @@ class Exchange:
         _lib.check(self._L.tq_exchange_wait(self._h, C.c_void_p(self.buf.local_flags), self.world, _stream_ptr(stream)),
                    "tq_exchange_wait")
 
-    def sum_f16(self, slots_offset: int, n_slots: int, slot_stride_elems: int, count: int, out_ptr: int, stream=None):
+    def sum_f16(self, slots_offset: int, n_slots: int, slot_stride_elems: int, count: int, out_ptr: int, residual_ptr: int = 0,
+                stream=None):
         import ctypes as C
         from . import _lib
         _lib.check(self._L.tq_exchange_sum_f16(C.c_void_p(self.buf.local + slots_offset), n_slots, slot_stride_elems, count,
-                                                C.c_void_p(out_ptr), _stream_ptr(stream)), "tq_exchange_sum_f16")
+                                                C.c_void_p(residual_ptr) if residual_ptr else None, C.c_void_p(out_ptr),
+                                                _stream_ptr(stream)), "tq_exchange_sum_f16")
 
     def merge_attention(self, outs_offset: int, lses_offset: int, parts: int, rows: int, head_dim: int, part_stride_out: int,
                         part_stride_lse: int, out_ptr: int, stream=None):
