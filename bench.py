@@ -978,7 +978,8 @@ def bench_c4_decode_step(tq, L, device, stream, rank, world, cbs, args):
                 kk = torch.randn((ctx, kvh, dim), generator=g, device=device).half()
                 c.append(li, kk, kk)
         arr = (C.c_void_p * batch)(*[c.handle for c in caches])
-        x = torch.randn((batch, hidden), generator=g, device=device).half() * 0.1
+        gx = torch.Generator(device=device).manual_seed(77 + batch)       # the residual stream is replicated: same on every rank
+        x = torch.randn((batch, hidden), generator=gx, device=device).half() * 0.1
         x0 = x.clone()
         h1 = torch.empty_like(x)
         q = torch.empty((batch, qh, dim), device=device, dtype=torch.float16)
@@ -1027,6 +1028,7 @@ def bench_c4_decode_step(tq, L, device, stream, rank, world, cbs, args):
             for li in range(n_layers):
                 layer_step(li)
 
+        torch.cuda.synchronize()           # the inputs were made on the default stream
         with torch.cuda.stream(stream):
             one_pass()                     # allocates scratch, uploads attention descriptors per layer
             x.copy_(x0)
@@ -1093,6 +1095,7 @@ def bench_c4_decode_step(tq, L, device, stream, rank, world, cbs, args):
         xl = xs[:, c0:c1].contiguous()
         got = torch.empty((batch, rows), device=device, dtype=torch.float16)
         cnt = batch * rows
+        torch.cuda.synchronize()           # the inputs were made on the default stream
         with torch.cuda.stream(stream):
             if exchange is None:
                 tmp = shard.forward(xl, stream=stream)

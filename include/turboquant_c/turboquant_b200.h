@@ -87,6 +87,16 @@ int tq_quantize_weight(const float* weight, int out_features, int in_features, c
                        int residual_bits, uint32_t block, int shared_rotation, uint8_t* packed_primary,
                        uint8_t* packed_residual, float* norms, uint32_t* seeds, void* stream);
 
+/** The same with the two rotation seeds given by the caller instead of derived from the weight's
+ *  bytes (derive_seed, src/quantizer.cpp:12-28): for callers that fix the seeds per layer, e.g. to
+ *  quantise shards of one matrix consistently.  seeds[] still receives {seed_primary, seed_residual
+ *  or 0 under shared rotation, block}. */
+int tq_quantize_weight_seeded(const float* weight, int out_features, int in_features, const float* primary_centroids,
+                              int n_primary, const float* residual_centroids, int n_residual, int primary_bits,
+                              int residual_bits, uint32_t block, int shared_rotation, uint32_t seed_primary,
+                              uint32_t seed_residual, uint8_t* packed_primary, uint8_t* packed_residual, float* norms,
+                              uint32_t* seeds, void* stream);
+
 /* ---- TurboQuantLinear (include/turboquant/linear.h:11-35) and the dequantiser
  *      (include/turboquant/dequantizer.h:11-39) ------------------------------------- */
 

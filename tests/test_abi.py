@@ -84,8 +84,14 @@ def test_model_handle(lib):
                 f.write(bad)
             assert lib.tq_model_load(d.encode()) is None
             assert b"tq_model_load" in lib.tq_last_error()
+            assert lib.tq_model_dequant(d.encode(), os.path.join(d, "out").encode()) == 1   # a broken shard: 1, as in the reference
         os.remove(os.path.join(d, "bad.safetensors"))
-        assert lib.tq_model_dequant(d.encode(), d.encode()) != 0
+        # a directory without shards: nothing to dequantise, side files are copied (needs no GPU)
+        with open(os.path.join(d, "tokenizer.json"), "w") as f:
+            f.write("{}")
+        assert lib.tq_model_dequant(d.encode(), os.path.join(d, "plain").encode()) == 0
+        assert open(os.path.join(d, "plain", "tokenizer.json")).read() == "{}"
+        assert lib.tq_model_dequant(os.path.join(d, "missing").encode(), d.encode()) == 1
     assert lib.tq_model_dequant(None, None) != 0
 
 

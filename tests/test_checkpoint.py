@@ -149,3 +149,46 @@ def test_c_model_load_uploads_every_layer(tq, oracle, tmp_path):
             assert rel_l2(y, want) < 1e-3, name
         assert L.tq_model_layer(m, b"missing") is None
         L.tq_model_free(m)
+
+
+@pytest.mark.gpu
+def test_model_dequant_writes_an_ordinary_model_directory(tq, oracle, tmp_path):
+    """tq_model_dequant (src/turboquant_c_dequant.cpp:20-191): side files copied, quantization_config
+    stripped from config.json, every quantised layer written as {name}.weight in the passthrough
+    tensors' dtype (bfloat16 without any) with the bits of dequantize_weight_cpu + one rounding,
+    passthrough tensors merged, foreign shards copied; bad paths give 1."""
+    from safetensors.numpy import load_file, save_file
+    from turboquant_mlx_core_b200 import checkpoint as ckpt
+    rng = np.random.default_rng(6)
+    src, dst = os.path.join(str(tmp_path), "tq"), os.path.join(str(tmp_path), "out", "plain")
+    os.makedirs(src)
+    layers, shard, norm_w = _write_model(tq, ckpt, oracle, src, rng)
+    with open(os.path.join(src, "config.json"), "w") as f:
+        f.write('{"hidden_size": 256, "quantization_config": {"method": "turboquant", "nested": {"bits": 8}}, "vocab": 40}')
+    with open(os.path.join(src, "tokenizer.json"), "w") as f:
+        f.write("{}")
+    foreign = {"extra.weight": rng.standard_normal((4, 4)).astype(np.float32)}
+    save_file(foreign, os.path.join(src, "other.safetensors"))
+    L = tq.load()
+    assert L.tq_model_dequant(src.encode(), dst.encode()) == 0, L.tq_last_error()
+    assert open(os.path.join(dst, "config.json")).read() == '{"hidden_size": 256, "vocab": 40}'
+    assert os.path.exists(os.path.join(dst, "tokenizer.json"))
+    assert np.array_equal(load_file(os.path.join(dst, "other.safetensors"))["extra.weight"], foreign["extra.weight"])
+    got = load_file(os.path.join(dst, os.path.basename(shard)))       # passthrough is fp32 here, so the weights are too
+    assert sorted(got) == sorted([n + ".weight" for n in layers] + ["model.norm.weight"])
+    assert np.array_equal(got["model.norm.weight"], norm_w)
+    for name, (pp, pr, norms, seeds, cbp, cbr, bs) in layers.items():
+        want = oracle.dequantize_weight(pp, pr, norms, seeds, cbp, cbr, bs)
+        assert got[name + ".weight"].dtype == np.float32
+        assert np.array_equal(got[name + ".weight"].view(np.uint32), want.view(np.uint32)), name
+    # without a passthrough file the output is bfloat16: the fp32 result rounded to nearest even
+    os.remove(os.path.join(src, os.path.basename(shard).replace(".safetensors", "_passthrough.safetensors")))
+    dst2 = os.path.join(str(tmp_path), "out2")
+    assert L.tq_model_dequant(src.encode(), dst2.encode()) == 0, L.tq_last_error()
+    tensors, _ = ckpt.read_safetensors(os.path.join(dst2, os.path.basename(shard)))
+    for name, (pp, pr, norms, seeds, cbp, cbr, bs) in layers.items():
+        want = oracle.dequantize_weight(pp, pr, norms, seeds, cbp, cbr, bs).view(np.uint32)
+        bf = ((want + 0x7FFF + ((want >> 16) & 1)) >> 16).astype(np.uint16)
+        assert np.array_equal(np.asarray(tensors[name + ".weight"]).view(np.uint16).reshape(bf.shape), bf), name
+    assert L.tq_model_dequant(os.path.join(src, "missing").encode(), dst.encode()) == 1
+    assert L.tq_model_dequant(None, dst.encode()) == 1

@@ -48,6 +48,24 @@ def test_append_bits_and_decode(tq, golden, case, dtype):
     cache.close()
 
 
+@pytest.mark.parametrize("heads,dim,tokens", [(4, 128, 300), (2, 64, 700), (1, 256, 530), (3, 32, 200), (1, 512, 515)])
+@pytest.mark.parametrize("dtype", [np.float16, np.float32])
+def test_bulk_append_bits_match_the_checker(tq, oracle, heads, dim, tokens, dtype):
+    """Appends of 512 vectors or more run the batched encoder (one thread per vector for the two
+    left-to-right sums of src/kv_cache.cpp:84-88, 226-231): every stored bit equals the CPU
+    restatement's, also when a later single-token append lands behind the bulk."""
+    k, v = kv_inputs(tokens + dim, tokens, heads, dim)
+    c = tq.TQKVCache(1, heads, dim)
+    c.append(0, k[:-1].astype(dtype), v[:-1].astype(dtype))
+    c.append(0, k[-1:].astype(dtype), v[-1:].astype(dtype))
+    ex = c.export(0)
+    kw, kn, qw, qn = oracle.kv_encode(k.astype(np.float32), oracle.kv_seed(0, 1), oracle.kv_seed(0, 3))
+    vw, vn, _, _ = oracle.kv_encode(v.astype(np.float32), oracle.kv_seed(0, 2))
+    for key, want in (("k_words", kw), ("k_norms", kn), ("qjl_words", qw), ("qjl_norms", qn), ("v_words", vw), ("v_norms", vn)):
+        assert bits_equal(np.asarray(ex[key]).reshape(np.asarray(want).shape), want), key
+    c.close()
+
+
 @pytest.mark.parametrize("case", KV_CASES, ids=[c[0] for c in KV_CASES])
 @pytest.mark.parametrize("use_qjl", [False, True])
 def test_attention_matches_oracle(tq, golden, case, use_qjl):

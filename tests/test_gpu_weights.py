@@ -72,6 +72,27 @@ def test_dequantize_bit_exact(tq, golden, case):
     assert bits_equal(deq16, golden[name + "_deq"].astype(np.float16))
 
 
+def test_caller_supplied_seeds(tq, oracle):
+    """With the seeds given, the quantiser reproduces what it derives itself when handed the derived
+    seeds, and other seeds give other codes that still dequantise to the weight within the format's
+    error (src/quantizer.cpp:12-28 derives; the sharded paths want to fix them)."""
+    w = gauss_weight(5, 32, 256)
+    cb = tq.generate_codebook(4)
+    cfg = tq.QuantizerConfig(4, 4, 128, True)
+    derived = tq.quantize_weight(w, cb, cb, cfg)
+    sp = oracle.derive_seed(w, 0)
+    assert int(derived.seeds[0]) == sp
+    same = tq.quantize_weight(w, cb, cb, cfg, seeds=(sp, oracle.derive_seed(w, 1)))
+    assert bits_equal(same.packed_primary, derived.packed_primary) and bits_equal(same.norms, derived.norms)
+    assert bits_equal(same.seeds, derived.seeds)
+    other = tq.quantize_weight(w, cb, cb, cfg, seeds=(12345, 678))
+    assert list(other.seeds) == [12345, 0, 128] and not bits_equal(other.packed_primary, derived.packed_primary)
+    back = tq.dequantize_weight(other, cb, cb, 128)
+    assert rel_l2(back, w) < 0.15
+    dual = tq.quantize_weight(w, cb, cb, tq.QuantizerConfig(4, 4, 128, False), seeds=(12345, 678))
+    assert list(dual.seeds) == [12345, 678, 128]
+
+
 def test_fitted_codebooks_bit_exact(tq, golden):
     w = gauss_weight(0, 64, 512)
     cbp, cbr = tq.codebook_from_centroids(golden["fit_cb_p"]), tq.codebook_from_centroids(golden["fit_cb_r"])

@@ -69,6 +69,7 @@ def load() -> C.CDLL:
     sig("tq_codebook_generate", i, [i, f32p, f32p])
     sig("tq_wht_rotate", i, [vp, vp, i, i, u32, u32, i, vp])
     sig("tq_quantize_weight", i, [vp, i, i, vp, i, vp, i, i, i, u32, i, vp, vp, vp, vp, vp])
+    sig("tq_quantize_weight_seeded", i, [vp, i, i, vp, i, vp, i, i, i, u32, i, u32, u32, vp, vp, vp, vp, vp])
 
     sig("tq_linear_create", vp, [i, i, vp, i, vp, vp, vp, vp, i, vp, i, u32])
     sig("tq_linear_forward", i, [vp, vp, i, i, vp, vp])

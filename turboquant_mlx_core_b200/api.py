@@ -136,8 +136,9 @@ class QuantizedWeight:
 
 
 def quantize_weight(weight, primary_codebook: Codebook, residual_codebook: Codebook,
-                    config: QuantizerConfig) -> QuantizedWeight:
-    """quantize_weight (src/quantizer.cpp:41-261) on the device; host arrays in and out."""
+                    config: QuantizerConfig, seeds=None) -> QuantizedWeight:
+    """quantize_weight (src/quantizer.cpp:41-261) on the device; host arrays in and out.  seeds =
+    (primary, residual) fixes the rotation seeds instead of deriving them from the weight's bytes."""
     L = _lib.load()
     w = weight if _is_torch(weight) else _np(weight, np.float32)
     out_f, in_f = int(w.shape[0]), int(w.shape[1])
@@ -146,12 +147,18 @@ def quantize_weight(weight, primary_codebook: Codebook, residual_codebook: Codeb
     pp = np.zeros((out_f, in_f // 2 if config.primary_bits <= 4 else in_f), np.uint8)
     pr = np.zeros((out_f, in_f // 2), np.uint8)
     norms = np.zeros(out_f, np.float32)
-    seeds = np.zeros(3, np.uint32)
     cp, cr = _np(primary_codebook.centroids, np.float32), _np(residual_codebook.centroids, np.float32)
-    check(L.tq_quantize_weight(_ptr(w), out_f, in_f, _ptr(cp), cp.size, _ptr(cr), cr.size, config.primary_bits,
-                               config.residual_bits, config.block_size, int(config.shared_rotation), _ptr(pp),
-                               _ptr(pr), _ptr(norms), _ptr(seeds), None), "quantize_weight")
-    return QuantizedWeight(pp, pr, norms, seeds)
+    out_seeds = np.zeros(3, np.uint32)
+    if seeds is None:
+        check(L.tq_quantize_weight(_ptr(w), out_f, in_f, _ptr(cp), cp.size, _ptr(cr), cr.size, config.primary_bits,
+                                   config.residual_bits, config.block_size, int(config.shared_rotation), _ptr(pp),
+                                   _ptr(pr), _ptr(norms), _ptr(out_seeds), None), "quantize_weight")
+    else:
+        check(L.tq_quantize_weight_seeded(_ptr(w), out_f, in_f, _ptr(cp), cp.size, _ptr(cr), cr.size, config.primary_bits,
+                                          config.residual_bits, config.block_size, int(config.shared_rotation),
+                                          int(seeds[0]) & 0xFFFFFFFF, int(seeds[1]) & 0xFFFFFFFF, _ptr(pp), _ptr(pr), _ptr(norms),
+                                          _ptr(out_seeds), None), "quantize_weight")
+    return QuantizedWeight(pp, pr, norms, out_seeds)
 
 
 class TurboQuantLinear:

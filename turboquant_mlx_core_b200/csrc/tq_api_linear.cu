@@ -130,9 +130,10 @@ public:
         TQ_REQUIRE(batch >= 0, "TurboQuantLinear::forward: negative batch");
         TQ_REQUIRE(x_dtype == TQ_F32 || x_dtype == TQ_F16, "TurboQuantLinear::forward: x must be fp32 or fp16");
         if (batch == 0) return;
-        TQ_CUDA(cudaSetDevice(device_));
+        make_current();
         const size_t nx = static_cast<size_t>(batch) * in_, ny = static_cast<size_t>(batch) * out_;
-        const bool x_dev = tq::is_device_pointer(x), y_dev = tq::is_device_pointer(y);
+        const PointerKind kx = classify(x), ky = classify(y);
+        const bool x_dev = kx.device, y_dev = ky.device;
 
         const __half* d_x;
         if (x_dtype == TQ_F16) {
@@ -156,7 +157,7 @@ public:
         }
         // A few rows into page-locked host memory: the decode kernel stores them there itself
         // (8 KB of posted writes cost less than a separate copy); anything larger or pageable is staged.
-        void* y_alias = (!y_dev && batch <= 8) ? tq::pinned_host_device_alias(y) : nullptr;
+        void* y_alias = (!y_dev && batch <= 8) ? ky.pinned_alias : nullptr;
         __half* d_y;
         if (y_dev) d_y = static_cast<__half*>(y);
         else if (y_alias) d_y = static_cast<__half*>(y_alias);
@@ -298,6 +299,40 @@ public:
     }
 
 private:
+    // What the driver knows about a caller's pointer.  A decode loop passes the same few buffers on
+    // every call, so the last answers are kept (four per handle, round robin): the look-up costs a
+    // driver call each time otherwise.  A buffer that is freed and re-created at the same address
+    // as another KIND of memory (device / page-locked / pageable) between two calls on one handle
+    // would be misjudged; callers that do that use a fresh handle or device pointers.
+    struct PointerKind {
+        const void* ptr = nullptr;
+        bool device = false;
+        void* pinned_alias = nullptr;   // device-side address of page-locked host memory, else NULL
+    };
+    PointerKind classify(const void* p) {
+        for (const PointerKind& k : kinds_)
+            if (k.ptr == p) return k;
+        PointerKind k;
+        k.ptr = p;
+        cudaPointerAttributes attr{};
+        if (cudaPointerGetAttributes(&attr, p) != cudaSuccess) {
+            cudaGetLastError();
+        } else {
+            k.device = attr.type == cudaMemoryTypeDevice || attr.type == cudaMemoryTypeManaged;
+            k.pinned_alias = attr.type == cudaMemoryTypeHost ? attr.devicePointer : nullptr;
+        }
+        kinds_[next_kind_] = k;
+        next_kind_ = (next_kind_ + 1) & 3;
+        return k;
+    }
+    // cudaSetDevice only when another device is current (it is not free even as a no-op).
+    void make_current() {
+        int cur = -1;
+        if (cudaGetDevice(&cur) != cudaSuccess || cur != device_) TQ_CUDA(cudaSetDevice(device_));
+    }
+    PointerKind kinds_[4];
+    int next_kind_ = 0;
+
     static void require_ok(unsigned int h) {
         if (h == 0) return;
         const char* what = h == 1 ? "decode kernel: unexpected shared-memory base address, kernel did not run"
@@ -420,10 +455,10 @@ int tq_linear_dequantize(tq_linear_t lin, void* result, int result_dtype, void* 
     });
 }
 
-int tq_quantize_weight(const float* weight, int out_features, int in_features, const float* primary_centroids,
-                       int n_primary, const float* residual_centroids, int n_residual, int primary_bits,
-                       int residual_bits, uint32_t block, int shared_rotation, uint8_t* packed_primary,
-                       uint8_t* packed_residual, float* norms, uint32_t* seeds, void* stream) {
+static int quantize_weight_impl(const float* weight, int out_features, int in_features, const float* primary_centroids,
+                                int n_primary, const float* residual_centroids, int n_residual, int primary_bits,
+                                int residual_bits, uint32_t block, int shared_rotation, const uint32_t* given_seeds,
+                                uint8_t* packed_primary, uint8_t* packed_residual, float* norms, uint32_t* seeds, void* stream) {
     return guarded<int>(0, -1, [&]() {
         TQ_REQUIRE(weight && primary_centroids && residual_centroids && packed_primary && packed_residual && norms && seeds,
                    "tq_quantize_weight: NULL argument");
@@ -447,7 +482,12 @@ int tq_quantize_weight(const float* weight, int out_features, int in_features, c
         if (!pr_dev) { pr_stage.reserve(pr_bytes + 4); d_pr = pr_stage.as<uint8_t>(); }
         if (!nm_dev) { nm_stage.reserve(static_cast<size_t>(out_features) * 4 + 4); d_nm = nm_stage.as<float>(); }
         uint32_t seed_p = 0, seed_r = 0;
-        derive_seeds(d_w, n, &seed_p, &seed_r, st);  // src/quantizer.cpp:69-70
+        if (given_seeds != nullptr) {
+            seed_p = given_seeds[0];
+            seed_r = given_seeds[1];
+        } else {
+            derive_seeds(d_w, n, &seed_p, &seed_r, st);  // src/quantizer.cpp:69-70
+        }
         launch_quantize_weight(d_w, out_features, in_features, cp.data(), n_primary, cr.data(), n_residual, primary_bits,
                                residual_bits, block, shared_rotation != 0, seed_p, seed_r, d_pp, d_pr, d_nm,
                                orig.as<float>(), recon.as<float>(), st);
@@ -460,6 +500,26 @@ int tq_quantize_weight(const float* weight, int out_features, int in_features, c
         TQ_CUDA(cudaStreamSynchronize(st));  // scratch and staging buffers die here
         return 0;
     });
+}
+
+int tq_quantize_weight(const float* weight, int out_features, int in_features, const float* primary_centroids,
+                       int n_primary, const float* residual_centroids, int n_residual, int primary_bits,
+                       int residual_bits, uint32_t block, int shared_rotation, uint8_t* packed_primary,
+                       uint8_t* packed_residual, float* norms, uint32_t* seeds, void* stream) {
+    return quantize_weight_impl(weight, out_features, in_features, primary_centroids, n_primary, residual_centroids, n_residual,
+                                primary_bits, residual_bits, block, shared_rotation, nullptr, packed_primary, packed_residual,
+                                norms, seeds, stream);
+}
+
+int tq_quantize_weight_seeded(const float* weight, int out_features, int in_features, const float* primary_centroids,
+                              int n_primary, const float* residual_centroids, int n_residual, int primary_bits,
+                              int residual_bits, uint32_t block, int shared_rotation, uint32_t seed_primary,
+                              uint32_t seed_residual, uint8_t* packed_primary, uint8_t* packed_residual, float* norms,
+                              uint32_t* seeds, void* stream) {
+    const uint32_t given[2] = {seed_primary, seed_residual};
+    return quantize_weight_impl(weight, out_features, in_features, primary_centroids, n_primary, residual_centroids, n_residual,
+                                primary_bits, residual_bits, block, shared_rotation, given, packed_primary, packed_residual, norms,
+                                seeds, stream);
 }
 
 int tq_linear_forward_scatter(tq_linear_t lin, const void* x_fp16_device, int batch, void* const* dst, int n_dst,

@@ -312,6 +312,183 @@ void load_shard(const std::string& path, tq_model_s& model) {
     }
 }
 
+
+// ---- writing a dequantised model directory (src/turboquant_c_dequant.cpp:20-191) ----------------
+
+void make_dirs(const std::string& path) {
+    std::string cur;
+    for (size_t i = 0; i <= path.size(); ++i) {
+        if (i == path.size() || path[i] == '/') {
+            if (!cur.empty() && cur != "/") {
+                if (mkdir(cur.c_str(), 0777) != 0 && errno != EEXIST) throw Error("cannot create directory " + cur);
+            }
+        }
+        if (i < path.size()) cur.push_back(path[i]);
+    }
+}
+
+std::string read_file(const std::string& path) {
+    std::unique_ptr<std::FILE, FileCloser> f(std::fopen(path.c_str(), "rb"));
+    if (!f) throw Error("cannot open " + path);
+    std::string out;
+    char buf[1 << 16];
+    size_t n;
+    while ((n = std::fread(buf, 1, sizeof buf, f.get())) > 0) out.append(buf, n);
+    return out;
+}
+
+void write_file(const std::string& path, const std::string& bytes) {
+    std::unique_ptr<std::FILE, FileCloser> f(std::fopen(path.c_str(), "wb"));
+    if (!f || (!bytes.empty() && std::fwrite(bytes.data(), 1, bytes.size(), f.get()) != bytes.size()))
+        throw Error("cannot write " + path);
+}
+
+// The copied config.json loses its "quantization_config" object (with the comma before it), so
+// that downstream loaders take the output for an ordinary model (:36-66).
+std::string strip_quantization_config(std::string json) {
+    const size_t qc = json.find("\"quantization_config\"");
+    if (qc == std::string::npos) return json;
+    const size_t open = json.find('{', qc);
+    if (open == std::string::npos) return json;
+    int depth = 1;
+    size_t pos = open + 1;
+    while (pos < json.size() && depth > 0) {
+        if (json[pos] == '{') ++depth;
+        else if (json[pos] == '}') --depth;
+        ++pos;
+    }
+    const size_t comma = json.rfind(',', qc);
+    if (comma != std::string::npos && comma < qc) json.erase(comma, pos - comma);
+    return json;
+}
+
+struct OutTensor {
+    std::string dtype;
+    std::vector<long> shape;
+    std::vector<unsigned char> bytes;
+};
+
+// A safetensors file: 8-byte little-endian header length, JSON header (padded with spaces to a
+// multiple of 8), tensor bytes in name order.
+void write_safetensors_file(const std::string& path, const std::map<std::string, OutTensor>& tensors) {
+    std::string header = "{\"__metadata__\":{\"format\":\"mlx\"}";
+    unsigned long long off = 0;
+    for (const auto& kv : tensors) {
+        header += ",\"";
+        for (char c : kv.first) {
+            if (c == '"' || c == '\\') header.push_back('\\');
+            header.push_back(c);
+        }
+        header += "\":{\"dtype\":\"" + kv.second.dtype + "\",\"shape\":[";
+        for (size_t i = 0; i < kv.second.shape.size(); ++i) header += (i ? "," : "") + std::to_string(kv.second.shape[i]);
+        header += "],\"data_offsets\":[" + std::to_string(off) + "," + std::to_string(off + kv.second.bytes.size()) + "]}";
+        off += kv.second.bytes.size();
+    }
+    header += "}";
+    while (header.size() % 8) header.push_back(' ');
+    std::unique_ptr<std::FILE, FileCloser> f(std::fopen(path.c_str(), "wb"));
+    if (!f) throw Error("cannot write " + path);
+    unsigned char len[8];
+    unsigned long long n = header.size();
+    for (int i = 0; i < 8; ++i) len[i] = static_cast<unsigned char>((n >> (8 * i)) & 0xff);
+    bool ok = std::fwrite(len, 1, 8, f.get()) == 8 && std::fwrite(header.data(), 1, header.size(), f.get()) == header.size();
+    for (const auto& kv : tensors)
+        ok = ok && (kv.second.bytes.empty() || std::fwrite(kv.second.bytes.data(), 1, kv.second.bytes.size(), f.get()) == kv.second.bytes.size());
+    if (!ok) throw Error("short write to " + path);
+}
+
+// fp32 -> bf16, round to nearest even (what a framework's astype does); NaN stays NaN.
+uint16_t f32_to_bf16(uint32_t u) {
+    if ((u & 0x7fffffffu) > 0x7f800000u) return static_cast<uint16_t>((u >> 16) | 0x0040u);
+    return static_cast<uint16_t>((u + 0x7fffu + ((u >> 16) & 1u)) >> 16);
+}
+
+void dequant_shard(const std::string& in_dir, const std::string& fname, const std::string& out_dir) {
+    const std::string path = in_dir + "/" + fname;
+    const Shard shard(path);
+    const auto method = shard.metadata.find("quantization_method");
+    if (method == shard.metadata.end() || method->second != "turboquant") {   // not ours: copied as it is (:77-82)
+        write_file(out_dir + "/" + fname, read_file(path));
+        return;
+    }
+    // The output dtype is the passthrough tensors' (they keep the source model's), bfloat16 without
+    // a passthrough file (:152-163); the first tensor in name order decides.
+    const std::string stem = fname.substr(0, fname.size() - std::string(".safetensors").size());
+    const std::string pt_path = in_dir + "/" + stem + "_passthrough.safetensors";
+    struct stat sb;
+    std::unique_ptr<Shard> pt;
+    if (stat(pt_path.c_str(), &sb) == 0) pt.reset(new Shard(pt_path));
+    std::string target = "BF16";
+    if (pt && !pt->tensors.empty()) target = pt->tensors.begin()->second.dtype;
+    if (target != "BF16" && target != "F16" && target != "F32") target = "BF16";
+
+    // every quantised layer of the shard becomes a device-resident linear (the loader's rules)
+    tq_model_s model;
+    load_shard(path, model);
+    std::map<std::string, OutTensor> out;
+    for (size_t i = 0; i < model.layers.size(); ++i) {
+        tq_linear_t lin = model.layers[i];
+        const long rows = tq_linear_out_features(lin), cols = tq_linear_in_features(lin);
+        OutTensor t;
+        t.dtype = target;
+        t.shape = {rows, cols};
+        const size_t n = static_cast<size_t>(rows) * cols;
+        if (target == "F16") {
+            t.bytes.resize(n * 2);
+            if (tq_linear_dequantize(lin, t.bytes.data(), TQ_F16, nullptr) != 0) throw Error(model.names[i] + ": " + tq_last_error());
+        } else {
+            std::vector<uint32_t> w(n);
+            if (tq_linear_dequantize(lin, w.data(), TQ_F32, nullptr) != 0) throw Error(model.names[i] + ": " + tq_last_error());
+            if (target == "F32") {
+                t.bytes.resize(n * 4);
+                std::memcpy(t.bytes.data(), w.data(), n * 4);
+            } else {
+                t.bytes.resize(n * 2);
+                uint16_t* o = reinterpret_cast<uint16_t*>(t.bytes.data());
+                for (size_t k = 0; k < n; ++k) o[k] = f32_to_bf16(w[k]);
+            }
+        }
+        out[model.names[i] + ".weight"] = std::move(t);
+    }
+    // passthrough tensors (layers kept unquantised) are merged under their own names (:172-179)
+    if (pt) {
+        for (const auto& kv : pt->tensors) {
+            if (out.count(kv.first)) continue;
+            OutTensor t;
+            t.dtype = kv.second.dtype;
+            t.shape = kv.second.shape;
+            const size_t es = kv.second.count() ? static_cast<size_t>(kv.second.end - kv.second.begin) / kv.second.count() : 1;
+            t.bytes = pt->read(kv.first, kv.second.dtype.c_str(), es);
+            out[kv.first] = std::move(t);
+        }
+    }
+    write_safetensors_file(out_dir + "/" + fname, out);
+}
+
+void dequant_model_dir(const std::string& in_dir, const std::string& out_dir) {
+    make_dirs(out_dir);
+    std::vector<std::string> shards;
+    DIR* d = opendir(in_dir.c_str());
+    if (!d) throw Error("cannot read " + in_dir);
+    while (const dirent* e = readdir(d)) {
+        const std::string name = e->d_name;
+        if (name == "." || name == "..") continue;
+        struct stat sb;
+        if (stat((in_dir + "/" + name).c_str(), &sb) != 0 || !S_ISREG(sb.st_mode)) continue;
+        if (ends_with(name, ".safetensors")) {
+            if (name.find("_passthrough") == std::string::npos) shards.push_back(name);
+            continue;
+        }
+        // config, tokenizer, generation settings: copied (:28-34)
+        std::string bytes = read_file(in_dir + "/" + name);
+        if (name == "config.json") bytes = strip_quantization_config(std::move(bytes));
+        write_file(out_dir + "/" + name, bytes);
+    }
+    closedir(d);
+    std::sort(shards.begin(), shards.end());
+    for (const std::string& f : shards) dequant_shard(in_dir, f, out_dir);
+}
+
 }  // namespace
 
 extern "C" {
@@ -366,8 +543,18 @@ tq_linear_t tq_model_layer(tq_model_t model, const char* name) {
 }
 
 int tq_model_dequant(const char* tq_model_path, const char* output_path) {
+    // src/turboquant_c_dequant.cpp:20-191: 0 on success, 1 on any failure.
     if (!tq_model_path || !output_path) return 1;
-    tq::set_last_error("tq_model_dequant: writing dequantised model directories is not provided; load the model and call tq_linear_dequantize per layer");
+    try {
+        struct stat sb;
+        if (stat(tq_model_path, &sb) != 0 || !S_ISDIR(sb.st_mode)) throw Error("not a model directory");
+        dequant_model_dir(tq_model_path, output_path);
+        return 0;
+    } catch (const std::exception& e) {
+        tq::set_last_error(std::string("tq_model_dequant: ") + e.what());
+    } catch (...) {
+        tq::set_last_error("tq_model_dequant: unknown error");
+    }
     return 1;
 }
 

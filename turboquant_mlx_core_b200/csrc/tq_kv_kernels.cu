@@ -137,6 +137,141 @@ __global__ void __launch_bounds__(128) kv_encode_kernel(const InT* __restrict__ 
     }
 }
 
+// The same encoder for bulk appends: a CTA takes VB vectors at a time through shared memory so that
+// the two left-to-right sums of squares (the vector's norm and the residual's norm; their order is
+// fixed by src/kv_cache.cpp:84-88, 226-231 and bit-exactness) run with ONE THREAD PER VECTOR, VB of
+// them side by side, instead of one lane per warp while 31 wait.  The rotation, the codes and the
+// sign bits are still done a warp per vector.  Rows of the staging array are one float longer than
+// the vector: thread t walking row t then touches bank (t + j) % 32.
+template <int E> struct KvBatch { static constexpr int kVecs = E <= 4 ? 128 : (E == 8 ? 64 : 32); };
+
+constexpr int kKvBatchThreads = 512;   // 16 warps share a batch: the warp-per-vector part is latency-bound
+template <int E, typename InT>
+__global__ void __launch_bounds__(kKvBatchThreads) kv_encode_batch_kernel(const InT* __restrict__ x, long n_vec, uint32_t wht_seed,
+                                                              uint32_t qjl_seed, int with_qjl, float scale, float inv_sqrt,
+                                                              const __grid_constant__ KvEncodeTable tab, long vec_per_seg) {
+    constexpr int D = 32 * E;
+    constexpr int WPH = (D + 9) / 10;
+    constexpr int QPH = D / 32;
+    constexpr int VB = KvBatch<E>::kVecs;
+    constexpr int RS = D + 1;   // row stride of the staging array, in floats
+    extern __shared__ float s_stage[];          // [VB][RS]
+    __shared__ float s_norm[VB];
+    __shared__ uint8_t s_code[kKvBatchThreads / 32][D];
+    __shared__ uint32_t s_bits[kKvBatchThreads / 32][QPH];
+    __shared__ float s_bounds[7];
+    __shared__ float s_cent[8];
+    if (threadIdx.x < 8) s_cent[threadIdx.x] = kC3[threadIdx.x];
+    if (threadIdx.x < 7) s_bounds[threadIdx.x] = __fmul_rn(__fadd_rn(kC3[threadIdx.x], kC3[threadIdx.x + 1]), 0.5f);
+
+    const int tid = threadIdx.x, lane = tid & 31, wib = tid >> 5;
+    float sgn[E];
+#pragma unroll
+    for (int j = 0; j < E; ++j) sgn[j] = sign_value(wht_seed, static_cast<uint32_t>(lane * E + j));
+
+    for (long base = static_cast<long>(blockIdx.x) * VB; base < n_vec; base += static_cast<long>(gridDim.x) * VB) {
+        const int nb = static_cast<int>(n_vec - base < VB ? n_vec - base : VB);
+        __syncthreads();   // the previous batch has been consumed (and the tables are written)
+        // 16-byte loads (the batch is contiguous in x and starts at a multiple of VB * D elements)
+        constexpr int kPer = 16 / static_cast<int>(sizeof(InT));   // elements per load
+        const InT* xb = x + static_cast<size_t>(base) * D;
+        if (reinterpret_cast<uintptr_t>(xb) % 16 == 0) {
+            for (int i = tid; i < nb * D / kPer; i += kKvBatchThreads) {
+                const int e0 = i * kPer, vi = e0 / D, e = e0 - vi * D;
+                const uint4 raw = __ldg(reinterpret_cast<const uint4*>(xb) + i);
+                float* dst = s_stage + vi * RS + e;
+                if constexpr (sizeof(InT) == 2) {
+                    const __half2* h = reinterpret_cast<const __half2*>(&raw);
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) {
+                        const float2 f = __half22float2(h[k]);
+                        dst[2 * k] = f.x;
+                        dst[2 * k + 1] = f.y;
+                    }
+                } else {
+                    dst[0] = __uint_as_float(raw.x);
+                    dst[1] = __uint_as_float(raw.y);
+                    dst[2] = __uint_as_float(raw.z);
+                    dst[3] = __uint_as_float(raw.w);
+                }
+            }
+        } else {
+            for (int i = tid; i < nb * D; i += kKvBatchThreads) {
+                const int vi = i / D, e = i - vi * D;
+                s_stage[vi * RS + e] = load_as_f32(x, static_cast<size_t>(base + vi) * D + e);
+            }
+        }
+        __syncthreads();
+        // ---- norms: one thread per vector, left to right ----
+        if (tid < nb) {
+            float acc = 0.0f;
+            for (int j = 0; j < D; ++j) {
+                const float t = s_stage[tid * RS + j];
+                acc = __fadd_rn(acc, __fmul_rn(t, t));
+            }
+            const float norm = __fsqrt_rn(acc);
+            s_norm[tid] = norm;
+            const long gvec = base + tid, sidx = gvec / vec_per_seg;
+            tab.seg[sidx].norms[gvec - sidx * vec_per_seg] = norm;
+        }
+        __syncthreads();
+        // ---- rotation, codes, sign bits: a warp per vector ----
+        for (int vi = wib; vi < nb; vi += kKvBatchThreads / 32) {
+            const long gvec = base + vi, sidx = gvec / vec_per_seg, vec = gvec - sidx * vec_per_seg;
+            const KvEncodeDst& dst = tab.seg[sidx];
+            const float norm = s_norm[vi];
+            const float inv_norm = (norm > 1e-10f) ? __fdiv_rn(1.0f, norm) : 0.0f;
+            float v[E];
+#pragma unroll
+            for (int j = 0; j < E; ++j) v[j] = __fmul_rn(__fmul_rn(s_stage[vi * RS + lane * E + j], inv_norm), sgn[j]);
+            warp_fwht<E>(v, lane);
+            if (lane < QPH) s_bits[wib][lane] = 0u;
+            __syncwarp();
+            uint32_t my_bits = 0u;
+#pragma unroll
+            for (int j = 0; j < E; ++j) {
+                v[j] = __fmul_rn(__fmul_rn(v[j], inv_sqrt), scale);
+                int idx = 0;
+#pragma unroll
+                for (int b = 0; b < 7; ++b) idx += (s_bounds[b] < v[j]) ? 1 : 0;
+                s_code[wib][lane * E + j] = static_cast<uint8_t>(idx);
+                if (with_qjl) {
+                    const float r = __fsub_rn(v[j], s_cent[idx]);
+                    s_stage[vi * RS + lane * E + j] = r;     // the residual replaces the vector
+                    const float sg = qjl_sign_is_positive(qjl_seed, static_cast<uint32_t>(lane * E + j)) ? 1.0f : -1.0f;
+                    if (__fmul_rn(r, sg) > 0.0f) my_bits |= 1u << j;
+                }
+            }
+            if (with_qjl && my_bits) atomicOr(&s_bits[wib][(lane * E) >> 5], my_bits << ((lane * E) & 31));
+            __syncwarp();
+            if (with_qjl && lane < QPH) dst.qjl_words[vec * QPH + lane] = s_bits[wib][lane];
+            for (int w = lane; w < WPH; w += 32) {
+                uint32_t word = 0;
+#pragma unroll
+                for (int k = 0; k < 10; ++k) {
+                    const int e = w * 10 + k;
+                    if (e < D) word |= (static_cast<uint32_t>(s_code[wib][e]) & 7u) << (3 * k);
+                }
+                dst.words[vec * WPH + w] = word;
+            }
+            __syncwarp();
+        }
+        // ---- residual norms: one thread per vector again ----
+        if (with_qjl) {
+            __syncthreads();
+            if (tid < nb) {
+                float acc = 0.0f;
+                for (int j = 0; j < D; ++j) {
+                    const float t = s_stage[tid * RS + j];
+                    acc = __fadd_rn(acc, __fmul_rn(t, t));
+                }
+                const long gvec = base + tid, sidx = gvec / vec_per_seg;
+                tab.seg[sidx].qjl_norms[gvec - sidx * vec_per_seg] = __fsqrt_rn(acc);
+            }
+        }
+    }
+}
+
 // ---- range decoder (src/kv_cache.cpp:292-365) -------------------------------------------------
 template <int E>
 __global__ void __launch_bounds__(128) kv_decode_kernel(const uint32_t* __restrict__ words, const float* __restrict__ norms,
@@ -1103,6 +1238,36 @@ void launch_kv_encode_segments(const void* x, bool x_is_f16, long n_vec, long ve
     for (int i = 0; i < n_segs; ++i) tab.seg[i] = KvEncodeDst{segs[i].words, segs[i].norms, segs[i].qjl_words, segs[i].qjl_norms};
     const float scale = std::sqrt(static_cast<float>(head_dim));             // src/kv_cache.cpp:72
     const float inv_sqrt = 1.0f / std::sqrt(static_cast<float>(head_dim));   // src/rotation.cpp:301
+    // Bulk appends go through the batched kernel (one thread per vector for the sequential sums);
+    // a handful of vectors (a decode step) keep the warp-per-vector kernel and its lower latency.
+    if (n_vec >= 512) {
+#define TQ_ENCB(EV)                                                                                                       \
+    {                                                                                                                     \
+        constexpr int kVB = KvBatch<EV>::kVecs;                                                                           \
+        const int smem = kVB * (32 * EV + 1) * static_cast<int>(sizeof(float));                                           \
+        long blocks = (n_vec + kVB - 1) / kVB;                                                                            \
+        if (blocks > 148 * 3) blocks = 148 * 3;                                                                           \
+        static bool configured[2][64] = {{false}};                                                                        \
+        int dev = 0;                                                                                                      \
+        TQ_CUDA(cudaGetDevice(&dev));                                                                                     \
+        const int ti = x_is_f16 ? 0 : 1;                                                                                  \
+        if (dev < 0 || dev >= 64 || !configured[ti][dev]) {                                                               \
+            if (x_is_f16) TQ_CUDA(cudaFuncSetAttribute(kv_encode_batch_kernel<EV, __half>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem)); \
+            else TQ_CUDA(cudaFuncSetAttribute(kv_encode_batch_kernel<EV, float>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));           \
+            if (dev >= 0 && dev < 64) configured[ti][dev] = true;                                                         \
+        }                                                                                                                 \
+        if (x_is_f16)                                                                                                     \
+            kv_encode_batch_kernel<EV, __half><<<static_cast<unsigned>(blocks), kKvBatchThreads, smem, stream>>>(                     \
+                static_cast<const __half*>(x), n_vec, wht_seed, qjl_seed, with_qjl ? 1 : 0, scale, inv_sqrt, tab, vec_per_seg); \
+        else                                                                                                              \
+            kv_encode_batch_kernel<EV, float><<<static_cast<unsigned>(blocks), kKvBatchThreads, smem, stream>>>(                      \
+                static_cast<const float*>(x), n_vec, wht_seed, qjl_seed, with_qjl ? 1 : 0, scale, inv_sqrt, tab, vec_per_seg);  \
+    }
+        TQ_D_SWITCH(head_dim, TQ_ENCB)
+#undef TQ_ENCB
+        TQ_CUDA(cudaGetLastError());
+        return;
+    }
     const int grid = grid_for_warps(n_vec, 4, 148 * 16);
 #define TQ_ENC(EV)                                                                                                      \
     if (x_is_f16)                                                                                                       \
