@@ -252,6 +252,11 @@ def run_cuda(args):
                     raise RuntimeError(L.tq_last_error().decode())
                 exchange.broadcast(off, 1, OUT_F * 2, OUT_F * 2, stream=stream)
 
+    # The exchange's waits give up after a second, so the ranks must be within a second of each other
+    # when the first exchanging kernel starts: set-up times differ by more than that.
+    if world > 1:
+        torch.cuda.synchronize()
+        dist.barrier()
     # the launch-bound inner loop is captured once and replayed
     with torch.cuda.stream(stream):
         one_pass()
@@ -514,6 +519,9 @@ def bench_attention(tq, L, device, stream, rank, world, args, ctx):
     # on every call, so it cannot be captured in a CUDA graph)
     per_call = 1
 
+    if world > 1:                          # exchanging kernels wait a second at most: start together
+        torch.cuda.synchronize()
+        dist.barrier()
     with torch.cuda.stream(stream):
         for _ in range(3):
             call()
@@ -774,6 +782,9 @@ def bench_lm_head(tq, L, device, stream, rank, world, cbs, args):
 
     def timed(fn, graph=False):
         """(device us per call, host us per call when issued eagerly)"""
+        if world > 1:                      # exchanging kernels wait a second at most: start together
+            torch.cuda.synchronize()
+            dist.barrier()
         with torch.cuda.stream(stream):
             for _ in range(3):
                 fn()
@@ -1029,6 +1040,8 @@ def bench_c4_decode_step(tq, L, device, stream, rank, world, cbs, args):
                 layer_step(li)
 
         torch.cuda.synchronize()           # the inputs were made on the default stream
+        if world > 1:
+            dist.barrier()                 # exchanging kernels wait a second at most: start together
         with torch.cuda.stream(stream):
             one_pass()                     # allocates scratch, uploads attention descriptors per layer
             x.copy_(x0)
@@ -1096,6 +1109,8 @@ def bench_c4_decode_step(tq, L, device, stream, rank, world, cbs, args):
         got = torch.empty((batch, rows), device=device, dtype=torch.float16)
         cnt = batch * rows
         torch.cuda.synchronize()           # the inputs were made on the default stream
+        if world > 1:
+            dist.barrier()
         with torch.cuda.stream(stream):
             if exchange is None:
                 tmp = shard.forward(xl, stream=stream)
