@@ -713,36 +713,38 @@ def bench_prefill(tq, L, layers, device, stream, args):
 
 def bench_decoder_layer(tq, L, device, stream, cbs, args):
     """The seven projections of a Qwen2.5-7B-shaped decoder layer (hidden 3584, intermediate 18944,
-    28 query / 4 KV heads of 128), TQ8, at batch 1, 8 and 64: one pass = q, k, v, o, gate, up, down
+    28 query / 4 KV heads of 128), TQ8, at batch 1, 8, 16 and 64: one pass = q, k, v, o, gate, up, down
     back to back (233 MB of codes per pass > L2).  Only the linears are timed (no attention, norms
-    or activations: those are outside the path)."""
+    or activations).  `fused` is the same layer with q/k/v stored as one 4608-row matrix and gate/up as
+    one 37888-row matrix (four launches; possible when the projections that share x are quantised with
+    the same rotation seeds).  Also: the widest projection's result against a matmul over its
+    dequantised weights, and 2048-row prefill on these shapes."""
     import torch
     hidden, inter, q_out, kv_out = 3584, 18944, 28 * 128, 4 * 128
     shapes = [("q", q_out, hidden), ("k", kv_out, hidden), ("v", kv_out, hidden), ("o", hidden, q_out),
               ("gate", inter, hidden), ("up", inter, hidden), ("down", hidden, inter)]
-    lins = []
-    for i, (_, out_f, in_f) in enumerate(shapes):
-        lins.append(make_layer(tq, 7000 + i, device, cbs, out_f=out_f, in_f=in_f)[0])
+    fused_shapes = [("qkv", q_out + 2 * kv_out, hidden), ("o", hidden, q_out), ("gate_up", 2 * inter, hidden), ("down", hidden, inter)]
     code_bytes = sum(o * i for _, o, i in shapes)
     sp = C.c_void_p(stream.cuda_stream)
     g = torch.Generator(device=device).manual_seed(77)
-    res = {"workload": "config 1: q/k/v/o/gate/up/down of a Qwen2.5-7B-shaped layer, TQ8, block 128",
-           "code_bytes_per_pass": code_bytes}
-    for batch in (1, 8, 64):
-        xs = [torch.randn((batch, in_f), generator=g, device=device).half() for _, _, in_f in shapes]
-        ys = [torch.empty((batch, out_f), device=device, dtype=torch.float16) for _, out_f, _ in shapes]
+    res = {"workload": "q/k/v/o/gate/up/down of a Qwen2.5-7B-shaped layer, TQ8, block 128", "code_bytes_per_pass": code_bytes}
+    peak_tf = None
+    pth = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(pth):
+        peak_tf = float(json.load(open(pth)).get("bf16_tflops", 0)) or None
+    peak_tf = peak_tf or 1590.0
 
+    def time_pass(lins, xs, ys, batch, reps):
         def one_pass():
             for lin, x, y in zip(lins, xs, ys):
                 rc = L.tq_linear_forward(lin.handle, C.c_void_p(x.data_ptr()), tq.TQ_F16, batch, C.c_void_p(y.data_ptr()), sp)
                 if rc:
                     raise RuntimeError(L.tq_last_error().decode())
-
+        torch.cuda.synchronize()
         with torch.cuda.stream(stream):
             for _ in range(3):
                 one_pass()
         torch.cuda.synchronize()
-        reps = 10
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         with torch.cuda.stream(stream):
             e0.record(stream)
@@ -750,10 +752,45 @@ def bench_decoder_layer(tq, L, device, stream, cbs, args):
                 one_pass()
             e1.record(stream)
         torch.cuda.synchronize()
-        us = e0.elapsed_time(e1) * 1e3 / reps
-        res[f"b{batch}"] = {"us_per_layer": us, "tok_per_s": batch / (us * 1e-6), "code_gb_per_s": code_bytes / (us * 1e-6) / 1e9}
-    for lin in lins:
-        lin.close()
+        return e0.elapsed_time(e1) * 1e3 / reps
+
+    for tag, shp in (("", shapes), ("fused_", fused_shapes)):
+        lins = [make_layer(tq, 7000 + i, device, cbs, out_f=out_f, in_f=in_f)[0] for i, (_, out_f, in_f) in enumerate(shp)]
+        for batch in (1, 8, 16, 64):
+            xs = [torch.randn((batch, in_f), generator=g, device=device).half() for _, _, in_f in shp]
+            ys = [torch.empty((batch, out_f), device=device, dtype=torch.float16) for _, out_f, _ in shp]
+            us = time_pass(lins, xs, ys, batch, 10)
+            res[f"{tag}b{batch}"] = {"us_per_layer": us, "tok_per_s": batch / (us * 1e-6), "code_gb_per_s": code_bytes / (us * 1e-6) / 1e9,
+                                     "launches_per_layer": len(shp) if batch <= 8 else None}
+        if tag == "":
+            # the widest dot products of the layer (down_proj, K = 18944): result against fp32 matmul over
+            # this library's own dequantised weights (which the parity tests hold bit-equal to the reference's)
+            down = lins[-1]
+            wd = torch.empty((hidden, inter), device=device, dtype=torch.float16)
+            down.dequantize(out=wd)
+            for batch in (1, 8, 64):
+                xb = torch.randn((batch, inter), generator=g, device=device).half()
+                yb = down.forward(xb)
+                torch.cuda.synchronize()
+                ref = xb.float() @ wd.float().t()
+                res[f"down_proj_rel_l2_b{batch}"] = float((yb.float() - ref).norm() / ref.norm())
+            del wd
+            # 2048-row prefill on this layer's shapes (rotation + GEMM), one projection at a time
+            pf = {}
+            for (name, out_f, in_f), lin in zip(shp, lins):
+                if name in ("k", "v", "up"):
+                    continue
+                xp = torch.randn((2048, in_f), generator=g, device=device).half()
+                yp = torch.empty((2048, out_f), device=device, dtype=torch.float16)
+                us = time_pass([lin], [xp], [yp], 2048, 5)
+                tf = 2.0 * 2048 * out_f * in_f / (us * 1e-6) / 1e12
+                pf[name] = {"shape": f"{out_f}x{in_f}", "us": us, "tflops": tf, "frac_of_tensor_peak": tf / peak_tf}
+                del xp, yp
+            res["prefill_2048_rows"] = pf
+        for lin in lins:
+            lin.close()
+        del lins
+        torch.cuda.empty_cache()
     return res
 
 
@@ -1098,13 +1135,14 @@ def bench_c4_decode_step(tq, L, device, stream, rank, world, cbs, args):
         rows, cols, batch = 512, 2048, 3
         gq = torch.Generator(device=device).manual_seed(4242)            # the same on every rank
         wfull = (torch.randn((rows, cols), generator=gq, device=device) * 0.02).half().float()
-        qwf = tq.quantize_weight(wfull, cbs[0], cbs[1], tq.QuantizerConfig(4, 4, BLOCK, True))
-        full = tq.TurboQuantLinear(cols, rows, qwf, cbs[0], cbs[1], BLOCK)
+        cbc = tq.generate_codebook(4)       # analytic: the same on every rank (the fitted ones come from rank-seeded weights)
+        qwf = tq.quantize_weight(wfull, cbc, cbc, tq.QuantizerConfig(4, 4, BLOCK, True))
+        full = tq.TurboQuantLinear(cols, rows, qwf, cbc, cbc, BLOCK)
         xs = torch.randn((batch, cols), generator=gq, device=device).half()
         want = full.forward(xs)
         pp, pr, nrm, (c0, c1) = shard_quantized_cols(qwf.packed_primary, qwf.packed_residual, qwf.norms, cols, BLOCK, rank, world)
         shard = tq.TurboQuantLinear(c1 - c0, rows, tq.QuantizedWeight(np.ascontiguousarray(pp), np.ascontiguousarray(pr), nrm, qwf.seeds),
-                                    cbs[0], cbs[1], BLOCK)
+                                    cbc, cbc, BLOCK)
         xl = xs[:, c0:c1].contiguous()
         got = torch.empty((batch, rows), device=device, dtype=torch.float16)
         cnt = batch * rows
