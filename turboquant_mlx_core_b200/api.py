@@ -344,11 +344,12 @@ class TQKVCache:
         """Make room for `tokens` tokens of `layer` up front (growth otherwise doubles and copies)."""
         check(self._L.tq_kv_reserve(self._h, layer, int(tokens), _stream_ptr(stream)), "TQKVCache.reserve")
 
-    ATTENTION_AUTO, ATTENTION_LOADS, ATTENTION_PIPELINE = 0, 1, 2
+    ATTENTION_AUTO, ATTENTION_LOADS, ATTENTION_PIPELINE, ATTENTION_TENSOR_MEMORY = 0, 1, 2, 3
 
     def set_attention_kernel(self, kernel: int):
         """Decode-attention kernel for calls that name this cache first: automatic (by job size),
-        the load-based kernel, or the bulk-copy pipeline."""
+        the load-based kernel, the bulk-copy pipeline, or the tensor-memory kernel (head_dim 128, four KV
+        heads; other shapes fall back to the automatic choice)."""
         check(self._L.tq_kv_set_attention_kernel(self._h, int(kernel)), "TQKVCache.set_attention_kernel")
 
     def check_attention_status(self):

@@ -434,7 +434,7 @@ public:
     DeviceBuffer& attn_lse() { return attn_lse_; }
     int attention_kernel() const { return attention_kernel_; }
     void set_attention_kernel(int k) {
-        TQ_REQUIRE(k >= 0 && k <= 2, "attention kernel: 0 (automatic), 1 (load-based) or 2 (bulk-copy pipeline)");
+        TQ_REQUIRE(k >= 0 && k <= 3, "attention kernel: 0 (automatic), 1 (load-based), 2 (bulk-copy pipeline) or 3 (tensor memory)");
         attention_kernel_ = k;
     }
     // Status word of the attention kernels: page-locked host memory that the device writes

@@ -120,6 +120,7 @@ void launch_quantize_weight(const float* d_weight, long out, int in, const float
 struct AttnPlan {
     int n_splits;     // context splits per sequence
     int pipe_heads;   // KV heads per CTA of the bulk-copy pipeline kernel; 0: load-based kernels
+    int tensor_memory;   // 1: the tensor-memory kernel (tq_attn_tc.cu) instead of either
 };
 
 struct KvEncodeSegment {

@@ -7,7 +7,9 @@
 //   QJL    : ceil(d/32) uint32 sign words + fp32 residual norm per key vector
 // so a snapshot in the reference's wire format is a plain copy.
 #include <cmath>
+#include <cstdlib>
 
+#include "tq_attn.cuh"
 #include "tq_common.cuh"
 #include "tq_kernels.cuh"
 
@@ -322,16 +324,6 @@ __global__ void __launch_bounds__(128) kv_decode_kernel(const uint32_t* __restri
 // (max, sum, accumulator) triples are merged by attn_combine_kernel.
 constexpr int kAttnGMax = 8;
 
-struct AttnSeq {
-    const uint32_t* k_words;
-    const uint32_t* v_words;
-    const float* k_norms;
-    const float* v_norms;
-    const uint32_t* qjl_words;
-    const float* qjl_norms;
-    int start, end;
-};
-
 template <int E, typename QT>
 __global__ void __launch_bounds__(128) attn_partial_kernel(const AttnSeq* __restrict__ seqs, const QT* __restrict__ q,
                                                            int q_heads, int kv_heads, int n_splits, uint32_t k_seed,
@@ -507,10 +499,7 @@ __global__ void __launch_bounds__(128) attn_combine_kernel(const float* __restri
 // the same on both operands of each product and is undone when the partial result is written.
 // V tiles are looked up in [token x dim] order and transposed in registers (movmatrix).
 constexpr int kMmaThreads = 128;
-// The table holds kCentroidScale * centroid: with this factor all four centroid magnitudes
-// round to fp16 with a relative error below 1.4e-5 (unscaled: up to 3e-4, which the softmax
-// amplifies); the factor is divided out of the key and value norms.
-constexpr float kCentroidScale = 1.1979075f;
+constexpr float kCentroidScale = kAttnCentroidScale;
 
 __device__ __forceinline__ void mma_f16(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
                                         uint32_t b1) {
@@ -828,7 +817,7 @@ __global__ void __launch_bounds__(kMmaThreads, 3) attn_mma_kernel(const AttnSeq*
 // are masked.  Every mbarrier wait is bounded: on a time-out the CTA raises *status, lets the
 // copies in flight land, and returns without writing a result.
 constexpr int kPipeStages = 4;
-constexpr float kSoftmaxSlack = 2.0f;
+constexpr float kSoftmaxSlack = kAttnSoftmaxSlack;
 constexpr int kPipeWarpsPerSm = 16;   // 128 registers per thread
 constexpr unsigned long long kPipeWaitLimitNs = 200ull * 1000 * 1000;
 
@@ -1318,6 +1307,31 @@ static int attn_pipe_heads(int head_dim, int kv_heads) {
 AttnPlan attn_make_plan(int n_seqs, int q_heads, int kv_heads, int head_dim, int max_tok, int sm_count, int kernel) {
     const int G = q_heads / kv_heads;
     const int gchunks = (G + kAttnGMax - 1) / kAttnGMax;
+    if (kernel == 0) {
+        static const int env_kernel = [] {
+            const char* e = std::getenv("TQ_ATTENTION_KERNEL");
+            return e ? std::atoi(e) : 0;
+        }();
+        kernel = env_kernel;
+    }
+    if (kernel == 3 && head_dim == 128 && kv_heads == 4) {
+        // tensor-memory kernel: a CTA is (sequence, query-head group, split) over all four KV heads
+        const long ctas_per_split = static_cast<long>(n_seqs) * gchunks;
+        const long resident = static_cast<long>(sm_count) * kAttnTcCtasPerSm;
+        const int max_splits = std::max(1, std::min(512, max_tok / 256));
+        AttnPlan plan{1, 0, 1};
+        double best = 1e300;
+        for (int n = 1; n <= max_splits; ++n) {
+            const long waves = (ctas_per_split * n + resident - 1) / resident;
+            const double cost = static_cast<double>(waves) * (static_cast<double>(max_tok) / n + 256.0);
+            if (cost < best * 0.999) {
+                best = cost;
+                plan.n_splits = n;
+            }
+        }
+        return plan;
+    }
+    if (kernel == 3) kernel = 0;
     int gh = kernel == 1 ? 0 : attn_pipe_heads(head_dim, kv_heads);
     if (gh && kernel == 0) {
         const long slots = static_cast<long>(sm_count) * (kPipeWarpsPerSm / gh);
@@ -1329,7 +1343,7 @@ AttnPlan attn_make_plan(int n_seqs, int q_heads, int kv_heads, int head_dim, int
     const double walk = gh ? 1.0 : 0.25, setup = gh ? 96.0 : 40.0;
     const int min_tok = gh ? 128 : 256;
     const int max_splits = std::max(1, std::min(gh ? 512 : 128, max_tok / min_tok));
-    AttnPlan plan{1, gh};
+    AttnPlan plan{1, gh, 0};
     double best = 1e300;
     for (int n = 1; n <= max_splits; ++n) {
         const long waves = (ctas_per_split * n + resident - 1) / resident;
@@ -1390,6 +1404,14 @@ void launch_kv_attention(const void* d_seqs, int n_seqs, const void* q, bool q_i
                                                                  inv_scale_d, attn_scale, gamma, part_acc, part_ml);     \
     attn_combine_kernel<EV><<<static_cast<int>((n_rows + 3) / 4), 128, 0, stream>>>(part_acc, part_ml, n_rows, n_splits, \
                                                                                    v_seed, inv_sqrt, inv_scale_d, out, lse);
+    if (plan.tensor_memory) {
+        launch_attn_tc(static_cast<const AttnSeq*>(d_seqs), n_seqs, q, q_is_f16, q_heads, kv_heads, n_splits, k_seed, qjl_seed, use_qjl,
+                       inv_sqrt, inv_scale_d, attn_scale, gamma, part_acc, part_ml, status, stream);
+        attn_combine_kernel<4><<<static_cast<int>((n_rows + 3) / 4), 128, 0, stream>>>(part_acc, part_ml, n_rows, n_splits,
+                                                                                      v_seed, inv_sqrt, inv_scale_d, out, lse);
+        TQ_CUDA(cudaGetLastError());
+        return;
+    }
     if (const int gh = plan.pipe_heads) {
         TQ_REQUIRE(gh == attn_pipe_heads(head_dim, kv_heads), "attention: plan does not match the cache shape");
         const AttnSeq* seqs = static_cast<const AttnSeq*>(d_seqs);
