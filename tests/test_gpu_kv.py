@@ -266,13 +266,20 @@ def test_attention_head_counts_and_ragged_ranges(tq, oracle, heads, q_heads):
                                 ex["qjl_words"], ex["qjl_norms"], layer=0, start=start, end=end, use_qjl=use_qjl)
         assert np.all(np.isfinite(out.astype(np.float32)))
         assert rel_l2(out[0], want) < ATTN_TOL, (start, end, use_qjl, rel_l2(out[0], want))
+        if heads == 4:
+            # the tensor-memory kernel (tcgen05): tiles of 32 tokens, partial first and last tiles
+            c.set_attention_kernel(c.ATTENTION_TENSOR_MEMORY)
+            tm = tq.compressed_attention([c], 0, q, start=start, end=end, use_qjl=use_qjl)
+            c.check_attention_status()
+            assert np.all(np.isfinite(tm.astype(np.float32)))
+            assert rel_l2(tm[0], want) < ATTN_TOL, ("tensor memory", start, end, use_qjl, rel_l2(tm[0], want))
     c.close()
 
 
 @pytest.mark.parametrize("tokens", [4096, 32768])
 def test_attention_at_benchmark_contexts_matches_oracle(tq, oracle, tokens):
     """One sequence, 4 KV / 28 query heads, at the context lengths the throughput figures are quoted
-    on: both CUDA kernels (bulk-copy pipeline and load-based), residual bits off and on, each against
+    on: the three CUDA kernels (bulk-copy pipeline, load-based, tensor memory), residual bits off and on, each against
     the CPU checker (mirrors src/attention_dispatch.cpp:58-73 over the fp16 keys and values that
     src/kv_cache.cpp:292-365 would hand it).  At these lengths the context is cut into dozens of
     splits, the softmax reference moves lazily and the parts are merged in fixed order."""
@@ -285,7 +292,7 @@ def test_attention_at_benchmark_contexts_matches_oracle(tq, oracle, tokens):
     for use_qjl in (False, True):
         want = oracle.attention(q[0].astype(np.float32), heads, ex["k_words"], ex["k_norms"], ex["v_words"], ex["v_norms"],
                                 ex["qjl_words"], ex["qjl_norms"], layer=0, use_qjl=use_qjl)
-        for kernel in (c.ATTENTION_PIPELINE, c.ATTENTION_LOADS):
+        for kernel in (c.ATTENTION_PIPELINE, c.ATTENTION_LOADS, c.ATTENTION_TENSOR_MEMORY):
             c.set_attention_kernel(kernel)
             out = tq.compressed_attention([c], 0, q, use_qjl=use_qjl)
             c.check_attention_status()

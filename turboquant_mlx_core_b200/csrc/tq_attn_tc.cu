@@ -13,9 +13,11 @@
 // and writes 64 registers to its tensor-memory lane (keys, signs) or sixteen 16-byte chunks to the
 // value tile in shared memory (MN-major, no swizzle: [8-dim chunk][row][8 fp16]).
 //
-// Warps: 0-3 workers, 4 issues the MMAs (one thread), 5 issues the bulk copies (one thread).  The
-// cache records of a tile are fetched with cp.async.bulk into a two-stage ring (six arrays, each a
-// contiguous slab because records are token-major with the four heads adjacent).
+// Warps: 0-3 key group (keys and signs into tensor memory, upper half of the value tile), 4-7 value
+// group (lower half of the value tile, scores, softmax, P'), 8 issues the MMAs (one thread), 9 the
+// bulk copies (one thread).  Thread t of either group owns record t of the tile and tensor-memory
+// lane t.  The cache records of a tile are fetched with cp.async.bulk into a two-stage ring (six
+// arrays, each a contiguous slab because records are token-major with the four heads adjacent).
 //
 // Softmax: the reference maximum per (head, query head) is shared by the CTA and lazy: it moves
 // only when some score exceeds it by more than kAttnSoftmaxSlack; then all workers meet, rescale
@@ -36,8 +38,9 @@ namespace {
 
 __constant__ float kTcC3[8] = {-2.152176f, -1.344318f, -0.756130f, -0.245379f, 0.245379f, 0.756130f, 1.344318f, 2.152176f};
 
-constexpr int kTcThreads = 192;
-constexpr int kTcWorkers = 128;
+constexpr int kTcThreads = 320;
+constexpr int kTcGroup = 128;   // threads of a worker group
+constexpr int kTcMmaWarp = 8, kTcCopyWarp = 9;
 constexpr int kTcTile = 32;     // tokens per tile
 constexpr int kTcStages = 2;
 constexpr uint32_t kTcTmemCols = 256;
@@ -55,8 +58,8 @@ struct TcSmem {
     static constexpr int kOffP = kOffVhat + 32768;             // P', 4 chunks x 2 KB
     static constexpr int kOffBq = kOffP + 8192;                // rotated queries, K-major core matrices
     static constexpr int kOffBs = kOffBq + 8192;               // sign-weighted rotated queries
-    static constexpr int kOffBars = kOffBs + 8192;             // 8 mbarriers
-    static constexpr int kOffM = kOffBars + 64;                // reference maxima [32]
+    static constexpr int kOffBars = kOffBs + 8192;             // 9 mbarriers
+    static constexpr int kOffM = kOffBars + 128;               // reference maxima [32], log2 domain
     static constexpr int kOffFactor = kOffM + 128;             // rescale factors [32]
     static constexpr int kOffWmax = kOffFactor + 128;          // per-warp maxima / sums [4][32]
     static constexpr int kSmemBytes = kOffWmax + 512;
@@ -70,7 +73,9 @@ __device__ __forceinline__ unsigned long long tc_timer_ns() {
     asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
     return t;
 }
-__device__ __forceinline__ bool tc_wait(uint32_t bar, uint32_t parity, volatile unsigned int* abort_flag) {
+// Bounded wait.  sleep_ns > 0: back off between polls (the threads that only issue copies or MMAs
+// wait most of the time; a busy poll loop would take issue slots from the workers).
+__device__ __forceinline__ bool tc_wait(uint32_t bar, uint32_t parity, volatile unsigned int* abort_flag, unsigned sleep_ns = 0) {
     unsigned long long t0 = 0;
     for (uint32_t spin = 0;; ++spin) {
         uint32_t done;
@@ -79,9 +84,13 @@ __device__ __forceinline__ bool tc_wait(uint32_t bar, uint32_t parity, volatile 
                      : "r"(bar), "r"(parity)
                      : "memory");
         if (done) return true;
-        if ((spin & 15) == 15 && *abort_flag) return false;
-        if (spin == 64) t0 = tc_timer_ns();
-        if (spin > 64 && (spin & 63) == 0 && tc_timer_ns() - t0 > kTcWaitLimitNs) return false;
+        if (sleep_ns) __nanosleep(sleep_ns);
+        if ((spin & 63u) == 63u) {
+            if (*abort_flag) return false;
+            const unsigned long long now = tc_timer_ns();
+            if (t0 == 0) t0 = now;
+            else if (now - t0 > kTcWaitLimitNs) return false;
+        }
     }
 }
 // The same for a whole warp: the outcome is made uniform, because the tensor-memory accesses that
@@ -100,6 +109,11 @@ __device__ __forceinline__ void tc_copy(uint32_t dst, const void* src, uint32_t 
 __device__ __forceinline__ uint32_t tc_pack_half2(float lo, float hi) {
     const __half2 h = __floats2half2_rn(lo, hi);
     return *reinterpret_cast<const uint32_t*>(&h);
+}
+__device__ __forceinline__ float tc_ex2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
 }
 // instruction descriptor: D fp32, A and B fp16, M 128, N 32; bits 15 / 16: A / B are MN-major
 constexpr uint32_t kIdescS = (1u << 4) | ((32u >> 3) << 17) | ((128u >> 4) << 24);
@@ -149,9 +163,9 @@ __device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t (&v)[32]) {
         : "r"(taddr));
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
-// Barrier 1 over the 128 workers.
-__device__ __forceinline__ void tc_workers_sync() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
-__device__ __forceinline__ bool tc_workers_or(bool pred) {
+// Barriers 1 (value group) and 2 (key group), 128 threads each.
+__device__ __forceinline__ void tc_group_sync(int id) { asm volatile("bar.sync %0, 128;" ::"r"(id) : "memory"); }
+__device__ __forceinline__ bool tc_value_group_or(bool pred) {
     uint32_t out;
     asm volatile("{ .reg .pred p, q; setp.ne.u32 p, %1, 0; bar.red.or.pred q, 1, 128, p; selp.u32 %0, 1, 0, q; }"
                  : "=r"(out)
@@ -169,6 +183,7 @@ __global__ void __launch_bounds__(kTcThreads, kAttnTcCtasPerSm) attn_tc_kernel(c
                                                                               unsigned int* __restrict__ status) {
     using LY = TcSmem;
     constexpr int D = 128;
+    constexpr float kLog2e = 1.4426950408889634f, kLn2 = 0.6931471805599453f;
     extern __shared__ __align__(128) unsigned char tc_smem[];
     __shared__ __align__(16) uint32_t s_lut[64 * 32];   // pair table [pair index][lane]
     __shared__ unsigned int s_abort;
@@ -191,8 +206,10 @@ __global__ void __launch_bounds__(kTcThreads, kAttnTcCtasPerSm) attn_tc_kernel(c
     unsigned char* const base = tc_smem;
     const uint32_t raw = tc_smem_addr(tc_smem);
     const uint32_t bar0 = raw + LY::kOffBars;
+    // full / empty per stage; a_ready: keys and signs of a tile are in tensor memory; s_ready: its scores are;
+    // d_free: the scores have been read; vp_ready: value tile and P' are written; v_free: O += V~^T P' is done
     const uint32_t bar_full = bar0, bar_empty = bar0 + 8u * kTcStages, bar_aready = bar0 + 32u, bar_sready = bar0 + 40u,
-                   bar_vpready = bar0 + 48u, bar_vfree = bar0 + 56u;
+                   bar_vpready = bar0 + 48u, bar_vfree = bar0 + 56u, bar_dfree = bar0 + 64u;
     static_assert(kTcStages == 2, "barrier offsets above assume two stages");
     float* const s_m = reinterpret_cast<float*>(base + LY::kOffM);
     float* const s_factor = reinterpret_cast<float*>(base + LY::kOffFactor);
@@ -203,16 +220,17 @@ __global__ void __launch_bounds__(kTcThreads, kAttnTcCtasPerSm) attn_tc_kernel(c
         s_abort = 0u;
         for (int s = 0; s < kTcStages; ++s) {
             asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar_full + 8u * s), "r"(1) : "memory");
-            asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar_empty + 8u * s), "r"(4) : "memory");
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar_empty + 8u * s), "r"(8) : "memory");
         }
         asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar_aready), "r"(4) : "memory");
         asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar_sready), "r"(1) : "memory");
-        asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar_vpready), "r"(4) : "memory");
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar_vpready), "r"(8) : "memory");
         asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar_vfree), "r"(1) : "memory");
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar_dfree), "r"(4) : "memory");
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (tid < 32) s_m[tid] = -INFINITY;
-    if (warp == 4) {
+    if (warp == kTcMmaWarp) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tc_smem_addr(&s_tmem_base)),
                      "r"(kTcTmemCols)
                      : "memory");
@@ -245,16 +263,18 @@ __global__ void __launch_bounds__(kTcThreads, kAttnTcCtasPerSm) attn_tc_kernel(c
         }
     };
     // the first tiles start moving while the tables below are set up
-    if (warp == 5 && lane == 0)
+    if (warp == kTcCopyWarp && lane == 0)
         for (int it = 0; it < min(kTcStages, n_tiles); ++it) issue_tile(it);
 
-    // ---- set-up by the workers: pair table, P' zeros, rotated queries ------------------------------
-    if (warp < 4) {
-        for (int i = tid; i < 64 * 32; i += kTcWorkers) {
+    // ---- set-up: pair table and P' zeros (value group), rotated queries (key group) ------------------
+    if (warp >= 4 && warp < 8) {
+        for (int i = tid - kTcGroup; i < 64 * 32; i += kTcGroup) {
             const int idx = i >> 5;
             s_lut[i] = tc_pack_half2(kAttnCentroidScale * kTcC3[idx & 7], kAttnCentroidScale * kTcC3[idx >> 3]);
         }
-        for (int i = tid; i < 8192 / 16; i += kTcWorkers) reinterpret_cast<uint4*>(base + LY::kOffP)[i] = make_uint4(0u, 0u, 0u, 0u);
+        for (int i = tid - kTcGroup; i < 8192 / 16; i += kTcGroup) reinterpret_cast<uint4*>(base + LY::kOffP)[i] = make_uint4(0u, 0u, 0u, 0u);
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    } else if (warp < 4) {
         // warp = KV head: fp16-round, sign, butterfly, 1/sqrt(d), fp16-round; row n = 8 * head + h
         __half* const scratch = reinterpret_cast<__half*>(base + LY::kOffVhat);   // [32][128], natural dim order
         for (int h = 0; h < 8; ++h) {
@@ -274,9 +294,9 @@ __global__ void __launch_bounds__(kTcThreads, kAttnTcCtasPerSm) attn_tc_kernel(c
             *reinterpret_cast<uint2*>(base + LY::kOffBq + warp * 2048 + (lane >> 1) * 128 + h * 16 + (lane & 1) * 8) = make_uint2(lo, hi);
             *reinterpret_cast<uint2*>(scratch + (warp * 8 + h) * D + lane * 4) = make_uint2(lo, hi);
         }
-        tc_workers_sync();
+        tc_group_sync(2);
         // sign operand: column c = 16 * j + pp of the sign tile holds dims (32 j + pp, 32 j + pp + 16)
-        for (int idx = tid; idx < 32 * 64; idx += kTcWorkers) {
+        for (int idx = tid; idx < 32 * 64; idx += kTcGroup) {
             const int n = idx >> 6, c = idx & 63;
             const int e = 32 * (c >> 4) + (c & 15);
             const float s0 = qjl_sign_is_positive(qjl_seed, static_cast<uint32_t>(e)) ? 1.f : -1.f;
@@ -288,11 +308,31 @@ __global__ void __launch_bounds__(kTcThreads, kAttnTcCtasPerSm) attn_tc_kernel(c
     }
     __syncthreads();
 
-    if (warp == 5) {
+    // every worker thread owns record `row` of a tile (= 4 * token-in-tile + head) and tensor-memory lane `row`
+    const int row = 32 * (warp & 3) + lane;
+    const int hh = lane & 3, tt = row >> 2;
+    const uint32_t lane_off = static_cast<uint32_t>(lane) * 4u;
+    const uint32_t tm_lane = tmem + (static_cast<uint32_t>(32 * (warp & 3)) << 16);
+    auto lut_pair = [&](uint32_t word, int bit) -> uint32_t {
+        // byte offset ((word >> bit) & 63) * 128 + lane * 4: one shift, one logic op; the table's address is an immediate
+        const uint32_t sh = bit >= 7 ? (word >> (bit - 7)) : (word << (7 - bit));
+        return *reinterpret_cast<const uint32_t*>(reinterpret_cast<const unsigned char*>(s_lut) + ((sh & (63u << 7)) | lane_off));
+    };
+    // 16-byte chunk c of a record's value row (dims 8c .. 8c+7) -> value tile [chunk][row][8 fp16]
+    auto value_chunk = [&](const uint32_t (&vw)[13], int c) {
+        uint4 o;
+        o.x = lut_pair(vw[(4 * c) / 5], 6 * ((4 * c) % 5));
+        o.y = lut_pair(vw[(4 * c + 1) / 5], 6 * ((4 * c + 1) % 5));
+        o.z = lut_pair(vw[(4 * c + 2) / 5], 6 * ((4 * c + 2) % 5));
+        o.w = lut_pair(vw[(4 * c + 3) / 5], 6 * ((4 * c + 3) % 5));
+        *reinterpret_cast<uint4*>(base + LY::kOffVhat + c * 2048 + row * 16) = o;
+    };
+
+    if (warp == kTcCopyWarp) {
         // ---- copies: one thread keeps the ring full -----------------------------------------------
         if (lane == 0) {
             for (int it = kTcStages; it < n_tiles; ++it) {
-                if (!tc_wait(bar_empty + 8u * (it % kTcStages), static_cast<uint32_t>(it / kTcStages - 1) & 1u, abort_flag)) {
+                if (!tc_wait(bar_empty + 8u * (it % kTcStages), static_cast<uint32_t>(it / kTcStages - 1) & 1u, abort_flag, 64)) {
                     ok = false;
                     break;
                 }
@@ -300,18 +340,19 @@ __global__ void __launch_bounds__(kTcThreads, kAttnTcCtasPerSm) attn_tc_kernel(c
             }
         }
         __syncwarp();
-    } else if (warp == 4) {
+    } else if (warp == kTcMmaWarp) {
         // ---- MMA issue (one thread) -------------------------------------------------------------------
         if (lane == 0) {
             // no-swizzle descriptors, K-major and MN-major alike: the leading byte offset is the step to the next
             // core matrix along K (8 rows of 16 bytes, stored contiguously here), the stride byte offset the step
             // along M / N (the next 8 rows of a K-major operand, the next 8-element chunk of an MN-major one)
             const uint32_t lbo = 128u, sbo = 2048u;
-            const uint64_t desc_q = tc_desc(raw + LY::kOffBq, 128u, 2048u), desc_s = tc_desc(raw + LY::kOffBs, 128u, 2048u);
+            const uint64_t desc_q = tc_desc(raw + LY::kOffBq, lbo, sbo), desc_s = tc_desc(raw + LY::kOffBs, lbo, sbo);
             const uint64_t desc_v = tc_desc(raw + LY::kOffVhat, lbo, sbo), desc_p = tc_desc(raw + LY::kOffP, lbo, sbo);
             for (int it = 0; it < n_tiles; ++it) {
                 const uint32_t par = static_cast<uint32_t>(it) & 1u;
-                if (!tc_wait(bar_aready, par, abort_flag)) {
+                if (!tc_wait(bar_aready, par, abort_flag, 32) ||
+                    (it > 0 && !tc_wait(bar_dfree, static_cast<uint32_t>(it - 1) & 1u, abort_flag, 32))) {
                     ok = false;
                     break;
                 }
@@ -325,7 +366,7 @@ __global__ void __launch_bounds__(kTcThreads, kAttnTcCtasPerSm) attn_tc_kernel(c
                         tc_mma_ts(tmem + kColD2, tmem + kColAS + 8u * ks, desc_s + static_cast<uint64_t>(16 * ks), kIdescS, ks ? 1u : 0u);
                 }
                 tc_commit(bar_sready);
-                if (!tc_wait(bar_vpready, par, abort_flag)) {
+                if (!tc_wait(bar_vpready, par, abort_flag, 32)) {
                     ok = false;
                     break;
                 }
@@ -339,17 +380,76 @@ __global__ void __launch_bounds__(kTcThreads, kAttnTcCtasPerSm) attn_tc_kernel(c
         }
         __syncwarp();
     } else if (warp < 4) {
-        // ---- workers: one cache record per thread ----------------------------------------------------
-        const int row = 32 * warp + lane;       // = 4 * token-in-tile + head
-        const int hh = lane & 3, tt = row >> 2;
-        const uint32_t lane_off = static_cast<uint32_t>(lane) * 4u;
-        const uint32_t tm_lane = tmem + (static_cast<uint32_t>(32 * warp) << 16);
-        auto lut_pair = [&](uint32_t word, int bit) -> uint32_t {
-            const uint32_t sh = bit >= 7 ? (word >> (bit - 7)) : (word << (7 - bit));
-            return *reinterpret_cast<const uint32_t*>(reinterpret_cast<const unsigned char*>(s_lut) + ((sh & (63u << 7)) | lane_off));
-        };
-        const float kscale = inv_scale_d * attn_scale / kAttnCentroidScale;
+        // ---- key group: keys and residual signs into tensor memory, value chunks 8..15 -----------------
+        for (int it = 0; it < n_tiles; ++it) {
+            const int s = it % kTcStages;
+            if (!tc_wait_warp(bar_full + 8u * s, static_cast<uint32_t>(it / kTcStages) & 1u, abort_flag)) {
+                ok = false;
+                break;
+            }
+            const unsigned char* st = base + s * LY::kStageBytes;
+            const uint32_t* sk = reinterpret_cast<const uint32_t*>(st) + row * 13;
+            const uint32_t* sv = reinterpret_cast<const uint32_t*>(st + LY::kOffV) + row * 13;
+            uint32_t kw[13], vw[13];
+#pragma unroll
+            for (int j = 0; j < 13; ++j) {
+                kw[j] = sk[j];
+                vw[j] = sv[j];
+            }
+            uint4 sw = make_uint4(0u, 0u, 0u, 0u);
+            if (use_qjl) sw = *reinterpret_cast<const uint4*>(st + LY::kOffS + row * 16);
+            __syncwarp();
+            if (lane == 0) tc_arrive(bar_empty + 8u * s);
+            // the previous tile's score MMAs must have read the key and sign tiles
+            if (it > 0 && !tc_wait_warp(bar_sready, static_cast<uint32_t>(it - 1) & 1u, abort_flag)) {
+                ok = false;
+                break;
+            }
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            {
+                uint32_t a[16];
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) {
+                        const int p = 16 * c + i;
+                        a[i] = lut_pair(kw[p / 5], 6 * (p % 5));
+                    }
+                    tc_st16(tm_lane + kColAK + 16u * c, a);
+                }
+                if (use_qjl) {
+                    const uint32_t inv[4] = {~sw.x, ~sw.y, ~sw.z, ~sw.w};
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+#pragma unroll
+                        for (int pp = 0; pp < 16; ++pp) {
+                            const uint32_t sh = pp == 15 ? inv[j] : (inv[j] << (15 - pp));
+                            a[pp] = (sh & 0x80008000u) | 0x3C003C00u;
+                        }
+                        tc_st16(tm_lane + kColAS + 16u * j, a);
+                    }
+                }
+            }
+            asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) tc_arrive(bar_aready);
+            // the previous tile's O += V~^T P' must have read the value tile
+            if (it > 0 && !tc_wait_warp(bar_vfree, static_cast<uint32_t>(it - 1) & 1u, abort_flag)) {
+                ok = false;
+                break;
+            }
+#pragma unroll
+            for (int c = 8; c < 16; ++c) value_chunk(vw, c);
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) tc_arrive(bar_vpready);
+        }
+    } else {
+        // ---- value group: value chunks 0..7, scores, softmax, P' -----------------------------------------
+        const float kscale = inv_scale_d * attn_scale / kAttnCentroidScale * kLog2e;   // scores in the log2 domain
         const float qscale = gamma * kAttnCentroidScale;
+        const float slack = kAttnSoftmaxSlack * kLog2e;
         float l_run[8];
 #pragma unroll
         for (int g = 0; g < 8; ++g) l_run[g] = 0.f;
@@ -358,26 +458,16 @@ __global__ void __launch_bounds__(kTcThreads, kAttnTcCtasPerSm) attn_tc_kernel(c
             const int s = it % kTcStages;
             bool fail = !ok;
             float sc[8];
-            bool valid = false;
+            bool valid = false, trigger = false;
             float vnq = 0.f;
-            bool trigger = false;
             if (!fail && !tc_wait_warp(bar_full + 8u * s, static_cast<uint32_t>(it / kTcStages) & 1u, abort_flag)) fail = true;
             if (!fail) {
                 const unsigned char* st = base + s * LY::kStageBytes;
-                const uint32_t* sk = reinterpret_cast<const uint32_t*>(st) + row * 13;
                 const uint32_t* sv = reinterpret_cast<const uint32_t*>(st + LY::kOffV) + row * 13;
-                uint32_t kw[13], vw[13];
+                uint32_t vw[13];
 #pragma unroll
-                for (int j = 0; j < 13; ++j) {
-                    kw[j] = sk[j];
-                    vw[j] = sv[j];
-                }
-                uint4 sw = make_uint4(0u, 0u, 0u, 0u);
-                float qa = 0.f;
-                if (use_qjl) {
-                    sw = *reinterpret_cast<const uint4*>(st + LY::kOffS + row * 16);
-                    qa = reinterpret_cast<const float*>(st + LY::kOffQN)[row] * qscale;
-                }
+                for (int j = 0; j < 13; ++j) vw[j] = sv[j];
+                const float qa = use_qjl ? reinterpret_cast<const float*>(st + LY::kOffQN)[row] * qscale : 0.f;
                 const float kn = reinterpret_cast<const float*>(st + LY::kOffKN)[row] * kscale;
                 const float vn = reinterpret_cast<const float*>(st + LY::kOffVN)[row];
                 const int token = (tile0 + it) * kTcTile + tt;
@@ -385,53 +475,11 @@ __global__ void __launch_bounds__(kTcThreads, kAttnTcCtasPerSm) attn_tc_kernel(c
                 vnq = valid ? vn * (1.0f / kAttnCentroidScale) : 0.f;
                 __syncwarp();
                 if (lane == 0) tc_arrive(bar_empty + 8u * s);
-
-                // keys: 64 pairs in natural dim order -> tensor-memory columns kColAK .. +63 of this lane
-                {
-                    uint32_t a[16];
-#pragma unroll
-                    for (int c = 0; c < 4; ++c) {
-#pragma unroll
-                        for (int i = 0; i < 16; ++i) {
-                            const int p = 16 * c + i;
-                            a[i] = lut_pair(kw[p / 5], 6 * (p % 5));
-                        }
-                        tc_st16(tm_lane + kColAK + 16u * c, a);
-                    }
-                    if (use_qjl) {
-                        const uint32_t inv[4] = {~sw.x, ~sw.y, ~sw.z, ~sw.w};
-#pragma unroll
-                        for (int j = 0; j < 4; ++j) {
-#pragma unroll
-                            for (int pp = 0; pp < 16; ++pp) {
-                                const uint32_t sh = pp == 15 ? inv[j] : (inv[j] << (15 - pp));
-                                a[pp] = (sh & 0x80008000u) | 0x3C003C00u;
-                            }
-                            tc_st16(tm_lane + kColAS + 16u * j, a);
-                        }
-                    }
-                }
-                asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
-                asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-                __syncwarp();
-                if (lane == 0) tc_arrive(bar_aready);
-
-                // values: the previous tile's O += V~^T P' must have read the value tile and P'
                 if (it > 0 && !tc_wait_warp(bar_vfree, static_cast<uint32_t>(it - 1) & 1u, abort_flag)) fail = true;
                 if (!fail) {
-                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                    unsigned char* const vrow = base + LY::kOffVhat + row * 16;
 #pragma unroll
-                    for (int c = 0; c < 16; ++c) {
-                        uint4 o;
-                        o.x = lut_pair(vw[(4 * c) / 5], 6 * ((4 * c) % 5));
-                        o.y = lut_pair(vw[(4 * c + 1) / 5], 6 * ((4 * c + 1) % 5));
-                        o.z = lut_pair(vw[(4 * c + 2) / 5], 6 * ((4 * c + 2) % 5));
-                        o.w = lut_pair(vw[(4 * c + 3) / 5], 6 * ((4 * c + 3) % 5));
-                        *reinterpret_cast<uint4*>(vrow + c * 2048) = o;
-                    }
+                    for (int c = 0; c < 8; ++c) value_chunk(vw, c);
                 }
-                // scores
                 if (!fail && !tc_wait_warp(bar_sready, static_cast<uint32_t>(it) & 1u, abort_flag)) fail = true;
                 if (!fail) {
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -450,12 +498,15 @@ __global__ void __launch_bounds__(kTcThreads, kAttnTcCtasPerSm) attn_tc_kernel(c
                             sc[g] = fmaf(qa, __uint_as_float((hh & 2) ? b : a), sc[g]);
                         }
                     }
+                    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                    __syncwarp();
+                    if (lane == 0) tc_arrive(bar_dfree);
                     const float4 m0 = *reinterpret_cast<const float4*>(s_m + hh * 8), m1 = *reinterpret_cast<const float4*>(s_m + hh * 8 + 4);
                     const float mr[8] = {m0.x, m0.y, m0.z, m0.w, m1.x, m1.y, m1.z, m1.w};
 #pragma unroll
                     for (int g = 0; g < 8; ++g) {
                         sc[g] = valid ? sc[g] * kn : -INFINITY;
-                        trigger = trigger || sc[g] > mr[g] + kAttnSoftmaxSlack;
+                        trigger = trigger || sc[g] > mr[g] + slack;
                     }
                 }
             }
@@ -463,8 +514,8 @@ __global__ void __launch_bounds__(kTcThreads, kAttnTcCtasPerSm) attn_tc_kernel(c
                 atomicExch(&s_abort, 1u);
                 ok = false;
             }
-            // every worker votes once per tile, whatever happened to it
-            const bool move = tc_workers_or(trigger || fail);
+            // every thread of the group votes once per tile, whatever happened to it
+            const bool move = tc_value_group_or(trigger || fail);
             if (*abort_flag) {
                 ok = false;
                 break;
@@ -480,19 +531,21 @@ __global__ void __launch_bounds__(kTcThreads, kAttnTcCtasPerSm) attn_tc_kernel(c
                 }
                 if (lane < 4) {
 #pragma unroll
-                    for (int g = 0; g < 8; ++g) s_wmax[warp * 32 + lane * 8 + g] = tm[g];
+                    for (int g = 0; g < 8; ++g) s_wmax[(warp & 3) * 32 + lane * 8 + g] = tm[g];
                 }
-                tc_workers_sync();
-                if (tid < 32) {
-                    const float old = s_m[tid];
-                    const float nm = fmaxf(fmaxf(old, fmaxf(s_wmax[tid], s_wmax[32 + tid])), fmaxf(s_wmax[64 + tid], s_wmax[96 + tid]));
-                    s_factor[tid] = (nm == -INFINITY) ? 1.f : __expf(old - nm);
-                    s_m[tid] = nm;
+                tc_group_sync(1);
+                const int t = tid - kTcGroup;
+                if (t < 32) {
+                    const float old = s_m[t];
+                    const float nm = fmaxf(fmaxf(old, fmaxf(s_wmax[t], s_wmax[32 + t])), fmaxf(s_wmax[64 + t], s_wmax[96 + t]));
+                    s_factor[t] = (nm == -INFINITY) ? 1.f : tc_ex2(old - nm);
+                    s_m[t] = nm;
                 }
-                tc_workers_sync();
+                tc_group_sync(1);
 #pragma unroll
                 for (int g = 0; g < 8; ++g) l_run[g] *= s_factor[hh * 8 + g];
                 if (it > 0) {
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                     uint32_t o[32];
                     tc_ld32(tm_lane + kColO, o);
 #pragma unroll
@@ -508,7 +561,7 @@ __global__ void __launch_bounds__(kTcThreads, kAttnTcCtasPerSm) attn_tc_kernel(c
                 float p[8];
 #pragma unroll
                 for (int g = 0; g < 8; ++g) {
-                    p[g] = valid ? __expf(sc[g] - mr[g]) : 0.f;
+                    p[g] = valid ? tc_ex2(sc[g] - mr[g]) : 0.f;
                     l_run[g] += p[g];
                 }
                 uint4 o;
@@ -525,10 +578,7 @@ __global__ void __launch_bounds__(kTcThreads, kAttnTcCtasPerSm) attn_tc_kernel(c
         }
 
         // ---- publish the partial result -------------------------------------------------------------
-        if (ok && n_tiles > 0 && !tc_wait_warp(bar_vfree, static_cast<uint32_t>(n_tiles - 1) & 1u, abort_flag)) {
-            atomicExch(&s_abort, 1u);
-            ok = false;
-        }
+        if (ok && n_tiles > 0 && !tc_wait_warp(bar_vfree, static_cast<uint32_t>(n_tiles - 1) & 1u, abort_flag)) ok = false;
         if (ok) {
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             uint32_t o[32];
@@ -554,7 +604,7 @@ __global__ void __launch_bounds__(kTcThreads, kAttnTcCtasPerSm) attn_tc_kernel(c
             }
             if (lane < 4) {
 #pragma unroll
-                for (int g = 0; g < 8; ++g) s_wmax[warp * 32 + lane * 8 + g] = l_run[g];
+                for (int g = 0; g < 8; ++g) s_wmax[(warp & 3) * 32 + lane * 8 + g] = l_run[g];
             }
         }
     }
@@ -565,11 +615,11 @@ __global__ void __launch_bounds__(kTcThreads, kAttnTcCtasPerSm) attn_tc_kernel(c
         const int h = tid >> 3, g = tid & 7;
         if (g < ng) {
             const size_t slot = (static_cast<size_t>(seq) * q_heads + h * G + g0 + g) * n_splits + split;
-            part_ml[slot * 2] = s_m[tid];
+            part_ml[slot * 2] = s_m[tid] * kLn2;   // natural-log domain, as attn_combine_kernel expects
             part_ml[slot * 2 + 1] = (s_wmax[tid] + s_wmax[32 + tid]) + (s_wmax[64 + tid] + s_wmax[96 + tid]);
         }
     }
-    if (warp == 4) {
+    if (warp == kTcMmaWarp) {
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kTcTmemCols) : "memory");
     }
