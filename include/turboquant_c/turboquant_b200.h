@@ -389,6 +389,42 @@ int tq_kv_attention(const tq_kv_cache_t* caches, int n_seqs, int layer, const vo
 int tq_kv_attention_lse(const tq_kv_cache_t* caches, int n_seqs, int layer, const void* queries, int q_dtype,
                         int q_heads, void* out_fp16, float* lse_out, int start, int end, int use_qjl, void* stream);
 
+/* ---- fp16 decode window and hybrid attention -------------------------------------------------
+ * The reference keeps these in its C++ layer only (no C symbol): turboquant::DecodeBuffer
+ * (include/turboquant/decode_buffer.h:11-47, src/decode_buffer.cpp) and hybrid_attention
+ * (src/attention_dispatch.cpp:21-74).  Here the window lives in device memory as fp16
+ * [slot][head][dim]; slot = absolute token index % window_size. */
+typedef struct tq_decode_buffer_s* tq_decode_buffer_t;
+
+/** DecodeBuffer(window_size, num_heads, head_dim), zero-filled (src/decode_buffer.cpp:9-14). */
+tq_decode_buffer_t tq_decode_buffer_create(int window_size, int num_heads, int head_dim);
+void tq_decode_buffer_free(tq_decode_buffer_t buf);
+int tq_decode_buffer_window_size(tq_decode_buffer_t buf);
+int tq_decode_buffer_current_length(tq_decode_buffer_t buf);
+/** rebuild (src/decode_buffer.cpp:16-47): keys / values [num_tokens, heads, head_dim] (TQ_F32 or
+ *  TQ_F16, host or device); the first min(num_tokens, window) tokens go to slots 0.., the length
+ *  becomes num_tokens and the slide position 0. */
+int tq_decode_buffer_rebuild(tq_decode_buffer_t buf, const void* keys, const void* values, int dtype, int num_tokens,
+                             void* stream);
+/** append_token (src/decode_buffer.cpp:49-70): one token [heads, head_dim] into slot length % window. */
+int tq_decode_buffer_append_token(tq_decode_buffer_t buf, const void* key, const void* value, int dtype, void* stream);
+/** slide_window (src/decode_buffer.cpp:72-103): num_tokens tokens over the oldest slots, from the
+ *  slide position, which then advances by num_tokens (mod window). */
+int tq_decode_buffer_slide_window(tq_decode_buffer_t buf, const void* new_keys, const void* new_values, int dtype,
+                                  int num_tokens, void* stream);
+/** keys(start, end) / values(start, end) (src/decode_buffer.cpp:128-142): fp16 [end - start, heads,
+ *  head_dim] to host or device memory; fails unless 0 <= start < end <= current_length. */
+int tq_decode_buffer_keys(tq_decode_buffer_t buf, int start, int end, void* out_fp16, void* stream);
+int tq_decode_buffer_values(tq_decode_buffer_t buf, int start, int end, void* out_fp16, void* stream);
+
+/** hybrid_attention (src/attention_dispatch.cpp:21-74) for one query position: queries
+ *  [q_heads, head_dim] (TQ_F32 / TQ_F16, rounded to fp16) -> out fp16 [q_heads, head_dim].  An empty
+ *  cache gives zeros; a context of at most window_size tokens is attended in the window (plain
+ *  scaled-dot-product attention over its fp16 keys and values, scale 1/sqrt(head_dim)); a longer
+ *  one over the compressed cache (the reference decompresses it first; residual bits not used). */
+int tq_hybrid_attention(tq_kv_cache_t cache, tq_decode_buffer_t buf, int layer, const void* queries, int q_dtype,
+                        int q_heads, void* out_fp16, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

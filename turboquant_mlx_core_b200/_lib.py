@@ -133,6 +133,17 @@ def load() -> C.CDLL:
     sig("tq_kv_attention", i, [C.POINTER(C.c_void_p), i, i, vp, i, i, vp, i, i, i, vp])
     sig("tq_kv_attention_lse", i, [C.POINTER(C.c_void_p), i, i, vp, i, i, vp, vp, i, i, i, vp])
 
+    sig("tq_decode_buffer_create", vp, [i, i, i])
+    sig("tq_decode_buffer_free", None, [vp])
+    sig("tq_decode_buffer_window_size", i, [vp])
+    sig("tq_decode_buffer_current_length", i, [vp])
+    sig("tq_decode_buffer_rebuild", i, [vp, vp, vp, i, i, vp])
+    sig("tq_decode_buffer_append_token", i, [vp, vp, vp, i, vp])
+    sig("tq_decode_buffer_slide_window", i, [vp, vp, vp, i, i, vp])
+    sig("tq_decode_buffer_keys", i, [vp, i, i, vp, vp])
+    sig("tq_decode_buffer_values", i, [vp, i, i, vp, vp])
+    sig("tq_hybrid_attention", i, [vp, vp, i, vp, i, i, vp, vp])
+
     sig("tq_distributed_init", vp, [C.c_char_p, C.c_char_p])
     sig("tq_distributed_init_local", vp, [])
     sig("tq_distributed_rank", i, [vp])

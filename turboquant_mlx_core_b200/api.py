@@ -402,6 +402,103 @@ class TQKVCache:
             pass
 
 
+class DecodeBuffer:
+    """The fp16 decode window (include/turboquant/decode_buffer.h:11-47) in device memory: a ring of
+    `window_size` token slots shadowing the most recent tokens of a sequence, so that short contexts
+    are attended without touching the compressed cache."""
+
+    def __init__(self, window_size: int, num_heads: int, head_dim: int):
+        self._L = _lib.load()
+        self.num_heads, self.head_dim = int(num_heads), int(head_dim)
+        self._h = self._L.tq_decode_buffer_create(int(window_size), self.num_heads, self.head_dim)
+        if not self._h:
+            raise TQError("DecodeBuffer: " + _lib.last_error())
+
+    @property
+    def handle(self):
+        return self._h
+
+    def window_size(self) -> int:
+        return self._L.tq_decode_buffer_window_size(self._h)
+
+    def current_length(self) -> int:
+        return self._L.tq_decode_buffer_current_length(self._h)
+
+    def _kv(self, keys, values, ndim):
+        if not _is_torch(keys):
+            keys = np.ascontiguousarray(keys)
+            values = np.ascontiguousarray(values)
+        if tuple(keys.shape) != tuple(values.shape) or len(keys.shape) != ndim or tuple(keys.shape[-2:]) != (self.num_heads, self.head_dim):
+            raise ValueError("keys and values must both be [..., num_heads, head_dim]")
+        return keys, values
+
+    def rebuild(self, keys, values, stream=None):
+        """keys / values [tokens, heads, head_dim]: fill the window from a decompressed prefix
+        (src/decode_buffer.cpp:16-47)."""
+        keys, values = self._kv(keys, values, 3)
+        check(self._L.tq_decode_buffer_rebuild(self._h, _ptr(keys), _ptr(values), _dtype_tag(keys), int(keys.shape[0]),
+                                               _stream_ptr(stream)), "DecodeBuffer.rebuild")
+
+    def append_token(self, key, value, stream=None):
+        """One token, [1, heads, head_dim] or [heads, head_dim] (src/decode_buffer.cpp:49-70)."""
+        if len(key.shape) == 3:
+            key, value = key[0], value[0]
+        key, value = self._kv(key, value, 2)
+        check(self._L.tq_decode_buffer_append_token(self._h, _ptr(key), _ptr(value), _dtype_tag(key), _stream_ptr(stream)),
+              "DecodeBuffer.append_token")
+
+    def slide_window(self, new_keys, new_values, stream=None):
+        """Overwrite the oldest slots with [tokens, heads, head_dim] (src/decode_buffer.cpp:72-103)."""
+        new_keys, new_values = self._kv(new_keys, new_values, 3)
+        check(self._L.tq_decode_buffer_slide_window(self._h, _ptr(new_keys), _ptr(new_values), _dtype_tag(new_keys),
+                                                    int(new_keys.shape[0]), _stream_ptr(stream)), "DecodeBuffer.slide_window")
+
+    def _read(self, fn, what, start, end):
+        n = max(int(end) - int(start), 0)
+        out = np.empty((n, self.num_heads, self.head_dim), np.float16)
+        if fn(self._h, int(start), int(end), _ptr(out) if n else None, None) != 0:
+            raise IndexError(f"DecodeBuffer.{what}: " + _lib.last_error())
+        return out
+
+    def keys(self, start: int, end: int):
+        """fp16 [end - start, heads, head_dim]; IndexError unless 0 <= start < end <= current_length()."""
+        return self._read(self._L.tq_decode_buffer_keys, "keys", start, end)
+
+    def values(self, start: int, end: int):
+        return self._read(self._L.tq_decode_buffer_values, "values", start, end)
+
+    def close(self):
+        if self._h:
+            self._L.tq_decode_buffer_free(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+def hybrid_attention(cache, buffer, layer: int, queries, out=None, stream=None):
+    """hybrid_attention (src/attention_dispatch.cpp:21-74) for one query position: queries
+    [q_heads, head_dim] -> fp16 [q_heads, head_dim].  Contexts that fit the decode window are attended
+    there, longer ones over the compressed cache."""
+    L = _lib.load()
+    if not _is_torch(queries):
+        queries = np.ascontiguousarray(queries)
+    if len(queries.shape) != 2 or queries.shape[-1] != cache.head_dim:
+        raise ValueError("queries must be [q_heads, head_dim]")
+    if out is None:
+        if _is_torch(queries):
+            import torch
+            out = torch.empty(tuple(queries.shape), dtype=torch.float16, device=queries.device)
+        else:
+            out = np.empty(queries.shape, np.float16)
+    check(L.tq_hybrid_attention(cache.handle, buffer.handle, layer, _ptr(queries), _dtype_tag(queries), int(queries.shape[0]),
+                                _ptr(out), _stream_ptr(stream)), "hybrid_attention")
+    return out
+
+
 def append_batch(caches, layer: int, keys, values, stream=None):
     """One decode step of a batch: row i of keys / values ([n_seqs, heads, head_dim], device
     tensors) is appended as one token to caches[i]; two kernel launches per 32 sequences."""

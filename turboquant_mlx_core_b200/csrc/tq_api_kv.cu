@@ -11,6 +11,7 @@
 #include <cstring>
 #include <string>
 
+#include "tq_attn.cuh"
 #include "tq_host.hpp"
 #include "tq_kernels.cuh"
 #include "turboquant_c/turboquant_b200.h"
@@ -586,10 +587,154 @@ void attention_batched(TQKVCache* const* caches, int n_seqs, int layer, const vo
     }
 }
 
+// ---- the fp16 decode window (include/turboquant/decode_buffer.h:11-47, src/decode_buffer.cpp) --------
+// A ring of `window` token slots on the device, [slot][head][dim] fp16 per tensor; slot of a token =
+// absolute index % window.  Same state machine as the reference: rebuild() fills slots 0.. from a
+// decompressed prefix and sets the length to the number of tokens it was given (even beyond the
+// window, src/decode_buffer.cpp:45-46), append_token() writes slot length % window, slide_window()
+// overwrites from window_start and advances it, keys()/values() gather [start, end) by slot.
+class DecodeBuffer {
+public:
+    DecodeBuffer(int window, int heads, int dim) : window_(window), heads_(heads), dim_(dim), device_(tq::current_device()) {
+        TQ_REQUIRE(window > 0 && heads > 0 && dim > 0, "decode buffer: window, heads and head_dim must be positive");
+        const size_t bytes = static_cast<size_t>(window) * heads * dim * sizeof(__half);
+        k_.resize(bytes);
+        v_.resize(bytes);
+        TQ_CUDA(cudaMemset(k_.as<void>(), 0, bytes));
+        TQ_CUDA(cudaMemset(v_.as<void>(), 0, bytes));
+    }
+    int window_size() const { return window_; }
+    int current_length() const { return current_length_; }
+    int num_heads() const { return heads_; }
+    int head_dim() const { return dim_; }
+    int device() const { return device_; }
+    const __half* key_ring() const { return k_.as<__half>(); }
+    const __half* value_ring() const { return v_.as<__half>(); }
+    DeviceBuffer& scratch() { return scratch_; }
+    DeviceBuffer& q_stage() { return q_stage_; }
+    DeviceBuffer& out_stage() { return out_stage_; }
+
+    void rebuild(const void* keys, const void* values, int dtype, int num_tokens, cudaStream_t st) {
+        TQ_REQUIRE(num_tokens >= 0, "decode buffer: negative token count");
+        write(keys, values, dtype, std::min(num_tokens, window_), 0, st);
+        current_length_ = num_tokens;
+        window_start_ = 0;
+    }
+    void append_token(const void* key, const void* value, int dtype, cudaStream_t st) {
+        write(key, value, dtype, 1, current_length_ % window_, st);
+        ++current_length_;
+    }
+    void slide_window(const void* keys, const void* values, int dtype, int num_tokens, cudaStream_t st) {
+        TQ_REQUIRE(num_tokens >= 0, "decode buffer: negative token count");
+        write(keys, values, dtype, num_tokens, window_start_, st);
+        window_start_ = static_cast<int>((static_cast<long>(window_start_) + num_tokens) % window_);
+    }
+    void read(bool values, int start, int end, void* out, cudaStream_t st) {
+        // src/decode_buffer.cpp:128-141
+        TQ_REQUIRE(start >= 0 && end > start && end <= current_length_, "DecodeBuffer: requested range is out of bounds");
+        TQ_REQUIRE(out != nullptr, "decode buffer: NULL output");
+        TQ_CUDA(cudaSetDevice(device_));
+        const long n = end - start;
+        const int row = heads_ * dim_;
+        const bool dev = tq::is_device_pointer(out);
+        __half* d_out = static_cast<__half*>(out);
+        if (!dev) {
+            out_stage_.reserve(static_cast<size_t>(n) * row * sizeof(__half));
+            d_out = out_stage_.as<__half>();
+        }
+        tq::launch_ring_read(values ? v_.as<__half>() : k_.as<__half>(), n, row, window_, start, d_out, st);
+        if (!dev) {
+            TQ_CUDA(cudaMemcpyAsync(out, d_out, static_cast<size_t>(n) * row * sizeof(__half), cudaMemcpyDeviceToHost, st));
+            TQ_CUDA(cudaStreamSynchronize(st));
+        }
+    }
+
+private:
+    void write(const void* keys, const void* values, int dtype, int n, int slot0, cudaStream_t st) {
+        TQ_REQUIRE(dtype == TQ_F32 || dtype == TQ_F16, "decode buffer: keys and values must be fp32 or fp16");
+        if (n == 0) return;
+        TQ_REQUIRE(keys != nullptr && values != nullptr, "decode buffer: NULL keys or values");
+        TQ_CUDA(cudaSetDevice(device_));
+        const int row = heads_ * dim_;
+        const size_t bytes = static_cast<size_t>(n) * row * (dtype == TQ_F32 ? 4 : 2);
+        const void* dk = keys;
+        const void* dv = values;
+        if (!tq::is_device_pointer(keys)) {
+            k_stage_.reserve(bytes);
+            TQ_CUDA(cudaMemcpyAsync(k_stage_.as<void>(), keys, bytes, cudaMemcpyHostToDevice, st));
+            dk = k_stage_.as<void>();
+        }
+        if (!tq::is_device_pointer(values)) {
+            v_stage_.reserve(bytes);
+            TQ_CUDA(cudaMemcpyAsync(v_stage_.as<void>(), values, bytes, cudaMemcpyHostToDevice, st));
+            dv = v_stage_.as<void>();
+        }
+        tq::launch_ring_write(dk, dv, dtype == TQ_F16, n, 0, row, window_, slot0, k_.as<__half>(), v_.as<__half>(), st);
+    }
+
+    int window_, heads_, dim_, device_;
+    int current_length_ = 0, window_start_ = 0;
+    DeviceBuffer k_, v_, k_stage_, v_stage_, out_stage_, q_stage_, scratch_;
+};
+
+// hybrid_attention (src/attention_dispatch.cpp:21-74) for one query position.  Nothing cached: zeros.
+// A context that fits the window: scaled-dot-product attention over the window's fp16 keys and values
+// [0, seq_len).  A longer one: the reference decompresses every key and value (centroids only, the
+// residual bits are not read) and runs the same attention; here that is the fused kernel over the
+// compressed records, which never materialises them.
+void hybrid_attention(TQKVCache* cache, DecodeBuffer* buf, int layer, const void* q, int q_dtype, int q_heads, void* out,
+                      cudaStream_t st) {
+    TQ_REQUIRE(cache && buf && q && out, "hybrid_attention: bad argument");
+    TQ_REQUIRE(q_dtype == TQ_F32 || q_dtype == TQ_F16, "hybrid_attention: queries must be fp32 or fp16");
+    const int heads = cache->num_heads(), dim = cache->head_dim();
+    TQ_REQUIRE(buf->num_heads() == heads && buf->head_dim() == dim && buf->device() == cache->device(),
+               "hybrid_attention: the decode buffer does not match the cache");
+    TQ_REQUIRE(q_heads > 0 && q_heads % heads == 0, "hybrid_attention: query heads must be a multiple of KV heads");
+    const int seq_len = cache->seq_length();
+    const size_t n_q = static_cast<size_t>(q_heads) * dim;
+    TQ_CUDA(cudaSetDevice(cache->device()));
+    if (seq_len == 0) {
+        if (tq::is_device_pointer(out)) TQ_CUDA(cudaMemsetAsync(out, 0, n_q * sizeof(__half), st));
+        else std::memset(out, 0, n_q * sizeof(__half));
+        return;
+    }
+    if (seq_len > buf->window_size()) {
+        TQKVCache* one[1] = {cache};
+        const int start = 0, end = seq_len;
+        attention_batched(one, 1, layer, q, q_dtype, q_heads, &start, &end, false, out, nullptr, st);
+        return;
+    }
+    TQ_REQUIRE(seq_len <= buf->current_length(), "DecodeBuffer: requested range is out of bounds");
+    const size_t q_es = q_dtype == TQ_F32 ? 4 : 2;
+    const void* d_q = q;
+    if (!tq::is_device_pointer(q)) {
+        buf->q_stage().reserve(n_q * q_es);
+        TQ_CUDA(cudaMemcpyAsync(buf->q_stage().as<void>(), q, n_q * q_es, cudaMemcpyHostToDevice, st));
+        d_q = buf->q_stage().as<void>();
+    }
+    const bool out_dev = tq::is_device_pointer(out);
+    __half* d_out = static_cast<__half*>(out);
+    if (!out_dev) {
+        buf->out_stage().reserve(n_q * sizeof(__half));
+        d_out = buf->out_stage().as<__half>();
+    }
+    const int n_splits = tq::dense_attention_splits(seq_len, heads, q_heads, tq::sm_count(cache->device()));
+    buf->scratch().reserve(tq::dense_attention_scratch_bytes(q_heads, dim, n_splits));
+    tq::launch_dense_attention(buf->key_ring(), buf->value_ring(), seq_len, heads, dim, d_q, q_dtype == TQ_F16, q_heads, n_splits,
+                               buf->scratch().as<void>(), d_out, st);
+    if (!out_dev) {
+        TQ_CUDA(cudaMemcpyAsync(out, d_out, n_q * sizeof(__half), cudaMemcpyDeviceToHost, st));
+        TQ_CUDA(cudaStreamSynchronize(st));
+    }
+}
+
 }  // namespace turboquant
 
 struct tq_kv_cache_s {
     turboquant::TQKVCache* cache;
+};
+struct tq_decode_buffer_s {
+    turboquant::DecodeBuffer* buf;
 };
 
 using namespace tq;
@@ -831,6 +976,72 @@ int tq_kv_attention_lse(const tq_kv_cache_t* caches, int n_seqs, int layer, cons
         }
         turboquant::attention_batched(cs.data(), n_seqs, layer, queries, q_dtype, q_heads, starts.data(), ends.data(),
                                       use_qjl != 0, out_fp16, lse_out, static_cast<cudaStream_t>(stream));
+        return 0;
+    });
+}
+
+tq_decode_buffer_t tq_decode_buffer_create(int window_size, int num_heads, int head_dim) {
+    return guarded<tq_decode_buffer_t>(nullptr, nullptr, [&]() -> tq_decode_buffer_t {
+        auto* b = new turboquant::DecodeBuffer(window_size, num_heads, head_dim);
+        return new tq_decode_buffer_s{b};
+    });
+}
+
+void tq_decode_buffer_free(tq_decode_buffer_t buf) {
+    if (!buf) return;
+    delete buf->buf;
+    delete buf;
+}
+
+int tq_decode_buffer_window_size(tq_decode_buffer_t buf) { return (buf && buf->buf) ? buf->buf->window_size() : 0; }
+int tq_decode_buffer_current_length(tq_decode_buffer_t buf) { return (buf && buf->buf) ? buf->buf->current_length() : 0; }
+
+int tq_decode_buffer_rebuild(tq_decode_buffer_t buf, const void* keys, const void* values, int dtype, int num_tokens, void* stream) {
+    return guarded<int>(0, -1, [&]() {
+        TQ_REQUIRE(buf && buf->buf, "tq_decode_buffer_rebuild: NULL buffer");
+        buf->buf->rebuild(keys, values, dtype, num_tokens, static_cast<cudaStream_t>(stream));
+        return 0;
+    });
+}
+
+int tq_decode_buffer_append_token(tq_decode_buffer_t buf, const void* key, const void* value, int dtype, void* stream) {
+    return guarded<int>(0, -1, [&]() {
+        TQ_REQUIRE(buf && buf->buf, "tq_decode_buffer_append_token: NULL buffer");
+        buf->buf->append_token(key, value, dtype, static_cast<cudaStream_t>(stream));
+        return 0;
+    });
+}
+
+int tq_decode_buffer_slide_window(tq_decode_buffer_t buf, const void* new_keys, const void* new_values, int dtype, int num_tokens,
+                                  void* stream) {
+    return guarded<int>(0, -1, [&]() {
+        TQ_REQUIRE(buf && buf->buf, "tq_decode_buffer_slide_window: NULL buffer");
+        buf->buf->slide_window(new_keys, new_values, dtype, num_tokens, static_cast<cudaStream_t>(stream));
+        return 0;
+    });
+}
+
+int tq_decode_buffer_keys(tq_decode_buffer_t buf, int start, int end, void* out_fp16, void* stream) {
+    return guarded<int>(0, -1, [&]() {
+        TQ_REQUIRE(buf && buf->buf, "tq_decode_buffer_keys: NULL buffer");
+        buf->buf->read(false, start, end, out_fp16, static_cast<cudaStream_t>(stream));
+        return 0;
+    });
+}
+
+int tq_decode_buffer_values(tq_decode_buffer_t buf, int start, int end, void* out_fp16, void* stream) {
+    return guarded<int>(0, -1, [&]() {
+        TQ_REQUIRE(buf && buf->buf, "tq_decode_buffer_values: NULL buffer");
+        buf->buf->read(true, start, end, out_fp16, static_cast<cudaStream_t>(stream));
+        return 0;
+    });
+}
+
+int tq_hybrid_attention(tq_kv_cache_t cache, tq_decode_buffer_t buf, int layer, const void* queries, int q_dtype, int q_heads,
+                        void* out_fp16, void* stream) {
+    return guarded<int>(0, -1, [&]() {
+        TQ_REQUIRE(cache && cache->cache && buf && buf->buf, "tq_hybrid_attention: NULL cache or buffer");
+        turboquant::hybrid_attention(cache->cache, buf->buf, layer, queries, q_dtype, q_heads, out_fp16, static_cast<cudaStream_t>(stream));
         return 0;
     });
 }
