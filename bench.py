@@ -113,45 +113,11 @@ class ClockSampler:
 
 # ---- synthetic inputs ------------------------------------------------------------------------
 
-def fit_codebook_torch(data, init, iterations=100):
-    """Lloyd-Max on the device (input preparation only): bin by midpoints, ties to the lower
-    bin, float64 bin means, stop when no centroid moves by 1e-6 — the reference's rule
-    (src/codebook.cpp:99-143)."""
-    import torch
-    c = torch.tensor(init, dtype=torch.float32, device=data.device)
-    flat = data.reshape(-1)
-    flat64 = flat.double()
-    for _ in range(iterations):
-        b = (c[:-1] + c[1:]) * 0.5
-        idx = torch.bucketize(flat, b, right=False)
-        sums = torch.zeros(c.numel(), dtype=torch.float64, device=data.device).index_add_(0, idx, flat64)
-        cnt = torch.bincount(idx, minlength=c.numel()).double()
-        new = torch.where(cnt > 0, (sums / cnt.clamp(min=1)).float(), c)
-        shift = (new - c).abs().max().item()
-        c = new
-        if shift < 1e-6:
-            break
-    return c.cpu().numpy().astype(np.float32)
-
-
 def build_codebooks(tq, w0):
-    """Per-layer codebooks as the reference's converter fits them (src/converter.cpp:291-372):
-    primary on the rotated, scaled weights; residual on what the primary leaves."""
-    import torch
-    out_f, in_f = w0.shape
-    analytic = tq.generate_codebook(4)
-    qw = tq.quantize_weight(w0, analytic, analytic, tq.QuantizerConfig(4, 4, BLOCK, True))
-    seed = int(qw.seeds[0])
-    nrm = torch.linalg.vector_norm(w0, dim=1, keepdim=True).clamp(min=1e-10)
-    rot = tq.apply_wht_rotation((w0 / nrm).contiguous(), seed, BLOCK)
-    torch.cuda.synchronize()
-    rot = rot * float(np.sqrt(np.float32(in_f)))
-    cp = fit_codebook_torch(rot, analytic.centroids)
-    cpt = torch.tensor(cp, device=rot.device)
-    idx = torch.bucketize(rot.reshape(-1), (cpt[:-1] + cpt[1:]) * 0.5, right=False)
-    res = rot.reshape(-1) - cpt[idx]
-    cr = fit_codebook_torch(res, analytic.centroids)
-    return tq.codebook_from_centroids(cp), tq.codebook_from_centroids(cr)
+    """Per-layer codebooks as the reference's converter fits them (src/converter.cpp:291-372): primary on
+    the rotated, scaled weights; residual on what the shared primary codebook leaves; Lloyd-Max on the
+    device through the library (tq_fit_layer_codebooks)."""
+    return tq.fit_layer_codebooks(w0, BLOCK, 4, 4, 100)
 
 
 def make_layer(tq, seed, device, cbs=None, out_f=OUT_F, in_f=IN_F):

@@ -67,6 +67,32 @@ int tq_array_to_host(tq_array_t a, void* dst, size_t dst_bytes);
 /** generate_codebook (src/codebook.cpp:71-85): 2^bits centroids, 2^bits-1 boundaries. */
 int tq_codebook_generate(int bits, float* centroids, float* boundaries);
 
+/** generate_codebook_from_data (include/turboquant/codebook.h:42, src/codebook.cpp:99-143, 269-282):
+ *  Lloyd-Max fit of 2^bits centroids to data[n] (fp32, host or device), started from the analytic
+ *  codebook, at most `iterations` rounds, stopping when no centroid moves by 1e-6 or more.  Runs on the
+ *  device for every n; bins by lower_bound and sums in double like the reference's CPU path.  n = 0
+ *  returns the analytic codebook.  centroids[2^bits], boundaries[2^bits - 1] (may be NULL) and
+ *  iterations_run (may be NULL) are host memory. */
+int tq_codebook_fit(const float* data, long n, int bits, int iterations, float* centroids, float* boundaries,
+                    int* iterations_run, void* stream);
+
+/** The converter's per-layer codebook fit (src/converter.cpp:291-368) for one weight matrix
+ *  [out_features, in_features] (fp32, host or device): the primary codebook is fitted to
+ *  sqrt(in) * WHT(row / |row|) with the seed the quantiser derives from the weight, the residual
+ *  codebook (residual_bits > 0) to what the shared analytic primary codebook leaves of those samples.
+ *  Outputs are host arrays: 2^bits centroids, 2^bits - 1 boundaries (boundaries may be NULL). */
+int tq_fit_layer_codebooks(const float* weight, int out_features, int in_features, uint32_t block, int primary_bits,
+                           int residual_bits, int iterations, float* primary_centroids, float* primary_boundaries,
+                           float* residual_centroids, float* residual_boundaries, void* stream);
+
+/** Largest power of two <= max_block dividing in_features (src/converter.cpp:228-240). */
+uint32_t tq_adaptive_block_size(int in_features, uint32_t max_block);
+/** N of the first ".layers.N." in a tensor name, -1 if none (src/converter.cpp:52-59). */
+int tq_layer_index(const char* name);
+/** 1 when a layer is kept at fp16: index < sensitive_start or > max_layer_index - sensitive_end
+ *  (src/converter.cpp:81-93); never for index < 0. */
+int tq_is_sensitive_layer(int layer_index, int max_layer_index, int sensitive_start, int sensitive_end);
+
 /* ---- rotation: apply_wht_rotation / apply_inverse_wht_rotation
  *      (include/turboquant/quantizer.h:29-39, src/rotation.cpp:364-403) --------------- */
 

@@ -133,6 +133,11 @@ def load() -> C.CDLL:
     sig("tq_kv_attention", i, [C.POINTER(C.c_void_p), i, i, vp, i, i, vp, i, i, i, vp])
     sig("tq_kv_attention_lse", i, [C.POINTER(C.c_void_p), i, i, vp, i, i, vp, vp, i, i, i, vp])
 
+    sig("tq_codebook_fit", i, [vp, C.c_long, i, i, vp, vp, C.POINTER(C.c_int), vp])
+    sig("tq_fit_layer_codebooks", i, [vp, i, i, u32, i, i, i, vp, vp, vp, vp, vp])
+    sig("tq_adaptive_block_size", u32, [i, u32])
+    sig("tq_layer_index", i, [C.c_char_p])
+    sig("tq_is_sensitive_layer", i, [i, i, i, i])
     sig("tq_decode_buffer_create", vp, [i, i, i])
     sig("tq_decode_buffer_free", None, [vp])
     sig("tq_decode_buffer_window_size", i, [vp])

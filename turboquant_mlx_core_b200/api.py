@@ -78,6 +78,63 @@ def generate_codebook(bits: int) -> Codebook:
     return Codebook(c, b[: (1 << bits) - 1], bits)
 
 
+def generate_codebook_from_data(data, bits: int, iterations: int = 100, stream=None, return_iterations: bool = False):
+    """generate_codebook_from_data (src/codebook.cpp:269-282): Lloyd-Max fit on the device.  data: fp32,
+    numpy or a CUDA tensor, any shape."""
+    L = _lib.load()
+    if not 1 <= bits <= 5:
+        raise ValueError("Unsupported bit width; must be 1-5")
+    if _is_torch(data):
+        data = data.reshape(-1).contiguous().float()
+        n = int(data.numel())
+    else:
+        data = np.ascontiguousarray(data, np.float32).reshape(-1)
+        n = int(data.size)
+    c = np.zeros(1 << bits, np.float32)
+    b = np.zeros(max((1 << bits) - 1, 1), np.float32)
+    run = C.c_int(0)
+    check(L.tq_codebook_fit(_ptr(data) if n else None, n, bits, int(iterations), c.ctypes.data, b.ctypes.data, C.byref(run),
+                            _stream_ptr(stream)), "generate_codebook_from_data")
+    cb = Codebook(c, b[: (1 << bits) - 1], bits)
+    return (cb, run.value) if return_iterations else cb
+
+
+def fit_layer_codebooks(weight, block_size: int, primary_bits: int = 4, residual_bits: int = 4, iterations: int = 100, stream=None):
+    """Per-layer codebooks as the converter fits them (src/converter.cpp:291-368): (primary, residual);
+    residual is None when residual_bits is 0.  weight: fp32 [out, in], numpy or a CUDA tensor."""
+    L = _lib.load()
+    if _is_torch(weight):
+        weight = weight.contiguous().float()
+    else:
+        weight = np.ascontiguousarray(weight, np.float32)
+    out_f, in_f = int(weight.shape[0]), int(weight.shape[1])
+    cp = np.zeros(1 << primary_bits, np.float32)
+    bp = np.zeros(max((1 << primary_bits) - 1, 1), np.float32)
+    cr = np.zeros(1 << max(residual_bits, 1), np.float32)
+    br = np.zeros(max((1 << max(residual_bits, 1)) - 1, 1), np.float32)
+    check(L.tq_fit_layer_codebooks(_ptr(weight), out_f, in_f, int(block_size), int(primary_bits), int(residual_bits), int(iterations),
+                                   cp.ctypes.data, bp.ctypes.data, cr.ctypes.data, br.ctypes.data, _stream_ptr(stream)),
+          "fit_layer_codebooks")
+    primary = Codebook(cp, bp[: (1 << primary_bits) - 1], primary_bits)
+    residual = Codebook(cr, br[: (1 << residual_bits) - 1], residual_bits) if residual_bits > 0 else None
+    return primary, residual
+
+
+def adaptive_block_size(in_features: int, max_block: int) -> int:
+    """Largest power of two <= max_block dividing in_features (src/converter.cpp:228-240)."""
+    return int(_lib.load().tq_adaptive_block_size(int(in_features), int(max_block)))
+
+
+def layer_index(name: str) -> int:
+    """N of the first ".layers.N." in a tensor name, -1 if none (src/converter.cpp:52-59)."""
+    return int(_lib.load().tq_layer_index(name.encode()))
+
+
+def is_sensitive_layer(index: int, max_index: int, sensitive_start: int, sensitive_end: int) -> bool:
+    """Kept at fp16 by the converter (src/converter.cpp:81-93)."""
+    return bool(_lib.load().tq_is_sensitive_layer(int(index), int(max_index), int(sensitive_start), int(sensitive_end)))
+
+
 def codebook_from_centroids(centroids) -> Codebook:
     c = _np(centroids, np.float32)
     b = ((c[:-1] + c[1:]) * np.float32(0.5)).astype(np.float32)

@@ -176,6 +176,91 @@ int tq_codebook_generate(int bits, float* centroids, float* boundaries) {
     });
 }
 
+// generate_codebook_from_data (src/codebook.cpp:269-282) on the device, whatever the sample count.
+int tq_codebook_fit(const float* data, long n, int bits, int iterations, float* centroids, float* boundaries, int* iterations_run,
+                    void* stream) {
+    return guarded<int>(0, -1, [&]() {
+        const float* c0 = analytic_centroids(bits);
+        TQ_REQUIRE(c0, "Unsupported bit width; must be 1-5");
+        TQ_REQUIRE(centroids && n >= 0 && (n == 0 || data), "tq_codebook_fit: bad argument");
+        auto st = static_cast<cudaStream_t>(stream);
+        DeviceBuffer stage;
+        const float* d_data = n ? device_view(data, static_cast<size_t>(n), stage, st) : nullptr;
+        const int run = launch_codebook_fit(d_data, n, bits, iterations, c0, centroids, boundaries, st);
+        if (iterations_run) *iterations_run = run;
+        return 0;
+    });
+}
+
+// The converter's per-layer fit (src/converter.cpp:291-368): samples = sqrt(in) * WHT(row / |row|) with the
+// seed the quantiser will derive; the primary codebook is fitted to them, the residual codebook to what the
+// SHARED analytic primary codebook leaves of them.
+int tq_fit_layer_codebooks(const float* weight, int out_features, int in_features, uint32_t block, int primary_bits, int residual_bits,
+                           int iterations, float* primary_centroids, float* primary_boundaries, float* residual_centroids,
+                           float* residual_boundaries, void* stream) {
+    return guarded<int>(0, -1, [&]() {
+        TQ_REQUIRE(weight && out_features > 0 && in_features > 0 && primary_centroids, "tq_fit_layer_codebooks: bad argument");
+        const float* cp0 = analytic_centroids(primary_bits);
+        TQ_REQUIRE(cp0, "Unsupported bit width; must be 1-5");
+        const bool need_residual = residual_bits > 0;
+        const float* cr0 = need_residual ? analytic_centroids(residual_bits) : nullptr;
+        TQ_REQUIRE(!need_residual || (cr0 && residual_centroids), "tq_fit_layer_codebooks: bad residual bit width or NULL output");
+        auto st = static_cast<cudaStream_t>(stream);
+        const size_t n = static_cast<size_t>(out_features) * in_features;
+        DeviceBuffer w_stage, norms(static_cast<size_t>(out_features) * 4), scaled(n * 4), resid(need_residual ? n * 4 : 0);
+        const float* d_w = device_view(weight, n, w_stage, st);
+        uint32_t seed_p = 0, seed_r = 0;
+        derive_seeds(d_w, n, &seed_p, &seed_r, st);
+        launch_row_norms(d_w, norms.as<float>(), out_features, in_features, st);
+        launch_layer_samples(d_w, norms.as<float>(), out_features, in_features, block, seed_p, cp0, 1 << primary_bits,
+                             scaled.as<float>(), need_residual ? resid.as<float>() : nullptr, st);
+        launch_codebook_fit(scaled.as<float>(), static_cast<long>(n), primary_bits, iterations, cp0, primary_centroids,
+                            primary_boundaries, st);
+        if (need_residual)
+            launch_codebook_fit(resid.as<float>(), static_cast<long>(n), residual_bits, iterations, cr0, residual_centroids,
+                                residual_boundaries, st);
+        TQ_CUDA(cudaStreamSynchronize(st));
+        return 0;
+    });
+}
+
+// Largest power of two <= max_block that divides in_features (src/converter.cpp:228-240); 1 when none does.
+uint32_t tq_adaptive_block_size(int in_features, uint32_t max_block) {
+    uint32_t best = 1;
+    for (int p = 1; p < 20; ++p) {
+        const uint32_t c = 1u << p;
+        if (c > max_block) break;
+        if (in_features % static_cast<int>(c) == 0) best = c;
+    }
+    return best;
+}
+
+// Index N of the first ".layers.N." in a tensor name, -1 when there is none (src/converter.cpp:52-59).
+int tq_layer_index(const char* name) {
+    if (!name) return -1;
+    const char* key = ".layers.";
+    for (const char* p = std::strstr(name, key); p; p = std::strstr(p + 1, key)) {
+        const char* d = p + 8;
+        if (*d < '0' || *d > '9') continue;
+        long v = 0;
+        while (*d >= '0' && *d <= '9') {
+            v = v * 10 + (*d - '0');
+            if (v > 0x7fffffffL) return -1;
+            ++d;
+        }
+        if (*d == '.') return static_cast<int>(v);
+    }
+    return -1;
+}
+
+// Layers kept at fp16: the first `sensitive_start` and the last `sensitive_end` of the stack (src/converter.cpp:81-93).
+int tq_is_sensitive_layer(int layer_index, int max_layer_index, int sensitive_start, int sensitive_end) {
+    if (layer_index < 0) return 0;
+    if (layer_index < sensitive_start) return 1;
+    if (layer_index > max_layer_index - sensitive_end) return 1;
+    return 0;
+}
+
 int tq_wht_rotate(const float* in, float* out, int rows, int cols, uint32_t seed, uint32_t block, int inverse,
                   void* stream) {
     return guarded<int>(0, -1, [&]() {

@@ -112,6 +112,15 @@ void launch_quantize_weight(const float* d_weight, long out, int in, const float
                             uint32_t seed_p, uint32_t seed_r, uint8_t* d_packed_primary, uint8_t* d_packed_residual,
                             float* d_norms, float* d_orig_norm_tmp, float* d_recon_tmp, cudaStream_t stream);
 
+// Row L2 norms with the quantiser's summation order (left to right in fp32).
+void launch_row_norms(const float* d_matrix, float* d_out, long rows, int cols, cudaStream_t stream);
+
+// tq_codebook_fit.cu — Lloyd-Max fit on the device and the per-layer sample extraction.
+int launch_codebook_fit(const float* d_data, long n, int bits, int iterations, const float* init_centroids, float* centroids_out,
+                        float* boundaries_out, cudaStream_t stream);
+void launch_layer_samples(const float* d_weight, const float* d_row_norms, long rows, int in, uint32_t block, uint32_t seed_p,
+                          const float* primary_centroids, int n_primary, float* d_scaled, float* d_residual, cudaStream_t stream);
+
 // tq_kv_kernels.cu — KV-cache encoder with several destinations: the n_vec input vectors
 // ([n_vec, head_dim], contiguous) are cut into segments of vec_per_seg vectors and segment s is
 // written to segs[s] (at most 32 segments per launch).  A decode step that appends one token to

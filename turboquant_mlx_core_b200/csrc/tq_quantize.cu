@@ -202,6 +202,12 @@ uint32_t fnv1a(const std::vector<uint8_t>& bytes, uint32_t salt) {
 
 }  // namespace
 
+void launch_row_norms(const float* d_matrix, float* d_out, long rows, int cols, cudaStream_t stream) {
+    if (rows == 0) return;
+    row_norm_seq_kernel<<<static_cast<int>((rows + 7) / 8), 256, 0, stream>>>(d_matrix, d_out, rows, cols);
+    TQ_CUDA(cudaGetLastError());
+}
+
 void derive_seeds(const float* d_weight, size_t n_elems, uint32_t* seed_primary, uint32_t* seed_residual,
                   cudaStream_t stream) {
     const size_t byte_count = n_elems * sizeof(float);
