@@ -385,6 +385,11 @@ def run_cuda(args):
             line["prefill"] = bench_prefill(tq, L, layers, device, stream, args)
         except Exception as e:
             line["prefill"] = {"error": str(e)}
+        if world > 1:
+            try:
+                line["prefill_sharded"] = bench_prefill_sharded(tq, L, device, stream, rank, world, cbs, args)
+            except Exception as e:
+                line["prefill_sharded"] = {"error": str(e)}
     if "lm_head" in legs:
         try:
             line["lm_head"] = bench_lm_head(tq, L, device, stream, rank, world, cbs, args)
@@ -673,6 +678,97 @@ def bench_prefill(tq, L, layers, device, stream, args):
     return {"workload": f"{m} activation rows x 4096x4096 TQ8 layer (rotation + fused dequant GEMM, fp16 in, fp32 accumulate)",
             "us_per_layer": us, "tok_per_s": m / (us * 1e-6), "tflops": tf, "frac_of_tensor_peak": tf / peak,
             "peak_tflops": peak, "peak_kind": peak_kind}
+
+
+def bench_prefill_sharded(tq, L, device, stream, rank, world, cbs, args):
+    """The prefill GEMM with the layer's output rows split over the ranks: every rank multiplies the same 2048
+    activation rows by its 4096 / world weight rows straight into its column block of a shared [2048, 4096]
+    result (strided output), copies that block to every peer with 16-byte stores (one row piece per activation
+    row) and waits for the peers' blocks.  Beside it: the same shard followed by an NCCL all-gather."""
+    import torch
+    import torch.distributed as dist
+    from turboquant_mlx_core_b200.sharding import Exchange, all_gather_rows, row_range
+    m = 2048
+    s, e = row_range(OUT_F, rank, world)
+    rows = e - s
+    n_layers = 4
+    lins = [make_layer(tq, 7000 + 10 * li + rank, device, cbs, out_f=rows)[0] for li in range(n_layers)]
+    g = torch.Generator(device=device).manual_seed(901)        # the same activations on every rank
+    x = torch.randn((m, IN_F), generator=g, device=device).half()
+    y = torch.empty((m, rows), device=device, dtype=torch.float16)
+    sp = C.c_void_p(stream.cuda_stream)
+    res = {"workload": f"{m} activation rows x 4096x4096 TQ8 layer, output rows split over {world} ranks "
+                       f"({rows} per rank), result gathered on every rank"}
+    exchange, setup_error = None, None
+    try:
+        exchange = Exchange(2 * m * OUT_F * 2)
+    except Exception as exc:
+        setup_error = str(exc)
+    ok_t = torch.tensor([0.0 if setup_error else 1.0], device=device)
+    dist.all_reduce(ok_t, op=dist.ReduceOp.MIN)
+    if ok_t.item() != 1.0:
+        if exchange is not None:
+            exchange.close()
+        exchange = None
+        res["exchange"] = {"skipped": "shared buffers could not be mapped on every rank", "local_error": setup_error}
+
+    def timed(fn, reps=5):
+        torch.cuda.synchronize()
+        dist.barrier()
+        with torch.cuda.stream(stream):
+            for lin in lins:
+                fn(lin)
+        torch.cuda.synchronize()
+        dist.barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        with torch.cuda.stream(stream):
+            e0.record(stream)
+            for _ in range(reps):
+                for lin in lins:
+                    fn(lin)
+            e1.record(stream)
+        torch.cuda.synchronize()
+        t = torch.tensor([e0.elapsed_time(e1) * 1e3 / (reps * n_layers)], device=device, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    def nccl(lin):
+        rc = L.tq_linear_forward(lin.handle, C.c_void_p(x.data_ptr()), tq.TQ_F16, m, C.c_void_p(y.data_ptr()), sp)
+        if rc:
+            raise RuntimeError(L.tq_last_error().decode())
+        return all_gather_rows(y, OUT_F, world)
+
+    flops = 2.0 * m * OUT_F * IN_F
+    us = timed(nccl)
+    res["nccl_all_gather"] = {"us_per_layer": us, "tflops_aggregate": flops / (us * 1e-6) / 1e12, "tok_per_s": m / (us * 1e-6)}
+    if exchange is not None:
+        step = [0]
+
+        def ex(lin):
+            half = step[0] & 1
+            step[0] += 1
+            base = half * m * OUT_F * 2
+            lin.forward_strided(x, exchange.local + base + s * 2, OUT_F, stream=stream)
+            exchange.broadcast(base + s * 2, m, rows * 2, OUT_F * 2, stream=stream)
+            exchange.wait(stream=stream)
+
+        us_x = timed(ex)
+        exchange.check_status()
+        # the last layer's gathered result against the all-gather of the same shard
+        with torch.cuda.stream(stream):
+            full = nccl(lins[(step[0] - 1) % n_layers])
+        torch.cuda.synchronize()
+        got = exchange.buf.tensor((2, m, OUT_F), torch.float16)[(step[0] - 1) & 1]
+        same = torch.tensor([1.0 if torch.equal(full, got) else 0.0], device=device)
+        dist.all_reduce(same, op=dist.ReduceOp.MIN)
+        res["exchange"] = {"us_per_layer": us_x, "tflops_aggregate": flops / (us_x * 1e-6) / 1e12, "tok_per_s": m / (us_x * 1e-6),
+                           "bytes_to_each_peer": m * rows * 2,
+                           "path": "strided-output GEMM into the shared result + tq_exchange_broadcast + tq_exchange_wait",
+                           "identical_to_all_gather_on_every_rank": bool(same.item() == 1.0)}
+        exchange.close()
+    for lin in lins:
+        lin.close()
+    return res
 
 
 # ---- secondary: decoder-layer projections at decode batch sizes (Qwen2.5-7B shapes) ----------------
