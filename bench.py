@@ -807,13 +807,22 @@ def bench_decoder_layer(tq, L, device, stream, cbs, args):
             for _ in range(3):
                 one_pass()
         torch.cuda.synchronize()
+        # one pass = 7 (or 4) library calls of two or three kernels each: replayed as a CUDA graph, as a decode
+        # step would be, so that the figure is the kernels' and not the host's launch rate
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=stream):
+            one_pass()
+        with torch.cuda.stream(stream):
+            graph.replay()
+        torch.cuda.synchronize()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         with torch.cuda.stream(stream):
             e0.record(stream)
             for _ in range(reps):
-                one_pass()
+                graph.replay()
             e1.record(stream)
         torch.cuda.synchronize()
+        del graph
         return e0.elapsed_time(e1) * 1e3 / reps
 
     for tag, shp in (("", shapes), ("fused_", fused_shapes)):

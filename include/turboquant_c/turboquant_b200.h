@@ -85,6 +85,19 @@ int tq_fit_layer_codebooks(const float* weight, int out_features, int in_feature
                            int residual_bits, int iterations, float* primary_centroids, float* primary_boundaries,
                            float* residual_centroids, float* residual_boundaries, void* stream);
 
+/** metal/turboquant_qjl.metal:52-137 (tq_qjl_compress): the shader's 1-bit residual compression with a dense
+ *  +-1 projection.  residual fp32 [num_tokens, num_heads, head_dim]; proj_dim a power of two <= 1024;
+ *  signs_out uint32 [num_tokens * num_heads * ceil(proj_dim / 32)] (bit i of word w = sign of projection
+ *  32 w + i, 1 for >= 0); norms_out fp32 [num_tokens * num_heads] (the shader's tree sum over the first
+ *  min(head_dim, proj_dim) squares).  Host or device pointers.  At most 65535 tokens per call. */
+int tq_qjl_compress(const float* residual, int num_tokens, int num_heads, int head_dim, int proj_dim, uint32_t proj_seed,
+                    uint32_t* signs_out, float* norms_out, void* stream);
+/** metal/turboquant_qjl.metal:163-216 (tq_qjl_dot_correction) for head head_idx:
+ *  corrections[q * num_keys + k] = sqrt(pi/2) / proj_dim * (2 * popcount(~(signs_q ^ signs_k)) - proj_dim) * norms_k
+ *  (the shader's index expression `query_idx * gid.x + key_idx` equals this one for query 0, the decode case). */
+int tq_qjl_dot_correction(const uint32_t* signs_q, const uint32_t* signs_k, const float* norms_k, int num_queries,
+                          int num_keys, int num_heads, int head_idx, int proj_dim, float* corrections, void* stream);
+
 /** Largest power of two <= max_block dividing in_features (src/converter.cpp:228-240). */
 uint32_t tq_adaptive_block_size(int in_features, uint32_t max_block);
 /** N of the first ".layers.N." in a tensor name, -1 if none (src/converter.cpp:52-59). */

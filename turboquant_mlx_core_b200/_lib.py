@@ -138,6 +138,8 @@ def load() -> C.CDLL:
     sig("tq_adaptive_block_size", u32, [i, u32])
     sig("tq_layer_index", i, [C.c_char_p])
     sig("tq_is_sensitive_layer", i, [i, i, i, i])
+    sig("tq_qjl_compress", i, [vp, i, i, i, i, u32, vp, vp, vp])
+    sig("tq_qjl_dot_correction", i, [vp, vp, vp, i, i, i, i, i, vp, vp])
     sig("tq_decode_buffer_create", vp, [i, i, i])
     sig("tq_decode_buffer_free", None, [vp])
     sig("tq_decode_buffer_window_size", i, [vp])

@@ -135,6 +135,31 @@ def is_sensitive_layer(index: int, max_index: int, sensitive_start: int, sensiti
     return bool(_lib.load().tq_is_sensitive_layer(int(index), int(max_index), int(sensitive_start), int(sensitive_end)))
 
 
+def qjl_compress(residual, proj_dim: int, proj_seed: int):
+    """metal/turboquant_qjl.metal tq_qjl_compress: residual fp32 [tokens, heads, head_dim] (numpy) ->
+    (signs uint32 [tokens, heads, ceil(proj_dim / 32)], norms fp32 [tokens, heads])."""
+    L = _lib.load()
+    r = np.ascontiguousarray(residual, np.float32)
+    t, h, d = r.shape
+    words = (proj_dim + 31) // 32
+    signs = np.zeros((t, h, words), np.uint32)
+    norms = np.zeros((t, h), np.float32)
+    check(L.tq_qjl_compress(_ptr(r), t, h, d, int(proj_dim), int(proj_seed) & 0xFFFFFFFF, _ptr(signs), _ptr(norms), None), "qjl_compress")
+    return signs, norms
+
+
+def qjl_dot_correction(signs_q, signs_k, norms_k, head_idx: int, proj_dim: int):
+    """metal/turboquant_qjl.metal tq_qjl_dot_correction: -> fp32 [num_queries, num_keys] for one head."""
+    L = _lib.load()
+    sq = np.ascontiguousarray(signs_q, np.uint32)
+    sk = np.ascontiguousarray(signs_k, np.uint32)
+    nk = np.ascontiguousarray(norms_k, np.float32)
+    out = np.zeros((sq.shape[0], sk.shape[0]), np.float32)
+    check(L.tq_qjl_dot_correction(_ptr(sq), _ptr(sk), _ptr(nk), sq.shape[0], sk.shape[0], sk.shape[1], int(head_idx), int(proj_dim),
+                                  _ptr(out), None), "qjl_dot_correction")
+    return out
+
+
 def codebook_from_centroids(centroids) -> Codebook:
     c = _np(centroids, np.float32)
     b = ((c[:-1] + c[1:]) * np.float32(0.5)).astype(np.float32)

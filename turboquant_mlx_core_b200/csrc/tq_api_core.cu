@@ -261,6 +261,51 @@ int tq_is_sensitive_layer(int layer_index, int max_layer_index, int sensitive_st
     return 0;
 }
 
+// metal/turboquant_qjl.metal:52-137 (tq_qjl_compress)
+int tq_qjl_compress(const float* residual, int num_tokens, int num_heads, int head_dim, int proj_dim, uint32_t proj_seed,
+                    uint32_t* signs_out, float* norms_out, void* stream) {
+    return guarded<int>(0, -1, [&]() {
+        TQ_REQUIRE(residual && signs_out && norms_out, "tq_qjl_compress: NULL argument");
+        auto st = static_cast<cudaStream_t>(stream);
+        const size_t n = static_cast<size_t>(num_tokens) * num_heads * head_dim;
+        const size_t n_vec = static_cast<size_t>(num_tokens) * num_heads, words = (static_cast<size_t>(proj_dim) + 31) / 32;
+        DeviceBuffer in_stage, s_stage, n_stage;
+        const float* d_r = device_view(residual, n, in_stage, st);
+        const bool s_dev = is_device_pointer(signs_out), n_dev = is_device_pointer(norms_out);
+        uint32_t* d_s = signs_out;
+        float* d_n = norms_out;
+        if (!s_dev) { s_stage.reserve(n_vec * words * 4); d_s = s_stage.as<uint32_t>(); }
+        if (!n_dev) { n_stage.reserve(n_vec * 4); d_n = n_stage.as<float>(); }
+        launch_qjl_compress(d_r, num_tokens, num_heads, head_dim, proj_dim, proj_seed, d_s, d_n, st);
+        if (!s_dev && n_vec) TQ_CUDA(cudaMemcpyAsync(signs_out, d_s, n_vec * words * 4, cudaMemcpyDeviceToHost, st));
+        if (!n_dev && n_vec) TQ_CUDA(cudaMemcpyAsync(norms_out, d_n, n_vec * 4, cudaMemcpyDeviceToHost, st));
+        if (!s_dev || !n_dev || in_stage.bytes()) TQ_CUDA(cudaStreamSynchronize(st));
+        return 0;
+    });
+}
+
+// metal/turboquant_qjl.metal:163-216 (tq_qjl_dot_correction); corrections[query * num_keys + key]
+int tq_qjl_dot_correction(const uint32_t* signs_q, const uint32_t* signs_k, const float* norms_k, int num_queries, int num_keys,
+                          int num_heads, int head_idx, int proj_dim, float* corrections, void* stream) {
+    return guarded<int>(0, -1, [&]() {
+        TQ_REQUIRE(signs_q && signs_k && norms_k && corrections && num_queries >= 0 && num_keys >= 0, "tq_qjl_dot_correction: bad argument");
+        auto st = static_cast<cudaStream_t>(stream);
+        const size_t words = (static_cast<size_t>(proj_dim) + 31) / 32;
+        DeviceBuffer q_stage, k_stage, n_stage, c_stage;
+        const uint32_t* d_q = device_view(signs_q, static_cast<size_t>(num_queries) * num_heads * words, q_stage, st);
+        const uint32_t* d_k = device_view(signs_k, static_cast<size_t>(num_keys) * num_heads * words, k_stage, st);
+        const float* d_n = device_view(norms_k, static_cast<size_t>(num_keys) * num_heads, n_stage, st);
+        const size_t total = static_cast<size_t>(num_queries) * num_keys;
+        const bool c_dev = is_device_pointer(corrections);
+        float* d_c = corrections;
+        if (!c_dev) { c_stage.reserve(total * 4); d_c = c_stage.as<float>(); }
+        launch_qjl_dot_correction(d_q, d_k, d_n, num_queries, num_keys, num_heads, head_idx, proj_dim, d_c, st);
+        if (!c_dev && total) TQ_CUDA(cudaMemcpyAsync(corrections, d_c, total * 4, cudaMemcpyDeviceToHost, st));
+        TQ_CUDA(cudaStreamSynchronize(st));
+        return 0;
+    });
+}
+
 int tq_wht_rotate(const float* in, float* out, int rows, int cols, uint32_t seed, uint32_t block, int inverse,
                   void* stream) {
     return guarded<int>(0, -1, [&]() {

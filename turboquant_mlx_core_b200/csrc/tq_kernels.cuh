@@ -121,6 +121,12 @@ int launch_codebook_fit(const float* d_data, long n, int bits, int iterations, c
 void launch_layer_samples(const float* d_weight, const float* d_row_norms, long rows, int in, uint32_t block, uint32_t seed_p,
                           const float* primary_centroids, int n_primary, float* d_scaled, float* d_residual, cudaStream_t stream);
 
+// tq_qjl_shader.cu — the reference's QJL shader kernels (metal/turboquant_qjl.metal).
+void launch_qjl_compress(const float* d_residual, int num_tokens, int num_heads, int head_dim, int proj_dim, uint32_t seed,
+                         uint32_t* d_signs, float* d_norms, cudaStream_t stream);
+void launch_qjl_dot_correction(const uint32_t* d_signs_q, const uint32_t* d_signs_k, const float* d_norms_k, int num_queries, int num_keys,
+                               int num_heads, int head_idx, int proj_dim, float* d_corrections, cudaStream_t stream);
+
 // tq_kv_kernels.cu — KV-cache encoder with several destinations: the n_vec input vectors
 // ([n_vec, head_dim], contiguous) are cut into segments of vec_per_seg vectors and segment s is
 // written to segs[s] (at most 32 segments per launch).  A decode step that appends one token to
