@@ -6,6 +6,9 @@
 //   tq_qjl_dot_correction (lines 163-216): matches = popcount(~(q ^ k)) summed over the words (unused high
 //     bits of a last partial word are equal in both operands and so count as matches, as in the shader);
 //     correction = sqrt(pi/2) / proj_dim * (2 * matches - proj_dim) * norm_k, evaluated left to right.
+// The hash takes bit 0 of (h ^ h >> 16) * odd with h = seed ^ row * A ^ col * B: that bit is an XOR of a row term
+// and a column term, so the projection matrix has rank one (sign(row, col) = a(row) * b(col)) and a vector's sign
+// word is one fixed pattern or its complement.  Kept as the shader has it.
 // This is the residual correction the reference ships as a shader; the KV cache's own 1-bit residual
 // (src/kv_cache.cpp:215-258, a +-1 diagonal) is what the attention kernels read.
 #include <cstdint>
