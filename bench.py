@@ -630,6 +630,40 @@ def bench_side_kernels(tq, L, layers, device, stream, args):
     res["kv_append_1_token_x16_seqs"]["us_per_step_batched_call"] = us
     for c in seqs:
         c.close()
+
+    # hybrid_attention's window branch: one query position over a 131 072-token fp16 decode window
+    # (4 KV / 28 query heads, d 128): 4 * head_dim bytes per (token, KV head) = 268 MB > L2
+    try:
+        wtok, wheads, wq = 131072, 4, 28
+        kfull = torch.randn((wtok, wheads, dim), device=device).half()
+        wcache = tq.TQKVCache(1, wheads, dim)
+        for t0 in range(0, wtok, 16384):
+            wcache.append(0, kfull[t0:t0 + 16384], kfull[t0:t0 + 16384], stream=stream)
+        buf = tq.DecodeBuffer(wtok, wheads, dim)
+        buf.rebuild(kfull, kfull, stream=stream)
+        qw = torch.randn((wq, dim), device=device).half()
+        ow = torch.empty_like(qw)
+        us = timed(lambda: tq.hybrid_attention(wcache, buf, 0, qw, out=ow, stream=stream), reps=10)
+        b = wtok * wheads * 4 * dim
+        res["window_attention_1seq_ctx131072"] = {"us": us, "gb_per_s": b / (us * 1e-6) / 1e9, "frac_of_peak": b / (us * 1e-6) / 1e9 / peak}
+        wcache.close()
+        buf.close()
+        del kfull
+    except Exception as exc:
+        res["window_attention_1seq_ctx131072"] = {"error": str(exc)}
+
+    # Lloyd-Max fit of a 16-entry codebook to the 16.8 M rotated samples of a 4096 x 4096 layer
+    try:
+        samples = torch.randn((OUT_F * IN_F,), device=device)
+        t0 = time.perf_counter()
+        cb, it_run = tq.generate_codebook_from_data(samples, 4, 100, return_iterations=True)
+        torch.cuda.synchronize()
+        dt = time.perf_counter() - t0
+        res["codebook_fit_16M_samples"] = {"ms": dt * 1e3, "iterations": it_run, "us_per_iteration": dt * 1e6 / max(it_run, 1),
+                                           "gb_per_s_per_iteration": samples.numel() * 4 / (dt / max(it_run, 1)) / 1e9}
+        del samples
+    except Exception as exc:
+        res["codebook_fit_16M_samples"] = {"error": str(exc)}
     return res
 
 

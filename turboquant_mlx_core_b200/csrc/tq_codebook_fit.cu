@@ -52,8 +52,8 @@ __global__ void __launch_bounds__(kFitThreads) fit_partial_kernel(const float* _
         h_cnt[b * kFitThreads + tid] = 0u;
     }
     __syncthreads();
-    // a block takes whole chunks of 2^20 values, so a thread's count fits 32 bits whatever n is
-    const long chunk = 1L << 20;
+    // blocks take chunks of 2^14 values in turn; a thread's 32-bit count holds n / (blocks * 256) values
+    const long chunk = 1L << 14;
     for (long c0 = static_cast<long>(blockIdx.x) * chunk; c0 < n_values; c0 += static_cast<long>(gridDim.x) * chunk) {
         const long c1 = c0 + chunk < n_values ? c0 + chunk : n_values;
         for (long i = c0 + tid; i < c1; i += kFitThreads) {
@@ -184,7 +184,8 @@ int launch_codebook_fit(const float* d_data, long n, int bits, int iterations, c
         int dev = 0, sms = 148;
         TQ_CUDA(cudaGetDevice(&dev));
         TQ_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
-        const long chunks = (n + (1L << 20) - 1) >> 20;
+        TQ_REQUIRE(n < (1L << 40), "tq_codebook_fit: at most 2^40 samples");
+        const long chunks = (n + (1L << 14) - 1) >> 14;
         const int blocks = static_cast<int>(std::min<long>(chunks, 2L * sms));
         const size_t smem = (sizeof(double) + sizeof(unsigned int)) * kFitMaxBins * kFitThreads;
         static bool configured[64] = {false};
