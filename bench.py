@@ -179,7 +179,9 @@ def run_cuda(args):
         from turboquant_mlx_core_b200.sharding import Exchange
         err = None
         try:
-            exchange = Exchange(2 * world * OUT_F * 2)
+            # [2 gather buffers][world][OUT_F] fp16, then the packet area of the flag-in-data variant:
+            # [2 epoch parities][world source ranks][OUT_F / 4 packets of 16 bytes]
+            exchange = Exchange(2 * world * OUT_F * 2 + 2 * world * OUT_F * 4)
         except Exception as exc:
             err = str(exc)
         ok_t = torch.tensor([0.0 if err else 1.0], device=device)
@@ -189,12 +191,19 @@ def run_cuda(args):
                 exchange.close()
             exchange, exchange_note = None, "shared buffers could not be mapped on every rank: independent layers, no exchange"
 
+    gather_mode = os.environ.get("TQ_BENCH_GATHER", "packets")
+    fused_gather = gather_mode != "split"
+    packets_off = 2 * world * OUT_F * 2
     if exchange is not None:
+        torch.cuda.synchronize()
+        dist.barrier()
         # every fused call below waits for the exchange before it; this one is there for the first
         with torch.cuda.stream(stream):
-            exchange.broadcast(0, 1, 16, 16, stream=stream)
-
-    fused_gather = os.environ.get("TQ_BENCH_GATHER", "fused") != "split"
+            if gather_mode == "packets":
+                exchange.forward_allgather_packets(layers[-1], x_dev[nbuf - 1:nbuf], y_dev[nbuf - 1:nbuf], packets_off, wait=False,
+                                                   stream=stream)
+            else:
+                exchange.broadcast(0, 1, 16, 16, stream=stream)
 
     def one_pass():
         for i, lin in enumerate(layers):
@@ -203,6 +212,10 @@ def run_cuda(args):
                                          C.c_void_p(y_dev[i].data_ptr()), sp)
                 if rc:
                     raise RuntimeError(L.tq_last_error().decode())
+            elif gather_mode == "packets":
+                # ONE kernel per layer: poll the packets of the previous layer's gather, GEMV into this rank's own rows,
+                # then the last CTA writes them to the other ranks as {data, epoch} packets: no fence, no flag store
+                exchange.forward_allgather_packets(lin, x_dev[i:i + 1], y_dev[i:i + 1], packets_off, wait=True, stream=stream)
             elif fused_gather:
                 # ONE kernel per layer: wait for the previous layer's gather, GEMV into this rank's rows of
                 # the gathered output, copy them to the peers, raise the flags
@@ -228,6 +241,8 @@ def run_cuda(args):
         one_pass()
     stream.synchronize()
     launch_mode = "CUDA graph of one GEMV per layer" + ("" if exchange is None else
+                                                         " fused with the wait for the previous gather and the peer copy of its output as "
+                                                         "flag-in-data packets" if gather_mode == "packets" else
                                                          " fused with the wait for the previous gather, the peer copy of its output and the flags"
                                                          if fused_gather else " + tq_exchange_wait before and tq_exchange_broadcast after it")
     try:
@@ -304,6 +319,32 @@ def run_cuda(args):
     gathered_ok = None
     if exchange is None:
         same = bool(torch.equal(y_dev.cpu(), y_host))
+    elif gather_mode == "packets":
+        # every rank has finished its kernels, so every packet has landed: the two epoch parities hold the last two
+        # layers' rows of every OTHER rank; this rank's own rows are in y_dev
+        dist.barrier()
+        torch.cuda.synchronize()
+        exchange.check_status()
+        for lin in layers:
+            lin.check_status()
+        same = bool(torch.equal(y_dev.cpu(), y_host))
+        n_pk = OUT_F // 4
+        raw = exchange.buf.tensor((packets_off + 2 * world * n_pk * 16,), torch.uint8)[packets_off:].view(torch.int32).view(2, world, n_pk, 4)
+        other = (rank + 1) % world
+        newest = 0 if int(raw[0, other, 0, 1].item()) > int(raw[1, other, 0, 1].item()) else 1   # parity of the last layer's epoch
+        gath = torch.empty((2, world, OUT_F), device=device, dtype=torch.float16)
+        for k, parity in enumerate((1 - newest, newest)):            # k = 0: layer nbuf - 2, k = 1: layer nbuf - 1
+            for src in range(world):
+                if src == rank:
+                    gath[k, src] = y_dev[nbuf - 2 + k]
+                else:
+                    exchange.unpack_packets(packets_off + ((parity * world + src) * n_pk) * 16, n_pk, gath[k, src], stream=None)
+        torch.cuda.synchronize()
+        ref = gath.clone()
+        dist.broadcast(ref, src=0)
+        ok = torch.tensor([1.0 if torch.equal(ref, gath) else 0.0], device=device)
+        dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+        gathered_ok = bool(ok.item() == 1.0)
     else:
         # the last two layers' gathered outputs sit in the two buffers: this rank's slots must equal
         # the host path's results, and every rank must hold the same gathered bytes
@@ -337,7 +378,8 @@ def run_cuda(args):
                    "launch": launch_mode,
                    "per_gpu": ("independent layers, no collective" if exchange is None else
                                "one 4096 x 4096 row shard of a (4096 N) x 4096 layer per launch; after every layer the fp16 output "
-                               "shards are all-gathered over NVLink (peer stores + flags, no collective library)"),
+                               "shards are all-gathered over NVLink (peer stores" + (" of {data, epoch} packets" if gather_mode == "packets"
+                                                                                    else " + flags") + ", no collective library)"),
                    "exchange_note": exchange_note,
                    "vs_baseline_note": "published 671 tok/s is the reference on an Apple GPU at block 512"},
         "gb_per_s": achieved * world,

@@ -308,6 +308,23 @@ int tq_exchange_merge_attention(const void* outs_fp16, const void* lses_fp32, in
 int tq_linear_forward_allgather(tq_linear_t lin, tq_exchange_t ex, const void* x_fp16_device, int batch, void* const* dst,
                                 int n_dst, long dst_row_stride, long row_offset, void* const* flags, int n_flags,
                                 const void* wait_local_flags, int n_wait, void* stream);
+
+/** The same all-gather with the flag inside the data ("packets"): the kernel stores this rank's rows to
+ *  y_fp16_device (plain fp16, rows y_row_stride apart) and its last CTA writes them to every OTHER rank as
+ *  16-byte packets {2 halves, epoch, 2 halves, epoch} - each 8-byte half lands atomically, so a reader that
+ *  sees the epoch in both halves has the data, and no fence or separate flag is on the path.
+ *  packet_buffers[r] is rank r's packet buffer (its own for r = this rank; peers' mapped with
+ *  tq_shared_open), each 2 * world * batch * (out / 4) * 16 bytes, zero-filled before the first use:
+ *  [epoch parity][source rank][packet].  wait_previous != 0: every CTA first polls (bounded, 1 s) the
+ *  packets the other ranks wrote in the previous call of this sequence - the dependency a decoder layer has
+ *  on the gathered output of the layer before.  Every rank issues the same sequence of calls on `ex`
+ *  (and none of tq_exchange_broadcast / _wait in between: they share the epochs).  out % 4 == 0, batch <= 8.
+ *  tq_exchange_unpack_packets turns a source rank's packets back into contiguous fp16.
+ *  No counterpart in the reference. */
+int tq_linear_forward_allgather_packets(tq_linear_t lin, tq_exchange_t ex, const void* x_fp16_device, int batch,
+                                        void* y_fp16_device, long y_row_stride, void* const* packet_buffers,
+                                        int wait_previous, void* stream);
+int tq_exchange_unpack_packets(const void* packets, long n_packets, void* out_fp16, void* stream);
 /* Element-wise glue of a decoder layer, device fp16 in and out, fp32 arithmetic.  The reference
  * leaves these to MLX in the host application (no file of its own computes them); they are here so
  * that a whole tensor-parallel decode step runs on this library's stream without a framework.

@@ -113,6 +113,55 @@ def test_forward_fused_with_all_gather(tq, oracle):
         lin.close()
 
 
+def test_forward_fused_with_packet_all_gather(tq, oracle):
+    """tq_linear_forward_allgather_packets with two ranks emulated on one stream: each rank's kernel stores its
+    rows locally and its last CTA writes them to the other rank as {2 halves, epoch, 2 halves, epoch} packets
+    (region [epoch parity][source rank]); the next step's kernels poll those packets before they start, and
+    tq_exchange_unpack_packets gives the rows back."""
+    torch = pytest.importorskip("torch")
+    L = tq.load()
+    rng = np.random.default_rng(22)
+    cb = oracle.codebook(4)[0]
+    world, rows, cols = 2, 208, 512
+    lins = []
+    for r in range(world):
+        w = (rng.standard_normal((rows, cols)) * 0.02).astype(np.float16).astype(np.float32)
+        pp, pr, norms, seeds = oracle.quantize_weight(w, cb, cb, 4, 4, 128, True)
+        lins.append(tq.TurboQuantLinear(cols, rows, tq.QuantizedWeight(pp, pr, norms, seeds), tq.codebook_from_centroids(cb),
+                                        tq.codebook_from_centroids(cb), 128))
+    for batch in (1, 3):
+        n_pk = batch * rows // 4
+        bufs = [torch.zeros(2 * world * n_pk * 16, dtype=torch.uint8, device="cuda") for _ in range(world)]
+        ex = [L.tq_exchange_create(r, world) for r in range(world)]
+        for step in range(4):
+            x = torch.from_numpy(rng.standard_normal((batch, cols)).astype(np.float16)).cuda()
+            want = [lin.forward(x) for lin in lins]
+            ys = [torch.zeros((batch, rows), dtype=torch.float16, device="cuda") for _ in range(world)]
+            for r in range(world):
+                rc = L.tq_linear_forward_allgather_packets(lins[r].handle, ex[r], C.c_void_p(x.data_ptr()), batch,
+                                                           C.c_void_p(ys[r].data_ptr()), rows, _ptrs([b.data_ptr() for b in bufs]),
+                                                           1 if step > 0 else 0, None)
+                assert rc == 0, L.tq_last_error().decode()
+            torch.cuda.synchronize()
+            parity = (step + 1) & 1
+            for r in range(world):
+                assert torch.equal(ys[r], want[r]), (batch, step, r)
+                src = 1 - r
+                region = bufs[r][(parity * world + src) * n_pk * 16:(parity * world + src + 1) * n_pk * 16]
+                pk = region.view(torch.int32).view(n_pk, 4)
+                assert bool((pk[:, 1] == step + 1).all()) and bool((pk[:, 3] == step + 1).all())
+                got = torch.empty((batch, rows), dtype=torch.float16, device="cuda")
+                assert L.tq_exchange_unpack_packets(C.c_void_p(region.data_ptr()), n_pk, C.c_void_p(got.data_ptr()), None) == 0
+                torch.cuda.synchronize()
+                assert torch.equal(got, want[src]), (batch, step, r)
+        for r in range(world):
+            assert L.tq_exchange_status(ex[r]) == 0
+            lins[r].check_status()
+            L.tq_exchange_free(ex[r])
+    for lin in lins:
+        lin.close()
+
+
 def test_wait_for_a_flag_nobody_raises_gives_up(tq):
     """A rank that never broadcasts: the wait runs out after its limit (about a second) and the
     status says so; the device stays usable."""

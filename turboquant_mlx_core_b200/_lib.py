@@ -140,6 +140,8 @@ def load() -> C.CDLL:
     sig("tq_is_sensitive_layer", i, [i, i, i, i])
     sig("tq_qjl_compress", i, [vp, i, i, i, i, u32, vp, vp, vp])
     sig("tq_qjl_dot_correction", i, [vp, vp, vp, i, i, i, i, i, vp, vp])
+    sig("tq_linear_forward_allgather_packets", i, [vp, vp, vp, i, vp, C.c_long, C.POINTER(C.c_void_p), i, vp])
+    sig("tq_exchange_unpack_packets", i, [vp, C.c_long, vp, vp])
     sig("tq_decode_buffer_create", vp, [i, i, i])
     sig("tq_decode_buffer_free", None, [vp])
     sig("tq_decode_buffer_window_size", i, [vp])

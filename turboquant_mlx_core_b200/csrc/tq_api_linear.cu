@@ -238,6 +238,25 @@ public:
                                     d_status_, sm_count_, st, sig, slot, 0u, counter_.as<unsigned int>(), &g, n_flags);
     }
 
+    // The same with the flag-in-data exchange: y (this rank's rows, plain fp16) plus packets to every other rank.
+    void forward_allgather_packets(const void* x, int batch, void* y, long y_stride, void* const* packet_bufs, int rank, int world,
+                                   unsigned int* epoch, bool wait, unsigned int* wait_epoch, cudaStream_t st) {
+        TQ_REQUIRE(x && y && packet_bufs, "forward_allgather_packets: NULL argument");
+        TQ_REQUIRE(batch >= 1 && batch <= 8, "forward_allgather_packets: batch must be 1..8");
+        TQ_REQUIRE(world >= 1 && world <= 8 && rank >= 0 && rank < world, "forward_allgather_packets: bad rank / world");
+        TQ_REQUIRE(y_stride >= out_, "forward_allgather_packets: row stride smaller than the layer's rows");
+        TQ_REQUIRE(tq::is_device_pointer(x) && tq::is_device_pointer(y), "forward_allgather_packets: x and y must be device pointers");
+        TQ_CUDA(cudaSetDevice(device_));
+        __half* d[1] = {static_cast<__half*>(y)};
+        tq::GemvGather g{epoch, nullptr, wait ? 1 : 0, wait_epoch};
+        g.ll_rank = rank;
+        g.ll_world = world;
+        for (int r = 0; r < world; ++r) g.ll_base[r] = packet_bufs[r];
+        tq::launch_tq8_gemv_scatter(codes_.as<uint8_t>(), norms_.as<float>(), tables_.as<float>(), static_cast<const __half*>(x), d, 1,
+                                    y_stride, out_, in_, batch, block_, dual_ ? 2 : 1, seed_p_, seed_r_, scratch_.as<void>(), d_status_,
+                                    sm_count_, st, nullptr, 0, 0u, counter_.as<unsigned int>(), &g, 0);
+    }
+
     void wait_peers(const void* flags, int n, unsigned int value, cudaStream_t st) {
         TQ_CUDA(cudaSetDevice(device_));
         tq::launch_peer_wait(static_cast<const unsigned int*>(flags), n, value, d_status_, st);
@@ -546,6 +565,7 @@ int tq_linear_forward_scatter_signal(tq_linear_t lin, const void* x_fp16_device,
 
 // (tq_exchange_s is defined in tq_api_peer.cu; only its counters are needed here)
 extern "C" unsigned int* tq_exchange_words(tq_exchange_t ex, int* rank);
+extern "C" unsigned int* tq_exchange_words_world(tq_exchange_t ex, int* rank, int* world);
 
 int tq_linear_forward_allgather(tq_linear_t lin, tq_exchange_t ex, const void* x_fp16_device, int batch, void* const* dst,
                                 int n_dst, long dst_row_stride, long row_offset, void* const* flags, int n_flags,
@@ -557,6 +577,19 @@ int tq_linear_forward_allgather(tq_linear_t lin, tq_exchange_t ex, const void* x
         unsigned int* w = tq_exchange_words(ex, &rank);
         lin->impl->forward_allgather(x_fp16_device, batch, dst, n_dst, dst_row_stride, row_offset, flags, n_flags, rank, w + 1,
                                      wait_local_flags, n_wait, w + 2, static_cast<cudaStream_t>(stream));
+        return 0;
+    });
+}
+
+int tq_linear_forward_allgather_packets(tq_linear_t lin, tq_exchange_t ex, const void* x_fp16_device, int batch, void* y_fp16_device,
+                                        long y_row_stride, void* const* packet_buffers, int wait_previous, void* stream) {
+    return guarded<int>(0, -1, [&]() {
+        TQ_REQUIRE(lin && lin->impl, "tq_linear_forward_allgather_packets: NULL handle");
+        TQ_REQUIRE(ex != nullptr, "tq_linear_forward_allgather_packets: NULL exchange");
+        int rank = 0, world = 0;
+        unsigned int* w = tq_exchange_words_world(ex, &rank, &world);
+        lin->impl->forward_allgather_packets(x_fp16_device, batch, y_fp16_device, y_row_stride, packet_buffers, rank, world, w + 1,
+                                             wait_previous != 0, w + 2, static_cast<cudaStream_t>(stream));
         return 0;
     });
 }

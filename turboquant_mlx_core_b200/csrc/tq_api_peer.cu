@@ -128,5 +128,19 @@ unsigned int* tq_exchange_words(tq_exchange_t ex, int* rank) {
     if (rank) *rank = ex->rank;
     return ex->words.as<unsigned int>();
 }
+unsigned int* tq_exchange_words_world(tq_exchange_t ex, int* rank, int* world) {
+    if (rank) *rank = ex->rank;
+    if (world) *world = ex->world;
+    return ex->words.as<unsigned int>();
+}
+
+int tq_exchange_unpack_packets(const void* packets, long n_packets, void* out_fp16, void* stream) {
+    return guarded<int>(0, -1, [&]() {
+        TQ_REQUIRE(packets && out_fp16 && n_packets >= 0, "tq_exchange_unpack_packets: bad argument");
+        launch_exchange_unpack_packets(static_cast<const uint4*>(packets), n_packets, static_cast<__half*>(out_fp16),
+                                       static_cast<cudaStream_t>(stream));
+        return 0;
+    });
+}
 
 }  // extern "C"

@@ -166,6 +166,15 @@ struct ScatterArgs {
     const unsigned int* wait_flags;
     int n_wait;
     unsigned int* wait_epoch;
+    // Flag-in-data exchange (ll != 0, with bulk): instead of data, a fence and a flag, the completing CTA
+    // writes 16-byte packets {2 halves, epoch, 2 halves, epoch} - each 8-byte half is written atomically
+    // by the one store, so a reader that sees the epoch in both halves holds valid data and nothing has to
+    // be fenced.  Every rank's packet buffer is [2 halves of the double buffer][ll_world source ranks]
+    // [packets] (ll_base[r] = rank r's buffer, ll_base[ll_rank] this rank's own); the half is the parity of
+    // the epoch.  With n_wait > 0 every CTA first polls - bounded - the packets all other ranks wrote for
+    // epoch *wait_epoch + 1.
+    int ll, ll_rank, ll_world;
+    uint4* ll_base[8];
 };
 
 // One output element goes to the caller's buffer and, when the call scatters, to the same
@@ -251,6 +260,50 @@ __device__ __forceinline__ void mma_tf32(float (&c)[4], uint32_t a0, uint32_t a1
     asm("mma.sync.aligned.m16n8k8.row.col.f32.tf32.tf32.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
         : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+// ---- flag-in-data exchange (see ScatterArgs): out of line, so that the decode loop keeps its registers ----
+struct LlBases {
+    uint4* p[8];
+};
+__device__ __noinline__ void ll_wait_packets(const unsigned int* wait_epoch, const uint4* mine, int rank, int world, long packets,
+                                             unsigned int* status) {
+    const unsigned int want = *reinterpret_cast<const volatile unsigned int*>(wait_epoch) + 1u;
+    const uint4* const half = mine + static_cast<size_t>(want & 1u) * world * packets;
+    const unsigned long long t0 = global_timer_ns();
+    for (int src = 0; src < world; ++src) {
+        if (src == rank) continue;
+        const uint4* region = half + static_cast<size_t>(src) * packets;
+        for (long i = threadIdx.x; i < packets; i += kCtaThreads) {
+            for (unsigned int spin = 0;; ++spin) {
+                uint4 pk;
+                asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];"
+                             : "=r"(pk.x), "=r"(pk.y), "=r"(pk.z), "=r"(pk.w)
+                             : "l"(region + i)
+                             : "memory");
+                if (static_cast<int>(pk.y - want) >= 0 && static_cast<int>(pk.w - want) >= 0) break;
+                if ((spin & 255u) == 255u && global_timer_ns() - t0 > 5ull * kWaitLimitNs) {   // 1 s: a peer is gone
+                    raise_status(status, 10u);
+                    return;
+                }
+            }
+        }
+    }
+}
+__device__ __noinline__ void ll_send_packets(const unsigned int* epoch, const __half* y, long y_stride, int per_row, int batch, int rank,
+                                             int world, LlBases bases) {
+    // packets of this launch to every other rank: no fence, no flag - the epoch travels with the data
+    const unsigned int value = *reinterpret_cast<const volatile unsigned int*>(epoch) + 1u;
+    const long packets = static_cast<long>(batch) * per_row;
+    const size_t region = (static_cast<size_t>(value & 1u) * world + rank) * packets;
+    for (long i = threadIdx.x; i < packets; i += kCtaThreads) {
+        const int n = static_cast<int>(i / per_row), c = static_cast<int>(i - static_cast<long>(n) * per_row);
+        const uint2 v = __ldcg(reinterpret_cast<const uint2*>(y + static_cast<size_t>(n) * y_stride + static_cast<size_t>(c) * 4));
+        for (int d = 0; d < world; ++d)
+            if (d != rank)
+                asm volatile("st.volatile.global.v4.u32 [%0], {%1, %2, %3, %2};" ::"l"(bases.p[d] + region + i), "r"(v.x), "r"(value), "r"(v.y)
+                             : "memory");
+    }
 }
 
 // BP = activation rows padded to 1, 2, 4 or 8 (compile time, so that the partial-sum ring
@@ -377,7 +430,12 @@ __device__ __forceinline__ void gemv_body(const GemvArgs& p, const ScatterArgs& 
     // Everything below reads or writes data the preceding kernels produce or still use.
     grid_dependency_sync();
     if constexpr (SCATTER) {
-        if (sargs.n_wait > 0) {
+        if (sargs.n_wait > 0 && sargs.ll) {
+            // the activation comes out of a flag-in-data exchange: every packet of every other rank must carry the epoch
+            ll_wait_packets(sargs.wait_epoch, sargs.ll_base[sargs.ll_rank], sargs.ll_rank, sargs.ll_world,
+                            static_cast<long>(p.batch) * (p.out / 4), p.status);
+            __syncthreads();
+        } else if (sargs.n_wait > 0) {
             // the activation comes out of an exchange: wait until every rank's part has arrived
             if (tid < sargs.n_wait) {
                 const unsigned int want = *reinterpret_cast<volatile unsigned int*>(sargs.wait_epoch) + 1u;
@@ -682,7 +740,7 @@ __device__ __forceinline__ void gemv_body(const GemvArgs& p, const ScatterArgs& 
     // the CTA that completes the grid publishes the flag everywhere.  Whoever then reads the flag
     // with acquire semantics sees all of this launch's results.
     if constexpr (SCATTER) {
-    if (sargs.n_signal > 0) {
+    if (sargs.n_signal > 0 || sargs.ll) {
         __shared__ unsigned int s_last;
         // results that went to other GPUs need a system-scope fence; with the bulk copy every CTA's
         // results are local and only the copying CTA pays for one
@@ -694,7 +752,19 @@ __device__ __forceinline__ void gemv_body(const GemvArgs& p, const ScatterArgs& 
             s_last = (prev == gridDim.x - 1) ? 1u : 0u;
         }
         __syncthreads();
-        if (s_last) {
+        if (s_last && sargs.ll) {
+            __threadfence();
+            LlBases bases;
+#pragma unroll
+            for (int d = 0; d < 8; ++d) bases.p[d] = sargs.ll_base[d];
+            ll_send_packets(sargs.epoch, p.y, sargs.y_stride, p.out / 4, p.batch, sargs.ll_rank, sargs.ll_world, bases);
+            __syncthreads();
+            if (tid == 0) {
+                *sargs.done_counter = 0u;  // ready for the next launch (stream order)
+                atomicAdd(sargs.epoch, 1u);
+                if (sargs.n_wait > 0) atomicAdd(sargs.wait_epoch, 1u);   // every CTA has read it by now
+            }
+        } else if (s_last) {
             __threadfence();
             if (sargs.bulk && sargs.n_peer > 0) {
                 // the whole block (batch rows of `out` halves, y_stride apart) to every peer: 16-byte
@@ -840,11 +910,27 @@ void launch_tq8_gemv_scatter(const uint8_t* codes, const float* norms, const flo
         sa.done_counter = done_counter;
     }
     if (gather != nullptr) {
-        TQ_REQUIRE(signal != nullptr && gather->epoch != nullptr, "tq8_gemv: the fused all-gather needs flags and an epoch counter");
+        TQ_REQUIRE((signal != nullptr || gather->ll_world > 0) && gather->epoch != nullptr,
+                   "tq8_gemv: the fused all-gather needs flags (or packet buffers) and an epoch counter");
         TQ_REQUIRE(gather->n_wait >= 0 && gather->n_wait <= 32, "tq8_gemv: 0..32 flags to wait for");
-        TQ_REQUIRE(gather->n_wait == 0 || (gather->wait_flags != nullptr && gather->wait_epoch != nullptr),
+        TQ_REQUIRE(gather->n_wait == 0 || ((gather->wait_flags != nullptr || gather->ll_world > 0) && gather->wait_epoch != nullptr),
                    "tq8_gemv: waiting needs the local flag array and the wait counter");
         sa.bulk = 1;
+        if (gather->ll_world > 0) {
+            TQ_REQUIRE(gather->ll_world <= 8 && gather->ll_rank >= 0 && gather->ll_rank < gather->ll_world, "tq8_gemv: bad rank / world");
+            TQ_REQUIRE(out % 4 == 0 && dst_stride % 4 == 0 && reinterpret_cast<uintptr_t>(y) % 8 == 0,
+                       "tq8_gemv: the flag-in-data exchange moves groups of four rows (8-byte aligned)");
+            sa.ll = 1;
+            sa.ll_rank = gather->ll_rank;
+            sa.ll_world = gather->ll_world;
+            for (int r = 0; r < gather->ll_world; ++r) {
+                TQ_REQUIRE(gather->ll_base[r] != nullptr, "tq8_gemv: NULL packet buffer");
+                sa.ll_base[r] = static_cast<uint4*>(gather->ll_base[r]);
+            }
+            sa.n_peer = 0;   // results are stored locally; the packets carry them to the other ranks
+            TQ_REQUIRE(done_counter != nullptr, "tq8_gemv: the exchange needs a completion counter in device memory");
+            sa.done_counter = done_counter;
+        }
         sa.epoch = gather->epoch;
         sa.wait_flags = gather->wait_flags;
         sa.n_wait = gather->n_wait;
@@ -930,7 +1016,7 @@ void launch_tq8_gemv_scatter(const uint8_t* codes, const float* norms, const flo
         cfg.attrs = attr;
         cfg.numAttrs = n_attr;
         // one destination with the layer's own row stride and no signal: the plain variant
-        const bool scatter = sa.n_peer > 0 || sa.n_signal > 0 || sa.y_stride != a.out;
+        const bool scatter = sa.n_peer > 0 || sa.n_signal > 0 || sa.ll != 0 || sa.y_stride != a.out;
 #define TQ_GEMV_LAUNCH(BPV)                                                   \
     if (scatter) TQ_CUDA(cudaLaunchKernelEx(&cfg, tq8_gemv_scatter_kernel<BPV>, a, sa)); \
     else TQ_CUDA(cudaLaunchKernelEx(&cfg, tq8_gemv_kernel<BPV>, a));

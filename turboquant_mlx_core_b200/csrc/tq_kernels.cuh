@@ -50,6 +50,9 @@ struct GemvGather {
     const unsigned int* wait_flags;
     int n_wait;
     unsigned int* wait_epoch;
+    // flag-in-data variant (ll_world > 0): every rank's packet buffer, this rank's own at [ll_rank]
+    int ll_rank = 0, ll_world = 0;
+    void* ll_base[8] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
 };
 void launch_tq8_gemv_scatter(const uint8_t* codes, const float* norms, const float* table, const __half* x,
                              __half* const* dst, int n_dst, long dst_stride, int out, int in, int batch, uint32_t block,
@@ -155,6 +158,7 @@ void launch_exchange_broadcast(const void* src, void* const* dst, int n_dst, int
 void launch_exchange_wait(const unsigned int* flags, int n, unsigned int* epoch, unsigned int* status, cudaStream_t stream);
 void launch_exchange_sum_f16(const __half* slots, int n_slots, long slot_stride, long count, const __half* residual, __half* out,
                              cudaStream_t stream);
+void launch_exchange_unpack_packets(const uint4* packets, long n_packets, __half* out, cudaStream_t stream);
 void launch_exchange_merge_attention(const __half* outs, const float* lses, int parts, long rows, int dim, long part_stride_o,
                                      long part_stride_l, __half* out, cudaStream_t stream);
 

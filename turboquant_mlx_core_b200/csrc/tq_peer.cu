@@ -123,6 +123,14 @@ __global__ void __launch_bounds__(256) exchange_sum_f16_kernel(const __half* __r
     }
 }
 
+// Packets of the flag-in-data exchange {2 halves, epoch, 2 halves, epoch} -> contiguous fp16 (4 per packet).
+__global__ void __launch_bounds__(256) exchange_unpack_packets_kernel(const uint4* __restrict__ packets, long n, uint2* __restrict__ out) {
+    for (long i = static_cast<long>(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += static_cast<long>(gridDim.x) * blockDim.x) {
+        const uint4 pk = packets[i];
+        out[i] = make_uint2(pk.x, pk.z);
+    }
+}
+
 // Softmax parts over disjoint token ranges of the same rows -> attention over the union:
 //   out = sum_p w_p * out_p / sum_p w_p,  w_p = exp(lse_p - max_p lse_p)   (parts in order).
 // outs: [parts][rows][dim] fp16 (part_stride_o elements apart), lses: [parts][rows] fp32.
@@ -213,6 +221,14 @@ void launch_exchange_sum_f16(const __half* slots, int n_slots, long slot_stride,
     cudaLaunchAttribute attr[1];
     cudaLaunchConfig_t cfg = pdl_config(dim3(static_cast<unsigned>(blocks)), dim3(256), stream, attr);
     TQ_CUDA(cudaLaunchKernelEx(&cfg, exchange_sum_f16_kernel, slots, n_slots, slot_stride, count, residual, out));
+}
+
+void launch_exchange_unpack_packets(const uint4* packets, long n_packets, __half* out, cudaStream_t stream) {
+    TQ_REQUIRE(reinterpret_cast<uintptr_t>(out) % 8 == 0, "packet unpack: the destination must be 8-byte aligned");
+    if (n_packets == 0) return;
+    const int blocks = static_cast<int>(n_packets + 255 < 296L * 256 ? (n_packets + 255) / 256 : 296);
+    exchange_unpack_packets_kernel<<<blocks, 256, 0, stream>>>(packets, n_packets, reinterpret_cast<uint2*>(out));
+    TQ_CUDA(cudaGetLastError());
 }
 
 void launch_exchange_merge_attention(const __half* outs, const float* lses, int parts, long rows, int dim, long part_stride_o,

@@ -255,6 +255,34 @@ class Exchange:
                                                         C.c_void_p(self.buf.local_flags) if wait else None, self.world,
                                                         _stream_ptr(stream)), "tq_linear_forward_allgather")
 
+    def rank_ptrs(self):
+        """Every rank's buffer address in RANK order (this rank's own at index rank)."""
+        others = iter(self.buf.ptrs[1:])
+        return [self.buf.local if r == self.rank else next(others) for r in range(self.world)]
+
+    def forward_allgather_packets(self, lin, x, y, packets_offset: int = 0, wait: bool = True, stream=None):
+        """tq_linear_forward_allgather_packets: y (device fp16 [batch, out]) gets this rank's rows; the other ranks
+        get them as flag-in-data packets in their buffers at byte `packets_offset`
+        ([epoch parity][source rank][batch * out / 4 packets of 16 bytes]); with wait=True every CTA first polls
+        the packets of the previous call.  The packet region must be zero before the first call."""
+        import ctypes as C
+        import numpy as np
+        from . import _lib
+        from .api import _ptr
+        batch = int(np.prod(x.shape[:-1])) if len(x.shape) > 1 else 1
+        bufs = (C.c_void_p * self.world)(*[p + packets_offset for p in self.rank_ptrs()])
+        _lib.check(self._L.tq_linear_forward_allgather_packets(lin.handle, self._h, _ptr(x), batch, _ptr(y), int(y.shape[-1]), bufs,
+                                                                1 if wait else 0, _stream_ptr(stream)),
+                   "tq_linear_forward_allgather_packets")
+
+    def unpack_packets(self, packets_offset: int, n_packets: int, out, stream=None):
+        """Packets at byte `packets_offset` of this rank's buffer -> contiguous fp16 in `out` (4 values per packet)."""
+        import ctypes as C
+        from . import _lib
+        from .api import _ptr
+        _lib.check(self._L.tq_exchange_unpack_packets(C.c_void_p(self.buf.local + packets_offset), int(n_packets), _ptr(out),
+                                                       _stream_ptr(stream)), "tq_exchange_unpack_packets")
+
     def wait(self, stream=None):
         import ctypes as C
         from . import _lib
