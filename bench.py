@@ -1000,9 +1000,10 @@ def bench_lm_head(tq, L, device, stream, rank, world, cbs, args):
         return float(t.item()), host_us
 
     exchange, setup_error = None, None
+    lm_packets_off = 2 * 32 * vocab * 2        # packet area behind the two logits buffers: [2][world][8 * rows / 4] x 16 bytes
     if world > 1:
         try:
-            exchange = Exchange(2 * 32 * vocab * 2)
+            exchange = Exchange(lm_packets_off + 2 * world * 8 * (rows // 4 + 1) * 16)
         except Exception as exc:
             setup_error = str(exc)
         ok_t = torch.tensor([0.0 if setup_error else 1.0], device=device)
@@ -1063,6 +1064,25 @@ def bench_lm_head(tq, L, device, stream, rank, world, cbs, args):
                 exchange.check_status()
                 lin.check_status()
                 fused_logits = exchange.buf.tensor((2, batch, vocab), torch.float16).clone()
+            us_p = None
+            if batch <= 8 and rows % 4 == 0 and (vocab // world) == rows:
+                pstep = [0]
+
+                def call_packets():
+                    half = pstep[0] & 1
+                    pstep[0] += 1
+                    base = exchange.local + half * batch * vocab * 2
+                    # this rank's rows go straight to their place in the logits; every CTA sends its own rows to the other
+                    # ranks as {data, epoch} packets while the rest of the grid is still computing; a second kernel waits
+                    # for the other ranks' packets and writes their rows beside them
+                    exchange.forward_allgather_packets(lin, x, None, lm_packets_off, wait=False, stream=stream, y_ptr=base + s * 2,
+                                                       y_row_stride=vocab)
+                    exchange.wait_packets(lm_packets_off, rows, batch, base, vocab, stream=stream)
+
+                us_p, host_p = timed(call_packets, graph=True)
+                exchange.check_status()
+                lin.check_status()
+                packet_logits = exchange.buf.tensor((2, batch, vocab), torch.float16).clone()
             us_x, host_x = timed(call_exchange, graph=True)
             exchange.check_status()
             with torch.cuda.stream(stream):
@@ -1081,6 +1101,15 @@ def bench_lm_head(tq, L, device, stream, rank, world, cbs, args):
                                        "path": "tq_linear_forward_allgather: one kernel waits for the previous gather, computes the "
                                                "shard, copies it to the peers and raises the flags (CUDA graph)",
                                        "identical_to_all_gather_on_every_rank": bool(sf.item() == 1.0)}
+            if us_p is not None:
+                same_p = bool(torch.equal(full, packet_logits[0])) and bool(torch.equal(full, packet_logits[1]))
+                spk = torch.tensor([1.0 if same_p else 0.0], device=device)
+                dist.all_reduce(spk, op=dist.ReduceOp.MIN)
+                res[key + "_packets"] = {"us": us_p, "tok_per_s": batch / (us_p * 1e-6), "gb_per_s_aggregate": algo / (us_p * 1e-6) / 1e9,
+                                         "host_us_per_call_eager": host_p,
+                                         "path": "tq_linear_forward_allgather_packets (every CTA sends its own rows as {data, epoch} packets) "
+                                                 "+ tq_exchange_wait_packets (CUDA graph)",
+                                         "identical_to_all_gather_on_every_rank": bool(spk.item() == 1.0)}
             res[key + "_exchange"] = {"us": us_x, "tok_per_s": batch / (us_x * 1e-6), "gb_per_s_aggregate": algo / (us_x * 1e-6) / 1e9,
                                       "host_us_per_call_eager": host_x,
                                       "path": "forward into the shared logits + tq_exchange_broadcast + tq_exchange_wait (CUDA graph)",

@@ -324,6 +324,13 @@ int tq_linear_forward_allgather(tq_linear_t lin, tq_exchange_t ex, const void* x
 int tq_linear_forward_allgather_packets(tq_linear_t lin, tq_exchange_t ex, const void* x_fp16_device, int batch,
                                         void* y_fp16_device, long y_row_stride, void* const* packet_buffers,
                                         int wait_previous, void* stream);
+/** After a tq_linear_forward_allgather_packets call on this rank (same stream): waits - bounded, 1 s - for the
+ *  packets the other ranks wrote in that exchange and writes their rows into the gathered result
+ *  out[n * out_row_stride + source * rows_per_rank + row] (this rank's own block is not touched: let the forward
+ *  write it there).  local_packets = this rank's packet buffer.  A peer that never sends shows up in
+ *  tq_exchange_status. */
+int tq_exchange_wait_packets(tq_exchange_t ex, const void* local_packets, long rows_per_rank, int batch, void* out_fp16,
+                             long out_row_stride, void* stream);
 int tq_exchange_unpack_packets(const void* packets, long n_packets, void* out_fp16, void* stream);
 /* Element-wise glue of a decoder layer, device fp16 in and out, fp32 arithmetic.  The reference
  * leaves these to MLX in the host application (no file of its own computes them); they are here so

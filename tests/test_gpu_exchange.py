@@ -154,6 +154,13 @@ def test_forward_fused_with_packet_all_gather(tq, oracle):
                 assert L.tq_exchange_unpack_packets(C.c_void_p(region.data_ptr()), n_pk, C.c_void_p(got.data_ptr()), None) == 0
                 torch.cuda.synchronize()
                 assert torch.equal(got, want[src]), (batch, step, r)
+                # the waiting variant: the other rank's rows land beside this rank's own in the gathered result
+                gathered = torch.zeros((batch, world * rows), dtype=torch.float16, device="cuda")
+                gathered[:, r * rows:(r + 1) * rows] = ys[r]
+                assert L.tq_exchange_wait_packets(ex[r], C.c_void_p(bufs[r].data_ptr()), rows, batch, C.c_void_p(gathered.data_ptr()),
+                                                  world * rows, None) == 0
+                torch.cuda.synchronize()
+                assert torch.equal(gathered, torch.cat(want, dim=1)), (batch, step, r)
         for r in range(world):
             assert L.tq_exchange_status(ex[r]) == 0
             lins[r].check_status()

@@ -134,6 +134,17 @@ unsigned int* tq_exchange_words_world(tq_exchange_t ex, int* rank, int* world) {
     return ex->words.as<unsigned int>();
 }
 
+int tq_exchange_wait_packets(tq_exchange_t ex, const void* local_packets, long rows_per_rank, int batch, void* out_fp16, long out_row_stride,
+                             void* stream) {
+    return guarded<int>(0, -1, [&]() {
+        TQ_REQUIRE(ex != nullptr && local_packets && out_fp16, "tq_exchange_wait_packets: NULL argument");
+        launch_exchange_wait_packets(static_cast<const uint4*>(local_packets), ex->words.as<unsigned int>() + 1, ex->rank, ex->world,
+                                     rows_per_rank, batch, static_cast<__half*>(out_fp16), out_row_stride, ex->d_status,
+                                     static_cast<cudaStream_t>(stream));
+        return 0;
+    });
+}
+
 int tq_exchange_unpack_packets(const void* packets, long n_packets, void* out_fp16, void* stream) {
     return guarded<int>(0, -1, [&]() {
         TQ_REQUIRE(packets && out_fp16 && n_packets >= 0, "tq_exchange_unpack_packets: bad argument");

@@ -290,18 +290,21 @@ __device__ __noinline__ void ll_wait_packets(const unsigned int* wait_epoch, con
         }
     }
 }
+// Packets c0 .. c1 - 1 (groups of four rows) of every activation row, to every other rank.
 __device__ __noinline__ void ll_send_packets(const unsigned int* epoch, const __half* y, long y_stride, int per_row, int batch, int rank,
-                                             int world, LlBases bases) {
-    // packets of this launch to every other rank: no fence, no flag - the epoch travels with the data
+                                             int world, LlBases bases, int c0, int c1) {
+    // no fence, no flag - the epoch travels with the data
     const unsigned int value = *reinterpret_cast<const volatile unsigned int*>(epoch) + 1u;
     const long packets = static_cast<long>(batch) * per_row;
     const size_t region = (static_cast<size_t>(value & 1u) * world + rank) * packets;
-    for (long i = threadIdx.x; i < packets; i += kCtaThreads) {
-        const int n = static_cast<int>(i / per_row), c = static_cast<int>(i - static_cast<long>(n) * per_row);
+    const int span = c1 - c0;
+    for (long i = threadIdx.x; i < static_cast<long>(batch) * span; i += kCtaThreads) {
+        const int n = static_cast<int>(i / span), c = c0 + static_cast<int>(i - static_cast<long>(n) * span);
         const uint2 v = __ldcg(reinterpret_cast<const uint2*>(y + static_cast<size_t>(n) * y_stride + static_cast<size_t>(c) * 4));
+        const size_t at = region + static_cast<size_t>(n) * per_row + c;
         for (int d = 0; d < world; ++d)
             if (d != rank)
-                asm volatile("st.volatile.global.v4.u32 [%0], {%1, %2, %3, %2};" ::"l"(bases.p[d] + region + i), "r"(v.x), "r"(value), "r"(v.y)
+                asm volatile("st.volatile.global.v4.u32 [%0], {%1, %2, %3, %2};" ::"l"(bases.p[d] + at), "r"(v.x), "r"(value), "r"(v.y)
                              : "memory");
     }
 }
@@ -742,6 +745,19 @@ __device__ __forceinline__ void gemv_body(const GemvArgs& p, const ScatterArgs& 
     if constexpr (SCATTER) {
     if (sargs.n_signal > 0 || sargs.ll) {
         __shared__ unsigned int s_last;
+        // Packets, one slot: every row of this CTA's units was stored by this CTA, so it sends its own rows as soon
+        // as it is done - the sends of the grid run side by side and nothing waits for the slowest CTA.  (With several
+        // slots the CTA that completes a row tile is not known in advance: the completing CTA of the grid sends all.)
+        const bool own_rows = sargs.ll && p.n_slots == 1;
+        if (own_rows) {
+            __syncthreads();   // this CTA's stores are ordered before the loads below (read back through L2)
+            LlBases bases;
+#pragma unroll
+            for (int d = 0; d < 8; ++d) bases.p[d] = sargs.ll_base[d];
+            const int per_row = p.out / 4;
+            const int c0 = u_begin * p.tpu * 4, c1 = min(per_row, u_end * p.tpu * 4);
+            ll_send_packets(sargs.epoch, p.y, sargs.y_stride, per_row, p.batch, sargs.ll_rank, sargs.ll_world, bases, c0, c1);
+        }
         // results that went to other GPUs need a system-scope fence; with the bulk copy every CTA's
         // results are local and only the copying CTA pays for one
         if (sargs.bulk) __threadfence();
@@ -754,10 +770,12 @@ __device__ __forceinline__ void gemv_body(const GemvArgs& p, const ScatterArgs& 
         __syncthreads();
         if (s_last && sargs.ll) {
             __threadfence();
-            LlBases bases;
+            if (!own_rows) {
+                LlBases bases;
 #pragma unroll
-            for (int d = 0; d < 8; ++d) bases.p[d] = sargs.ll_base[d];
-            ll_send_packets(sargs.epoch, p.y, sargs.y_stride, p.out / 4, p.batch, sargs.ll_rank, sargs.ll_world, bases);
+                for (int d = 0; d < 8; ++d) bases.p[d] = sargs.ll_base[d];
+                ll_send_packets(sargs.epoch, p.y, sargs.y_stride, p.out / 4, p.batch, sargs.ll_rank, sargs.ll_world, bases, 0, p.out / 4);
+            }
             __syncthreads();
             if (tid == 0) {
                 *sargs.done_counter = 0u;  // ready for the next launch (stream order)

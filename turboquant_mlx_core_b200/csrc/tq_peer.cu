@@ -131,6 +131,37 @@ __global__ void __launch_bounds__(256) exchange_unpack_packets_kernel(const uint
     }
 }
 
+// Waits (bounded) for the packets every other rank wrote in the exchange that has just completed on this rank
+// (*epoch is its number) and writes their rows into the gathered result: row block `src` of every activation row.
+__global__ void __launch_bounds__(256) exchange_wait_packets_kernel(const uint4* __restrict__ base, const unsigned int* __restrict__ epoch,
+                                                                    int rank, int world, long per_row, int batch, long rows,
+                                                                    __half* __restrict__ out, long out_stride, unsigned int* status) {
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;");
+    const unsigned int want = *reinterpret_cast<const volatile unsigned int*>(epoch);
+    const long packets = static_cast<long>(batch) * per_row;
+    const uint4* const half = base + static_cast<size_t>(want & 1u) * world * packets;
+    const unsigned long long t0 = p_timer_ns();
+    const long total = packets * (world - 1);
+    for (long j = static_cast<long>(blockIdx.x) * blockDim.x + threadIdx.x; j < total; j += static_cast<long>(gridDim.x) * blockDim.x) {
+        int src = static_cast<int>(j / packets);
+        const long i = j - static_cast<long>(src) * packets;
+        if (src >= rank) ++src;
+        const uint4* at = half + static_cast<size_t>(src) * packets + i;
+        uint4 pk;
+        for (unsigned int spin = 0;; ++spin) {
+            asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(pk.x), "=r"(pk.y), "=r"(pk.z), "=r"(pk.w) : "l"(at) : "memory");
+            if (static_cast<int>(pk.y - want) >= 0 && static_cast<int>(pk.w - want) >= 0) break;
+            if ((spin & 255u) == 255u && p_timer_ns() - t0 > kPeerWaitNs) {
+                raise_status(status, 10u);
+                return;
+            }
+        }
+        const long n = i / per_row, c = i - n * per_row;
+        *reinterpret_cast<uint2*>(out + n * out_stride + static_cast<long>(src) * rows + 4 * c) = make_uint2(pk.x, pk.z);
+    }
+}
+
 // Softmax parts over disjoint token ranges of the same rows -> attention over the union:
 //   out = sum_p w_p * out_p / sum_p w_p,  w_p = exp(lse_p - max_p lse_p)   (parts in order).
 // outs: [parts][rows][dim] fp16 (part_stride_o elements apart), lses: [parts][rows] fp32.
@@ -229,6 +260,19 @@ void launch_exchange_unpack_packets(const uint4* packets, long n_packets, __half
     const int blocks = static_cast<int>(n_packets + 255 < 296L * 256 ? (n_packets + 255) / 256 : 296);
     exchange_unpack_packets_kernel<<<blocks, 256, 0, stream>>>(packets, n_packets, reinterpret_cast<uint2*>(out));
     TQ_CUDA(cudaGetLastError());
+}
+
+void launch_exchange_wait_packets(const uint4* base, const unsigned int* epoch, int rank, int world, long rows, int batch, __half* out,
+                                  long out_stride, unsigned int* status, cudaStream_t stream) {
+    TQ_REQUIRE(base && epoch && out && world >= 1 && rank >= 0 && rank < world && rows % 4 == 0 && out_stride % 4 == 0 &&
+                   reinterpret_cast<uintptr_t>(out) % 8 == 0,
+               "packet wait: rows and strides in groups of four, 8-byte aligned destination");
+    if (world == 1 || rows == 0 || batch == 0) return;
+    const long total = static_cast<long>(batch) * (rows / 4) * (world - 1);
+    const int blocks = static_cast<int>(total + 255 < 296L * 256 ? (total + 255) / 256 : 296);
+    cudaLaunchAttribute attr[1];
+    cudaLaunchConfig_t cfg = pdl_config(dim3(static_cast<unsigned>(blocks)), dim3(256), stream, attr);
+    TQ_CUDA(cudaLaunchKernelEx(&cfg, exchange_wait_packets_kernel, base, epoch, rank, world, rows / 4, batch, rows, out, out_stride, status));
 }
 
 void launch_exchange_merge_attention(const __half* outs, const float* lses, int parts, long rows, int dim, long part_stride_o,

@@ -260,7 +260,16 @@ class Exchange:
         others = iter(self.buf.ptrs[1:])
         return [self.buf.local if r == self.rank else next(others) for r in range(self.world)]
 
-    def forward_allgather_packets(self, lin, x, y, packets_offset: int = 0, wait: bool = True, stream=None):
+    def wait_packets(self, packets_offset: int, rows_per_rank: int, batch: int, out_ptr: int, out_row_stride: int, stream=None):
+        """tq_exchange_wait_packets: after forward_allgather_packets on the same stream, wait for the other ranks' packets and
+        write their rows into the gathered result at raw device address out_ptr ([batch][out_row_stride] fp16)."""
+        import ctypes as C
+        from . import _lib
+        _lib.check(self._L.tq_exchange_wait_packets(self._h, C.c_void_p(self.buf.local + packets_offset), int(rows_per_rank), int(batch),
+                                                     C.c_void_p(int(out_ptr)), int(out_row_stride), _stream_ptr(stream)),
+                   "tq_exchange_wait_packets")
+
+    def forward_allgather_packets(self, lin, x, y, packets_offset: int = 0, wait: bool = True, stream=None, y_ptr=None, y_row_stride=None):
         """tq_linear_forward_allgather_packets: y (device fp16 [batch, out]) gets this rank's rows; the other ranks
         get them as flag-in-data packets in their buffers at byte `packets_offset`
         ([epoch parity][source rank][batch * out / 4 packets of 16 bytes]); with wait=True every CTA first polls
@@ -271,7 +280,9 @@ class Exchange:
         from .api import _ptr
         batch = int(np.prod(x.shape[:-1])) if len(x.shape) > 1 else 1
         bufs = (C.c_void_p * self.world)(*[p + packets_offset for p in self.rank_ptrs()])
-        _lib.check(self._L.tq_linear_forward_allgather_packets(lin.handle, self._h, _ptr(x), batch, _ptr(y), int(y.shape[-1]), bufs,
+        yp = C.c_void_p(int(y_ptr)) if y_ptr is not None else _ptr(y)
+        ys = int(y_row_stride) if y_row_stride is not None else int(y.shape[-1])
+        _lib.check(self._L.tq_linear_forward_allgather_packets(lin.handle, self._h, _ptr(x), batch, yp, ys, bufs,
                                                                 1 if wait else 0, _stream_ptr(stream)),
                    "tq_linear_forward_allgather_packets")
 
