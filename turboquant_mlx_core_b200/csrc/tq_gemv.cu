@@ -262,12 +262,9 @@ __device__ __forceinline__ void mma_tf32(float (&c)[4], uint32_t a0, uint32_t a1
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
-// ---- flag-in-data exchange (see ScatterArgs): out of line, so that the decode loop keeps its registers ----
-struct LlBases {
-    uint4* p[8];
-};
-__device__ __noinline__ void ll_wait_packets(const unsigned int* wait_epoch, const uint4* mine, int rank, int world, long packets,
-                                             unsigned int* status) {
+// ---- flag-in-data exchange (see ScatterArgs) ----
+__device__ __forceinline__ void ll_wait_packets(const unsigned int* wait_epoch, const uint4* mine, int rank, int world, long packets,
+                                                unsigned int* status) {
     const unsigned int want = *reinterpret_cast<const volatile unsigned int*>(wait_epoch) + 1u;
     const uint4* const half = mine + static_cast<size_t>(want & 1u) * world * packets;
     const unsigned long long t0 = global_timer_ns();
@@ -290,28 +287,28 @@ __device__ __noinline__ void ll_wait_packets(const unsigned int* wait_epoch, con
         }
     }
 }
-// Packets c0 .. c1 - 1 (groups of four rows) of every activation row, to every other rank.
-__device__ __noinline__ void ll_send_packets(const unsigned int* epoch, const __half* y, long y_stride, int per_row, int batch, int rank,
-                                             int world, LlBases bases, int c0, int c1) {
-    // no fence, no flag - the epoch travels with the data
-    const unsigned int value = *reinterpret_cast<const volatile unsigned int*>(epoch) + 1u;
+// Packets c0 .. c1 - 1 (groups of four rows) of every activation row, to every other rank: no fence, no flag -
+// the epoch travels with the data.
+__device__ __forceinline__ void ll_send_packets(const ScatterArgs& sc, const __half* y, int per_row, int batch, int c0, int c1) {
+    const unsigned int value = *reinterpret_cast<const volatile unsigned int*>(sc.epoch) + 1u;
     const long packets = static_cast<long>(batch) * per_row;
-    const size_t region = (static_cast<size_t>(value & 1u) * world + rank) * packets;
+    const size_t region = (static_cast<size_t>(value & 1u) * sc.ll_world + sc.ll_rank) * packets;
     const int span = c1 - c0;
     for (long i = threadIdx.x; i < static_cast<long>(batch) * span; i += kCtaThreads) {
         const int n = static_cast<int>(i / span), c = c0 + static_cast<int>(i - static_cast<long>(n) * span);
-        const uint2 v = __ldcg(reinterpret_cast<const uint2*>(y + static_cast<size_t>(n) * y_stride + static_cast<size_t>(c) * 4));
+        const uint2 v = __ldcg(reinterpret_cast<const uint2*>(y + static_cast<size_t>(n) * sc.y_stride + static_cast<size_t>(c) * 4));
         const size_t at = region + static_cast<size_t>(n) * per_row + c;
-        for (int d = 0; d < world; ++d)
-            if (d != rank)
-                asm volatile("st.volatile.global.v4.u32 [%0], {%1, %2, %3, %2};" ::"l"(bases.p[d] + at), "r"(v.x), "r"(value), "r"(v.y)
+#pragma unroll
+        for (int d = 0; d < 8; ++d)
+            if (d < sc.ll_world && d != sc.ll_rank)
+                asm volatile("st.volatile.global.v4.u32 [%0], {%1, %2, %3, %2};" ::"l"(sc.ll_base[d] + at), "r"(v.x), "r"(value), "r"(v.y)
                              : "memory");
     }
 }
 
 // BP = activation rows padded to 1, 2, 4 or 8 (compile time, so that the partial-sum ring
 // geometry and the reduction need no runtime arithmetic).
-template <int BP, bool SCATTER>
+template <int BP, bool SCATTER, bool LL = false>
 __device__ __forceinline__ void gemv_body(const GemvArgs& p, const ScatterArgs& sargs) {
     // A warp's partial tile is [16 rows][BP] floats plus 4 floats of padding: the 16 tiles a
     // reduction reads side by side then start 4 banks apart instead of in the same bank.
@@ -433,10 +430,12 @@ __device__ __forceinline__ void gemv_body(const GemvArgs& p, const ScatterArgs& 
     // Everything below reads or writes data the preceding kernels produce or still use.
     grid_dependency_sync();
     if constexpr (SCATTER) {
-        if (sargs.n_wait > 0 && sargs.ll) {
+        if (LL && sargs.n_wait > 0) {
             // the activation comes out of a flag-in-data exchange: every packet of every other rank must carry the epoch
-            ll_wait_packets(sargs.wait_epoch, sargs.ll_base[sargs.ll_rank], sargs.ll_rank, sargs.ll_world,
-                            static_cast<long>(p.batch) * (p.out / 4), p.status);
+            if constexpr (LL) {
+                ll_wait_packets(sargs.wait_epoch, sargs.ll_base[sargs.ll_rank], sargs.ll_rank, sargs.ll_world,
+                                static_cast<long>(p.batch) * (p.out / 4), p.status);
+            }
             __syncthreads();
         } else if (sargs.n_wait > 0) {
             // the activation comes out of an exchange: wait until every rank's part has arrived
@@ -743,20 +742,19 @@ __device__ __forceinline__ void gemv_body(const GemvArgs& p, const ScatterArgs& 
     // the CTA that completes the grid publishes the flag everywhere.  Whoever then reads the flag
     // with acquire semantics sees all of this launch's results.
     if constexpr (SCATTER) {
-    if (sargs.n_signal > 0 || sargs.ll) {
+    if (sargs.n_signal > 0 || LL) {
         __shared__ unsigned int s_last;
         // Packets, one slot: every row of this CTA's units was stored by this CTA, so it sends its own rows as soon
         // as it is done - the sends of the grid run side by side and nothing waits for the slowest CTA.  (With several
         // slots the CTA that completes a row tile is not known in advance: the completing CTA of the grid sends all.)
-        const bool own_rows = sargs.ll && p.n_slots == 1;
-        if (own_rows) {
+        const bool own_rows = LL && p.n_slots == 1;
+        if constexpr (LL) if (own_rows) {
             __syncthreads();   // this CTA's stores are ordered before the loads below (read back through L2)
-            LlBases bases;
-#pragma unroll
-            for (int d = 0; d < 8; ++d) bases.p[d] = sargs.ll_base[d];
             const int per_row = p.out / 4;
-            const int c0 = u_begin * p.tpu * 4, c1 = min(per_row, u_end * p.tpu * 4);
-            ll_send_packets(sargs.epoch, p.y, sargs.y_stride, per_row, p.batch, sargs.ll_rank, sargs.ll_world, bases, c0, c1);
+            const int n_units_all = p.n_row_units * p.n_slots;
+            const int ub = static_cast<int>(static_cast<long>(n_units_all) * blockIdx.x / gridDim.x);
+            const int ue = static_cast<int>(static_cast<long>(n_units_all) * (blockIdx.x + 1) / gridDim.x);
+            ll_send_packets(sargs, p.y, per_row, p.batch, ub * p.tpu * 4, min(per_row, ue * p.tpu * 4));
         }
         // results that went to other GPUs need a system-scope fence; with the bulk copy every CTA's
         // results are local and only the copying CTA pays for one
@@ -768,14 +766,9 @@ __device__ __forceinline__ void gemv_body(const GemvArgs& p, const ScatterArgs& 
             s_last = (prev == gridDim.x - 1) ? 1u : 0u;
         }
         __syncthreads();
-        if (s_last && sargs.ll) {
+        if (LL && s_last) {
             __threadfence();
-            if (!own_rows) {
-                LlBases bases;
-#pragma unroll
-                for (int d = 0; d < 8; ++d) bases.p[d] = sargs.ll_base[d];
-                ll_send_packets(sargs.epoch, p.y, sargs.y_stride, p.out / 4, p.batch, sargs.ll_rank, sargs.ll_world, bases, 0, p.out / 4);
-            }
+            if constexpr (LL) if (!own_rows) ll_send_packets(sargs, p.y, p.out / 4, p.batch, 0, p.out / 4);
             __syncthreads();
             if (tid == 0) {
                 *sargs.done_counter = 0u;  // ready for the next launch (stream order)
@@ -830,6 +823,10 @@ __device__ __forceinline__ void gemv_body(const GemvArgs& p, const ScatterArgs& 
 template <int BP>
 __global__ void __launch_bounds__(kCtaThreads, 1) tq8_gemv_kernel(const GemvArgs p) {
     gemv_body<BP, false>(p, ScatterArgs{});
+}
+template <int BP>
+__global__ void __launch_bounds__(kCtaThreads, 1) tq8_gemv_packets_kernel(const GemvArgs p, const ScatterArgs sc) {
+    gemv_body<BP, true, true>(p, sc);
 }
 template <int BP>
 __global__ void __launch_bounds__(kCtaThreads, 1) tq8_gemv_scatter_kernel(const GemvArgs p, const ScatterArgs sc) {
@@ -989,7 +986,8 @@ void launch_tq8_gemv_scatter(const uint8_t* codes, const float* norms, const flo
     if (dev >= 64 || !configured[dev]) {
 #define TQ_GEMV_ATTR(BPV)                                                                                                          \
     TQ_CUDA(cudaFuncSetAttribute(tq8_gemv_kernel<BPV>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kGemvSmem))); \
-    TQ_CUDA(cudaFuncSetAttribute(tq8_gemv_scatter_kernel<BPV>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kGemvSmem)));
+    TQ_CUDA(cudaFuncSetAttribute(tq8_gemv_scatter_kernel<BPV>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kGemvSmem))); \
+    TQ_CUDA(cudaFuncSetAttribute(tq8_gemv_packets_kernel<BPV>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kGemvSmem)));
         TQ_GEMV_ATTR(1)
         TQ_GEMV_ATTR(2)
         TQ_GEMV_ATTR(4)
@@ -1036,7 +1034,8 @@ void launch_tq8_gemv_scatter(const uint8_t* codes, const float* norms, const flo
         // one destination with the layer's own row stride and no signal: the plain variant
         const bool scatter = sa.n_peer > 0 || sa.n_signal > 0 || sa.ll != 0 || sa.y_stride != a.out;
 #define TQ_GEMV_LAUNCH(BPV)                                                   \
-    if (scatter) TQ_CUDA(cudaLaunchKernelEx(&cfg, tq8_gemv_scatter_kernel<BPV>, a, sa)); \
+    if (sa.ll) TQ_CUDA(cudaLaunchKernelEx(&cfg, tq8_gemv_packets_kernel<BPV>, a, sa)); \
+    else if (scatter) TQ_CUDA(cudaLaunchKernelEx(&cfg, tq8_gemv_scatter_kernel<BPV>, a, sa)); \
     else TQ_CUDA(cudaLaunchKernelEx(&cfg, tq8_gemv_kernel<BPV>, a));
         switch (bp) {
             case 1: TQ_GEMV_LAUNCH(1) break;
