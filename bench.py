@@ -1182,7 +1182,9 @@ def bench_c4_decode_step(tq, L, device, stream, rank, world, cbs, args):
     if world > 1:
         err = None
         try:
-            exchange = Exchange(2 * world * 32 * hidden * 2)
+            # two all-reduce buffers of [world][32 rows][hidden] fp16, then the packet area for batches up to 8:
+            # [2 epoch parities][world][8 * hidden / 4 packets of 16 bytes]
+            exchange = Exchange(2 * world * 32 * hidden * 2 + 2 * world * 8 * (hidden // 4) * 16)
         except Exception as exc:
             err = str(exc)
         ok_t = torch.tensor([0.0 if err else 1.0], device=device)
@@ -1218,6 +1220,19 @@ def bench_c4_decode_step(tq, L, device, stream, rank, world, cbs, args):
         count = batch * hidden
         toggle = [0]
 
+        c4_packets_off = 2 * world * 32 * hidden * 2
+        use_packets = exchange is not None and batch <= 8 and os.environ.get("TQ_BENCH_ALLREDUCE", "packets") == "packets"
+        if use_packets:
+            pk_bufs = (C.c_void_p * world)(*[p + c4_packets_off for p in exchange.rank_ptrs()])
+
+        def all_reduce_add_packets(h, xin_ptr, residual, out):
+            """The column-sharded linear h writes its partial locally and sends it as packets from inside its kernel; one more
+            kernel waits for the other ranks' packets and adds everything in rank order."""
+            chk(L.tq_linear_forward_allgather_packets(h, exchange._h, C.c_void_p(xin_ptr), batch, C.c_void_p(part.data_ptr()), hidden,
+                                                      pk_bufs, 0, sp))
+            chk(L.tq_exchange_sum_packets(exchange._h, C.c_void_p(exchange.local + c4_packets_off), C.c_void_p(part.data_ptr()), count,
+                                          C.c_void_p(residual.data_ptr()), C.c_void_p(out.data_ptr()), sp))
+
         def all_reduce_add(partial_of, residual, out):
             """partial_of(ptr) writes this rank's partial [batch, hidden] at ptr; out = residual + sum over ranks."""
             if exchange is None:
@@ -1242,11 +1257,17 @@ def bench_c4_decode_step(tq, L, device, stream, rank, world, cbs, args):
             chk(L.tq_rope_f16(C.c_void_p(k.data_ptr()), C.c_void_p(pos.data_ptr()), batch, kvh, dim, 1e6, sp))
             chk(L.tq_kv_append_batch(arr, batch, li, C.c_void_p(k.data_ptr()), C.c_void_p(v.data_ptr()), tq.TQ_F16, sp))
             chk(L.tq_kv_attention(arr, batch, li, C.c_void_p(q.data_ptr()), tq.TQ_F16, qh, C.c_void_p(attn.data_ptr()), 0, ctx, 1, sp))
-            all_reduce_add(lambda ptr: fwd(w["o"], attn.data_ptr(), batch, ptr), x, x1)
+            if use_packets:
+                all_reduce_add_packets(w["o"], attn.data_ptr(), x, x1)
+            else:
+                all_reduce_add(lambda ptr: fwd(w["o"], attn.data_ptr(), batch, ptr), x, x1)
             chk(L.tq_rmsnorm_f16(C.c_void_p(x1.data_ptr()), C.c_void_p(w["n2"].data_ptr()), C.c_void_p(h1.data_ptr()), batch, hidden, 1e-6, sp))
             fwd(w["gu"], h1.data_ptr(), batch, gu.data_ptr())
             chk(L.tq_swiglu_f16(C.c_void_p(gu.data_ptr()), C.c_void_p(act.data_ptr()), batch, il, sp))
-            all_reduce_add(lambda ptr: fwd(w["down"], act.data_ptr(), batch, ptr), x1, x)
+            if use_packets:
+                all_reduce_add_packets(w["down"], act.data_ptr(), x1, x)
+            else:
+                all_reduce_add(lambda ptr: fwd(w["down"], act.data_ptr(), batch, ptr), x1, x)
 
         def one_pass():
             for li in range(n_layers):
@@ -1302,6 +1323,9 @@ def bench_c4_decode_step(tq, L, device, stream, rank, world, cbs, args):
                             "bytes_per_layer_per_gpu": weight_bytes + kv_bytes, "distinct_layers_cycled": n_layers,
                             "kernels_per_layer": "rmsnorm, q, k, v, rope x2, kv append x2, attention, o_proj, [copy to peers, wait,] "
                                                  "sum + residual, rmsnorm, gate-up, swiglu, down, [copy to peers, wait,] sum + residual",
+                            "all_reduce": ("none (one rank)" if exchange is None else
+                                           "partials sent as packets from inside o_proj / down_proj, one kernel waits and adds" if use_packets
+                                           else "tq_exchange_broadcast + tq_exchange_wait + tq_exchange_sum_f16"),
                             "residual_stream_finite": finite, "identical_on_every_rank": same}
         for c in caches:
             c.close()

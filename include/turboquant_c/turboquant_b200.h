@@ -328,9 +328,17 @@ int tq_linear_forward_allgather_packets(tq_linear_t lin, tq_exchange_t ex, const
  *  packets the other ranks wrote in that exchange and writes their rows into the gathered result
  *  out[n * out_row_stride + source * rows_per_rank + row] (this rank's own block is not touched: let the forward
  *  write it there).  local_packets = this rank's packet buffer.  A peer that never sends shows up in
- *  tq_exchange_status. */
+ *  tq_exchange_status.  This is the wait of that exchange: use it (or tq_exchange_sum_packets) after calls made with
+ *  wait_previous = 0, and not for an exchange that the next call's wait_previous = 1 already waits for. */
 int tq_exchange_wait_packets(tq_exchange_t ex, const void* local_packets, long rows_per_rank, int batch, void* out_fp16,
                              long out_row_stride, void* stream);
+/** The all-reduce of a column-sharded layer over packets: after tq_linear_forward_allgather_packets wrote this
+ *  rank's partial output to local_partial_fp16 ([batch][rows] contiguous, count = batch * rows elements) and sent it
+ *  to the other ranks, this waits - bounded - for their packets and writes
+ *  out = fp16(residual + sum over ranks in rank order, fp32): the arithmetic of tq_exchange_sum_f16, so every rank
+ *  gets the same bits.  residual_fp16 may be NULL.  Counts as this exchange's wait. */
+int tq_exchange_sum_packets(tq_exchange_t ex, const void* local_packets, const void* local_partial_fp16, long count,
+                            const void* residual_fp16, void* out_fp16, void* stream);
 int tq_exchange_unpack_packets(const void* packets, long n_packets, void* out_fp16, void* stream);
 /* Element-wise glue of a decoder layer, device fp16 in and out, fp32 arithmetic.  The reference
  * leaves these to MLX in the host application (no file of its own computes them); they are here so

@@ -154,13 +154,27 @@ def test_forward_fused_with_packet_all_gather(tq, oracle):
                 assert L.tq_exchange_unpack_packets(C.c_void_p(region.data_ptr()), n_pk, C.c_void_p(got.data_ptr()), None) == 0
                 torch.cuda.synchronize()
                 assert torch.equal(got, want[src]), (batch, step, r)
-                # the waiting variant: the other rank's rows land beside this rank's own in the gathered result
-                gathered = torch.zeros((batch, world * rows), dtype=torch.float16, device="cuda")
-                gathered[:, r * rows:(r + 1) * rows] = ys[r]
-                assert L.tq_exchange_wait_packets(ex[r], C.c_void_p(bufs[r].data_ptr()), rows, batch, C.c_void_p(gathered.data_ptr()),
-                                                  world * rows, None) == 0
-                torch.cuda.synchronize()
-                assert torch.equal(gathered, torch.cat(want, dim=1)), (batch, step, r)
+        # the last exchange has not been waited for yet (each step's kernels waited for the one before): the waiting
+        # kernel puts the other rank's rows beside this rank's own in the gathered result
+        for r in range(world):
+            gathered = torch.zeros((batch, world * rows), dtype=torch.float16, device="cuda")
+            gathered[:, r * rows:(r + 1) * rows] = ys[r]
+            assert L.tq_exchange_wait_packets(ex[r], C.c_void_p(bufs[r].data_ptr()), rows, batch, C.c_void_p(gathered.data_ptr()),
+                                              world * rows, None) == 0
+            torch.cuda.synchronize()
+            assert torch.equal(gathered, torch.cat(want, dim=1)), (batch, r)
+        # the same packets as the partial sums of an all-reduce: residual + the ranks' rows in rank order, fp32
+        # (each rank's second waiting call of this exchange: the packets are still there, the epoch is the same)
+        resid = torch.from_numpy(rng.standard_normal((batch, rows)).astype(np.float16)).cuda()
+        for r in range(world):
+            out = torch.empty((batch, rows), dtype=torch.float16, device="cuda")
+            assert L.tq_exchange_sum_packets(ex[r], C.c_void_p(bufs[r].data_ptr()), C.c_void_p(ys[r].data_ptr()), batch * rows,
+                                             C.c_void_p(resid.data_ptr()), C.c_void_p(out.data_ptr()), None) == 0
+            torch.cuda.synchronize()
+            acc = resid.float()
+            for src in range(world):
+                acc = acc + want[src].float()
+            assert torch.equal(out, acc.half()), (batch, r)
         for r in range(world):
             assert L.tq_exchange_status(ex[r]) == 0
             lins[r].check_status()

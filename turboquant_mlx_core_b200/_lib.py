@@ -143,6 +143,7 @@ def load() -> C.CDLL:
     sig("tq_linear_forward_allgather_packets", i, [vp, vp, vp, i, vp, C.c_long, C.POINTER(C.c_void_p), i, vp])
     sig("tq_exchange_unpack_packets", i, [vp, C.c_long, vp, vp])
     sig("tq_exchange_wait_packets", i, [vp, vp, C.c_long, i, vp, C.c_long, vp])
+    sig("tq_exchange_sum_packets", i, [vp, vp, vp, C.c_long, vp, vp, vp])
     sig("tq_decode_buffer_create", vp, [i, i, i])
     sig("tq_decode_buffer_free", None, [vp])
     sig("tq_decode_buffer_window_size", i, [vp])

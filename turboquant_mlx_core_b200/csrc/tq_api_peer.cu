@@ -138,9 +138,21 @@ int tq_exchange_wait_packets(tq_exchange_t ex, const void* local_packets, long r
                              void* stream) {
     return guarded<int>(0, -1, [&]() {
         TQ_REQUIRE(ex != nullptr && local_packets && out_fp16, "tq_exchange_wait_packets: NULL argument");
-        launch_exchange_wait_packets(static_cast<const uint4*>(local_packets), ex->words.as<unsigned int>() + 1, ex->rank, ex->world,
-                                     rows_per_rank, batch, static_cast<__half*>(out_fp16), out_row_stride, ex->d_status,
+        launch_exchange_wait_packets(static_cast<const uint4*>(local_packets), ex->words.as<unsigned int>() + 1,
+                                     ex->words.as<unsigned int>() + 2, ex->rank, ex->world, rows_per_rank, batch, static_cast<__half*>(out_fp16), out_row_stride, ex->d_status,
                                      static_cast<cudaStream_t>(stream));
+        return 0;
+    });
+}
+
+int tq_exchange_sum_packets(tq_exchange_t ex, const void* local_packets, const void* local_partial_fp16, long count,
+                            const void* residual_fp16, void* out_fp16, void* stream) {
+    return guarded<int>(0, -1, [&]() {
+        TQ_REQUIRE(ex != nullptr && local_packets && local_partial_fp16 && out_fp16, "tq_exchange_sum_packets: NULL argument");
+        launch_exchange_sum_packets(static_cast<const uint4*>(local_packets), ex->words.as<unsigned int>() + 1,
+                                    ex->words.as<unsigned int>() + 2, ex->rank, ex->world, count,
+                                    static_cast<const __half*>(local_partial_fp16), static_cast<const __half*>(residual_fp16),
+                                    static_cast<__half*>(out_fp16), ex->d_status, static_cast<cudaStream_t>(stream));
         return 0;
     });
 }

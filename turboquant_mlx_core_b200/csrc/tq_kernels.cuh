@@ -158,8 +158,10 @@ void launch_exchange_broadcast(const void* src, void* const* dst, int n_dst, int
 void launch_exchange_wait(const unsigned int* flags, int n, unsigned int* epoch, unsigned int* status, cudaStream_t stream);
 void launch_exchange_sum_f16(const __half* slots, int n_slots, long slot_stride, long count, const __half* residual, __half* out,
                              cudaStream_t stream);
-void launch_exchange_wait_packets(const uint4* base, const unsigned int* epoch, int rank, int world, long rows, int batch, __half* out,
-                                  long out_stride, unsigned int* status, cudaStream_t stream);
+void launch_exchange_wait_packets(const uint4* base, const unsigned int* epoch, unsigned int* wait_epoch, int rank, int world, long rows,
+                                  int batch, __half* out, long out_stride, unsigned int* status, cudaStream_t stream);
+void launch_exchange_sum_packets(const uint4* base, const unsigned int* epoch, unsigned int* wait_epoch, int rank, int world, long count,
+                                 const __half* local, const __half* residual, __half* out, unsigned int* status, cudaStream_t stream);
 void launch_exchange_unpack_packets(const uint4* packets, long n_packets, __half* out, cudaStream_t stream);
 void launch_exchange_merge_attention(const __half* outs, const float* lses, int parts, long rows, int dim, long part_stride_o,
                                      long part_stride_l, __half* out, cudaStream_t stream);

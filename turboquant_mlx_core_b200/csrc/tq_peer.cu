@@ -134,11 +134,13 @@ __global__ void __launch_bounds__(256) exchange_unpack_packets_kernel(const uint
 // Waits (bounded) for the packets every other rank wrote in the exchange that has just completed on this rank
 // (*epoch is its number) and writes their rows into the gathered result: row block `src` of every activation row.
 __global__ void __launch_bounds__(256) exchange_wait_packets_kernel(const uint4* __restrict__ base, const unsigned int* __restrict__ epoch,
-                                                                    int rank, int world, long per_row, int batch, long rows,
-                                                                    __half* __restrict__ out, long out_stride, unsigned int* status) {
+                                                                    unsigned int* __restrict__ wait_epoch, int rank, int world, long per_row,
+                                                                    int batch, long rows, __half* __restrict__ out, long out_stride,
+                                                                    unsigned int* status) {
     asm volatile("griddepcontrol.wait;" ::: "memory");
     asm volatile("griddepcontrol.launch_dependents;");
     const unsigned int want = *reinterpret_cast<const volatile unsigned int*>(epoch);
+    if (blockIdx.x == 0 && threadIdx.x == 0) atomicAdd(wait_epoch, 1u);   // one wait per exchange, like tq_exchange_wait
     const long packets = static_cast<long>(batch) * per_row;
     const uint4* const half = base + static_cast<size_t>(want & 1u) * world * packets;
     const unsigned long long t0 = p_timer_ns();
@@ -159,6 +161,51 @@ __global__ void __launch_bounds__(256) exchange_wait_packets_kernel(const uint4*
         }
         const long n = i / per_row, c = i - n * per_row;
         *reinterpret_cast<uint2*>(out + n * out_stride + static_cast<long>(src) * rows + 4 * c) = make_uint2(pk.x, pk.z);
+    }
+}
+
+// All-reduce tail for partial sums that travelled as packets: out = fp16(residual + sum over ranks, in rank order, fp32),
+// this rank's own partial read from `local` ([batch][rows] fp16), the others' polled (bounded) from the packets of the
+// exchange that has just completed on this rank.  The arithmetic is exchange_sum_f16_kernel's.
+__global__ void __launch_bounds__(256) exchange_sum_packets_kernel(const uint4* __restrict__ base, const unsigned int* __restrict__ epoch,
+                                                                   unsigned int* __restrict__ wait_epoch, int rank, int world, long packets,
+                                                                   const __half* __restrict__ local, const __half* __restrict__ residual,
+                                                                   __half* __restrict__ out, unsigned int* status) {
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;");
+    const unsigned int want = *reinterpret_cast<const volatile unsigned int*>(epoch);
+    if (blockIdx.x == 0 && threadIdx.x == 0) atomicAdd(wait_epoch, 1u);
+    const uint4* const half = base + static_cast<size_t>(want & 1u) * world * packets;
+    const unsigned long long t0 = p_timer_ns();
+    for (long i = static_cast<long>(blockIdx.x) * blockDim.x + threadIdx.x; i < packets; i += static_cast<long>(gridDim.x) * blockDim.x) {
+        float a[4] = {0.f, 0.f, 0.f, 0.f};
+        if (residual != nullptr) {
+            const uint2 r = *reinterpret_cast<const uint2*>(residual + 4 * i);
+            const float2 r0 = __half22float2(*reinterpret_cast<const __half2*>(&r.x)), r1 = __half22float2(*reinterpret_cast<const __half2*>(&r.y));
+            a[0] = r0.x; a[1] = r0.y; a[2] = r1.x; a[3] = r1.y;
+        }
+        for (int src = 0; src < world; ++src) {
+            uint2 v;
+            if (src == rank) {
+                v = *reinterpret_cast<const uint2*>(local + 4 * i);
+            } else {
+                const uint4* at = half + static_cast<size_t>(src) * packets + i;
+                uint4 pk;
+                for (unsigned int spin = 0;; ++spin) {
+                    asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(pk.x), "=r"(pk.y), "=r"(pk.z), "=r"(pk.w) : "l"(at) : "memory");
+                    if (static_cast<int>(pk.y - want) >= 0 && static_cast<int>(pk.w - want) >= 0) break;
+                    if ((spin & 255u) == 255u && p_timer_ns() - t0 > kPeerWaitNs) {
+                        raise_status(status, 10u);
+                        return;
+                    }
+                }
+                v = make_uint2(pk.x, pk.z);
+            }
+            const float2 v0 = __half22float2(*reinterpret_cast<const __half2*>(&v.x)), v1 = __half22float2(*reinterpret_cast<const __half2*>(&v.y));
+            a[0] += v0.x; a[1] += v0.y; a[2] += v1.x; a[3] += v1.y;
+        }
+        const __half2 o0 = __floats2half2_rn(a[0], a[1]), o1 = __floats2half2_rn(a[2], a[3]);
+        *reinterpret_cast<uint2*>(out + 4 * i) = make_uint2(*reinterpret_cast<const uint32_t*>(&o0), *reinterpret_cast<const uint32_t*>(&o1));
     }
 }
 
@@ -262,8 +309,23 @@ void launch_exchange_unpack_packets(const uint4* packets, long n_packets, __half
     TQ_CUDA(cudaGetLastError());
 }
 
-void launch_exchange_wait_packets(const uint4* base, const unsigned int* epoch, int rank, int world, long rows, int batch, __half* out,
-                                  long out_stride, unsigned int* status, cudaStream_t stream) {
+void launch_exchange_sum_packets(const uint4* base, const unsigned int* epoch, unsigned int* wait_epoch, int rank, int world, long count,
+                                 const __half* local, const __half* residual, __half* out, unsigned int* status, cudaStream_t stream) {
+    TQ_REQUIRE(base && epoch && wait_epoch && local && out && world >= 1 && rank >= 0 && rank < world && count % 4 == 0,
+               "packet sum: element counts in groups of four");
+    TQ_REQUIRE(reinterpret_cast<uintptr_t>(local) % 8 == 0 && reinterpret_cast<uintptr_t>(out) % 8 == 0 &&
+                   reinterpret_cast<uintptr_t>(residual) % 8 == 0,
+               "packet sum: 8-byte aligned buffers");
+    if (count == 0) return;
+    const long packets = count / 4;
+    const int blocks = static_cast<int>(packets + 255 < 296L * 256 ? (packets + 255) / 256 : 296);
+    cudaLaunchAttribute attr[1];
+    cudaLaunchConfig_t cfg = pdl_config(dim3(static_cast<unsigned>(blocks)), dim3(256), stream, attr);
+    TQ_CUDA(cudaLaunchKernelEx(&cfg, exchange_sum_packets_kernel, base, epoch, wait_epoch, rank, world, packets, local, residual, out, status));
+}
+
+void launch_exchange_wait_packets(const uint4* base, const unsigned int* epoch, unsigned int* wait_epoch, int rank, int world, long rows,
+                                  int batch, __half* out, long out_stride, unsigned int* status, cudaStream_t stream) {
     TQ_REQUIRE(base && epoch && out && world >= 1 && rank >= 0 && rank < world && rows % 4 == 0 && out_stride % 4 == 0 &&
                    reinterpret_cast<uintptr_t>(out) % 8 == 0,
                "packet wait: rows and strides in groups of four, 8-byte aligned destination");
@@ -272,7 +334,8 @@ void launch_exchange_wait_packets(const uint4* base, const unsigned int* epoch, 
     const int blocks = static_cast<int>(total + 255 < 296L * 256 ? (total + 255) / 256 : 296);
     cudaLaunchAttribute attr[1];
     cudaLaunchConfig_t cfg = pdl_config(dim3(static_cast<unsigned>(blocks)), dim3(256), stream, attr);
-    TQ_CUDA(cudaLaunchKernelEx(&cfg, exchange_wait_packets_kernel, base, epoch, rank, world, rows / 4, batch, rows, out, out_stride, status));
+    TQ_CUDA(cudaLaunchKernelEx(&cfg, exchange_wait_packets_kernel, base, epoch, wait_epoch, rank, world, rows / 4, batch, rows, out, out_stride,
+                               status));
 }
 
 void launch_exchange_merge_attention(const __half* outs, const float* lses, int parts, long rows, int dim, long part_stride_o,
