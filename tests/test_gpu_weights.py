@@ -175,6 +175,31 @@ def test_linear_widest_layers_match_oracle(tq, oracle, cols):
     lin.close()
 
 
+@pytest.mark.parametrize("cols,shared", [(5120, True), (2560, True), (1280, True), (13824, True), (6912, False), (3456, True), (5120, False)])
+def test_linear_chunked_columns_match_oracle(tq, oracle, cols, shared):
+    """Input widths above 4096 columns whose last 4096-column chunk would be mostly empty (the Qwen2.5-32B shapes:
+    hidden 5120 and its shards, intermediate 27648 / 2 and / 4) run with narrower chunks and several row tiles per
+    unit; 3456 keeps one chunk with a partly filled last slice.  Ragged row counts, 1 / 3 / 8 activation rows, both
+    rotation modes, against dequantize_weight_cpu + matmul; results are run-to-run identical."""
+    rng = np.random.default_rng(cols + int(shared))
+    rows, bs = 400, 128
+    cb = oracle.codebook(4)[0]
+    w = (rng.standard_normal((rows, cols)) * 0.02).astype(np.float16).astype(np.float32)
+    pp, pr, norms, seeds = oracle.quantize_weight(w, cb, cb, 4, 4, bs, shared)
+    deq = oracle.dequantize_weight(pp, pr, norms, seeds, cb, cb, bs).astype(np.float64)
+    lin = tq.TurboQuantLinear(cols, rows, tq.QuantizedWeight(pp, pr, norms, seeds), tq.codebook_from_centroids(cb),
+                              tq.codebook_from_centroids(cb), bs)
+    for batch in (1, 3, 8):
+        x = rng.standard_normal((batch, cols)).astype(np.float16)
+        want = x.astype(np.float64) @ deq.T
+        y = lin.forward(x)
+        assert np.all(np.isfinite(y.astype(np.float32)))
+        assert rel_l2(y, want) < LINEAR_TOL, (cols, batch, rel_l2(y, want))
+        assert bits_equal(lin.forward(x), y)
+    lin.check_status()
+    lin.close()
+
+
 def test_linear_device_tensors_and_stream(tq, oracle):
     torch = pytest.importorskip("torch")
     rng = np.random.default_rng(2)

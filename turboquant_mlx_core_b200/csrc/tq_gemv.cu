@@ -59,7 +59,7 @@ namespace {
 constexpr int kWarps = 16;
 constexpr int kThreads = kWarps * 32;
 constexpr int kSlice = 256;               // columns per warp
-constexpr int kChunk = kWarps * kSlice;   // columns per unit
+constexpr int kChunk = kWarps * kSlice;   // widest chunk: columns one unit covers with all 16 warps on one row tile
 constexpr uint32_t kLutAddr = 0x10000u;   // shared-window address of the table
 constexpr uint32_t kLutBytes = 0x10000u;  // 256 entries * 256 B
 constexpr int kRedBytes = 32768;           // partial-sum ring: ring * 16 warps * (16 rows * bp + 4) floats
@@ -310,6 +310,8 @@ __device__ __forceinline__ void ll_send_packets(const ScatterArgs& sc, const __h
 // geometry and the reduction need no runtime arithmetic).
 template <int BP, bool SCATTER, bool LL = false>
 __device__ __forceinline__ void gemv_body(const GemvArgs& p, const ScatterArgs& sargs) {
+    // columns per chunk, derived here: one more field in GemvArgs made ptxas spill within the 128 registers
+    const int chunk_cols = p.wpt * kSlice;
     // A warp's partial tile is [16 rows][BP] floats plus 4 floats of padding: the 16 tiles a
     // reduction reads side by side then start 4 banks apart instead of in the same bank.
     constexpr int kTileFloats = 16 * BP + 4;
@@ -371,7 +373,7 @@ __device__ __forceinline__ void gemv_body(const GemvArgs& p, const ScatterArgs& 
         Pos u;
         u.slot = unit / p.n_row_units;
         u.ru = unit - u.slot * p.n_row_units;
-        const int c = (u.slot % p.n_chunks) * kChunk + slice0;  // first column of this warp's slice
+        const int c = (u.slot % p.n_chunks) * chunk_cols + slice0;  // first column of this warp's slice
         const int tile = u.ru * p.tpu + tile_in_unit;
         u.ptr = p.codes + (static_cast<size_t>(tile) * tiles_per_row + static_cast<size_t>(c >> 6)) * kCodeTileBytes + g * 64 + 16 * q;
         u.ok = 0;
@@ -457,7 +459,7 @@ __device__ __forceinline__ void gemv_body(const GemvArgs& p, const ScatterArgs& 
     }
     uint4 x_first = make_uint4(0, 0, 0, 0);
     if (p.x != nullptr) {
-        const int cl0 = (cur.slot - staged_plane * p.n_chunks) * kChunk + slice0 + 8 * lane;
+        const int cl0 = (cur.slot - staged_plane * p.n_chunks) * chunk_cols + slice0 + 8 * lane;
         if (cl0 < p.in) x_first = __ldg(reinterpret_cast<const uint4*>(p.x + cl0));
     }
 #pragma unroll
@@ -567,7 +569,7 @@ __device__ __forceinline__ void gemv_body(const GemvArgs& p, const ScatterArgs& 
                 staged_plane = plane;
             }
             // B fragment of MMA (s, m): k = q -> column 64 s + 16 q + 2 m, k = q+4 -> the next column; n = g.
-            const int colw = (slot - plane * p.n_chunks) * kChunk + slice0;  // first column of this warp's slice
+            const int colw = (slot - plane * p.n_chunks) * chunk_cols + slice0;  // first column of this warp's slice
             const int col0 = colw + 16 * q;
             if (p.x != nullptr) {
                 // Rotate this warp's 256 activation columns here: lane l holds columns 8l..8l+7 of
@@ -852,19 +854,32 @@ __global__ void peer_wait_kernel(const unsigned int* __restrict__ flags, int n, 
 
 size_t align256(size_t v) { return (v + 255) & ~static_cast<size_t>(255); }
 
-// Warps that share one 16-row tile: enough 256-column slices to cover a chunk, as a power of two.
+// Warps that share one 16-row tile (a power of two up to 16); a chunk is that many 256-column slices, and
+// the 16 / wpt row tiles of a unit run side by side.  Up to 4096 columns: the fewest warps that cover the
+// row (one chunk).  Above: 16 warps per tile unless the last chunk would leave more than 15 % of the warps'
+// slices empty (5120 columns = 20 slices: 16 + 4, i.e. 62 %); then the widest tile that fills its chunks to
+// 95 % with at most 8 chunks (5120: 4 warps, five chunks of 1024 columns), if there is one.
 int warps_per_tile(int in) {
-    const int cols = in < kChunk ? in : kChunk;
-    int w = 1;
-    while (w < kWarps && w * kSlice < cols) w <<= 1;
-    return w;
+    const int slices = (in + kSlice - 1) / kSlice;
+    if (in <= kWarps * kSlice) {
+        int w = 1;
+        while (w < kWarps && w < slices) w <<= 1;
+        return w;
+    }
+    auto fill = [&](int w) { return static_cast<double>(slices) / (static_cast<double>((slices + w - 1) / w) * w); };
+    if (fill(kWarps) >= 0.85) return kWarps;
+    for (int w = kWarps / 2; w >= 1; w >>= 1)
+        if (fill(w) >= 0.95 && (slices + w - 1) / w <= 8) return w;
+    return kWarps;
 }
+int chunk_columns(int in) { return warps_per_tile(in) * kSlice; }
 
 }  // namespace
 
 // Scratch layout: [xrot: n_planes*8*in fp32][partials: n_slots*8*out_pad fp32][counters: n_row_tiles u32]
 size_t gemv_scratch_bytes(int out, int in, int n_planes) {
-    const int n_slots = ((in + kChunk - 1) / kChunk) * n_planes;
+    const int chunk = chunk_columns(in);
+    const int n_slots = ((in + chunk - 1) / chunk) * n_planes;
     const int n_row_tiles = (out + 15) / 16;
     const size_t out_pad = static_cast<size_t>(n_row_tiles) * 16;
     size_t bytes = align256(static_cast<size_t>(n_planes) * 8 * in * sizeof(float));
@@ -953,11 +968,12 @@ void launch_tq8_gemv_scatter(const uint8_t* codes, const float* norms, const flo
     }
     a.out = out; a.in = in; a.batch = batch;
     const int n_row_tiles = (out + 15) / 16;
-    a.n_chunks = (in + kChunk - 1) / kChunk;
-    a.n_slots = a.n_chunks * n_planes;
-    a.out_pad = n_row_tiles * 16;
     a.wpt = warps_per_tile(in);
     a.tpu = kWarps / a.wpt;
+    const int chunk = a.wpt * kSlice;  // columns per chunk
+    a.n_chunks = (in + chunk - 1) / chunk;
+    a.n_slots = a.n_chunks * n_planes;
+    a.out_pad = n_row_tiles * 16;
     a.n_row_units = (n_row_tiles + a.tpu - 1) / a.tpu;
     const int bp = batch <= 1 ? 1 : (batch <= 2 ? 2 : (batch <= 4 ? 4 : 8));
     a.inv_scale = 1.0f / std::sqrt(static_cast<float>(in));
