@@ -1247,27 +1247,46 @@ def bench_c4_decode_step(tq, L, device, stream, rank, world, cbs, args):
             exchange.wait(stream=stream)
             exchange.sum_f16(base, world, count, count, out.data_ptr(), residual_ptr=residual.data_ptr(), stream=stream)
 
+        marks = None                       # set to a list: layer_step then records an event after every group of kernels
+
+        def mark(name):
+            if marks is not None:
+                e = torch.cuda.Event(enable_timing=True)
+                e.record(stream)
+                marks.append((name, e))
+
         def layer_step(li):
             w = layers[li]
+            mark("start")
             chk(L.tq_rmsnorm_f16(C.c_void_p(x.data_ptr()), C.c_void_p(w["n1"].data_ptr()), C.c_void_p(h1.data_ptr()), batch, hidden, 1e-6, sp))
+            mark("rmsnorm_1")
             fwd(w["q"], h1.data_ptr(), batch, q.data_ptr())
             fwd(w["k"], h1.data_ptr(), batch, k.data_ptr())
             fwd(w["v"], h1.data_ptr(), batch, v.data_ptr())
+            mark("q_k_v")
             chk(L.tq_rope_f16(C.c_void_p(q.data_ptr()), C.c_void_p(pos.data_ptr()), batch, qh, dim, 1e6, sp))
             chk(L.tq_rope_f16(C.c_void_p(k.data_ptr()), C.c_void_p(pos.data_ptr()), batch, kvh, dim, 1e6, sp))
+            mark("rope_x2")
             chk(L.tq_kv_append_batch(arr, batch, li, C.c_void_p(k.data_ptr()), C.c_void_p(v.data_ptr()), tq.TQ_F16, sp))
+            mark("kv_append")
             chk(L.tq_kv_attention(arr, batch, li, C.c_void_p(q.data_ptr()), tq.TQ_F16, qh, C.c_void_p(attn.data_ptr()), 0, ctx, 1, sp))
+            mark("attention")
             if use_packets:
                 all_reduce_add_packets(w["o"], attn.data_ptr(), x, x1)
             else:
                 all_reduce_add(lambda ptr: fwd(w["o"], attn.data_ptr(), batch, ptr), x, x1)
+            mark("o_proj_sum_residual")
             chk(L.tq_rmsnorm_f16(C.c_void_p(x1.data_ptr()), C.c_void_p(w["n2"].data_ptr()), C.c_void_p(h1.data_ptr()), batch, hidden, 1e-6, sp))
+            mark("rmsnorm_2")
             fwd(w["gu"], h1.data_ptr(), batch, gu.data_ptr())
+            mark("gate_up")
             chk(L.tq_swiglu_f16(C.c_void_p(gu.data_ptr()), C.c_void_p(act.data_ptr()), batch, il, sp))
+            mark("swiglu")
             if use_packets:
                 all_reduce_add_packets(w["down"], act.data_ptr(), x1, x)
             else:
                 all_reduce_add(lambda ptr: fwd(w["down"], act.data_ptr(), batch, ptr), x1, x)
+            mark("down_proj_sum_residual")
 
         def one_pass():
             for li in range(n_layers):
@@ -1316,6 +1335,21 @@ def bench_c4_decode_step(tq, L, device, stream, rank, world, cbs, args):
             dist.all_reduce(ok, op=dist.ReduceOp.MIN)
             same = bool(ok.item() == 1.0)
             exchange.check_status()
+        # where the step's time goes: one eager pass with an event after every group of kernels (median over the
+        # layers; eager launches, so each group also carries its launch gaps - the graph figure above is the step)
+        breakdown = None
+        if world == 1:
+            marks = []
+            with torch.cuda.stream(stream):
+                for _ in range(3):
+                    one_pass()
+            torch.cuda.synchronize()
+            groups = {}
+            for (n0, ev0), (n1, ev1) in zip(marks, marks[1:]):
+                if n1 != "start":
+                    groups.setdefault(n1, []).append(ev0.elapsed_time(ev1) * 1e3)
+            breakdown = {n: round(float(np.median(v)), 2) for n, v in groups.items()}
+            marks = None
         weight_bytes = bytes_per_layer
         kv_bytes = batch * kvh * ctx * 118
         res[f"b{batch}"] = {"us_per_layer": us, "tok_per_s_64_layers": batch / (us * 1e-6 * n_model_layers),
@@ -1327,6 +1361,8 @@ def bench_c4_decode_step(tq, L, device, stream, rank, world, cbs, args):
                                            "partials sent as packets from inside o_proj / down_proj, one kernel waits and adds" if use_packets
                                            else "tq_exchange_broadcast + tq_exchange_wait + tq_exchange_sum_f16"),
                             "residual_stream_finite": finite, "identical_on_every_rank": same}
+        if breakdown is not None:
+            res[f"b{batch}"]["eager_us_by_kernel_group"] = breakdown
         for c in caches:
             c.close()
 

@@ -32,15 +32,17 @@
 // copy `lane` of entry `code` is a pure byte permutation of (code word, per-lane
 // constant): no shift, mask or add.
 //
-// Work split.  A unit is one 4096-column chunk (a "slot") of a 16-row tile; when
-// in_features <= 2048 the 16 warps are split over 2, 4, 8 or 16 row tiles instead, so no
-// warp idles on narrow matrices.  Units are
-// ordered slot-major and dealt to CTAs in contiguous ranges, so a CTA reloads its B
-// fragments only when its slot changes.  With more than one slot (in_features > 4096,
-// or dual rotation) each unit writes fp32 partial sums to scratch and the CTA that
-// completes a row tile (per-tile arrival counter) adds the partials in slot order - a
-// fixed order, so results do not depend on scheduling - applies norm*inv_scale and
-// writes fp16.
+// Work split.  The 16 warps of a CTA are split into groups of wpt warps (a power of two); a group multiplies one
+// 16-row tile against a chunk of wpt * 256 columns, so a unit is 16 / wpt row tiles of one chunk (a "slot").  Up to
+// 4096 columns there is one chunk and wpt is the fewest warps that cover the row; above, wpt = 16 unless the last
+// chunk would leave more than 15 % of the slices empty (5120 columns: five chunks of 1024 with wpt = 4).  Units are
+// ordered slot-major and dealt to CTAs in contiguous ranges, so a CTA reloads its B fragments only when its slot
+// changes.  A warp's partial tiles are added across the group through a ring in shared memory, one pass of
+// log2(wpt) lane exchanges per unit.  With more than one slot (in_features > 4096, or dual rotation) the sums go
+// to scratch as fp32; every warp owns the same rows in every slot and counts its arrivals per (row unit, warp) -
+// once per 8 units, since the fence before the count stalls the warp - and the warp that completes a row unit adds
+// the slots' partial sums in slot order (a fixed order, so results do not depend on scheduling), applies
+// norm*inv_scale and writes fp16.
 // Dual-rotation weights (separate sign seeds for the primary and residual planes,
 // src/dequantizer.cpp:214-246) run as two "planes": plane 0 looks up the primary
 // centroid of each joint byte against x rotated with the primary seed, plane 1 the
@@ -64,6 +66,7 @@ constexpr uint32_t kLutAddr = 0x10000u;   // shared-window address of the table
 constexpr uint32_t kLutBytes = 0x10000u;  // 256 entries * 256 B
 constexpr int kRedBytes = 32768;           // partial-sum ring: ring * 16 warps * (16 rows * bp + 4) floats
 constexpr int kMaxRing = 16;
+constexpr int kFlushUnits = 8;             // units a warp finishes between two arrival counts (several slots only)
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
 
@@ -132,7 +135,7 @@ struct GemvArgs {
     const __half* x;        // [batch, in] fp16: rotate inside the kernel (WHT block <= 256), else nullptr
     __half* y;              // [batch, y_stride]: row r of activation row n at y[n * y_stride + r]
     float* partial;         // [n_slots, 8, out_pad] (only when n_slots > 1)
-    unsigned int* counters; // [n_row_units]         (only when n_slots > 1)
+    unsigned int* counters; // [n_row_units][16 warps] (only when n_slots > 1)
     unsigned int* status;   // device error word (0 = ok)
     int out, in, batch;
     int n_row_units, n_chunks, n_slots, out_pad;  // n_slots = n_planes * n_chunks
@@ -308,7 +311,9 @@ __device__ __forceinline__ void ll_send_packets(const ScatterArgs& sc, const __h
 
 // BP = activation rows padded to 1, 2, 4 or 8 (compile time, so that the partial-sum ring
 // geometry and the reduction need no runtime arithmetic).
-template <int BP, bool SCATTER, bool LL = false>
+// MULTI = more than one slot (row units finished through partial sums in scratch); compile time, so that the
+// single-slot kernels carry none of that path's state in their 128 registers.
+template <int BP, bool SCATTER, bool LL, bool MULTI>
 __device__ __forceinline__ void gemv_body(const GemvArgs& p, const ScatterArgs& sargs) {
     // columns per chunk, derived here: one more field in GemvArgs made ptxas spill within the 128 registers
     const int chunk_cols = p.wpt * kSlice;
@@ -471,44 +476,88 @@ __device__ __forceinline__ void gemv_body(const GemvArgs& p, const ScatterArgs& 
 
     // ---- sum of one unit's per-warp partial tiles ----
     // Ring slot layout: [warp][16 rows][BP] floats (+ 4 floats of padding per warp).  Warp w owns the (tile, row) pairs
-    // w*tpu .. w*tpu+tpu-1 of the unit; lane l reads what warp (l & 15) of that row tile's
-    // group wrote, activation columns (l >> 4) * kPer .., and a fixed shuffle tree adds the
-    // 16 (fixed order: results do not depend on timing).
-    const int pw = lane & 15, hv = lane >> 4;
+    // w*tpu .. w*tpu+tpu-1 of the unit.  The 16 lanes of a half warp cover those tpu pairs times the wpt warps that
+    // worked on the pair's row tile (tpu * wpt = 16): lane l reads what warp (l & (wpt - 1)) of the group wrote for pair
+    // (l & 15) / wpt, activation columns (l >> 4) * kPer .., and a fixed tree of log2(wpt) lane exchanges adds them
+    // (fixed order: results do not depend on timing).  One pass per unit whatever the split.
+    const int pw = lane & (p.wpt - 1), hv = lane >> 4;
     const int n0 = BP >= 2 ? hv * kPer : 0;
-    const bool red_active = pw < p.wpt && (BP >= 2 || hv == 0);
-    const bool red_writer = pw == 0 && (BP >= 2 || hv == 0);
+    const int red_pi = warp * p.tpu + (lane & 15) / p.wpt;       // this lane's pair: row tile red_pi >> 4 of the unit, row red_pi & 15
+    const int red_row = (red_pi >> 4) * 16 + (red_pi & 15);      // its row inside the row unit
+    const uint32_t red_src = red_addr + static_cast<uint32_t>(((red_pi >> 4) * p.wpt + pw) * kTileFloats + (red_pi & 15) * BP + n0) * 4u;
+    const bool red_active = BP >= 2 || hv == 0;
+    const bool red_writer = pw == 0 && red_active;
+    // Counts this warp's last `pend` units (row units ru_last - pend + 1 .. ru_last of one slot) in and finishes the
+    // row units it completes.
+    int pend = 0;
+    auto flush_pending = [&](int ru_last) {
+        __threadfence();
+        __syncwarp();
+        const int ru0 = ru_last - pend + 1;
+        unsigned int prev = 0xffffffffu;
+        if (lane < pend) prev = atomicAdd(&p.counters[(ru0 + lane) * kWarps + warp], 1u);
+        unsigned int done = __ballot_sync(0xffffffffu, prev == static_cast<unsigned int>(p.n_slots) - 1u);
+        pend = 0;
+        if (done == 0u) return;
+        __threadfence();
+        if (prev == static_cast<unsigned int>(p.n_slots) - 1u) p.counters[(ru0 + lane) * kWarps + warp] = 0u;  // ready for the next launch
+        // the outputs of all completed row units side by side over the lanes; up to 8 slots' partial sums are requested
+        // at once (one round trip to L2) and added in slot order
+        const int per_unit = p.tpu * BP;
+        const int n_done = __popc(done) * per_unit;
+        for (int idx = lane; idx < n_done; idx += 32) {
+            const int k = idx / per_unit, e = idx - k * per_unit;
+            const int ru = ru0 + static_cast<int>(__fns(done, 0u, k + 1));
+            const int n = e % BP, pi = warp * p.tpu + e / BP;
+            const int row = (ru * p.tpu + (pi >> 4)) * 16 + (pi & 15);
+            if (row < p.out && n < p.batch) {
+                const float sc = __ldg(p.norms + row) * p.inv_scale;
+                const float* src = p.partial + static_cast<size_t>(n) * p.out_pad + row;
+                float total = 0.f;
+                for (int c0 = 0; c0 < p.n_slots; c0 += 8) {
+                    float t[8];
+#pragma unroll
+                    for (int c = 0; c < 8; ++c)
+                        t[c] = (c0 + c < p.n_slots) ? __ldcg(src + static_cast<size_t>(c0 + c) * 8 * p.out_pad) : 0.f;
+#pragma unroll
+                    for (int c = 0; c < 8; ++c) total += t[c];
+                }
+                store_y<SCATTER>(p, sargs, n, row, __float2half_rn(total * sc));
+            }
+        }
+    };
     auto reduce_unit = [&](int slot, int ru, int rs, uint32_t parity) {
         if (!mbar_wait(bar_written + 8u * rs, parity)) {
             raise_status(p.status, 5u);
             atomicExch(&s_abort, 1u);
         }
-        for (int j = 0; j < p.tpu; ++j) {
-            const int pi = warp * p.tpu + j, t = pi >> 4, r = pi & 15;
-            const int row = (ru * p.tpu + t) * 16 + r;
+        {
+            const int row = ru * p.tpu * 16 + red_row;
             const bool wr = red_writer && row < p.out;
-            // the norm is fetched first so that its latency hides behind the shuffles
-            const float sc = wr ? __ldg(p.norms + row) * p.inv_scale : 0.f;
+            float sc = 0.f;
+            // the norm is fetched first so that its latency hides behind the exchanges
+            if constexpr (!MULTI) sc = wr ? __ldg(p.norms + row) * p.inv_scale : 0.f;
             float v[kPer];
 #pragma unroll
             for (int k = 0; k < kPer; ++k) v[k] = 0.f;
             if (red_active) {
-                const uint32_t src = red_addr + static_cast<uint32_t>(rs) * kSlotBytes +
-                                     static_cast<uint32_t>((t * p.wpt + pw) * kTileFloats + r * BP + n0) * 4u;
+                const uint32_t src = red_src + static_cast<uint32_t>(rs) * kSlotBytes;
                 if constexpr (kPer == 4) asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v[0]), "=f"(v[1]), "=f"(v[2]), "=f"(v[3]) : "r"(src));
                 else if constexpr (kPer == 2) asm volatile("ld.shared.v2.f32 {%0, %1}, [%2];" : "=f"(v[0]), "=f"(v[1]) : "r"(src));
                 else asm volatile("ld.shared.f32 %0, [%1];" : "=f"(v[0]) : "r"(src));
             }
 #pragma unroll
             for (int o = 1; o < 16; o <<= 1) {
+                if (o < p.wpt) {
 #pragma unroll
-                for (int k = 0; k < kPer; ++k) v[k] += __shfl_xor_sync(0xffffffffu, v[k], o);
+                    for (int k = 0; k < kPer; ++k) v[k] += __shfl_xor_sync(0xffffffffu, v[k], o);
+                }
             }
             if (wr) {
 #pragma unroll
                 for (int k = 0; k < kPer; ++k) {
                     const int n = n0 + k;
-                    if (p.n_slots == 1) {
+                    if constexpr (!MULTI) {
                         if (n < p.batch) store_y<SCATTER>(p, sargs, n, row, __float2half_rn(v[k] * sc));
                     } else {
                         p.partial[(static_cast<size_t>(slot) * 8 + n) * p.out_pad + row] = v[k];
@@ -518,36 +567,16 @@ __device__ __forceinline__ void gemv_body(const GemvArgs& p, const ScatterArgs& 
         }
         __syncwarp();
         if (lane == 0) mbar_arrive(bar_read + 8u * rs);
-        if (p.n_slots > 1) {
-            // Row units spread over several slots: every warp counts in; the warp that brings the
-            // count to n_slots * 16 adds the slots' partial sums in slot order and writes y.
-            __threadfence();
-            __syncwarp();
-            unsigned int last = 0;
-            if (lane == 0) {
-                const unsigned int target = static_cast<unsigned int>(p.n_slots * kWarps);
-                const unsigned int prev = atomicAdd(&p.counters[ru], 1u);
-                last = (prev == target - 1u) ? 1u : 0u;
-                if (last) p.counters[ru] = 0u;  // ready for the next launch
-            }
-            last = __shfl_sync(0xffffffffu, last, 0);
-            if (last) {
-                __threadfence();
-                const int n_out = p.tpu * 16 * BP;
-                for (int idx = lane; idx < n_out; idx += 32) {
-                    const int n = idx % BP, tr = idx / BP;
-                    const int row = ru * p.tpu * 16 + tr;
-                    if (row < p.out && n < p.batch) {
-                        float total = 0.f;
-                        for (int c = 0; c < p.n_slots; ++c)
-                            total += __ldcg(p.partial + (static_cast<size_t>(c) * 8 + n) * p.out_pad + row);
-                        store_y<SCATTER>(p, sargs, n, row, __float2half_rn(total * (p.norms[row] * p.inv_scale)));
-                    }
-                }
-            }
+        if constexpr (MULTI) {
+            // Row units spread over several slots.  A warp owns the same rows of a row unit in every slot, so the
+            // arrival count is kept per (row unit, warp): the warp that brings it to n_slots adds the slots' partial
+            // sums of its rows in slot order and writes y.  The fence between the partial stores and the count makes
+            // the warp wait for its memory traffic, code loads in flight included, so it is paid once per
+            // kFlushUnits units (consecutive row units of one slot), not per unit.
+            ++pend;
+            if (pend == kFlushUnits || ru + 1 == p.n_row_units) flush_pending(ru);
         }
     };
-
     uint32_t bfrag[4][16];
     int staged_slot = -1;
     // ring bookkeeping: slot / parity for the unit being written and the unit being summed
@@ -735,6 +764,7 @@ __device__ __forceinline__ void gemv_body(const GemvArgs& p, const ScatterArgs& 
     // the last kLag units (or all of them, for a short range) are still to be summed
     for (int k = (n_local > kLag ? n_local - kLag : 0); k < n_local; ++k) {
         reduce_unit(red.slot, red.ru, rs, rpar);
+        if constexpr (MULTI) if (k + 1 == n_local && pend > 0) flush_pending(red.ru);
         red = next_pos(red);
         if (++rs == kRing) { rs = 0; rpar ^= 1u; }
     }
@@ -749,7 +779,7 @@ __device__ __forceinline__ void gemv_body(const GemvArgs& p, const ScatterArgs& 
         // Packets, one slot: every row of this CTA's units was stored by this CTA, so it sends its own rows as soon
         // as it is done - the sends of the grid run side by side and nothing waits for the slowest CTA.  (With several
         // slots the CTA that completes a row tile is not known in advance: the completing CTA of the grid sends all.)
-        const bool own_rows = LL && p.n_slots == 1;
+        const bool own_rows = LL && !MULTI;
         if constexpr (LL) if (own_rows) {
             __syncthreads();   // this CTA's stores are ordered before the loads below (read back through L2)
             const int per_row = p.out / 4;
@@ -822,17 +852,17 @@ __device__ __forceinline__ void gemv_body(const GemvArgs& p, const ScatterArgs& 
     }
 }
 
-template <int BP>
+template <int BP, bool MULTI>
 __global__ void __launch_bounds__(kCtaThreads, 1) tq8_gemv_kernel(const GemvArgs p) {
-    gemv_body<BP, false>(p, ScatterArgs{});
+    gemv_body<BP, false, false, MULTI>(p, ScatterArgs{});
 }
-template <int BP>
+template <int BP, bool MULTI>
 __global__ void __launch_bounds__(kCtaThreads, 1) tq8_gemv_packets_kernel(const GemvArgs p, const ScatterArgs sc) {
-    gemv_body<BP, true, true>(p, sc);
+    gemv_body<BP, true, true, MULTI>(p, sc);
 }
-template <int BP>
+template <int BP, bool MULTI>
 __global__ void __launch_bounds__(kCtaThreads, 1) tq8_gemv_scatter_kernel(const GemvArgs p, const ScatterArgs sc) {
-    gemv_body<BP, true>(p, sc);
+    gemv_body<BP, true, false, MULTI>(p, sc);
 }
 
 // Waits (bounded) until flags[0..n) have all reached `value`: the receiving side of the completion
@@ -876,7 +906,7 @@ int chunk_columns(int in) { return warps_per_tile(in) * kSlice; }
 
 }  // namespace
 
-// Scratch layout: [xrot: n_planes*8*in fp32][partials: n_slots*8*out_pad fp32][counters: n_row_tiles u32]
+// Scratch layout: [xrot: n_planes*8*in fp32][partials: n_slots*8*out_pad fp32][counters: n_row_tiles*16 u32]
 size_t gemv_scratch_bytes(int out, int in, int n_planes) {
     const int chunk = chunk_columns(in);
     const int n_slots = ((in + chunk - 1) / chunk) * n_planes;
@@ -885,7 +915,7 @@ size_t gemv_scratch_bytes(int out, int in, int n_planes) {
     size_t bytes = align256(static_cast<size_t>(n_planes) * 8 * in * sizeof(float));
     if (n_slots > 1)
         bytes += align256(static_cast<size_t>(n_slots) * 8 * out_pad * sizeof(float)) +
-                 align256(static_cast<size_t>(n_row_tiles) * sizeof(unsigned int));
+                 align256(static_cast<size_t>(n_row_tiles) * kWarps * sizeof(unsigned int));
     return bytes;
 }
 
@@ -979,8 +1009,11 @@ void launch_tq8_gemv_scatter(const uint8_t* codes, const float* norms, const flo
     a.inv_scale = 1.0f / std::sqrt(static_cast<float>(in));
     // Blocks that fit a warp's 256-column slice are rotated inside the GEMV kernel (16-byte
     // activation loads); larger blocks, or an unaligned activation, go through rotate_x_kernel.
+    // In-kernel rotation handles one activation row after the other (a chain of lane exchanges per row) in every
+    // warp, which costs more than the pre-kernel from two rows on (4096 x 4096: 9.0 / 11.3 / 15.3 us in-kernel
+    // against 8.3 / 9.2 / 10.8 us with the pre-kernel at 2 / 4 / 8 rows; the same at one row).
     const bool fused_rotation = block <= static_cast<uint32_t>(kSlice) && in % 8 == 0 &&
-                                reinterpret_cast<uintptr_t>(x) % 16 == 0;
+                                reinterpret_cast<uintptr_t>(x) % 16 == 0 && batch == 1;
     a.x = fused_rotation ? x : nullptr;
     a.seed_p = seed_p; a.seed_r = seed_r;
     a.block = static_cast<int>(block);
@@ -1000,15 +1033,20 @@ void launch_tq8_gemv_scatter(const uint8_t* codes, const float* norms, const flo
     int dev = 0;
     TQ_CUDA(cudaGetDevice(&dev));
     if (dev >= 64 || !configured[dev]) {
-#define TQ_GEMV_ATTR(BPV)                                                                                                          \
-    TQ_CUDA(cudaFuncSetAttribute(tq8_gemv_kernel<BPV>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kGemvSmem))); \
-    TQ_CUDA(cudaFuncSetAttribute(tq8_gemv_scatter_kernel<BPV>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kGemvSmem))); \
-    TQ_CUDA(cudaFuncSetAttribute(tq8_gemv_packets_kernel<BPV>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kGemvSmem)));
+#define TQ_GEMV_ATTR1(K) TQ_CUDA(cudaFuncSetAttribute(K, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kGemvSmem)));
+#define TQ_GEMV_ATTR(BPV)                                \
+    TQ_GEMV_ATTR1((tq8_gemv_kernel<BPV, false>))         \
+    TQ_GEMV_ATTR1((tq8_gemv_kernel<BPV, true>))          \
+    TQ_GEMV_ATTR1((tq8_gemv_scatter_kernel<BPV, false>)) \
+    TQ_GEMV_ATTR1((tq8_gemv_scatter_kernel<BPV, true>))  \
+    TQ_GEMV_ATTR1((tq8_gemv_packets_kernel<BPV, false>)) \
+    TQ_GEMV_ATTR1((tq8_gemv_packets_kernel<BPV, true>))
         TQ_GEMV_ATTR(1)
         TQ_GEMV_ATTR(2)
         TQ_GEMV_ATTR(4)
         TQ_GEMV_ATTR(8)
 #undef TQ_GEMV_ATTR
+#undef TQ_GEMV_ATTR1
         if (dev < 64) configured[dev] = true;
     }
 
@@ -1049,10 +1087,13 @@ void launch_tq8_gemv_scatter(const uint8_t* codes, const float* norms, const flo
         cfg.numAttrs = n_attr;
         // one destination with the layer's own row stride and no signal: the plain variant
         const bool scatter = sa.n_peer > 0 || sa.n_signal > 0 || sa.ll != 0 || sa.y_stride != a.out;
-#define TQ_GEMV_LAUNCH(BPV)                                                   \
-    if (sa.ll) TQ_CUDA(cudaLaunchKernelEx(&cfg, tq8_gemv_packets_kernel<BPV>, a, sa)); \
-    else if (scatter) TQ_CUDA(cudaLaunchKernelEx(&cfg, tq8_gemv_scatter_kernel<BPV>, a, sa)); \
-    else TQ_CUDA(cudaLaunchKernelEx(&cfg, tq8_gemv_kernel<BPV>, a));
+#define TQ_GEMV_LAUNCH2(BPV, MV)                                                                  \
+    if (sa.ll) TQ_CUDA(cudaLaunchKernelEx(&cfg, tq8_gemv_packets_kernel<BPV, MV>, a, sa));        \
+    else if (scatter) TQ_CUDA(cudaLaunchKernelEx(&cfg, tq8_gemv_scatter_kernel<BPV, MV>, a, sa)); \
+    else TQ_CUDA(cudaLaunchKernelEx(&cfg, tq8_gemv_kernel<BPV, MV>, a));
+#define TQ_GEMV_LAUNCH(BPV)                           \
+    if (a.n_slots > 1) { TQ_GEMV_LAUNCH2(BPV, true) } \
+    else { TQ_GEMV_LAUNCH2(BPV, false) }
         switch (bp) {
             case 1: TQ_GEMV_LAUNCH(1) break;
             case 2: TQ_GEMV_LAUNCH(2) break;
@@ -1060,6 +1101,7 @@ void launch_tq8_gemv_scatter(const uint8_t* codes, const float* norms, const flo
             default: TQ_GEMV_LAUNCH(8) break;
         }
 #undef TQ_GEMV_LAUNCH
+#undef TQ_GEMV_LAUNCH2
     }
 }
 
@@ -1131,7 +1173,7 @@ void launch_tq8_gemv_static(const uint8_t* codes, const float* norms, const floa
     const size_t xrot_bytes = align256(static_cast<size_t>(n_planes) * 8 * in * sizeof(float));
     if (need > xrot_bytes) {
         const int n_row_tiles = (out + 15) / 16;
-        const size_t counter_bytes = align256(static_cast<size_t>(n_row_tiles) * sizeof(unsigned int));
+        const size_t counter_bytes = align256(static_cast<size_t>(n_row_tiles) * kWarps * sizeof(unsigned int));
         TQ_CUDA(cudaMemsetAsync(static_cast<uint8_t*>(scratch) + need - counter_bytes, 0, counter_bytes, stream));
     }
     launch_tq8_gemv(codes, norms, table, x, y, out, in, batch, block, n_planes, seed_p, seed_r, scratch, status, sm_count,
