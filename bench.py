@@ -1338,8 +1338,10 @@ def bench_c4_decode_step(tq, L, device, stream, rank, world, cbs, args):
         # where the step's time goes: one eager pass with an event after every group of kernels (median over the
         # layers; eager launches, so each group also carries its launch gaps - the graph figure above is the step)
         breakdown = None
-        if world == 1:
+        if True:                           # every rank runs the passes (the exchanges need all of them); rank 0 reports
             marks = []
+            if world > 1:
+                dist.barrier()
             with torch.cuda.stream(stream):
                 for _ in range(3):
                     one_pass()

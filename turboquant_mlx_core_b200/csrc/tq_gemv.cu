@@ -334,11 +334,14 @@ __device__ __forceinline__ void gemv_body(const GemvArgs& p, const ScatterArgs& 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
 
     // ---- unit range of this CTA: unit = (slot, row unit), slot = plane * n_chunks + chunk ----
+    // (the first `rem` CTAs take one unit more; one 32-bit division - the prologue runs once per launch on
+    // instructions that are not cached yet, and cannot overlap the preceding kernel, whose CTA fills this SM)
     const int n_units = p.n_row_units * p.n_slots;
-    const int u_begin = static_cast<int>(static_cast<long>(n_units) * blockIdx.x / gridDim.x);
-    const int u_end = static_cast<int>(static_cast<long>(n_units) * (blockIdx.x + 1) / gridDim.x);
-    if (u_begin >= u_end) return;
-    const int n_local = u_end - u_begin;
+    const int u_quot = n_units / static_cast<int>(gridDim.x), u_rem = n_units - u_quot * static_cast<int>(gridDim.x);
+    const int bid = static_cast<int>(blockIdx.x);
+    const int u_begin = u_quot * bid + (bid < u_rem ? bid : u_rem);
+    const int n_local = u_quot + (bid < u_rem ? 1 : 0);
+    if (n_local <= 0) return;
 
     // ---- shared-memory map: [partial-sum ring | rotation strips | unused | table at 0x10000] ----
     const uint32_t base = smem_u32(smem_raw);
@@ -359,8 +362,9 @@ __device__ __forceinline__ void gemv_body(const GemvArgs& p, const ScatterArgs& 
     }
 
     const int g = lane >> 2, q = lane & 3;
-    const int tile_in_unit = warp / p.wpt;                      // which of the unit's row tiles this warp works on
-    const int slice0 = (warp - tile_in_unit * p.wpt) * kSlice;  // column of this warp's slice inside the chunk
+    const int wpt_shift = 31 - __clz(p.wpt);                    // wpt is a power of two
+    const int tile_in_unit = warp >> wpt_shift;                 // which of the unit's row tiles this warp works on
+    const int slice0 = (warp & (p.wpt - 1)) * kSlice;           // column of this warp's slice inside the chunk
     const uint32_t lane_const = 0x00010000u | static_cast<uint32_t>(lane * 4);
     // Codes are stored in 16-row x 64-column tiles of 1 KB (code_offset): a step of a warp is one
     // tile, of which lane (g, q) reads bytes g*64 + 16q (row g) and 512 + g*64 + 16q (row g + 8) -
@@ -376,9 +380,14 @@ __device__ __forceinline__ void gemv_body(const GemvArgs& p, const ScatterArgs& 
     };
     auto make_pos = [&](int unit) {
         Pos u;
-        u.slot = unit / p.n_row_units;
-        u.ru = unit - u.slot * p.n_row_units;
-        const int c = (u.slot % p.n_chunks) * chunk_cols + slice0;  // first column of this warp's slice
+        if constexpr (MULTI) {
+            u.slot = unit / p.n_row_units;
+            u.ru = unit - u.slot * p.n_row_units;
+        } else {
+            u.slot = 0;
+            u.ru = unit;
+        }
+        const int c = (MULTI ? (u.slot % p.n_chunks) * chunk_cols : 0) + slice0;  // first column of this warp's slice
         const int tile = u.ru * p.tpu + tile_in_unit;
         u.ptr = p.codes + (static_cast<size_t>(tile) * tiles_per_row + static_cast<size_t>(c >> 6)) * kCodeTileBytes + g * 64 + 16 * q;
         u.ok = 0;
@@ -389,7 +398,7 @@ __device__ __forceinline__ void gemv_body(const GemvArgs& p, const ScatterArgs& 
     };
     auto next_pos = [&](const Pos& u) {
         Pos n = u;
-        if (u.ru + 1 < p.n_row_units) {   // same slot, next row unit: only the rows move
+        if (!MULTI || u.ru + 1 < p.n_row_units) {   // same slot, next row unit: only the rows move
             n.ru = u.ru + 1;
             n.ptr = u.ptr + unit_stride;
             n.ok = (u.ok & 15u) | (((n.ru * p.tpu + tile_in_unit) * 16 < p.out) ? 48u : 0u);
@@ -429,7 +438,7 @@ __device__ __forceinline__ void gemv_body(const GemvArgs& p, const ScatterArgs& 
     // preceding kernel), then comes the dependency wait, then this warp's activation slice of
     // the first unit is requested, and only then are the table entries written to shared
     // memory - so the activation's latency hides behind the table build.
-    int staged_plane = cur.slot / p.n_chunks;
+    int staged_plane = MULTI ? cur.slot / p.n_chunks : 0;
     float tab_first[4];
 #pragma unroll
     for (int k = 0; k < 4; ++k) tab_first[k] = __ldg(p.table + staged_plane * 256 + (tid >> 3) + 64 * k);
@@ -464,7 +473,7 @@ __device__ __forceinline__ void gemv_body(const GemvArgs& p, const ScatterArgs& 
     }
     uint4 x_first = make_uint4(0, 0, 0, 0);
     if (p.x != nullptr) {
-        const int cl0 = (cur.slot - staged_plane * p.n_chunks) * chunk_cols + slice0 + 8 * lane;
+        const int cl0 = (MULTI ? (cur.slot - staged_plane * p.n_chunks) * chunk_cols : 0) + slice0 + 8 * lane;
         if (cl0 < p.in) x_first = __ldg(reinterpret_cast<const uint4*>(p.x + cl0));
     }
 #pragma unroll
@@ -482,7 +491,7 @@ __device__ __forceinline__ void gemv_body(const GemvArgs& p, const ScatterArgs& 
     // (fixed order: results do not depend on timing).  One pass per unit whatever the split.
     const int pw = lane & (p.wpt - 1), hv = lane >> 4;
     const int n0 = BP >= 2 ? hv * kPer : 0;
-    const int red_pi = warp * p.tpu + (lane & 15) / p.wpt;       // this lane's pair: row tile red_pi >> 4 of the unit, row red_pi & 15
+    const int red_pi = warp * p.tpu + ((lane & 15) >> wpt_shift);       // this lane's pair: row tile red_pi >> 4 of the unit, row red_pi & 15
     const int red_row = (red_pi >> 4) * 16 + (red_pi & 15);      // its row inside the row unit
     const uint32_t red_src = red_addr + static_cast<uint32_t>(((red_pi >> 4) * p.wpt + pw) * kTileFloats + (red_pi & 15) * BP + n0) * 4u;
     const bool red_active = BP >= 2 || hv == 0;
@@ -590,7 +599,7 @@ __device__ __forceinline__ void gemv_body(const GemvArgs& p, const ScatterArgs& 
     // warp's B fragments.  x0 is this lane's first-row activation when the caller has already
     // requested it (have_x0).
     auto stage_slot = [&](int slot, const uint4& x0, bool have_x0) {
-        const int plane = slot / p.n_chunks;
+        const int plane = MULTI ? slot / p.n_chunks : 0;
             if (plane != staged_plane) {
                 named_barrier_sync(1, kConsumerThreads);  // nobody still reads the previous table
                 build_table(plane);
@@ -598,75 +607,62 @@ __device__ __forceinline__ void gemv_body(const GemvArgs& p, const ScatterArgs& 
                 staged_plane = plane;
             }
             // B fragment of MMA (s, m): k = q -> column 64 s + 16 q + 2 m, k = q+4 -> the next column; n = g.
-            const int colw = (slot - plane * p.n_chunks) * chunk_cols + slice0;  // first column of this warp's slice
+            const int colw = (MULTI ? (slot - plane * p.n_chunks) * chunk_cols : 0) + slice0;  // first column of this warp's slice
             const int col0 = colw + 16 * q;
-            if (p.x != nullptr) {
-                // Rotate this warp's 256 activation columns here: lane l holds columns 8l..8l+7 of
-                // the slice, stages below 8 stay in the lane, the rest are lane exchanges (same
-                // add tree as rotate_x_kernel).  A 1 KB strip of shared memory per warp turns the
-                // result into the fragment layout, one activation row at a time.
+            if (BP == 1 && p.x != nullptr) {
+                // One activation row (the launcher rotates in here only then): rotate this warp's 256 columns of it.
+                // Lane l holds columns 8l..8l+7 of the slice, stages below 8 stay in the lane, the rest are lane
+                // exchanges (same add tree as rotate_x_kernel).  A 1 KB strip of shared memory per warp turns the
+                // result into the fragment layout.  Every lane loads the row's fragment, so B columns 1..7 repeat
+                // column 0 and their results are never read: nothing to clear.
                 const uint32_t seed = plane ? p.seed_r : p.seed_p;
                 const int cl = colw + 8 * lane;
-                const bool c_ok = cl < p.in;
-                // bit j: the sign of this lane's column j is negative
-                uint32_t neg = 0;
+                uint4 xc = x0;
+                if (!have_x0) {
+                    xc = make_uint4(0, 0, 0, 0);
+                    if (cl < p.in) xc = __ldg(reinterpret_cast<const uint4*>(p.x + cl));
+                }
+                const uint32_t xw[4] = {xc.x, xc.y, xc.z, xc.w};
+                float v[8];
 #pragma unroll
-                for (int j = 0; j < 8; ++j)
-                    neg |= sign_is_positive(seed, static_cast<uint32_t>((8 * lane + j) & (p.block - 1))) ? 0u : (1u << j);
+                for (int j = 0; j < 4; ++j) {
+                    const __half2 h2 = *reinterpret_cast<const __half2*>(&xw[j]);
+                    const float lo = __low2float(h2), hi = __high2float(h2);
+                    v[2 * j] = sign_is_positive(seed, static_cast<uint32_t>((8 * lane + 2 * j) & (p.block - 1))) ? lo : -lo;
+                    v[2 * j + 1] = sign_is_positive(seed, static_cast<uint32_t>((8 * lane + 2 * j + 1) & (p.block - 1))) ? hi : -hi;
+                }
+#pragma unroll
+                for (int h = 1; h < 8; h <<= 1)
+#pragma unroll
+                    for (int i = 0; i < 8; i += 2 * h)
+#pragma unroll
+                        for (int j = i; j < i + h; ++j) {
+                            const float a = v[j], b = v[j + h];
+                            v[j] = __fadd_rn(a, b);
+                            v[j + h] = __fsub_rn(a, b);
+                        }
+                const int lane_steps = p.block >> 3;  // lanes per WHT block
+                for (int m = 1; m < lane_steps; m <<= 1) {
+                    const bool upper = (lane & m) != 0;
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        const float o = __shfl_xor_sync(0xffffffffu, v[j], m);
+                        v[j] = upper ? __fsub_rn(o, v[j]) : __fadd_rn(v[j], o);
+                    }
+                }
+#pragma unroll
+                for (int j = 0; j < 8; ++j) v[j] = to_tf32(v[j] * p.inv_sqrt_block);
+                sts_v4(strip_addr + static_cast<uint32_t>(lane) * 32u, v[0], v[1], v[2], v[3]);
+                sts_v4(strip_addr + static_cast<uint32_t>(lane) * 32u + 16u, v[4], v[5], v[6], v[7]);
+                __syncwarp();
 #pragma unroll
                 for (int s = 0; s < 4; ++s)
 #pragma unroll
-                    for (int k = 0; k < 16; ++k) bfrag[s][k] = 0u;
-                const int lane_steps = p.block >> 3;  // lanes per WHT block
-                uint4 xn = x0;
-                if (!have_x0 && c_ok) xn = __ldg(reinterpret_cast<const uint4*>(p.x + cl));
-                for (int n = 0; n < p.batch; ++n) {
-                    const uint4 xc = xn;
-                    if (n + 1 < p.batch && c_ok)
-                        xn = __ldg(reinterpret_cast<const uint4*>(p.x + static_cast<size_t>(n + 1) * p.in + cl));
-                    const uint32_t xw[4] = {xc.x, xc.y, xc.z, xc.w};
-                    float v[8];
-#pragma unroll
-                    for (int j = 0; j < 4; ++j) {
-                        const __half2 h2 = *reinterpret_cast<const __half2*>(&xw[j]);
-                        const float lo = __low2float(h2), hi = __high2float(h2);
-                        v[2 * j] = (neg >> (2 * j)) & 1u ? -lo : lo;
-                        v[2 * j + 1] = (neg >> (2 * j + 1)) & 1u ? -hi : hi;
-                    }
-#pragma unroll
-                    for (int h = 1; h < 8; h <<= 1)
-#pragma unroll
-                        for (int i = 0; i < 8; i += 2 * h)
-#pragma unroll
-                            for (int j = i; j < i + h; ++j) {
-                                const float a = v[j], b = v[j + h];
-                                v[j] = __fadd_rn(a, b);
-                                v[j + h] = __fsub_rn(a, b);
-                            }
-                    for (int m = 1; m < lane_steps; m <<= 1) {
-                        const bool upper = (lane & m) != 0;
-#pragma unroll
-                        for (int j = 0; j < 8; ++j) {
-                            const float o = __shfl_xor_sync(0xffffffffu, v[j], m);
-                            v[j] = upper ? __fsub_rn(o, v[j]) : __fadd_rn(v[j], o);
-                        }
-                    }
-#pragma unroll
-                    for (int j = 0; j < 8; ++j) v[j] = to_tf32(v[j] * p.inv_sqrt_block);
-                    sts_v4(strip_addr + static_cast<uint32_t>(lane) * 32u, v[0], v[1], v[2], v[3]);
-                    sts_v4(strip_addr + static_cast<uint32_t>(lane) * 32u + 16u, v[4], v[5], v[6], v[7]);
-                    __syncwarp();
-                    if (g == n) {
-#pragma unroll
-                        for (int s = 0; s < 4; ++s)
-#pragma unroll
-                            for (int k = 0; k < 16; k += 4)
-                                asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
-                                             : "=r"(bfrag[s][k]), "=r"(bfrag[s][k + 1]), "=r"(bfrag[s][k + 2]), "=r"(bfrag[s][k + 3])
-                                             : "r"(strip_addr + static_cast<uint32_t>(64 * s + 16 * q + k) * 4u));
-                    }
-                    __syncwarp();
-                }
+                    for (int k = 0; k < 16; k += 4)
+                        asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
+                                     : "=r"(bfrag[s][k]), "=r"(bfrag[s][k + 1]), "=r"(bfrag[s][k + 2]), "=r"(bfrag[s][k + 3])
+                                     : "r"(strip_addr + static_cast<uint32_t>(64 * s + 16 * q + k) * 4u));
+                __syncwarp();
             } else {
             const float* xr = p.xrot + (static_cast<size_t>(plane) * p.batch + g) * p.in + col0;
             const bool have_row = g < p.batch;
@@ -783,10 +779,7 @@ __device__ __forceinline__ void gemv_body(const GemvArgs& p, const ScatterArgs& 
         if constexpr (LL) if (own_rows) {
             __syncthreads();   // this CTA's stores are ordered before the loads below (read back through L2)
             const int per_row = p.out / 4;
-            const int n_units_all = p.n_row_units * p.n_slots;
-            const int ub = static_cast<int>(static_cast<long>(n_units_all) * blockIdx.x / gridDim.x);
-            const int ue = static_cast<int>(static_cast<long>(n_units_all) * (blockIdx.x + 1) / gridDim.x);
-            ll_send_packets(sargs, p.y, per_row, p.batch, ub * p.tpu * 4, min(per_row, ue * p.tpu * 4));
+            ll_send_packets(sargs, p.y, per_row, p.batch, u_begin * p.tpu * 4, min(per_row, (u_begin + n_local) * p.tpu * 4));
         }
         // results that went to other GPUs need a system-scope fence; with the bulk copy every CTA's
         // results are local and only the copying CTA pays for one
