@@ -872,10 +872,22 @@ def bench_decoder_layer(tq, L, device, stream, cbs, args):
         peak_tf = float(json.load(open(pth)).get("bf16_tflops", 0)) or None
     peak_tf = peak_tf or 1590.0
 
-    def time_pass(lins, xs, ys, batch, reps):
+    def time_pass(lins, xs, ys, batch, reps, groups=None):
+        """groups: lists of layer indices that share their input and go out as one tq_linear_forward_group launch."""
+        calls = []
+        for grp in (groups or [[i] for i in range(len(lins))]):
+            if len(grp) == 1:
+                calls.append((lins[grp[0]].handle, xs[grp[0]], ys[grp[0]]))
+            else:
+                calls.append(((C.c_void_p * len(grp))(*[lins[i].handle for i in grp]), xs[grp[0]],
+                              (C.c_void_p * len(grp))(*[ys[i].data_ptr() for i in grp]), len(grp)))
+
         def one_pass():
-            for lin, x, y in zip(lins, xs, ys):
-                rc = L.tq_linear_forward(lin.handle, C.c_void_p(x.data_ptr()), tq.TQ_F16, batch, C.c_void_p(y.data_ptr()), sp)
+            for c in calls:
+                if len(c) == 3:
+                    rc = L.tq_linear_forward(c[0], C.c_void_p(c[1].data_ptr()), tq.TQ_F16, batch, C.c_void_p(c[2].data_ptr()), sp)
+                else:
+                    rc = L.tq_linear_forward_group(c[0], c[3], C.c_void_p(c[1].data_ptr()), batch, c[2], sp)
                 if rc:
                     raise RuntimeError(L.tq_last_error().decode())
         torch.cuda.synchronize()
@@ -909,6 +921,16 @@ def bench_decoder_layer(tq, L, device, stream, cbs, args):
             us = time_pass(lins, xs, ys, batch, 10)
             res[f"{tag}b{batch}"] = {"us_per_layer": us, "tok_per_s": batch / (us * 1e-6), "code_gb_per_s": code_bytes / (us * 1e-6) / 1e9,
                                      "launches_per_layer": len(shp) if batch <= 8 else None}
+            if tag == "" and batch <= 8:
+                # the same seven separately quantised matrices, q / k / v and gate / up each as ONE grouped launch
+                grouped = [[0, 1, 2], [3], [4, 5], [6]]
+                us = time_pass(lins, xs, ys, batch, 10, groups=grouped)
+                same = True
+                for gi in (0, 1, 2, 4, 5):
+                    want = lins[gi].forward(xs[0] if gi < 3 else xs[4])
+                    same = same and bool(torch.equal(want, ys[gi]))
+                res[f"grouped_b{batch}"] = {"us_per_layer": us, "tok_per_s": batch / (us * 1e-6), "code_gb_per_s": code_bytes / (us * 1e-6) / 1e9,
+                                            "launches_per_layer": len(grouped), "bit_equal_to_separate_calls": same}
         if tag == "":
             # the widest dot products of the layer (down_proj, K = 18944): result against fp32 matmul over
             # this library's own dequantised weights (which the parity tests hold bit-equal to the reference's)

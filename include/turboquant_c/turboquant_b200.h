@@ -225,6 +225,15 @@ int tq_linear_dequantize(tq_linear_t lin, void* result, int result_dtype, void* 
 int tq_linear_forward_scatter(tq_linear_t lin, const void* x_fp16_device, int batch, void* const* dst, int n_dst,
                               long dst_row_stride, long row_offset, void* stream);
 
+/** Several layers that multiply the same activation (q / k / v, gate / up: 1..4 handles with the same
+ *  in_features and rotation mode, 1..8 activation rows, x and every y[i] device fp16) in ONE kernel launch:
+ *  y[i] = [batch, out_features of layer i], each bit-equal to tq_linear_forward on that layer alone.
+ *  The SMs are divided among the layers in proportion to their sizes, so a decode step's small
+ *  projections pay the launch and the kernel's set-up once.  Stands in for consecutive calls of the
+ *  reference's forward (src/linear.cpp:19-28) on the same input. */
+int tq_linear_forward_group(const tq_linear_t* lins, int n, const void* x_fp16_device, int batch, void* const* y_fp16_device,
+                            void* stream);
+
 /** Forward whose fp16 result is this layer's rows inside a wider buffer: activation row n goes to
  *  y_fp16_device[n * y_row_stride ...] (y_row_stride >= out_features, in elements).  x and y are
  *  device pointers; any batch size (decode kernel up to 8 rows, tensor-memory kernel above).  A

@@ -200,6 +200,66 @@ def test_linear_chunked_columns_match_oracle(tq, oracle, cols, shared):
     lin.close()
 
 
+def test_linear_pinned_host_activation_is_read_fresh(tq, oracle):
+    """x and y in page-locked host memory (the decode loop's end-to-end call; up to 8 rows are stored by the kernel
+    straight into the host buffer).  The same buffers are refilled between calls and every call must see the new
+    contents: results bit-equal to the device-pointer call on the same values, for 1 and 5 rows."""
+    import torch
+    rng = np.random.default_rng(77)
+    rows, cols, bs = 272, 1024, 128
+    cb = oracle.codebook(4)[0]
+    w = (rng.standard_normal((rows, cols)) * 0.02).astype(np.float16).astype(np.float32)
+    pp, pr, norms, seeds = oracle.quantize_weight(w, cb, cb, 4, 4, bs, True)
+    lin = tq.TurboQuantLinear(cols, rows, tq.QuantizedWeight(pp, pr, norms, seeds), tq.codebook_from_centroids(cb),
+                              tq.codebook_from_centroids(cb), bs)
+    for batch in (1, 5):
+        xh = torch.empty((batch, cols), dtype=torch.float16).pin_memory()
+        yh = torch.empty((batch, rows), dtype=torch.float16).pin_memory()
+        for rep in range(4):
+            vals = torch.from_numpy(rng.standard_normal((batch, cols)).astype(np.float16))
+            xh.copy_(vals)
+            yh.fill_(0)
+            lin.forward(xh, out=yh)
+            want = lin.forward(vals.cuda())
+            torch.cuda.synchronize()
+            assert torch.equal(yh, want.cpu()), (batch, rep)
+    lin.check_status()
+    lin.close()
+
+
+@pytest.mark.parametrize("cols,shared", [(1024, True), (5120, True), (768, False), (8192, True)])
+def test_forward_group_equals_separate_forwards(tq, oracle, cols, shared):
+    """tq_linear_forward_group: three layers of different heights (ragged, one smaller than a row tile) with their
+    own seeds and norms on one activation in one launch, 1 / 3 / 8 rows, one and several column chunks, shared and
+    dual rotation: every result bit-equal to the layer's own forward, and within tolerance of the oracle."""
+    import torch
+    rng = np.random.default_rng(cols)
+    bs = 128
+    cb = oracle.codebook(4)[0]
+    lins, deqs = [], []
+    for rows in (272, 9, 130):
+        w = (rng.standard_normal((rows, cols)) * 0.02).astype(np.float16).astype(np.float32)
+        pp, pr, norms, seeds = oracle.quantize_weight(w, cb, cb, 4, 4, bs, shared)   # seeds follow the shape: one set per layer
+        lins.append(tq.TurboQuantLinear(cols, rows, tq.QuantizedWeight(pp, pr, norms, seeds), tq.codebook_from_centroids(cb),
+                                        tq.codebook_from_centroids(cb), bs))
+        deq = oracle.dequantize_weight(pp, pr, norms, seeds, cb, cb, bs).astype(np.float64)
+        deqs.append(deq)
+    for batch in (1, 3, 8):
+        x = torch.from_numpy(rng.standard_normal((batch, cols)).astype(np.float16)).cuda()
+        got = tq.forward_group(lins, x)
+        torch.cuda.synchronize()
+        for lin, y, deq in zip(lins, got, deqs):
+            want = lin.forward(x)
+            assert torch.equal(y, want), (cols, batch, lin.out_features_)
+            assert rel_l2(y.cpu().numpy(), x.cpu().numpy().astype(np.float64) @ deq.T) < LINEAR_TOL
+        again = tq.forward_group(lins, x)
+        for y, z in zip(got, again):
+            assert torch.equal(y, z)
+    for lin in lins:
+        lin.check_status()
+        lin.close()
+
+
 def test_linear_device_tensors_and_stream(tq, oracle):
     torch = pytest.importorskip("torch")
     rng = np.random.default_rng(2)

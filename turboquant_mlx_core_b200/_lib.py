@@ -76,6 +76,7 @@ def load() -> C.CDLL:
     sig("tq_linear_forward_noalloc", i, [vp, vp, i, vp, vp])
     sig("tq_linear_forward_strided", i, [vp, vp, i, vp, C.c_long, vp])
     sig("tq_linear_noalloc_scratch_limit", C.c_size_t, [])
+    sig("tq_linear_forward_group", i, [C.POINTER(C.c_void_p), i, vp, i, C.POINTER(C.c_void_p), vp])
     sig("tq_linear_dequantize", i, [vp, vp, i, vp])
     sig("tq_linear_status", i, [vp])
     sig("tq_linear_forward_scatter", i, [vp, vp, i, C.POINTER(C.c_void_p), i, C.c_long, C.c_long, vp])

@@ -347,6 +347,22 @@ class TurboQuantLinear:
             pass
 
 
+def forward_group(linears, x, outs=None, stream=None):
+    """Several TurboQuantLinear layers on the same device activation x ([batch <= 8, in] fp16 torch tensor) in one
+    kernel launch (tq_linear_forward_group): returns the list of fp16 [batch, out_i] results, each bit-equal to
+    linears[i].forward(x).  The layers must share in_features and the rotation mode (q / k / v, gate / up)."""
+    import torch
+    if not linears or len(linears) > 4:
+        raise ValueError("forward_group takes 1..4 layers")
+    batch = int(np.prod(x.shape[:-1])) if len(x.shape) > 1 else 1
+    if outs is None:
+        outs = [torch.empty((batch, lin.out_features_), dtype=torch.float16, device=x.device) for lin in linears]
+    hs = (C.c_void_p * len(linears))(*[lin._h for lin in linears])
+    ys = (C.c_void_p * len(linears))(*[o.data_ptr() for o in outs])
+    check(linears[0]._L.tq_linear_forward_group(hs, len(linears), _ptr(x), batch, ys, _stream_ptr(stream)), "forward_group")
+    return outs
+
+
 def dequantize_weight(qw: QuantizedWeight, primary_codebook: Codebook, residual_codebook: Codebook, block_size: int,
                       dtype=np.float32):
     """dequantize_weight_cpu / _gpu (include/turboquant/dequantizer.h:11-22) -> [out, in]."""

@@ -202,6 +202,19 @@ public:
                                     sm_count_, st, signal ? sig : nullptr, signal_slot, signal_value, counter_.as<unsigned int>());
     }
 
+    // This layer as one matrix of a grouped decode launch (see tq_linear_forward_group).
+    tq::GemvGroupItem group_item(void* y) const {
+        tq::GemvGroupItem it{};
+        it.codes = codes_.as<uint8_t>(); it.norms = norms_.as<float>(); it.table = tables_.as<float>();
+        it.y = static_cast<__half*>(y);
+        it.out = out_; it.in = in_; it.block = block_; it.n_planes = dual_ ? 2 : 1;
+        it.seed_p = seed_p_; it.seed_r = seed_r_;
+        it.scratch = scratch_.as<void>(); it.status = d_status_;
+        return it;
+    }
+    int device() const { return device_; }
+    int sm_count() const { return sm_count_; }
+
     // Device fp16 in, device fp16 out whose activation rows are y_stride elements apart (this layer's
     // rows inside a wider buffer, e.g. a rank's shard of the full logits).
     void forward_strided(const void* x, int batch, void* y, long y_stride, cudaStream_t st) {
@@ -452,6 +465,30 @@ int tq_linear_forward_strided(tq_linear_t lin, const void* x_fp16_device, int ba
     return guarded<int>(0, -1, [&]() {
         TQ_REQUIRE(lin && lin->impl, "tq_linear_forward_strided: NULL handle");
         lin->impl->forward_strided(x_fp16_device, batch, y_fp16_device, y_row_stride, static_cast<cudaStream_t>(stream));
+        return 0;
+    });
+}
+
+int tq_linear_forward_group(const tq_linear_t* lins, int n, const void* x_fp16_device, int batch, void* const* y_fp16_device,
+                            void* stream) {
+    return guarded<int>(0, -1, [&]() {
+        TQ_REQUIRE(lins && y_fp16_device && x_fp16_device, "tq_linear_forward_group: NULL argument");
+        TQ_REQUIRE(n >= 1 && n <= 4, "tq_linear_forward_group: 1..4 layers");
+        TQ_REQUIRE(batch >= 1 && batch <= 8, "tq_linear_forward_group: batch must be 1..8");
+        TQ_REQUIRE(tq::is_device_pointer(x_fp16_device), "tq_linear_forward_group: x must be a device pointer");
+        tq::GemvGroupItem items[4];
+        for (int i = 0; i < n; ++i) {
+            TQ_REQUIRE(lins[i] && lins[i]->impl, "tq_linear_forward_group: NULL handle");
+            TQ_REQUIRE(y_fp16_device[i] && tq::is_device_pointer(y_fp16_device[i]), "tq_linear_forward_group: y must be device pointers");
+            TQ_REQUIRE(lins[i]->impl->device() == lins[0]->impl->device(), "tq_linear_forward_group: layers on different devices");
+            TQ_REQUIRE(lins[i]->impl->in_features() == lins[0]->impl->in_features() &&
+                       lins[i]->impl->shared_rotation() == lins[0]->impl->shared_rotation(),
+                       "tq_linear_forward_group: the layers must share in_features and the rotation mode");
+            items[i] = lins[i]->impl->group_item(y_fp16_device[i]);
+        }
+        TQ_CUDA(cudaSetDevice(lins[0]->impl->device()));
+        tq::launch_tq8_gemv_group(items, n, static_cast<const __half*>(x_fp16_device), batch, lins[0]->impl->sm_count(),
+                                  static_cast<cudaStream_t>(stream));
         return 0;
     });
 }

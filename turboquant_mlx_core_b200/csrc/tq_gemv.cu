@@ -314,7 +314,7 @@ __device__ __forceinline__ void ll_send_packets(const ScatterArgs& sc, const __h
 // MULTI = more than one slot (row units finished through partial sums in scratch); compile time, so that the
 // single-slot kernels carry none of that path's state in their 128 registers.
 template <int BP, bool SCATTER, bool LL, bool MULTI>
-__device__ __forceinline__ void gemv_body(const GemvArgs& p, const ScatterArgs& sargs) {
+__device__ __forceinline__ void gemv_body(const GemvArgs& p, const ScatterArgs& sargs, const int bid, const int nblk) {
     // columns per chunk, derived here: one more field in GemvArgs made ptxas spill within the 128 registers
     const int chunk_cols = p.wpt * kSlice;
     // A warp's partial tile is [16 rows][BP] floats plus 4 floats of padding: the 16 tiles a
@@ -337,8 +337,7 @@ __device__ __forceinline__ void gemv_body(const GemvArgs& p, const ScatterArgs& 
     // (the first `rem` CTAs take one unit more; one 32-bit division - the prologue runs once per launch on
     // instructions that are not cached yet, and cannot overlap the preceding kernel, whose CTA fills this SM)
     const int n_units = p.n_row_units * p.n_slots;
-    const int u_quot = n_units / static_cast<int>(gridDim.x), u_rem = n_units - u_quot * static_cast<int>(gridDim.x);
-    const int bid = static_cast<int>(blockIdx.x);
+    const int u_quot = n_units / nblk, u_rem = n_units - u_quot * nblk;   // bid of nblk CTAs work on this matrix
     const int u_begin = u_quot * bid + (bid < u_rem ? bid : u_rem);
     const int n_local = u_quot + (bid < u_rem ? 1 : 0);
     if (n_local <= 0) return;
@@ -786,7 +785,7 @@ __device__ __forceinline__ void gemv_body(const GemvArgs& p, const ScatterArgs& 
         __syncthreads();
         if (tid == 0) {
             const unsigned int prev = atomicAdd(sargs.done_counter, 1u);
-            s_last = (prev == gridDim.x - 1) ? 1u : 0u;
+            s_last = (prev == static_cast<unsigned int>(nblk) - 1u) ? 1u : 0u;
         }
         __syncthreads();
         if (LL && s_last) {
@@ -845,15 +844,32 @@ __device__ __forceinline__ void gemv_body(const GemvArgs& p, const ScatterArgs& 
 
 template <int BP, bool MULTI>
 __global__ void __launch_bounds__(kCtaThreads, 1) tq8_gemv_kernel(const GemvArgs p) {
-    gemv_body<BP, false, false, MULTI>(p, ScatterArgs{});
+    gemv_body<BP, false, false, MULTI>(p, ScatterArgs{}, static_cast<int>(blockIdx.x), static_cast<int>(gridDim.x));
 }
 template <int BP, bool MULTI>
 __global__ void __launch_bounds__(kCtaThreads, 1) tq8_gemv_packets_kernel(const GemvArgs p, const ScatterArgs sc) {
-    gemv_body<BP, true, true, MULTI>(p, sc);
+    gemv_body<BP, true, true, MULTI>(p, sc, static_cast<int>(blockIdx.x), static_cast<int>(gridDim.x));
 }
 template <int BP, bool MULTI>
 __global__ void __launch_bounds__(kCtaThreads, 1) tq8_gemv_scatter_kernel(const GemvArgs p, const ScatterArgs sc) {
-    gemv_body<BP, true, false, MULTI>(p, sc);
+    gemv_body<BP, true, false, MULTI>(p, sc, static_cast<int>(blockIdx.x), static_cast<int>(gridDim.x));
+}
+
+// Several matrices that multiply the same activation (q / k / v, gate / up) in one launch: the grid is cut into one
+// range of CTAs per matrix, in proportion to the matrices' units, and every CTA runs the ordinary body on its matrix
+// with its index inside the range.  A decode layer's small projections then pay the launch and the prologue once.
+constexpr int kMaxGroup = 4;
+struct GemvGroupArgs {
+    GemvArgs m[kMaxGroup];
+    int cta_start[kMaxGroup + 1];   // CTAs cta_start[i] .. cta_start[i + 1] - 1 work on matrix i
+    int n;
+};
+template <int BP, bool MULTI>
+__global__ void __launch_bounds__(kCtaThreads, 1) tq8_gemv_group_kernel(const __grid_constant__ GemvGroupArgs grp) {
+    const int b = static_cast<int>(blockIdx.x);
+    int i = 0;
+    while (i + 1 < grp.n && b >= grp.cta_start[i + 1]) ++i;
+    gemv_body<BP, false, false, MULTI>(grp.m[i], ScatterArgs{}, b - grp.cta_start[i], grp.cta_start[i + 1] - grp.cta_start[i]);
 }
 
 // Waits (bounded) until flags[0..n) have all reached `value`: the receiving side of the completion
@@ -909,6 +925,49 @@ size_t gemv_scratch_bytes(int out, int in, int n_planes) {
                  align256(static_cast<size_t>(n_row_tiles) * kWarps * sizeof(unsigned int));
     return bytes;
 }
+
+// Geometry, rotation mode and scratch pointers of one matrix (codes, norms, table, y and status are the caller's).
+// Returns whether the kernel rotates the activation itself; otherwise rotate_x_kernel fills a.xrot first.
+static bool fill_gemv_args(GemvArgs& a, const __half* x, int out, int in, int batch, uint32_t block, int n_planes, uint32_t seed_p,
+                           uint32_t seed_r, void* scratch) {
+    a.out = out; a.in = in; a.batch = batch;
+    const int n_row_tiles = (out + 15) / 16;
+    a.wpt = warps_per_tile(in);
+    a.tpu = kWarps / a.wpt;
+    const int chunk = a.wpt * kSlice;  // columns per chunk
+    a.n_chunks = (in + chunk - 1) / chunk;
+    a.n_slots = a.n_chunks * n_planes;
+    a.out_pad = n_row_tiles * 16;
+    a.n_row_units = (n_row_tiles + a.tpu - 1) / a.tpu;
+    a.inv_scale = 1.0f / std::sqrt(static_cast<float>(in));
+    // Blocks that fit a warp's 256-column slice are rotated inside the GEMV kernel (16-byte
+    // activation loads); larger blocks, or an unaligned activation, go through rotate_x_kernel.
+    // In-kernel rotation handles one activation row after the other (a chain of lane exchanges per row) in every
+    // warp, which costs more than the pre-kernel from two rows on (4096 x 4096: 9.0 / 11.3 / 15.3 us in-kernel
+    // against 8.3 / 9.2 / 10.8 us with the pre-kernel at 2 / 4 / 8 rows; the same at one row).
+    const bool fused_rotation = block <= static_cast<uint32_t>(kSlice) && in % 8 == 0 &&
+                                reinterpret_cast<uintptr_t>(x) % 16 == 0 && batch == 1;
+    a.x = fused_rotation ? x : nullptr;
+    a.seed_p = seed_p; a.seed_r = seed_r;
+    a.block = static_cast<int>(block);
+    a.inv_sqrt_block = 1.0f / std::sqrt(static_cast<float>(block));
+    uint8_t* sp = static_cast<uint8_t*>(scratch);
+    float* xrot = reinterpret_cast<float*>(sp);
+    a.xrot = xrot;
+    if (a.n_slots > 1) {
+        sp += align256(static_cast<size_t>(n_planes) * 8 * in * sizeof(float));
+        a.partial = reinterpret_cast<float*>(sp);
+        sp += align256(static_cast<size_t>(a.n_slots) * 8 * a.out_pad * sizeof(float));
+        a.counters = reinterpret_cast<unsigned int*>(sp);
+    }
+
+    return fused_rotation;
+}
+
+// Shared-memory opt-in of every instantiation, once per device.
+static void configure_gemv_kernels();
+static void launch_rotate_x_pdl(const __half* x, float* xrot, int in, int batch, uint32_t block, int n_planes, uint32_t seed_p,
+                                uint32_t seed_r, cudaStream_t stream);
 
 void launch_tq8_gemv(const uint8_t* codes, const float* norms, const float* table, const __half* x, __half* y,
                      int out, int in, int batch, uint32_t block, int n_planes, uint32_t seed_p, uint32_t seed_r,
@@ -987,59 +1046,11 @@ void launch_tq8_gemv_scatter(const uint8_t* codes, const float* norms, const flo
         sa.n_wait = gather->n_wait;
         sa.wait_epoch = gather->wait_epoch;
     }
-    a.out = out; a.in = in; a.batch = batch;
-    const int n_row_tiles = (out + 15) / 16;
-    a.wpt = warps_per_tile(in);
-    a.tpu = kWarps / a.wpt;
-    const int chunk = a.wpt * kSlice;  // columns per chunk
-    a.n_chunks = (in + chunk - 1) / chunk;
-    a.n_slots = a.n_chunks * n_planes;
-    a.out_pad = n_row_tiles * 16;
-    a.n_row_units = (n_row_tiles + a.tpu - 1) / a.tpu;
+    const bool fused_rotation = fill_gemv_args(a, x, out, in, batch, block, n_planes, seed_p, seed_r, scratch);
+    float* xrot = const_cast<float*>(a.xrot);
     const int bp = batch <= 1 ? 1 : (batch <= 2 ? 2 : (batch <= 4 ? 4 : 8));
-    a.inv_scale = 1.0f / std::sqrt(static_cast<float>(in));
-    // Blocks that fit a warp's 256-column slice are rotated inside the GEMV kernel (16-byte
-    // activation loads); larger blocks, or an unaligned activation, go through rotate_x_kernel.
-    // In-kernel rotation handles one activation row after the other (a chain of lane exchanges per row) in every
-    // warp, which costs more than the pre-kernel from two rows on (4096 x 4096: 9.0 / 11.3 / 15.3 us in-kernel
-    // against 8.3 / 9.2 / 10.8 us with the pre-kernel at 2 / 4 / 8 rows; the same at one row).
-    const bool fused_rotation = block <= static_cast<uint32_t>(kSlice) && in % 8 == 0 &&
-                                reinterpret_cast<uintptr_t>(x) % 16 == 0 && batch == 1;
-    a.x = fused_rotation ? x : nullptr;
-    a.seed_p = seed_p; a.seed_r = seed_r;
-    a.block = static_cast<int>(block);
-    a.inv_sqrt_block = 1.0f / std::sqrt(static_cast<float>(block));
-    uint8_t* sp = static_cast<uint8_t*>(scratch);
-    float* xrot = reinterpret_cast<float*>(sp);
-    a.xrot = xrot;
-    if (a.n_slots > 1) {
-        sp += align256(static_cast<size_t>(n_planes) * 8 * in * sizeof(float));
-        a.partial = reinterpret_cast<float*>(sp);
-        sp += align256(static_cast<size_t>(a.n_slots) * 8 * a.out_pad * sizeof(float));
-        a.counters = reinterpret_cast<unsigned int*>(sp);
-    }
 
-    // the opt-in shared-memory size is a per-device function attribute
-    static bool configured[64] = {false};
-    int dev = 0;
-    TQ_CUDA(cudaGetDevice(&dev));
-    if (dev >= 64 || !configured[dev]) {
-#define TQ_GEMV_ATTR1(K) TQ_CUDA(cudaFuncSetAttribute(K, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kGemvSmem)));
-#define TQ_GEMV_ATTR(BPV)                                \
-    TQ_GEMV_ATTR1((tq8_gemv_kernel<BPV, false>))         \
-    TQ_GEMV_ATTR1((tq8_gemv_kernel<BPV, true>))          \
-    TQ_GEMV_ATTR1((tq8_gemv_scatter_kernel<BPV, false>)) \
-    TQ_GEMV_ATTR1((tq8_gemv_scatter_kernel<BPV, true>))  \
-    TQ_GEMV_ATTR1((tq8_gemv_packets_kernel<BPV, false>)) \
-    TQ_GEMV_ATTR1((tq8_gemv_packets_kernel<BPV, true>))
-        TQ_GEMV_ATTR(1)
-        TQ_GEMV_ATTR(2)
-        TQ_GEMV_ATTR(4)
-        TQ_GEMV_ATTR(8)
-#undef TQ_GEMV_ATTR
-#undef TQ_GEMV_ATTR1
-        if (dev < 64) configured[dev] = true;
-    }
+    configure_gemv_kernels();
 
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
@@ -1047,25 +1058,7 @@ void launch_tq8_gemv_scatter(const uint8_t* codes, const float* norms, const flo
     const int n_attr = 1;
 
     // 1. rotate the activation (one warp per plane x row x block)
-    if (!fused_rotation) {
-        const float inv_sqrt = 1.0f / std::sqrt(static_cast<float>(block));
-        const int n_warps = n_planes * batch * (in / static_cast<int>(block));
-        cudaLaunchConfig_t cfg{};
-        cfg.gridDim = dim3((n_warps + 3) / 4);
-        cfg.blockDim = dim3(128);
-        cfg.stream = stream;
-        cfg.attrs = attr;
-        cfg.numAttrs = n_attr;
-#define TQ_ROT_CASE(EV)                                                                                            \
-    case 32 * EV:                                                                                                  \
-        TQ_CUDA(cudaLaunchKernelEx(&cfg, rotate_x_kernel<EV>, x, xrot, in, batch, n_planes, seed_p, seed_r, inv_sqrt)); \
-        break;
-        switch (block) {
-            TQ_ROT_CASE(1) TQ_ROT_CASE(2) TQ_ROT_CASE(4) TQ_ROT_CASE(8) TQ_ROT_CASE(16) TQ_ROT_CASE(32)
-            default: throw Error("unsupported WHT block size");
-        }
-#undef TQ_ROT_CASE
-    }
+    if (!fused_rotation) launch_rotate_x_pdl(x, xrot, in, batch, block, n_planes, seed_p, seed_r, stream);
     // 2. the GEMV itself
     {
         const int n_units = a.n_row_units * a.n_slots;
@@ -1094,6 +1087,129 @@ void launch_tq8_gemv_scatter(const uint8_t* codes, const float* norms, const flo
 #undef TQ_GEMV_LAUNCH
 #undef TQ_GEMV_LAUNCH2
     }
+}
+
+static void configure_gemv_kernels() {
+    // the opt-in shared-memory size is a per-device function attribute
+    static bool configured[64] = {false};
+    int dev = 0;
+    TQ_CUDA(cudaGetDevice(&dev));
+    if (dev < 64 && configured[dev]) return;
+#define TQ_GEMV_ATTR1(K) TQ_CUDA(cudaFuncSetAttribute(K, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kGemvSmem)));
+#define TQ_GEMV_ATTR(BPV)                                \
+    TQ_GEMV_ATTR1((tq8_gemv_kernel<BPV, false>))         \
+    TQ_GEMV_ATTR1((tq8_gemv_kernel<BPV, true>))          \
+    TQ_GEMV_ATTR1((tq8_gemv_scatter_kernel<BPV, false>)) \
+    TQ_GEMV_ATTR1((tq8_gemv_scatter_kernel<BPV, true>))  \
+    TQ_GEMV_ATTR1((tq8_gemv_packets_kernel<BPV, false>)) \
+    TQ_GEMV_ATTR1((tq8_gemv_packets_kernel<BPV, true>))  \
+    TQ_GEMV_ATTR1((tq8_gemv_group_kernel<BPV, false>))   \
+    TQ_GEMV_ATTR1((tq8_gemv_group_kernel<BPV, true>))
+    TQ_GEMV_ATTR(1)
+    TQ_GEMV_ATTR(2)
+    TQ_GEMV_ATTR(4)
+    TQ_GEMV_ATTR(8)
+#undef TQ_GEMV_ATTR
+#undef TQ_GEMV_ATTR1
+    if (dev < 64) configured[dev] = true;
+}
+
+static void launch_rotate_x_pdl(const __half* x, float* xrot, int in, int batch, uint32_t block, int n_planes, uint32_t seed_p,
+                                uint32_t seed_r, cudaStream_t stream) {
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    const float inv_sqrt = 1.0f / std::sqrt(static_cast<float>(block));
+    const int n_warps = n_planes * batch * (in / static_cast<int>(block));
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3((n_warps + 3) / 4);
+    cfg.blockDim = dim3(128);
+    cfg.stream = stream;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+#define TQ_ROT_CASE(EV)                                                                                            \
+    case 32 * EV:                                                                                                  \
+        TQ_CUDA(cudaLaunchKernelEx(&cfg, rotate_x_kernel<EV>, x, xrot, in, batch, n_planes, seed_p, seed_r, inv_sqrt)); \
+        break;
+    switch (block) {
+        TQ_ROT_CASE(1) TQ_ROT_CASE(2) TQ_ROT_CASE(4) TQ_ROT_CASE(8) TQ_ROT_CASE(16) TQ_ROT_CASE(32)
+        default: throw Error("unsupported WHT block size");
+    }
+#undef TQ_ROT_CASE
+}
+
+void launch_tq8_gemv_group(const GemvGroupItem* items, int n, const __half* x, int batch, int sm_count, cudaStream_t stream) {
+    TQ_REQUIRE(items != nullptr && n >= 1 && n <= kMaxGroup, "tq8_gemv group: 1..4 matrices");
+    TQ_REQUIRE(x != nullptr && batch >= 1 && batch <= 8, "tq8_gemv group: 1..8 activation rows");
+    GemvGroupArgs grp{};
+    grp.n = n;
+    int units[kMaxGroup], total_units = 0;
+    bool fused[kMaxGroup];
+    for (int i = 0; i < n; ++i) {
+        const GemvGroupItem& it = items[i];
+        TQ_REQUIRE(it.codes && it.norms && it.table && it.y && it.scratch, "tq8_gemv group: NULL argument");
+        TQ_REQUIRE(it.out >= 1 && it.in == items[0].in && it.n_planes == items[0].n_planes,
+                   "tq8_gemv group: the matrices must share in_features and the rotation mode");
+        TQ_REQUIRE(it.n_planes == 1 || it.n_planes == 2, "n_planes must be 1 or 2");
+        TQ_REQUIRE(is_pow2(it.block) && it.block >= 32 && it.block <= 1024, "WHT block size must be a power of two in [32, 1024]");
+        TQ_REQUIRE(it.in % static_cast<int>(it.block) == 0, "in_features must be divisible by block_size");
+        GemvArgs& a = grp.m[i];
+        a.codes = it.codes; a.norms = it.norms; a.table = it.table; a.y = it.y; a.status = it.status;
+        fused[i] = fill_gemv_args(a, x, it.out, it.in, batch, it.block, it.n_planes, it.seed_p, it.seed_r, it.scratch);
+        units[i] = a.n_row_units * a.n_slots;
+        total_units += units[i];
+    }
+    // CTAs in proportion to the units, at least one per matrix, never more than a matrix has units
+    const int total = total_units < sm_count ? total_units : sm_count;
+    TQ_REQUIRE(total >= n, "tq8_gemv group: fewer SMs than matrices");
+    int ctas[kMaxGroup], given = 0;
+    for (int i = 0; i < n; ++i) {
+        long c = static_cast<long>(total) * units[i] / total_units;
+        ctas[i] = static_cast<int>(c < 1 ? 1 : (c > units[i] ? units[i] : c));
+        given += ctas[i];
+    }
+    while (given > total) {   // the minimum of one pushed the sum over: take from the largest
+        int big = 0;
+        for (int i = 1; i < n; ++i) if (ctas[i] > ctas[big]) big = i;
+        --ctas[big]; --given;
+    }
+    while (given < total) {   // rounding left CTAs over: to the matrix with the most units per CTA that can still use one
+        int best = -1;
+        for (int i = 0; i < n; ++i)
+            if (ctas[i] < units[i] && (best < 0 || static_cast<long>(units[i]) * ctas[best] > static_cast<long>(units[best]) * ctas[i])) best = i;
+        if (best < 0) break;
+        ++ctas[best]; ++given;
+    }
+    grp.cta_start[0] = 0;
+    for (int i = 0; i < n; ++i) grp.cta_start[i + 1] = grp.cta_start[i] + ctas[i];
+    for (int i = n; i < kMaxGroup; ++i) grp.cta_start[i + 1] = grp.cta_start[n];
+    configure_gemv_kernels();
+    for (int i = 0; i < n; ++i)
+        if (!fused[i])
+            launch_rotate_x_pdl(x, const_cast<float*>(grp.m[i].xrot), items[i].in, batch, items[i].block, items[i].n_planes,
+                                items[i].seed_p, items[i].seed_r, stream);
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(grp.cta_start[n]);
+    cfg.blockDim = dim3(kCtaThreads);
+    cfg.dynamicSmemBytes = kGemvSmem;
+    cfg.stream = stream;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    const int bp = batch <= 1 ? 1 : (batch <= 2 ? 2 : (batch <= 4 ? 4 : 8));
+    const bool multi = grp.m[0].n_slots > 1;   // the same for all: same in_features and planes
+#define TQ_GROUP_LAUNCH(BPV)                                                              \
+    if (multi) TQ_CUDA(cudaLaunchKernelEx(&cfg, tq8_gemv_group_kernel<BPV, true>, grp)); \
+    else TQ_CUDA(cudaLaunchKernelEx(&cfg, tq8_gemv_group_kernel<BPV, false>, grp));
+    switch (bp) {
+        case 1: TQ_GROUP_LAUNCH(1) break;
+        case 2: TQ_GROUP_LAUNCH(2) break;
+        case 4: TQ_GROUP_LAUNCH(4) break;
+        default: TQ_GROUP_LAUNCH(8) break;
+    }
+#undef TQ_GROUP_LAUNCH
 }
 
 // The activation rotation alone (the pre-kernel of WHT blocks above 256 columns), for the other

@@ -60,6 +60,22 @@ void launch_tq8_gemv_scatter(const uint8_t* codes, const float* norms, const flo
                              int sm_count, cudaStream_t stream, unsigned int* const* signal = nullptr, int signal_slot = 0,
                              unsigned int signal_value = 0, unsigned int* done_counter = nullptr,
                              const GemvGather* gather = nullptr, int n_signal = 0);
+// Several matrices against the same activation (device fp16, 1..8 rows) in one launch: y of matrix i = its own
+// [batch, out_i] buffer.  The matrices share in_features and the rotation mode; each brings its own scratch
+// (gemv_scratch_bytes) and status word.
+struct GemvGroupItem {
+    const uint8_t* codes;
+    const float* norms;
+    const float* table;
+    __half* y;
+    int out, in;
+    uint32_t block;
+    int n_planes;
+    uint32_t seed_p, seed_r;
+    void* scratch;
+    unsigned int* status;
+};
+void launch_tq8_gemv_group(const GemvGroupItem* items, int n, const __half* x, int batch, int sm_count, cudaStream_t stream);
 // With `signal` (one flag array per destination): once the whole grid has stored its results,
 // signal[d][signal_slot] = signal_value on every destination (release, system scope); `done_counter`
 // must be a zero-initialised word in device memory (grid completion counter).  `status` may be
