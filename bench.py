@@ -1282,9 +1282,14 @@ def bench_c4_decode_step(tq, L, device, stream, rank, world, cbs, args):
             mark("start")
             chk(L.tq_rmsnorm_f16(C.c_void_p(x.data_ptr()), C.c_void_p(w["n1"].data_ptr()), C.c_void_p(h1.data_ptr()), batch, hidden, 1e-6, sp))
             mark("rmsnorm_1")
-            fwd(w["q"], h1.data_ptr(), batch, q.data_ptr())
-            fwd(w["k"], h1.data_ptr(), batch, k.data_ptr())
-            fwd(w["v"], h1.data_ptr(), batch, v.data_ptr())
+            if batch <= 8:
+                # q, k and v read the same activation: one grouped launch (bit-equal to the three calls)
+                chk(L.tq_linear_forward_group((C.c_void_p * 3)(w["q"], w["k"], w["v"]), 3, C.c_void_p(h1.data_ptr()), batch,
+                                              (C.c_void_p * 3)(q.data_ptr(), k.data_ptr(), v.data_ptr()), sp))
+            else:
+                fwd(w["q"], h1.data_ptr(), batch, q.data_ptr())
+                fwd(w["k"], h1.data_ptr(), batch, k.data_ptr())
+                fwd(w["v"], h1.data_ptr(), batch, v.data_ptr())
             mark("q_k_v")
             chk(L.tq_rope_f16(C.c_void_p(q.data_ptr()), C.c_void_p(pos.data_ptr()), batch, qh, dim, 1e6, sp))
             chk(L.tq_rope_f16(C.c_void_p(k.data_ptr()), C.c_void_p(pos.data_ptr()), batch, kvh, dim, 1e6, sp))
@@ -1379,8 +1384,8 @@ def bench_c4_decode_step(tq, L, device, stream, rank, world, cbs, args):
         res[f"b{batch}"] = {"us_per_layer": us, "tok_per_s_64_layers": batch / (us * 1e-6 * n_model_layers),
                             "gb_per_s_per_gpu": (weight_bytes + kv_bytes) / (us * 1e-6) / 1e9,
                             "bytes_per_layer_per_gpu": weight_bytes + kv_bytes, "distinct_layers_cycled": n_layers,
-                            "kernels_per_layer": "rmsnorm, q, k, v, rope x2, kv append x2, attention, o_proj, [copy to peers, wait,] "
-                                                 "sum + residual, rmsnorm, gate-up, swiglu, down, [copy to peers, wait,] sum + residual",
+                            "kernels_per_layer": "rmsnorm, q + k + v (one grouped launch up to 8 rows), rope x2, kv append x2, attention, o_proj, "
+                                                 "[copy to peers, wait,] sum + residual, rmsnorm, gate-up, swiglu, down, [copy to peers, wait,] sum + residual",
                             "all_reduce": ("none (one rank)" if exchange is None else
                                            "partials sent as packets from inside o_proj / down_proj, one kernel waits and adds" if use_packets
                                            else "tq_exchange_broadcast + tq_exchange_wait + tq_exchange_sum_f16"),
