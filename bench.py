@@ -42,7 +42,7 @@ OUT_F, IN_F, BLOCK = 4096, 4096, 128
 ALGO_BYTES = OUT_F * IN_F + 4 * OUT_F + 2 * IN_F + 2 * OUT_F   # codes + norms + x + y = 16 809 984
 PUBLISHED_TOK_S = 671.0   # reference README: 1.49 ms/token, Apple GPU, same shape, block 512
 # dram__bytes_read.sum + dram__bytes_write.sum of one tq8_gemv_kernel launch at this shape
-# (ncu capture summarised in profiles/tq8_gemv_kernel_4096x4096_b1.md): reads only, no DRAM writes.
+# (from an ncu capture of that launch): reads only, no DRAM writes.
 GEMV_DRAM_TRAFFIC = 16824704
 
 
