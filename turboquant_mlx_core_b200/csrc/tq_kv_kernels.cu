@@ -1333,6 +1333,10 @@ AttnPlan attn_make_plan(int n_seqs, int q_heads, int kv_heads, int head_dim, int
     }
     if (kernel == 3) kernel = 0;
     int gh = kernel == 1 ? 0 : attn_pipe_heads(head_dim, kv_heads);
+    // A CTA that takes only some of the KV heads copies its tiles token by token (the records of a token's heads are
+    // contiguous, a head group's are not): 32 x 8 heads x ctx 8192 then ran at 920 GB/s against 1610 GB/s for the
+    // load-based kernel, so the pipeline is chosen only when one CTA takes all the heads.
+    if (gh && kernel == 0 && gh != kv_heads) gh = 0;
     if (gh && kernel == 0) {
         const long slots = static_cast<long>(sm_count) * (kPipeWarpsPerSm / gh);
         const long ctas_at_512 = static_cast<long>(n_seqs) * (kv_heads / gh) * gchunks * (max_tok / 512);
