@@ -1247,27 +1247,40 @@ def bench_c4_decode_step(tq, L, device, stream, rank, world, cbs, args):
         if use_packets:
             pk_bufs = (C.c_void_p * world)(*[p + c4_packets_off for p in exchange.rank_ptrs()])
 
-        def all_reduce_add_packets(h, xin_ptr, residual, out):
+        def all_reduce_add_packets(h, xin_ptr, residual, out, norm_w=None):
             """The column-sharded linear h writes its partial locally and sends it as packets from inside its kernel; one more
-            kernel waits for the other ranks' packets and adds everything in rank order."""
+            kernel waits for the other ranks' packets and adds everything in rank order - and, with norm_w, writes the
+            RMSNorm of the summed rows to h1 as well (the next projection's input)."""
             chk(L.tq_linear_forward_allgather_packets(h, exchange._h, C.c_void_p(xin_ptr), batch, C.c_void_p(part.data_ptr()), hidden,
                                                       pk_bufs, 0, sp))
-            chk(L.tq_exchange_sum_packets(exchange._h, C.c_void_p(exchange.local + c4_packets_off), C.c_void_p(part.data_ptr()), count,
-                                          C.c_void_p(residual.data_ptr()), C.c_void_p(out.data_ptr()), sp))
+            if norm_w is None:
+                chk(L.tq_exchange_sum_packets(exchange._h, C.c_void_p(exchange.local + c4_packets_off), C.c_void_p(part.data_ptr()), count,
+                                              C.c_void_p(residual.data_ptr()), C.c_void_p(out.data_ptr()), sp))
+            else:
+                chk(L.tq_exchange_sum_packets_rmsnorm(exchange._h, C.c_void_p(exchange.local + c4_packets_off), C.c_void_p(part.data_ptr()),
+                                                      batch, hidden, C.c_void_p(residual.data_ptr()), C.c_void_p(out.data_ptr()),
+                                                      C.c_void_p(norm_w.data_ptr()), C.c_void_p(h1.data_ptr()), 1e-6, sp))
 
-        def all_reduce_add(partial_of, residual, out):
-            """partial_of(ptr) writes this rank's partial [batch, hidden] at ptr; out = residual + sum over ranks."""
+        def all_reduce_add(partial_of, residual, out, norm_w=None):
+            """partial_of(ptr) writes this rank's partial [batch, hidden] at ptr; out = residual + sum over ranks; with norm_w
+            the summing kernel also writes the RMSNorm of the summed rows to h1."""
             if exchange is None:
                 partial_of(part.data_ptr())
-                chk(L.tq_exchange_sum_f16(C.c_void_p(part.data_ptr()), 1, count, count, C.c_void_p(residual.data_ptr()),
+                slots_ptr, n_slots = part.data_ptr(), 1
+            else:
+                base = (toggle[0] & 1) * world * count * 2
+                toggle[0] += 1
+                partial_of(exchange.local + base + rank * count * 2)
+                exchange.broadcast(base + rank * count * 2, 1, count * 2, count * 2, stream=stream)
+                exchange.wait(stream=stream)
+                slots_ptr, n_slots = exchange.local + base, world
+            if norm_w is None:
+                chk(L.tq_exchange_sum_f16(C.c_void_p(slots_ptr), n_slots, count, count, C.c_void_p(residual.data_ptr()),
                                           C.c_void_p(out.data_ptr()), sp))
-                return
-            base = (toggle[0] & 1) * world * count * 2
-            toggle[0] += 1
-            partial_of(exchange.local + base + rank * count * 2)
-            exchange.broadcast(base + rank * count * 2, 1, count * 2, count * 2, stream=stream)
-            exchange.wait(stream=stream)
-            exchange.sum_f16(base, world, count, count, out.data_ptr(), residual_ptr=residual.data_ptr(), stream=stream)
+            else:
+                chk(L.tq_exchange_sum_f16_rmsnorm(C.c_void_p(slots_ptr), n_slots, count, batch, hidden, C.c_void_p(residual.data_ptr()),
+                                                  C.c_void_p(out.data_ptr()), C.c_void_p(norm_w.data_ptr()), C.c_void_p(h1.data_ptr()),
+                                                  1e-6, sp))
 
         marks = None                       # set to a list: layer_step then records an event after every group of kernels
 
@@ -1280,7 +1293,8 @@ def bench_c4_decode_step(tq, L, device, stream, rank, world, cbs, args):
         def layer_step(li):
             w = layers[li]
             mark("start")
-            chk(L.tq_rmsnorm_f16(C.c_void_p(x.data_ptr()), C.c_void_p(w["n1"].data_ptr()), C.c_void_p(h1.data_ptr()), batch, hidden, 1e-6, sp))
+            if li == 0:      # later layers' input norm comes out of the previous layer's last all-reduce kernel
+                chk(L.tq_rmsnorm_f16(C.c_void_p(x.data_ptr()), C.c_void_p(w["n1"].data_ptr()), C.c_void_p(h1.data_ptr()), batch, hidden, 1e-6, sp))
             mark("rmsnorm_1")
             if batch <= 8:
                 # q, k and v read the same activation: one grouped launch (bit-equal to the three calls)
@@ -1291,29 +1305,27 @@ def bench_c4_decode_step(tq, L, device, stream, rank, world, cbs, args):
                 fwd(w["k"], h1.data_ptr(), batch, k.data_ptr())
                 fwd(w["v"], h1.data_ptr(), batch, v.data_ptr())
             mark("q_k_v")
-            chk(L.tq_rope_f16(C.c_void_p(q.data_ptr()), C.c_void_p(pos.data_ptr()), batch, qh, dim, 1e6, sp))
-            chk(L.tq_rope_f16(C.c_void_p(k.data_ptr()), C.c_void_p(pos.data_ptr()), batch, kvh, dim, 1e6, sp))
-            mark("rope_x2")
+            chk(L.tq_rope_qk_f16(C.c_void_p(q.data_ptr()), C.c_void_p(k.data_ptr()), C.c_void_p(pos.data_ptr()), batch, qh, kvh, dim, 1e6, sp))
+            mark("rope_q_k")
             chk(L.tq_kv_append_batch(arr, batch, li, C.c_void_p(k.data_ptr()), C.c_void_p(v.data_ptr()), tq.TQ_F16, sp))
             mark("kv_append")
             chk(L.tq_kv_attention(arr, batch, li, C.c_void_p(q.data_ptr()), tq.TQ_F16, qh, C.c_void_p(attn.data_ptr()), 0, ctx, 1, sp))
             mark("attention")
             if use_packets:
-                all_reduce_add_packets(w["o"], attn.data_ptr(), x, x1)
+                all_reduce_add_packets(w["o"], attn.data_ptr(), x, x1, norm_w=w["n2"])
             else:
-                all_reduce_add(lambda ptr: fwd(w["o"], attn.data_ptr(), batch, ptr), x, x1)
-            mark("o_proj_sum_residual")
-            chk(L.tq_rmsnorm_f16(C.c_void_p(x1.data_ptr()), C.c_void_p(w["n2"].data_ptr()), C.c_void_p(h1.data_ptr()), batch, hidden, 1e-6, sp))
-            mark("rmsnorm_2")
+                all_reduce_add(lambda ptr: fwd(w["o"], attn.data_ptr(), batch, ptr), x, x1, norm_w=w["n2"])
+            mark("o_proj_sum_residual_rmsnorm")
             fwd(w["gu"], h1.data_ptr(), batch, gu.data_ptr())
             mark("gate_up")
             chk(L.tq_swiglu_f16(C.c_void_p(gu.data_ptr()), C.c_void_p(act.data_ptr()), batch, il, sp))
             mark("swiglu")
+            nxt = layers[li + 1]["n1"] if li + 1 < n_layers else None
             if use_packets:
-                all_reduce_add_packets(w["down"], act.data_ptr(), x1, x)
+                all_reduce_add_packets(w["down"], act.data_ptr(), x1, x, norm_w=nxt)
             else:
-                all_reduce_add(lambda ptr: fwd(w["down"], act.data_ptr(), batch, ptr), x1, x)
-            mark("down_proj_sum_residual")
+                all_reduce_add(lambda ptr: fwd(w["down"], act.data_ptr(), batch, ptr), x1, x, norm_w=nxt)
+            mark("down_proj_sum_residual_rmsnorm")
 
         def one_pass():
             for li in range(n_layers):
@@ -1384,8 +1396,9 @@ def bench_c4_decode_step(tq, L, device, stream, rank, world, cbs, args):
         res[f"b{batch}"] = {"us_per_layer": us, "tok_per_s_64_layers": batch / (us * 1e-6 * n_model_layers),
                             "gb_per_s_per_gpu": (weight_bytes + kv_bytes) / (us * 1e-6) / 1e9,
                             "bytes_per_layer_per_gpu": weight_bytes + kv_bytes, "distinct_layers_cycled": n_layers,
-                            "kernels_per_layer": "rmsnorm, q + k + v (one grouped launch up to 8 rows), rope x2, kv append x2, attention, o_proj, "
-                                                 "[copy to peers, wait,] sum + residual, rmsnorm, gate-up, swiglu, down, [copy to peers, wait,] sum + residual",
+                            "kernels_per_layer": "q + k + v (one grouped launch up to 8 rows), rope of q and k, kv append x2, attention, o_proj, "
+                                                 "[copy to peers, wait,] sum + residual + rmsnorm, gate-up, swiglu, down, [copy to peers, wait,] "
+                                                 "sum + residual + the next layer's rmsnorm",
                             "all_reduce": ("none (one rank)" if exchange is None else
                                            "partials sent as packets from inside o_proj / down_proj, one kernel waits and adds" if use_packets
                                            else "tq_exchange_broadcast + tq_exchange_wait + tq_exchange_sum_f16"),

@@ -299,6 +299,10 @@ int tq_exchange_wait(tq_exchange_t ex, const void* local_flags, int n_flags, voi
  *  and gets the same bits. */
 int tq_exchange_sum_f16(const void* slots_fp16, int n_slots, long slot_stride, long count, const void* residual_fp16,
                         void* out_fp16, void* stream);
+/** tq_exchange_sum_f16 over whole rows ([rows, cols]) followed in the same kernel by the RMSNorm of the summed rows
+ *  (see tq_exchange_sum_packets_rmsnorm). */
+int tq_exchange_sum_f16_rmsnorm(const void* slots_fp16, int n_slots, long slot_stride, long rows, int cols, const void* residual_fp16,
+                                void* out_fp16, const void* norm_weight_fp16, void* normed_fp16, float eps, void* stream);
 /** Attention over the union of disjoint token ranges from each range's output and log-sum-exp
  *  (tq_kv_attention_lse): outs [parts][rows][head_dim] fp16, lses [parts][rows] fp32, parts
  *  part_stride_out / part_stride_lse elements apart. */
@@ -348,6 +352,12 @@ int tq_exchange_wait_packets(tq_exchange_t ex, const void* local_packets, long r
  *  gets the same bits.  residual_fp16 may be NULL.  Counts as this exchange's wait. */
 int tq_exchange_sum_packets(tq_exchange_t ex, const void* local_packets, const void* local_partial_fp16, long count,
                             const void* residual_fp16, void* out_fp16, void* stream);
+/** tq_exchange_sum_packets over whole rows ([rows, cols], cols a multiple of 4) followed, in the same kernel (one CTA per
+ *  row), by the RMSNorm of the summed rows: normed = out * rsqrt(mean(out^2) + eps) * norm_weight, the bits
+ *  tq_rmsnorm_f16 gives on out.  The residual stream (out) and the next projection's input (normed) in one launch. */
+int tq_exchange_sum_packets_rmsnorm(tq_exchange_t ex, const void* local_packets, const void* local_partial_fp16, long rows, int cols,
+                                    const void* residual_fp16, void* out_fp16, const void* norm_weight_fp16, void* normed_fp16, float eps,
+                                    void* stream);
 int tq_exchange_unpack_packets(const void* packets, long n_packets, void* out_fp16, void* stream);
 /* Element-wise glue of a decoder layer, device fp16 in and out, fp32 arithmetic.  The reference
  * leaves these to MLX in the host application (no file of its own computes them); they are here so
@@ -358,6 +368,9 @@ int tq_exchange_unpack_packets(const void* packets, long n_packets, void* out_fp
  *   tq_swiglu_f16 : act[r,j] = silu(gate_up[r,j]) * gate_up[r, intermediate + j] */
 int tq_rmsnorm_f16(const void* x_fp16, const void* weight_fp16, void* y_fp16, long rows, int cols, float eps, void* stream);
 int tq_rope_f16(void* x_fp16, const int* positions, long rows, int heads, int head_dim, float theta, void* stream);
+/** tq_rope_f16 on the queries [rows, q_heads, head_dim] and the keys [rows, kv_heads, head_dim] of a step in one launch. */
+int tq_rope_qk_f16(void* q_fp16, void* k_fp16, const int* positions, long rows, int q_heads, int kv_heads, int head_dim, float theta,
+                   void* stream);
 int tq_swiglu_f16(const void* gate_up_fp16, void* act_fp16, long rows, int intermediate, void* stream);
 
 /** Waits for the device; non-zero if a wait of this exchange gave up. */

@@ -59,6 +59,28 @@ def test_rmsnorm_rope_swiglu_match_their_definitions(tq):
     assert torch.equal(out, want)
     assert L.tq_rmsnorm_f16(C.c_void_p(xd.data_ptr()), C.c_void_p(wd.data_ptr()), C.c_void_p(y.data_ptr()), rows, 5121, 1e-6, None) != 0
 
+    # the same sum with the RMSNorm of the summed rows in one kernel: both results bit-equal to the two separate calls
+    out2 = torch.empty_like(out)
+    normed, normed2 = torch.empty_like(out), torch.empty_like(out)
+    assert L.tq_exchange_sum_f16_rmsnorm(C.c_void_p(slots.data_ptr()), 3, rows * cols, rows, cols, C.c_void_p(res.data_ptr()),
+                                         C.c_void_p(out2.data_ptr()), C.c_void_p(wd.data_ptr()), C.c_void_p(normed2.data_ptr()),
+                                         1e-6, None) == 0
+    assert L.tq_rmsnorm_f16(C.c_void_p(out.data_ptr()), C.c_void_p(wd.data_ptr()), C.c_void_p(normed.data_ptr()), rows, cols, 1e-6, None) == 0
+    torch.cuda.synchronize()
+    assert torch.equal(out2, out) and torch.equal(normed2, normed)
+
+    # queries and keys through the rotary embedding in one launch: the bits of the two separate calls
+    kv_heads = 2
+    k = rng.standard_normal((rows, kv_heads, dim)).astype(np.float16)
+    q1, k1 = torch.from_numpy(q).cuda(), torch.from_numpy(k).cuda()
+    q2, k2 = q1.clone(), k1.clone()
+    assert L.tq_rope_f16(C.c_void_p(q1.data_ptr()), C.c_void_p(pd.data_ptr()), rows, heads, dim, theta, None) == 0
+    assert L.tq_rope_f16(C.c_void_p(k1.data_ptr()), C.c_void_p(pd.data_ptr()), rows, kv_heads, dim, theta, None) == 0
+    assert L.tq_rope_qk_f16(C.c_void_p(q2.data_ptr()), C.c_void_p(k2.data_ptr()), C.c_void_p(pd.data_ptr()), rows, heads, kv_heads, dim,
+                            theta, None) == 0
+    torch.cuda.synchronize()
+    assert torch.equal(q1, q2) and torch.equal(k1, k2) and torch.equal(q1, qd)
+
 
 def test_attention_replays_inside_a_cuda_graph(tq):
     """A decode-attention call whose descriptors repeat the previous call's enqueues kernels only: captured

@@ -175,6 +175,17 @@ def test_forward_fused_with_packet_all_gather(tq, oracle):
             for src in range(world):
                 acc = acc + want[src].float()
             assert torch.equal(out, acc.half()), (batch, r)
+            # the same sum followed in the same kernel by the RMSNorm of the summed rows (rows of 4-element groups)
+            if rows % 4 == 0:
+                wn = torch.from_numpy((1 + 0.1 * rng.standard_normal(rows)).astype(np.float16)).cuda()
+                out2, normed2, normed = torch.empty_like(out), torch.empty_like(out), torch.empty_like(out)
+                assert L.tq_exchange_sum_packets_rmsnorm(ex[r], C.c_void_p(bufs[r].data_ptr()), C.c_void_p(ys[r].data_ptr()), batch, rows,
+                                                         C.c_void_p(resid.data_ptr()), C.c_void_p(out2.data_ptr()),
+                                                         C.c_void_p(wn.data_ptr()), C.c_void_p(normed2.data_ptr()), 1e-6, None) == 0
+                assert L.tq_rmsnorm_f16(C.c_void_p(out.data_ptr()), C.c_void_p(wn.data_ptr()), C.c_void_p(normed.data_ptr()), batch, rows,
+                                        1e-6, None) == 0
+                torch.cuda.synchronize()
+                assert torch.equal(out2, out) and torch.equal(normed2, normed), (batch, r)
         for r in range(world):
             assert L.tq_exchange_status(ex[r]) == 0
             lins[r].check_status()

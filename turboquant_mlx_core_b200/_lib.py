@@ -94,6 +94,8 @@ def load() -> C.CDLL:
     sig("tq_exchange_sum_f16", i, [vp, i, C.c_long, C.c_long, vp, vp, vp])
     sig("tq_rmsnorm_f16", i, [vp, vp, vp, C.c_long, i, C.c_float, vp])
     sig("tq_rope_f16", i, [vp, vp, C.c_long, i, i, C.c_float, vp])
+    sig("tq_rope_qk_f16", i, [vp, vp, vp, C.c_long, i, i, i, C.c_float, vp])
+    sig("tq_exchange_sum_f16_rmsnorm", i, [vp, i, C.c_long, C.c_long, i, vp, vp, vp, vp, C.c_float, vp])
     sig("tq_swiglu_f16", i, [vp, vp, C.c_long, i, vp])
     sig("tq_exchange_merge_attention", i, [vp, vp, i, C.c_long, i, C.c_long, C.c_long, vp, vp])
     sig("tq_linear_forward_allgather", i, [vp, vp, vp, i, C.POINTER(C.c_void_p), i, C.c_long, C.c_long, C.POINTER(C.c_void_p), i,
@@ -145,6 +147,7 @@ def load() -> C.CDLL:
     sig("tq_exchange_unpack_packets", i, [vp, C.c_long, vp, vp])
     sig("tq_exchange_wait_packets", i, [vp, vp, C.c_long, i, vp, C.c_long, vp])
     sig("tq_exchange_sum_packets", i, [vp, vp, vp, C.c_long, vp, vp, vp])
+    sig("tq_exchange_sum_packets_rmsnorm", i, [vp, vp, vp, C.c_long, i, vp, vp, vp, vp, C.c_float, vp])
     sig("tq_decode_buffer_create", vp, [i, i, i])
     sig("tq_decode_buffer_free", None, [vp])
     sig("tq_decode_buffer_window_size", i, [vp])

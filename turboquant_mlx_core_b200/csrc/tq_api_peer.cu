@@ -75,6 +75,27 @@ int tq_exchange_sum_f16(const void* slots_fp16, int n_slots, long slot_stride, l
     });
 }
 
+int tq_exchange_sum_f16_rmsnorm(const void* slots_fp16, int n_slots, long slot_stride, long rows, int cols, const void* residual_fp16,
+                                void* out_fp16, const void* norm_weight_fp16, void* normed_fp16, float eps, void* stream) {
+    return guarded<int>(0, -1, [&]() {
+        TQ_REQUIRE(norm_weight_fp16 && normed_fp16, "tq_exchange_sum_f16_rmsnorm: NULL argument");
+        launch_exchange_sum_f16(static_cast<const __half*>(slots_fp16), n_slots, slot_stride, rows * cols,
+                                static_cast<const __half*>(residual_fp16), static_cast<__half*>(out_fp16),
+                                static_cast<cudaStream_t>(stream), static_cast<const __half*>(norm_weight_fp16),
+                                static_cast<__half*>(normed_fp16), cols, eps);
+        return 0;
+    });
+}
+
+int tq_rope_qk_f16(void* q_fp16, void* k_fp16, const int* positions, long rows, int q_heads, int kv_heads, int head_dim, float theta,
+                   void* stream) {
+    return guarded<int>(0, -1, [&]() {
+        launch_rope_qk_f16(static_cast<__half*>(q_fp16), static_cast<__half*>(k_fp16), positions, rows, q_heads, kv_heads, head_dim, theta,
+                           static_cast<cudaStream_t>(stream));
+        return 0;
+    });
+}
+
 int tq_rmsnorm_f16(const void* x_fp16, const void* weight_fp16, void* y_fp16, long rows, int cols, float eps, void* stream) {
     return guarded<int>(0, -1, [&]() {
         launch_rmsnorm_f16(static_cast<const __half*>(x_fp16), static_cast<const __half*>(weight_fp16), static_cast<__half*>(y_fp16),
@@ -153,6 +174,21 @@ int tq_exchange_sum_packets(tq_exchange_t ex, const void* local_packets, const v
                                     ex->words.as<unsigned int>() + 2, ex->rank, ex->world, count,
                                     static_cast<const __half*>(local_partial_fp16), static_cast<const __half*>(residual_fp16),
                                     static_cast<__half*>(out_fp16), ex->d_status, static_cast<cudaStream_t>(stream));
+        return 0;
+    });
+}
+
+int tq_exchange_sum_packets_rmsnorm(tq_exchange_t ex, const void* local_packets, const void* local_partial_fp16, long rows, int cols,
+                                    const void* residual_fp16, void* out_fp16, const void* norm_weight_fp16, void* normed_fp16, float eps,
+                                    void* stream) {
+    return guarded<int>(0, -1, [&]() {
+        TQ_REQUIRE(ex != nullptr && local_packets && local_partial_fp16 && out_fp16 && norm_weight_fp16 && normed_fp16,
+                   "tq_exchange_sum_packets_rmsnorm: NULL argument");
+        launch_exchange_sum_packets(static_cast<const uint4*>(local_packets), ex->words.as<unsigned int>() + 1,
+                                    ex->words.as<unsigned int>() + 2, ex->rank, ex->world, rows * cols,
+                                    static_cast<const __half*>(local_partial_fp16), static_cast<const __half*>(residual_fp16),
+                                    static_cast<__half*>(out_fp16), ex->d_status, static_cast<cudaStream_t>(stream),
+                                    static_cast<const __half*>(norm_weight_fp16), static_cast<__half*>(normed_fp16), cols, eps);
         return 0;
     });
 }

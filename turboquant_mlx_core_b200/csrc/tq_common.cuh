@@ -111,6 +111,34 @@ __host__ __device__ __forceinline__ size_t code_offset(long row, int col, size_t
 
 // Report a failure from a kernel.  The status word may live in page-locked HOST memory (so that
 // the host reads it without a copy): a plain store followed by a system-scope fence, no atomic.
+// Threads of a CTA that normalises one row (the RMSNorm kernel and the row-wise all-reduce tails: the same count, so the
+// same order of additions).  A decode step has a handful of rows: the row's latency, not the SM count, is what matters.
+constexpr int kRowNormThreads = 1024;
+
+// yr[:] = xr[:] * rsqrt(mean(xr[:]^2) + eps) * w for one row, by the whole CTA (up to 1024 threads, a multiple of 32;
+// cols even).  Shared by the RMSNorm kernel and the all-reduce tails that normalise the row they have just summed, so
+// the fused and the separate form give the same bits.
+__device__ __forceinline__ void rmsnorm_row(const __half* xr, const __half* __restrict__ w, __half* yr, int cols, float eps) {
+    float ss = 0.f;
+    for (int c = threadIdx.x * 2; c < cols; c += blockDim.x * 2) {
+        const float2 v = __half22float2(*reinterpret_cast<const __half2*>(xr + c));
+        ss += v.x * v.x + v.y * v.y;
+    }
+    __shared__ float s_part[32];
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    if ((threadIdx.x & 31) == 0) s_part[threadIdx.x >> 5] = ss;
+    __syncthreads();
+    float tot = 0.f;
+    for (int i = 0; i < static_cast<int>(blockDim.x >> 5); ++i) tot += s_part[i];   // fixed order
+    const float scale = rsqrtf(tot / static_cast<float>(cols) + eps);
+    for (int c = threadIdx.x * 2; c < cols; c += blockDim.x * 2) {
+        const float2 v = __half22float2(*reinterpret_cast<const __half2*>(xr + c));
+        const float2 g = __half22float2(*reinterpret_cast<const __half2*>(w + c));
+        *reinterpret_cast<__half2*>(yr + c) = __floats2half2_rn(v.x * scale * g.x, v.y * scale * g.y);
+    }
+}
+
 __device__ __forceinline__ void raise_status(unsigned int* status, unsigned int code) {
     *reinterpret_cast<volatile unsigned int*>(status) = code;
     __threadfence_system();

@@ -20,45 +20,32 @@ __device__ __forceinline__ void ops_dependency_sync() {
 }
 
 // y[r, :] = x[r, :] * rsqrt(mean(x[r, :]^2) + eps) * w      one CTA per row
-__global__ void __launch_bounds__(256) rmsnorm_kernel(const __half* __restrict__ x, const __half* __restrict__ w, __half* __restrict__ y,
+__global__ void __launch_bounds__(kRowNormThreads) rmsnorm_kernel(const __half* __restrict__ x, const __half* __restrict__ w, __half* __restrict__ y,
                                                       int cols, float eps) {
     ops_dependency_sync();
-    const __half* xr = x + static_cast<size_t>(blockIdx.x) * cols;
-    __half* yr = y + static_cast<size_t>(blockIdx.x) * cols;
-    float ss = 0.f;
-    for (int c = threadIdx.x * 2; c < cols; c += blockDim.x * 2) {
-        const float2 v = __half22float2(*reinterpret_cast<const __half2*>(xr + c));
-        ss += v.x * v.x + v.y * v.y;
-    }
-    __shared__ float s_part[8];
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
-    if ((threadIdx.x & 31) == 0) s_part[threadIdx.x >> 5] = ss;
-    __syncthreads();
-    float tot = 0.f;
-    for (int i = 0; i < static_cast<int>(blockDim.x >> 5); ++i) tot += s_part[i];   // fixed order
-    const float scale = rsqrtf(tot / static_cast<float>(cols) + eps);
-    for (int c = threadIdx.x * 2; c < cols; c += blockDim.x * 2) {
-        const float2 v = __half22float2(*reinterpret_cast<const __half2*>(xr + c));
-        const float2 g = __half22float2(*reinterpret_cast<const __half2*>(w + c));
-        *reinterpret_cast<__half2*>(yr + c) = __floats2half2_rn(v.x * scale * g.x, v.y * scale * g.y);
-    }
+    rmsnorm_row(x + static_cast<size_t>(blockIdx.x) * cols, w, y + static_cast<size_t>(blockIdx.x) * cols, cols, eps);
 }
 
 // Rotary embedding, "rotate half" convention: element i of a head pairs with element i + d/2;
 // angle = position * theta^(-2 i / d).  x: [rows, heads, d] in place, positions: [rows].
+// A second tensor x2 [rows, heads2, d] (the keys beside the queries) rides in the same launch: pairs beyond x's.
 __global__ void __launch_bounds__(128) rope_kernel(__half* __restrict__ x, const int* __restrict__ positions, int heads, int dim,
-                                                   float log2_theta, long total_pairs) {
+                                                   float log2_theta, long total_pairs, __half* __restrict__ x2, int heads2, long total_pairs2) {
     ops_dependency_sync();
     const int half = dim >> 1;
-    for (long i = static_cast<long>(blockIdx.x) * blockDim.x + threadIdx.x; i < total_pairs; i += static_cast<long>(gridDim.x) * blockDim.x) {
+    for (long i0 = static_cast<long>(blockIdx.x) * blockDim.x + threadIdx.x; i0 < total_pairs + total_pairs2;
+         i0 += static_cast<long>(gridDim.x) * blockDim.x) {
+        const bool second = i0 >= total_pairs;
+        const long i = second ? i0 - total_pairs : i0;
+        __half* const xb = second ? x2 : x;
+        const int hh = second ? heads2 : heads;
         const int p = static_cast<int>(i % half);
         const long vec = i / half;               // (row, head)
-        const long row = vec / heads;
+        const long row = vec / hh;
         const float inv_freq = exp2f(-log2_theta * (2.0f * static_cast<float>(p) / static_cast<float>(dim)));
         float s, c;
         sincosf(static_cast<float>(positions[row]) * inv_freq, &s, &c);
-        __half* v = x + vec * dim;
+        __half* v = xb + vec * dim;
         const float a = __half2float(v[p]), b = __half2float(v[p + half]);
         v[p] = __float2half_rn(a * c - b * s);
         v[p + half] = __float2half_rn(b * c + a * s);
@@ -97,7 +84,7 @@ void launch_rmsnorm_f16(const __half* x, const __half* weight, __half* y, long r
     TQ_REQUIRE(cols > 0 && cols % 2 == 0, "rmsnorm: an even number of columns");
     if (rows == 0) return;
     cudaLaunchAttribute attr[1];
-    cudaLaunchConfig_t cfg = ops_config(static_cast<unsigned>(rows), 256, stream, attr);
+    cudaLaunchConfig_t cfg = ops_config(static_cast<unsigned>(rows), kRowNormThreads, stream, attr);
     TQ_CUDA(cudaLaunchKernelEx(&cfg, rmsnorm_kernel, x, weight, y, cols, eps));
 }
 
@@ -110,7 +97,20 @@ void launch_rope_f16(__half* x, const int* positions, long rows, int heads, int 
     if (blocks > 1184) blocks = 1184;
     cudaLaunchAttribute attr[1];
     cudaLaunchConfig_t cfg = ops_config(static_cast<unsigned>(blocks), 128, stream, attr);
-    TQ_CUDA(cudaLaunchKernelEx(&cfg, rope_kernel, x, positions, heads, dim, std::log2(theta), pairs));
+    TQ_CUDA(cudaLaunchKernelEx(&cfg, rope_kernel, x, positions, heads, dim, std::log2(theta), pairs, static_cast<__half*>(nullptr), 1, 0L));
+}
+
+void launch_rope_qk_f16(__half* q, __half* k, const int* positions, long rows, int q_heads, int kv_heads, int dim, float theta,
+                        cudaStream_t stream) {
+    TQ_REQUIRE(q && k && positions, "rope: NULL argument");
+    TQ_REQUIRE(dim > 0 && dim % 2 == 0 && q_heads > 0 && kv_heads > 0 && theta > 1.0f, "rope: bad shape");
+    if (rows == 0) return;
+    const long pairs_q = rows * q_heads * (dim / 2), pairs_k = rows * kv_heads * (dim / 2);
+    long blocks = (pairs_q + pairs_k + 127) / 128;
+    if (blocks > 1184) blocks = 1184;
+    cudaLaunchAttribute attr[1];
+    cudaLaunchConfig_t cfg = ops_config(static_cast<unsigned>(blocks), 128, stream, attr);
+    TQ_CUDA(cudaLaunchKernelEx(&cfg, rope_kernel, q, positions, q_heads, dim, std::log2(theta), pairs_q, k, kv_heads, pairs_k));
 }
 
 void launch_swiglu_f16(const __half* gate_up, __half* act, long rows, int inter, cudaStream_t stream) {

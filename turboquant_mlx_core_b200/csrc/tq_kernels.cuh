@@ -172,12 +172,16 @@ void launch_exchange_broadcast(const void* src, void* const* dst, int n_dst, int
                                long dst_stride, unsigned int* const* signal, int n_signal, int slot, unsigned int* done,
                                unsigned int* epoch, cudaStream_t stream);
 void launch_exchange_wait(const unsigned int* flags, int n, unsigned int* epoch, unsigned int* status, cudaStream_t stream);
+// With norm_w: count is whole rows of `cols` elements, one CTA per row, which then also writes
+// normed[row] = RMSNorm(out[row]) * norm_w (the bits launch_rmsnorm_f16 gives on out).
 void launch_exchange_sum_f16(const __half* slots, int n_slots, long slot_stride, long count, const __half* residual, __half* out,
-                             cudaStream_t stream);
+                             cudaStream_t stream, const __half* norm_w = nullptr, __half* normed = nullptr, int cols = 0,
+                             float eps = 0.f);
 void launch_exchange_wait_packets(const uint4* base, const unsigned int* epoch, unsigned int* wait_epoch, int rank, int world, long rows,
                                   int batch, __half* out, long out_stride, unsigned int* status, cudaStream_t stream);
 void launch_exchange_sum_packets(const uint4* base, const unsigned int* epoch, unsigned int* wait_epoch, int rank, int world, long count,
-                                 const __half* local, const __half* residual, __half* out, unsigned int* status, cudaStream_t stream);
+                                 const __half* local, const __half* residual, __half* out, unsigned int* status, cudaStream_t stream,
+                                 const __half* norm_w = nullptr, __half* normed = nullptr, int cols = 0, float eps = 0.f);
 void launch_exchange_unpack_packets(const uint4* packets, long n_packets, __half* out, cudaStream_t stream);
 void launch_exchange_merge_attention(const __half* outs, const float* lses, int parts, long rows, int dim, long part_stride_o,
                                      long part_stride_l, __half* out, cudaStream_t stream);
@@ -185,6 +189,9 @@ void launch_exchange_merge_attention(const __half* outs, const float* lses, int 
 // tq_decoder_ops.cu — element-wise glue of a decoder layer (fp16 in / out, fp32 arithmetic).
 void launch_rmsnorm_f16(const __half* x, const __half* weight, __half* y, long rows, int cols, float eps, cudaStream_t stream);
 void launch_rope_f16(__half* x, const int* positions, long rows, int heads, int dim, float theta, cudaStream_t stream);
+// queries [rows, q_heads, dim] and keys [rows, kv_heads, dim] in one launch
+void launch_rope_qk_f16(__half* q, __half* k, const int* positions, long rows, int q_heads, int kv_heads, int dim, float theta,
+                        cudaStream_t stream);
 void launch_swiglu_f16(const __half* gate_up, __half* act, long rows, int inter, cudaStream_t stream);
 
 // tq_misc.cu — small element-wise helpers.

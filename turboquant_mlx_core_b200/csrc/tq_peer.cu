@@ -102,12 +102,19 @@ __global__ void exchange_wait_kernel(const unsigned int* __restrict__ flags, int
 }
 
 // out[i] = fp16( residual[i] + sum over slots s, in slot order, of fp32(slots[s][i]) )   (residual may be NULL)
-__global__ void __launch_bounds__(256) exchange_sum_f16_kernel(const __half* __restrict__ slots, int n_slots, long slot_stride,
-                                                               long count, const __half* __restrict__ residual, __half* __restrict__ out) {
+// With norm_w (one CTA per row of `cols` elements): the CTA then writes normed[row] = RMSNorm(out[row]) * norm_w, the
+// bits rmsnorm_kernel would give on out.
+__global__ void __launch_bounds__(kRowNormThreads) exchange_sum_f16_kernel(const __half* __restrict__ slots, int n_slots, long slot_stride,
+                                                               long count, const __half* __restrict__ residual, __half* __restrict__ out,
+                                                               const __half* __restrict__ norm_w, __half* __restrict__ normed, int cols,
+                                                               float eps) {
     asm volatile("griddepcontrol.wait;" ::: "memory");
     asm volatile("griddepcontrol.launch_dependents;");
-    for (long i = (static_cast<long>(blockIdx.x) * blockDim.x + threadIdx.x) * 2; i < count;
-         i += static_cast<long>(gridDim.x) * blockDim.x * 2) {
+    const bool by_row = norm_w != nullptr;
+    const long first = by_row ? static_cast<long>(blockIdx.x) * cols + threadIdx.x * 2 : (static_cast<long>(blockIdx.x) * blockDim.x + threadIdx.x) * 2;
+    const long last = by_row ? static_cast<long>(blockIdx.x + 1) * cols : count;
+    const long step = by_row ? static_cast<long>(blockDim.x) * 2 : static_cast<long>(gridDim.x) * blockDim.x * 2;
+    for (long i = first; i < last; i += step) {
         float a = 0.f, b = 0.f;
         if (residual != nullptr) {
             const __half2 h = *reinterpret_cast<const __half2*>(residual + i);
@@ -120,6 +127,10 @@ __global__ void __launch_bounds__(256) exchange_sum_f16_kernel(const __half* __r
             b += __high2float(h);
         }
         *reinterpret_cast<__half2*>(out + i) = __floats2half2_rn(a, b);
+    }
+    if (by_row) {
+        __syncthreads();   // the row is complete (this CTA wrote all of it)
+        rmsnorm_row(out + static_cast<long>(blockIdx.x) * cols, norm_w, normed + static_cast<long>(blockIdx.x) * cols, cols, eps);
     }
 }
 
@@ -167,45 +178,73 @@ __global__ void __launch_bounds__(256) exchange_wait_packets_kernel(const uint4*
 // All-reduce tail for partial sums that travelled as packets: out = fp16(residual + sum over ranks, in rank order, fp32),
 // this rank's own partial read from `local` ([batch][rows] fp16), the others' polled (bounded) from the packets of the
 // exchange that has just completed on this rank.  The arithmetic is exchange_sum_f16_kernel's.
-__global__ void __launch_bounds__(256) exchange_sum_packets_kernel(const uint4* __restrict__ base, const unsigned int* __restrict__ epoch,
+__global__ void __launch_bounds__(kRowNormThreads) exchange_sum_packets_kernel(const uint4* __restrict__ base, const unsigned int* __restrict__ epoch,
                                                                    unsigned int* __restrict__ wait_epoch, int rank, int world, long packets,
                                                                    const __half* __restrict__ local, const __half* __restrict__ residual,
-                                                                   __half* __restrict__ out, unsigned int* status) {
+                                                                   __half* __restrict__ out, unsigned int* status,
+                                                                   const __half* __restrict__ norm_w, __half* __restrict__ normed, int cols,
+                                                                   float eps) {
     asm volatile("griddepcontrol.wait;" ::: "memory");
     asm volatile("griddepcontrol.launch_dependents;");
     const unsigned int want = *reinterpret_cast<const volatile unsigned int*>(epoch);
     if (blockIdx.x == 0 && threadIdx.x == 0) atomicAdd(wait_epoch, 1u);
     const uint4* const half = base + static_cast<size_t>(want & 1u) * world * packets;
     const unsigned long long t0 = p_timer_ns();
-    for (long i = static_cast<long>(blockIdx.x) * blockDim.x + threadIdx.x; i < packets; i += static_cast<long>(gridDim.x) * blockDim.x) {
+    // with norm_w: one CTA per row of cols elements (cols / 4 packets), which it normalises afterwards
+    const bool by_row = norm_w != nullptr;
+    const long per_row = cols / 4;
+    const long first = by_row ? static_cast<long>(blockIdx.x) * per_row + threadIdx.x : static_cast<long>(blockIdx.x) * blockDim.x + threadIdx.x;
+    const long last = by_row ? static_cast<long>(blockIdx.x + 1) * per_row : packets;
+    const long step = by_row ? static_cast<long>(blockDim.x) : static_cast<long>(gridDim.x) * blockDim.x;
+    bool gave_up = false;
+    for (long i = first; i < last && !gave_up; i += step) {
         float a[4] = {0.f, 0.f, 0.f, 0.f};
         if (residual != nullptr) {
             const uint2 r = *reinterpret_cast<const uint2*>(residual + 4 * i);
             const float2 r0 = __half22float2(*reinterpret_cast<const __half2*>(&r.x)), r1 = __half22float2(*reinterpret_cast<const __half2*>(&r.y));
             a[0] = r0.x; a[1] = r0.y; a[2] = r1.x; a[3] = r1.y;
         }
-        for (int src = 0; src < world; ++src) {
-            uint2 v;
-            if (src == rank) {
-                v = *reinterpret_cast<const uint2*>(local + 4 * i);
-            } else {
+        // every rank's packet is requested first (one round trip for all of them), then checked, and only what has
+        // not arrived yet is polled again; the additions run in rank order afterwards
+        uint4 pk[8];
+#pragma unroll
+        for (int src = 0; src < 8; ++src) {
+            if (src < world && src != rank) {
                 const uint4* at = half + static_cast<size_t>(src) * packets + i;
-                uint4 pk;
-                for (unsigned int spin = 0;; ++spin) {
-                    asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(pk.x), "=r"(pk.y), "=r"(pk.z), "=r"(pk.w) : "l"(at) : "memory");
-                    if (static_cast<int>(pk.y - want) >= 0 && static_cast<int>(pk.w - want) >= 0) break;
-                    if ((spin & 255u) == 255u && p_timer_ns() - t0 > kPeerWaitNs) {
-                        raise_status(status, 10u);
-                        return;
-                    }
-                }
-                v = make_uint2(pk.x, pk.z);
+                asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(pk[src].x), "=r"(pk[src].y), "=r"(pk[src].z), "=r"(pk[src].w) : "l"(at) : "memory");
             }
-            const float2 v0 = __half22float2(*reinterpret_cast<const __half2*>(&v.x)), v1 = __half22float2(*reinterpret_cast<const __half2*>(&v.y));
-            a[0] += v0.x; a[1] += v0.y; a[2] += v1.x; a[3] += v1.y;
         }
+#pragma unroll
+        for (int src = 0; src < 8; ++src) {
+            if (src < world && src != rank && !gave_up) {
+                const uint4* at = half + static_cast<size_t>(src) * packets + i;
+                for (unsigned int spin = 0; !(static_cast<int>(pk[src].y - want) >= 0 && static_cast<int>(pk[src].w - want) >= 0); ++spin) {
+                    if ((spin & 255u) == 255u && p_timer_ns() - t0 > kPeerWaitNs) {   // a peer is gone: stop polling
+                        raise_status(status, 10u);
+                        gave_up = true;
+                        break;
+                    }
+                    asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(pk[src].x), "=r"(pk[src].y), "=r"(pk[src].z), "=r"(pk[src].w) : "l"(at) : "memory");
+                }
+            }
+        }
+#pragma unroll
+        for (int src = 0; src < 8; ++src) {
+            if (src < world) {
+                uint2 v;
+                if (src == rank) v = *reinterpret_cast<const uint2*>(local + 4 * i);
+                else v = make_uint2(pk[src].x, pk[src].z);
+                const float2 v0 = __half22float2(*reinterpret_cast<const __half2*>(&v.x)), v1 = __half22float2(*reinterpret_cast<const __half2*>(&v.y));
+                a[0] += v0.x; a[1] += v0.y; a[2] += v1.x; a[3] += v1.y;
+            }
+        }
+        if (gave_up) break;
         const __half2 o0 = __floats2half2_rn(a[0], a[1]), o1 = __floats2half2_rn(a[2], a[3]);
         *reinterpret_cast<uint2*>(out + 4 * i) = make_uint2(*reinterpret_cast<const uint32_t*>(&o0), *reinterpret_cast<const uint32_t*>(&o1));
+    }
+    if (by_row) {
+        __syncthreads();   // the row is complete (every thread gets here, also after a timeout)
+        rmsnorm_row(out + static_cast<long>(blockIdx.x) * cols, norm_w, normed + static_cast<long>(blockIdx.x) * cols, cols, eps);
     }
 }
 
@@ -288,7 +327,7 @@ void launch_exchange_wait(const unsigned int* flags, int n, unsigned int* epoch,
 }
 
 void launch_exchange_sum_f16(const __half* slots, int n_slots, long slot_stride, long count, const __half* residual, __half* out,
-                             cudaStream_t stream) {
+                             cudaStream_t stream, const __half* norm_w, __half* normed, int cols, float eps) {
     TQ_REQUIRE(slots != nullptr && out != nullptr && n_slots >= 1, "exchange sum: NULL argument");
     TQ_REQUIRE(count % 2 == 0 && slot_stride % 2 == 0 && reinterpret_cast<uintptr_t>(slots) % 4 == 0 &&
                    reinterpret_cast<uintptr_t>(out) % 4 == 0,
@@ -296,9 +335,13 @@ void launch_exchange_sum_f16(const __half* slots, int n_slots, long slot_stride,
     if (count == 0) return;
     long blocks = (count / 2 + 255) / 256;
     if (blocks > 296) blocks = 296;
+    if (norm_w != nullptr) {
+        TQ_REQUIRE(normed != nullptr && cols > 0 && cols % 2 == 0 && count % cols == 0, "exchange sum + RMSNorm: whole rows of an even length");
+        blocks = count / cols;
+    }
     cudaLaunchAttribute attr[1];
-    cudaLaunchConfig_t cfg = pdl_config(dim3(static_cast<unsigned>(blocks)), dim3(256), stream, attr);
-    TQ_CUDA(cudaLaunchKernelEx(&cfg, exchange_sum_f16_kernel, slots, n_slots, slot_stride, count, residual, out));
+    cudaLaunchConfig_t cfg = pdl_config(dim3(static_cast<unsigned>(blocks)), dim3(norm_w ? kRowNormThreads : 256), stream, attr);
+    TQ_CUDA(cudaLaunchKernelEx(&cfg, exchange_sum_f16_kernel, slots, n_slots, slot_stride, count, residual, out, norm_w, normed, cols, eps));
 }
 
 void launch_exchange_unpack_packets(const uint4* packets, long n_packets, __half* out, cudaStream_t stream) {
@@ -310,18 +353,24 @@ void launch_exchange_unpack_packets(const uint4* packets, long n_packets, __half
 }
 
 void launch_exchange_sum_packets(const uint4* base, const unsigned int* epoch, unsigned int* wait_epoch, int rank, int world, long count,
-                                 const __half* local, const __half* residual, __half* out, unsigned int* status, cudaStream_t stream) {
-    TQ_REQUIRE(base && epoch && wait_epoch && local && out && world >= 1 && rank >= 0 && rank < world && count % 4 == 0,
+                                 const __half* local, const __half* residual, __half* out, unsigned int* status, cudaStream_t stream,
+                                 const __half* norm_w, __half* normed, int cols, float eps) {
+    TQ_REQUIRE(base && epoch && wait_epoch && local && out && world >= 1 && world <= 8 && rank >= 0 && rank < world && count % 4 == 0,
                "packet sum: element counts in groups of four");
     TQ_REQUIRE(reinterpret_cast<uintptr_t>(local) % 8 == 0 && reinterpret_cast<uintptr_t>(out) % 8 == 0 &&
                    reinterpret_cast<uintptr_t>(residual) % 8 == 0,
                "packet sum: 8-byte aligned buffers");
     if (count == 0) return;
     const long packets = count / 4;
-    const int blocks = static_cast<int>(packets + 255 < 296L * 256 ? (packets + 255) / 256 : 296);
+    int blocks = static_cast<int>(packets + 255 < 296L * 256 ? (packets + 255) / 256 : 296);
+    if (norm_w != nullptr) {
+        TQ_REQUIRE(normed != nullptr && cols > 0 && cols % 4 == 0 && count % cols == 0, "packet sum + RMSNorm: whole rows, a multiple of four long");
+        blocks = static_cast<int>(count / cols);
+    }
     cudaLaunchAttribute attr[1];
-    cudaLaunchConfig_t cfg = pdl_config(dim3(static_cast<unsigned>(blocks)), dim3(256), stream, attr);
-    TQ_CUDA(cudaLaunchKernelEx(&cfg, exchange_sum_packets_kernel, base, epoch, wait_epoch, rank, world, packets, local, residual, out, status));
+    cudaLaunchConfig_t cfg = pdl_config(dim3(static_cast<unsigned>(blocks)), dim3(norm_w ? kRowNormThreads : 256), stream, attr);
+    TQ_CUDA(cudaLaunchKernelEx(&cfg, exchange_sum_packets_kernel, base, epoch, wait_epoch, rank, world, packets, local, residual, out, status,
+                               norm_w, normed, cols, eps));
 }
 
 void launch_exchange_wait_packets(const uint4* base, const unsigned int* epoch, unsigned int* wait_epoch, int rank, int world, long rows,
