@@ -103,11 +103,11 @@ public:
         const uint32_t ks = tq::kv_layer_seed(static_cast<uint32_t>(layer), 1);  // src/kv_cache.cpp:40-42
         const uint32_t vs = tq::kv_layer_seed(static_cast<uint32_t>(layer), 2);
         const uint32_t qs = tq::kv_layer_seed(static_cast<uint32_t>(layer), 3);
-        tq::launch_kv_encode(d_k, dtype == TQ_F16, static_cast<long>(n_vec), dim_, ks, qs, true,
-                             L.k_words.as<uint32_t>() + off * wph, L.k_norms.as<float>() + off,
-                             L.qjl_words.as<uint32_t>() + off * qph, L.qjl_norms.as<float>() + off, st);
-        tq::launch_kv_encode(d_v, dtype == TQ_F16, static_cast<long>(n_vec), dim_, vs, 0u, false,
-                             L.v_words.as<uint32_t>() + off * wph, L.v_norms.as<float>() + off, nullptr, nullptr, st);
+        const tq::KvEncodeSegment kseg{L.k_words.as<uint32_t>() + off * wph, L.k_norms.as<float>() + off,
+                                       L.qjl_words.as<uint32_t>() + off * qph, L.qjl_norms.as<float>() + off};
+        const tq::KvEncodeSegment vseg{L.v_words.as<uint32_t>() + off * wph, L.v_norms.as<float>() + off, nullptr, nullptr};
+        tq::launch_kv_encode_pair_segments(d_k, d_v, dtype == TQ_F16, static_cast<long>(n_vec), static_cast<long>(n_vec), dim_, ks, vs, qs,
+                                           &kseg, &vseg, 1, st);
         L.num_tokens += tokens;
         seq_length_ = std::max(seq_length_, L.num_tokens);
     }
@@ -157,8 +157,7 @@ public:
             const long n_vec = static_cast<long>(nb) * c0->heads_;
             const char* kp = static_cast<const char*>(keys) + static_cast<size_t>(b0) * vec_bytes;
             const char* vp = static_cast<const char*>(values) + static_cast<size_t>(b0) * vec_bytes;
-            tq::launch_kv_encode_segments(kp, dtype == TQ_F16, n_vec, c0->heads_, c0->dim_, ks, qs, true, kseg, nb, st);
-            tq::launch_kv_encode_segments(vp, dtype == TQ_F16, n_vec, c0->heads_, c0->dim_, vs, 0u, false, vseg, nb, st);
+            tq::launch_kv_encode_pair_segments(kp, vp, dtype == TQ_F16, n_vec, c0->heads_, c0->dim_, ks, vs, qs, kseg, vseg, nb, st);
             for (int i = 0; i < nb; ++i) {
                 TQKVCache* c = caches[b0 + i];
                 LayerKVStorage& L = c->layers_[static_cast<size_t>(layer)];

@@ -166,6 +166,10 @@ struct KvEncodeSegment {
 void launch_kv_encode_segments(const void* x, bool x_is_f16, long n_vec, long vec_per_seg, int head_dim, uint32_t wht_seed,
                                uint32_t qjl_seed, bool with_qjl, const KvEncodeSegment* segs, int n_segs,
                                cudaStream_t stream);
+// keys (with residual bits) and values of the same tokens: one launch when there are fewer than 512 vectors
+void launch_kv_encode_pair_segments(const void* k, const void* v, bool x_is_f16, long n_vec, long vec_per_seg, int head_dim,
+                                    uint32_t k_seed, uint32_t v_seed, uint32_t qjl_seed, const KvEncodeSegment* ksegs,
+                                    const KvEncodeSegment* vsegs, int n_segs, cudaStream_t stream);
 
 // tq_peer.cu — exchange between ranks over peer-mapped memory (plain stores, flags with epochs).
 void launch_exchange_broadcast(const void* src, void* const* dst, int n_dst, int rows, long row_bytes, long src_stride,

@@ -37,14 +37,23 @@ struct KvEncodeDst {
     float* qjl_norms;
 };
 constexpr int kKvEncodeMaxSegments = 32;
-struct KvEncodeTable {
-    KvEncodeDst seg[kKvEncodeMaxSegments];
+template <int NSEG>
+struct KvEncodeTableT {
+    KvEncodeDst seg[NSEG];
 };
+using KvEncodeTable = KvEncodeTableT<kKvEncodeMaxSegments>;
 
-template <int E, typename InT>
+// A second tensor (the values beside the keys of a decode step: x2, wht_seed2, tab2, never with residual bits) rides in
+// the same launch as vectors n_vec .. n_vec + n_vec2 - 1.
+// The segment tables are kernel parameters; NSEG is their capacity (1, 8 or 32 segments): a launch whose parameters
+// run to kilobytes costs the host several microseconds more than a small one, and a decode step appends to one or
+// a few sequences.
+template <int E, typename InT, int NSEG>
 __global__ void __launch_bounds__(128) kv_encode_kernel(const InT* __restrict__ x, long n_vec, uint32_t wht_seed,
-                                                        uint32_t qjl_seed, int with_qjl, float scale, float inv_sqrt,
-                                                        const __grid_constant__ KvEncodeTable tab, long vec_per_seg) {
+                                                        uint32_t qjl_seed, int with_qjl_first, float scale, float inv_sqrt,
+                                                        const __grid_constant__ KvEncodeTableT<NSEG> tab, long vec_per_seg,
+                                                        const InT* __restrict__ x2, long n_vec2, uint32_t wht_seed2,
+                                                        const __grid_constant__ KvEncodeTableT<NSEG> tab2) {
     constexpr int D = 32 * E;
     constexpr int WPH = (D + 9) / 10;
     constexpr int QPH = D / 32;
@@ -60,15 +69,19 @@ __global__ void __launch_bounds__(128) kv_encode_kernel(const InT* __restrict__ 
     const int lane = threadIdx.x & 31, wib = threadIdx.x >> 5;
     const long warp0 = static_cast<long>(blockIdx.x) * 4 + wib;
     const long n_warps = static_cast<long>(gridDim.x) * 4;
-    float sgn[E];
+    for (long gall = warp0; gall < n_vec + n_vec2; gall += n_warps) {
+        const bool second = gall >= n_vec;
+        const long gvec = second ? gall - n_vec : gall;
+        const InT* const xs = second ? x2 : x;
+        const uint32_t seed = second ? wht_seed2 : wht_seed;
+        const int with_qjl = second ? 0 : with_qjl_first;
+        float sgn[E];
 #pragma unroll
-    for (int j = 0; j < E; ++j) sgn[j] = sign_value(wht_seed, static_cast<uint32_t>(lane * E + j));
-
-    for (long gvec = warp0; gvec < n_vec; gvec += n_warps) {
+        for (int j = 0; j < E; ++j) sgn[j] = sign_value(seed, static_cast<uint32_t>(lane * E + j));
         // destination of this vector: segment and position inside it
         const long sidx = gvec / vec_per_seg;
         const long vec = gvec - sidx * vec_per_seg;
-        const KvEncodeDst& dst = tab.seg[sidx];
+        const KvEncodeDst& dst = second ? tab2.seg[sidx] : tab.seg[sidx];
         uint32_t* const words = dst.words;
         float* const norms = dst.norms;
         uint32_t* const qjl_words = dst.qjl_words;
@@ -76,7 +89,7 @@ __global__ void __launch_bounds__(128) kv_encode_kernel(const InT* __restrict__ 
         float v[E];
 #pragma unroll
         for (int j = 0; j < E; ++j) {
-            v[j] = load_as_f32(x, static_cast<size_t>(gvec) * D + lane * E + j);
+            v[j] = load_as_f32(xs, static_cast<size_t>(gvec) * D + lane * E + j);
             s_val[wib][lane * E + j] = v[j];
         }
         __syncwarp();
@@ -1217,6 +1230,51 @@ void launch_kv_encode(const void* x, bool x_is_f16, long n_vec, int head_dim, ui
     launch_kv_encode_segments(x, x_is_f16, n_vec, n_vec, head_dim, wht_seed, qjl_seed, with_qjl, &one, 1, stream);
 }
 
+// The warp-per-vector kernel on one tensor (n2 == 0) or on a tensor and a second one without residual bits.
+template <int NSEG>
+static void launch_kv_encode_small(const void* x, const void* x2, bool x_is_f16, long n_vec, long n2, long vec_per_seg, int head_dim,
+                                   uint32_t seed, uint32_t seed2, uint32_t qjl_seed, bool with_qjl, const KvEncodeSegment* segs,
+                                   const KvEncodeSegment* segs2, int n_segs, cudaStream_t stream) {
+    KvEncodeTableT<NSEG> t1{}, t2{};
+    for (int i = 0; i < n_segs; ++i) {
+        t1.seg[i] = KvEncodeDst{segs[i].words, segs[i].norms, segs[i].qjl_words, segs[i].qjl_norms};
+        if (n2 > 0) t2.seg[i] = KvEncodeDst{segs2[i].words, segs2[i].norms, nullptr, nullptr};
+    }
+    const float scale = std::sqrt(static_cast<float>(head_dim));             // src/kv_cache.cpp:72
+    const float inv_sqrt = 1.0f / std::sqrt(static_cast<float>(head_dim));   // src/rotation.cpp:301
+    const int grid = grid_for_warps(n_vec + n2, 4, 148 * 16);
+#define TQ_ENC2(EV)                                                                                                                 \
+    if (x_is_f16)                                                                                                                   \
+        kv_encode_kernel<EV, __half, NSEG><<<grid, 128, 0, stream>>>(static_cast<const __half*>(x), n_vec, seed, qjl_seed,            \
+                                                                     with_qjl ? 1 : 0, scale, inv_sqrt, t1, vec_per_seg,            \
+                                                                     static_cast<const __half*>(x2), n2, seed2, t2);                \
+    else                                                                                                                            \
+        kv_encode_kernel<EV, float, NSEG><<<grid, 128, 0, stream>>>(static_cast<const float*>(x), n_vec, seed, qjl_seed,              \
+                                                                    with_qjl ? 1 : 0, scale, inv_sqrt, t1, vec_per_seg,             \
+                                                                    static_cast<const float*>(x2), n2, seed2, t2);
+    TQ_D_SWITCH(head_dim, TQ_ENC2)
+#undef TQ_ENC2
+    TQ_CUDA(cudaGetLastError());
+}
+
+// Keys (with residual bits) and values of a few tokens in ONE launch of the warp-per-vector kernel; bulk appends
+// keep one launch per tensor of the batched kernel.
+void launch_kv_encode_pair_segments(const void* k, const void* v, bool x_is_f16, long n_vec, long vec_per_seg, int head_dim,
+                                    uint32_t k_seed, uint32_t v_seed, uint32_t qjl_seed, const KvEncodeSegment* ksegs,
+                                    const KvEncodeSegment* vsegs, int n_segs, cudaStream_t stream) {
+    if (n_vec == 0) return;
+    if (n_vec >= 512) {
+        launch_kv_encode_segments(k, x_is_f16, n_vec, vec_per_seg, head_dim, k_seed, qjl_seed, true, ksegs, n_segs, stream);
+        launch_kv_encode_segments(v, x_is_f16, n_vec, vec_per_seg, head_dim, v_seed, 0u, false, vsegs, n_segs, stream);
+        return;
+    }
+    TQ_REQUIRE(n_segs >= 1 && n_segs <= kKvEncodeMaxSegments, "kv encode: 1..32 segments per launch");
+    TQ_REQUIRE(vec_per_seg > 0 && (n_vec + vec_per_seg - 1) / vec_per_seg <= n_segs, "kv encode: segments do not cover the input");
+    if (n_segs == 1) launch_kv_encode_small<1>(k, v, x_is_f16, n_vec, n_vec, vec_per_seg, head_dim, k_seed, v_seed, qjl_seed, true, ksegs, vsegs, n_segs, stream);
+    else if (n_segs <= 8) launch_kv_encode_small<8>(k, v, x_is_f16, n_vec, n_vec, vec_per_seg, head_dim, k_seed, v_seed, qjl_seed, true, ksegs, vsegs, n_segs, stream);
+    else launch_kv_encode_small<kKvEncodeMaxSegments>(k, v, x_is_f16, n_vec, n_vec, vec_per_seg, head_dim, k_seed, v_seed, qjl_seed, true, ksegs, vsegs, n_segs, stream);
+}
+
 void launch_kv_encode_segments(const void* x, bool x_is_f16, long n_vec, long vec_per_seg, int head_dim, uint32_t wht_seed,
                                uint32_t qjl_seed, bool with_qjl, const KvEncodeSegment* segs, int n_segs,
                                cudaStream_t stream) {
@@ -1257,17 +1315,9 @@ void launch_kv_encode_segments(const void* x, bool x_is_f16, long n_vec, long ve
         TQ_CUDA(cudaGetLastError());
         return;
     }
-    const int grid = grid_for_warps(n_vec, 4, 148 * 16);
-#define TQ_ENC(EV)                                                                                                      \
-    if (x_is_f16)                                                                                                       \
-        kv_encode_kernel<EV, __half><<<grid, 128, 0, stream>>>(static_cast<const __half*>(x), n_vec, wht_seed, qjl_seed, \
-                                                               with_qjl ? 1 : 0, scale, inv_sqrt, tab, vec_per_seg);    \
-    else                                                                                                                \
-        kv_encode_kernel<EV, float><<<grid, 128, 0, stream>>>(static_cast<const float*>(x), n_vec, wht_seed, qjl_seed,   \
-                                                              with_qjl ? 1 : 0, scale, inv_sqrt, tab, vec_per_seg);
-    TQ_D_SWITCH(head_dim, TQ_ENC)
-#undef TQ_ENC
-    TQ_CUDA(cudaGetLastError());
+    if (n_segs == 1) launch_kv_encode_small<1>(x, nullptr, x_is_f16, n_vec, 0, vec_per_seg, head_dim, wht_seed, 0u, qjl_seed, with_qjl, segs, nullptr, n_segs, stream);
+    else if (n_segs <= 8) launch_kv_encode_small<8>(x, nullptr, x_is_f16, n_vec, 0, vec_per_seg, head_dim, wht_seed, 0u, qjl_seed, with_qjl, segs, nullptr, n_segs, stream);
+    else launch_kv_encode_small<kKvEncodeMaxSegments>(x, nullptr, x_is_f16, n_vec, 0, vec_per_seg, head_dim, wht_seed, 0u, qjl_seed, with_qjl, segs, nullptr, n_segs, stream);
 }
 
 void launch_kv_decode_f16(const uint32_t* words, const float* norms, long n_vec, int head_dim, uint32_t wht_seed,
