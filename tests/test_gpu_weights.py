@@ -227,14 +227,15 @@ def test_linear_pinned_host_activation_is_read_fresh(tq, oracle):
     lin.close()
 
 
-@pytest.mark.parametrize("cols,shared", [(1024, True), (5120, True), (768, False), (8192, True)])
-def test_forward_group_equals_separate_forwards(tq, oracle, cols, shared):
+@pytest.mark.parametrize("cols,shared,bs", [(1024, True, 128), (5120, True, 128), (768, False, 128), (8192, True, 128),
+                                             (1024, True, 512), (2048, False, 1024)])
+def test_forward_group_equals_separate_forwards(tq, oracle, cols, shared, bs):
     """tq_linear_forward_group: three layers of different heights (ragged, one smaller than a row tile) with their
     own seeds and norms on one activation in one launch, 1 / 3 / 8 rows, one and several column chunks, shared and
-    dual rotation: every result bit-equal to the layer's own forward, and within tolerance of the oracle."""
+    dual rotation, WHT blocks that are rotated inside the kernel and by the pre-kernel: every result bit-equal to the
+    layer's own forward, and within tolerance of the oracle."""
     import torch
-    rng = np.random.default_rng(cols)
-    bs = 128
+    rng = np.random.default_rng(cols + bs)
     cb = oracle.codebook(4)[0]
     lins, deqs = [], []
     for rows in (272, 9, 130):
