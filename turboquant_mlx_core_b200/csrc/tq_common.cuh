@@ -111,6 +111,28 @@ __host__ __device__ __forceinline__ size_t code_offset(long row, int col, size_t
 
 // Report a failure from a kernel.  The status word may live in page-locked HOST memory (so that
 // the host reads it without a copy): a plain store followed by a system-scope fence, no atomic.
+// Programmatic dependent launch for the small kernels of a decode step: launched with the attribute, a kernel's CTAs are
+// set up while the kernel before it is still draining; they wait here until that kernel has completed (and its
+// writes are visible) before they touch anything, and let the kernel after them start setting up in turn.
+__device__ __forceinline__ void pdl_wait_release() {
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;");
+}
+template <typename Kernel, typename... Args>
+inline void launch_pdl(Kernel kernel, dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args... args) {
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    TQ_CUDA(cudaLaunchKernelEx(&cfg, kernel, args...));
+}
+
 // Threads of a CTA that normalises one row (the RMSNorm kernel and the row-wise all-reduce tails: the same count, so the
 // same order of additions).  A decode step has a handful of rows: the row's latency, not the SM count, is what matters.
 constexpr int kRowNormThreads = 1024;

@@ -54,6 +54,7 @@ __global__ void __launch_bounds__(128) kv_encode_kernel(const InT* __restrict__ 
                                                         const __grid_constant__ KvEncodeTableT<NSEG> tab, long vec_per_seg,
                                                         const InT* __restrict__ x2, long n_vec2, uint32_t wht_seed2,
                                                         const __grid_constant__ KvEncodeTableT<NSEG> tab2) {
+    pdl_wait_release();
     constexpr int D = 32 * E;
     constexpr int WPH = (D + 9) / 10;
     constexpr int QPH = D / 32;
@@ -471,6 +472,7 @@ __global__ void __launch_bounds__(128) attn_combine_kernel(const float* __restri
                                                            long n_rows, int n_splits, uint32_t v_seed, float inv_sqrt,
                                                            float inv_scale_d, __half* __restrict__ out,
                                                            float* __restrict__ lse) {
+    pdl_wait_release();
     constexpr int D = 32 * E;
     const int lane = threadIdx.x & 31;
     const long row = (static_cast<long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
@@ -540,6 +542,7 @@ __global__ void __launch_bounds__(kMmaThreads, 3) attn_mma_kernel(const AttnSeq*
                                                                uint32_t qjl_seed, int use_qjl, float inv_sqrt,
                                                                float inv_scale_d, float attn_scale, float gamma,
                                                                float* __restrict__ part_acc, float* __restrict__ part_ml) {
+    pdl_wait_release();
     constexpr int D = 128, WPH = 13, QPH = 4;
     // The pair table sits at a shared-window address that is a multiple of its size, so that
     // "table base + lane offset" and the scaled index occupy disjoint bits and one logic op
@@ -1245,11 +1248,11 @@ static void launch_kv_encode_small(const void* x, const void* x2, bool x_is_f16,
     const int grid = grid_for_warps(n_vec + n2, 4, 148 * 16);
 #define TQ_ENC2(EV)                                                                                                                 \
     if (x_is_f16)                                                                                                                   \
-        kv_encode_kernel<EV, __half, NSEG><<<grid, 128, 0, stream>>>(static_cast<const __half*>(x), n_vec, seed, qjl_seed,            \
+        launch_pdl(kv_encode_kernel<EV, __half, NSEG>, dim3(grid), dim3(128), 0, stream, static_cast<const __half*>(x), n_vec, seed, qjl_seed, \
                                                                      with_qjl ? 1 : 0, scale, inv_sqrt, t1, vec_per_seg,            \
                                                                      static_cast<const __half*>(x2), n2, seed2, t2);                \
     else                                                                                                                            \
-        kv_encode_kernel<EV, float, NSEG><<<grid, 128, 0, stream>>>(static_cast<const float*>(x), n_vec, seed, qjl_seed,              \
+        launch_pdl(kv_encode_kernel<EV, float, NSEG>, dim3(grid), dim3(128), 0, stream, static_cast<const float*>(x), n_vec, seed, qjl_seed, \
                                                                     with_qjl ? 1 : 0, scale, inv_sqrt, t1, vec_per_seg,             \
                                                                     static_cast<const float*>(x2), n2, seed2, t2);
     TQ_D_SWITCH(head_dim, TQ_ENC2)
@@ -1456,13 +1459,13 @@ void launch_kv_attention(const void* d_seqs, int n_seqs, const void* q, bool q_i
                                                                  static_cast<const float*>(q), q_heads, kv_heads,        \
                                                                  n_splits, k_seed, qjl_seed, use_qjl ? 1 : 0, inv_sqrt,   \
                                                                  inv_scale_d, attn_scale, gamma, part_acc, part_ml);     \
-    attn_combine_kernel<EV><<<static_cast<int>((n_rows + 3) / 4), 128, 0, stream>>>(part_acc, part_ml, n_rows, n_splits, \
-                                                                                   v_seed, inv_sqrt, inv_scale_d, out, lse);
+    launch_pdl(attn_combine_kernel<EV>, dim3(static_cast<unsigned>((n_rows + 3) / 4)), dim3(128), 0, stream, part_acc, part_ml, n_rows, \
+               n_splits, v_seed, inv_sqrt, inv_scale_d, out, lse);
     if (plan.tensor_memory) {
         launch_attn_tc(static_cast<const AttnSeq*>(d_seqs), n_seqs, q, q_is_f16, q_heads, kv_heads, n_splits, k_seed, qjl_seed, use_qjl,
                        inv_sqrt, inv_scale_d, attn_scale, gamma, part_acc, part_ml, status, stream);
-        attn_combine_kernel<4><<<static_cast<int>((n_rows + 3) / 4), 128, 0, stream>>>(part_acc, part_ml, n_rows, n_splits,
-                                                                                      v_seed, inv_sqrt, inv_scale_d, out, lse);
+        launch_pdl(attn_combine_kernel<4>, dim3(static_cast<unsigned>((n_rows + 3) / 4)), dim3(128), 0, stream, part_acc, part_ml, n_rows,
+                   n_splits, v_seed, inv_sqrt, inv_scale_d, out, lse);
         TQ_CUDA(cudaGetLastError());
         return;
     }
@@ -1484,24 +1487,22 @@ void launch_kv_attention(const void* d_seqs, int n_seqs, const void* q, bool q_i
             TQ_PIPE(1)
         }
 #undef TQ_PIPE
-        attn_combine_kernel<4><<<static_cast<int>((n_rows + 3) / 4), 128, 0, stream>>>(part_acc, part_ml, n_rows, n_splits,
-                                                                                      v_seed, inv_sqrt, inv_scale_d, out, lse);
+        launch_pdl(attn_combine_kernel<4>, dim3(static_cast<unsigned>((n_rows + 3) / 4)), dim3(128), 0, stream, part_acc, part_ml, n_rows,
+                   n_splits, v_seed, inv_sqrt, inv_scale_d, out, lse);
         TQ_CUDA(cudaGetLastError());
         return;
     }
     if (head_dim == 128) {
         if (q_is_f16)
-            attn_mma_kernel<__half><<<grid, kMmaThreads, 0, stream>>>(static_cast<const AttnSeq*>(d_seqs),
-                                                                        static_cast<const __half*>(q), q_heads, kv_heads,
-                                                                        n_splits, k_seed, qjl_seed, use_qjl ? 1 : 0, inv_sqrt,
-                                                                        inv_scale_d, attn_scale, gamma, part_acc, part_ml);
+            launch_pdl(attn_mma_kernel<__half>, grid, dim3(kMmaThreads), 0, stream, static_cast<const AttnSeq*>(d_seqs),
+                       static_cast<const __half*>(q), q_heads, kv_heads, n_splits, k_seed, qjl_seed, use_qjl ? 1 : 0, inv_sqrt,
+                       inv_scale_d, attn_scale, gamma, part_acc, part_ml);
         else
-            attn_mma_kernel<float><<<grid, kMmaThreads, 0, stream>>>(static_cast<const AttnSeq*>(d_seqs),
-                                                                       static_cast<const float*>(q), q_heads, kv_heads,
-                                                                       n_splits, k_seed, qjl_seed, use_qjl ? 1 : 0, inv_sqrt,
-                                                                       inv_scale_d, attn_scale, gamma, part_acc, part_ml);
-        attn_combine_kernel<4><<<static_cast<int>((n_rows + 3) / 4), 128, 0, stream>>>(part_acc, part_ml, n_rows, n_splits,
-                                                                                      v_seed, inv_sqrt, inv_scale_d, out, lse);
+            launch_pdl(attn_mma_kernel<float>, grid, dim3(kMmaThreads), 0, stream, static_cast<const AttnSeq*>(d_seqs),
+                       static_cast<const float*>(q), q_heads, kv_heads, n_splits, k_seed, qjl_seed, use_qjl ? 1 : 0, inv_sqrt,
+                       inv_scale_d, attn_scale, gamma, part_acc, part_ml);
+        launch_pdl(attn_combine_kernel<4>, dim3(static_cast<unsigned>((n_rows + 3) / 4)), dim3(128), 0, stream, part_acc, part_ml, n_rows,
+                   n_splits, v_seed, inv_sqrt, inv_scale_d, out, lse);
         TQ_CUDA(cudaGetLastError());
         return;
     }
