@@ -886,6 +886,7 @@ __global__ void __launch_bounds__(32 * GH, kPipeWarpsPerSm / GH) attn_pipe_kerne
                                                                     float inv_scale_d, float attn_scale, float gamma,
                                                                     float* __restrict__ part_acc, float* __restrict__ part_ml,
                                                                     unsigned int* __restrict__ status) {
+    pdl_wait_release();
     using LY = PipeLayout<GH>;
     constexpr int D = 128;
     extern __shared__ __align__(16) unsigned char pipe_smem[];
@@ -1427,9 +1428,8 @@ static void launch_attn_pipe(const AttnSeq* seqs, int n_seqs, const QT* q, int q
     }
     const int gchunks = (q_heads / kv_heads + kAttnGMax - 1) / kAttnGMax;
     const dim3 grid(n_splits, (kv_heads / GH) * gchunks, n_seqs);
-    attn_pipe_kernel<GH, QT><<<grid, 32 * GH, PipeLayout<GH>::kSmemBytes, stream>>>(seqs, q, q_heads, kv_heads, n_splits, k_seed, qjl_seed,
-                                                                                  use_qjl ? 1 : 0, inv_sqrt, inv_scale_d, attn_scale,
-                                                                                  gamma, part_acc, part_ml, status);
+    launch_pdl(attn_pipe_kernel<GH, QT>, grid, dim3(32 * GH), PipeLayout<GH>::kSmemBytes, stream, seqs, q, q_heads, kv_heads, n_splits, k_seed,
+               qjl_seed, use_qjl ? 1 : 0, inv_sqrt, inv_scale_d, attn_scale, gamma, part_acc, part_ml, status);
 }
 
 void launch_kv_attention(const void* d_seqs, int n_seqs, const void* q, bool q_is_f16, int q_heads, int kv_heads,
