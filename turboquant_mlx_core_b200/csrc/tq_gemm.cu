@@ -177,6 +177,7 @@ template <int E>
 __global__ void __launch_bounds__(128) rotate_rows_f16_kernel(const __half* __restrict__ x, __half* __restrict__ xrot,
                                                               int in, long rows, int n_planes, uint32_t seed_p,
                                                               uint32_t seed_r, float inv_sqrt) {
+    pdl_wait_release();   // x, and the scratch this kernel overwrites, belong to the kernels before it until they are done
     constexpr int BS = 32 * E;
     constexpr int V = E < 8 ? E : 8;  // halves per vector store (one core-matrix row holds 8)
     const int lane = threadIdx.x & 31;
@@ -220,6 +221,7 @@ __global__ void __launch_bounds__(128) rotate_rows_f16_kernel(const __half* __re
 __global__ void __launch_bounds__(256) rotate_rows_f16_wide_kernel(const __half* __restrict__ x, __half* __restrict__ xrot,
                                                                    int in, long rows, int n_planes, int block,
                                                                    uint32_t seed_p, uint32_t seed_r, float inv_sqrt) {
+    pdl_wait_release();   // x, and the scratch this kernel overwrites, belong to the kernels before it until they are done
     const int lane = threadIdx.x & 31, wib = threadIdx.x >> 5;
     const long groups_per_row = (in + 255) / 256;
     const long row_groups = (rows + 7) / 8;
@@ -443,6 +445,10 @@ __global__ void __launch_bounds__(kGemmThreads, 1) tq8_gemm_kernel(const GemmArg
         // One thread runs the whole loop; ring slot and phase are kept incrementally (no divisions on
         // this serial path).
         if (lane == 0) {
+            // The rotated activations are the only input the kernel before this one produces (launched with the
+            // programmatic-dependency attribute, the CTA has set up its barriers, tensor memory and tables and the
+            // producers are already streaming codes meanwhile): wait for that kernel here.
+            asm volatile("griddepcontrol.wait;" ::: "memory");
             const size_t n_tok_tiles = (static_cast<size_t>(p.m) + kTileTok - 1) / kTileTok;
             int slot = 0;
             uint32_t par = 1u;   // parity of the "empty" phase to wait for
@@ -467,6 +473,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1) tq8_gemm_kernel(const GemmArg
                 }
                 if (++slot == n_st) { slot = 0; par ^= 1u; }
             }
+            // every activation tile of this CTA is on its way: the kernel after this one may start setting up
+            asm volatile("griddepcontrol.launch_dependents;");
         }
         __syncwarp();
     } else {
@@ -544,6 +552,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) tq8_gemm_kernel(const GemmArg
 __global__ void __launch_bounds__(256) gemm_finish_kernel(const float* __restrict__ partial, const float* __restrict__ norms,
                                                           __half* __restrict__ y, long y_stride, long m, int out, int k_splits,
                                                           float inv_scale) {
+    pdl_wait_release();
     const long n = m * out;
     for (long i = static_cast<long>(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += static_cast<long>(gridDim.x) * blockDim.x) {
         float acc = 0.f;
@@ -599,12 +608,12 @@ void launch_tq8_gemm(const uint8_t* codes, const float* norms, const float* tabl
         const unsigned int grid = static_cast<unsigned int>((n_warps + 3) / 4);
         const long wide_blocks = static_cast<long>(n_planes) * ((in + 255) / 256) * ((m + 7) / 8);
         if (block <= 256 && reinterpret_cast<uintptr_t>(x) % 16 == 0 && wide_blocks < (1L << 31)) {
-            rotate_rows_f16_wide_kernel<<<static_cast<unsigned int>(wide_blocks), 256, 0, stream>>>(
-                x, xrot, in, m, n_planes, static_cast<int>(block), seed_p, seed_r, inv_sqrt);
+            launch_pdl(rotate_rows_f16_wide_kernel, dim3(static_cast<unsigned int>(wide_blocks)), dim3(256), 0, stream, x, xrot, in, m,
+                       n_planes, static_cast<int>(block), seed_p, seed_r, inv_sqrt);
         } else
 #define TQ_ROT16_CASE(EV)                                                                                          \
     case 32 * EV:                                                                                                  \
-        rotate_rows_f16_kernel<EV><<<grid, 128, 0, stream>>>(x, xrot, in, m, n_planes, seed_p, seed_r, inv_sqrt);  \
+        launch_pdl(rotate_rows_f16_kernel<EV>, dim3(grid), dim3(128), 0, stream, x, xrot, in, m, n_planes, seed_p, seed_r, inv_sqrt); \
         break;
         switch (block) {
             TQ_ROT16_CASE(1) TQ_ROT16_CASE(2) TQ_ROT16_CASE(4) TQ_ROT16_CASE(8) TQ_ROT16_CASE(16) TQ_ROT16_CASE(32)
@@ -632,12 +641,12 @@ void launch_tq8_gemm(const uint8_t* codes, const float* norms, const float* tabl
     }
     const dim3 grid(static_cast<unsigned int>((out + kTileRows - 1) / kTileRows),
                     static_cast<unsigned int>((m + kTileTok - 1) / kTileTok), static_cast<unsigned int>(a.k_splits));
-    tq8_gemm_kernel<<<grid, kGemmThreads, smem, stream>>>(a);
+    launch_pdl(tq8_gemm_kernel, grid, dim3(kGemmThreads), smem, stream, a);
     TQ_CUDA(cudaGetLastError());
     if (a.k_splits > 1) {
         const long n = m * out;
         const unsigned int blocks = static_cast<unsigned int>(std::min<long>((n + 255) / 256, 148L * 8));
-        gemm_finish_kernel<<<blocks, 256, 0, stream>>>(a.partial, norms, y, y_stride, m, out, a.k_splits, a.inv_scale);
+        launch_pdl(gemm_finish_kernel, dim3(blocks), dim3(256), 0, stream, a.partial, norms, y, y_stride, m, out, a.k_splits, a.inv_scale);
         TQ_CUDA(cudaGetLastError());
     }
 }
