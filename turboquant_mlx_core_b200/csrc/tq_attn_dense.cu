@@ -31,6 +31,7 @@ template <typename InT>
 __global__ void __launch_bounds__(256) ring_write_kernel(const InT* __restrict__ src_k, const InT* __restrict__ src_v, long n_tokens,
                                                          long src_token0, int row, int window, long slot0, __half* __restrict__ ring_k,
                                                          __half* __restrict__ ring_v) {
+    pdl_wait_release();
     // token t of the source (counted from src_token0) goes to slot (slot0 + t) % window; `row` = heads * dim
     const long total = n_tokens * row;
     for (long i = static_cast<long>(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += static_cast<long>(gridDim.x) * blockDim.x) {
@@ -263,6 +264,7 @@ __global__ void __launch_bounds__(128, 3) dense_attn_mma_kernel(const __half* __
                                                                 int n_tokens, int kv_heads, int q_heads, const QT* __restrict__ q,
                                                                 int n_splits, float scale, float* __restrict__ part_acc,
                                                                 float* __restrict__ part_ml) {
+    pdl_wait_release();
     constexpr int D = 128;
     __shared__ __half s_q[8][D + 8];
     __shared__ float s_m[4][8], s_l[4][8];
@@ -411,6 +413,7 @@ __global__ void __launch_bounds__(128, 3) dense_attn_mma_kernel(const __half* __
 
 __global__ void __launch_bounds__(128) dense_combine_kernel(const float* __restrict__ part_acc, const float* __restrict__ part_ml,
                                                             int q_heads, int D, int n_splits, __half* __restrict__ out) {
+    pdl_wait_release();
     const int h = blockIdx.x;
     if (h >= q_heads) return;
     float M = -INFINITY;
@@ -439,11 +442,11 @@ void launch_ring_write(const void* keys, const void* values, bool is_f16, long n
     const long total = n_tokens * row;
     const int blocks = static_cast<int>(std::min<long>((total + 255) / 256, 148L * 8));
     if (is_f16)
-        ring_write_kernel<__half><<<blocks, 256, 0, stream>>>(static_cast<const __half*>(keys), static_cast<const __half*>(values), n_tokens,
-                                                             src_token0, row, window, slot0, ring_k, ring_v);
+        launch_pdl(ring_write_kernel<__half>, dim3(blocks), dim3(256), 0, stream, static_cast<const __half*>(keys),
+                   static_cast<const __half*>(values), n_tokens, src_token0, row, window, slot0, ring_k, ring_v);
     else
-        ring_write_kernel<float><<<blocks, 256, 0, stream>>>(static_cast<const float*>(keys), static_cast<const float*>(values), n_tokens,
-                                                            src_token0, row, window, slot0, ring_k, ring_v);
+        launch_pdl(ring_write_kernel<float>, dim3(blocks), dim3(256), 0, stream, static_cast<const float*>(keys),
+                   static_cast<const float*>(values), n_tokens, src_token0, row, window, slot0, ring_k, ring_v);
     TQ_CUDA(cudaGetLastError());
 }
 
@@ -489,12 +492,12 @@ void launch_dense_attention(const __half* keys, const __half* values, int n_toke
     static const bool cuda_core_only = std::getenv("TQ_WINDOW_ATTENTION_FMA") != nullptr;   // measurement switch: the fp32-FMA kernel at head_dim 128
     if (head_dim == 128 && !cuda_core_only) {
         if (q_is_f16)
-            dense_attn_mma_kernel<__half><<<grid, 128, 0, stream>>>(keys, values, n_tokens, kv_heads, q_heads, static_cast<const __half*>(q),
-                                                                    n_splits, scale, part_acc, part_ml);
+            launch_pdl(dense_attn_mma_kernel<__half>, grid, dim3(128), 0, stream, keys, values, n_tokens, kv_heads, q_heads,
+                       static_cast<const __half*>(q), n_splits, scale, part_acc, part_ml);
         else
-            dense_attn_mma_kernel<float><<<grid, 128, 0, stream>>>(keys, values, n_tokens, kv_heads, q_heads, static_cast<const float*>(q),
-                                                                   n_splits, scale, part_acc, part_ml);
-        dense_combine_kernel<<<q_heads, 128, 0, stream>>>(part_acc, part_ml, q_heads, head_dim, n_splits, out);
+            launch_pdl(dense_attn_mma_kernel<float>, grid, dim3(128), 0, stream, keys, values, n_tokens, kv_heads, q_heads,
+                       static_cast<const float*>(q), n_splits, scale, part_acc, part_ml);
+        launch_pdl(dense_combine_kernel, dim3(q_heads), dim3(128), 0, stream, part_acc, part_ml, q_heads, head_dim, n_splits, out);
         TQ_CUDA(cudaGetLastError());
         return;
     }
@@ -506,7 +509,7 @@ void launch_dense_attention(const __half* keys, const __half* values, int n_toke
         default: throw Error("window attention: head_dim must be 32, 64, 128 or 256");
     }
 #undef TQ_DENSE
-    dense_combine_kernel<<<q_heads, 128, 0, stream>>>(part_acc, part_ml, q_heads, head_dim, n_splits, out);
+    launch_pdl(dense_combine_kernel, dim3(q_heads), dim3(128), 0, stream, part_acc, part_ml, q_heads, head_dim, n_splits, out);
     TQ_CUDA(cudaGetLastError());
 }
 
