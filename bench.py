@@ -921,7 +921,7 @@ def bench_decoder_layer(tq, L, device, stream, cbs, args):
             us = time_pass(lins, xs, ys, batch, 10)
             res[f"{tag}b{batch}"] = {"us_per_layer": us, "tok_per_s": batch / (us * 1e-6), "code_gb_per_s": code_bytes / (us * 1e-6) / 1e9,
                                      "launches_per_layer": len(shp) if batch <= 8 else None}
-            if tag == "" and batch <= 8:
+            if tag == "":
                 # the same seven separately quantised matrices, q / k / v and gate / up each as ONE grouped launch
                 grouped = [[0, 1, 2], [3], [4, 5], [6]]
                 us = time_pass(lins, xs, ys, batch, 10, groups=grouped)
@@ -1296,14 +1296,9 @@ def bench_c4_decode_step(tq, L, device, stream, rank, world, cbs, args):
             if li == 0:      # later layers' input norm comes out of the previous layer's last all-reduce kernel
                 chk(L.tq_rmsnorm_f16(C.c_void_p(x.data_ptr()), C.c_void_p(w["n1"].data_ptr()), C.c_void_p(h1.data_ptr()), batch, hidden, 1e-6, sp))
             mark("rmsnorm_1")
-            if batch <= 8:
-                # q, k and v read the same activation: one grouped launch (bit-equal to the three calls)
-                chk(L.tq_linear_forward_group((C.c_void_p * 3)(w["q"], w["k"], w["v"]), 3, C.c_void_p(h1.data_ptr()), batch,
-                                              (C.c_void_p * 3)(q.data_ptr(), k.data_ptr(), v.data_ptr()), sp))
-            else:
-                fwd(w["q"], h1.data_ptr(), batch, q.data_ptr())
-                fwd(w["k"], h1.data_ptr(), batch, k.data_ptr())
-                fwd(w["v"], h1.data_ptr(), batch, v.data_ptr())
+            # q, k and v read the same activation: one grouped launch per kernel of the path (bit-equal to the three calls)
+            chk(L.tq_linear_forward_group((C.c_void_p * 3)(w["q"], w["k"], w["v"]), 3, C.c_void_p(h1.data_ptr()), batch,
+                                          (C.c_void_p * 3)(q.data_ptr(), k.data_ptr(), v.data_ptr()), sp))
             mark("q_k_v")
             chk(L.tq_rope_qk_f16(C.c_void_p(q.data_ptr()), C.c_void_p(k.data_ptr()), C.c_void_p(pos.data_ptr()), batch, qh, kvh, dim, 1e6, sp))
             mark("rope_q_k")
@@ -1396,7 +1391,7 @@ def bench_c4_decode_step(tq, L, device, stream, rank, world, cbs, args):
         res[f"b{batch}"] = {"us_per_layer": us, "tok_per_s_64_layers": batch / (us * 1e-6 * n_model_layers),
                             "gb_per_s_per_gpu": (weight_bytes + kv_bytes) / (us * 1e-6) / 1e9,
                             "bytes_per_layer_per_gpu": weight_bytes + kv_bytes, "distinct_layers_cycled": n_layers,
-                            "kernels_per_layer": "q + k + v (one grouped launch up to 8 rows), rope of q and k, kv append x2, attention, o_proj, "
+                            "kernels_per_layer": "q + k + v (one grouped launch), rope of q and k, kv append x2, attention, o_proj, "
                                                  "[copy to peers, wait,] sum + residual + rmsnorm, gate-up, swiglu, down, [copy to peers, wait,] "
                                                  "sum + residual + the next layer's rmsnorm",
                             "all_reduce": ("none (one rank)" if exchange is None else

@@ -226,10 +226,11 @@ int tq_linear_forward_scatter(tq_linear_t lin, const void* x_fp16_device, int ba
                               long dst_row_stride, long row_offset, void* stream);
 
 /** Several layers that multiply the same activation (q / k / v, gate / up: 1..4 handles with the same
- *  in_features and rotation mode, 1..8 activation rows, x and every y[i] device fp16) in ONE kernel launch:
- *  y[i] = [batch, out_features of layer i], each bit-equal to tq_linear_forward on that layer alone.
- *  The SMs are divided among the layers in proportion to their sizes, so a decode step's small
- *  projections pay the launch and the kernel's set-up once.  Stands in for consecutive calls of the
+ *  in_features, WHT block and rotation mode; x and every y[i] device fp16) in ONE launch of each kernel
+ *  of the path: y[i] = [batch, out_features of layer i], each bit-equal to tq_linear_forward on that
+ *  layer alone.  Up to 8 rows the SMs of the decode kernel are divided among the layers in proportion to
+ *  their sizes; from 9 rows on the group shares one rotation launch, one tensor-memory GEMM launch and
+ *  one split-K finish.  A decode step's small projections pay the launches and the set-up once.  Stands in for consecutive calls of the
  *  reference's forward (src/linear.cpp:19-28) on the same input. */
 int tq_linear_forward_group(const tq_linear_t* lins, int n, const void* x_fp16_device, int batch, void* const* y_fp16_device,
                             void* stream);

@@ -245,7 +245,7 @@ def test_forward_group_equals_separate_forwards(tq, oracle, cols, shared, bs):
                                         tq.codebook_from_centroids(cb), bs))
         deq = oracle.dequantize_weight(pp, pr, norms, seeds, cb, cb, bs).astype(np.float64)
         deqs.append(deq)
-    for batch in (1, 3, 8):
+    for batch in (1, 3, 8, 11, 40, 300):     # decode kernel up to 8 rows, tensor-memory GEMM above (two token tiles at 300)
         x = torch.from_numpy(rng.standard_normal((batch, cols)).astype(np.float16)).cuda()
         got = tq.forward_group(lins, x)
         torch.cuda.synchronize()

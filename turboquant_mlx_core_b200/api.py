@@ -348,9 +348,9 @@ class TurboQuantLinear:
 
 
 def forward_group(linears, x, outs=None, stream=None):
-    """Several TurboQuantLinear layers on the same device activation x ([batch <= 8, in] fp16 torch tensor) in one
-    kernel launch (tq_linear_forward_group): returns the list of fp16 [batch, out_i] results, each bit-equal to
-    linears[i].forward(x).  The layers must share in_features and the rotation mode (q / k / v, gate / up)."""
+    """Several TurboQuantLinear layers on the same device activation x ([batch, in] fp16 torch tensor) in one launch
+    of each kernel of the path (tq_linear_forward_group): returns the list of fp16 [batch, out_i] results, each bit-equal
+    to linears[i].forward(x).  The layers must share in_features, the WHT block and the rotation mode (q / k / v, gate / up)."""
     import torch
     if not linears or len(linears) > 4:
         raise ValueError("forward_group takes 1..4 layers")

@@ -212,6 +212,20 @@ public:
         it.scratch = scratch_.as<void>(); it.status = d_status_;
         return it;
     }
+    // The same for batches that go to the tensor-memory GEMM (scratch for `batch` rows is reserved here).
+    tq::GemmGroupItem gemm_group_item(void* y, int batch) {
+        const int planes = dual_ ? 2 : 1;
+        gemm_scratch_.reserve(tq::gemm_scratch_bytes(out_, in_, batch, planes, sm_count_));
+        tq::GemmGroupItem it{};
+        it.codes = codes_.as<uint8_t>(); it.norms = norms_.as<float>(); it.table = tables_.as<float>();
+        it.y = static_cast<__half*>(y);
+        it.out = out_; it.in = in_; it.block = block_; it.n_planes = planes;
+        it.seed_p = seed_p_; it.seed_r = seed_r_;
+        it.scratch = gemm_scratch_.as<void>(); it.status = d_status_;
+        return it;
+    }
+    bool gemm_path(int batch) const { return batch > kGemmMinBatch && tq::gemm_supported(in_); }
+    int block_size() const { return static_cast<int>(block_); }
     int device() const { return device_; }
     int sm_count() const { return sm_count_; }
 
@@ -474,21 +488,35 @@ int tq_linear_forward_group(const tq_linear_t* lins, int n, const void* x_fp16_d
     return guarded<int>(0, -1, [&]() {
         TQ_REQUIRE(lins && y_fp16_device && x_fp16_device, "tq_linear_forward_group: NULL argument");
         TQ_REQUIRE(n >= 1 && n <= 4, "tq_linear_forward_group: 1..4 layers");
-        TQ_REQUIRE(batch >= 1 && batch <= 8, "tq_linear_forward_group: batch must be 1..8");
+        TQ_REQUIRE(batch >= 1, "tq_linear_forward_group: batch must be positive");
         TQ_REQUIRE(tq::is_device_pointer(x_fp16_device), "tq_linear_forward_group: x must be a device pointer");
-        tq::GemvGroupItem items[4];
         for (int i = 0; i < n; ++i) {
             TQ_REQUIRE(lins[i] && lins[i]->impl, "tq_linear_forward_group: NULL handle");
             TQ_REQUIRE(y_fp16_device[i] && tq::is_device_pointer(y_fp16_device[i]), "tq_linear_forward_group: y must be device pointers");
             TQ_REQUIRE(lins[i]->impl->device() == lins[0]->impl->device(), "tq_linear_forward_group: layers on different devices");
             TQ_REQUIRE(lins[i]->impl->in_features() == lins[0]->impl->in_features() &&
-                       lins[i]->impl->shared_rotation() == lins[0]->impl->shared_rotation(),
-                       "tq_linear_forward_group: the layers must share in_features and the rotation mode");
-            items[i] = lins[i]->impl->group_item(y_fp16_device[i]);
+                       lins[i]->impl->shared_rotation() == lins[0]->impl->shared_rotation() &&
+                       lins[i]->impl->block_size() == lins[0]->impl->block_size(),
+                       "tq_linear_forward_group: the layers must share in_features, the WHT block and the rotation mode");
         }
         TQ_CUDA(cudaSetDevice(lins[0]->impl->device()));
-        tq::launch_tq8_gemv_group(items, n, static_cast<const __half*>(x_fp16_device), batch, lins[0]->impl->sm_count(),
-                                  static_cast<cudaStream_t>(stream));
+        cudaStream_t st = static_cast<cudaStream_t>(stream);
+        if (lins[0]->impl->gemm_path(batch)) {
+            // 9 rows and up: one rotation launch, one tensor-memory GEMM launch and one split-K finish for the group
+            tq::GemmGroupItem items[4];
+            for (int i = 0; i < n; ++i) items[i] = lins[i]->impl->gemm_group_item(y_fp16_device[i], batch);
+            tq::launch_tq8_gemm_group(items, n, static_cast<const __half*>(x_fp16_device), batch, lins[0]->impl->sm_count(), st);
+            return 0;
+        }
+        // the decode kernel takes up to 8 rows per launch
+        for (int b0 = 0; b0 < batch; b0 += 8) {
+            const int nb = batch - b0 < 8 ? batch - b0 : 8;
+            tq::GemvGroupItem items[4];
+            for (int i = 0; i < n; ++i)
+                items[i] = lins[i]->impl->group_item(static_cast<__half*>(y_fp16_device[i]) + static_cast<size_t>(b0) * lins[i]->impl->out_features());
+            tq::launch_tq8_gemv_group(items, n, static_cast<const __half*>(x_fp16_device) + static_cast<size_t>(b0) * lins[0]->impl->in_features(),
+                                      nb, lins[0]->impl->sm_count(), st);
+        }
         return 0;
     });
 }

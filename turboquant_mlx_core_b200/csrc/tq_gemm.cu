@@ -218,10 +218,8 @@ __global__ void __launch_bounds__(128) rotate_rows_f16_kernel(const __half* __re
 // of one row, lane l the 8 columns 8l..8l+7 (one core-matrix row of the output tile); butterfly
 // stages below 8 stay in the lane, the rest are lane exchanges (the add tree of warp_fwht).  The
 // 8 warps of a CTA take 8 consecutive rows, so their stores complete whole 128-byte core matrices.
-__global__ void __launch_bounds__(256) rotate_rows_f16_wide_kernel(const __half* __restrict__ x, __half* __restrict__ xrot,
-                                                                   int in, long rows, int n_planes, int block,
-                                                                   uint32_t seed_p, uint32_t seed_r, float inv_sqrt) {
-    pdl_wait_release();   // x, and the scratch this kernel overwrites, belong to the kernels before it until they are done
+__device__ __forceinline__ void rotate_rows_wide_body(const __half* __restrict__ x, __half* __restrict__ xrot, int in, long rows,
+                                                      int n_planes, int block, uint32_t seed_p, uint32_t seed_r, float inv_sqrt) {
     const int lane = threadIdx.x & 31, wib = threadIdx.x >> 5;
     const long groups_per_row = (in + 255) / 256;
     const long row_groups = (rows + 7) / 8;
@@ -276,6 +274,22 @@ __global__ void __launch_bounds__(256) rotate_rows_f16_wide_kernel(const __half*
     for (int j = 0; j < 8; ++j) hv[j] = __float2half_rn(v[j] * inv_sqrt);
     *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<const uint4*>(hv);
 }
+__global__ void __launch_bounds__(256) rotate_rows_f16_wide_kernel(const __half* __restrict__ x, __half* __restrict__ xrot,
+                                                                   int in, long rows, int n_planes, int block,
+                                                                   uint32_t seed_p, uint32_t seed_r, float inv_sqrt) {
+    pdl_wait_release();   // x, and the scratch this kernel overwrites, belong to the kernels before it until they are done
+    rotate_rows_wide_body(x, xrot, in, rows, n_planes, block, seed_p, seed_r, inv_sqrt);
+}
+// The same rows rotated for several matrices at once (their own seeds and destinations): blockIdx.y = matrix.
+struct RotateGroupArgs {
+    __half* xrot[4];
+    uint32_t seed_p[4], seed_r[4];
+};
+__global__ void __launch_bounds__(256) rotate_rows_f16_wide_group_kernel(const __half* __restrict__ x, const RotateGroupArgs g, int in,
+                                                                         long rows, int n_planes, int block, float inv_sqrt) {
+    pdl_wait_release();
+    rotate_rows_wide_body(x, g.xrot[blockIdx.y], in, rows, n_planes, block, g.seed_p[blockIdx.y], g.seed_r[blockIdx.y], inv_sqrt);
+}
 
 struct GemmArgs {
     const uint8_t* codes;   // joint bytes in 16 x 64 tiles (code_offset)
@@ -291,14 +305,15 @@ struct GemmArgs {
     float inv_scale;
 };
 
-__global__ void __launch_bounds__(kGemmThreads, 1) tq8_gemm_kernel(const GemmArgs p) {
+// One CTA's work: output tile (row tile bx, token tile blockIdx.y), K split bz of matrix p.
+__device__ __forceinline__ void gemm_body(const GemmArgs& p, const int bx, const int bz) {
     extern __shared__ __align__(128) uint8_t gemm_smem[];
     __shared__ __align__(8) unsigned long long s_full[kStagesMax], s_empty[kStagesMax], s_accum;
     __shared__ uint32_t s_tmem_base;
     __shared__ unsigned int s_abort;
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int row0 = blockIdx.x * kTileRows;  // first weight row of the tile
+    const int row0 = bx * kTileRows;  // first weight row of the tile
     const int tok0 = blockIdx.y * kTileTok;   // first activation row of the tile
     // Activation rows this tile really has, rounded up to the MMA's granularity of 16: a short tile
     // (a decode batch of 9..64 rows, or the tail of a prefill) costs a short MMA and a short copy.
@@ -358,8 +373,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1) tq8_gemm_kernel(const GemmArg
     // A stage is two consecutive K blocks of the range (the last one may hold a single block).
     const int kb_per_plane = p.in / kBlockK;
     const int n_kb_total = kb_per_plane * p.n_planes;
-    const int kb_base = static_cast<int>(static_cast<long>(n_kb_total) * blockIdx.z / p.k_splits);
-    const int n_kb = static_cast<int>(static_cast<long>(n_kb_total) * (blockIdx.z + 1) / p.k_splits) - kb_base;
+    const int kb_base = static_cast<int>(static_cast<long>(n_kb_total) * bz / p.k_splits);
+    const int n_kb = static_cast<int>(static_cast<long>(n_kb_total) * (bz + 1) / p.k_splits) - kb_base;
     const int n_it = (n_kb + kSubPerStage - 1) / kSubPerStage;
 
     if (warp < kProducerWarps) {
@@ -534,7 +549,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) tq8_gemm_kernel(const GemmArg
                     const int tok = tok0 + col0 + j;
                     if (r_ok && tok < p.m) {
                         if (p.k_splits == 1) p.y[static_cast<size_t>(tok) * p.y_stride + r] = __float2half_rn(__uint_as_float(v[j]) * scale);
-                        else p.partial[(static_cast<size_t>(blockIdx.z) * p.m + tok) * p.out + r] = __uint_as_float(v[j]);
+                        else p.partial[(static_cast<size_t>(bz) * p.m + tok) * p.out + r] = __uint_as_float(v[j]);
                     }
                 }
             }
@@ -548,6 +563,27 @@ __global__ void __launch_bounds__(kGemmThreads, 1) tq8_gemm_kernel(const GemmArg
     }
 }
 
+__global__ void __launch_bounds__(kGemmThreads, 1) tq8_gemm_kernel(const GemmArgs p) {
+    gemm_body(p, static_cast<int>(blockIdx.x), static_cast<int>(blockIdx.z));
+}
+
+// Several matrices that multiply the same activation rows (q / k / v, gate / up) in one launch: gridDim.x is cut into
+// one range of row tiles per matrix, gridDim.z is the largest K split of the group (CTAs beyond a matrix's own split
+// count leave at once).  Every matrix brings its own rotated activations (its own seeds), scratch and status word.
+constexpr int kMaxGemmGroup = 4;
+struct GemmGroupArgs {
+    GemmArgs m[kMaxGemmGroup];
+    int tile_start[kMaxGemmGroup + 1];   // row tiles tile_start[i] .. tile_start[i + 1] - 1 belong to matrix i
+    int n;
+};
+__global__ void __launch_bounds__(kGemmThreads, 1) tq8_gemm_group_kernel(const __grid_constant__ GemmGroupArgs grp) {
+    const int b = static_cast<int>(blockIdx.x);
+    int i = 0;
+    while (i + 1 < grp.n && b >= grp.tile_start[i + 1]) ++i;
+    if (static_cast<int>(blockIdx.z) >= grp.m[i].k_splits) return;
+    gemm_body(grp.m[i], b - grp.tile_start[i], static_cast<int>(blockIdx.z));
+}
+
 // y = fp16(norm * inv_scale * sum over K splits, in split order) — fixed order, run-to-run identical.
 __global__ void __launch_bounds__(256) gemm_finish_kernel(const float* __restrict__ partial, const float* __restrict__ norms,
                                                           __half* __restrict__ y, long y_stride, long m, int out, int k_splits,
@@ -558,6 +594,31 @@ __global__ void __launch_bounds__(256) gemm_finish_kernel(const float* __restric
         float acc = 0.f;
         for (int z = 0; z < k_splits; ++z) acc += partial[static_cast<long>(z) * n + i];
         y[(i / out) * y_stride + i % out] = __float2half_rn(acc * (__ldg(norms + i % out) * inv_scale));
+    }
+}
+
+// The split-K finish of a group: blockIdx.y = matrix (matrices without a split have nothing to finish).
+struct FinishGroupArgs {
+    const float* partial[4];
+    const float* norms[4];
+    __half* y[4];
+    long y_stride[4];
+    int out[4], k_splits[4];
+    float inv_scale[4];
+};
+__global__ void __launch_bounds__(256) gemm_finish_group_kernel(const FinishGroupArgs g, long m) {
+    pdl_wait_release();
+    const int i = blockIdx.y;
+    const int k_splits = g.k_splits[i], out = g.out[i];
+    if (k_splits <= 1) return;
+    const float* __restrict__ partial = g.partial[i];
+    const float* __restrict__ norms = g.norms[i];
+    __half* __restrict__ y = g.y[i];
+    const long n = m * out;
+    for (long e = static_cast<long>(blockIdx.x) * blockDim.x + threadIdx.x; e < n; e += static_cast<long>(gridDim.x) * blockDim.x) {
+        float acc = 0.f;
+        for (int z = 0; z < k_splits; ++z) acc += partial[static_cast<long>(z) * n + e];
+        y[(e / out) * g.y_stride[i] + e % out] = __float2half_rn(acc * (__ldg(norms + e % out) * g.inv_scale[i]));
     }
 }
 
@@ -648,6 +709,85 @@ void launch_tq8_gemm(const uint8_t* codes, const float* norms, const float* tabl
         const unsigned int blocks = static_cast<unsigned int>(std::min<long>((n + 255) / 256, 148L * 8));
         launch_pdl(gemm_finish_kernel, dim3(blocks), dim3(256), 0, stream, a.partial, norms, y, y_stride, m, out, a.k_splits, a.inv_scale);
         TQ_CUDA(cudaGetLastError());
+    }
+}
+
+void launch_tq8_gemm_group(const GemmGroupItem* items, int n, const __half* x, long m, int sm_count, cudaStream_t stream) {
+    TQ_REQUIRE(items != nullptr && n >= 1 && n <= kMaxGemmGroup, "tq8_gemm group: 1..4 matrices");
+    TQ_REQUIRE(x != nullptr && m >= 1 && m < (1L << 30), "tq8_gemm group: bad number of activation rows");
+    const int in = items[0].in, n_planes = items[0].n_planes;
+    const uint32_t block = items[0].block;
+    TQ_REQUIRE(n_planes == 1 || n_planes == 2, "tq8_gemm: one or two rotation planes");
+    TQ_REQUIRE(gemm_supported(in), "tq8_gemm: in_features must be a multiple of 64");
+    TQ_REQUIRE(is_pow2(block) && block >= 32 && block <= 1024, "WHT block size must be a power of two in [32, 1024]");
+    TQ_REQUIRE(in % static_cast<int>(block) == 0, "in_features must be divisible by block_size");
+    GemmGroupArgs grp{};
+    RotateGroupArgs rot{};
+    FinishGroupArgs fin{};
+    grp.n = n;
+    grp.tile_start[0] = 0;
+    int max_splits = 1;
+    bool any_split = false;
+    for (int i = 0; i < n; ++i) {
+        const GemmGroupItem& it = items[i];
+        TQ_REQUIRE(it.codes && it.norms && it.table && it.y && it.scratch && it.out >= 1, "tq8_gemm group: NULL argument");
+        TQ_REQUIRE(it.in == in && it.n_planes == n_planes && it.block == block,
+                   "tq8_gemm group: the matrices must share in_features, the WHT block and the rotation mode");
+        GemmArgs& a = grp.m[i];
+        a.codes = it.codes; a.norms = it.norms; a.table = it.table; a.y = it.y; a.y_stride = it.out; a.status = it.status;
+        a.xrot = static_cast<__half*>(it.scratch);
+        a.out = it.out; a.in = in; a.m = static_cast<int>(m); a.n_planes = n_planes;
+        a.inv_scale = 1.0f / std::sqrt(static_cast<float>(in));
+        a.k_splits = gemm_k_splits(it.out, in, m, n_planes, sm_count);
+        a.partial = a.k_splits > 1 ? reinterpret_cast<float*>(static_cast<uint8_t*>(it.scratch) + xrot_bytes(in, m, n_planes)) : nullptr;
+        grp.tile_start[i + 1] = grp.tile_start[i] + (it.out + kTileRows - 1) / kTileRows;
+        max_splits = std::max(max_splits, a.k_splits);
+        any_split = any_split || a.k_splits > 1;
+        rot.xrot[i] = static_cast<__half*>(it.scratch);
+        rot.seed_p[i] = it.seed_p; rot.seed_r[i] = it.seed_r;
+        fin.partial[i] = a.partial; fin.norms[i] = it.norms; fin.y[i] = it.y; fin.y_stride[i] = it.out; fin.out[i] = it.out;
+        fin.k_splits[i] = a.k_splits; fin.inv_scale[i] = a.inv_scale;
+    }
+    for (int i = n; i < kMaxGemmGroup; ++i) grp.tile_start[i + 1] = grp.tile_start[n];
+    // 1. the rotations: one launch for the group where the wide kernel applies
+    const float inv_sqrt = 1.0f / std::sqrt(static_cast<float>(block));
+    const long wide_blocks = static_cast<long>(n_planes) * ((in + 255) / 256) * ((m + 7) / 8);
+    if (block <= 256 && reinterpret_cast<uintptr_t>(x) % 16 == 0 && wide_blocks < (1L << 31)) {
+        launch_pdl(rotate_rows_f16_wide_group_kernel, dim3(static_cast<unsigned int>(wide_blocks), static_cast<unsigned int>(n)), dim3(256), 0,
+                   stream, x, rot, in, m, n_planes, static_cast<int>(block), inv_sqrt);
+    } else {
+        const long n_warps = static_cast<long>(n_planes) * m * (in / static_cast<int>(block));
+        const unsigned int grid = static_cast<unsigned int>((n_warps + 3) / 4);
+        for (int i = 0; i < n; ++i) {
+#define TQ_ROT16G_CASE(EV)                                                                                                              \
+    case 32 * EV:                                                                                                                       \
+        launch_pdl(rotate_rows_f16_kernel<EV>, dim3(grid), dim3(128), 0, stream, x, rot.xrot[i], in, m, n_planes, rot.seed_p[i], rot.seed_r[i], \
+                   inv_sqrt);                                                                                                           \
+        break;
+            switch (block) {
+                TQ_ROT16G_CASE(1) TQ_ROT16G_CASE(2) TQ_ROT16G_CASE(4) TQ_ROT16G_CASE(8) TQ_ROT16G_CASE(16) TQ_ROT16G_CASE(32)
+                default: throw Error("unsupported WHT block size");
+            }
+#undef TQ_ROT16G_CASE
+        }
+    }
+    // 2. the GEMMs
+    static bool configured[64] = {false};
+    int dev = 0;
+    TQ_CUDA(cudaGetDevice(&dev));
+    if (dev >= 64 || !configured[dev]) {
+        TQ_CUDA(cudaFuncSetAttribute(tq8_gemm_group_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kGemmSmemBytes)));
+        if (dev < 64) configured[dev] = true;
+    }
+    const dim3 grid(static_cast<unsigned int>(grp.tile_start[n]), static_cast<unsigned int>((m + kTileTok - 1) / kTileTok),
+                    static_cast<unsigned int>(max_splits));
+    launch_pdl(tq8_gemm_group_kernel, grid, dim3(kGemmThreads), kGemmSmemBytes, stream, grp);
+    // 3. the split-K sums
+    if (any_split) {
+        long biggest = 0;
+        for (int i = 0; i < n; ++i) if (fin.k_splits[i] > 1) biggest = std::max<long>(biggest, m * fin.out[i]);
+        const unsigned int blocks = static_cast<unsigned int>(std::min<long>((biggest + 255) / 256, 148L * 8));
+        launch_pdl(gemm_finish_group_kernel, dim3(blocks, static_cast<unsigned int>(n)), dim3(256), 0, stream, fin, m);
     }
 }
 

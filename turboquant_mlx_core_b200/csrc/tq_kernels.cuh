@@ -120,6 +120,22 @@ size_t gemm_scratch_bytes(int out, int in, long m, int n_planes, int sm_count);
 void launch_tq8_gemm(const uint8_t* codes, const float* norms, const float* table, const __half* x, __half* y, int out,
                      int in, long m, uint32_t block, int n_planes, uint32_t seed_p, uint32_t seed_r, void* scratch,
                      unsigned int* status, int sm_count, cudaStream_t stream, long y_stride = 0);
+// Several matrices against the same activation rows in one rotation launch, one GEMM launch and one split-K finish:
+// y of matrix i = its own [m, out_i] buffer.  The matrices share in_features, the WHT block and the rotation mode; each
+// brings its own scratch (gemm_scratch_bytes for its own shape) and status word.
+struct GemmGroupItem {
+    const uint8_t* codes;
+    const float* norms;
+    const float* table;
+    __half* y;
+    int out, in;
+    uint32_t block;
+    int n_planes;
+    uint32_t seed_p, seed_r;
+    void* scratch;
+    unsigned int* status;
+};
+void launch_tq8_gemm_group(const GemmGroupItem* items, int n, const __half* x, long m, int sm_count, cudaStream_t stream);
 
 // tq_quantize.cu — bit-exact weight quantiser.  derive_seeds hashes the sampled bytes
 // of the fp32 weight (synchronises the stream).  launch_quantize_weight: cb_p / cb_r are
