@@ -141,9 +141,14 @@ def test_library_is_standalone():
     """The product library must not depend on torch, MLX or the checker libraries."""
     import subprocess
     from turboquant_mlx_core_b200 import LIB_PATH
-    out = subprocess.run(["ldd", LIB_PATH], capture_output=True, text=True).stdout
+    r = subprocess.run(["ldd", LIB_PATH], capture_output=True, text=True)
+    assert r.returncode == 0, r.stderr
+    # the NAMES of the dependencies (the left-hand side of "name => path"): a directory on the way to a system library
+    # may be called anything
+    names = [os.path.basename(line.split()[0]) for line in r.stdout.splitlines() if line.strip()]
+    assert names, r.stdout
     for banned in ("torch", "mlx", "tq_oracle", "tq_ref", "c10"):
-        assert banned not in out
+        assert not any(banned in n for n in names), names
 
 
 def test_headers_are_plain_c(tmp_path):
