@@ -175,7 +175,8 @@ def test_linear_widest_layers_match_oracle(tq, oracle, cols):
     lin.close()
 
 
-@pytest.mark.parametrize("cols,shared", [(5120, True), (2560, True), (1280, True), (13824, True), (6912, False), (3456, True), (5120, False)])
+@pytest.mark.parametrize("cols,shared", [(5120, True), (2560, True), (1280, True), (13824, True), (6912, False), (3456, True), (5120, False),
+                                         (4608, True), (6144, False), (4352, True)])
 def test_linear_chunked_columns_match_oracle(tq, oracle, cols, shared):
     """Input widths above 4096 columns whose last 4096-column chunk would be mostly empty (the Qwen2.5-32B shapes:
     hidden 5120 and its shards, intermediate 27648 / 2 and / 4) run with narrower chunks and several row tiles per

@@ -894,8 +894,8 @@ size_t align256(size_t v) { return (v + 255) & ~static_cast<size_t>(255); }
 // Warps that share one 16-row tile (a power of two up to 16); a chunk is that many 256-column slices, and
 // the 16 / wpt row tiles of a unit run side by side.  Up to 4096 columns: the fewest warps that cover the
 // row (one chunk).  Above: 16 warps per tile unless the last chunk would leave more than 15 % of the warps'
-// slices empty (5120 columns = 20 slices: 16 + 4, i.e. 62 %); then the widest tile that fills its chunks to
-// 95 % with at most 8 chunks (5120: 4 warps, five chunks of 1024 columns), if there is one.
+// slices empty (5120 columns = 20 slices: 16 + 4, i.e. 62 %); then the split with at most 8 chunks that leaves the
+// fewest slices empty (5120: 4 warps, five chunks of 1024 columns; 4608: 4 warps, 90 %; 6144: 8 warps, 100 %).
 int warps_per_tile(int in) {
     const int slices = (in + kSlice - 1) / kSlice;
     if (in <= kWarps * kSlice) {
@@ -905,9 +905,11 @@ int warps_per_tile(int in) {
     }
     auto fill = [&](int w) { return static_cast<double>(slices) / (static_cast<double>((slices + w - 1) / w) * w); };
     if (fill(kWarps) >= 0.85) return kWarps;
+    // otherwise the split (at most 8 chunks) that leaves the fewest slices empty; the wider one when two are close
+    int best = kWarps;
     for (int w = kWarps / 2; w >= 1; w >>= 1)
-        if (fill(w) >= 0.95 && (slices + w - 1) / w <= 8) return w;
-    return kWarps;
+        if ((slices + w - 1) / w <= 8 && fill(w) > fill(best) + 0.02) best = w;
+    return best;
 }
 int chunk_columns(int in) { return warps_per_tile(in) * kSlice; }
 
