@@ -53,6 +53,11 @@ def test_version_and_null_safety(lib):
     assert lib.tq_kv_cache_get_keys_fp16(None, 0, 0, 1) is None
     assert lib.tq_kv_cache_attention(None, 0, None, 0, 1) is None
     lib.tq_kv_cache_append(None, 0, None, None)
+    # the tensor-level entry points refuse NULL arguments with a message instead of touching the device
+    assert lib.tq_linear_forward_group(None, 3, None, 1, None, None) != 0
+    assert b"NULL" in lib.tq_last_error()
+    assert lib.tq_rope_qk_f16(None, None, None, 1, 1, 1, 128, 1e6, None) != 0
+    assert lib.tq_exchange_sum_f16_rmsnorm(None, 1, 0, 1, 8, None, None, None, None, 1e-6, None) != 0
 
 
 def test_model_handle(lib):
